@@ -1,0 +1,226 @@
+#!/usr/bin/env python
+"""Headline benchmark: 1B-config training tokens/s over full windows (inner steps + compress +
+gather + outer step), device-timed, max over ranks.
+
+    python bench.py --gpus N --steps K --warmup W            (N>1: launched through torchrun)
+    python bench.py --impl reference ...                      (the unmodified reference, same window)
+
+One *step* is one window of the benchmark configuration: ``accum`` micro-batches of
+``micro_batch x seq_len`` uniform-random tokens per GPU (forward + backward, fp32 gradient
+accumulation), one clipped AdamW inner step, the pseudo-gradient compression (error feedback,
+chunk-64 DCT, top-32, 12-bit packing), the gather of 8 peers' payloads and the fused
+unpack/clip/mean/inverse-DCT/outer update.  Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="1B")
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--accum", type=int, default=4)
+    ap.add_argument("--peers", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=32)
+    ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
+    ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while timing."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_ours(a):
+    import torch.distributed as dist
+    from templar_b200.models.llama import PRESETS, build_model
+    from templar_b200.ops import functional as OF, native
+    from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+    from templar_b200.parallel import symmetric
+
+    rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    heap = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        heap = symmetric.SymmetricHeap.create(dev, rank, world)
+    if a.gemm:
+        OF.set_gemm_backend(a.gemm)
+    args = PRESETS[a.model]
+    model = build_model(args, device=dev, dtype=torch.bfloat16, seed=0)
+    cfg = EngineConfig(topk=a.topk, use_dct=True, outer_update=a.outer_update, max_peers=a.peers)
+    eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
+    L = eng.layout
+    B, S, A = a.micro_batch, a.seq_len, a.accum
+    g = torch.Generator().manual_seed(1234 + rank)
+    # synthetic data: a pool of pinned host batches (uniform-random token ids)
+    n_pool = A * 2
+    host_tokens = [torch.randint(0, args.vocab_size, (B, S + 1), generator=g).pin_memory() for _ in range(n_pool)]
+    dev_tokens = [t.to(dev) for t in host_tokens]
+    # synthetic peers 1..P-1: seeded payloads in pinned host memory (flat wire format of this layout)
+    hosted = [j for j in range(1, a.peers) if j % world == rank]
+    host_payload = {}
+    from templar_b200.utils.synthetic import synthetic_payload
+    for j in hosted:
+        idx, val = synthetic_payload(L, 99 + j, device=dev)
+        host_payload[j] = (idx.cpu().pin_memory(), val.cpu().pin_memory())
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def window(e2e: bool, w: int):
+        eng.snapshot()
+        losses = []
+        for m in range(A):
+            if e2e:
+                tok = host_tokens[(w * A + m) % n_pool].to(dev, non_blocking=True)
+            else:
+                tok = dev_tokens[(w * A + m) % n_pool]
+            losses.append(eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0 / A))
+        eng.optimizer_step()
+        own_ptrs = None
+        if heap is not None:
+            own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
+        eng.compress(own_slot_ptrs=own_ptrs)
+        for j in hosted:
+            eng.load_peer_payload(j // world, host_payload[j])
+        if world > 1:
+            eng._barrier()
+        eng.outer_step(a.peers)
+        loss = torch.stack(losses).mean()
+        if e2e:
+            loss_host.copy_(loss.reshape(1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(loss_host[0])
+        return loss
+
+    def timed(e2e: bool, steps: int, warmup: int):
+        for w in range(warmup):
+            window(e2e, w)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local); sampler.start()
+        l0 = native.launch_count
+        t0w = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for w in range(steps):
+            window(e2e, warmup + w)
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        wall = time.perf_counter() - t0w
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms if not e2e else wall * 1e3], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), native.launch_count - l0, clocks
+
+    ms_total, launches, clocks = timed(False, a.steps, a.warmup)
+    tokens_per_step = B * S * A * world
+    value = tokens_per_step * a.steps / (ms_total / 1e3)
+    e2e = None
+    if not a.no_e2e:
+        ms_e2e, _, _ = timed(True, a.steps, 1)
+        e2e = {"value": tokens_per_step * a.steps / (ms_e2e / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(A * B * (S + 1) * 8 + sum(i.numel() + v.numel() * 4 for i, v in host_payload.values())),
+               "d2h_bytes_per_step": 4}
+    status = eng.check_status()
+    if rank == 0:
+        mfu = value / world * args.flops_per_token(S) / 1e12
+        out = {"metric": "1B tokens/s (device-timed, max over ranks); window = inner step + compress + gather + outer step",
+               "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+               "ms_per_step": ms_total / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights, seeded synthetic peer payloads",
+               "impl": "ours", "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+               "model_tflops_per_gpu": mfu, "kernel_status": status, "gemm_backend": OF.gemm_backend(),
+               "config": {"model": f"llama-{a.model} (d{args.dim} L{args.n_layers} H{args.n_heads} F{args.ffn_hidden} V{args.vocab_size})",
+                          "global_batch": B * A * world, "micro_batch": B, "accum": A, "seq_len": S,
+                          "parallelism": f"zero-shard{world}" if world > 1 else "single",
+                          "peers": a.peers, "topk": a.topk, "use_dct": True, "outer_update": a.outer_update,
+                          "payload_values": "fp32", "l2": "inputs larger than L2 (2.4 GB bf16 weights, 134 MB activations per layer)"}}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(a):
+    try:
+        from baseline import reference_bench
+    except Exception as e:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline harness import failed: {e}"[:300]}))
+        return
+    reference_bench.main(a)
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

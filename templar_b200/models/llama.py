@@ -1,0 +1,255 @@
+"""LLaMA-architecture decoder with the parameter names of the reference's model.
+
+State-dict keys match the torchtitan ``Transformer`` the reference trains
+(models/llama3/model/model.py:20-436): ``tok_embeddings.weight``,
+``layers.{i}.attention.{wq,wk,wv,wo}.weight``, ``layers.{i}.feed_forward.{w1,w2,w3}.weight``,
+``layers.{i}.{attention_norm,ffn_norm}.weight``, ``norm.weight``, ``output.weight`` and the
+persistent complex buffer ``freqs_cis`` — so DCP checkpoints are interchangeable.
+
+Execution differs from the reference: Q/K/V are one GEMM against the packed
+``[wq; wk; wv]`` rows and gate/up one GEMM against ``[w1; w3]`` (the flat parameter store
+lays those tensors out adjacently, so the packed matrices are views, not copies), RoPE is
+applied in place on the packed projection, SwiGLU reads the packed projection, and the
+loss kernel emits the logit gradient during the forward pass.  All of these go through
+:mod:`templar_b200.ops.functional`, i.e. hand-written kernels on a B200 and PyTorch on CPU.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as OF
+
+
+@dataclass
+class ModelArgs:
+    dim: int = 2048
+    n_layers: int = 16
+    n_heads: int = 16
+    n_kv_heads: int | None = None
+    vocab_size: int = 32000
+    intermediate_size: int | None = None
+    multiple_of: int = 256
+    ffn_dim_multiplier: float | None = None
+    norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    max_seq_len: int = 2048
+    depth_init: bool = True
+    tie_embeddings: bool = False
+
+    @property
+    def kv_heads(self) -> int:
+        return self.n_kv_heads or self.n_heads
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+    @property
+    def ffn_hidden(self) -> int:
+        if self.intermediate_size is not None:
+            return int(self.intermediate_size)
+        hidden = int(2 * (4 * self.dim) / 3)
+        if self.ffn_dim_multiplier is not None:
+            hidden = int(self.ffn_dim_multiplier * hidden)
+        return self.multiple_of * ((hidden + self.multiple_of - 1) // self.multiple_of)
+
+    def num_params(self) -> int:
+        d, f, v, kv = self.dim, self.ffn_hidden, self.vocab_size, self.kv_heads * self.head_dim
+        per_layer = 2 * d * d + 2 * kv * d + 3 * d * f + 2 * d
+        return self.n_layers * per_layer + v * d * (1 if self.tie_embeddings else 2) + d
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Forward+backward model FLOPs per token (6 N for the matmuls + causal attention)."""
+        d, f, v, kv = self.dim, self.ffn_hidden, self.vocab_size, self.kv_heads * self.head_dim
+        mm = self.n_layers * (2 * d * d + 2 * kv * d + 3 * d * f) + v * d
+        attn = self.n_layers * 2 * seq_len * d / 2  # QK^T and PV, causal half
+        return 6.0 * mm + 6.0 * attn
+
+
+# Named presets.  "150M" and "1B" are the benchmark configurations; the llama3 sizes follow the
+# public architecture tables.
+PRESETS: dict[str, ModelArgs] = {
+    "tiny": ModelArgs(dim=128, n_layers=2, n_heads=4, vocab_size=512, intermediate_size=256, max_seq_len=128),
+    "150M": ModelArgs(dim=768, n_layers=12, n_heads=12, vocab_size=32000, intermediate_size=3072),
+    "1B": ModelArgs(dim=2048, n_layers=16, n_heads=16, vocab_size=32000, intermediate_size=8192),
+    "8B": ModelArgs(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256, intermediate_size=14336,
+                    rope_theta=500000.0),
+    "18B-tp": ModelArgs(dim=8192, n_layers=16, n_heads=64, n_kv_heads=8, vocab_size=128256,
+                        intermediate_size=28672, rope_theta=500000.0),
+    "70B": ModelArgs(dim=8192, n_layers=80, n_heads=64, n_kv_heads=8, vocab_size=128256, intermediate_size=28672,
+                     rope_theta=500000.0),
+}
+
+
+class _Weight(nn.Module):
+    """A bias-free linear layer's parameter holder (keeps the ``.weight`` FQN)."""
+
+    def __init__(self, out_features: int, in_features: int):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+
+    def forward(self, x):
+        return OF.linear(x, self.weight)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        return OF.rmsnorm(x, self.weight, self.eps)
+
+
+class Attention(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.n_heads, self.n_kv, self.hd = args.n_heads, args.kv_heads, args.head_dim
+        self.wq = _Weight(args.n_heads * self.hd, args.dim)
+        self.wk = _Weight(self.n_kv * self.hd, args.dim)
+        self.wv = _Weight(self.n_kv * self.hd, args.dim)
+        self.wo = _Weight(args.dim, args.n_heads * self.hd)
+        self.packed = None  # (weight view, main_grad view) of [wq; wk; wv] set by the flat store
+
+    def forward(self, x, cos, sin):
+        B, S, _ = x.shape
+        if self.packed is not None:
+            qkv = OF.linear(x, self.packed[0], self.packed[1])
+        else:
+            qkv = OF.linear(x, torch.cat((self.wq.weight, self.wk.weight, self.wv.weight), dim=0))
+        qkv = OF.rope(qkv, cos, sin, self.n_heads + self.n_kv, self.hd)
+        nq, nk = self.n_heads * self.hd, self.n_kv * self.hd
+        q = qkv[..., :nq].view(B, S, self.n_heads, self.hd)
+        k = qkv[..., nq:nq + nk].view(B, S, self.n_kv, self.hd)
+        v = qkv[..., nq + nk:].view(B, S, self.n_kv, self.hd)
+        o = OF.attention(q, k, v).reshape(B, S, nq)
+        return self.wo(o)
+
+
+class FeedForward(nn.Module):
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.w1 = _Weight(args.ffn_hidden, args.dim)
+        self.w2 = _Weight(args.dim, args.ffn_hidden)
+        self.w3 = _Weight(args.ffn_hidden, args.dim)
+        self.packed = None  # [w1; w3]
+
+    def forward(self, x):
+        if self.packed is not None:
+            h = OF.linear(x, self.packed[0], self.packed[1])
+        else:
+            h = OF.linear(x, torch.cat((self.w1.weight, self.w3.weight), dim=0))
+        return self.w2(OF.swiglu(h))
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, layer_id: int, args: ModelArgs):
+        super().__init__()
+        self.attention = Attention(args)
+        self.feed_forward = FeedForward(args)
+        self.attention_norm = RMSNorm(args.dim, args.norm_eps)
+        self.ffn_norm = RMSNorm(args.dim, args.norm_eps)
+        self.layer_id = layer_id
+        self.weight_init_std = (0.02 / (2 * (layer_id + 1)) ** 0.5 if args.depth_init
+                                else 0.02 / (2 * args.n_layers) ** 0.5)
+
+    def forward(self, x, cos, sin):
+        h = x + self.attention(self.attention_norm(x), cos, sin)
+        return h + self.feed_forward(self.ffn_norm(h))
+
+    def init_weights(self, generator=None):
+        for norm in (self.attention_norm, self.ffn_norm):
+            nn.init.ones_(norm.weight)
+        for lin in (self.attention.wq, self.attention.wk, self.attention.wv, self.feed_forward.w1):
+            nn.init.trunc_normal_(lin.weight, mean=0.0, std=0.02, generator=generator)
+        for lin in (self.attention.wo, self.feed_forward.w2, self.feed_forward.w3):
+            nn.init.trunc_normal_(lin.weight, mean=0.0, std=self.weight_init_std, generator=generator)
+
+
+class LlamaModel(nn.Module):
+    """``forward(tokens, labels=None)`` returns logits; :meth:`loss` returns the mean CE."""
+
+    def __init__(self, args: ModelArgs):
+        super().__init__()
+        self.args = args
+        self.model_args = args  # name used by torchtitan-style callers
+        self.tok_embeddings = nn.Embedding(args.vocab_size, args.dim)
+        self.layers = nn.ModuleDict({str(i): TransformerBlock(i, args) for i in range(args.n_layers)})
+        self.norm = RMSNorm(args.dim, args.norm_eps)
+        self.output = _Weight(args.vocab_size, args.dim)
+        if args.tie_embeddings:
+            self.output.weight = self.tok_embeddings.weight
+        self.register_buffer("freqs_cis", self._freqs_cis(), persistent=True)
+        self._rope_cache: dict = {}
+        self.activation_checkpointing = False
+
+    # -- rotary tables --------------------------------------------------------------------
+    def _freqs_cis(self) -> torch.Tensor:
+        cos, sin = OF.rope_tables(self.args.max_seq_len, self.args.head_dim, self.args.rope_theta)
+        return torch.complex(cos, sin)
+
+    def _rope(self, device):
+        key = str(device)
+        if key not in self._rope_cache:
+            cos, sin = OF.rope_tables(self.args.max_seq_len, self.args.head_dim, self.args.rope_theta, device)
+            self._rope_cache[key] = (cos.contiguous(), sin.contiguous())
+        return self._rope_cache[key]
+
+    # -- init ------------------------------------------------------------------------------
+    @torch.no_grad()
+    def init_weights(self, seed: int | None = None, buffer_device=None):
+        gen = None
+        dev = self.tok_embeddings.weight.device
+        if seed is not None:
+            gen = torch.Generator(device=dev)
+            gen.manual_seed(seed)
+        self.tok_embeddings.weight.normal_(generator=gen)
+        for layer in self.layers.values():
+            layer.init_weights(gen)
+        nn.init.ones_(self.norm.weight)
+        if not self.args.tie_embeddings:
+            std = self.args.dim ** -0.5
+            nn.init.trunc_normal_(self.output.weight, mean=0.0, std=std, a=-3 * std, b=3 * std, generator=gen)
+        self.freqs_cis = self._freqs_cis().to(buffer_device or self.freqs_cis.device)
+
+    # -- forward ---------------------------------------------------------------------------
+    def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
+        cos, sin = self._rope(tokens.device)
+        h = OF.embedding(tokens, self.tok_embeddings.weight)
+        for layer in self.layers.values():
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                h = checkpoint(layer, h, cos, sin, use_reentrant=False)
+            else:
+                h = layer(h, cos, sin)
+        return self.norm(h)
+
+    def forward(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
+        return self.output(self.hidden_states(tokens))
+
+    def loss(self, tokens: torch.Tensor, labels: torch.Tensor, grad_scale: float = 1.0,
+             ignore_index: int = -100) -> torch.Tensor:
+        """Mean cross entropy over ``labels != ignore_index``.  The gradient that flows back is
+        ``grad_scale`` times the gradient of this mean (see ``ops.functional.cross_entropy``)."""
+        logits = self.forward(tokens)
+        return OF.cross_entropy(logits, labels, grad_scale, ignore_index)
+
+
+def build_model(args: ModelArgs | str, device=None, dtype=None, seed: int | None = 42) -> LlamaModel:
+    if isinstance(args, str):
+        args = PRESETS[args]
+    with torch.device(device or "cpu"):
+        model = LlamaModel(args)
+    if dtype is not None:
+        fc = model.freqs_cis
+        model = model.to(dtype)
+        model.freqs_cis = fc  # complex buffer keeps its dtype
+    if seed is not None:
+        model.init_weights(seed)
+    return model

@@ -1,0 +1,584 @@
+// Per-window compression and aggregation kernels (sm_100a).
+//
+//   tplr_compress_chunks   error-feedback update  e <- gamma*e + delta,  2-D chunk DCT,
+//                          per-chunk magnitude top-k, 12-bit index packing, value
+//                          write-out, and the error-feedback residual
+//                          e <- e - iDCT(selected), all in ONE pass over the dense tensors
+//                          (reads theta0/theta/e once, writes e once).
+//   tplr_peer_sumsq / tplr_clip_factors
+//                          per-(peer, tensor) L2 norms of the received values and the
+//                          median-norm clip factors, without any host round trip.
+//   tplr_aggregate_apply   for every chunk: pull each peer's packed (index, value)
+//                          lists (the pointers may be peer-GPU memory mapped over
+//                          NVLink), unpack, scale by the clip factor, mean over the
+//                          contributors of each coefficient, inverse chunk DCT and the
+//                          outer update theta <- theta0 - lr * g (or its sign form),
+//                          writing the fp32 master and the bf16 compute copy.
+//
+// One CTA owns one chunk at a time (persistent grid-stride loop); a launch covers
+// every tensor of the model through a descriptor table, so a window costs a handful
+// of launches instead of dozens per tensor.
+//
+// Semantics follow the reference's src/tplr/compress.py:225-292 (chunking + DCT),
+// :385-481 (top-k, scatter-mean over contributors), :526-556 (median-norm clip) and
+// src/tplr/neurons.py:138-173 (error feedback), :342-450 (outer step).
+#include "common.cuh"
+
+#define NT 256
+#define LD 64
+
+// acc[a][b] = sum_k At[k][4*ty+a] * B[k][4*tx+b]   (ty = tid/16, tx = tid%16)
+static __device__ __forceinline__ void mm_tile(const float* __restrict__ At,
+                                               const float* __restrict__ B, int K,
+                                               float acc[4][4]) {
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const float4* a4 = reinterpret_cast<const float4*>(At) + ty;
+  const float4* b4 = reinterpret_cast<const float4*>(B) + tx;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+  for (int k = 0; k < K; ++k) {
+    const float4 a = a4[k * (LD / 4)];
+    const float4 b = b4[k * (LD / 4)];
+    const float av[4] = {a.x, a.y, a.z, a.w};
+    const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+  }
+}
+
+static __device__ __forceinline__ void store_tile(float* __restrict__ C, const float acc[4][4]) {
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    reinterpret_cast<float4*>(C + (4 * ty + i) * LD)[tx] =
+        make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+}
+
+static __device__ __forceinline__ int find_desc(const TplrParamDesc* __restrict__ descs, int n, int c) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (__ldg(&descs[mid].chunk_begin) <= c) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// Loads the n x n DCT matrix F (row-major, ld = n) zero-padded into F[64][64] and its
+// transpose into Ft[64][64].
+static __device__ __forceinline__ void load_basis(const float* __restrict__ g, int n,
+                                                  float* F, float* Ft) {
+  for (int i = threadIdx.x; i < TPLR_TILE_ELEMS; i += NT) {
+    int r = i >> 6, c = i & 63;
+    float v = (r < n && c < n) ? __ldg(g + r * n + c) : 0.f;
+    F[i] = v;
+    Ft[c * LD + r] = v;
+  }
+}
+
+struct CompressArgs {
+  const TplrParamDesc* descs;
+  const float* basis;
+  float* ef;
+  const float* theta0;
+  const float* theta;
+  uint8_t* idx_out;
+  float* val_out;
+  unsigned int* status;
+  int n_desc, total_chunks;
+  float gamma;
+  int use_dct, delta_mode, null_round, write_residual, distinct;
+};
+
+__global__ void __launch_bounds__(NT, 2) compress_kernel(const CompressArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  float* X = smem;
+  float* Y = X + TPLR_TILE_ELEMS;
+  float* U = Y + TPLR_TILE_ELEMS;
+  float* Fh = U + TPLR_TILE_ELEMS;
+  float* Fht = Fh + TPLR_TILE_ELEMS;
+  float* Fw = a.distinct ? Fht + TPLR_TILE_ELEMS : Fh;
+  float* Fwt = a.distinct ? Fw + TPLR_TILE_ELEMS : Fht;
+  __shared__ int s_hist[256];
+  __shared__ int s_wsum[8];
+  __shared__ int s_bin, s_krem;
+  __shared__ int s_sel_idx[TPLR_TILE];
+  __shared__ float s_sel_val[TPLR_TILE];
+
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int ty = tid >> 4, tx = tid & 15;
+  int cur_fh = -1, cur_fw = -1;
+
+  for (int c = blockIdx.x; c < a.total_chunks; c += gridDim.x) {
+    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, c)];
+    const int h = d.h, w = d.w, n = h * w, k = d.k;
+    const int cl = c - d.chunk_begin;
+    const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
+    const long long base = d.elem_off + (long long)cy * h * d.cols + (long long)cx * w;
+    __syncthreads();  // previous chunk's smem fully consumed
+    if (a.use_dct && (d.fh_off != cur_fh || d.fw_off != cur_fw)) {
+      load_basis(a.basis + d.fh_off, h, Fh, Fht);
+      if (a.distinct) load_basis(a.basis + d.fw_off, w, Fw, Fwt);
+      cur_fh = d.fh_off;
+      cur_fw = d.fw_off;
+    }
+    // ---- X = gamma*e + delta, zero padded to 64x64 -------------------------------
+    const bool vec = (w == 64) && ((d.cols & 3) == 0) && ((base & 3) == 0);
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < h && !a.null_round) {
+          const long long g = base + (long long)r * d.cols + 4 * tx;
+          const float4 e = *reinterpret_cast<const float4*>(a.ef + g);
+          float4 dl = *reinterpret_cast<const float4*>(a.theta0 + g);
+          if (a.delta_mode) {
+            const float4 t = *reinterpret_cast<const float4*>(a.theta + g);
+            dl.x -= t.x; dl.y -= t.y; dl.z -= t.z; dl.w -= t.w;
+          }
+          x.x = fmaf(a.gamma, e.x, dl.x); x.y = fmaf(a.gamma, e.y, dl.y);
+          x.z = fmaf(a.gamma, e.z, dl.z); x.w = fmaf(a.gamma, e.w, dl.w);
+        }
+        reinterpret_cast<float4*>(X + r * LD)[tx] = x;
+      }
+    } else {
+      for (int i = tid; i < TPLR_TILE_ELEMS; i += NT) {
+        const int r = i >> 6, cc = i & 63;
+        float x = 0.f;
+        if (r < h && cc < w && !a.null_round) {
+          const long long g = base + (long long)r * d.cols + cc;
+          float dl = a.theta0[g];
+          if (a.delta_mode) dl -= a.theta[g];
+          x = fmaf(a.gamma, a.ef[g], dl);
+        }
+        X[i] = x;
+      }
+    }
+    __syncthreads();
+    // ---- Y = F_h X F_w^T ------------------------------------------------------------
+    const float* Ysel = X;
+    if (a.use_dct) {
+      float acc[4][4];
+      mm_tile(X, Fht, h, acc);   // U[c][b] = sum_r X[r][c] F_h[b][r]
+      store_tile(U, acc);
+      __syncthreads();
+      mm_tile(U, Fwt, w, acc);   // Y[b][d] = sum_c U[c][b] F_w[d][c]
+      store_tile(Y, acc);
+      __syncthreads();
+      Ysel = Y;
+    }
+    // ---- radix select of the k largest |Y| over the n valid coefficients -----------
+    unsigned int key[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = i * NT + tid;
+      key[i] = 0u;
+      if (e < n) key[i] = __float_as_uint(Ysel[(e / w) * LD + (e % w)]) & 0x7fffffffu;
+    }
+    unsigned int prefix = 0u, mask = 0u;
+    int krem = k;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      s_hist[tid] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (i * NT + tid < n && (key[i] & mask) == prefix) atomicAdd(&s_hist[(key[i] >> shift) & 255u], 1);
+      __syncthreads();
+      if (wid == 0) {
+        const int hi = 255 - 8 * lane;
+        int s = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += s_hist[hi - j];
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const int excl = incl - s;
+        if (excl < krem && krem <= incl) {
+          int run = excl;
+          for (int j = 0; j < 8; ++j) {
+            const int cnt = s_hist[hi - j];
+            if (run + cnt >= krem) { s_bin = hi - j; s_krem = krem - run; break; }
+            run += cnt;
+          }
+        }
+      }
+      __syncthreads();
+      prefix |= ((unsigned int)s_bin) << shift;
+      mask |= 255u << shift;
+      krem = s_krem;
+      __syncthreads();
+    }
+    // ---- ordered compaction (thread-major order): all keys above the threshold, then the
+    //      first krem keys equal to it; deterministic for a given input ------------------
+    int g = 0, q = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i * NT + tid < n) { g += key[i] > prefix; q += key[i] == prefix; }
+    int packed = g | (q << 16);
+    int incl = packed;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_wsum[wid] = incl;
+    __syncthreads();
+    int woff = 0;
+    for (int j = 0; j < wid; ++j) woff += s_wsum[j];
+    int excl = incl - packed + woff;
+    int gb = excl & 0xffff, qb = excl >> 16;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = i * NT + tid;
+      if (e < n) {
+        int pos = -1;
+        if (key[i] > prefix) { pos = gb + min(qb, krem); ++gb; }
+        else if (key[i] == prefix) { if (qb < krem) pos = gb + qb; ++qb; }
+        if (pos >= 0 && pos < TPLR_TILE) {
+          s_sel_idx[pos] = e;
+          s_sel_val[pos] = Ysel[(e / w) * LD + (e % w)];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- payload: 3 bytes per index pair, fp32 values ------------------------------
+    {
+      uint8_t* ip = a.idx_out + d.idx_off + (long long)cl * (k / 2) * 3;
+      float* vp = a.val_out + d.val_off + (long long)cl * k;
+      if (tid < k / 2) {
+        const int i0 = s_sel_idx[2 * tid], i1 = s_sel_idx[2 * tid + 1];
+        ip[3 * tid + 0] = (uint8_t)(i0 & 0xff);
+        ip[3 * tid + 1] = (uint8_t)(((i0 >> 8) & 0xf) | ((i1 & 0xf) << 4));
+        ip[3 * tid + 2] = (uint8_t)((i1 >> 4) & 0xff);
+      }
+      if (tid >= 64 && tid < 64 + k) vp[tid - 64] = s_sel_val[tid - 64];
+    }
+    // ---- error feedback residual -----------------------------------------------------
+    float acc[4][4];
+    if (a.write_residual && a.use_dct) {
+      // transmit = F_h^T S F_w with S the k selected coefficients:
+      //   Y[j][r] <- F_h[b_j][r],  U[j][l] <- v_j F_w[d_j][l],  out = Y^T U over j < k
+      for (int i = tid; i < k * LD; i += NT) {
+        const int j = i >> 6, r = i & 63;
+        const int e = s_sel_idx[j];
+        Y[i] = Fh[(e / w) * LD + r];
+        U[i] = s_sel_val[j] * Fw[(e % w) * LD + r];
+      }
+      __syncthreads();
+      mm_tile(Y, U, k, acc);
+    } else {
+      if (a.write_residual) {
+        if (tid < k) { const int e = s_sel_idx[tid]; X[(e / w) * LD + (e % w)] = 0.f; }
+        __syncthreads();
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * ty + i;
+      if (r >= h) continue;
+      const float4 x = reinterpret_cast<const float4*>(X + r * LD)[tx];
+      const float o[4] = {x.x - acc[i][0], x.y - acc[i][1], x.z - acc[i][2], x.w - acc[i][3]};
+      const long long g0 = base + (long long)r * d.cols + 4 * tx;
+      if (vec) {
+        *reinterpret_cast<float4*>(a.ef + g0) = make_float4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (4 * tx + j < w) a.ef[g0 + j] = o[j];
+      }
+    }
+  }
+}
+
+TPLR_API int tplr_compress_chunks(const void* descs, int n_desc, int total_chunks, const float* basis,
+                                  float* ef, const float* theta0, const float* theta,
+                                  uint8_t* idx_out, float* val_out, unsigned int* status,
+                                  float gamma, int use_dct, int delta_mode, int null_round,
+                                  int write_residual, int distinct, void* stream) {
+  if (total_chunks <= 0) return 0;
+  CompressArgs a;
+  a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.theta0 = theta0; a.theta = theta;
+  a.idx_out = idx_out; a.val_out = val_out; a.status = status; a.n_desc = n_desc;
+  a.total_chunks = total_chunks; a.gamma = gamma; a.use_dct = use_dct; a.delta_mode = delta_mode;
+  a.null_round = null_round; a.write_residual = write_residual; a.distinct = distinct;
+  const int smem = (distinct ? 7 : 5) * TPLR_TILE_ELEMS * (int)sizeof(float);
+  cudaError_t err = cudaFuncSetAttribute(compress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return (int)err;
+  int grid = tplr_sm_count() * (distinct ? 1 : 2);
+  if (grid > total_chunks) grid = total_chunks;
+  compress_kernel<<<grid, NT, smem, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// received-payload norms and clip factors
+// ------------------------------------------------------------------------------------- //
+struct PeerPtrs {
+  const uint8_t* idx[TPLR_MAX_PEERS];
+  const void* val[TPLR_MAX_PEERS];
+};
+
+// val_dtype: 0 fp32, 1 bf16, 2 uint8 codes with a per-(peer, tensor) table of
+// n_bins lookup entries followed by the shift.
+static __device__ __forceinline__ float load_val(const void* p, long long i, int val_dtype,
+                                                 const float* qt, int n_bins) {
+  if (val_dtype == 0) return reinterpret_cast<const float*>(p)[i];
+  if (val_dtype == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  const int code = reinterpret_cast<const uint8_t*>(p)[i];
+  return qt[min(code, n_bins - 1)] + qt[n_bins];
+}
+
+#define SUMSQ_SPLIT 8
+__global__ void __launch_bounds__(256) peer_sumsq_kernel(const TplrParamDesc* __restrict__ descs,
+                                                         PeerPtrs pp, int n_params, int val_dtype,
+                                                         const float* __restrict__ qtable, int n_bins,
+                                                         float* __restrict__ partial) {
+  __shared__ float red[32];
+  const TplrParamDesc d = descs[blockIdx.x];
+  const int peer = blockIdx.y, split = blockIdx.z;
+  const long long n = (long long)d.n_chunks * d.k;
+  const long long per = (n + SUMSQ_SPLIT - 1) / SUMSQ_SPLIT;
+  const long long lo = per * split, hi = min(n, lo + per);
+  const float* qt = qtable ? qtable + ((long long)peer * n_params + d.param_id) * (n_bins + 1) : nullptr;
+  float s = 0.f;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = load_val(pp.val[peer], d.val_off + i, val_dtype, qt, n_bins);
+    s = fmaf(v, v, s);
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partial[((long long)peer * n_params + d.param_id) * SUMSQ_SPLIT + split] = s;
+}
+
+TPLR_API int tplr_peer_sumsq(const void* descs, int n_desc, int n_params, int n_peers,
+                             const void* const* val_ptrs, int val_dtype, const float* qtable,
+                             int n_bins, float* partial, void* stream) {
+  if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
+  PeerPtrs pp;
+  for (int i = 0; i < n_peers; ++i) { pp.val[i] = val_ptrs[i]; pp.idx[i] = nullptr; }
+  dim3 grid(n_desc, n_peers, SUMSQ_SPLIT);
+  peer_sumsq_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const TplrParamDesc*)descs, pp, n_params,
+                                                             val_dtype, qtable, n_bins, partial);
+  return (int)cudaGetLastError();
+}
+
+// One thread per tensor: norms, lower median over peers, clip = min(1, med / (norm + 1e-8)).
+// A tensor with a non-finite norm from any peer is marked skipped (its update would be
+// non-finite and is dropped as a whole).
+__global__ void clip_factors_kernel(const float* __restrict__ partial, int n_params, int n_peers,
+                                    float* __restrict__ norms, float* __restrict__ clip,
+                                    float* __restrict__ median, int* __restrict__ skip,
+                                    unsigned int* status) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_params) return;
+  float nv[TPLR_MAX_PEERS];
+  bool bad = false;
+  for (int i = 0; i < n_peers; ++i) {
+    float s = 0.f;
+    const float* q = partial + ((long long)i * n_params + p) * SUMSQ_SPLIT;
+    for (int j = 0; j < SUMSQ_SPLIT; ++j) s += q[j];
+    const float nrm = sqrtf(s);
+    norms[(long long)i * n_params + p] = nrm;
+    nv[i] = nrm;
+    bad |= !isfinite(nrm);
+  }
+  for (int i = 1; i < n_peers; ++i) {  // insertion sort, n_peers <= 32
+    const float x = nv[i];
+    int j = i - 1;
+    while (j >= 0 && nv[j] > x) { nv[j + 1] = nv[j]; --j; }
+    nv[j + 1] = x;
+  }
+  const float med = nv[(n_peers - 1) / 2];
+  median[p] = med;
+  skip[p] = bad ? 1 : 0;
+  if (bad && status) atomicOr(status, TPLR_ST_NONFINITE);
+  for (int i = 0; i < n_peers; ++i) {
+    const float nrm = norms[(long long)i * n_params + p];
+    clip[(long long)i * n_params + p] = bad ? 0.f : fminf(1.f, med / (nrm + 1e-8f));
+  }
+}
+
+TPLR_API int tplr_clip_factors(const float* partial, int n_params, int n_peers, float* norms,
+                               float* clip, float* median, int* skip, unsigned int* status,
+                               void* stream) {
+  if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
+  clip_factors_kernel<<<(n_params + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+      partial, n_params, n_peers, norms, clip, median, skip, status);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// aggregate + inverse DCT + outer update
+// ------------------------------------------------------------------------------------- //
+struct AggArgs {
+  const TplrParamDesc* descs;
+  const float* basis;
+  const float* clip;        // [n_peers][n_params] or null
+  const int* skip;          // [n_params] or null
+  const float* qtable;      // see load_val
+  const float* theta0;
+  float* theta;
+  __nv_bfloat16* theta_bf16;
+  float* grad_out;
+  unsigned int* status;
+  int n_desc, total_chunks, n_peers, n_params, n_bins;
+  float lr, weight_decay;
+  int use_dct, update_mode, val_dtype, distinct;
+  PeerPtrs pp;
+};
+
+__global__ void __launch_bounds__(NT, 2) aggregate_kernel(const AggArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  float* S = smem;
+  float* V = S + TPLR_TILE_ELEMS;
+  int* Cnt = reinterpret_cast<int*>(V + TPLR_TILE_ELEMS);
+  float* Fh = reinterpret_cast<float*>(Cnt + TPLR_TILE_ELEMS);
+  float* Fw = a.distinct ? Fh + TPLR_TILE_ELEMS : Fh;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  int cur_fh = -1, cur_fw = -1;
+
+  for (int c = blockIdx.x; c < a.total_chunks; c += gridDim.x) {
+    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, c)];
+    const bool skipped = a.skip && a.skip[d.param_id];   // uniform per block
+    const int h = d.h, w = d.w, n = h * w, k = d.k;
+    const int cl = c - d.chunk_begin;
+    const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
+    const long long base = d.elem_off + (long long)cy * h * d.cols + (long long)cx * w;
+    __syncthreads();
+    if (a.use_dct && (d.fh_off != cur_fh || d.fw_off != cur_fw)) {
+      for (int i = tid; i < TPLR_TILE_ELEMS; i += NT) {
+        const int r = i >> 6, cc = i & 63;
+        Fh[i] = (r < h && cc < h) ? __ldg(a.basis + d.fh_off + r * h + cc) : 0.f;
+        if (a.distinct) Fw[i] = (r < w && cc < w) ? __ldg(a.basis + d.fw_off + r * w + cc) : 0.f;
+      }
+      cur_fh = d.fh_off;
+      cur_fw = d.fw_off;
+    }
+    for (int i = tid; i < TPLR_TILE_ELEMS; i += NT) { S[i] = 0.f; Cnt[i] = 0; }
+    __syncthreads();
+    // ---- pull + unpack + scale + scatter-add -----------------------------------------
+    const int pairs = k / 2;
+    for (int t = tid; t < (skipped ? 0 : a.n_peers * pairs); t += NT) {
+      const int peer = t / pairs, pr = t - peer * pairs;
+      const uint8_t* ip = a.pp.idx[peer] + d.idx_off + ((long long)cl * pairs + pr) * 3;
+      const unsigned b0 = ip[0], b1 = ip[1], b2 = ip[2];
+      const int i0 = (int)(b0 | ((b1 & 0xfu) << 8));
+      const int i1 = (int)(((b1 >> 4) & 0xfu) | (b2 << 4));
+      const long long vo = d.val_off + (long long)cl * k + 2 * pr;
+      const float* qt = a.qtable ? a.qtable + ((long long)peer * a.n_params + d.param_id) * (a.n_bins + 1) : nullptr;
+      const float sc = a.clip ? a.clip[(long long)peer * a.n_params + d.param_id] : 1.f;
+      const float v0 = load_val(a.pp.val[peer], vo, a.val_dtype, qt, a.n_bins) * sc;
+      const float v1 = load_val(a.pp.val[peer], vo + 1, a.val_dtype, qt, a.n_bins) * sc;
+      if (i0 < n) { const int p = (i0 / w) * LD + (i0 % w); atomicAdd(&S[p], v0); atomicAdd(&Cnt[p], 1); }
+      else atomicOr(a.status, TPLR_ST_BAD_INDEX);
+      if (i1 < n) { const int p = (i1 / w) * LD + (i1 % w); atomicAdd(&S[p], v1); atomicAdd(&Cnt[p], 1); }
+      else atomicOr(a.status, TPLR_ST_BAD_INDEX);
+    }
+    __syncthreads();
+    for (int i = tid; i < TPLR_TILE_ELEMS; i += NT) {
+      const int cnt = Cnt[i];
+      if (cnt > 1) S[i] = S[i] / (float)cnt;
+    }
+    __syncthreads();
+    // ---- g = F_h^T S F_w -------------------------------------------------------------
+    float acc[4][4];
+    if (a.use_dct) {
+      mm_tile(S, Fh, h, acc);    // V[d][r] = sum_b S[b][d] F_h[b][r]
+      store_tile(V, acc);
+      __syncthreads();
+      mm_tile(V, Fw, w, acc);    // g[r][c] = sum_d V[d][r] F_w[d][c]
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 s = reinterpret_cast<const float4*>(S + (4 * ty + i) * LD)[tx];
+        acc[i][0] = s.x; acc[i][1] = s.y; acc[i][2] = s.z; acc[i][3] = s.w;
+      }
+    }
+    // ---- outer update ----------------------------------------------------------------
+    const bool vec = (w == 64) && ((d.cols & 3) == 0) && ((base & 3) == 0);
+    const float lr = skipped ? 0.f : a.lr;
+    const float decay = skipped ? 1.f : (1.f - a.lr * a.weight_decay);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * ty + i;
+      if (r >= h) continue;
+      const long long g0 = base + (long long)r * d.cols + 4 * tx;
+      float gv[4] = {acc[i][0], acc[i][1], acc[i][2], acc[i][3]};
+      if (skipped) { gv[0] = gv[1] = gv[2] = gv[3] = 0.f; }
+      if (vec) {
+        if (a.grad_out) *reinterpret_cast<float4*>(a.grad_out + g0) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+        if (a.update_mode != 2) {
+          const float4 t0 = *reinterpret_cast<const float4*>(a.theta0 + g0);
+          const float tv[4] = {t0.x, t0.y, t0.z, t0.w};
+          float o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float step = (a.update_mode == 1) ? (gv[j] > 0.f ? 1.f : (gv[j] < 0.f ? -1.f : 0.f)) : gv[j];
+            o[j] = tv[j] * decay - lr * step;
+          }
+          *reinterpret_cast<float4*>(a.theta + g0) = make_float4(o[0], o[1], o[2], o[3]);
+          if (a.theta_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned int*>(&lo);
+            pk.y = *reinterpret_cast<unsigned int*>(&hi);
+            *reinterpret_cast<uint2*>(a.theta_bf16 + g0) = pk;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (4 * tx + j >= w) continue;
+          const float g = gv[j];
+          if (a.grad_out) a.grad_out[g0 + j] = g;
+          if (a.update_mode != 2) {
+            const float step = (a.update_mode == 1) ? (g > 0.f ? 1.f : (g < 0.f ? -1.f : 0.f)) : g;
+            const float t = a.theta0[g0 + j] * decay - lr * step;
+            a.theta[g0 + j] = t;
+            if (a.theta_bf16) a.theta_bf16[g0 + j] = __float2bfloat16(t);
+          }
+        }
+      }
+    }
+  }
+}
+
+TPLR_API int tplr_aggregate_apply(const void* descs, int n_desc, int total_chunks, const float* basis,
+                                  int n_peers, const void* const* idx_ptrs, const void* const* val_ptrs,
+                                  int val_dtype, const float* qtable, int n_bins, int n_params,
+                                  const float* clip, const int* skip, const float* theta0, float* theta,
+                                  void* theta_bf16, float* grad_out, float lr, float weight_decay,
+                                  int use_dct, int update_mode, int distinct, unsigned int* status,
+                                  void* stream) {
+  if (total_chunks <= 0) return 0;
+  if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
+  AggArgs a;
+  a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.clip = clip; a.skip = skip; a.qtable = qtable;
+  a.theta0 = theta0; a.theta = theta; a.theta_bf16 = (__nv_bfloat16*)theta_bf16; a.grad_out = grad_out;
+  a.status = status; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_peers = n_peers;
+  a.n_params = n_params; a.n_bins = n_bins; a.lr = lr; a.weight_decay = weight_decay; a.use_dct = use_dct;
+  a.update_mode = update_mode; a.val_dtype = val_dtype; a.distinct = distinct;
+  for (int i = 0; i < n_peers; ++i) { a.pp.idx[i] = (const uint8_t*)idx_ptrs[i]; a.pp.val[i] = val_ptrs[i]; }
+  const int smem = (distinct ? 5 : 4) * TPLR_TILE_ELEMS * (int)sizeof(float);
+  cudaError_t err = cudaFuncSetAttribute(aggregate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return (int)err;
+  int grid = tplr_sm_count() * 2;
+  if (grid > total_chunks) grid = total_chunks;
+  aggregate_kernel<<<grid, NT, smem, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+TPLR_API int tplr_param_desc_size() { return (int)sizeof(TplrParamDesc); }

@@ -1,0 +1,146 @@
+// Peer-memory runtime (one process per GPU, NVLink/NVSwitch peer access through CUDA IPC):
+// symmetric allocations, handle export/import, a flag barrier with bounded waits, and the
+// copy/reduce kernels that move shards directly between GPUs with plain loads and stores.
+//
+// This is the transport under the sharded optimizer step and the compressed-gradient
+// gather; the reference uses torch.distributed/NCCL for all of it
+// (src/tplr/distributed.py:35-549, FSDP2 all-gather / reduce-scatter).
+#include "common.cuh"
+#include <string.h>
+
+TPLR_API int tplr_heap_alloc(unsigned long long bytes, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(p, 0, bytes);
+  *out = p;
+  return (int)e;
+}
+TPLR_API int tplr_heap_free(void* p) { return (int)cudaFree(p); }
+
+TPLR_API int tplr_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
+TPLR_API int tplr_ipc_get(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e == cudaSuccess) memcpy(handle_out, &h, sizeof(h));
+  return (int)e;
+}
+TPLR_API int tplr_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+TPLR_API int tplr_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+// ------------------------------------------------------------------------------------- //
+// Flag barrier. Every rank owns an array of `n_ranks` 64-bit slots in symmetric memory.
+// Arrive: write `epoch` into slot[my_rank] of every rank (release, system scope).
+// Wait: poll own slots until all >= epoch (acquire, system scope), at most `timeout_ns`;
+// on expiry set TPLR_ST_WAIT_TIMEOUT in *status and return — nothing spins forever.
+// ------------------------------------------------------------------------------------- //
+struct BarrierArgs {
+  unsigned long long* flags[TPLR_MAX_PEERS];
+  int n_ranks, my_rank;
+  unsigned long long epoch, timeout_ns;
+  unsigned int* status;
+};
+
+static __device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void barrier_kernel(const BarrierArgs a) {
+  const int r = threadIdx.x;
+  if (r >= a.n_ranks) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.flags[r] + a.my_rank), "l"(a.epoch) : "memory");
+  const unsigned long long t0 = gtime_ns();
+  const unsigned long long* mine = a.flags[a.my_rank] + r;
+  for (;;) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+    if (v >= a.epoch) break;
+    if (gtime_ns() - t0 > a.timeout_ns) {
+      if (a.status) atomicOr(a.status, TPLR_ST_WAIT_TIMEOUT);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+TPLR_API int tplr_barrier(void* const* flag_ptrs, int n_ranks, int my_rank, unsigned long long epoch,
+                          unsigned long long timeout_ns, unsigned int* status, void* stream) {
+  if (n_ranks > TPLR_MAX_PEERS || n_ranks <= 0) return (int)cudaErrorInvalidValue;
+  BarrierArgs a;
+  for (int i = 0; i < n_ranks; ++i) a.flags[i] = (unsigned long long*)flag_ptrs[i];
+  a.n_ranks = n_ranks; a.my_rank = my_rank; a.epoch = epoch; a.timeout_ns = timeout_ns; a.status = status;
+  barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// Reduce-scatter by pulling: own[lo : lo+n] += sum over the other ranks' buffers of the same
+// range (fp32, read over NVLink with 16-byte loads). The caller orders it after a barrier.
+// ------------------------------------------------------------------------------------- //
+struct ReduceArgs {
+  float* bufs[TPLR_MAX_PEERS];
+  int n_ranks, my_rank;
+  long long lo, n4;
+};
+
+__global__ void __launch_bounds__(256) reduce_shards_kernel(const ReduceArgs a) {
+  float4* own = reinterpret_cast<float4*>(a.bufs[a.my_rank] + a.lo);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 s = own[i];
+    for (int r = 0; r < a.n_ranks; ++r) {
+      if (r == a.my_rank) continue;
+      const float4 v = reinterpret_cast<const float4*>(a.bufs[r] + a.lo)[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    own[i] = s;
+  }
+}
+
+TPLR_API int tplr_reduce_shards(void* const* bufs, int n_ranks, int my_rank, long long lo, long long n,
+                                void* stream) {
+  if (n_ranks > TPLR_MAX_PEERS || (n % 4) || (lo % 4)) return (int)cudaErrorInvalidValue;
+  if (n <= 0) return 0;
+  ReduceArgs a;
+  for (int i = 0; i < n_ranks; ++i) a.bufs[i] = (float*)bufs[i];
+  a.n_ranks = n_ranks; a.my_rank = my_rank; a.lo = lo; a.n4 = n / 4;
+  long long grid = (a.n4 + 255) / 256;
+  const long long cap = (long long)tplr_sm_count() * 8;
+  if (grid > cap) grid = cap;
+  reduce_shards_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// dst_k[0:bytes] = src[0:bytes] for every destination (16-byte aligned, bytes % 16 == 0)
+struct PushArgs {
+  uint4* dst[TPLR_MAX_PEERS];
+  const uint4* src;
+  int n_dst;
+  long long n16;
+};
+__global__ void __launch_bounds__(256) push_copy_kernel(const PushArgs a) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.n16;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = a.src[i];
+    for (int d = 0; d < a.n_dst; ++d) a.dst[d][i] = v;
+  }
+}
+TPLR_API int tplr_push_copy(const void* src, void* const* dsts, int n_dst, long long bytes, void* stream) {
+  if (n_dst > TPLR_MAX_PEERS || (bytes % 16)) return (int)cudaErrorInvalidValue;
+  if (bytes <= 0 || n_dst <= 0) return 0;
+  PushArgs a;
+  a.src = (const uint4*)src; a.n_dst = n_dst; a.n16 = bytes / 16;
+  for (int i = 0; i < n_dst; ++i) a.dst[i] = (uint4*)dsts[i];
+  long long grid = (a.n16 + 255) / 256;
+  const long long cap = (long long)tplr_sm_count() * 8;
+  if (grid > cap) grid = cap;
+  push_copy_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}

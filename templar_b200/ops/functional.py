@@ -1,0 +1,401 @@
+"""Differentiable model ops with a hand-written sm_100a kernel behind each on CUDA.
+
+Each op is a ``torch.autograd.Function`` whose forward/backward call the native kernels
+for bf16 CUDA tensors and an equivalent plain-PyTorch expression otherwise (CPU, fp32),
+so the same model code trains on a B200 and runs the CPU/gloo test tier.
+
+Weight gradients: when a weight tensor carries a ``main_grad`` attribute (an fp32 view
+into the flat gradient buffer of :class:`templar_b200.parallel.flat.FlatParamStore`) the
+backward accumulates straight into it and returns ``None`` to autograd; otherwise the
+gradient is returned as usual.
+
+Reference ops replaced (torchtitan LLaMA used by the reference, models/llama3/model/model.py):
+RMSNorm :276-277, RoPE :69-95, attention :185-198, SwiGLU :236-237, output + CE :351 and
+components/loss.py:18-22.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+# "tcgen05": own GEMM kernel on CUDA bf16; "cublas": torch.matmul (library).  Switched by
+# templar_b200.ops.set_gemm_backend().
+_GEMM_BACKEND = "tcgen05"
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def set_gemm_backend(name: str) -> None:
+    global _GEMM_BACKEND
+    if name not in ("tcgen05", "cublas"):
+        raise ValueError(name)
+    _GEMM_BACKEND = name
+
+
+def gemm_backend() -> str:
+    return _GEMM_BACKEND
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device uint32 status word the kernels OR error bits into (0 = healthy)."""
+    idx = torch.device(device).index or 0
+    t = _status_words.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = t
+    return t
+
+
+def _native_ok(*ts) -> bool:
+    return all(t.is_cuda for t in ts) and all(t.dtype == torch.bfloat16 for t in ts if t.is_floating_point())
+
+
+# --------------------------------------------------------------------------- #
+# GEMM
+# --------------------------------------------------------------------------- #
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, accumulate: bool = False,
+         out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``C = op(A) op(B)^T`` with ``A``: [M,K] (or [K,M] when ``a_mn``), ``B``: [N,K] (or [K,N] when ``b_mn``).
+
+    bf16 CUDA operands go to the tcgen05 kernel (fp32 accumulation in TMEM); ``accumulate``
+    adds into an fp32 ``out``.  Rows may be strided (leading dimension), columns contiguous.
+    """
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    Kb = b.shape[0] if b_mn else b.shape[1]
+    if K != Kb:
+        raise ValueError(f"gemm inner dimensions differ: {K} vs {Kb}")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else a.dtype
+    use_native = (_GEMM_BACKEND == "tcgen05" and a.is_cuda and a.dtype == torch.bfloat16
+                  and b.dtype == torch.bfloat16 and a.stride(-1) == 1 and b.stride(-1) == 1
+                  and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0
+                  and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+                  and out_dtype in (torch.bfloat16, torch.float32))
+    if use_native:
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+            accumulate = False
+        native.require(out.stride(-1) == 1 and out.shape == (M, N), "gemm: bad out")
+        if accumulate and out.dtype != torch.float32:
+            raise ValueError("gemm: accumulate needs an fp32 out")
+        epi = 0 if out.dtype == torch.bfloat16 else (1 if accumulate else 2)
+        err = native.lib().tplr_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                                           a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), epi,
+                                           status_word(a.device).data_ptr(), 0, native.stream_ptr())
+        native.check(err, "tplr_gemm_bf16")
+        return out
+    A = a.t() if a_mn else a
+    Bt = b if b_mn else b.t()
+    c = A @ Bt
+    if out is None:
+        return c.to(out_dtype)
+    if accumulate:
+        out.add_(c.to(out.dtype))
+    else:
+        out.copy_(c)
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T for W [N, K]; dW goes to ``main_grad`` when given."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        ctx.save_for_backward(x, w)
+        ctx.main_grad = main_grad
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view_as(x)
+        if ctx.main_grad is not None:
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+        elif ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, main_grad: torch.Tensor | None = None) -> torch.Tensor:
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    return _Linear.apply(x, w, main_grad)
+
+
+# --------------------------------------------------------------------------- #
+# RMSNorm
+# --------------------------------------------------------------------------- #
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, main_grad):
+        ctx.eps = eps
+        ctx.main_grad = main_grad
+        if _native_ok(x, w) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+            xc = x.contiguous()
+            T = xc.numel() // xc.shape[-1]
+            y = torch.empty_like(xc)
+            rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+            native.check(native.lib().tplr_rmsnorm_fwd(xc.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(),
+                                                       T, xc.shape[-1], eps, native.stream_ptr()), "rmsnorm_fwd")
+            ctx.native = True
+            ctx.save_for_backward(xc, w, rstd)
+            return y
+        ctx.native = False
+        xf = x.float()
+        rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        ctx.save_for_backward(x, w, rstd)
+        return (xf * rstd * w.float()).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        mg = ctx.main_grad
+        if ctx.native:
+            dyc = dy.contiguous()
+            T, D = x.numel() // x.shape[-1], x.shape[-1]
+            dx = torch.empty_like(x)
+            dw_buf = mg if mg is not None else torch.zeros(D, dtype=torch.float32, device=x.device)
+            native.check(native.lib().tplr_rmsnorm_bwd(dyc.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                                       dx.data_ptr(), dw_buf.data_ptr(), T, D, native.stream_ptr()),
+                         "rmsnorm_bwd")
+            return dx, (None if mg is not None else dw_buf.to(w.dtype)), None, None
+        xf, g = x.float(), dy.float()
+        xh = xf * rstd
+        gw = g * w.float()
+        dx = rstd * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+        dw = (g * xh).reshape(-1, x.shape[-1]).sum(0)
+        if mg is not None:
+            mg.add_(dw.to(mg.dtype))
+            dw = None
+        else:
+            dw = dw.to(w.dtype)
+        return dx.to(x.dtype), dw, None, None
+
+
+def rmsnorm(x, w, eps: float = 1e-5, main_grad=None):
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    return _RMSNorm.apply(x, w, eps, main_grad)
+
+
+# --------------------------------------------------------------------------- #
+# RoPE (interleaved pairs), applied to the leading rotary heads of a packed projection
+# --------------------------------------------------------------------------- #
+def rope_tables(seq_len: int, head_dim: int, theta: float = 10000.0, device=None):
+    """cos/sin tables [S, head_dim/2] (fp32) of the angles ``pos * theta^(-2i/head_dim)``."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32)[: head_dim // 2] / head_dim))
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float32), inv)
+    return torch.cos(ang).to(device), torch.sin(ang).to(device)
+
+
+def _rope_torch(x, cos, sin, n_rot_cols, head_dim, inverse):
+    # x: [B, S, C]; rotate the first n_rot_cols columns head by head
+    B, S, _ = x.shape
+    rot = x[..., :n_rot_cols].float().reshape(B, S, n_rot_cols // head_dim, head_dim // 2, 2)
+    c = cos[:S].view(1, S, 1, head_dim // 2)
+    s = sin[:S].view(1, S, 1, head_dim // 2)
+    if inverse:
+        s = -s
+    a, b = rot[..., 0], rot[..., 1]
+    out = torch.stack((a * c - b * s, a * s + b * c), dim=-1).reshape(B, S, n_rot_cols)
+    return torch.cat((out.to(x.dtype), x[..., n_rot_cols:]), dim=-1)
+
+
+class _Rope(torch.autograd.Function):
+    """On CUDA bf16 the rotation is done in place (the input is the private output of the QKV
+    projection, which its producer does not need again); the backward rotates the incoming
+    gradient by the opposite angle, also in place."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, n_rot_heads, head_dim):
+        ctx.save_for_backward(cos, sin)
+        ctx.cfg = (n_rot_heads, head_dim)
+        B, S, C = x.shape
+        if _native_ok(x) and head_dim % 8 == 0 and C % 8 == 0 and x.is_contiguous():
+            native.check(native.lib().tplr_rope(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), B * S, S, n_rot_heads,
+                                                head_dim, C, 0, native.stream_ptr()), "rope")
+            ctx.mark_dirty(x)
+            return x
+        return _rope_torch(x, cos, sin, n_rot_heads * head_dim, head_dim, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        n_rot_heads, head_dim = ctx.cfg
+        B, S, C = dy.shape
+        if _native_ok(dy) and head_dim % 8 == 0 and C % 8 == 0:
+            dx = dy if dy.is_contiguous() else dy.contiguous()
+            native.check(native.lib().tplr_rope(dx.data_ptr(), cos.data_ptr(), sin.data_ptr(), B * S, S, n_rot_heads,
+                                                head_dim, C, 1, native.stream_ptr()), "rope_bwd")
+            return dx, None, None, None, None
+        return _rope_torch(dy, cos, sin, n_rot_heads * head_dim, head_dim, True), None, None, None, None
+
+
+def rope(x, cos, sin, n_rot_heads: int, head_dim: int):
+    """Rotate the first ``n_rot_heads`` heads of ``x`` [B, S, C] (heads laid out along C)."""
+    return _Rope.apply(x, cos, sin, n_rot_heads, head_dim)
+
+
+# --------------------------------------------------------------------------- #
+# SwiGLU on a packed [.., 2F] projection
+# --------------------------------------------------------------------------- #
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h):
+        F2 = h.shape[-1]
+        Fd = F2 // 2
+        ctx.save_for_backward(h)
+        if _native_ok(h) and Fd % 8 == 0 and h.is_contiguous():
+            T = h.numel() // F2
+            y = torch.empty(*h.shape[:-1], Fd, dtype=h.dtype, device=h.device)
+            native.check(native.lib().tplr_swiglu_fwd(h.data_ptr(), y.data_ptr(), T, Fd, native.stream_ptr()), "swiglu_fwd")
+            return y
+        a, b = h[..., :Fd].float(), h[..., Fd:].float()
+        return (F.silu(a) * b).to(h.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (h,) = ctx.saved_tensors
+        F2 = h.shape[-1]
+        Fd = F2 // 2
+        if _native_ok(h, dy) and Fd % 8 == 0 and h.is_contiguous():
+            dyc = dy.contiguous()
+            dh = torch.empty_like(h)
+            native.check(native.lib().tplr_swiglu_bwd(h.data_ptr(), dyc.data_ptr(), dh.data_ptr(), h.numel() // F2, Fd,
+                                                      native.stream_ptr()), "swiglu_bwd")
+            return dh
+        a, b, g = h[..., :Fd].float(), h[..., Fd:].float(), dy.float()
+        sg = torch.sigmoid(a)
+        silu = a * sg
+        return torch.cat((g * b * (sg + silu * (1 - sg)), g * silu), dim=-1).to(h.dtype)
+
+
+def swiglu(h):
+    return _SwiGLU.apply(h)
+
+
+# --------------------------------------------------------------------------- #
+# Embedding
+# --------------------------------------------------------------------------- #
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, table, main_grad):
+        ctx.save_for_backward(tokens)
+        ctx.main_grad = main_grad
+        ctx.tshape = table.shape
+        ctx.tdtype = table.dtype
+        if _native_ok(table) and table.shape[1] % 8 == 0 and table.is_contiguous():
+            tok = tokens.contiguous().to(torch.int64)
+            out = torch.empty(*tokens.shape, table.shape[1], dtype=table.dtype, device=table.device)
+            native.check(native.lib().tplr_embedding_fwd(tok.data_ptr(), table.data_ptr(), out.data_ptr(), tok.numel(),
+                                                         table.shape[1], table.shape[0], native.stream_ptr()), "embedding_fwd")
+            return out
+        return F.embedding(tokens, table)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (tokens,) = ctx.saved_tensors
+        V, D = ctx.tshape
+        mg = ctx.main_grad
+        if mg is not None and dy.is_cuda and dy.dtype == torch.bfloat16 and D % 8 == 0:
+            dyc = dy.contiguous()
+            tok = tokens.contiguous().to(torch.int64)
+            native.check(native.lib().tplr_embedding_bwd(tok.data_ptr(), dyc.data_ptr(), mg.data_ptr(), tok.numel(), D, V,
+                                                         native.stream_ptr()), "embedding_bwd")
+            return None, None, None
+        grad = torch.zeros(V, D, dtype=torch.float32, device=dy.device)
+        grad.index_add_(0, tokens.reshape(-1), dy.reshape(-1, D).float())
+        if mg is not None:
+            mg.add_(grad.to(mg.dtype))
+            return None, None, None
+        return None, grad.to(ctx.tdtype), None
+
+
+def embedding(tokens, table, main_grad=None):
+    if main_grad is None:
+        main_grad = getattr(table, "main_grad", None)
+    return _Embedding.apply(tokens, table, main_grad)
+
+
+# --------------------------------------------------------------------------- #
+# Attention (causal, GQA)
+# --------------------------------------------------------------------------- #
+def attention(q, k, v):
+    """Causal attention on [B, S, H, Dh] / [B, S, KV, Dh] tensors (strided views allowed)."""
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    gqa = kh.shape[1] != qh.shape[1]
+    if gqa and not q.is_cuda:
+        rep = qh.shape[1] // kh.shape[1]
+        kh = kh.repeat_interleave(rep, dim=1)
+        vh = vh.repeat_interleave(rep, dim=1)
+        gqa = False
+    o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=gqa)
+    return o.transpose(1, 2)
+
+
+# --------------------------------------------------------------------------- #
+# Cross entropy with the logit gradient produced in the forward pass
+# --------------------------------------------------------------------------- #
+class _CrossEntropy(torch.autograd.Function):
+    """Mean CE over labels != ignore_index.  The backward assumes the loss is the root of the
+    graph: the gradient ``(softmax - onehot) * grad_scale / n_valid`` is computed in the
+    forward kernel, in place in the logits buffer, and ``grad_scale`` replaces the incoming
+    ``grad_output`` (no extra pass over the logits, no host sync)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, grad_scale, ignore_index):
+        T = labels.numel()
+        V = logits.shape[-1]
+        lg = logits.reshape(T, V)
+        if _native_ok(lg) and lg.stride(-1) == 1 and lg.stride(0) % 8 == 0:
+            lab = labels.reshape(-1).contiguous().to(torch.int64)
+            losses = torch.empty(T, dtype=torch.float32, device=lg.device)
+            nvalid = torch.empty(1, dtype=torch.int32, device=lg.device)
+            loss = torch.empty((), dtype=torch.float32, device=lg.device)
+            want_grad = ctx.needs_input_grad[0]
+            native.check(native.lib().tplr_cross_entropy(lg.data_ptr(), lab.data_ptr(), losses.data_ptr(), nvalid.data_ptr(),
+                                                         loss.data_ptr(), float(grad_scale), T, V, lg.stride(0),
+                                                         int(ignore_index), int(want_grad), native.stream_ptr()), "cross_entropy")
+            # the logits buffer now holds d(loss)/d(logits); it is handed to autograd in backward
+            ctx.inplace = True
+            ctx.shape = logits.shape
+            ctx.dlogits = lg
+            return loss
+        ctx.inplace = False
+        ctx.grad_scale = grad_scale
+        ctx.ignore_index = ignore_index
+        ctx.shape = logits.shape
+        ctx.save_for_backward(lg, labels.reshape(-1))
+        return F.cross_entropy(lg.float(), labels.reshape(-1), ignore_index=ignore_index)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        if ctx.inplace:
+            return ctx.dlogits.view(ctx.shape), None, None, None
+        lg, labels = ctx.saved_tensors
+        lf = lg.float()
+        valid = labels != ctx.ignore_index
+        n = valid.sum().clamp(min=1)
+        p = torch.softmax(lf, dim=-1)
+        p[valid, labels[valid]] -= 1.0
+        p[~valid] = 0
+        return (p * (ctx.grad_scale / n)).to(lg.dtype).view(ctx.shape), None, None, None
+
+
+def cross_entropy(logits, labels, grad_scale: float = 1.0, ignore_index: int = -100):
+    return _CrossEntropy.apply(logits, labels, grad_scale, ignore_index)

@@ -1,0 +1,418 @@
+"""Device-resident window pipeline of a miner / validator node.
+
+One object owns every per-window buffer of a rank and drives the fused kernels:
+
+    snapshot()            theta0 <- master                       (start of a window)
+    micro_step()          forward + backward of one micro-batch, fp32 gradient accumulation
+    optimizer_step()      cross-rank gradient reduction into the owned shard, global-norm clip,
+                          fused AdamW on the shard, bf16 parameters pushed to every rank
+    compress()            e <- gamma e + (theta0 - theta); chunk DCT; top-k; 12-bit pack; residual
+    load_peer_payload()   place a peer's packed payload in a device slot
+    outer_step()          per-peer norms -> median clip -> pull/unpack/mean/iDCT -> theta <- theta0 - lr g
+    apply_single_peer()/restore()   the validator's before/after evaluation of one peer
+
+Differences from the reference's flow (neurons/miner.py:536-795, src/tplr/neurons.py:47-476,
+src/tplr/distributed.py:364-545): the parameter snapshot stays in HBM instead of pinned
+host memory, every rank compresses and aggregates its own chunk-aligned shard instead of an
+owner rank handling whole tensors and rank 0 decompressing everything, and no step reads a
+scalar back to the host.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import compress as C
+from ..ops import functional as OF
+from ..ops import native
+from .flat import FlatLayout, FlatParamStore
+
+
+@dataclass
+class EngineConfig:
+    topk: int = 32
+    target_chunk: int = 64
+    use_dct: bool = True
+    momentum_decay: float = 0.95
+    outer_lr: float = 0.4
+    outer_update: str = "sgd"          # "sgd" (reference behaviour) or "sign"
+    outer_weight_decay: float = 0.0
+    inner_lr: float = 1.17e-4
+    betas: tuple = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    max_peers: int = 8
+    val_dtype: torch.dtype = torch.float32
+
+
+class WindowEngine:
+    def __init__(self, model: torch.nn.Module, cfg: EngineConfig, *, device=None, rank: int = 0,
+                 world_size: int = 1, group=None, heap=None, compute_dtype: torch.dtype | None = None):
+        self.cfg = cfg
+        self.model = model
+        self.rank, self.world_size, self.group = rank, world_size, group
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.cuda = self.device.type == "cuda"
+        self.heap = heap
+        if compute_dtype is None:
+            compute_dtype = torch.bfloat16 if self.cuda else torch.float32
+        alloc = None
+        if heap is not None:
+            def alloc(n, dtype, symmetric=False):
+                if symmetric:
+                    return heap.alloc(n, dtype)
+                return torch.zeros(n, dtype=dtype, device=self.device)
+        self.store = FlatParamStore(model, compute_dtype=compute_dtype, device=self.device,
+                                    target_chunk=cfg.target_chunk, topk=cfg.topk, rank=rank,
+                                    world_size=world_size, alloc=alloc)
+        L = self.layout = self.store.layout
+        n_shard = self.store.hi - self.store.lo
+        z = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=self.device)
+        self.exp_avg, self.exp_avg_sq = z(n_shard), z(n_shard)
+        self.theta0 = z(n_shard)
+        self.ef = z(n_shard)
+        self.adam_step = 0
+        # payload: this node's own (full layout) + peer slots
+        palloc = (lambda n, dt: heap.alloc(n, dt)) if heap is not None else z
+        self.own_idx = palloc(L.idx_bytes, torch.uint8)
+        self.own_val = palloc(L.val_elems, torch.float32)
+        self.peer_idx = [palloc(L.idx_bytes, torch.uint8) for _ in range(self._slots())]
+        self.peer_val = [palloc(L.val_elems, cfg.val_dtype) for _ in range(self._slots())]
+        self.basis = L.basis_table().to(self.device)
+        self._desc = {}
+        for square in (True, False):
+            arr = L.descriptors(rank if world_size > 1 else None, square=square)
+            self._desc[square] = (torch.from_numpy(arr.view(np.uint8).reshape(-1).copy()).to(self.device), len(arr),
+                                  int(arr["n_chunks"].sum()) if len(arr) else 0)
+        full = L.descriptors(None, square=None)
+        self._desc_full = (torch.from_numpy(full.view(np.uint8).reshape(-1).copy()).to(self.device), len(full))
+        P = cfg.max_peers
+        self.sumsq_partial = z(P * L.n_params * 8)
+        self.peer_norms, self.clip = z(P * L.n_params), z(P * L.n_params)
+        self.median = z(L.n_params)
+        self.skip = z(L.n_params, torch.int32)
+        self.gnorm_sq = z(1)
+        self._sumsq_scratch = z(native.lib().tplr_sumsq_blocks() if self.cuda else 1)
+        self.status = OF.status_word(self.device) if self.cuda else torch.zeros(1, dtype=torch.int32)
+        self.window_losses: list[torch.Tensor] = []
+
+    def _slots(self) -> int:
+        return -(-self.cfg.max_peers // self.world_size)
+
+    # ------------------------------------------------------------------------------------ #
+    # inner loop
+    # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def snapshot(self) -> None:
+        self.theta0.copy_(self.store.master_shard)
+
+    def zero_grad(self) -> None:
+        self.store.grad.zero_()
+
+    def micro_step(self, tokens: torch.Tensor, labels: torch.Tensor, grad_scale: float = 1.0) -> torch.Tensor:
+        """Forward + backward of one micro-batch; returns the (device) mean loss."""
+        loss = self.model.loss(tokens, labels, grad_scale)
+        loss.backward()
+        return loss.detach()
+
+    @torch.no_grad()
+    def optimizer_step(self, lr: float | None = None) -> None:
+        """Clip by global norm and apply AdamW on the owned shard; refresh the compute copy."""
+        cfg, st = self.cfg, self.store
+        lr = cfg.inner_lr if lr is None else lr
+        self.adam_step += 1
+        if self.world_size > 1:
+            self._reduce_grads()
+        gshard = st.grad[st.lo:st.hi]
+        n = st.hi - st.lo
+        if self.cuda:
+            L = native.lib()
+            native.check(L.tplr_sumsq(gshard.data_ptr(), n, self._sumsq_scratch.data_ptr(), self.gnorm_sq.data_ptr(),
+                                      native.stream_ptr()), "sumsq")
+            if self.world_size > 1:
+                dist.all_reduce(self.gnorm_sq, group=self.group)
+            shadows = self._compute_shadow_ptrs()
+            native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                                      gshard.data_ptr(), native.ptr_array(shadows), len(shadows), n, lr, cfg.betas[0],
+                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0, cfg.max_grad_norm,
+                                      self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
+            if self.world_size > 1:
+                self._barrier()
+                st.grad.zero_()
+            return
+        # CPU path (same arithmetic)
+        g = gshard
+        self.gnorm_sq.copy_((g * g).sum().reshape(1))
+        if self.world_size > 1:
+            dist.all_reduce(self.gnorm_sq, group=self.group)
+        coef = torch.clamp(cfg.max_grad_norm / (self.gnorm_sq.sqrt() + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else 1.0
+        g = g * coef
+        b1, b2 = cfg.betas
+        self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        bc1, bc2 = 1 - b1 ** self.adam_step, 1 - b2 ** self.adam_step
+        p = st.master_shard
+        p.mul_(1 - lr * cfg.weight_decay)
+        p.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + cfg.eps, value=-lr)
+        st.grad.zero_()
+        self._publish_compute()
+
+    def _compute_shadow_ptrs(self) -> list[int]:
+        st = self.store
+        if st.compute is st.master_shard:
+            return []
+        esz = st.compute.element_size()
+        if self.heap is not None and self.world_size > 1:
+            return [self.heap.peer_ptr(st.compute, r) + st.lo * esz for r in range(self.world_size)]
+        return [st.compute.data_ptr() + st.lo * esz]
+
+    def _publish_compute(self) -> None:
+        """CPU / generic path: compute[lo:hi] <- master shard, then make every rank's copy whole."""
+        st = self.store
+        if st.compute is not st.master_shard:
+            st.compute[st.lo:st.hi].copy_(st.master_shard.to(st.compute.dtype))
+        if self.world_size > 1:
+            self._allgather_compute()
+
+    def _allgather_compute(self) -> None:
+        st = self.store
+        parts = [st.compute[a:b] for a, b in (self.layout.shard_range(r) for r in range(self.world_size))]
+        for r, part in enumerate(parts):
+            dist.broadcast(part, src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                           group=self.group)
+
+    def _reduce_grads(self) -> None:
+        st = self.store
+        if self.cuda and self.heap is not None:
+            self._barrier()
+            ptrs = [self.heap.peer_ptr(st.grad, r) for r in range(self.world_size)]
+            native.check(native.lib().tplr_reduce_shards(native.ptr_array(ptrs), self.world_size, self.rank, st.lo,
+                                                         st.hi - st.lo, native.stream_ptr()), "reduce_shards")
+            return
+        for r in range(self.world_size):
+            a, b = self.layout.shard_range(r)
+            dist.reduce(st.grad[a:b], dst=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                        group=self.group)
+
+    def _barrier(self) -> None:
+        if self.world_size > 1:
+            if self.heap is not None and self.cuda:
+                self.heap.barrier()
+            else:
+                dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------------------------ #
+    # compression of the window's pseudo-gradient
+    # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def compress(self, null_round: bool = False, own_slot_ptrs: tuple[int, int] | None = None) -> None:
+        """Runs the fused compress kernel over the owned shard.
+
+        Reads theta0 and the current master (delta = theta0 - theta), updates the error feedback
+        in place and writes this rank's part of the node payload into ``own_idx`` / ``own_val``
+        (or into ``own_slot_ptrs``, e.g. the hosting rank's buffers in peer memory).
+        """
+        cfg, st = self.cfg, self.store
+        if not self.cuda:
+            return self._compress_torch(null_round)
+        idx_ptr, val_ptr = own_slot_ptrs or (self.own_idx.data_ptr(), self.own_val.data_ptr())
+        # flat pointers are biased so that descriptor offsets (full-model) address the shard arrays
+        bias = st.lo * 4
+        L = native.lib()
+        for square in (True, False):
+            desc, n_desc, n_chunks = self._desc[square]
+            if n_chunks == 0:
+                continue
+            native.check(L.tplr_compress_chunks(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(),
+                                                self.ef.data_ptr() - bias, self.theta0.data_ptr() - bias,
+                                                st.master_shard.data_ptr() - bias, idx_ptr, val_ptr,
+                                                self.status.data_ptr(), cfg.momentum_decay, int(cfg.use_dct), 1,
+                                                int(null_round), 1, int(not square), native.stream_ptr()), "compress")
+
+    def _compress_torch(self, null_round: bool) -> None:
+        """CPU oracle path: the same arithmetic through :mod:`templar_b200.compress`, tensor by tensor."""
+        cfg, st, L = self.cfg, self.store, self.layout
+        tr = C.ChunkingTransformer(None, cfg.target_chunk)
+        comp = C.TopKCompressor(use_quantization=False)
+        for s, r0, nrows in (L.shard_entries(self.rank) if self.world_size > 1
+                             else [(s, 0, s.chunk_rows) for s in L.specs]):
+            a = s.offset + r0 * s.h * s.cols - st.lo
+            b = a + nrows * s.h * s.cols
+            shape = (nrows * s.h, s.cols) if len(s.shape) >= 2 else (s.cols,)
+            tr.register_shape(shape)
+            e = self.ef[a:b].view(shape)
+            if null_round:
+                e.zero_()
+            else:
+                e.mul_(cfg.momentum_decay).add_((self.theta0[a:b] - st.master_shard[a:b]).view(shape))
+            enc = tr.encode(e, use_dct=cfg.use_dct)
+            idx, val, xshape, totalk = comp.compress(enc, cfg.topk)
+            dec = tr.decode(comp.decompress(e, idx, val, xshape, totalk), use_dct=cfg.use_dct)
+            e.sub_(dec)
+            k = s.topk(cfg.topk)
+            c0 = r0 * s.chunks_x
+            io = L.idx_off[s.name] + c0 * (k // 2) * 3
+            vo = L.val_off[s.name] + c0 * k
+            self.own_idx[io: io + idx.numel()].copy_(idx)
+            self.own_val[vo: vo + val.numel()].copy_(val.reshape(-1))
+
+    def own_payload(self) -> dict:
+        """Reference-format gradient dict (``<name>idxs`` / ``<name>vals`` / ``<name>quant_params``)
+        as views of the flat payload buffers, in named_parameters() order."""
+        out = {}
+        for s in sorted(self.layout.specs, key=lambda s: s.index):
+            idx, val = self.layout.payload_views(self.own_idx, self.own_val, s.name)
+            out[s.name + "idxs"], out[s.name + "vals"], out[s.name + "quant_params"] = idx, val, None
+        return out
+
+    # ------------------------------------------------------------------------------------ #
+    # gather side
+    # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def load_peer_payload(self, slot: int, payload, non_blocking: bool = True) -> None:
+        """``payload``: (idx_flat uint8, val_flat) in this layout, or a reference-format dict."""
+        if isinstance(payload, dict):
+            for s in self.layout.specs:
+                idx, val = self.layout.payload_views(self.peer_idx[slot], self.peer_val[slot], s.name)
+                idx.copy_(payload[s.name + "idxs"].reshape(-1), non_blocking=non_blocking)
+                val.copy_(payload[s.name + "vals"].reshape(val.shape), non_blocking=non_blocking)
+            return
+        idx_flat, val_flat = payload
+        self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
+        self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
+
+    def _peer_ptrs(self, n_peers: int, include_own: bool):
+        """Pointers of the n_peers payloads: peer 0 = this node's own payload when include_own,
+        the others live round-robin in the ranks' slots (peer j on rank j % world, slot j // world)."""
+        idx_ptrs, val_ptrs = [], []
+        for j in range(n_peers):
+            if include_own and j == 0:
+                owner = 0
+                ib, vb = self.own_idx, self.own_val
+            else:
+                owner, slot = j % self.world_size, j // self.world_size
+                ib, vb = self.peer_idx[slot], self.peer_val[slot]
+            if self.heap is not None and self.world_size > 1:
+                idx_ptrs.append(self.heap.peer_ptr(ib, owner))
+                val_ptrs.append(self.heap.peer_ptr(vb, owner))
+            else:
+                idx_ptrs.append(ib.data_ptr())
+                val_ptrs.append(vb.data_ptr())
+        return idx_ptrs, val_ptrs
+
+    @torch.no_grad()
+    def outer_step(self, n_peers: int, *, lr: float | None = None, include_own: bool = True,
+                   clip_norm: bool = True, base: str = "theta0") -> None:
+        """Aggregate ``n_peers`` payloads and apply the outer update to the owned shard.
+
+        ``base='theta0'`` applies the update to the window-start snapshot (the miner's flow:
+        restore, then outer step); ``base='theta'`` applies it to the current master.
+        """
+        cfg, st = self.cfg, self.store
+        lr = cfg.outer_lr if lr is None else lr
+        if not self.cuda:
+            return self._outer_step_torch(n_peers, lr, include_own, clip_norm, base)
+        L = native.lib()
+        idx_ptrs, val_ptrs = self._peer_ptrs(n_peers, include_own)
+        vdt = {torch.float32: 0, torch.bfloat16: 1}[cfg.val_dtype]
+        stream = native.stream_ptr()
+        np_ = self.layout.n_params
+        if clip_norm:
+            desc_full, n_full = self._desc_full
+            native.check(L.tplr_peer_sumsq(desc_full.data_ptr(), n_full, np_, n_peers, native.ptr_array(val_ptrs), vdt,
+                                           None, 0, self.sumsq_partial.data_ptr(), stream), "peer_sumsq")
+            native.check(L.tplr_clip_factors(self.sumsq_partial.data_ptr(), np_, n_peers, self.peer_norms.data_ptr(),
+                                             self.clip.data_ptr(), self.median.data_ptr(), self.skip.data_ptr(),
+                                             self.status.data_ptr(), stream), "clip_factors")
+        bias = st.lo * 4
+        base_buf = self.theta0 if base == "theta0" else st.master_shard
+        shadow = None
+        if st.compute is not st.master_shard:
+            shadow = st.compute.data_ptr()   # full-size local compute buffer, descriptor offsets are absolute
+        mode = {"sgd": 0, "sign": 1}[cfg.outer_update]
+        for square in (True, False):
+            desc, n_desc, n_chunks = self._desc[square]
+            if n_chunks == 0:
+                continue
+            native.check(L.tplr_aggregate_apply(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(), n_peers,
+                                                native.ptr_array(idx_ptrs), native.ptr_array(val_ptrs), vdt, None, 0, np_,
+                                                self.clip.data_ptr() if clip_norm else None,
+                                                self.skip.data_ptr() if clip_norm else None,
+                                                base_buf.data_ptr() - bias, st.master_shard.data_ptr() - bias, shadow, None,
+                                                lr, cfg.outer_weight_decay, int(cfg.use_dct), mode, int(not square),
+                                                self.status.data_ptr(), stream), "aggregate_apply")
+        if self.world_size > 1:
+            self._barrier()
+            self._allgather_compute_native()
+
+    def _allgather_compute_native(self) -> None:
+        """Push the owned range of the compute buffer to every other rank (plain stores over NVLink)."""
+        st = self.store
+        esz = st.compute.element_size()
+        n = st.hi - st.lo
+        src = st.compute.data_ptr() + st.lo * esz
+        dsts = [self.heap.peer_ptr(st.compute, r) + st.lo * esz for r in range(self.world_size) if r != self.rank]
+        native.check(native.lib().tplr_push_copy(src, native.ptr_array(dsts), len(dsts), n * esz, native.stream_ptr()),
+                     "push_copy")
+        self._barrier()
+
+    def _outer_step_torch(self, n_peers, lr, include_own, clip_norm, base) -> None:
+        cfg, st, L = self.cfg, self.store, self.layout
+        tr = C.ChunkingTransformer(None, cfg.target_chunk)
+        comp = C.TopKCompressor(use_quantization=False)
+        bufs = []
+        for j in range(n_peers):
+            if include_own and j == 0:
+                bufs.append((self.own_idx, self.own_val))
+            else:
+                bufs.append((self.peer_idx[j // self.world_size], self.peer_val[j // self.world_size]))
+        base_buf = self.theta0 if base == "theta0" else st.master_shard
+        for s in L.specs:
+            tr.register_shape(s.shape)
+            idxs, vals = zip(*(L.payload_views(ib, vb, s.name) for ib, vb in bufs))
+            vals = [v.float() for v in vals]
+            ref = torch.empty(s.shape, dtype=torch.float32, device=self.device)
+            g = tr.decode(comp.batch_decompress(ref, list(idxs), list(vals), L.xshape(s.name), s.totalk,
+                                                clip_norm=clip_norm), use_dct=cfg.use_dct).reshape(-1)
+            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
+            if a >= b:
+                continue
+            g = g[a - s.offset: b - s.offset]
+            if not torch.isfinite(g).all():
+                st.master_shard[a - st.lo: b - st.lo].copy_(base_buf[a - st.lo: b - st.lo])
+                continue
+            step = torch.sign(g) if cfg.outer_update == "sign" else g
+            st.master_shard[a - st.lo: b - st.lo].copy_(
+                base_buf[a - st.lo: b - st.lo] * (1 - lr * cfg.outer_weight_decay) - lr * step)
+        self._publish_compute()
+
+    # ------------------------------------------------------------------------------------ #
+    # validator: single-peer apply and restore
+    # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def restore(self) -> None:
+        """master <- theta0 and compute copy refreshed (undo of an evaluation-time apply)."""
+        st = self.store
+        st.master_shard.copy_(self.theta0)
+        if self.cuda and st.compute is not st.master_shard:
+            native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(),
+                                                     st.compute.data_ptr() + st.lo * st.compute.element_size(),
+                                                     st.hi - st.lo, native.stream_ptr()), "cast_bf16")
+            if self.world_size > 1:
+                self._barrier()
+                self._allgather_compute_native()
+        else:
+            self._publish_compute()
+
+    def check_status(self) -> int:
+        """Reads (and clears) the kernel status word — a host sync; call between windows."""
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+        return v

@@ -1,0 +1,254 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from templar_b200 import compress as C
+from templar_b200.models.llama import ModelArgs, build_model
+from templar_b200.ops import functional as OF
+from templar_b200.ops import native
+from templar_b200.parallel.flat import FlatLayout
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+from templar_b200.utils.synthetic import synthetic_payload
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+class _Bag(torch.nn.Module):
+    """A module holding parameters of arbitrary shapes (drives the engine without a transformer)."""
+
+    def __init__(self, shapes, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.ps = torch.nn.ParameterList([torch.nn.Parameter(torch.randn(*s, generator=g) * 0.05) for s in shapes])
+
+
+def _oracle_compress(e, delta, gamma, tr, comp, topk, use_dct):
+    e = gamma * e + delta
+    enc = tr.encode(e, use_dct=use_dct)
+    idx, val, xshape, totalk = comp.compress(enc, topk)
+    dec = tr.decode(comp.decompress(e, idx, val, xshape, totalk), use_dct=use_dct)
+    return idx, val, xshape, totalk, e - dec, enc
+
+
+@pytest.mark.parametrize("use_dct", [True, False])
+@pytest.mark.parametrize("shapes,topk", [
+    ([(128, 192), (256,), (64, 64)], 32),
+    ([(96, 40), (192, 128), (130,)], 16),
+    ([(64, 256), (48,), (320, 64)], 64),
+])
+def test_compress_kernel_matches_oracle(shapes, topk, use_dct):
+    torch.manual_seed(1)
+    model = _Bag(shapes).to(DEV)
+    eng = WindowEngine(model, EngineConfig(topk=topk, use_dct=use_dct, momentum_decay=0.9), device=DEV,
+                       compute_dtype=torch.float32)
+    st = eng.store
+    eng.snapshot()
+    ef0 = torch.randn_like(eng.ef) * 0.01
+    eng.ef.copy_(ef0)
+    st.master_shard.add_(torch.randn_like(st.master_shard) * 0.02)   # theta after the inner steps
+    theta0, theta = eng.theta0.clone(), st.master_shard.clone()
+    eng.compress()
+    torch.cuda.synchronize()
+    assert eng.check_status() == 0
+    tr = C.ChunkingTransformer(model, 64)
+    comp = C.TopKCompressor()
+    for s in eng.layout.specs:
+        sl = slice(s.offset, s.offset + s.numel)
+        e = ef0[sl].view(s.shape).cpu().double()
+        d = (theta0[sl] - theta[sl]).view(s.shape).cpu().double()
+        tr64 = C.ChunkingTransformer(None, 64)
+        tr64.register_shape(s.shape, dtype=torch.float64)
+        idx_o, val_o, xshape, totalk, ef_o, enc = _oracle_compress(e, d, 0.9, tr64, comp, topk, use_dct)
+        idx_k, val_k = eng.layout.payload_views(eng.own_idx, eng.own_val, s.name)
+        k = s.topk(topk)
+        assert tuple(val_k.shape) == tuple(val_o.shape)
+        ik = C.unpack_12bit_indices(idx_k.cpu(), val_k.shape).reshape(-1, k)
+        io = C.unpack_12bit_indices(idx_o, val_o.shape).reshape(-1, k)
+        vk = val_k.cpu().double().reshape(-1, k)
+        encf = enc.reshape(-1, s.totalk)
+        # values are the coefficients at the reported indices
+        assert torch.allclose(vk, torch.gather(encf, 1, ik), atol=2e-6, rtol=1e-4)
+        # same selection up to ties at fp32 resolution: compare the selected magnitudes
+        mk = vk.abs().sort(dim=1).values
+        mo = val_o.reshape(-1, k).abs().sort(dim=1).values
+        assert torch.allclose(mk, mo, atol=2e-6, rtol=1e-4)
+        assert (ik.sort(dim=1).values[:, 1:] != ik.sort(dim=1).values[:, :-1]).all()   # distinct indices
+        assert int(ik.max()) < s.totalk
+        # error feedback residual
+        ef_k = eng.ef[sl].view(s.shape).cpu().double()
+        assert torch.allclose(ef_k, ef_o, atol=5e-6, rtol=1e-4), s.name
+        _ = io
+
+
+@pytest.mark.parametrize("use_dct", [True, False])
+@pytest.mark.parametrize("update", ["sgd", "sign"])
+def test_aggregate_kernel_matches_oracle(use_dct, update):
+    shapes = [(128, 192), (256,), (96, 40), (64, 64)]
+    n_peers, topk, lr = 5, 16, 0.3
+    model = _Bag(shapes).to(DEV)
+    eng = WindowEngine(model, EngineConfig(topk=topk, use_dct=use_dct, outer_lr=lr, outer_update=update,
+                                           max_peers=n_peers), device=DEV, compute_dtype=torch.float32)
+    eng.snapshot()
+    theta0 = eng.theta0.clone()
+    payloads = []
+    for j in range(n_peers):
+        idx, val = synthetic_payload(eng.layout, 10 + j, device=DEV, scale=1e-2 * (1 + 3 * j))
+        payloads.append((idx, val))
+        eng.load_peer_payload(j, (idx, val))
+    eng.outer_step(n_peers, include_own=False)
+    torch.cuda.synchronize()
+    assert eng.check_status() == 0
+    comp = C.TopKCompressor()
+    for s in eng.layout.specs:
+        tr = C.ChunkingTransformer(None, 64)
+        tr.register_shape(s.shape, dtype=torch.float64)
+        idxs, vals = [], []
+        for idx, val in payloads:
+            i, v = eng.layout.payload_views(idx, val, s.name)
+            idxs.append(i.cpu()); vals.append(v.cpu().double())
+        ref = torch.empty(s.shape, dtype=torch.float64)
+        g = tr.decode(comp.batch_decompress(ref, idxs, vals, eng.layout.xshape(s.name), s.totalk, clip_norm=True),
+                      use_dct=use_dct)
+        sl = slice(s.offset, s.offset + s.numel)
+        got = eng.store.master_shard[sl].view(s.shape).cpu().double()
+        t0 = theta0[sl].view(s.shape).cpu().double()
+        if update == "sgd":
+            assert torch.allclose(got, t0 - lr * g, atol=3e-6, rtol=1e-5), s.name
+        else:
+            stable = g.abs() > 1e-7
+            assert torch.allclose(got[stable], (t0 - lr * torch.sign(g))[stable], atol=1e-6), s.name
+
+
+def test_rmsnorm_fwd_bwd():
+    torch.manual_seed(0)
+    for D in (256, 2048, 8192):
+        x = torch.randn(3, 37, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+        y = OF.rmsnorm(x, w, 1e-5)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+        yr = F.rms_norm(xf, (D,), wf, 1e-5)
+        yr.backward(dy.float())
+        assert torch.allclose(y.float(), yr, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(x.grad.float(), xf.grad, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(w.grad.float(), wf.grad, atol=0.15, rtol=3e-2)
+
+
+def test_rope_matches_complex_multiply():
+    B, S, H, KV, Dh = 2, 64, 4, 2, 128
+    C_ = (H + 2 * KV) * Dh
+    x = torch.randn(B, S, C_, device=DEV, dtype=torch.bfloat16)
+    cos, sin = OF.rope_tables(S, Dh, 10000.0, DEV)
+    xr = x.clone().requires_grad_()
+    y = OF.rope(xr * 1.0, cos, sin, H + KV, Dh)
+    fc = torch.complex(cos, sin)
+    rot = torch.view_as_complex(x[..., :(H + KV) * Dh].float().reshape(B, S, H + KV, Dh // 2, 2))
+    ref = torch.view_as_real(rot * fc.view(1, S, 1, Dh // 2)).reshape(B, S, (H + KV) * Dh)
+    assert torch.allclose(y[..., :(H + KV) * Dh].float(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.equal(y[..., (H + KV) * Dh:], x[..., (H + KV) * Dh:])
+    dy = torch.randn_like(y)
+    y.backward(dy.clone())
+    drot = torch.view_as_complex(dy[..., :(H + KV) * Dh].float().reshape(B, S, H + KV, Dh // 2, 2))
+    dref = torch.view_as_real(drot * fc.conj().view(1, S, 1, Dh // 2)).reshape(B, S, (H + KV) * Dh)
+    assert torch.allclose(xr.grad[..., :(H + KV) * Dh].float(), dref, atol=2e-2, rtol=2e-2)
+
+
+def test_swiglu_fwd_bwd():
+    h = torch.randn(5, 33, 2 * 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = OF.swiglu(h)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    hf = h.detach().float().requires_grad_()
+    yr = F.silu(hf[..., :512]) * hf[..., 512:]
+    yr.backward(dy.float())
+    assert torch.allclose(y.float(), yr, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(h.grad.float(), hf.grad, atol=3e-2, rtol=3e-2)
+
+
+def test_cross_entropy_loss_and_grad():
+    T, V = 300, 32000
+    logits = (torch.randn(T, V, device=DEV) * 2).to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    lf = logits.float().requires_grad_()
+    ref = F.cross_entropy(lf, labels, ignore_index=-100)
+    ref.backward()
+    lg = logits.clone().requires_grad_()
+    work = lg * 1.0
+    loss = OF.cross_entropy(work, labels, 0.25)
+    loss.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3
+    assert torch.allclose(lg.grad.float(), 0.25 * lf.grad, atol=2e-5, rtol=2e-2)
+
+
+def test_embedding_fwd_bwd():
+    V, D = 1000, 256
+    table = torch.randn(V, D, device=DEV, dtype=torch.bfloat16)
+    table.main_grad = torch.zeros(V, D, device=DEV)
+    tok = torch.randint(0, V, (4, 50), device=DEV)
+    t = table.clone().requires_grad_()
+    out = OF.embedding(tok, t, table.main_grad)
+    assert torch.equal(out, table[tok])
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    ref = torch.zeros(V, D, device=DEV).index_add_(0, tok.reshape(-1), dy.reshape(-1, D).float())
+    assert torch.allclose(table.main_grad, ref, atol=1e-5)
+
+
+def test_adamw_and_sumsq_match_torch():
+    n = 4096 * 33
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV) * 3
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    shadow = torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    L = native.lib()
+    scratch = torch.zeros(L.tplr_sumsq_blocks(), device=DEV)
+    nsq = torch.zeros(1, device=DEV)
+    for step in (1, 2, 3):
+        gg = g * step
+        ref_p.grad = gg.clone()
+        torch.nn.utils.clip_grad_norm_([ref_p], 1.0)
+        opt.step()
+        gk = gg.clone()
+        native.check(L.tplr_sumsq(gk.data_ptr(), n, scratch.data_ptr(), nsq.data_ptr(), native.stream_ptr()), "sumsq")
+        assert abs(float(nsq) - float((gg.double() ** 2).sum())) / float((gg.double() ** 2).sum()) < 1e-5
+        native.check(L.tplr_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), gk.data_ptr(),
+                                  native.ptr_array([shadow.data_ptr()]), 1, n, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0, 1.0,
+                                  nsq.data_ptr(), 1, native.stream_ptr()), "adamw")
+        assert torch.allclose(p, ref_p.detach(), atol=1e-5, rtol=1e-4)
+        assert torch.equal(shadow, p.to(torch.bfloat16))
+        assert float(gk.abs().max()) == 0.0
+
+
+def test_model_step_native_vs_torch_reference():
+    """One forward/backward of a small model: kernels (bf16) against the same model in fp32 PyTorch."""
+    args = ModelArgs(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, intermediate_size=512, max_seq_len=128)
+    OF.set_gemm_backend("cublas")
+    try:
+        ref = build_model(args, device=DEV, seed=3)           # fp32, autograd weight grads
+        with torch.no_grad():
+            for p in ref.parameters():                        # make the weights bf16-representable
+                p.copy_(p.to(torch.bfloat16).float())
+        model = build_model(args, device=DEV, dtype=torch.bfloat16, seed=None)
+        model.load_state_dict(ref.state_dict())
+        eng = WindowEngine(model, EngineConfig(topk=8), device=DEV)
+        tok = torch.randint(0, 1024, (4, 129), device=DEV)
+        loss = eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0)
+        lr = ref.loss(tok[:, :-1], tok[:, 1:])
+        lr.backward()
+        assert abs(float(loss) - float(lr)) < 0.05
+        for n, p in ref.named_parameters():
+            g = dict(model.named_parameters())[n].main_grad
+            rel = (g - p.grad).norm() / (p.grad.norm() + 1e-12)
+            assert float(rel) < 0.08, (n, float(rel))
+    finally:
+        OF.set_gemm_backend("tcgen05")
