@@ -10,6 +10,10 @@
 
 #define TPLR_API extern "C" __attribute__((visibility("default")))
 
+// The CUDA runtime keeps a per-thread "last error"; another library's benign failure on the
+// calling thread must not be reported as ours, so every entry point clears it first.
+#define TPLR_ENTER() (void)cudaGetLastError()
+
 #define TPLR_MAX_PEERS 32
 #define TPLR_TILE 64            // maximum chunk edge (target_chunk)
 #define TPLR_TILE_ELEMS 4096    // 64*64: indices fit 12 bits

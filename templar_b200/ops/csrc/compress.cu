@@ -309,6 +309,7 @@ TPLR_API int tplr_compress_chunks(const void* descs, int n_desc, int total_chunk
                                   uint8_t* idx_out, float* val_out, unsigned int* status,
                                   float gamma, int use_dct, int delta_mode, int null_round,
                                   int write_residual, int distinct, void* stream) {
+  TPLR_ENTER();
   if (total_chunks <= 0) return 0;
   CompressArgs a;
   a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.theta0 = theta0; a.theta = theta;
@@ -366,6 +367,7 @@ __global__ void __launch_bounds__(256) peer_sumsq_kernel(const TplrParamDesc* __
 TPLR_API int tplr_peer_sumsq(const void* descs, int n_desc, int n_params, int n_peers,
                              const void* const* val_ptrs, int val_dtype, const float* qtable,
                              int n_bins, float* partial, void* stream) {
+  TPLR_ENTER();
   if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
   PeerPtrs pp;
   for (int i = 0; i < n_peers; ++i) { pp.val[i] = val_ptrs[i]; pp.idx[i] = nullptr; }
@@ -414,6 +416,7 @@ __global__ void clip_factors_kernel(const float* __restrict__ partial, int n_par
 TPLR_API int tplr_clip_factors(const float* partial, int n_params, int n_peers, float* norms,
                                float* clip, float* median, int* skip, unsigned int* status,
                                void* stream) {
+  TPLR_ENTER();
   if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
   clip_factors_kernel<<<(n_params + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
       partial, n_params, n_peers, norms, clip, median, skip, status);
@@ -563,6 +566,7 @@ TPLR_API int tplr_aggregate_apply(const void* descs, int n_desc, int total_chunk
                                   void* theta_bf16, float* grad_out, float lr, float weight_decay,
                                   int use_dct, int update_mode, int distinct, unsigned int* status,
                                   void* stream) {
+  TPLR_ENTER();
   if (total_chunks <= 0) return 0;
   if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
   AggArgs a;

@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
 
 TPLR_API int tplr_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long T, int D,
                               float eps, void* stream) {
+  TPLR_ENTER();
   if (D % 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   rmsnorm_fwd_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, D, eps);
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
 
 TPLR_API int tplr_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                               float* dw, long long T, int D, void* stream) {
+  TPLR_ENTER();
   if (D % 8 || D > RMS_MAXV * 256 * 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   long long grid = tplr_sm_count() * 4;
@@ -189,6 +191,7 @@ __global__ void __launch_bounds__(256) rope_kernel(bf16* __restrict__ buf, const
 
 TPLR_API int tplr_rope(void* buf, const float* cosb, const float* sinb, long long tokens, int S, int n_heads,
                        int Dh, long long row_stride, int inverse, void* stream) {
+  TPLR_ENTER();
   if (Dh % 8 || row_stride % 8) return (int)cudaErrorInvalidValue;
   const long long total = tokens * n_heads * (Dh / 8);
   if (total <= 0) return 0;
@@ -252,12 +255,14 @@ static inline unsigned ew_grid(long long total) {
 }
 
 TPLR_API int tplr_swiglu_fwd(const void* h, void* y, long long T, int F, void* stream) {
+  TPLR_ENTER();
   if (F % 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   swiglu_fwd_kernel<<<ew_grid(T * (F / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)h, (bf16*)y, T, F);
   return (int)cudaGetLastError();
 }
 TPLR_API int tplr_swiglu_bwd(const void* h, const void* dy, void* dh, long long T, int F, void* stream) {
+  TPLR_ENTER();
   if (F % 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   swiglu_bwd_kernel<<<ew_grid(T * (F / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)h, (const bf16*)dy, (bf16*)dh, T, F);
@@ -350,6 +355,7 @@ __global__ void __launch_bounds__(1024) sum_rows_kernel(const float* __restrict_
 TPLR_API int tplr_cross_entropy(void* logits, const long long* labels, float* losses, int* n_valid,
                                 float* loss_out, float grad_scale, long long T, int V, long long ld,
                                 long long ignore_index, int write_grad, void* stream) {
+  TPLR_ENTER();
   if (T <= 0) return 0;
   if (ld % 8) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
@@ -392,12 +398,14 @@ __global__ void __launch_bounds__(256) embedding_bwd_kernel(const long long* __r
   }
 }
 TPLR_API int tplr_embedding_fwd(const long long* tok, const void* table, void* out, long long T, int D, int V, void* stream) {
+  TPLR_ENTER();
   if (D % 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   embedding_fwd_kernel<<<ew_grid(T * (D / 8)), 256, 0, (cudaStream_t)stream>>>(tok, (const bf16*)table, (bf16*)out, T, D, V);
   return (int)cudaGetLastError();
 }
 TPLR_API int tplr_embedding_bwd(const long long* tok, const void* dy, float* dtable, long long T, int D, int V, void* stream) {
+  TPLR_ENTER();
   if (D % 8) return (int)cudaErrorInvalidValue;
   if (T <= 0) return 0;
   embedding_bwd_kernel<<<ew_grid(T * (D / 8)), 256, 0, (cudaStream_t)stream>>>(tok, (const bf16*)dy, dtable, T, D, V);
@@ -427,6 +435,7 @@ __global__ void __launch_bounds__(512) sumsq_partial_kernel(const float* __restr
 // partial must hold tplr_sumsq_blocks() floats; out[0] = sum(x^2). x must be 16-byte aligned.
 TPLR_API int tplr_sumsq_blocks() { return tplr_sm_count() * 4; }
 TPLR_API int tplr_sumsq(const float* x, long long n, float* partial, float* out, void* stream) {
+  TPLR_ENTER();
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = tplr_sumsq_blocks();
   sumsq_partial_kernel<<<blocks, 512, 0, st>>>(x, n, partial);
@@ -490,6 +499,7 @@ TPLR_API int tplr_adamw(float* p, float* m, float* v, float* g, void* const* sha
                         long long n, float lr, float b1, float b2, float eps, float wd, int step,
                         float grad_scale, float max_norm, const float* gnorm_sq, int zero_grad,
                         void* stream) {
+  TPLR_ENTER();
   if (n % 4 || n_shadow > TPLR_MAX_PEERS) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
   AdamArgs a;
@@ -515,6 +525,7 @@ __global__ void __launch_bounds__(256) cast_bf16_kernel(const float* __restrict_
   }
 }
 TPLR_API int tplr_cast_bf16(const float* src, void* dst, long long n, void* stream) {
+  TPLR_ENTER();
   if (n % 4) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
   cast_bf16_kernel<<<ew_grid(n / 4), 256, 0, (cudaStream_t)stream>>>(src, (bf16*)dst, n / 4);

@@ -340,6 +340,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, 
 TPLR_API int tplr_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                             long long ldb, long long ldc, int a_mn, int b_mn, int epi, unsigned int* status,
                             int max_ctas, void* stream) {
+  TPLR_ENTER();
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return (int)cudaErrorInvalidValue;
   CUtensorMap ta, tb;

@@ -9,6 +9,7 @@
 #include <string.h>
 
 TPLR_API int tplr_heap_alloc(unsigned long long bytes, void** out) {
+  TPLR_ENTER();
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, bytes);
   if (e != cudaSuccess) return (int)e;
@@ -16,21 +17,25 @@ TPLR_API int tplr_heap_alloc(unsigned long long bytes, void** out) {
   *out = p;
   return (int)e;
 }
-TPLR_API int tplr_heap_free(void* p) { return (int)cudaFree(p); }
+TPLR_API int tplr_heap_free(void* p) {
+  TPLR_ENTER(); return (int)cudaFree(p); }
 
 TPLR_API int tplr_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
 TPLR_API int tplr_ipc_get(void* p, void* handle_out) {
+  TPLR_ENTER();
   cudaIpcMemHandle_t h;
   cudaError_t e = cudaIpcGetMemHandle(&h, p);
   if (e == cudaSuccess) memcpy(handle_out, &h, sizeof(h));
   return (int)e;
 }
 TPLR_API int tplr_ipc_open(const void* handle, void** out) {
+  TPLR_ENTER();
   cudaIpcMemHandle_t h;
   memcpy(&h, handle, sizeof(h));
   return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
 }
-TPLR_API int tplr_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+TPLR_API int tplr_ipc_close(void* p) {
+  TPLR_ENTER(); return (int)cudaIpcCloseMemHandle(p); }
 
 // ------------------------------------------------------------------------------------- //
 // Flag barrier. Every rank owns an array of `n_ranks` 64-bit slots in symmetric memory.
@@ -72,6 +77,7 @@ __global__ void barrier_kernel(const BarrierArgs a) {
 
 TPLR_API int tplr_barrier(void* const* flag_ptrs, int n_ranks, int my_rank, unsigned long long epoch,
                           unsigned long long timeout_ns, unsigned int* status, void* stream) {
+  TPLR_ENTER();
   if (n_ranks > TPLR_MAX_PEERS || n_ranks <= 0) return (int)cudaErrorInvalidValue;
   BarrierArgs a;
   for (int i = 0; i < n_ranks; ++i) a.flags[i] = (unsigned long long*)flag_ptrs[i];
@@ -106,6 +112,7 @@ __global__ void __launch_bounds__(256) reduce_shards_kernel(const ReduceArgs a) 
 
 TPLR_API int tplr_reduce_shards(void* const* bufs, int n_ranks, int my_rank, long long lo, long long n,
                                 void* stream) {
+  TPLR_ENTER();
   if (n_ranks > TPLR_MAX_PEERS || (n % 4) || (lo % 4)) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
   ReduceArgs a;
@@ -133,6 +140,7 @@ __global__ void __launch_bounds__(256) push_copy_kernel(const PushArgs a) {
   }
 }
 TPLR_API int tplr_push_copy(const void* src, void* const* dsts, int n_dst, long long bytes, void* stream) {
+  TPLR_ENTER();
   if (n_dst > TPLR_MAX_PEERS || (bytes % 16)) return (int)cudaErrorInvalidValue;
   if (bytes <= 0 || n_dst <= 0) return 0;
   PushArgs a;

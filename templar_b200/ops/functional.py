@@ -111,8 +111,11 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         ctx.main_grad = main_grad
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
-        return y.view(*x.shape[:-1], w.shape[0])
+        # the output is allocated in its final shape (not returned as a view) so that in-place
+        # consumers such as RoPE may mark it dirty
+        y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, w, out=y.view(-1, w.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,162 @@
+"""Per-kernel microbenchmarks with CUDA-event timing and roofline fractions.
+
+    python -m templar_b200.ops.microbench gemm      [--m 16384 --n 8192 --k 2048] [--layout nt|nn|tn] [--compare]
+    python -m templar_b200.ops.microbench compress  [--model 1B] [--topk 32]
+    python -m templar_b200.ops.microbench aggregate [--model 1B] [--peers 8] [--topk 32]
+    python -m templar_b200.ops.microbench elementwise
+
+Each case warms up, flushes L2 between timed iterations (a 256 MB write), times with CUDA
+events on the launching stream and prints one JSON line with the achieved bandwidth / FLOP
+rate and its fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the repo root when
+present, otherwise the stated fallback).  ``--small`` shrinks a case for profiler captures.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import functional as OF
+from . import native
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return dict(FALLBACK_PEAKS)
+
+
+_flush_buf = None
+
+
+def flush_l2():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(a):
+    M, N, K = a.m, a.n, a.k
+    a_mn, b_mn = {"nt": (False, False), "nn": (False, True), "tn": (True, True)}[a.layout]
+    A = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
+    out_dtype = torch.float32 if a.layout == "tn" else torch.bfloat16
+    out = torch.zeros(M, N, device="cuda", dtype=out_dtype)
+    OF.set_gemm_backend("tcgen05")
+    med, best = time_ms(lambda: OF.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=(a.layout == "tn")), a.iters)
+    pk = peaks()
+    fl = 2.0 * M * N * K
+    rec = {"case": "gemm", "layout": a.layout, "M": M, "N": N, "K": K, "ms_median": med, "ms_best": best,
+           "tflops": fl / med / 1e9, "frac_of_peak": fl / med / 1e9 / pk["bf16_tflops"], "peaks": pk["source"],
+           "status": int(OF.status_word("cuda").item())}
+    if a.compare:
+        Am = A.t() if a_mn else A
+        Bm = B if b_mn else B.t()
+        med_c, _ = time_ms(lambda: torch.matmul(Am, Bm), a.iters)
+        rec["cublas_ms"] = med_c
+        rec["vs_cublas"] = med_c / med
+    print(json.dumps(rec))
+
+
+def _engine(model_name, topk, peers):
+    from ..models.llama import PRESETS, build_model
+    from ..parallel.window_engine import EngineConfig, WindowEngine
+
+    model = build_model(PRESETS[model_name], device="cuda", dtype=torch.bfloat16, seed=0)
+    return WindowEngine(model, EngineConfig(topk=topk, max_peers=peers), device="cuda")
+
+
+def bench_compress(a):
+    eng = _engine(a.model, a.topk, 1)
+    eng.snapshot()
+    eng.store.master_shard.add_(torch.randn_like(eng.store.master_shard) * 1e-3)
+    med, best = time_ms(lambda: eng.compress(), a.iters)
+    n = eng.layout.total
+    byts = n * 4 * 4  # theta0 + theta + e read, e written
+    pk = peaks()
+    print(json.dumps({"case": "compress", "model": a.model, "topk": a.topk, "elements": n, "ms_median": med,
+                      "ms_best": best, "gbs": byts / med / 1e6, "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"],
+                      "peaks": pk["source"], "status": eng.check_status()}))
+
+
+def bench_aggregate(a):
+    from ..utils.synthetic import synthetic_payload
+
+    eng = _engine(a.model, a.topk, a.peers)
+    eng.snapshot()
+    for j in range(a.peers):
+        eng.load_peer_payload(j, synthetic_payload(eng.layout, 7 + j, device="cuda"))
+    med, best = time_ms(lambda: eng.outer_step(a.peers, include_own=False), a.iters)
+    n = eng.layout.total
+    byts = n * (4 + 4 + 2) + a.peers * (eng.layout.idx_bytes + eng.layout.val_elems * 4) * 2
+    pk = peaks()
+    print(json.dumps({"case": "aggregate", "model": a.model, "peers": a.peers, "topk": a.topk, "ms_median": med,
+                      "ms_best": best, "gbs": byts / med / 1e6, "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"],
+                      "peaks": pk["source"], "status": eng.check_status()}))
+
+
+def bench_elementwise(a):
+    pk = peaks()
+    T, D, F, V = (2048, 2048, 8192, 32000) if a.small else (16384, 2048, 8192, 32000)
+    x = torch.randn(T, D, device="cuda").to(torch.bfloat16)
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    h = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, V, device="cuda").to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    cases = {
+        "rmsnorm_fwd": (lambda: OF.rmsnorm(x, w), T * D * 2 * 2),
+        "swiglu_fwd": (lambda: OF.swiglu(h), T * F * 2 * 3),
+        "cross_entropy_fwd_bwd": (lambda: OF.cross_entropy(logits.requires_grad_(), labels), T * V * 2 * 3),
+    }
+    for name, (fn, byts) in cases.items():
+        med, best = time_ms(fn, a.iters)
+        print(json.dumps({"case": name, "ms_median": med, "gbs": byts / med / 1e6,
+                          "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"], "peaks": pk["source"]}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "compress", "aggregate", "elementwise"])
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--model", default="1B")
+    ap.add_argument("--topk", type=int, default=32)
+    ap.add_argument("--peers", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    {"gemm": bench_gemm, "compress": bench_compress, "aggregate": bench_aggregate,
+     "elementwise": bench_elementwise}[a.case](a)
+
+
+if __name__ == "__main__":
+    main()

@@ -140,14 +140,14 @@ class WindowEngine:
             shadows = self._compute_shadow_ptrs()
             native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                                       gshard.data_ptr(), native.ptr_array(shadows), len(shadows), n, lr, cfg.betas[0],
-                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0, cfg.max_grad_norm,
-                                      self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
+                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
+                                      cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
             if self.world_size > 1:
                 self._barrier()
                 st.grad.zero_()
             return
-        # CPU path (same arithmetic)
-        g = gshard
+        # CPU path (same arithmetic); gradients were summed over ranks, the mean is what is applied
+        g = gshard / self.world_size
         self.gnorm_sq.copy_((g * g).sum().reshape(1))
         if self.world_size > 1:
             dist.all_reduce(self.gnorm_sq, group=self.group)
