@@ -1,0 +1,107 @@
+"""Worker launched by test_gpu_multi.py under torchrun (one process per GPU)."""
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from templar_b200.models.llama import ModelArgs, build_model  # noqa: E402
+from templar_b200.ops import functional as OF  # noqa: E402
+from templar_b200.parallel.symmetric import SymmetricHeap  # noqa: E402
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine  # noqa: E402
+from templar_b200.utils.synthetic import synthetic_payload  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    out = {}
+    heap = SymmetricHeap.create(dev, rank, world, timeout_s=20.0)
+
+    # 1. peer stores / loads and the flag barrier
+    buf = heap.alloc(1024, torch.float32)
+    buf.fill_(float(rank + 1))
+    heap.barrier()
+    from templar_b200.ops import native
+    dst = [heap.peer_ptr(buf, (rank + 1) % world) + 512 * 4]
+    native.check(native.lib().tplr_push_copy(buf.data_ptr(), native.ptr_array(dst), 1, 512 * 4, native.stream_ptr()), "push")
+    heap.barrier()
+    torch.cuda.synchronize()
+    left = (rank - 1) % world
+    out["push_ok"] = bool((buf[512:] == float(left + 1)).all().item() and (buf[:512] == float(rank + 1)).all().item())
+    heap.check()
+
+    # 2. a bounded wait that nothing satisfies: rank 0 waits on a barrier the others skip
+    heap.timeout_ns = int(0.3e9)
+    if rank == 0:
+        heap.barrier()
+        torch.cuda.synchronize()
+        try:
+            heap.check()
+            out["timeout_detected"] = False
+        except TimeoutError:
+            out["timeout_detected"] = True
+    else:
+        heap._epoch += 1          # stay in step with rank 0's epoch counter without arriving
+        out["timeout_detected"] = True
+    heap.timeout_ns = int(20e9)
+    dist.barrier()
+    heap.barrier()                # the late arrival of the skipped epoch is harmless: epochs only grow
+    torch.cuda.synchronize()
+    heap.check()
+
+    # 3. sharded window == single-rank window on the same global batch
+    OF.set_gemm_backend(os.environ.get("TPLR_TEST_GEMM", "tcgen05"))
+    args = ModelArgs(dim=256, n_layers=2, n_heads=4, vocab_size=1024, intermediate_size=512, max_seq_len=128)
+    cfg = EngineConfig(topk=8, max_peers=4, inner_lr=1e-3, outer_lr=0.5)
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, 1024, (world, 2, 4, 129), generator=g)   # [rank, micro, batch, seq+1]
+
+    def run(engine, my_ranks, hp):
+        engine.snapshot()
+        for m in range(2):
+            for r in my_ranks:
+                t = toks[r, m].to(dev)
+                engine.micro_step(t[:, :-1], t[:, 1:], 0.5 / (1 if engine.world_size > 1 else world))
+        engine.optimizer_step()
+        own = None
+        if engine.heap is not None:
+            own = (engine.heap.peer_ptr(engine.own_idx, 0), engine.heap.peer_ptr(engine.own_val, 0))
+        engine.compress(own_slot_ptrs=own)
+        for j in range(1, 4):
+            if j % engine.world_size == engine.rank:
+                engine.load_peer_payload(j // engine.world_size, synthetic_payload(engine.layout, 50 + j, device=dev))
+        engine._barrier()
+        engine.outer_step(4)
+        torch.cuda.synchronize()
+
+    model = build_model(args, device=dev, dtype=torch.bfloat16, seed=5)
+    eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
+    run(eng, [rank], heap)
+    heap.check()
+    out["status"] = eng.check_status()
+    ref_model = build_model(args, device=dev, dtype=torch.bfloat16, seed=5)
+    ref = WindowEngine(ref_model, cfg, device=dev)
+    run(ref, list(range(world)), None)
+    lo, hi = eng.store.lo, eng.store.hi
+    diff = (eng.store.master_shard - ref.store.master_shard[lo:hi]).abs().max().item()
+    scale = ref.store.master_shard.abs().max().item()
+    cdiff = (eng.store.compute.float() - ref.store.compute.float()).abs().max().item()
+    out["master_max_diff"], out["compute_max_diff"], out["scale"] = diff, cdiff, scale
+    moved = (ref.store.master_shard - ref.theta0).abs().max().item()
+    out["moved"] = moved
+    res = [None] * world
+    dist.all_gather_object(res, out)
+    if rank == 0:
+        print("RESULT " + json.dumps(res))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,39 @@
+"""Multi-GPU tier: peer-memory runtime, bounded waits and sharded-window equivalence.
+
+Spawns one process per GPU with torchrun (NCCL for the control plane, NVLS off, own kernels on
+plain peer loads/stores).  No test here faults, traps or hangs a GPU: the failure that is
+exercised is a barrier that a rank skips, which the waiting kernel turns into a status word.
+"""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, extra_env=None):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29731", os.path.join(HERE, "_multi_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert r.returncode == 0 and lines, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_runtime_and_window():
+    res = _run(2)
+    for r in res:
+        assert r["push_ok"], r
+        assert r["timeout_detected"], r
+        assert r["status"] == 0, r
+        assert r["moved"] > 1e-4, r
+        assert r["master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
+        assert r["compute_max_diff"] < 2e-2 * max(r["scale"], 1.0), r
