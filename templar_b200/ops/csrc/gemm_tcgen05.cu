@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <mutex>
+#include <stdio.h>
 
 namespace {
 
@@ -314,6 +315,17 @@ bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long oute
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // Driver-API call on a thread (e.g. an autograd worker) that has made no runtime call yet:
+    // bind the primary context of the thread's current device and encode again.
+    cudaFree(0);
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "[tplr] cuTensorMapEncodeTiled failed (%d): ptr=%p inner=%lld outer=%lld ld=%lld box=%dx%d\n",
+            (int)r, ptr, inner, outer, ld, box_inner, box_outer);
   return r == CUDA_SUCCESS;
 }
 
@@ -342,11 +354,11 @@ TPLR_API int tplr_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                             int max_ctas, void* stream) {
   TPLR_ENTER();
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return (int)cudaErrorInvalidValue;
+  // negative return codes are this library's own argument errors (CUDA errors are positive)
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -101;
   CUtensorMap ta, tb;
-  bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
-  ok = ok && (b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN));
-  if (!ok) return (int)cudaErrorInvalidValue;
+  if (!(a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM))) return -102;
+  if (!(b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN))) return -103;
   cudaStream_t st = (cudaStream_t)stream;
 #define TPLR_GEMM_CASE(AM, BMJ, E) \
   if (a_mn == AM && b_mn == BMJ && epi == E) return launch<AM != 0, BMJ != 0, E>(ta, tb, C, M, N, K, ldc, status, max_ctas, st);
@@ -355,5 +367,5 @@ TPLR_API int tplr_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   TPLR_GEMM_CASE(1, 1, 0) TPLR_GEMM_CASE(1, 1, 1) TPLR_GEMM_CASE(1, 1, 2)
   TPLR_GEMM_CASE(1, 0, 0) TPLR_GEMM_CASE(1, 0, 1) TPLR_GEMM_CASE(1, 0, 2)
 #undef TPLR_GEMM_CASE
-  return (int)cudaErrorInvalidValue;
+  return -104;
 }

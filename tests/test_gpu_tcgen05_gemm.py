@@ -56,3 +56,26 @@ def test_linear_backward_matches_autograd():
     (xf @ wf.t()).backward(dy.float())
     assert torch.allclose(x.grad.float(), xf.grad, atol=0.1, rtol=3e-2)
     assert torch.allclose(w.grad.float(), wf.grad, atol=0.5, rtol=3e-2)
+
+
+def test_gemm_from_a_fresh_thread():
+    """The tensor-map encode is a driver call; a thread that has not touched CUDA yet (like an
+    autograd worker) must still be able to launch the GEMM."""
+    import threading
+
+    A = torch.randn(256, 128, device=DEV).to(torch.bfloat16)
+    B = torch.randn(512, 128, device=DEV).to(torch.bfloat16)
+    box = {}
+
+    def work():
+        try:
+            box["out"] = OF.gemm(A, B)
+        except Exception as e:  # noqa: BLE001
+            box["err"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert "err" not in box, box.get("err")
+    assert (box["out"].float() - A.float() @ B.float().t()).abs().max().item() < 0.5
