@@ -100,17 +100,30 @@ class WindowEngine:
         self.gnorm_sq = z(1)
         self._sumsq_scratch = z(native.lib().tplr_sumsq_blocks() if self.cuda else 1)
         self.status = OF.status_word(self.device) if self.cuda else torch.zeros(1, dtype=torch.int32)
-        self.window_losses: list[torch.Tensor] = []
+        self.window_open = False
+        model._window_engine = self
 
     def _slots(self) -> int:
+        """Peer-payload slots held by this rank: with a symmetric heap the peers are spread
+        round-robin over the ranks, otherwise every rank keeps all of them."""
+        if self.heap is None:
+            return self.cfg.max_peers
         return -(-self.cfg.max_peers // self.world_size)
+
+    def slot_of(self, peer: int) -> tuple[int, int]:
+        """(owner rank, slot index) of peer ``peer``'s payload."""
+        if self.heap is None:
+            return self.rank, peer
+        return peer % self.world_size, peer // self.world_size
 
     # ------------------------------------------------------------------------------------ #
     # inner loop
     # ------------------------------------------------------------------------------------ #
     @torch.no_grad()
     def snapshot(self) -> None:
+        """theta0 <- master: opens a window (the next compress / outer step refer to this snapshot)."""
         self.theta0.copy_(self.store.master_shard)
+        self.window_open = True
 
     def zero_grad(self) -> None:
         self.store.grad.zero_()
@@ -296,7 +309,7 @@ class WindowEngine:
                 owner = 0
                 ib, vb = self.own_idx, self.own_val
             else:
-                owner, slot = j % self.world_size, j // self.world_size
+                owner, slot = self.slot_of(j)
                 ib, vb = self.peer_idx[slot], self.peer_val[slot]
             if self.heap is not None and self.world_size > 1:
                 idx_ptrs.append(self.heap.peer_ptr(ib, owner))
@@ -371,7 +384,7 @@ class WindowEngine:
             if include_own and j == 0:
                 bufs.append((self.own_idx, self.own_val))
             else:
-                bufs.append((self.peer_idx[j // self.world_size], self.peer_val[j // self.world_size]))
+                bufs.append((self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]]))
         base_buf = self.theta0 if base == "theta0" else st.master_shard
         for s in L.specs:
             tr.register_shape(s.shape)
@@ -409,6 +422,93 @@ class WindowEngine:
                 self._allgather_compute_native()
         else:
             self._publish_compute()
+
+    # ------------------------------------------------------------------------------------ #
+    # payload distribution and state dicts
+    # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def pack_payload(self, payload: dict, device=None):
+        """Reference-format dict (one peer) -> (idx_flat uint8, val_flat) in this layout."""
+        L = self.layout
+        device = device or "cpu"
+        idx = torch.zeros(L.idx_bytes, dtype=torch.uint8, device=device)
+        val = torch.zeros(L.val_elems, dtype=self.cfg.val_dtype, device=device)
+        for s in L.specs:
+            i, v = L.payload_views(idx, val, s.name)
+            i.copy_(payload[s.name + "idxs"].reshape(-1))
+            v.copy_(payload[s.name + "vals"].reshape(v.shape))
+        return idx, val
+
+    @torch.no_grad()
+    def distribute_peer_payloads(self, state_dict: dict | None, n_peers: int) -> None:
+        """Rank 0 holds the gathered per-key lists; peer j's payload ends up in ``slot_of(j)``.
+        With a symmetric heap rank 0 stores straight into the owner's slot over NVLink; without
+        one the flat buffers are broadcast and every rank keeps all peers."""
+        L = self.layout
+        for j in range(n_peers):
+            owner, slot = self.slot_of(j)
+            if self.heap is not None:
+                if self.rank == 0:
+                    one = {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in state_dict.items()
+                           if not k.endswith("quant_params")}
+                    idx, val = self.pack_payload(one, device=self.device)
+                    for src, dst in ((idx, self.peer_idx[slot]), (val, self.peer_val[slot])):
+                        native.check(native.lib().tplr_push_copy(
+                            src.data_ptr(), native.ptr_array([self.heap.peer_ptr(dst, owner)]), 1,
+                            -(-src.numel() * src.element_size() // 16) * 16, native.stream_ptr()), "push_copy")
+            else:
+                if self.rank == 0:
+                    one = {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in state_dict.items()
+                           if not k.endswith("quant_params")}
+                    idx, val = self.pack_payload(one, device=self.device)
+                    self.peer_idx[slot].copy_(idx)
+                    self.peer_val[slot].copy_(val)
+                if self.world_size > 1:
+                    dist.broadcast(self.peer_idx[slot], src=0, group=self.group)
+                    dist.broadcast(self.peer_val[slot], src=0, group=self.group)
+        self._barrier()
+
+    @torch.no_grad()
+    def full_master(self) -> torch.Tensor:
+        """The whole fp32 master vector on every rank (shards exchanged by broadcast)."""
+        st = self.store
+        if self.world_size == 1:
+            return st.master_shard
+        full = torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
+        full[st.lo:st.hi].copy_(st.master_shard)
+        for r in range(self.world_size):
+            a, b = self.layout.shard_range(r)
+            dist.broadcast(full[a:b], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                           group=self.group)
+        return full
+
+    @torch.no_grad()
+    def full_state_dict(self) -> dict:
+        """fp32 tensors keyed like ``model.state_dict()`` (parameters from the master weights, buffers as is)."""
+        full = self.full_master()
+        out = {}
+        for k, v in self.model.state_dict().items():
+            s = self.layout.by_name.get(k)
+            out[k] = full[s.offset: s.offset + s.numel].view(s.shape) if s is not None else v
+        return out
+
+    @torch.no_grad()
+    def load_full_state_dict(self, state: dict) -> None:
+        st = self.store
+        for s in self.layout.specs:
+            if s.name not in state:
+                continue
+            src = state[s.name].reshape(-1).to(device=self.device, dtype=torch.float32)
+            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
+            if a < b:
+                st.master_shard[a - st.lo: b - st.lo].copy_(src[a - s.offset: b - s.offset])
+            if st.compute is not st.master_shard:
+                st.compute[s.offset: s.offset + s.numel].copy_(src.to(st.compute.dtype))
+        for k, v in state.items():
+            if k not in self.layout.by_name:
+                buf = dict(self.model.named_buffers()).get(k)
+                if buf is not None and torch.is_tensor(v):
+                    buf.copy_(v.to(buf.device))
 
     def check_status(self) -> int:
         """Reads (and clears) the kernel status word — a host sync; call between windows."""
