@@ -147,7 +147,9 @@ def main(a) -> None:
             node.owned_params.add(n)
             node.error_feedback[n] = None
             node.error_feedback_cpu_buffers[n] = torch.empty(p.shape, device="cpu", pin_memory=has_cuda)
-        enc = node.transformer.encode(torch.empty(p.shape, dtype=torch.float16, device=dev), use_dct=True)
+        # shape dry-run as in neurons/miner.py:245-254; without the DCT (fp16 dummy x fp32 basis would
+        # not multiply) — the chunk grid does not depend on the transform
+        enc = node.transformer.encode(torch.empty(p.shape, dtype=torch.float16, device=dev), use_dct=False)
         _, _, xshape, totalk = node.compressor.compress(enc, node.hparams.topk_compression)
         node.xshapes[n], node.totalks[n] = xshape, totalk
     # data: the reference's own sampler + DataLoader over a host-resident synthetic dataset
