@@ -9,6 +9,7 @@
 // components/loss.py:18-22) and torch.optim.AdamW(fused=True) + clip_grad_norm_
 // (neurons/trainer.py:280-298, :940).
 #include "common.cuh"
+#include "no_alloc.h"
 
 typedef __nv_bfloat16 bf16;
 
@@ -529,5 +530,57 @@ TPLR_API int tplr_cast_bf16(const float* src, void* dst, long long n, void* stre
   if (n % 4) return (int)cudaErrorInvalidValue;
   if (n <= 0) return 0;
   cast_bf16_kernel<<<ew_grid(n / 4), 256, 0, (cudaStream_t)stream>>>(src, (bf16*)dst, n / 4);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// Cross entropy without caller-provided scratch (see no_alloc.h). The per-row losses and the
+// valid-row counter live in a file-scope device array. In host code the array's name is only a
+// handle: its device address is looked up once per device with cudaGetSymbolAddress (with that
+// device current) and that pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------- //
+// layout: word 0 is the valid-row counter (int), words 64.. are the per-row losses (256-byte aligned)
+#define CE_SCRATCH_HEADER 64
+static __device__ __align__(256) float g_ce_scratch[CE_SCRATCH_HEADER + TPLR_CE_NOALLOC_MAX_ROWS];
+
+#define TPLR_MAX_DEVICES 64
+static float* g_ce_scratch_addr[TPLR_MAX_DEVICES];   // null = not looked up yet on that device
+
+static int ce_scratch_for_current_device(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= TPLR_MAX_DEVICES) return TPLR_ERR_NOALLOC_BAD_ARG;
+  if (!g_ce_scratch_addr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_ce_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_ce_scratch_addr[dev] = p;
+  }
+  *out = g_ce_scratch_addr[dev];
+  return 0;
+}
+
+TPLR_API long long tplr_cross_entropy_noalloc_max_rows(void) { return TPLR_CE_NOALLOC_MAX_ROWS; }
+
+TPLR_API int tplr_cross_entropy_noalloc(void* logits, const long long* labels, float* loss_out, float grad_scale,
+                                        long long rows, int vocab, long long ld, long long ignore_index,
+                                        int write_grad, void* stream) {
+  TPLR_ENTER();
+  if (rows > TPLR_CE_NOALLOC_MAX_ROWS) return TPLR_ERR_NOALLOC_TOO_LARGE;
+  if (rows < 0 || vocab <= 0 || (ld % 8) || !logits || !labels || !loss_out) return TPLR_ERR_NOALLOC_BAD_ARG;
+  if (rows == 0) return 0;
+  float* sc = nullptr;
+  const int rc = ce_scratch_for_current_device(&sc);
+  if (rc != 0) return rc;
+  int* n_valid = reinterpret_cast<int*>(sc);
+  float* losses = sc + CE_SCRATCH_HEADER;
+  cudaStream_t st = (cudaStream_t)stream;
+  // count_valid_kernel overwrites n_valid and ce_kernel writes losses[0..rows) before
+  // sum_rows_kernel reads them, so whatever an earlier call left in the array is never used.
+  count_valid_kernel<<<1, 1024, 0, st>>>(labels, rows, ignore_index, n_valid);
+  ce_kernel<<<(unsigned)rows, 512, 0, st>>>((bf16*)logits, labels, losses, n_valid, grad_scale, vocab, ld,
+                                            ignore_index, write_grad);
+  sum_rows_kernel<<<1, 1024, 0, st>>>(losses, rows, n_valid, 1.f, loss_out);
   return (int)cudaGetLastError();
 }
