@@ -48,7 +48,7 @@ def _hparams(a, vocab: int, world: int, compile_blocks: bool):
         model_size=f"bench-{a.model}", sequence_length=a.seq_len, micro_batch_size=a.micro_batch,
         batch_size=a.micro_batch * a.accum * world, target_batch_size=a.micro_batch * a.accum * world,
         inner_steps=1, outer_learning_rate=0.4, momentum_decay=0.95, topk_compression=a.topk, target_chunk=64,
-        use_dct=True, weight_decay=0.1, learning_rate=1e-3, blocks_per_window=10, anneal_mode={"enabled": False},
+        use_dct=True, quantization_bins=256, quantization_range=6, weight_decay=0.1, learning_rate=1e-3, blocks_per_window=10, anneal_mode={"enabled": False},
         optimizer={"type": "adamw", "adamw": {"betas": [0.9, 0.95], "eps": 1e-8, "weight_decay": 0.1,
                                               "learning_rate": 1.17e-4,
                                               "scheduler": {"warmup_steps": 1500, "warmup_inner_steps": 0, "t_max": 140000,
@@ -137,7 +137,9 @@ def main(a) -> None:
             dist.destroy_process_group()
         return _unavailable(f"reference model_factory failed on the installed torchtitan: {type(e).__name__}: {e}")
     node.transformer = tplr.compress.ChunkingTransformer(node.model, target_chunk=node.hparams.target_chunk)
-    node.compressor = tplr.compress.TopKCompressor(use_quantization=False)
+    # neurons/miner.py:214-221: the reference always quantises payload values to 8 bit
+    node.compressor = tplr.compress.TopKCompressor(use_quantization=True, quantization_bins=node.hparams.quantization_bins,
+                                                   quantization_range=node.hparams.quantization_range)
     node.init_optimizers_schedulers()
     node.offload_optimizer = False
     node.error_feedback, node.error_feedback_cpu_buffers, node.owned_params = {}, {}, set()
@@ -150,7 +152,7 @@ def main(a) -> None:
         # shape dry-run as in neurons/miner.py:245-254; without the DCT (fp16 dummy x fp32 basis would
         # not multiply) — the chunk grid does not depend on the transform
         enc = node.transformer.encode(torch.empty(p.shape, dtype=torch.float16, device=dev), use_dct=False)
-        _, _, xshape, totalk = node.compressor.compress(enc, node.hparams.topk_compression)
+        _, _, xshape, totalk, _ = node.compressor.compress(enc, node.hparams.topk_compression)
         node.xshapes[n], node.totalks[n] = xshape, totalk
     # data: the reference's own sampler + DataLoader over a host-resident synthetic dataset
     B, S, A = a.micro_batch, a.seq_len, a.accum
@@ -168,8 +170,13 @@ def main(a) -> None:
     for j in range(1, a.peers):
         idx, val = synthetic_payload(layout, 99 + j, device=dev)
         idx, val = pin(idx.cpu()), pin(val.cpu())
-        peers_host.append({n: layout.payload_views(idx, val, n) for n, _ in shapes})
-    h2d_bytes = sum(i.numel() + v.numel() * 4 for d in peers_host for i, v in d.values()) // max(world, 1)
+        entry = {}
+        for n, _ in shapes:
+            i_view, v_view = layout.payload_views(idx, val, n)
+            q, qp = node.compressor._quantize_values(v_view.to(dev))     # the reference's own wire format
+            entry[n] = (pin(i_view.cpu().clone()), pin(q.cpu()), (qp[0].cpu(), qp[1], qp[2], qp[3].cpu(), qp[4]))
+        peers_host.append(entry)
+    h2d_bytes = sum(i.numel() + v.numel() for d in peers_host for i, v, _ in d.values())
 
     def has_dstate(model):
         return hasattr(node, "offload_inner_optimizer_states")
@@ -191,11 +198,13 @@ def main(a) -> None:
             for n, _ in shapes:
                 idxs = [own[n + "idxs"].to(dev, non_blocking=True)]
                 vals = [own[n + "vals"].to(dev, non_blocking=True)]
+                qps = [own[n + "quant_params"]]
                 for d in peers_host:
-                    i, v = d[n]
+                    i, v, qp = d[n]
                     idxs.append(i.to(dev, non_blocking=True))
                     vals.append(v.to(dev, non_blocking=True))
-                sd[n + "idxs"], sd[n + "vals"], sd[n + "quant_params"] = idxs, vals, [None] * len(idxs)
+                    qps.append(qp)
+                sd[n + "idxs"], sd[n + "vals"], sd[n + "quant_params"] = idxs, vals, qps
             gather_result = SimpleNamespace(state_dict=SimpleNamespace(**sd), uids=list(range(a.peers)),
                                             skipped_uids=[], success_rate=1.0)
         node.outer_step(gather_result)
@@ -249,6 +258,7 @@ def main(a) -> None:
             "config": {"model": f"torchtitan llama ({a.model})", "global_batch": B * A * world, "micro_batch": B,
                        "accum": A, "seq_len": S, "parallelism": f"fsdp2 dp_shard={world}", "peers": a.peers,
                        "topk": a.topk, "use_dct": True, "outer_update": "sgd", "compile": compile_blocks,
+                       "payload_values": "uint8 (256 bins) + per-tensor lookup, the reference's stock format",
                        "reference_version": tplr.__version__, "stubbed_packages": report["stubbed"]}}))
     if world > 1:
         dist.destroy_process_group()
