@@ -260,5 +260,5 @@ def main(a) -> None:
                        "topk": a.topk, "use_dct": True, "outer_update": "sgd", "compile": compile_blocks,
                        "payload_values": "uint8 (256 bins) + per-tensor lookup, the reference's stock format",
                        "reference_version": tplr.__version__, "stubbed_packages": report["stubbed"]}}))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
