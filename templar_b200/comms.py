@@ -103,9 +103,14 @@ class Comms(ChainManager):
         if "multiple" in cfg:
             cfg = random.choice(cfg["multiple"])
         cred = (cfg.get("credentials") or {}).get(access_type or "read") or {}
-        tag = f"{bucket_type}-{self.uid if self.uid is not None else 'self'}"
         account = cfg.get("account_id")
-        return Bucket(name=cfg.get("name") or account or f"local-{tag}",
+        if not account:
+            # offline: a per-uid account id that survives the 128-character chain commitment, where the
+            # bucket name is by construction the account id (the aggregator / dataset buckets are shared)
+            owner = self.uid if bucket_type == "gradients" and self.uid is not None else "shared"
+            account = f"{bucket_type}-{owner}-".ljust(32, "0")[:32]
+            cfg = {**cfg, "name": account}
+        return Bucket(name=cfg.get("name") or account,
                       account_id=_placeholder(account, 32, "a"),
                       access_key_id=_placeholder(cred.get("access_key_id"), 32, "k"),
                       secret_access_key=_placeholder(cred.get("secret_access_key"), 64, "s"))

@@ -141,6 +141,9 @@ def create_parallel_dims(world_size: int, hparams: SimpleNamespace,
         if v == 0:
             raise ValueError(f"{k} cannot be zero.")
     deg = {k: int(v) for k, v in deg.items()}
+    if deg["dp_shard"] == -1:       # "use whatever is left of the world": an addition to the reference's rules
+        rest = deg["dp_replicate"] * deg["tp_degree"] * deg["pp_degree"] * deg["cp_degree"]
+        deg["dp_shard"] = max(world_size // max(rest, 1), 1)
     if deg["dp_replicate"] > 1 and deg["dp_shard"] > 1:
         raise ValueError("Specify either torchtitan.dp_replicate or torchtitan.dp_shard, but not both.")
     if deg["dp_replicate"] > 1 and (deg["tp_degree"] > 1 or deg["pp_degree"] > 1 or deg["cp_degree"] > 1):

@@ -1,0 +1,64 @@
+"""Newton–Schulz orthogonalisation for Muon on the tcgen05 GEMM.
+
+Five quintic iterations with per-iteration coefficients (the schedule of the reference's
+src/tplr/muon/newton_schulz_triton.py:336-374):
+
+    A = X X^T                    "line 1"  -> ``gemm(X, X)``          (both operands K-major: one tensor, two roles)
+    B = b A + c A A              "line 2"  -> ``gemm(A, A)`` + axpby  (A is symmetric, so A A = A A^T)
+    X = a X + B X                "line 3"  -> ``gemm(B, X, b_mn=True)`` + axpby
+
+bf16 operands, fp32 accumulation in TMEM.  The reference runs lines 1-2 as Triton kernels and line 3
+through cuBLAS; here all three are the same hand-written kernel and no transposed copy is made.
+Batched inputs (leading dimensions) are processed matrix by matrix.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import functional as OF
+
+NS_CONSTS = [(4.0848, -6.8946, 2.9270), (3.9505, -6.3029, 2.6377), (3.7418, -5.5913, 2.3037),
+             (2.8769, -3.1427, 1.2046), (2.8366, -3.0525, 1.2012)]
+
+
+def _ns_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:
+    X = G.to(torch.bfloat16)
+    transposed = G.size(-2) > G.size(-1)
+    if transposed:
+        X = X.mT
+    X = (X / (X.float().norm() + epsilon).to(X.dtype)).contiguous()
+    for a, b, c in NS_CONSTS:
+        A = OF.gemm(X, X)                       # X X^T
+        AA = OF.gemm(A, A)                      # A A^T = A A
+        B = (b * A + c * AA).contiguous()
+        X = (a * X + OF.gemm(B, X, b_mn=True)).contiguous()
+    return X.mT if transposed else X
+
+
+@torch.no_grad()
+def newton_schulz(G: torch.Tensor, epsilon: float = 1e-7) -> torch.Tensor:
+    """Approximate ``U V^T`` of ``G = U S V^T`` (singular values pushed towards 1)."""
+    if G.ndim < 2:
+        raise ValueError("newton_schulz needs a matrix")
+    if G.ndim == 2:
+        return _ns_2d(G, epsilon)
+    flat = G.reshape(-1, G.size(-2), G.size(-1))
+    return torch.stack([_ns_2d(g, epsilon) for g in flat]).reshape(G.shape)
+
+
+def zeropower_via_newtonschulz5(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """Fixed-coefficient variant ``(3.4445, -4.7750, 2.0315)`` (plain PyTorch; kept for comparison)."""
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.bfloat16() if G.is_cuda else G.float()
+    t = G.size(-2) > G.size(-1)
+    if t:
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(steps):
+        A = X @ X.mT
+        X = a * X + (b * A + c * A @ A) @ X
+    return X.mT if t else X
+
+
+newton_schulz_triton = newton_schulz     # the name used by callers written against the reference

@@ -300,12 +300,19 @@ class WindowEngine:
         self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
         self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
 
-    def _peer_ptrs(self, n_peers: int, include_own: bool):
-        """Pointers of the n_peers payloads: peer 0 = this node's own payload when include_own,
-        the others live round-robin in the ranks' slots (peer j on rank j % world, slot j // world)."""
+    def _peer_list(self, n_peers, include_own: bool, peers=None) -> list[int]:
+        """Peer ids taking part: ``peers`` when given, else 0..n_peers-1; id -1 denotes this node's own payload."""
+        ids = list(peers) if peers is not None else list(range(n_peers))
+        if include_own and peers is None and ids:
+            ids[0] = -1
+        return ids
+
+    def _peer_ptrs(self, ids: list[int]):
+        """Pointers of the payloads: -1 = this node's own payload (held by rank 0), the others live
+        round-robin in the ranks' slots (peer j on rank j % world, slot j // world)."""
         idx_ptrs, val_ptrs = [], []
-        for j in range(n_peers):
-            if include_own and j == 0:
+        for j in ids:
+            if j < 0:
                 owner = 0
                 ib, vb = self.own_idx, self.own_val
             else:
@@ -320,29 +327,63 @@ class WindowEngine:
         return idx_ptrs, val_ptrs
 
     @torch.no_grad()
-    def outer_step(self, n_peers: int, *, lr: float | None = None, include_own: bool = True,
-                   clip_norm: bool = True, base: str = "theta0") -> None:
-        """Aggregate ``n_peers`` payloads and apply the outer update to the owned shard.
+    @torch.no_grad()
+    def compute_peer_norms(self, n_peers: int | None = None, *, include_own: bool = False, peers=None) -> torch.Tensor:
+        """Per-(peer, tensor) value norms, their per-tensor lower median, clip factors and skip flags
+        (all left on the device in ``peer_norms`` / ``median`` / ``clip`` / ``skip``).  Returns the medians."""
+        ids = self._peer_list(n_peers, include_own, peers)
+        np_ = self.layout.n_params
+        if not self.cuda:
+            norms = torch.zeros(len(ids), np_)
+            for a, j in enumerate(ids):
+                ib, vb = (self.own_idx, self.own_val) if j < 0 else (self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]])
+                for s in self.layout.specs:
+                    norms[a, s.index] = self.layout.payload_views(ib, vb, s.name)[1].float().norm()
+            med = norms.median(dim=0).values
+            self.peer_norms[: len(ids) * np_].copy_(norms.reshape(-1))
+            self.median.copy_(med)
+            self.clip[: len(ids) * np_].copy_(torch.clamp(med / (norms + 1e-8), max=1.0).reshape(-1))
+            self.skip.copy_((~torch.isfinite(norms).all(dim=0)).to(torch.int32))
+            return self.median
+        L = native.lib()
+        _, val_ptrs = self._peer_ptrs(ids)
+        vdt = {torch.float32: 0, torch.bfloat16: 1}[self.cfg.val_dtype]
+        stream = native.stream_ptr()
+        desc_full, n_full = self._desc_full
+        native.check(L.tplr_peer_sumsq(desc_full.data_ptr(), n_full, np_, len(ids), native.ptr_array(val_ptrs), vdt,
+                                       None, 0, self.sumsq_partial.data_ptr(), stream), "peer_sumsq")
+        native.check(L.tplr_clip_factors(self.sumsq_partial.data_ptr(), np_, len(ids), self.peer_norms.data_ptr(),
+                                         self.clip.data_ptr(), self.median.data_ptr(), self.skip.data_ptr(),
+                                         self.status.data_ptr(), stream), "clip_factors")
+        return self.median
+
+    @torch.no_grad()
+    def outer_step(self, n_peers: int | None = None, *, lr: float | None = None, include_own: bool = True,
+                   clip_norm: bool = True, base: str = "theta0", peers=None, clip_override: torch.Tensor | None = None) -> None:
+        """Aggregate the payloads of ``peers`` (default: peers 0..n_peers-1, peer 0 being this node's own
+        payload when ``include_own``) and apply the outer update to the owned shard.
 
         ``base='theta0'`` applies the update to the window-start snapshot (the miner's flow:
         restore, then outer step); ``base='theta'`` applies it to the current master.
+        ``clip_override`` ([len(peers), n_params] scale factors) replaces the median-norm clip.
         """
         cfg, st = self.cfg, self.store
         lr = cfg.outer_lr if lr is None else lr
+        ids = self._peer_list(n_peers, include_own, peers)
+        n_peers = len(ids)
+        if clip_override is not None:
+            self.clip[: clip_override.numel()].copy_(clip_override.reshape(-1).to(self.clip.dtype))
+            self.skip.zero_()
+        elif clip_norm:
+            self.compute_peer_norms(peers=ids)
+        use_clip = clip_norm or clip_override is not None
         if not self.cuda:
-            return self._outer_step_torch(n_peers, lr, include_own, clip_norm, base)
+            return self._outer_step_torch(ids, lr, use_clip, base)
         L = native.lib()
-        idx_ptrs, val_ptrs = self._peer_ptrs(n_peers, include_own)
+        idx_ptrs, val_ptrs = self._peer_ptrs(ids)
         vdt = {torch.float32: 0, torch.bfloat16: 1}[cfg.val_dtype]
         stream = native.stream_ptr()
         np_ = self.layout.n_params
-        if clip_norm:
-            desc_full, n_full = self._desc_full
-            native.check(L.tplr_peer_sumsq(desc_full.data_ptr(), n_full, np_, n_peers, native.ptr_array(val_ptrs), vdt,
-                                           None, 0, self.sumsq_partial.data_ptr(), stream), "peer_sumsq")
-            native.check(L.tplr_clip_factors(self.sumsq_partial.data_ptr(), np_, n_peers, self.peer_norms.data_ptr(),
-                                             self.clip.data_ptr(), self.median.data_ptr(), self.skip.data_ptr(),
-                                             self.status.data_ptr(), stream), "clip_factors")
         bias = st.lo * 4
         base_buf = self.theta0 if base == "theta0" else st.master_shard
         shadow = None
@@ -355,8 +396,8 @@ class WindowEngine:
                 continue
             native.check(L.tplr_aggregate_apply(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(), n_peers,
                                                 native.ptr_array(idx_ptrs), native.ptr_array(val_ptrs), vdt, None, 0, np_,
-                                                self.clip.data_ptr() if clip_norm else None,
-                                                self.skip.data_ptr() if clip_norm else None,
+                                                self.clip.data_ptr() if use_clip else None,
+                                                self.skip.data_ptr() if use_clip else None,
                                                 base_buf.data_ptr() - bias, st.master_shard.data_ptr() - bias, shadow, None,
                                                 lr, cfg.outer_weight_decay, int(cfg.use_dct), mode, int(not square),
                                                 self.status.data_ptr(), stream), "aggregate_apply")
@@ -375,24 +416,28 @@ class WindowEngine:
                      "push_copy")
         self._barrier()
 
-    def _outer_step_torch(self, n_peers, lr, include_own, clip_norm, base) -> None:
+    def _outer_step_torch(self, ids, lr, use_clip, base) -> None:
+        """CPU path: same result through :mod:`templar_b200.compress`, with the clip factors already in ``self.clip``."""
         cfg, st, L = self.cfg, self.store, self.layout
         tr = C.ChunkingTransformer(None, cfg.target_chunk)
         comp = C.TopKCompressor(use_quantization=False)
         bufs = []
-        for j in range(n_peers):
-            if include_own and j == 0:
+        for j in ids:
+            if j < 0:
                 bufs.append((self.own_idx, self.own_val))
             else:
                 bufs.append((self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]]))
         base_buf = self.theta0 if base == "theta0" else st.master_shard
+        clip = self.clip[: len(ids) * L.n_params].view(len(ids), L.n_params)
         for s in L.specs:
             tr.register_shape(s.shape)
             idxs, vals = zip(*(L.payload_views(ib, vb, s.name) for ib, vb in bufs))
-            vals = [v.float() for v in vals]
+            vals = [v.float() * (clip[a, s.index] if use_clip else 1.0) for a, v in enumerate(vals)]
             ref = torch.empty(s.shape, dtype=torch.float32, device=self.device)
+            if use_clip and bool(self.skip[s.index]):
+                vals = [v * float("nan") for v in vals]
             g = tr.decode(comp.batch_decompress(ref, list(idxs), list(vals), L.xshape(s.name), s.totalk,
-                                                clip_norm=clip_norm), use_dct=cfg.use_dct).reshape(-1)
+                                                clip_norm=False), use_dct=cfg.use_dct).reshape(-1)
             a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
             if a >= b:
                 continue
@@ -408,6 +453,21 @@ class WindowEngine:
     # ------------------------------------------------------------------------------------ #
     # validator: single-peer apply and restore
     # ------------------------------------------------------------------------------------ #
+    @torch.no_grad()
+    def apply_single_peer(self, peer: int, lr: float, median: torch.Tensor | None = None) -> None:
+        """theta <- theta0 - lr * decode(peer's payload), the peer's values clipped per tensor to
+        ``min(1, median / (norm + 1e-8))`` where ``median`` is the per-tensor median norm over the
+        gathered peers (validator scoring; reference neurons/validator.py:3563-3770)."""
+        np_ = self.layout.n_params
+        clip = None
+        if median is not None:
+            med = median.clone()
+            self.compute_peer_norms(peers=[peer])
+            clip = torch.clamp(med / (self.peer_norms[:np_] + 1e-8), max=1.0)
+            clip = torch.where(torch.isfinite(clip), clip, torch.zeros_like(clip))
+        self.outer_step(peers=[peer], lr=lr, include_own=False, clip_norm=False, base="theta0",
+                        clip_override=clip.view(1, np_) if clip is not None else None)
+
     @torch.no_grad()
     def restore(self) -> None:
         """master <- theta0 and compute copy refreshed (undo of an evaluation-time apply)."""
