@@ -1,0 +1,296 @@
+"""Comms over the in-memory / local stores, chain commitments, decorators, config and schemas.
+Failures are injected on the host (dropped, late, corrupt and malformed objects)."""
+
+import asyncio
+import os
+from datetime import datetime, timedelta, timezone
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import templar_b200 as tplr
+from templar_b200 import chain as chain_mod
+from templar_b200 import compress as C
+from templar_b200.backends.chain import StaticChain, StaticWallet
+from templar_b200.backends.store import LocalFSStore, MemoryStore, S3Store
+from templar_b200.schemas import Bucket
+
+
+def run(coro):
+    return asyncio.run(coro)
+
+
+def make_comms(uid, store, chain, topk=4):
+    hp = SimpleNamespace(topk_compression=topk, blocks_per_window=4, recent_windows=2, active_check_interval=1)
+    c = tplr.Comms(wallet=StaticWallet(f"hotkey-{uid}"), config=SimpleNamespace(netuid=3, device="cpu"), hparams=hp, uid=uid,
+                   store=store, subtensor=chain)
+    c.try_commit(c.wallet, c.bucket)
+    return c
+
+
+def payload(seed=0, k=4, shape=(2, 2, 64, 64), bad=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(*shape, generator=g)
+    idx, val, xshape, totalk = C.TopKCompressor().compress(x, k)
+    if bad == "nan":
+        val = val.clone(); val[0, 0, 0] = float("nan")
+    if bad == "index":
+        idx = C.pack_12bit_indices(torch.full(val.shape, 4095, dtype=torch.int64))
+    return {"w.idxs": idx, "w.vals": val, "w.quant_params": None}
+
+
+@pytest.fixture()
+def net():
+    store, chain = MemoryStore(), StaticChain(n=6, manual=True)
+    comms = {u: make_comms(u, store, chain) for u in range(4)}
+
+    async def sync():
+        for c in comms.values():
+            c.commitments = await c.get_commitments()
+    run(sync())
+    return store, chain, comms
+
+
+def test_commitment_roundtrip_and_validation():
+    b = Bucket(name="x" * 32, account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+    s = chain_mod.encode_commitment(b)
+    assert len(s) == 128
+    d = chain_mod.decode_commitment(s)
+    assert d.name == d.account_id == "a" * 32 and d.access_key_id == "k" * 32
+    with pytest.raises(ValueError):
+        chain_mod.decode_commitment("short")
+    with pytest.raises(ValueError):
+        chain_mod.encode_commitment(Bucket(name="n", account_id="a", access_key_id="k", secret_access_key="s"))
+    assert hash(b) == hash(Bucket(**b.model_dump())) and b == Bucket(**b.model_dump())
+
+
+def test_put_get_remote_and_local(net, tmp_path):
+    store, chain, comms = net
+
+    async def go():
+        await comms[1].put(payload(1), window=5, key="gradient", uid="1", global_step=9, local=False)
+        r = await comms[2].get(uid="1", window=5, key="gradient", local=False)
+        assert r.success and r.global_step == 9 and torch.equal(r.data["w.vals"], payload(1)["w.vals"])
+        assert (await comms[2].get(uid="1", window=6, key="gradient", local=False)).status == "NOT_FOUND"
+        assert (await comms[2].get(uid="5", window=5, key="gradient", local=False)).status == "NOT_FOUND"
+        await comms[1].put(payload(2), window=5, key="gradient", uid="1", local=True)
+        r = await comms[1].get(uid="1", window=5, key="gradient", local=True)
+        assert r.success
+    run(go())
+
+
+def test_time_window_too_early_too_late(net):
+    store, chain, comms = net
+
+    async def go():
+        await comms[1].put(payload(1), window=3, key="gradient", uid="1", local=False)
+        now = datetime.now(timezone.utc)
+        r = await comms[2].get(uid="1", window=3, key="gradient", local=False, time_min=now + timedelta(seconds=60))
+        assert r.status == "TOO_EARLY"
+        r = await comms[2].get(uid="1", window=3, key="gradient", local=False, time_max=now - timedelta(seconds=60))
+        assert r.status == "TOO_LATE"
+        naive = (now - timedelta(seconds=60)).replace(tzinfo=None)
+        r = await comms[2].get(uid="1", window=3, key="gradient", local=False, time_min=naive, time_max=now + timedelta(seconds=60))
+        assert r.success
+        assert await comms[2].get_with_retry(uid="1", window=3, key="gradient", timeout=5, local=False,
+                                             time_max=now - timedelta(seconds=60)) is None
+    run(go())
+
+
+def test_gather_validates_and_reserve_fills_in(net):
+    store, chain, comms = net
+    totalks, xshapes = {"w.": 4096}, {"w.": (2, 2, 64, 64)}
+
+    async def go():
+        await comms[0].put(payload(0), window=7, key="gradient", uid="0", local=False)
+        await comms[1].put(payload(1, bad="nan"), window=7, key="gradient", uid="1", local=False)
+        await comms[2].put(payload(2, bad="index") | {"w.idxs": C.pack_12bit_indices(torch.full((2, 2, 4), 4095))},
+                           window=7, key="gradient", uid="2", local=False)
+        await comms[3].put(payload(3), window=7, key="gradient", uid="3", local=False)
+        res = await comms[0].gather(my_uid=0, uids=[0, 1, 2], window=7, key="gradient", timeout=2, device="cpu",
+                                    totalks={"w.": 4000}, local=False, xshapes=xshapes,
+                                    expected_compressed_params={"w.idxs", "w.vals", "w.quant_params"})
+        assert res.uids == [0] and sorted(res.skipped_uids) == [1, 2]      # NaN values, index >= totalk
+        res = await comms[0].gather_with_reserve(my_uid=0, gather_uids=[0, 1], reserve_uids=[3], window=7, key="gradient",
+                                                 timeout=2, device="cpu", totalks=totalks, local=False, xshapes=xshapes)
+        assert res.uids == [0, 3] and res.success_rate == 1.0 and len(res.state_dict.__dict__["w.vals"]) == 2
+        # sharded payload (wrong chunk grid) is rejected
+        await comms[1].put(payload(5, shape=(1, 2, 64, 64)), window=8, key="gradient", uid="1", local=False)
+        res = await comms[0].gather(my_uid=0, uids=[1], window=8, key="gradient", timeout=1, device="cpu", totalks=totalks,
+                                    local=False, xshapes=xshapes)
+        assert res is None
+        # missing expected key
+        await comms[1].put({"w.idxs": payload(1)["w.idxs"], "w.vals": payload(1)["w.vals"]}, window=9, key="gradient", uid="1", local=False)
+        res = await comms[0].gather(my_uid=0, uids=[1], window=9, key="gradient", timeout=1, device="cpu", totalks=totalks,
+                                    local=False, expected_compressed_params={"w.idxs", "w.vals", "w.quant_params"})
+        assert res is None
+    run(go())
+
+
+def test_host_side_fault_injection_drop_corrupt_delay(net):
+    store, chain, comms = net
+    totalks = {"w.": 4096}
+
+    async def go():
+        for u in (1, 2, 3):
+            await comms[u].put(payload(u), window=11, key="gradient", uid=str(u), local=False)
+        store.faults = {"gradient-11-1-": "drop", "gradient-11-2-": "corrupt"}
+        res = await comms[0].gather(my_uid=0, uids=[1, 2, 3], window=11, key="gradient", timeout=2, device="cpu",
+                                    totalks=totalks, local=False)
+        assert res.uids == [3] and sorted(res.skipped_uids) == [1, 2] and abs(res.success_rate - 1 / 3) < 1e-9
+        store.faults = {"gradient-11-3-": ("delay", 5.0)}
+        comms[0].gather_timeout = 1
+        res = await comms[0].gather(my_uid=0, uids=[3], window=11, key="gradient", timeout=1, device="cpu", totalks=totalks, local=False)
+        assert res is None                                  # whole gather timed out, nothing hangs
+    run(go())
+
+
+def test_check_compressed_indices(net):
+    _, _, comms = net
+    c = comms[0]
+    vals = torch.zeros(3, 4)
+    good = C.pack_12bit_indices(torch.randint(0, 64, (3, 4)))
+    c.check_compressed_indices("p", good, 64, allowed_topk=4, vals=vals)
+    for bad_idx, kw in ((good.to(torch.int64), {}), (good, {"vals": None}), (good[:3], {}),
+                        (C.pack_12bit_indices(torch.full((3, 4), 70)), {}), (good, {"allowed_topk": 2})):
+        with pytest.raises(ValueError):
+            c.check_compressed_indices("p", bad_idx, 64, **({"allowed_topk": 4, "vals": vals} | kw))
+
+
+def test_peer_list_start_window_and_activity(net):
+    store, chain, comms = net
+
+    async def go():
+        v = comms[0]                     # uid 0 has the highest stake on the static chain
+        await v.post_start_window(42)
+        assert await comms[2].get_start_window(retries=1, retry_delay=0.01) == 42
+        await v.post_peer_list(peers=[1, 2], reserve_peers=[3], first_effective_window=10, sync_window=9, initial_selection=True)
+        await v.post_peer_list(peers=[2, 3], reserve_peers=[], first_effective_window=12, sync_window=11, initial_selection=False)
+        assert await comms[2].get_peer_list() == ([2, 3], [], 12)
+        assert await comms[2].get_peer_list(fetch_previous=True) == ([1, 2], [3], 10)
+        comms[2].current_window = 20
+        assert not await comms[2].is_miner_active(1, recent_windows=2)
+        await comms[1].put(payload(1), window=19, key="gradient", uid="1", local=False)
+        assert await comms[2].is_miner_active(1, recent_windows=2)
+        assert await comms[2].refresh_active_peers() == {1}
+        comms[2].update_peers_with_buckets()
+        assert comms[2].eval_peers == {1: 1}
+        comms[2].active_peers = set()
+        comms[2].eval_peers = {1: 1}
+        comms[2].active_peers = {3}
+        comms[2].update_peers_with_buckets()
+        assert comms[2].inactive_peers == {1} and 3 in comms[2].eval_peers
+    run(go())
+
+
+def test_weighted_sampling_and_stale_cleanup(net, tmp_path):
+    store, chain, comms = net
+    c = comms[1]
+    assert c.weighted_random_sample_no_replacement([], [], 3) == []
+    got = c.weighted_random_sample_no_replacement([1, 2, 3, 4], [0, 1, 1, 5], 3)
+    assert len(got) == 3 and 1 not in got and len(set(got)) == 3
+
+    async def go():
+        for w in (1, 2, 30):
+            await c.put(payload(w), window=w, key="gradient", uid="1", local=False)
+        await c.cleanup_s3_data(uid="1", current_window=30, stale_retention=10)
+        keys = [o.key for o in await store.list(c.bucket, "gradient-")]
+        assert len(keys) == 1 and "gradient-30-1-" in keys[0]
+    run(go())
+
+
+def test_local_fs_store_roundtrip(tmp_path):
+    st = LocalFSStore(tmp_path)
+    b = Bucket(name="bkt", account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+
+    async def go():
+        await st.put_bytes(b, "dir/x.bin", b"hello")
+        assert await st.get_bytes(b, "dir/x.bin") == b"hello" and (await st.head(b, "dir/x.bin")).size == 5
+        assert [o.key for o in await st.list(b, "dir/")] == ["dir/x.bin"]
+        assert await st.get_to_file(b, "dir/x.bin", str(tmp_path / "out.bin")) and not await st.get_to_file(b, "nope", "/tmp/z")
+        await st.delete(b, ["dir/x.bin"])
+        assert await st.head(b, "dir/x.bin") is None
+    run(go())
+
+
+class _FakeS3:
+    """aiobotocore-shaped client: multipart upload with a vanishing upload id and flaky parts."""
+
+    def __init__(self):
+        self.objects, self.uploads, self.fail_parts, self.forget_once = {}, {}, 2, True
+
+    async def create_multipart_upload(self, Bucket, Key):
+        uid = f"u{len(self.uploads)}"
+        self.uploads[uid] = {}
+        return {"UploadId": uid}
+
+    async def upload_part(self, Bucket, Key, PartNumber, UploadId, Body, ContentMD5=None):
+        if self.forget_once and PartNumber == 2:
+            self.forget_once = False
+            raise RuntimeError("NoSuchUpload")
+        if self.fail_parts > 0 and PartNumber == 1:
+            self.fail_parts -= 1
+            raise IOError("transient")
+        self.uploads[UploadId][PartNumber] = Body
+        return {"ETag": f"e{PartNumber}"}
+
+    async def complete_multipart_upload(self, Bucket, Key, UploadId, MultipartUpload):
+        self.objects[Key] = b"".join(self.uploads[UploadId][p["PartNumber"]] for p in MultipartUpload["Parts"])
+
+    async def abort_multipart_upload(self, **kw):
+        return None
+
+
+def test_s3_multipart_upload_retries_and_restarts(tmp_path, monkeypatch):
+    monkeypatch.setattr(asyncio, "sleep", _fast_sleep(asyncio.sleep))
+    fake = _FakeS3()
+    st = S3Store(client_factory=lambda b: fake, part_size=1024, concurrency=2, max_retries=4)
+    data = os.urandom(5000)
+    p = tmp_path / "big.bin"
+    p.write_bytes(data)
+    b = Bucket(name="bkt", account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+    run(st.upload_large_file(b, "big.bin", str(p)))
+    assert fake.objects["big.bin"] == data and len(fake.uploads) == 2      # restarted once with a new upload id
+    chunk, workers = st.download_plan(10 * 1024 ** 3, workers=8)
+    assert 64 * 1024 ** 2 <= chunk <= 1024 ** 3 and 1 <= workers <= 8
+
+
+def _fast_sleep(real):
+    async def s(t, *a, **k):
+        return await real(0)
+    return s
+
+
+def test_decorators_and_config(monkeypatch):
+    from templar_b200 import config, decos
+
+    calls = {"n": 0}
+
+    @decos.retry_on_failure(retries=3, delay=0.0)
+    async def flaky():
+        calls["n"] += 1
+        return None if calls["n"] < 3 else "ok"
+    assert run(flaky()) == "ok" and calls["n"] == 3
+
+    @decos.sync_exception_catcher(on_error_return=lambda e: -1)
+    def boom():
+        raise ValueError("x")
+    assert boom() == -1
+
+    class Node:
+        is_master = False
+
+        @decos.master_only
+        def f(self):
+            return 1
+    assert Node().f() is None
+    for v in config.REQUIRED_VARS:
+        monkeypatch.delenv(v, raising=False)
+    with pytest.raises(ImportError):
+        config.load_bucket_secrets(strict=True)
+    assert "gradients" in config.load_bucket_secrets(strict=False)
+    monkeypatch.setenv("R2_DATASET_BUCKET_LIST", '[{"name": "d1"}, {"name": "d2"}]')
+    assert config.load_bucket_secrets(strict=False)["dataset"]["multiple"][1]["name"] == "d2"
+    r = tplr.CommsGetResult(status="OK")
+    assert not r.success and tplr.CommsGetResult(data={}, status="OK").success

@@ -1,0 +1,29 @@
+"""Real multi-process tier on CPU (gloo, world_size 2): sharded window + DCP round trip."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def launch(nproc, args, timeout=900):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "_gloo_worker.py"), *map(str, args)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, TPLR_LOG_LEVEL="WARNING"))
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert r.returncode == 0 and lines, r.stdout[-2000:] + r.stderr[-4000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.parametrize("update", ["sgd", "sign"])
+def test_two_rank_window_and_checkpoint_roundtrip(tmp_path, update):
+    res = launch(2, ["small", 2, 64, update, tmp_path])
+    assert len(res) == 2
+    for r in res:
+        assert r["same_weights"] and r["master_roundtrip"] and r["compute_roundtrip"], r
+        assert r["ckpt"] == [7, 3] and r["status"] == 0
+        assert r["loss0"] > 0 and abs(r["loss1"] - r["loss0"]) > 1e-6       # the outer step moved the model

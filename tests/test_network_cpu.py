@@ -1,0 +1,383 @@
+"""End-to-end offline network on CPU: two miners and a validator exchanging gradients through an
+in-memory object store on a static chain; plus unit tests of the validator's scoring state,
+the trainer's LR warm-up / flatten rules, the model factory and small modules."""
+
+import asyncio
+import math
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import templar_b200 as tplr
+from neurons.burn import get_config as burn_config, run as burn_run
+from neurons.evaluator import Evaluator, ModelCache, compute_bpb
+from neurons.miner import Miner
+from neurons.trainer import Trainer
+from neurons.validator import Validator, min_power_normalization
+from templar_b200 import model_factory as mf
+from templar_b200.backends.chain import StaticChain
+from templar_b200.backends.store import MemoryStore
+from templar_b200.utils.rating import PlackettLuce
+
+
+def run(c):
+    return asyncio.run(c)
+
+
+@pytest.fixture()
+def cwd_tmp(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("TPLR_LOG_LEVEL", "WARNING")
+    monkeypatch.setenv("TPLR_METRICS_JSONL", str(tmp_path / "metrics.jsonl"))
+    return tmp_path
+
+
+def _node(cls, cfg_fn, argv, store, chain):
+    return cls(config=cfg_fn(["--local", "--device", "cpu", *argv]), store=store, subtensor=chain)
+
+
+def test_two_miners_and_a_validator_stay_in_sync(cwd_tmp):
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        miners = [_node(Miner, Miner.miner_config, ["--uid", str(u), "--peers", "2", "3"], store, chain) for u in (2, 3)]
+        for n in miners + [v]:
+            n.loop = asyncio.get_running_loop()
+            n.comms.commitments = await n.comms.get_commitments()
+            n.comms.peers = [2, 3]
+            n.gather_timeout = 5
+            await n.dataset_manager.initialize_datasets(0)
+        for m in miners:
+            m.set_dataloader()
+        v.set_dataloader(validator=True)
+        start = {n: p.detach().clone() for n, p in miners[0].model.named_parameters()}
+        for w in range(1, 4):
+            for m in miners:
+                m.current_window = m.comms.current_window = w
+            res = await asyncio.gather(*(m.run_window(w) for m in miners))
+            assert all(r["gather_success_rate"] == 1.0 and r["global_step"] == w for r in res)
+            v.current_window, v.comms.current_window, v.sync_window = w + 1, w, w
+            out = await v.run_window()
+            assert sorted(out["gathered"]) == [2, 3] and len(out["scored"]) == 2 and out["global_step"] == w
+        await v.ckpt.flush_background_uploads()
+        pm = [dict(m.model.named_parameters()) for m in miners]
+        pv = dict(v.model.named_parameters())
+        for n in pm[0]:
+            assert torch.allclose(pm[0][n], pm[1][n], atol=1e-6), n          # same peers, same update
+            assert torch.allclose(pm[0][n], pv[n], atol=1e-5), n             # the validator followed
+            assert not torch.equal(pm[0][n], start[n]) or pm[0][n].numel() < 4
+        assert v.evaluated_uids == {2, 3} and float(v.weights.sum()) == pytest.approx(1.0, abs=1e-5)
+        assert os.path.exists(v.state_path)
+        # checkpoint published at global_step 2 is complete and loadable by a fresh evaluator
+        assert await v.ckpt.check_checkpoint_exists(window=2)
+        e = _node(Evaluator, Evaluator.evaluator_config, ["--uid", "1", "--skip-lm-eval", "--custom-eval-batches", "1"], store, chain)
+        e.comms.commitments = await e.comms.get_commitments()
+        assert await e.check_latest_checkpoint() == 2
+        rep = await e.evaluate_window(2)
+        assert rep["global_step"] == 2 and rep["perplexity"] > 1 and rep["bits_per_byte"] > 0
+        # a miner that joins late catches up from the checkpoint + the validator's aggregated gradients
+        late = _node(Miner, Miner.miner_config, ["--uid", "1", "--peers", "2", "3"], store, chain)
+        late.loop = asyncio.get_running_loop()
+        late.comms.commitments = await late.comms.get_commitments()
+        late.comms.peers = [2, 3]
+        late.current_window, late.start_window = 4, 1
+        ok, win, step, boot = await tplr.neurons.load_checkpoint_with_fallback(late)
+        assert (ok, win, step, boot) == (True, 2, 2, False)
+        await tplr.neurons.handle_checkpoint_catchup(late, ok, win, step, boot)
+        assert late.global_step == 3
+        pl = dict(late.model.named_parameters())
+        for n in pv:
+            assert torch.allclose(pl[n], pv[n], atol=1e-5), n
+    run(go())
+
+
+def test_miner_survives_missing_and_corrupt_peers(cwd_tmp):
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        m = _node(Miner, Miner.miner_config, ["--uid", "2", "--peers", "1", "3"], store, chain)
+        m.loop = asyncio.get_running_loop()
+        m.comms.commitments = await m.comms.get_commitments()
+        m.comms.peers = [1, 3]                 # nobody else uploads
+        m.gather_timeout = 1
+        await m.dataset_manager.initialize_datasets(0)
+        m.set_dataloader()
+        before = {n: p.detach().clone() for n, p in m.model.named_parameters()}
+        m.current_window = 1
+        r = await m.run_window(1)
+        assert r["gather_success_rate"] == 0.0 and r["global_step"] == 0
+        for n, p in m.model.named_parameters():
+            assert torch.equal(p.detach(), before[n]), n          # window skipped: weights restored
+        assert float(m.engine.ef.abs().max()) > 0                 # but the error feedback kept the work
+    run(go())
+
+
+# --------------------------------------------------------------------------------------- #
+def _bare_validator():
+    v = object.__new__(Validator)
+    z = lambda: torch.zeros(256)  # noqa: E731
+    v.gradient_scores, v.sync_scores, v.binary_indicator_scores = z(), z(), z()
+    v.final_scores, v.binary_moving_averages, v.weights = z(), z(), z()
+    v.hparams = SimpleNamespace(burn_rate=0.5, gather_share=0.75, gather_peer_count=2, reserve_peer_count=2, gather_top_ratio=2.0,
+                                reserve_decay_ratio=0.5, gather_peers_slash_threshold=0.4, consecutive_negative_threshold=3,
+                                exclude_negative_peers=True, missing_gradient_penalty_score=-99.0, bma_threshold=0.1,
+                                bma_warmup_windows=0, sync_max_steps_behind=2, reset_inactivity_windows=3, uids_per_window=2,
+                                minimum_peers=1, peer_replacement_frequency=2, peer_list_window_margin=1)
+    v.openskill_model, v.openskill_ratings, v.current_window_scores = PlackettLuce(beta=7, tau=0.1), {}, {}
+    v.evaluated_uids, v.eval_peers, v.inactive_scores = set(), {}, {}
+    v.peer_eval_history, v.consecutive_negative_count, v.consecutive_missing_gradient_count = {}, {}, {}
+    v.missing_gradient_history, v.excluded_from_gather, v.exclusion_start_window = {}, set(), {}
+    v.peers_last_eval_window, v.naughty_peers = {}, {}
+    v.eval_history_limit, v.missing_gradient_history_limit, v.naughty_peer_timeout = 20, 10, 200
+    v.missing_gradient_slash_rate, v.sync_score_slash_rate, v.inactivity_slash_rate, v.score_zero_threshold = 0.75, 0.75, 0.25, 1e-4
+    v.idx_similarity_slashing_rate = tplr.neurons.instantiate_slashing_multiplier()
+    v.burn_uid, v.sync_window, v.current_window, v.start_window, v.is_master = 1, 10, 11, 0, True
+    v.metrics_logger = None
+    v.comms = SimpleNamespace(metagraph=SimpleNamespace(uids=torch.arange(256)), active_peers=set(), inactive_peers=set(),
+                              weighted_random_sample_no_replacement=lambda c, w, k: c[:k])
+    return v
+
+
+def test_update_weights_emission_schedule():
+    v = _bare_validator()
+    for u, s in ((5, 4.0), (6, 3.0), (7, 2.0), (8, 1.0), (9, 0.5), (10, -1.0)):
+        v.final_scores[u] = s
+        v.evaluated_uids.add(u)
+    v.update_weights()
+    w = v.weights
+    assert float(w.sum()) == pytest.approx(1.0, abs=1e-6) and float(w[1]) == pytest.approx(0.5)
+    assert w[5] > w[6] > w[7] > w[8] > 0 and w[9] == 0 and w[10] == 0
+    assert float(w[5] / w[6]) == pytest.approx(2.0, rel=1e-4)             # linear ramp top_ratio : 1
+    assert float(w[7]) <= float(w[6])                                       # reserve never above gather
+    v.final_scores.zero_()
+    v.update_weights()
+    assert float(v.weights[1]) == 1.0
+
+
+def test_missing_gradient_ladder_and_reset():
+    v = _bare_validator()
+    v.final_scores[7] = 1.0
+    v.binary_moving_averages[7] = 1.0
+    v.slash_for_missing_gradients([7], success_rate=0.9)
+    assert float(v.final_scores[7]) == pytest.approx(0.75)
+    v.slash_for_missing_gradients([7], success_rate=0.9)
+    assert float(v.final_scores[7]) == pytest.approx(0.375)
+    v.slash_for_missing_gradients([7], success_rate=0.9)
+    assert float(v.final_scores[7]) == 0.0 and v.current_window_scores[7] == -99.0
+    v.final_scores[8] = 1.0
+    v.slash_for_missing_gradients([8], success_rate=0.1)                  # poor gather: straight to 0
+    assert float(v.final_scores[8]) == 0.0
+    v.final_scores[9] = 1.0
+    for _ in range(8):
+        v.slash_for_missing_gradients([9], success_rate=0.9)
+    assert 9 in v.naughty_peers and 9 not in v.openskill_ratings or float(v.final_scores[9]) == 0.0
+    v.note_delivered([7])
+    assert v.consecutive_missing_gradient_count[7] == 0
+    v.slash_for_invalid_gradient(5, ValueError("bad"))
+    assert 5 in v.evaluated_uids
+
+
+def test_negative_evaluation_penalties_and_fifth_rank_rule():
+    v = _bare_validator()
+    v.final_scores[3] = 1.0
+    v.binary_moving_averages[3] = 1.0
+    for i in range(8):
+        v.gradient_scores[3] = -0.1 if i < 6 else 0.1
+        v.track_negative_evaluation(3)
+    v.current_window_scores = {3: 0.1, 4: 0.2}
+    v.apply_negative_evaluation_penalties()
+    assert float(v.final_scores[3]) == pytest.approx(0.25)
+    for _ in range(3):
+        v.gradient_scores[3] = -0.1
+        v.track_negative_evaluation(3)
+    v.current_window_scores = {u: -0.1 for u in range(5)}                 # everybody negative: no punishment
+    assert v.should_skip_negative_penalty() and not v.should_exclude_from_gather(3)
+    v.apply_negative_evaluation_penalties()
+    assert 3 not in v.excluded_from_gather
+    v.current_window_scores = {u: 0.1 for u in range(5)}
+    assert v.should_exclude_from_gather(3)
+    v.apply_negative_evaluation_penalties()
+    assert 3 in v.excluded_from_gather
+    v.gradient_scores[3] = 0.2
+    v.track_negative_evaluation(3)
+    assert 3 not in v.excluded_from_gather and v.consecutive_negative_count[3] == 0
+
+
+def test_openskill_update_overlap_slash_bins_and_inactivity():
+    v = _bare_validator()
+    v.current_window_scores = {1: 0.3, 2: 0.1, 3: -0.2}
+    for u in (1, 2, 3):
+        v.evaluated_uids.add(u)
+        v.sync_scores[u] = 1.0
+        v.binary_moving_averages[u] = 0.5
+    v.update_openskill_ratings()
+    assert v.openskill_ratings[1].mu > v.openskill_ratings[2].mu > v.openskill_ratings[3].mu and v.current_window_scores == {}
+    assert float(v.final_scores[1]) == pytest.approx(v.openskill_ratings[1].ordinal() * 0.5)
+    v.final_scores[2] = 2.0
+    v.slash_from_overlap({"uids_over_thresh": {2: "high", 3: "mega", 999: "max"}})
+    assert float(v.final_scores[2]) == pytest.approx(1.0) and 3 in v.naughty_peers and 3 not in v.openskill_ratings
+    v.eval_peers = {u: 1 for u in range(20)}
+    bins = v.bin_evaluation_peers(5)
+    assert len(bins) == 5 and sorted(sum(bins.values(), [])) == list(range(20))
+    assert len(v.select_evaluation_uids_from_bin(bins, 99)) == 2
+    assert v.bin_evaluation_peers(50) == {0: list(range(20))}
+    v.eval_peers = {}
+    v.comms.inactive_peers = {4}
+    v.final_scores[4] = 1.0
+    v.penalize_inactive_peers()
+    assert float(v.final_scores[4]) == pytest.approx(0.75)
+    v.current_window += 10
+    v.penalize_inactive_peers()
+    assert float(v.final_scores[4]) == 0.0 and 4 not in v.inactive_scores
+    assert torch.allclose(min_power_normalization(torch.tensor([1.0, 3.0])), torch.tensor([0.1, 0.9]))
+    assert float(min_power_normalization(torch.zeros(3)).sum()) == 0
+
+
+def test_peer_selection():
+    v = _bare_validator()
+    v.comms.active_peers = {2, 3, 4, 5, 6}
+    v.comms.metagraph.I = torch.zeros(256)
+    v.comms.metagraph.I[torch.tensor([2, 3])] = torch.tensor([0.5, 0.9])
+    g, r = v.select_initial_peers()
+    assert g == [3, 2] and len(r) == 2 and set(r) <= {4, 5, 6}
+    v.weights[torch.tensor([4, 5, 6])] = torch.tensor([0.3, 0.2, 0.1])
+    v.naughty_peers = {6: 5}
+    g, r = v.select_next_peers()
+    assert g == [4, 5] and 6 not in g + r
+    v.comms.active_peers = set()
+    assert v.select_next_peers() is None
+
+
+# --------------------------------------------------------------------------------------- #
+def _trainer(sched=None, anneal=None, inner_steps=10):
+    t = Trainer()
+    t.hparams = SimpleNamespace(inner_steps=inner_steps, anneal_mode=anneal or {"enabled": False},
+                                optimizer={"type": "adamw", "adamw": {"learning_rate": 1e-3, "scheduler": sched or {}}})
+    return t
+
+
+def test_lr_flatten_window():
+    t = _trainer({"flatten_start_step": 3, "flatten_duration": 2})
+    for count, want in ((0, False), (29, False), (30, True), (49, True), (50, False)):
+        t.inner_scheduler_step_count = count
+        assert t.should_skip_scheduler_step() is want
+    for s in ({}, {"flatten_start_step": None, "flatten_duration": 2}, {"flatten_start_step": 3, "flatten_duration": 0},
+              {"flatten_start_step": 0, "flatten_duration": 5}):
+        t2 = _trainer(s)
+        t2.inner_scheduler_step_count = 35
+        assert t2.should_skip_scheduler_step() is False
+
+
+def test_warmup_scale_and_schedulers():
+    t = _trainer({"warmup_steps": 4, "t_max": 100, "eta_min_factor": 0.1})
+    t.warmup_inner_steps, t.warmup_steps_taken = 4, 0
+    assert [round(t._warmup_scale(), 2) for t.warmup_steps_taken in (0, 1, 3, 4, 9)] == [0.25, 0.5, 1.0, 1.0, 1.0]
+    t.hparams.anneal_mode = {"enabled": True}
+    t.warmup_steps_taken = 0
+    assert t._warmup_scale() == 1.0
+    t.hparams.anneal_mode = {"enabled": False}
+    t.inner_optimizer = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1e-3)
+    s = t.get_inner_scheduler()
+    lrs = []
+    for _ in range(6):
+        lrs.append(t.inner_optimizer.param_groups[0]["lr"])
+        t.inner_optimizer.step()
+        s.step()
+    assert lrs[0] < lrs[1] < lrs[3] and lrs[4] == pytest.approx(1e-3, rel=1e-3) and lrs[5] < lrs[4]
+    t2 = _trainer(anneal={"enabled": True, "warmup_inner_steps": 2, "decay_outer_steps": 1, "peak_lr_factor": 0.5, "eta_min_factor": 0.0},
+                  inner_steps=4)
+    t2.inner_optimizer = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+    s2 = t2.get_inner_scheduler()
+    seq = []
+    for _ in range(7):
+        seq.append(t2.inner_optimizer.param_groups[0]["lr"])
+        t2.inner_optimizer.step()
+        s2.step()
+    assert seq[2] == pytest.approx(0.5, rel=1e-3) and seq[6] == pytest.approx(0.0, abs=1e-6)
+
+
+def test_model_factory_roles_and_errors():
+    hp = lambda **tt: SimpleNamespace(torchtitan=SimpleNamespace(**tt))  # noqa: E731
+    assert mf.create_parallel_dims(16, hp(), "evaluator").dp_shard == 8
+    assert mf.create_parallel_dims(8, hp(), "validator").dp_replicate == 2
+    with pytest.raises(ValueError):
+        mf.create_parallel_dims(6, hp(), "validator")
+    d = mf.create_parallel_dims(8, hp(dp_shard=4, tp_degree=2), "miner")
+    assert (d.dp_shard, d.tp, d.world_size) == (4, 2, 8) and d.mesh_shape() == {"dp_shard": 4, "tp": 2}
+    assert mf.create_parallel_dims(8, hp(dp_shard=-1, tp_degree=2), "miner").dp_shard == 4
+    for bad, msg in ((dict(dp_shard=0), "dp_shard cannot be zero"), (dict(dp_replicate=2, dp_shard=2), "but not both"),
+                     (dict(dp_replicate=2, tp_degree=2), "tp/pp/cp are all 1"), (dict(dp_shard=3), "must be divisible")):
+        with pytest.raises(ValueError, match=msg):
+            mf.create_parallel_dims(8, hp(**bad), "miner")
+    hpar = tplr.load_hparams(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "hparams"), True)
+    args = mf.get_titan_model_args(hpar)
+    assert (args.dim, args.ffn_hidden, args.vocab_size) == (128, 256, 512)
+    job = mf.create_job_config(hpar, "evaluator")
+    assert job.mixed_precision_param == "float32" and job.mixed_precision_reduce == "float32"
+    a = mf.initialize_torchtitan_model(hpar, "miner", "cpu", 1)
+    b = mf.initialize_torchtitan_model(hpar, "evaluator", "cpu", 1)
+    assert all(torch.equal(p, q) for p, q in zip(a.parameters(), b.parameters()))        # deterministic init
+    meta = mf.create_meta_model(hpar, "miner", 1)
+    assert next(meta.parameters()).is_meta
+
+
+def test_hf_export_matches_model_logits(tmp_path):
+    hpar = tplr.load_hparams(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "hparams"), True)
+    model = mf.initialize_torchtitan_model(hpar, "miner", "cpu", 1)
+    hf = mf.convert_titan_to_hf(model, hpar, save_path=str(tmp_path / "hf"), is_master=True)
+    assert (tmp_path / "hf" / "config.json").exists()
+    if not isinstance(hf, dict):
+        tok = torch.randint(0, 512, (2, 16))
+        with torch.no_grad():
+            assert torch.allclose(model(tok), hf(tok).logits, atol=2e-4, rtol=1e-3)
+
+
+def test_small_modules(tmp_path, monkeypatch):
+    assert compute_bpb(math.log(2.0) * 80, 10) == pytest.approx(8.0) and math.isinf(compute_bpb(1.0, 0))
+    c = ModelCache(tmp_path / "cache")
+    assert not c.is_valid(1, "v")
+    (tmp_path / "cache").mkdir()
+    (tmp_path / "cache" / "config.json").write_text("{}")
+    c.mark(1, "v")
+    assert c.is_valid(1, "v") and not c.is_valid(2, "v")
+    out = tmp_path / "lm"
+    out.mkdir()
+    (out / "results_1.json").write_text('{"results": {"arc_easy": {"acc,none": 0.5, "acc_norm,none": 0.6}, "piqa": {"acc,none": 0.7}}}')
+    assert Evaluator.parse_lm_eval_results(out) == {"arc_easy": 0.6, "piqa": 0.7}
+    chain = StaticChain(n=3, manual=True)
+    chain.advance(400)
+    assert burn_run(burn_config(["--max-iterations", "3", "--poll-seconds", "0"]), subtensor=chain, sleep=lambda s: chain.advance(200)) == 2
+    from templar_b200.metrics import MetricsLogger
+    from templar_b200.profilers import TimerProfiler, ShardProfiler, DummyTimerProfiler
+    from templar_b200.wandb_ops import NullRun, versioned
+    ml = MetricsLogger(prefix="T", uid=1, role="miner", jsonl_path=str(tmp_path / "m.jsonl"), flush_interval=0.05)
+    ml.log("m", {"w": 1}, {"loss": 1.5, "xs": [1, 2, 3], "t": torch.tensor([2.0, 4.0]), "flag": True, "name": "x", "none": None},
+           with_system_metrics=True)
+    ml.close()
+    import json
+    rec = json.loads((tmp_path / "m.jsonl").read_text().splitlines()[0])
+    assert rec["measurement"] == "Tm" and rec["fields"]["xs_mean"] == 2 and rec["fields"]["t_max"] == 4 and rec["tags"]["role"] == "miner"
+    assert versioned({"a": 1}, "9") == {"v9/a": 1, "latest/a": 1}
+    r = NullRun()
+    r.log({"a": 1}, step=2)
+    assert r.history == [({"a": 1}, 2)]
+    tp = TimerProfiler("t")
+
+    @tp.profile("f")
+    def f():
+        return 3
+
+    @tp.profile("g")
+    async def g():
+        return 4
+    assert f() == 3 and run(g()) == 4 and tp.get_stats("f")["count"] == 1 and tp.get_stats()["g"]["count"] == 1
+    assert DummyTimerProfiler().profile("x")(f)() == 3
+    sp = ShardProfiler("s", slow_read_s=10)
+    sp.end_read(sp.start_read("a.npy", {"idx": 1}))
+    sp.export_data(str(tmp_path / "rep.json"))
+    assert sp.get_stats("a.npy")["reads"] == 1 and (tmp_path / "rep.json").exists()
+    m = PlackettLuce()
+    a, b = m.rate([[m.rating()], [m.rating()]], scores=[1.0, 0.0])
+    assert a[0].mu > 25 > b[0].mu and a[0].sigma < 25 / 3
+    tplr.log_with_context("info", "hello", window=3, uid=1)

@@ -1,0 +1,275 @@
+"""Protocol logic on CPU: gradient preparation (error feedback maths, null rounds), outer step,
+engine path == generic path, sync metric, index overlap, slashing levels, peer rotation, catch-up."""
+
+import asyncio
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import templar_b200 as tplr
+from templar_b200 import compress as C
+from templar_b200.models.llama import ModelArgs, build_model
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+
+
+def run(c):
+    return asyncio.run(c)
+
+
+class Tiny(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(0)
+        self.a = torch.nn.Parameter(torch.randn(128, 64))
+        self.b = torch.nn.Parameter(torch.randn(64))
+
+
+def make_miner(use_dct=True, topk=8, quant=False):
+    model = Tiny()
+    m = SimpleNamespace(model=model, use_engine=False,
+                        hparams=SimpleNamespace(use_dct=use_dct, topk_compression=topk, momentum_decay=0.9),
+                        transformer=C.ChunkingTransformer(model, 64),
+                        compressor=C.TopKCompressor(use_quantization=quant, quantization_bins=256),
+                        owned_params={"a", "b"}, error_feedback={"a": None, "b": None}, error_feedback_cpu_buffers={})
+    return m
+
+
+@pytest.mark.parametrize("use_dct", [False, True])
+def test_prepare_gradient_dict_error_feedback_maths(use_dct):
+    m = make_miner(use_dct)
+    g1 = {n: torch.randn_like(p) for n, p in m.model.named_parameters()}
+    for n, p in m.model.named_parameters():
+        p.grad = g1[n].clone()
+    grad, xshapes, totalks = tplr.prepare_gradient_dict(m, step_window=3)
+    assert grad["metadata"] == {"window": 3} and set(xshapes) == {"a", "b"} and totalks == {"a": 4096, "b": 64}
+    assert grad["aidxs"].dtype == torch.uint8 and grad["avals"].shape == (2, 1, 8) and grad["aquant_params"] is None
+    for n, p in m.model.named_parameters():
+        sent = m.transformer.decode(m.compressor.decompress(p, grad[n + "idxs"], grad[n + "vals"], xshapes[n], totalks[n]),
+                                    use_dct=use_dct)
+        assert torch.allclose(m.error_feedback[n], g1[n] - sent, atol=1e-5)       # e = 0*gamma + g - sent
+        assert p.grad is None
+    e1 = {n: m.error_feedback[n].clone() for n in ("a", "b")}
+    for n, p in m.model.named_parameters():
+        p.grad = g1[n].clone()
+    grad2, _, _ = tplr.prepare_gradient_dict(m, 4)
+    for n, p in m.model.named_parameters():
+        sent = m.transformer.decode(m.compressor.decompress(p, grad2[n + "idxs"], grad2[n + "vals"], xshapes[n], totalks[n]),
+                                    use_dct=use_dct)
+        assert torch.allclose(m.error_feedback[n], 0.9 * e1[n] + g1[n] - sent, atol=1e-5)
+    for n, p in m.model.named_parameters():
+        p.grad = g1[n].clone()
+    grad3, _, _ = tplr.prepare_gradient_dict(m, 5, null_round=True)
+    assert all(float(m.error_feedback[n].abs().max()) == 0 for n in ("a", "b")) and float(grad3["avals"].abs().max()) == 0
+
+
+def test_prepare_gradient_dict_quantised_and_ownership():
+    m = make_miner(quant=True)
+    m.owned_params = {"a"}
+    for n, p in m.model.named_parameters():
+        p.grad = torch.randn_like(p)
+    grad, xs, tk = tplr.prepare_gradient_dict(m, 1)
+    assert "bidxs" not in grad and grad["avals"].dtype == torch.uint8 and len(grad["aquant_params"]) == 5
+    assert m.model.b.grad is None
+
+
+def _gather_result(model, n_peers, topk=8, use_dct=True, seed=0):
+    tr, comp = C.ChunkingTransformer(model, 64), C.TopKCompressor()
+    sd, xs, tk = {}, {}, {}
+    g = torch.Generator().manual_seed(seed)
+    for n, p in model.named_parameters():
+        idxs, vals = [], []
+        for j in range(n_peers):
+            enc = tr.encode(torch.randn(p.shape, generator=g) * (1 + j), use_dct=use_dct)
+            i, v, xs[n], tk[n] = comp.compress(enc, topk)
+            idxs.append(i), vals.append(v)
+        sd[n + "idxs"], sd[n + "vals"], sd[n + "quant_params"] = idxs, vals, [None] * n_peers
+    return SimpleNamespace(state_dict=SimpleNamespace(**sd), uids=list(range(n_peers)), skipped_uids=[], success_rate=1.0), tr, comp, xs, tk
+
+
+def test_outer_step_matches_manual_aggregation():
+    model = Tiny()
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    gr, tr, comp, xs, tk = _gather_result(model, 3)
+    opt = torch.optim.SGD(model.parameters(), lr=0.5)
+    fp = tplr.outer_step(model, opt, gather_result=gr, transformer=tr, compressor=comp, xshapes=xs, totalks=tk, device="cpu",
+                         is_master=True, world_size=1, use_dct=True)
+    assert set(fp) >= {"param_norms", "param_means", "global_l2_norm", "total_elements"} and fp["total_elements"] == 128 * 64 + 64
+    for n, p in model.named_parameters():
+        sd = vars(gr.state_dict)
+        g = tr.decode(comp.batch_decompress(p, sd[n + "idxs"], sd[n + "vals"], xs[n], tk[n], clip_norm=True), use_dct=True)
+        assert torch.allclose(p.detach(), before[n] - 0.5 * g, atol=1e-6)
+        assert abs(fp["param_norms"][n] - float(g.norm())) < 1e-4
+    assert tplr.outer_step(model, opt, gather_result=None, transformer=tr, compressor=comp, xshapes=xs, totalks=tk,
+                           device="cpu", is_master=True, world_size=1)["total_elements"] == 0
+
+
+def test_outer_step_skips_non_finite_parameter():
+    model = Tiny()
+    before = model.a.detach().clone()
+    gr, tr, comp, xs, tk = _gather_result(model, 2)
+    vars(gr.state_dict)["avals"][0][0, 0, 0] = float("inf")
+    opt = torch.optim.SGD(model.parameters(), lr=0.5)
+    tplr.outer_step(model, opt, gather_result=gr, transformer=tr, compressor=comp, xshapes=xs, totalks=tk, device="cpu",
+                    is_master=True, world_size=1, use_dct=True)
+    assert torch.equal(model.a.detach(), before) and not torch.equal(model.b.detach(), Tiny().b.detach())
+
+
+@pytest.mark.parametrize("update", ["sgd", "sign"])
+def test_engine_window_equals_generic_functions(update):
+    """The fused-path engine (CPU arithmetic) and the reference-semantics functions give the same weights."""
+    args = ModelArgs(dim=64, n_layers=1, n_heads=2, vocab_size=128, intermediate_size=128, max_seq_len=32)
+    torch.manual_seed(1)
+    tok = torch.randint(0, 128, (2, 33))
+    m1 = build_model(args, seed=3)
+    eng = WindowEngine(m1, EngineConfig(topk=8, use_dct=True, momentum_decay=0.9, outer_lr=0.3, outer_update=update,
+                                        inner_lr=1e-2, max_peers=3))
+    eng.snapshot()
+    eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0)
+    eng.optimizer_step()
+    eng.compress()
+    own = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in eng.own_payload().items()}
+    m2 = build_model(args, seed=3)
+    opt = torch.optim.AdamW(m2.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    theta0 = {n: p.detach().clone() for n, p in m2.named_parameters()}
+    m2.loss(tok[:, :-1], tok[:, 1:]).backward()
+    torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+    opt.step()
+    for n, p in m2.named_parameters():
+        assert torch.allclose(p.detach(), dict(m1.named_parameters())[n].detach(), atol=2e-6), n
+    miner = SimpleNamespace(model=m2, use_engine=False, hparams=SimpleNamespace(use_dct=True, topk_compression=8, momentum_decay=0.9),
+                            transformer=C.ChunkingTransformer(m2, 64), compressor=C.TopKCompressor(),
+                            owned_params={n for n, _ in m2.named_parameters()},
+                            error_feedback={n: None for n, _ in m2.named_parameters()}, error_feedback_cpu_buffers={})
+    with torch.no_grad():
+        for n, p in m2.named_parameters():
+            p.grad = theta0[n] - p.detach()
+            p.copy_(theta0[n])
+    grad, xs, tk = tplr.prepare_gradient_dict(miner, 0)
+    for n, _ in m2.named_parameters():
+        a = C.unpack_12bit_indices(own[n + "idxs"], own[n + "vals"].shape).sort(-1).values
+        b = C.unpack_12bit_indices(grad[n + "idxs"], grad[n + "vals"].shape).sort(-1).values
+        assert torch.equal(a, b), n
+        assert torch.allclose(own[n + "vals"].abs().sort(-1).values, grad[n + "vals"].abs().sort(-1).values, atol=1e-6)
+        assert torch.allclose(eng.store.view(eng.ef, n), miner.error_feedback[n], atol=1e-6)
+    if update == "sgd":
+        gr = SimpleNamespace(state_dict=SimpleNamespace(**{k: [v] for k, v in grad.items() if k != "metadata"}), uids=[0],
+                             skipped_uids=[], success_rate=1.0)
+        tplr.outer_step(m2, torch.optim.SGD(m2.parameters(), lr=0.3), gather_result=gr, transformer=miner.transformer,
+                        compressor=miner.compressor, xshapes=xs, totalks=tk, device="cpu", is_master=True, world_size=1, use_dct=True)
+        eng.outer_step(1)
+        for n, p in m2.named_parameters():
+            assert torch.allclose(p.detach(), dict(m1.named_parameters())[n].detach(), atol=2e-6), n
+    else:
+        eng.outer_step(1)
+        g = C.ChunkingTransformer(m1, 64)
+        moved = (eng.store.master_shard - eng.theta0).abs()
+        assert float(moved.max()) <= 0.3 + 1e-6 and float(moved[moved > 0].min()) >= 0.3 - 1e-6
+
+
+def test_engine_outer_step_through_public_api_and_fingerprint():
+    args = ModelArgs(dim=64, n_layers=1, n_heads=2, vocab_size=128, intermediate_size=128, max_seq_len=32)
+    m = build_model(args, seed=3)
+    eng = WindowEngine(m, EngineConfig(topk=8, use_dct=True, max_peers=4))
+    ref = build_model(args, seed=3)
+    gr, tr, comp, xs, tk = _gather_result(ref, 3, seed=5)
+    lr = 0.25
+    tplr.outer_step(ref, torch.optim.SGD(ref.parameters(), lr=lr), gather_result=gr, transformer=tr, compressor=comp,
+                    xshapes=xs, totalks=tk, device="cpu", is_master=True, world_size=1, use_dct=True)
+    fp = tplr.outer_step(m, torch.optim.SGD(m.parameters(), lr=lr), gather_result=gr, transformer=tr, compressor=comp,
+                         xshapes=xs, totalks=tk, device="cpu", is_master=True, world_size=1, use_dct=True)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(p.detach(), dict(m.named_parameters())[n].detach(), atol=2e-6), n
+    assert fp["global_l2_norm"] > 0
+
+
+def test_compare_model_with_debug_dict():
+    model = Tiny()
+    dbg = {n + "_debug": p.detach().flatten()[:2].tolist() for n, p in model.named_parameters()}
+    r = run(tplr.compare_model_with_debug_dict(model, dbg, learning_rate=0.01))
+    assert r["success"] and r["l2_norm"] == 0 and r["avg_steps_behind"] == 0 and r["param_count"] == 4
+    dbg["a_debug"] = [x + 0.02 for x in dbg["a_debug"]]
+    r = run(tplr.compare_model_with_debug_dict(model, dbg, learning_rate=0.01))
+    assert abs(r["max_steps_behind"] - 2.0) < 1e-3 and abs(r["max_diff"] - 0.02) < 1e-6
+    r = run(tplr.compare_model_with_debug_dict(model, dbg, 0.01, param_avg_change={"a": torch.tensor([0.04, 0.04])}))
+    assert abs(r["max_steps_behind"] - 0.5) < 1e-3
+    r = run(tplr.compare_model_with_debug_dict(model, {}, 0.01))
+    assert math.isinf(r["avg_steps_behind"]) and math.isinf(r["avg_l2_norm"])
+
+
+class _OverlapComms:
+    def __init__(self, ts): self.ts = ts
+    async def gradient_timestamp(self, uid, window): return self.ts[uid]
+
+
+def _overlap_case(idx_per_peer, ts, thr=0.9):
+    model = torch.nn.Module()
+    model.w = torch.nn.Parameter(torch.zeros(64, 64))
+    vals = [torch.zeros(i.shape) for i in idx_per_peer]
+    sd = SimpleNamespace(**{"widxs": [C.pack_12bit_indices(i) for i in idx_per_peer], "wvals": vals})
+    gr = SimpleNamespace(uids=list(ts), state_dict=sd)
+    neuron = SimpleNamespace(model=model, comms=_OverlapComms(ts), config=SimpleNamespace(device="cpu"))
+    return run(tplr.check_uid_index_overlap(neuron, gr, window=5, overlap_threshold=thr))
+
+
+def test_index_overlap_full_partial_none_and_offender_by_timestamp():
+    a = torch.arange(8).view(1, 1, 8)
+    full = _overlap_case([a, a.clone()], {10: 1.0, 11: 2.0})
+    assert full["pairs_high_ovlap"] == 1 and full["uids_over_thresh"] == {11: "mega"} and full["max_overlap"] == 1.0
+    half = _overlap_case([a, torch.tensor([[[0, 1, 2, 3, 100, 101, 102, 103]]])], {10: 5.0, 11: 2.0}, thr=0.5)
+    assert abs(half["mean_overlap"] - 0.5) < 1e-6 and half["uids_over_thresh"] == {10: "max"}
+    none = _overlap_case([a, a + 100, a + 200], {1: 1.0, 2: 2.0, 3: 3.0})
+    assert none["pairs_checked"] == 3 and none["pairs_high_ovlap"] == 0 and none["mean_overlap"] == 0
+    assert _overlap_case([a], {1: 1.0})["pairs_checked"] == 0
+
+
+def test_slash_levels():
+    assert [tplr.determine_slash_egregiousness(x) for x in (0.1, 0.5, 0.59, 0.6, 1.0)] == ["high", "max", "max", "mega", "mega"]
+    with pytest.raises(ValueError):
+        tplr.determine_slash_egregiousness(1.5)
+    assert tplr.instantiate_slashing_multiplier() == {"high": 0.5, "max": 0.0, "mega": 0.0}
+
+
+class _PeerComms:
+    def __init__(self, lists):
+        self.lists, self.peers, self.reserve_peers = lists, [], []
+    async def get_peer_list(self, fetch_previous=False):
+        return self.lists.get("prev" if fetch_previous else "cur")
+
+
+def test_update_peers_rotation():
+    inst = SimpleNamespace(comms=_PeerComms({"prev": ([1, 2], [3], 4), "cur": ([5, 6], [7], 10)}), next_peers=None,
+                           next_reserve_peers=None, peers_update_window=8,
+                           hparams=SimpleNamespace(peer_replacement_frequency=2, peer_list_window_margin=1))
+    run(tplr.update_peers(inst, window=9, peer_start=tplr.T()))
+    assert inst.comms.peers == [1, 2] and inst.next_peers == [5, 6] and inst.peers_update_window == 10
+    run(tplr.update_peers(inst, window=10, peer_start=tplr.T()))
+    assert inst.comms.peers == [5, 6] and inst.comms.reserve_peers == [7] and inst.next_peers is None
+
+
+def test_handle_checkpoint_catchup_replays_scheduler(monkeypatch):
+    calls = []
+
+    async def fake_catchup(instance, start, aggregator_device=None):
+        calls.append(start)
+    monkeypatch.setattr(tplr.neurons, "catchup_with_aggregation_server", fake_catchup)
+    sched = SimpleNamespace(n=0)
+    sched.step = lambda: setattr(sched, "n", sched.n + 1)
+    hp = SimpleNamespace(inner_steps=3, anneal_mode={"enabled": False},
+                         optimizer={"type": "adamw", "adamw": {"scheduler": {"warmup_inner_steps": 5, "initial_warmup_inner_steps": 9,
+                                                                             "replay_rewind_inner_steps": 4}}})
+    inst = SimpleNamespace(hparams=hp, start_window=10, current_window=20, inner_scheduler=sched, inner_scheduler_step_count=0,
+                           warmup_inner_steps=0, warmup_steps_taken=7, should_skip_scheduler_step=lambda: False)
+    run(tplr.handle_checkpoint_catchup(inst, True, 15, 6, False))
+    assert calls == [15] and sched.n == 6 * 3 - 4 and inst.warmup_inner_steps == 5 and inst.warmup_steps_taken == 0
+    run(tplr.handle_checkpoint_catchup(inst, True, 15, 6, True))
+    assert calls[-1] == 10 and inst.warmup_inner_steps == 9
+    run(tplr.handle_checkpoint_catchup(inst, False, 0, 0, False))
+    assert calls[-1] == 10
+    run(tplr.handle_checkpoint_catchup(inst, True, 20, 2, False))
+    assert len(calls) == 3                       # up to date: no replay
+    hp.anneal_mode = {"enabled": True, "start_global_step": 4, "warmup_inner_steps": 2}
+    sched.n = 0
+    run(tplr.handle_checkpoint_catchup(inst, True, 20, 6, False))
+    assert sched.n == 6 and inst.warmup_steps_taken == 2
