@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--peers", type=int, default=8)
     ap.add_argument("--topk", type=int, default=32)
     ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
-    ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
+    ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 

@@ -1,0 +1,721 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2), optionally fused with a tensor-parallel collective.
+//
+//   C[M,N] (+)= op(A) * op(B)     same operand layouts as tplr_gemm_bf16 (K-major or MN-major)
+//
+// A cluster of two CTAs computes one 256 x 256 tile: each CTA stages its own 128 rows of A and
+// its own 128 rows of B (so every shared-memory byte feeds two SMs' tensor cores), the even CTA
+// issues tcgen05.mma.cta_group::2, and each CTA drains its 128 x 256 half of the accumulator
+// from its own tensor memory.  6 smem stages of 32 KB per CTA, two accumulator buffers.
+//
+// Fused collectives (one process per GPU, peers mapped through the symmetric heap):
+//   gather  (all-gather -> GEMM): trailing "comm" CTAs of the same launch pull the peers' row
+//           shards of one operand into this GPU's full buffer with bulk copies, 128 rows at a
+//           time, and release one flag per 128 rows; the TMA producer of a compute CTA waits
+//           (bounded) for the flags of the rows it is about to load.  Every remote byte crosses
+//           NVLink once and the tiles of the local shard start at once.
+//   scatter (GEMM -> reduce-scatter): compute CTAs store the bf16 partial tile into this GPU's
+//           staging buffer and write one flag into the memory of the rank that owns those rows;
+//           that rank's comm CTAs wait (bounded) for the flags of all ranks, pull the partial
+//           tiles with TMA, sum them in fp32 and store the owned rows.
+// No load in this file carries a cluster-multicast qualifier; only tcgen05.commit does.
+// Every wait is bounded by wall time; on expiry TPLR_ST_WAIT_TIMEOUT is set and all roles return.
+//
+// Replaces cuBLAS + NCCL behind the reference's tensor-parallel plan: colwise q/k/v/w1/w3,
+// rowwise wo/w2 with sequence-sharded activations (torchtitan models/llama3/infra/parallelize.py:151-219).
+#include "tcgen05.cuh"
+
+namespace {
+using namespace tplr_tc;
+
+constexpr int TILE_M = 256, CTA_M = 128, TILE_N = 256, CTA_N = 128, BK = 64, STAGES = 6, UMMA_K = 16;
+constexpr int A_STAGE = CTA_M * BK * 2;            // 16 KB
+constexpr int B_STAGE = CTA_N * BK * 2;            // 16 KB
+constexpr int STAGE_BYTES = A_STAGE + B_STAGE;     // 32 KB
+constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;      // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_RANKS = 8;
+constexpr int CHUNK_ROWS = 128;                    // gather / scatter flag granularity (rows)
+constexpr int RS_ROWS = 16;                        // rows per reducer step
+constexpr int RS_STAGES = 3, RS_STAGE_BYTES = 2 * STAGE_BYTES;   // 3 x 64 KB
+
+struct Gemm2Params {
+  CUtensorMap tmA, tmB;
+  CUtensorMap tmC;                   // output: box 64 x 32 bf16 or 32 x 32 fp32, 128-byte swizzle
+  int c_tma;                         // 1: epilogue through TMA, 0: direct stores (unaligned C)
+  CUtensorMap tmPart[MAX_RANKS];     // scatter: every rank's staging buffer, box 256 x RS_ROWS, no swizzle
+  void* C;
+  long long ldc;
+  int M, N, K;
+  unsigned int* status;
+  int n_compute_pairs;               // CTA pairs [0, n_compute_pairs) compute, the rest are comm CTAs
+  int group_m;                       // tile order: bands of group_m tile rows, tile row fastest inside a band
+  int m_rot;                         // rotation of the tile-row order (in 256-row tiles)
+  int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
+  int world, rank;
+  unsigned int epoch;
+  // gather
+  int ag_operand;                    // 0 none, 1 A, 2 B
+  int ag_rows_per_rank;              // rows (outer dimension) of the gathered operand per rank
+  long long ag_row_bytes;            // bytes of one dense row
+  const uint8_t* ag_src[MAX_RANKS];  // base of every rank's full buffer (own entry unused)
+  uint8_t* ag_dst;                   // base of this rank's full buffer
+  unsigned int* ag_flags;            // one per CHUNK_ROWS rows of the full buffer (local memory)
+  // scatter
+  int rs_on;
+  int rs_rows_per_rank;
+  unsigned int* rs_flag_dst[MAX_RANKS];   // rank o's flag array [world][chunks_per_rank][tiles_n], as mapped here
+  unsigned int* rs_flags;            // this rank's flag array
+  __nv_bfloat16* rs_out;             // [rs_rows_per_rank, N] owned rows of the reduced result
+  long long rs_ld_out;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `saddr` (a shared::cta address of this CTA) inside CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: data lands in this CTA, completion bytes go to `bar` which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for *flag == want (flags carry the call's epoch).  SYS selects the scope of the acquire.
+template <bool SYS>
+__device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int want, volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    const unsigned int v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v == want) return true;
+    if ((i & 7u) == 7u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = gtimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// tile index -> (tile row, tile column) under the launch's order
+__device__ __forceinline__ void tile_coords(const Gemm2Params& p, int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band = p.group_m * tiles_n;
+  const int g = t / band, first = g * p.group_m;
+  const int rows = p.group_m < tiles_m - first ? p.group_m : tiles_m - first;
+  const int in = t - g * band;
+  int tml = first + in % rows;
+  tn = in / rows;
+  if (p.m_inter > 1) tml = (tml % p.m_inter) * (tiles_m / p.m_inter) + tml / p.m_inter;
+  tm = tml + p.m_rot;
+  if (tm >= tiles_m) tm -= tiles_m;
+}
+
+// Epilogue without TMA (C not 16-byte aligned or odd leading dimension): each lane stores its own row.
+template <int EPI>
+__device__ __forceinline__ void epilogue_direct(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int n0) {
+  const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+  for (int c = 0; c < TILE_N / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(quad * 32) << 16), r);
+    const int col0 = n0 + c * 32;
+    if (row < p.M && col0 < p.N) {
+      if (EPI == 0) {
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+        for (int e = 0; e < 32 && col0 + e < p.N; ++e) crow[e] = __float2bfloat16(__uint_as_float(r[e]));
+      } else {
+        float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+        for (int e = 0; e < 32 && col0 + e < p.N; ++e) {
+          const float o = __uint_as_float(r[e]);
+          crow[e] = (EPI == 1) ? crow[e] + o : o;
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+
+// Epilogue through shared memory and TMA: a warp stages 32 rows x 128 bytes (64 bf16 or 32 fp32
+// columns) in 128-byte-swizzled order, then one lane stores (EPI 0, 2) or reduce-adds (EPI 1) the
+// box.  Two staging buffers per warp; `n_boxes` counts the boxes this warp has issued so far.
+template <int EPI>
+__device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int n0,
+                                             uint32_t stage_base, uint32_t& n_boxes) {
+  constexpr int COLS = EPI == 0 ? 64 : 32;
+  const int row0 = m0 + quad * 32;
+  const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+  for (int c = 0; c < TILE_N / COLS; ++c) {
+    const int col0 = n0 + c * COLS;
+    if (row0 >= p.M || col0 >= p.N) break;          // warp-uniform: nothing of this box is inside C
+    const uint32_t buf = stage_base + (n_boxes & 1u) * 4096u;
+    if (n_boxes >= 2) {                              // the box issued two steps ago has left this buffer
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      __syncwarp();
+    }
+    const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
+    if (EPI == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + c * 64 + h * 32 + ((uint32_t)(quad * 32) << 16), r);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint32_t pw[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2 * e]), __uint_as_float(r[8 * v + 2 * e + 1]));
+            pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          const uint32_t j = (uint32_t)(h * 4 + v);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((j ^ sw) << 4)), "r"(pw[0]), "r"(pw[1]),
+                       "r"(pw[2]), "r"(pw[3]) : "memory");
+        }
+      }
+    } else {
+      uint32_t r[32];
+      tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(quad * 32) << 16), r);
+#pragma unroll
+      for (int v = 0; v < 8; ++v)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((uint32_t)v ^ sw) << 4)), "r"(r[4 * v]),
+                     "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3]) : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      if (EPI == 1) tma_reduce_add_2d(&p.tmC, buf, col0, row0);
+      else          tma_store_2d(&p.tmC, buf, col0, row0);
+      bulk_commit();
+    }
+    ++n_boxes;
+  }
+}
+
+// EPI: 0 store bf16, 1 fp32 accumulate (C += acc), 2 store fp32
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm2_kernel(const __grid_constant__ Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2], bar_epi[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ uint32_t s_ready[32];   // gather: bit c set once chunk c was seen ready (1024 chunks)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const bool is_compute = pair < p.n_compute_pairs;
+  const bool is_reducer = !is_compute && p.rs_on;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + TILE_N - 1) / TILE_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), is_reducer ? 4 : 1);
+    }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 8); mbar_init(smem_u32(&bar_epi[s]), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (threadIdx.x < 32) s_ready[threadIdx.x] = 0;
+  if (warp == 1 && is_compute) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before any remote arrive or TMA completion
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sA = sbase, sB = sbase + STAGES * A_STAGE, sEpi = sbase + STAGES * STAGE_BYTES;
+
+  if (is_compute) {
+    if (warp == 0) {
+      // ----------------------------- TMA producer (both CTAs of the pair) ------------
+      if (lane == 0) {
+        const int chunks_per_rank = p.ag_operand ? p.ag_rows_per_rank / CHUNK_ROWS : 1;
+        // bounded wait until rows [r0, r0 + nrows) of the gathered operand are in local memory
+        auto rows_ready = [&](int r0, int nrows) -> bool {
+          const int c0 = r0 / CHUNK_ROWS, c1 = (r0 + nrows - 1) / CHUNK_ROWS;
+          for (int c = c0; c <= c1; ++c) {
+            if (c / chunks_per_rank == p.rank || c >= p.world * chunks_per_rank) continue;
+            if (s_ready[(c >> 5) & 31] & (1u << (c & 31))) continue;
+            if (!flag_wait<false>(p.ag_flags + c, p.epoch, abort_flag)) return false;
+            fence_proxy_async();
+            s_ready[(c >> 5) & 31] |= 1u << (c & 31);
+          }
+          return true;
+        };
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs) {
+          int tm, tn;
+          tile_coords(p, t, tiles_m, tiles_n, tm, tn);
+          const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N + (int)cr * CTA_N;
+          if (p.ag_operand == 1 && !A_MN) ok = rows_ready(m0, CTA_M);
+          if (p.ag_operand == 2 && !B_MN) ok = ok && rows_ready(n0, CTA_N);
+          for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+            // k order rotated so that the rows of the local shard come first when k is the gathered dimension
+            int kbr = kb;
+            if ((p.ag_operand == 1 && A_MN) || (p.ag_operand == 2 && B_MN)) {
+              kbr = kb + p.rank * (p.ag_rows_per_rank / BK);
+              if (kbr >= k_blocks) kbr -= k_blocks;
+              if (!(ok = rows_ready(kbr * BK, BK))) break;
+            }
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!(ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, abort_flag))) break;
+            const uint32_t fb_local = smem_u32(&bar_full[s]);
+            const uint32_t fb = mapa(fb_local, 0);
+            if (cr == 0) mbar_expect_tx(fb_local, 2 * STAGE_BYTES);
+            const uint32_t a_dst = sA + s * A_STAGE, b_dst = sB + s * B_STAGE;
+            const int k0 = kbr * BK;
+            if (!A_MN) {
+              tma_load_2d_pair(a_dst, &p.tmA, fb, k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CTA_M / 64; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &p.tmA, fb, m0 + 64 * j, k0);
+            }
+            if (!B_MN) {
+              tma_load_2d_pair(b_dst, &p.tmB, fb, k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CTA_N / 64; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &p.tmB, fb, n0 + 64 * j, k0);
+            }
+          }
+        }
+        // drain (leader): every armed stage has landed in both CTAs before the pair may retire
+        if (cr == 0) {
+          for (uint32_t back = 0; back < STAGES && back < it; ++back) {
+            const uint32_t j = it - 1 - back;
+            mbar_wait(smem_u32(&bar_full[j % STAGES]), (j / STAGES) & 1, abort_flag);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ----------------------------- MMA issuer (even CTA only) ----------------------
+      if (lane == 0 && cr == 0) {
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                               ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+        uint32_t it = 0, tile_i = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
+          const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+          if (!(ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_ph ^ 1, abort_flag))) break;
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * TILE_N;
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag))) break;
+            tcgen05_fence_after();
+            const uint32_t a_base = sA + s * A_STAGE, b_base = sB + s * B_STAGE;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint64_t da = A_MN ? make_desc(a_base + kk * (UMMA_K * 128), BK * 128, 1024)
+                                       : make_desc(a_base + kk * (UMMA_K * 2), 16, 1024);
+              const uint64_t db = B_MN ? make_desc(b_base + kk * (UMMA_K * 128), BK * 128, 1024)
+                                       : make_desc(b_base + kk * (UMMA_K * 2), 16, 1024);
+              umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit_pair(smem_u32(&bar_empty[s]));
+          }
+          if (ok) umma_commit_pair(smem_u32(&bar_tfull[acc]));
+        }
+      }
+    } else {
+      // ----------------------------- epilogue (warps 2..5 of both CTAs) --------------
+      const int quad = warp & 3;
+      uint32_t tile_i = 0, n_boxes = 0;
+      bool ok = true;
+      const int chunks_per_rank = p.rs_on ? p.rs_rows_per_rank / CHUNK_ROWS : 1;
+      for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
+        int tm, tn;
+        tile_coords(p, t, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N;
+        const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
+        ok = mbar_wait(smem_u32(&bar_tfull[acc]), acc_ph, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * TILE_N;
+        if (p.c_tma) epilogue_tma<EPI>(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
+        else         epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (EPI == 0 && p.rs_on && lane == 0) {
+          bulk_wait0();            // this warp's rows of the partial tile are written
+          __threadfence();
+          mbar_arrive(smem_u32(&bar_epi[acc]));
+        }
+        if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[acc]), 0));
+        if (EPI == 0 && p.rs_on && warp == 2 && lane == 0) {
+          // once all four warps stored their rows (bounded wait), tell the rank that owns them
+          if (mbar_wait(smem_u32(&bar_epi[acc]), acc_ph, abort_flag) && m0 < p.M) {
+            const int chunk = m0 / CHUNK_ROWS, owner = chunk / chunks_per_rank, cl = chunk - owner * chunks_per_rank;
+            __threadfence_system();
+            st_release_sys(p.rs_flag_dst[owner] + ((long long)p.rank * chunks_per_rank + cl) * tiles_n + tn, p.epoch);
+          }
+        }
+      }
+      if (lane == 0) bulk_wait0();   // staging buffers are read out before the CTA retires
+    }
+  } else if (p.ag_operand) {
+    // ----------------------------- comm CTA: pull the peers' row shards -----------------
+    if (warp == 0 && lane == 0) {
+      const int ci = (pair - p.n_compute_pairs) * 2 + (int)cr, n_comm = (n_pairs - p.n_compute_pairs) * 2;
+      const int chunks_per_rank = p.ag_rows_per_rank / CHUNK_ROWS;
+      const long long chunk_bytes = (long long)CHUNK_ROWS * p.ag_row_bytes;
+      const int spc = (int)((chunk_bytes + STAGE_BYTES - 1) / STAGE_BYTES);   // steps per chunk
+      const int peer_chunks = (p.world - 1) * chunks_per_rank;
+      const int my_chunks = ci < peer_chunks ? (peer_chunks - ci + n_comm - 1) / n_comm : 0;
+      const long long total = (long long)my_chunks * spc;
+      auto locate = [&](long long g, long long& off, uint32_t& bytes, int& chunk, int& src, bool& last) {
+        const int q = ci + (int)(g / spc) * n_comm;          // q-th peer chunk in ring order
+        const int piece = (int)(g % spc);
+        src = (p.rank + 1 + q / chunks_per_rank) % p.world;
+        chunk = src * chunks_per_rank + q % chunks_per_rank;
+        off = (long long)chunk * chunk_bytes + (long long)piece * STAGE_BYTES;
+        const long long left = chunk_bytes - (long long)piece * STAGE_BYTES;
+        bytes = (uint32_t)(left < STAGE_BYTES ? left : STAGE_BYTES);
+        last = piece == spc - 1;
+      };
+      long long issued = 0, stored = 0;
+      bool ok = true;
+      while (stored < total && ok) {
+        // a stage is reused by load g only after the store of step g - STAGES finished reading it
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        while (issued < total && issued < stored + STAGES - 1) {
+          long long off; uint32_t bytes; int chunk, src; bool last;
+          locate(issued, off, bytes, chunk, src, last);
+          const int s = (int)(issued % STAGES);
+          const uint32_t fb = smem_u32(&bar_full[s]);
+          mbar_expect_tx(fb, bytes);
+          bulk_g2s(sbase + s * STAGE_BYTES, p.ag_src[src] + off, bytes, fb);
+          ++issued;
+        }
+        long long off; uint32_t bytes; int chunk, src; bool last;
+        locate(stored, off, bytes, chunk, src, last);
+        const int s = (int)(stored % STAGES);
+        if (!(ok = mbar_wait(smem_u32(&bar_full[s]), (uint32_t)((stored / STAGES) & 1), abort_flag))) break;
+        bulk_s2g(p.ag_dst + off, sbase + s * STAGE_BYTES, bytes);
+        bulk_commit();
+        ++stored;
+        if (last) {
+          bulk_wait0();            // the whole chunk is written
+          fence_proxy_async();
+          __threadfence();
+          st_release_gpu(p.ag_flags + chunk, p.epoch);
+        }
+      }
+      bulk_wait0();
+      // loads that were issued but never stored (abort path) must land before the CTA retires
+      for (long long g = stored; g < issued; ++g)
+        mbar_wait(smem_u32(&bar_full[g % STAGES]), (uint32_t)((g / STAGES) & 1), abort_flag);
+    }
+  } else if (p.rs_on) {
+    // ----------------------------- comm CTA: reduce the rows this rank owns -------------
+    const int ci = (pair - p.n_compute_pairs) * 2 + (int)cr, n_comm = (n_pairs - p.n_compute_pairs) * 2;
+    const int chunks_per_rank = p.rs_rows_per_rank / CHUNK_ROWS;
+    constexpr int SUBS = CHUNK_ROWS / RS_ROWS;
+    constexpr uint32_t SRC_BYTES = TILE_N * RS_ROWS * 2;   // 8 KB per source per step
+    if (warp == 0) {
+      if (lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        int cnt = 0;
+        for (int u = 0; u < 2 * num_tiles && ok; ++u) {
+          int tm, tn;
+          tile_coords(p, u >> 1, tiles_m, tiles_n, tm, tn);
+          const int chunk = tm * 2 + (u & 1);
+          if (chunk / chunks_per_rank != p.rank) continue;
+          if ((cnt++) % n_comm != ci) continue;
+          const int cl = chunk - p.rank * chunks_per_rank;
+          for (int s = 0; s < p.world && ok; ++s)
+            ok = flag_wait<true>(p.rs_flags + ((long long)s * chunks_per_rank + cl) * tiles_n + tn, p.epoch, abort_flag);
+          if (!ok) break;
+          fence_proxy_async();
+          for (int sub = 0; sub < SUBS; ++sub, ++it) {
+            const int st = it % RS_STAGES;
+            const uint32_t ph = (it / RS_STAGES) & 1;
+            if (!(ok = mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1, abort_flag))) break;
+            const uint32_t fb = smem_u32(&bar_full[st]);
+            mbar_expect_tx(fb, SRC_BYTES * p.world);
+            const int y = p.rank * p.rs_rows_per_rank + cl * CHUNK_ROWS + sub * RS_ROWS;
+            for (int j = 0; j < p.world; ++j) {
+              const int s = (p.rank + 1 + j) % p.world;
+              tma_load_2d(sbase + st * RS_STAGE_BYTES + s * SRC_BYTES, &p.tmPart[s], fb, tn * TILE_N, y);
+            }
+          }
+        }
+        for (uint32_t back = 0; back < RS_STAGES && back < it; ++back) {
+          const uint32_t j = it - 1 - back;
+          mbar_wait(smem_u32(&bar_full[j % RS_STAGES]), (j / RS_STAGES) & 1, abort_flag);
+        }
+      }
+    } else if (warp >= 2) {
+      const int tid = threadIdx.x - 64;   // 0..127
+      uint32_t it = 0;
+      bool ok = true;
+      int cnt = 0;
+      for (int u = 0; u < 2 * num_tiles && ok; ++u) {
+        int tm, tn;
+        tile_coords(p, u >> 1, tiles_m, tiles_n, tm, tn);
+        const int chunk = tm * 2 + (u & 1);
+        if (chunk / chunks_per_rank != p.rank) continue;
+        if ((cnt++) % n_comm != ci) continue;
+        const int cl = chunk - p.rank * chunks_per_rank;
+        for (int sub = 0; sub < SUBS; ++sub, ++it) {
+          const int st = it % RS_STAGES;
+          ok = mbar_wait(smem_u32(&bar_full[st]), (it / RS_STAGES) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const uint8_t* sb = smem + st * RS_STAGE_BYTES;
+#pragma unroll
+          for (int j = 0; j < (RS_ROWS * TILE_N / 8) / 128; ++j) {
+            const int v = tid + 128 * j, r = v >> 5, cv = v & 31;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            for (int s = 0; s < p.world; ++s) {
+              const uint4 q = *reinterpret_cast<const uint4*>(sb + s * SRC_BYTES + r * (TILE_N * 2) + cv * 16);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h[e]);
+                acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
+              }
+            }
+            const int orow = cl * CHUNK_ROWS + sub * RS_ROWS + r, ocol = tn * TILE_N + cv * 8;
+            if (ocol < p.N) {
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+              *reinterpret_cast<uint4*>(p.rs_out + (long long)orow * p.rs_ld_out + ocol) = o;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_empty[st]));
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // no CTA retires while its peer may still signal its barriers or read its smem
+  if (warp == 1 && is_compute) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+  if (threadIdx.x == 0 && s_abort && p.status) atomicOr(p.status, TPLR_ST_WAIT_TIMEOUT);
+}
+
+// ------------------------------ host side ----------------------------------------------
+template <bool A_MN, bool B_MN, int EPI>
+int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
+  auto kern = gemm2_kernel<A_MN, B_MN, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  // all CTAs must be resident at once: compute CTAs wait for comm CTAs of the same launch
+  static int max_clusters[2][2][3] = {};
+  int& mc = max_clusters[A_MN][B_MN][EPI];
+  if (mc == 0) {
+    cfg.gridDim = dim3(2 * (tplr_sm_count() / 2));
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) return (int)e;
+    mc = n > 0 ? n : -1;
+  }
+  if (mc < 1) return -105;
+  int pairs = mc < tplr_sm_count() / 2 ? mc : tplr_sm_count() / 2;
+  if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
+  if (n_comm_pairs >= pairs) return -106;
+  const int tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
+  int compute = pairs - n_comm_pairs;
+  if (compute > tiles) compute = tiles;
+  p.n_compute_pairs = compute;
+  cfg.gridDim = dim3(2 * (compute + n_comm_pairs));
+  return (int)cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int max_pairs, cudaStream_t st) {
+#define TPLR_GEMM2_CASE(AM, BMJ, E) \
+  if (a_mn == AM && b_mn == BMJ && epi == E) return launch2<AM != 0, BMJ != 0, E>(p, n_comm_pairs, max_pairs, st);
+  TPLR_GEMM2_CASE(0, 0, 0) TPLR_GEMM2_CASE(0, 0, 1) TPLR_GEMM2_CASE(0, 0, 2)
+  TPLR_GEMM2_CASE(0, 1, 0) TPLR_GEMM2_CASE(0, 1, 1) TPLR_GEMM2_CASE(0, 1, 2)
+  TPLR_GEMM2_CASE(1, 1, 0) TPLR_GEMM2_CASE(1, 1, 1) TPLR_GEMM2_CASE(1, 1, 2)
+  TPLR_GEMM2_CASE(1, 0, 0) TPLR_GEMM2_CASE(1, 0, 1) TPLR_GEMM2_CASE(1, 0, 2)
+#undef TPLR_GEMM2_CASE
+  return -104;
+}
+
+// Fills the operand maps and the plain fields; returns 0 or a negative argument error.
+int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                long long ldb, long long ldc, int a_mn, int b_mn, int epi, unsigned int* status) {
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -101;
+  if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
+  if (!(b_mn ? make_map(&p.tmB, B, N, K, ldb, 64, BK) : make_map(&p.tmB, B, K, N, ldb, BK, CTA_N))) return -103;
+  p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
+  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = 8; p.m_rot = 0; p.m_inter = 1;
+  p.ag_operand = 0; p.rs_on = 0;
+  const bool f32 = epi != 0;
+  p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
+  if (p.c_tma && !make_map(&p.tmC, C, N, M, ldc, f32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, f32)) return -110;
+  return 0;
+}
+
+}  // namespace
+
+// Same contract as tplr_gemm_bf16; max_pairs <= 0 uses every SM pair.
+TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                             long long ldb, long long ldc, int a_mn, int b_mn, int epi, unsigned int* status,
+                             int max_pairs, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
+  return dispatch2(p, a_mn, b_mn, epi, 0, max_pairs, (cudaStream_t)stream);
+}
+
+// All-gather fused into the GEMM.  Operand `ag_operand` (1 = A, 2 = B) is the local FULL buffer
+// whose rows (its outer dimension: m or n when K-major, k when MN-major) are sharded over `world`
+// ranks, `rows_per_rank` (multiple of 128) each; rank r's rows are valid in rank r's buffer when the
+// kernel starts (the caller runs a barrier first) and are copied from `peer_bases[r]` into the local
+// buffer by `n_comm_pairs` CTA pairs while the other pairs compute.  `flags` holds one zero-initialised
+// word per 128 rows of the full buffer; `epoch` must differ from every earlier call's on these flags.
+TPLR_API int tplr_gemm2_gather(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, int a_mn, int b_mn, int epi, int ag_operand,
+                               int world, int rank, int rows_per_rank, const void* const* peer_bases,
+                               unsigned int* flags, unsigned int epoch, int n_comm_pairs, unsigned int* status,
+                               void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || (ag_operand != 1 && ag_operand != 2)) return -107;
+  if (rows_per_rank % CHUNK_ROWS || (long long)world * rows_per_rank / CHUNK_ROWS > 1024 || n_comm_pairs < 1) return -107;
+  const bool mn = ag_operand == 1 ? a_mn != 0 : b_mn != 0;
+  const long long outer = mn ? K : (ag_operand == 1 ? M : N);
+  if (outer != (long long)world * rows_per_rank) return -108;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
+  p.world = world; p.rank = rank; p.epoch = epoch;
+  p.ag_operand = ag_operand; p.ag_rows_per_rank = rows_per_rank;
+  p.ag_row_bytes = (ag_operand == 1 ? lda : ldb) * 2;
+  for (int r = 0; r < world; ++r) p.ag_src[r] = static_cast<const uint8_t*>(peer_bases[r]);
+  p.ag_dst = static_cast<uint8_t*>(const_cast<void*>(ag_operand == 1 ? A : B));
+  p.ag_flags = flags;
+  if (!mn && ag_operand == 1) {           // tiles of the local row shard first, then the peers in ring order
+    p.group_m = 1;
+    p.m_rot = (int)(((long long)rank * rows_per_rank) / TILE_M);
+  }
+  return dispatch2(p, a_mn, b_mn, epi, world > 1 ? n_comm_pairs : 0, 0, (cudaStream_t)stream);
+}
+
+// GEMM fused with a reduce-scatter over the rows of C.  Every rank computes its partial
+// [M,N] = op(A) op(B) over its own K shard into its bf16 staging buffer `stage` (leading dimension
+// ldc); rank o owns rows [o*rows_per_rank, (o+1)*rows_per_rank) and receives their fp32-accumulated
+// sum over all ranks in `out` [rows_per_rank, N].  `peer_stage[r]` / `peer_flags[r]` are rank r's
+// staging buffer / flag array as mapped in this process (own entries are the local ones); the flag
+// array holds world * (rows_per_rank/128) * ceil(N/256) zero-initialised words.
+TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, void* stage, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int a_mn, int b_mn, int world, int rank,
+                                int rows_per_rank, const void* const* peer_stage, void* const* peer_flags,
+                                void* out, long long ld_out, unsigned int epoch, int n_comm_pairs,
+                                unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || n_comm_pairs < 1) return -107;
+  if (rows_per_rank % CHUNK_ROWS || M != world * rows_per_rank || (N % 8) || (ldc % 8) || (ld_out % 8)) return -108;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, A, B, stage, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, status)) return r;
+  p.world = world; p.rank = rank; p.epoch = epoch;
+  p.rs_on = 1; p.rs_rows_per_rank = rows_per_rank;
+  for (int r = 0; r < world; ++r) {
+    if (!make_map(&p.tmPart[r], peer_stage[r], N, M, ldc, TILE_N, RS_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return -109;
+    p.rs_flag_dst[r] = static_cast<unsigned int*>(peer_flags[r]);
+  }
+  p.rs_flags = static_cast<unsigned int*>(peer_flags[rank]);
+  p.rs_out = static_cast<__nv_bfloat16*>(out);
+  p.rs_ld_out = ld_out;
+  // every band of tile rows touches every owner, so all ranks' reducers work throughout the GEMM
+  const int tiles_m = (M + TILE_M - 1) / TILE_M;
+  if (world > 1 && tiles_m % world == 0) p.m_inter = world;
+  return dispatch2(p, a_mn, b_mn, 0, n_comm_pairs, 0, (cudaStream_t)stream);
+}

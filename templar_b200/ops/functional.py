@@ -23,15 +23,15 @@ import torch.nn.functional as F
 
 from . import native
 
-# "tcgen05": own GEMM kernel on CUDA bf16; "cublas": torch.matmul (library).  Switched by
-# templar_b200.ops.set_gemm_backend().
+# "tcgen05": own GEMM kernel, one CTA per tile; "tcgen05_2sm": own GEMM kernel on CTA pairs
+# (cta_group::2); "cublas": torch.matmul (library).  Switched by templar_b200.ops.set_gemm_backend().
 _GEMM_BACKEND = "tcgen05"
 _status_words: dict[int, torch.Tensor] = {}
 
 
 def set_gemm_backend(name: str) -> None:
     global _GEMM_BACKEND
-    if name not in ("tcgen05", "cublas"):
+    if name not in ("tcgen05", "tcgen05_2sm", "cublas"):
         raise ValueError(name)
     _GEMM_BACKEND = name
 
@@ -73,7 +73,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise ValueError(f"gemm inner dimensions differ: {K} vs {Kb}")
     if out_dtype is None:
         out_dtype = out.dtype if out is not None else a.dtype
-    use_native = (_GEMM_BACKEND == "tcgen05" and a.is_cuda and a.dtype == torch.bfloat16
+    use_native = (_GEMM_BACKEND != "cublas" and a.is_cuda and a.dtype == torch.bfloat16
                   and b.dtype == torch.bfloat16 and a.stride(-1) == 1 and b.stride(-1) == 1
                   and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0
                   and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
@@ -86,9 +86,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if accumulate and out.dtype != torch.float32:
             raise ValueError("gemm: accumulate needs an fp32 out")
         epi = 0 if out.dtype == torch.bfloat16 else (1 if accumulate else 2)
-        err = native.lib().tplr_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
-                                           a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), epi,
-                                           status_word(a.device).data_ptr(), 0, native.stream_ptr())
+        L = native.lib()
+        fn = L.tplr_gemm2_bf16 if _GEMM_BACKEND == "tcgen05_2sm" else L.tplr_gemm_bf16
+        err = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                 a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), epi,
+                 status_word(a.device).data_ptr(), 0, native.stream_ptr())
         native.check(err, "tplr_gemm_bf16")
         return out
     A = a.t() if a_mn else a

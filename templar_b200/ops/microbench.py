@@ -68,11 +68,11 @@ def bench_gemm(a):
     B = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
     out_dtype = torch.float32 if a.layout == "tn" else torch.bfloat16
     out = torch.zeros(M, N, device="cuda", dtype=out_dtype)
-    OF.set_gemm_backend("tcgen05")
+    OF.set_gemm_backend(a.backend)
     med, best = time_ms(lambda: OF.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=(a.layout == "tn")), a.iters)
     pk = peaks()
     fl = 2.0 * M * N * K
-    rec = {"case": "gemm", "layout": a.layout, "M": M, "N": N, "K": K, "ms_median": med, "ms_best": best,
+    rec = {"case": "gemm", "backend": a.backend, "layout": a.layout, "M": M, "N": N, "K": K, "ms_median": med, "ms_best": best,
            "tflops": fl / med / 1e9, "frac_of_peak": fl / med / 1e9 / pk["bf16_tflops"], "peaks": pk["source"],
            "status": int(OF.status_word("cuda").item())}
     if a.compare:
@@ -148,6 +148,7 @@ def main():
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
     ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--backend", default="tcgen05_2sm", choices=["tcgen05", "tcgen05_2sm"])
     ap.add_argument("--model", default="1B")
     ap.add_argument("--topk", type=int, default=32)
     ap.add_argument("--peers", type=int, default=8)

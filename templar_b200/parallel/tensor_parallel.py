@@ -1,0 +1,201 @@
+"""Tensor parallelism with sequence-sharded activations on fused compute+collective kernels.
+
+Plan (the reference's, torchtitan models/llama3/infra/parallelize.py:151-219): q/k/v and w1/w3 are
+split by output feature (column parallel), wo and w2 by input feature (row parallel), and the
+activations between blocks are sharded by token.  Where the reference runs an NCCL all-gather
+before a cuBLAS GEMM and a cuBLAS GEMM before an NCCL reduce-scatter, this module issues ONE
+kernel for each pair (``tplr_gemm2_gather`` / ``tplr_gemm2_scatter``): the collective moves over
+NVLink peer memory inside the GEMM launch, tile by tile.
+
+Buffers live on the symmetric heap: two gather buffers (alternated so that a rank may refill one
+while a slower peer still copies the other), one staging buffer for partial sums and one flag
+array.  Every fused call is preceded by one stream-ordered heap barrier, which both publishes the
+caller's rows to its peers and proves that all peers are done with the buffers of the call before
+the previous one.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import functional as OF
+from ..ops import native
+from .symmetric import SymmetricHeap
+
+_MAX_CHUNKS = 1024
+
+
+class TensorParallel:
+    """Workspace and launcher of the fused kernels for one tensor-parallel group.
+
+    ``rows`` is the number of tokens of the full (gathered) activation, ``width`` the widest
+    activation that is gathered or reduce-scattered (the model dimension)."""
+
+    def __init__(self, heap: SymmetricHeap, rows: int, width: int, n_comm_pairs: int = 8):
+        self.heap, self.rank, self.world = heap, heap.rank, heap.world_size
+        native.require(rows % (128 * self.world) == 0, "tensor parallel: rows must be a multiple of 128 * world")
+        native.require(rows // 128 <= _MAX_CHUNKS, "tensor parallel: too many rows")
+        self.rows, self.width = rows, width
+        self.rows_per_rank = rows // self.world
+        self.n_comm_pairs = n_comm_pairs
+        self.device = heap.device
+        self._g = [heap.alloc(rows * width, torch.bfloat16) for _ in range(2)]
+        self._s = heap.alloc(rows * width, torch.bfloat16)
+        tiles_n = -(-width // 256)
+        self._sflags = heap.alloc(self.world * (self.rows_per_rank // 128) * tiles_n, torch.int32)
+        self._sflags.zero_()
+        self._gflags = [torch.zeros(_MAX_CHUNKS, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._g_next = 0
+        self._epoch = 0
+        torch.cuda.synchronize(self.device)
+        heap.barrier()
+
+    # -- buffers --------------------------------------------------------------------------------
+    def gather_buffer(self, width: int) -> tuple[int, torch.Tensor, torch.Tensor]:
+        """Next gather buffer: (slot, full [rows, width] view, this rank's [rows/world, width] rows)."""
+        native.require(width <= self.width, "tensor parallel: activation wider than the workspace")
+        slot = self._g_next
+        self._g_next ^= 1
+        full = self._g[slot][: self.rows * width].view(self.rows, width)
+        own = full[self.rank * self.rows_per_rank:(self.rank + 1) * self.rows_per_rank]
+        return slot, full, own
+
+    def _next_epoch(self) -> int:
+        self._epoch += 1
+        return self._epoch
+
+    # -- fused kernels ----------------------------------------------------------------------------
+    def ag_gemm(self, slot: int, width: int, other: torch.Tensor, *, gathered: str = "A", a_mn: bool = False,
+                b_mn: bool = False, out: torch.Tensor | None = None, accumulate: bool = False,
+                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """GEMM whose operand ``gathered`` is gather buffer ``slot`` ([rows, width], token-sharded over ranks).
+
+        gathered == "A": ``C = G other^T`` (``a_mn`` False: G is [M, K]; True: G is [K, M] and K is the token axis).
+        gathered == "B": ``C = op(other) G`` with ``b_mn`` True (G is [K, N], K the token axis)."""
+        full = self._g[slot][: self.rows * width].view(self.rows, width)
+        if gathered == "A":
+            a, b = full, other
+        else:
+            a, b = other, full
+        M = a.shape[1] if a_mn else a.shape[0]
+        K = a.shape[0] if a_mn else a.shape[1]
+        N = b.shape[1] if b_mn else b.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=self.device)
+            accumulate = False
+        epi = 0 if out.dtype == torch.bfloat16 else (1 if accumulate else 2)
+        self.heap.barrier()
+        bases = [self.heap.peer_ptr(self._g[slot], r) for r in range(self.world)]
+        err = native.lib().tplr_gemm2_gather(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn), int(b_mn), epi, 1 if gathered == "A" else 2, self.world, self.rank, self.rows_per_rank,
+            native.ptr_array(bases), self._gflags[slot].data_ptr(), ctypes.c_uint(self._next_epoch()),
+            self.n_comm_pairs, OF.status_word(self.device).data_ptr(), native.stream_ptr())
+        native.check(err, "tplr_gemm2_gather")
+        return out
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """``out = reduce_scatter_rows(a op(b))``: a is [rows, K_local]; returns this rank's [rows/world, N] rows."""
+        M, K = a.shape
+        N = b.shape[1] if b_mn else b.shape[0]
+        native.require(M == self.rows and N <= self.width, "gemm_rs: shape outside the workspace")
+        if out is None:
+            out = torch.empty((self.rows_per_rank, N), dtype=torch.bfloat16, device=self.device)
+        stage = self._s[: M * N].view(M, N)
+        self.heap.barrier()
+        stages = [self.heap.peer_ptr(self._s, r) for r in range(self.world)]
+        flags = [self.heap.peer_ptr(self._sflags, r) for r in range(self.world)]
+        err = native.lib().tplr_gemm2_scatter(
+            a.data_ptr(), b.data_ptr(), stage.data_ptr(), M, N, K, a.stride(0), b.stride(0), stage.stride(0),
+            0, int(b_mn), self.world, self.rank, self.rows_per_rank, native.ptr_array(stages),
+            native.ptr_array(flags), out.data_ptr(), out.stride(0), ctypes.c_uint(self._next_epoch()),
+            self.n_comm_pairs, OF.status_word(self.device).data_ptr(), native.stream_ptr())
+        native.check(err, "tplr_gemm2_scatter")
+        return out
+
+    def check(self) -> None:
+        """Host sync; raises if a bounded wait expired in a fused kernel or a barrier."""
+        self.heap.check()
+        st = OF.status_word(self.device)
+        v = int(st.item())
+        if v:
+            st.zero_()
+            raise TimeoutError(f"tensor-parallel kernel gave up waiting for a peer (status {v:#x})")
+
+
+# --------------------------------------------------------------------------------------------- #
+# autograd pairs
+# --------------------------------------------------------------------------------------------- #
+class _ColumnParallel(torch.autograd.Function):
+    """y[T, N/w] = all_gather(x)[T, K] W^T; backward reduce-scatters dx and re-gathers x for dW."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, tp: TensorParallel, main_grad):
+        K = x_shard.shape[-1]
+        slot, _, own = tp.gather_buffer(K)
+        own.copy_(x_shard.reshape(-1, K))
+        y = tp.ag_gemm(slot, K, w)
+        ctx.save_for_backward(x_shard, w)
+        ctx.tp, ctx.main_grad = tp, main_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_shard, w = ctx.saved_tensors
+        tp: TensorParallel = ctx.tp
+        K = x_shard.shape[-1]
+        dy = dy.contiguous()
+        dw = None
+        if ctx.needs_input_grad[1] or ctx.main_grad is not None:
+            slot, _, own = tp.gather_buffer(K)
+            own.copy_(x_shard.reshape(-1, K))
+            if ctx.main_grad is not None:      # dW += dy^T X, accumulated in fp32 by the GEMM epilogue
+                tp.ag_gemm(slot, K, dy, gathered="B", a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+            else:
+                dw = tp.ag_gemm(slot, K, dy, gathered="B", a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = tp.gemm_rs(dy, w, b_mn=True).view_as(x_shard)
+        return dx, dw, None, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """y[T/w, N] = reduce_scatter(x[T, K/w] W^T); backward gathers dy once for dx and dW."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp: TensorParallel, main_grad):
+        ctx.save_for_backward(x, w)
+        ctx.tp, ctx.main_grad = tp, main_grad
+        return tp.gemm_rs(x.reshape(-1, x.shape[-1]), w)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        tp: TensorParallel = ctx.tp
+        N = dy_shard.shape[-1]
+        slot, full, own = tp.gather_buffer(N)
+        own.copy_(dy_shard.reshape(-1, N))
+        # dx = all_gather(dy) W : the gather lands dy in `full`, which the weight gradient then reads locally
+        dx = tp.ag_gemm(slot, N, w, b_mn=True).view_as(x)
+        dw = None
+        x2 = x.reshape(-1, x.shape[-1])
+        if ctx.main_grad is not None:
+            OF.gemm(full, x2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
+        elif ctx.needs_input_grad[1]:
+            dw = OF.gemm(full, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+        return dx, dw, None, None
+
+
+def column_parallel_linear(x_shard: torch.Tensor, w_local: torch.Tensor, tp: TensorParallel,
+                           main_grad: torch.Tensor | None = None) -> torch.Tensor:
+    """``x_shard`` [T/world, K] token shard, ``w_local`` [N/world, K]; returns [T, N/world]."""
+    return _ColumnParallel.apply(x_shard, w_local, tp, main_grad)
+
+
+def row_parallel_linear(x: torch.Tensor, w_local: torch.Tensor, tp: TensorParallel,
+                        main_grad: torch.Tensor | None = None) -> torch.Tensor:
+    """``x`` [T, K/world], ``w_local`` [N, K/world]; returns the token shard [T/world, N] of the summed product."""
+    return _RowParallel.apply(x, w_local, tp, main_grad)

@@ -17,10 +17,10 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, extra_env=None):
+def _run(nproc, extra_env=None, worker="_multi_worker.py"):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29731", os.path.join(HERE, "_multi_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", "29731", os.path.join(HERE, worker)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
     assert r.returncode == 0 and lines, r.stdout[-3000:] + r.stderr[-3000:]
@@ -37,3 +37,13 @@ def test_two_rank_runtime_and_window():
         assert r["moved"] > 1e-4, r
         assert r["master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
         assert r["compute_max_diff"] < 2e-2 * max(r["scale"], 1.0), r
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tensor_parallel_linears():
+    """all-gather->GEMM and GEMM->reduce-scatter kernels, forward and backward, against an fp32 reference."""
+    res = _run(min(torch.cuda.device_count(), 4) // 2 * 2, worker="_tp_worker.py")
+    for r in res:
+        assert r["status"] == 0, r
+        for k in ("h", "y", "dx", "dw1", "dw2"):
+            assert r[k] < 2e-2, (k, r)

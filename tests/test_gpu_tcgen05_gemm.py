@@ -9,6 +9,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=["tcgen05", "tcgen05_2sm"], autouse=True)
+def backend(request):
+    """Every test runs on the one-CTA-per-tile kernel and on the CTA-pair (cta_group::2) kernel."""
+    prev = OF.gemm_backend()
+    OF.set_gemm_backend(request.param)
+    yield request.param
+    OF.set_gemm_backend(prev)
+
+
 def _check(M, N, K, a_mn, b_mn, epi):
     torch.manual_seed(M + N + K)
     A = torch.randn((K, M) if a_mn else (M, K), device=DEV).to(torch.bfloat16)
@@ -41,7 +50,7 @@ def test_gemm_layouts(a_mn, b_mn, epi):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 256, 2048), (2048, 2048, 2048), (1000, 776, 136),
-                                   (4096, 32000, 512), (130, 264, 72)])
+                                   (4096, 32000, 512), (130, 264, 72), (8, 8, 8), (257, 513, 4104)])
 def test_gemm_shapes(M, N, K):
     _check(M, N, K, False, False, "bf16")
 
