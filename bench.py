@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
 
 
@@ -166,11 +168,15 @@ def run_ours(a):
         l0 = native.launch_count
         t0w = time.perf_counter()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if a.profiler_range:
+            torch.cuda.profiler.start()
         e0.record()
         for w in range(steps):
             window(e2e, warmup + w)
         e1.record()
         torch.cuda.synchronize()
+        if a.profiler_range:
+            torch.cuda.profiler.stop()
         if world > 1:
             dist.barrier()
         wall = time.perf_counter() - t0w

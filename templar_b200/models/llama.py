@@ -163,6 +163,17 @@ class TransformerBlock(nn.Module):
         h = x + self.attention(self.attention_norm(x), cos, sin)
         return h + self.feed_forward(self.ffn_norm(h))
 
+    def forward_fused(self, res, delta, cos, sin):
+        """Same block on a split residual stream: the hidden state is ``res + delta`` and the sum is
+        formed inside the norm kernels (``delta`` None: ``res`` alone).  Returns the next ``(res, delta)``."""
+        if delta is None:
+            y = self.attention_norm(res)
+        else:
+            res, y = OF.add_rmsnorm(res, delta, self.attention_norm.weight, self.attention_norm.eps)
+        a = self.attention(y, cos, sin)
+        res, y = OF.add_rmsnorm(res, a, self.ffn_norm.weight, self.ffn_norm.eps)
+        return res, self.feed_forward(y)
+
     def init_weights(self, generator=None):
         for norm in (self.attention_norm, self.ffn_norm):
             nn.init.ones_(norm.weight)
@@ -222,13 +233,16 @@ class LlamaModel(nn.Module):
     def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
         cos, sin = self._rope(tokens.device)
         h = OF.embedding(tokens, self.tok_embeddings.weight)
+        delta = None
         for layer in self.layers.values():
             if self.activation_checkpointing and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
-                h = checkpoint(layer, h, cos, sin, use_reentrant=False)
+                h, delta = checkpoint(layer.forward_fused, h, delta, cos, sin, use_reentrant=False)
             else:
-                h = layer(h, cos, sin)
-        return self.norm(h)
+                h, delta = layer.forward_fused(h, delta, cos, sin)
+        if delta is None:
+            return self.norm(h)
+        return OF.add_rmsnorm(h, delta, self.norm.weight, self.norm.eps)[1]
 
     def forward(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
         return self.output(self.hidden_states(tokens))

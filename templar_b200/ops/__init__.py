@@ -1,8 +1,8 @@
 """Kernels of the framework: ``functional`` (autograd ops with a CPU path), ``native``
 (ctypes bindings of the sm_100a library) and ``build`` (in-tree nvcc build)."""
 
-from .functional import (attention, cross_entropy, embedding, gemm, gemm_backend, linear, rmsnorm, rope,
+from .functional import (add_rmsnorm, attention, cross_entropy, embedding, gemm, gemm_backend, linear, rmsnorm, rope,
                          rope_tables, set_gemm_backend, swiglu)
 
-__all__ = ["attention", "cross_entropy", "embedding", "gemm", "gemm_backend", "linear", "rmsnorm", "rope",
+__all__ = ["add_rmsnorm", "attention", "cross_entropy", "embedding", "gemm", "gemm_backend", "linear", "rmsnorm", "rope",
            "rope_tables", "set_gemm_backend", "swiglu"]

@@ -159,6 +159,175 @@ TPLR_API int tplr_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
 }
 
 // ------------------------------------------------------------------------------------- //
+// Residual add fused with RMSNorm, one warp per row (D <= 2048): no block barrier, 8 rows in
+// flight per CTA.
+//   forward   h = res + delta (delta may be null: h = res);  y = h * rstd(h) * w;  h written when delta != null
+//   backward  dx = dres + rstd * (g - xhat * mean(g * xhat))  (dres may be null);  dw += sum_rows dy * xhat
+// The backward's dx is the gradient of both `res` and `delta`, so the residual stream needs no
+// separate add kernel in either direction (the reference leaves `h + attn(norm(h))` to eager adds:
+// torchtitan models/llama3/model/model.py:339-341).
+// ------------------------------------------------------------------------------------- //
+template <int VPL>
+__global__ void __launch_bounds__(256) add_rmsnorm_fwd_warp_kernel(const bf16* __restrict__ res, const bf16* __restrict__ delta,
+                                                                   const bf16* __restrict__ w, bf16* __restrict__ h_out,
+                                                                   bf16* __restrict__ y, float* __restrict__ rstd,
+                                                                   long long T, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int nv = D / 8;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(res + row * D);
+  const bf16x8* dr = delta ? reinterpret_cast<const bf16x8*>(delta + row * D) : nullptr;
+  bf16x8 hv[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + 32 * v;
+    if (i < nv) {
+      float a[8]; unpack8(xr[i], a);
+      if (dr) {
+        float b[8]; unpack8(dr[i], b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += b[e];
+        hv[v] = pack8(a);                 // the norm sees the bf16-rounded sum, as the stored residual does
+        unpack8(hv[v], a);
+        reinterpret_cast<bf16x8*>(h_out + row * D)[i] = hv[v];
+      } else {
+        hv[v] = xr[i];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(a[e], a[e], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)D + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + 32 * v;
+    if (i < nv) {
+      float a[8], wv[8], o[8];
+      unpack8(hv[v], a); unpack8(reinterpret_cast<const bf16x8*>(w)[i], wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = a[e] * r * wv[e];
+      reinterpret_cast<bf16x8*>(y + row * D)[i] = pack8(o);
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) add_rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                                   const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                                                   float* __restrict__ dw, long long T, int D) {
+  __shared__ float s_dw[8][32 * 8 + 1];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nv = D / 8;
+  float dwv[VPL][8];
+  bf16x8 wp[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const int i = lane + 32 * v;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwv[v][e] = 0.f;
+    if (i < nv) wp[v] = reinterpret_cast<const bf16x8*>(w)[i];
+  }
+  for (long long row = (long long)blockIdx.x * 8 + wid; row < T; row += (long long)gridDim.x * 8) {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    const bf16x8* gr = reinterpret_cast<const bf16x8*>(dy + row * D);
+    const float r = rstd[row];
+    bf16x8 xp[VPL], gp[VPL];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int i = lane + 32 * v;
+      if (i < nv) { xp[v] = xr[i]; gp[v] = gr[i]; }
+    }
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int i = lane + 32 * v;
+      if (i < nv) {
+        float xv[8], dv[8], wv[8];
+        unpack8(xp[v], xv); unpack8(gp[v], dv); unpack8(wp[v], wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = xv[e] * r;
+          dwv[v][e] = fmaf(dv[e], xh, dwv[v][e]);
+          dot = fmaf(dv[e] * wv[e], xh, dot);
+        }
+      }
+    }
+    dot = warp_sum(dot) / (float)D;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const int i = lane + 32 * v;
+      if (i < nv) {
+        float xv[8], dv[8], wv[8], o[8];
+        unpack8(xp[v], xv); unpack8(gp[v], dv); unpack8(wp[v], wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = r * (dv[e] * wv[e] - xv[e] * r * dot);
+        if (dres) {
+          float a[8]; unpack8(reinterpret_cast<const bf16x8*>(dres + row * D)[i], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
+        reinterpret_cast<bf16x8*>(dx + row * D)[i] = pack8(o);
+      }
+    }
+  }
+  if (!dw) return;
+  // reduce the eight warps' partial dw through shared memory, one slab of 32 vectors at a time
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_dw[wid][lane * 8 + e] = dwv[v][e];
+    __syncthreads();
+    const int col = threadIdx.x;                     // 256 columns of this slab
+    const int i = (col >> 3) + 32 * v;
+    if (i < nv) {
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc += s_dw[k][col];
+      atomicAdd(dw + (long long)i * 8 + (col & 7), acc);
+    }
+  }
+}
+
+// T rows of D (multiple of 8, <= 2048) bf16.  delta may be null (plain RMSNorm, h_out unused).
+TPLR_API int tplr_add_rmsnorm_fwd(const void* res, const void* delta, const void* w, void* h_out, void* y, float* rstd,
+                                  long long T, int D, float eps, void* stream) {
+  TPLR_ENTER();
+  if (D % 8 || D > 2048) return (int)cudaErrorInvalidValue;
+  if (T <= 0) return 0;
+  const int vpl = (D / 8 + 31) / 32;
+  const unsigned grid = (unsigned)((T + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+#define TPLR_ARN_FWD(V) add_rmsnorm_fwd_warp_kernel<V><<<grid, 256, 0, st>>>((const bf16*)res, (const bf16*)delta, \
+      (const bf16*)w, (bf16*)h_out, (bf16*)y, rstd, T, D, eps)
+  if (vpl <= 1) TPLR_ARN_FWD(1); else if (vpl <= 2) TPLR_ARN_FWD(2); else if (vpl <= 4) TPLR_ARN_FWD(4); else TPLR_ARN_FWD(8);
+#undef TPLR_ARN_FWD
+  return (int)cudaGetLastError();
+}
+
+// dres may be null; dw (fp32, D) is accumulated into with atomics and may be null.
+TPLR_API int tplr_add_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                  void* dx, float* dw, long long T, int D, void* stream) {
+  TPLR_ENTER();
+  if (D % 8 || D > 2048) return (int)cudaErrorInvalidValue;
+  if (T <= 0) return 0;
+  const int vpl = (D / 8 + 31) / 32;
+  long long grid = (long long)tplr_sm_count() * (vpl > 4 ? 1 : 2);   // resident CTAs: 240 registers at 8 vectors per lane
+  if (grid > (T + 7) / 8) grid = (T + 7) / 8;
+  cudaStream_t st = (cudaStream_t)stream;
+#define TPLR_ARN_BWD(V) add_rmsnorm_bwd_warp_kernel<V><<<(unsigned)grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, \
+      (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, dw, T, D)
+  if (vpl <= 1) TPLR_ARN_BWD(1); else if (vpl <= 2) TPLR_ARN_BWD(2); else if (vpl <= 4) TPLR_ARN_BWD(4); else TPLR_ARN_BWD(8);
+#undef TPLR_ARN_BWD
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
 // RoPE on interleaved pairs, in place on a packed [tokens, row_stride] buffer whose first
 // n_heads*Dh columns are rotary heads (q heads followed by k heads). inverse = backward.
 // ------------------------------------------------------------------------------------- //

@@ -36,14 +36,14 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_RANKS = 8;
 constexpr int CHUNK_ROWS = 128;                    // gather / scatter flag granularity (rows)
-constexpr int RS_ROWS = 16;                        // rows per reducer step
+constexpr int RS_ROWS_MIN = 16;                    // rows per reducer step at 8 ranks (more with fewer ranks)
 constexpr int RS_STAGES = 3, RS_STAGE_BYTES = 2 * STAGE_BYTES;   // 3 x 64 KB
 
 struct Gemm2Params {
   CUtensorMap tmA, tmB;
   CUtensorMap tmC;                   // output: box 64 x 32 bf16 or 32 x 32 fp32, 128-byte swizzle
   int c_tma;                         // 1: epilogue through TMA, 0: direct stores (unaligned C)
-  CUtensorMap tmPart[MAX_RANKS];     // scatter: every rank's staging buffer, box 256 x RS_ROWS, no swizzle
+  CUtensorMap tmPart[MAX_RANKS];     // scatter: every rank's staging buffer, box 256 x rs_rows, no swizzle
   void* C;
   long long ldc;
   int M, N, K;
@@ -63,6 +63,7 @@ struct Gemm2Params {
   unsigned int* ag_flags;            // one per CHUNK_ROWS rows of the full buffer (local memory)
   // scatter
   int rs_on;
+  int rs_rows;                       // rows per reducer step: world * rs_rows * 512 B fill one 64 KB stage
   int rs_rows_per_rank;
   unsigned int* rs_flag_dst[MAX_RANKS];   // rank o's flag array [world][chunks_per_rank][tiles_n], as mapped here
   unsigned int* rs_flags;            // this rank's flag array
@@ -139,6 +140,24 @@ __device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int
   unsigned long long t0 = 0;
   for (uint32_t i = 0;; ++i) {
     const unsigned int v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v == want) return true;
+    if ((i & 7u) == 7u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = gtimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// Bounded wait with relaxed polls (the flag lives in local memory); the caller issues the acquire fence.
+__device__ __forceinline__ bool flag_wait_relaxed(const unsigned int* flag, unsigned int want, volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    unsigned int v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v == want) return true;
     if ((i & 7u) == 7u) {
       if (*abort_flag) return false;
@@ -485,8 +504,8 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
     // ----------------------------- comm CTA: reduce the rows this rank owns -------------
     const int ci = (pair - p.n_compute_pairs) * 2 + (int)cr, n_comm = (n_pairs - p.n_compute_pairs) * 2;
     const int chunks_per_rank = p.rs_rows_per_rank / CHUNK_ROWS;
-    constexpr int SUBS = CHUNK_ROWS / RS_ROWS;
-    constexpr uint32_t SRC_BYTES = TILE_N * RS_ROWS * 2;   // 8 KB per source per step
+    const int RS_ROWS = p.rs_rows, SUBS = CHUNK_ROWS / RS_ROWS;
+    const uint32_t SRC_BYTES = (uint32_t)(TILE_N * RS_ROWS * 2);   // bytes per source per step
     if (warp == 0) {
       if (lane == 0) {
         uint32_t it = 0;
@@ -500,8 +519,9 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
           if ((cnt++) % n_comm != ci) continue;
           const int cl = chunk - p.rank * chunks_per_rank;
           for (int s = 0; s < p.world && ok; ++s)
-            ok = flag_wait<true>(p.rs_flags + ((long long)s * chunks_per_rank + cl) * tiles_n + tn, p.epoch, abort_flag);
+            ok = flag_wait_relaxed(p.rs_flags + ((long long)s * chunks_per_rank + cl) * tiles_n + tn, p.epoch, abort_flag);
           if (!ok) break;
+          asm volatile("fence.acq_rel.sys;" ::: "memory");   // one acquire for all the flags of the unit
           fence_proxy_async();
           for (int sub = 0; sub < SUBS; ++sub, ++it) {
             const int st = it % RS_STAGES;
@@ -539,7 +559,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint8_t* sb = smem + st * RS_STAGE_BYTES;
-#pragma unroll
+#pragma unroll 4
           for (int j = 0; j < (RS_ROWS * TILE_N / 8) / 128; ++j) {
             const int v = tid + 128 * j, r = v >> 5, cv = v & 31;
             float acc[8];
@@ -707,8 +727,10 @@ TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, void* stage, int M
   if (int r = fill_common(p, A, B, stage, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, status)) return r;
   p.world = world; p.rank = rank; p.epoch = epoch;
   p.rs_on = 1; p.rs_rows_per_rank = rows_per_rank;
+  p.rs_rows = RS_ROWS_MIN;
+  while (p.rs_rows * 2 * world * TILE_N * 2 <= RS_STAGE_BYTES && p.rs_rows * 2 <= CHUNK_ROWS) p.rs_rows *= 2;
   for (int r = 0; r < world; ++r) {
-    if (!make_map(&p.tmPart[r], peer_stage[r], N, M, ldc, TILE_N, RS_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return -109;
+    if (!make_map(&p.tmPart[r], peer_stage[r], N, M, ldc, TILE_N, p.rs_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return -109;
     p.rs_flag_dst[r] = static_cast<unsigned int*>(peer_flags[r]);
   }
   p.rs_flags = static_cast<unsigned int*>(peer_flags[rank]);

@@ -25,7 +25,7 @@ from . import native
 
 # "tcgen05": own GEMM kernel, one CTA per tile; "tcgen05_2sm": own GEMM kernel on CTA pairs
 # (cta_group::2); "cublas": torch.matmul (library).  Switched by templar_b200.ops.set_gemm_backend().
-_GEMM_BACKEND = "tcgen05"
+_GEMM_BACKEND = "tcgen05_2sm"
 _status_words: dict[int, torch.Tensor] = {}
 
 
@@ -196,6 +196,70 @@ def rmsnorm(x, w, eps: float = 1e-5, main_grad=None):
     if main_grad is None:
         main_grad = getattr(w, "main_grad", None)
     return _RMSNorm.apply(x, w, eps, main_grad)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """(h, y) = (res + delta, rmsnorm(res + delta) * w) in one kernel; the backward folds the
+    residual gradient into the norm's input gradient, which serves ``res`` and ``delta`` alike."""
+
+    @staticmethod
+    def forward(ctx, res, delta, w, eps, main_grad):
+        ctx.eps, ctx.main_grad = eps, main_grad
+        D = res.shape[-1]
+        if _native_ok(res, delta, w) and D % 8 == 0 and D <= 2048 and res.is_contiguous() and delta.is_contiguous():
+            T = res.numel() // D
+            h = torch.empty_like(res)
+            y = torch.empty_like(res)
+            rstd = torch.empty(T, dtype=torch.float32, device=res.device)
+            native.check(native.lib().tplr_add_rmsnorm_fwd(res.data_ptr(), delta.data_ptr(), w.data_ptr(), h.data_ptr(),
+                                                           y.data_ptr(), rstd.data_ptr(), T, D, eps, native.stream_ptr()),
+                         "add_rmsnorm_fwd")
+            ctx.native = True
+        else:
+            h = res + delta
+            hf = h.float()
+            rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
+            y = (hf * rstd * w.float()).to(res.dtype)
+            ctx.native = False
+        ctx.save_for_backward(h, w, rstd)
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        h, w, rstd = ctx.saved_tensors
+        mg = ctx.main_grad
+        D = h.shape[-1]
+        if ctx.native:
+            T = h.numel() // D
+            dyc = dy.contiguous()
+            dhc = dh.contiguous() if dh is not None else None
+            dx = torch.empty_like(h)
+            dw_buf = mg if mg is not None else torch.zeros(D, dtype=torch.float32, device=h.device)
+            native.check(native.lib().tplr_add_rmsnorm_bwd(dyc.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                                           dhc.data_ptr() if dhc is not None else None, dx.data_ptr(),
+                                                           dw_buf.data_ptr(), T, D, native.stream_ptr()), "add_rmsnorm_bwd")
+            return dx, dx, (None if mg is not None else dw_buf.to(w.dtype)), None, None
+        hf, g = h.float(), dy.float()
+        xh = hf * rstd
+        gw = g * w.float()
+        dx = rstd * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+        if dh is not None:
+            dx = dx + dh.float()
+        dw = (g * xh).reshape(-1, D).sum(0)
+        if mg is not None:
+            mg.add_(dw.to(mg.dtype))
+            dw = None
+        else:
+            dw = dw.to(w.dtype)
+        dx = dx.to(h.dtype)
+        return dx, dx, dw, None, None
+
+
+def add_rmsnorm(res, delta, w, eps: float = 1e-5, main_grad=None):
+    """Returns ``(res + delta, rmsnorm(res + delta) * w)``."""
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    return _AddRMSNorm.apply(res, delta, w, eps, main_grad)
 
 
 # --------------------------------------------------------------------------- #

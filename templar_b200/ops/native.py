@@ -61,6 +61,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_aggregate_apply": [vp, i, i, vp, i, vp, vp, i, vp, i, i, vp, vp, vp, vp, vp, vp, f, f, i, i, i, vp, vp],
         "tplr_rmsnorm_fwd": [vp, vp, vp, vp, ll, i, f, vp],
         "tplr_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, ll, i, vp],
+        "tplr_add_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, ll, i, f, vp],
+        "tplr_add_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, ll, i, vp],
         "tplr_rope": [vp, vp, vp, ll, i, i, i, ll, i, vp],
         "tplr_swiglu_fwd": [vp, vp, ll, i, vp],
         "tplr_swiglu_bwd": [vp, vp, vp, ll, i, vp],

@@ -33,7 +33,7 @@ class TensorParallel:
     ``rows`` is the number of tokens of the full (gathered) activation, ``width`` the widest
     activation that is gathered or reduce-scattered (the model dimension)."""
 
-    def __init__(self, heap: SymmetricHeap, rows: int, width: int, n_comm_pairs: int = 8):
+    def __init__(self, heap: SymmetricHeap, rows: int, width: int, n_comm_pairs: int | None = None):
         self.heap, self.rank, self.world = heap, heap.rank, heap.world_size
         native.require(rows % (128 * self.world) == 0, "tensor parallel: rows must be a multiple of 128 * world")
         native.require(rows // 128 <= _MAX_CHUNKS, "tensor parallel: too many rows")
@@ -66,6 +66,18 @@ class TensorParallel:
         self._epoch += 1
         return self._epoch
 
+    def _comm_pairs(self, flops: float, link_bytes: float) -> int:
+        """CTA pairs set aside for the collective: enough to move ``link_bytes`` within the GEMM's
+        own time (about 50 GB/s per CTA with its shared memory full of loads in flight), no more
+        than what saturates one NVLink direction."""
+        if self.n_comm_pairs is not None:
+            return self.n_comm_pairs
+        if self.world == 1:
+            return 1
+        t_gemm = flops / 1.4e15
+        need_gbs = min(link_bytes / max(t_gemm, 1e-6) / 1e9, 800.0)
+        return max(1, min(8, -(-int(need_gbs / 50.0 + 0.999) // 2)))
+
     # -- fused kernels ----------------------------------------------------------------------------
     def ag_gemm(self, slot: int, width: int, other: torch.Tensor, *, gathered: str = "A", a_mn: bool = False,
                 b_mn: bool = False, out: torch.Tensor | None = None, accumulate: bool = False,
@@ -92,7 +104,8 @@ class TensorParallel:
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             int(a_mn), int(b_mn), epi, 1 if gathered == "A" else 2, self.world, self.rank, self.rows_per_rank,
             native.ptr_array(bases), self._gflags[slot].data_ptr(), ctypes.c_uint(self._next_epoch()),
-            self.n_comm_pairs, OF.status_word(self.device).data_ptr(), native.stream_ptr())
+            self._comm_pairs(2.0 * M * N * K, (self.world - 1) * self.rows_per_rank * width * 2),
+            OF.status_word(self.device).data_ptr(), native.stream_ptr())
         native.check(err, "tplr_gemm2_gather")
         return out
 
@@ -112,7 +125,8 @@ class TensorParallel:
             a.data_ptr(), b.data_ptr(), stage.data_ptr(), M, N, K, a.stride(0), b.stride(0), stage.stride(0),
             0, int(b_mn), self.world, self.rank, self.rows_per_rank, native.ptr_array(stages),
             native.ptr_array(flags), out.data_ptr(), out.stride(0), ctypes.c_uint(self._next_epoch()),
-            self.n_comm_pairs, OF.status_word(self.device).data_ptr(), native.stream_ptr())
+            self._comm_pairs(2.0 * M * N * K, (self.world - 1) * self.rows_per_rank * N * 2),
+            OF.status_word(self.device).data_ptr(), native.stream_ptr())
         native.check(err, "tplr_gemm2_scatter")
         return out
 

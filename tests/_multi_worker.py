@@ -57,7 +57,7 @@ def main():
     heap.check()
 
     # 3. sharded window == single-rank window on the same global batch
-    OF.set_gemm_backend(os.environ.get("TPLR_TEST_GEMM", "tcgen05"))
+    OF.set_gemm_backend(os.environ.get("TPLR_TEST_GEMM", "tcgen05_2sm"))
     args = ModelArgs(dim=256, n_layers=2, n_heads=4, vocab_size=1024, intermediate_size=512, max_seq_len=128)
     cfg = EngineConfig(topk=8, max_peers=4, inner_lr=1e-3, outer_lr=0.5)
     g = torch.Generator().manual_seed(7)

@@ -141,6 +141,27 @@ def test_rmsnorm_fwd_bwd():
         assert torch.allclose(w.grad.float(), wf.grad, atol=0.15, rtol=3e-2)
 
 
+def test_add_rmsnorm_fwd_bwd():
+    """Residual add fused with RMSNorm (warp-per-row kernels) against fp32 autograd of the same math."""
+    torch.manual_seed(1)
+    for D, T in ((256, 37), (1024, 300), (2048, 2051), (776, 19)):
+        res = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        delta = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+        h, y = OF.add_rmsnorm(res, delta, w, 1e-5)
+        dh, dy = torch.randn_like(h), torch.randn_like(y)
+        torch.autograd.backward([h, y], [dh, dy])
+        rf, df, wf = (t.detach().float().requires_grad_() for t in (res, delta, w))
+        hr = (rf + df).to(torch.bfloat16).float() + (rf + df - (rf + df).detach())   # bf16-rounded sum, identity gradient
+        yr = F.rms_norm(hr, (D,), wf, 1e-5)
+        torch.autograd.backward([hr, yr], [dh.float(), dy.float()])
+        assert torch.equal(h, (res.detach().float() + delta.detach().float()).to(torch.bfloat16))
+        assert torch.allclose(y.float(), yr, atol=3e-2, rtol=2e-2)
+        assert torch.allclose(res.grad.float(), rf.grad, atol=4e-2, rtol=2e-2)
+        assert torch.equal(res.grad, delta.grad)
+        assert torch.allclose(w.grad.float(), wf.grad, atol=0.05 * T ** 0.5, rtol=3e-2)
+
+
 def test_rope_matches_complex_multiply():
     B, S, H, KV, Dh = 2, 64, 4, 2, 128
     C_ = (H + 2 * KV) * Dh
@@ -229,10 +250,13 @@ def test_adamw_and_sumsq_match_torch():
         assert float(gk.abs().max()) == 0.0
 
 
-def test_model_step_native_vs_torch_reference():
-    """One forward/backward of a small model: kernels (bf16) against the same model in fp32 PyTorch."""
+@pytest.mark.parametrize("backend", ["tcgen05_2sm", "tcgen05"])
+def test_model_step_native_vs_torch_reference(backend):
+    """One forward/backward of a small model: kernels (bf16) against the same model in fp32 PyTorch
+    (fp32 operands never reach the own GEMM, so the reference side is torch.matmul)."""
     args = ModelArgs(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, intermediate_size=512, max_seq_len=128)
-    OF.set_gemm_backend("cublas")
+    prev = OF.gemm_backend()
+    OF.set_gemm_backend(backend)
     try:
         ref = build_model(args, device=DEV, seed=3)           # fp32, autograd weight grads
         with torch.no_grad():
@@ -251,4 +275,4 @@ def test_model_step_native_vs_torch_reference():
             rel = (g - p.grad).norm() / (p.grad.norm() + 1e-12)
             assert float(rel) < 0.08, (n, float(rel))
     finally:
-        OF.set_gemm_backend("tcgen05")
+        OF.set_gemm_backend(prev)
