@@ -124,12 +124,7 @@ class Attention(nn.Module):
         else:
             qkv = OF.linear(x, torch.cat((self.wq.weight, self.wk.weight, self.wv.weight), dim=0))
         qkv = OF.rope(qkv, cos, sin, self.n_heads + self.n_kv, self.hd)
-        nq, nk = self.n_heads * self.hd, self.n_kv * self.hd
-        q = qkv[..., :nq].view(B, S, self.n_heads, self.hd)
-        k = qkv[..., nq:nq + nk].view(B, S, self.n_kv, self.hd)
-        v = qkv[..., nq + nk:].view(B, S, self.n_kv, self.hd)
-        o = OF.attention(q, k, v).reshape(B, S, nq)
-        return self.wo(o)
+        return self.wo(OF.attention_packed(qkv, self.n_heads, self.n_kv, self.hd))
 
 
 class FeedForward(nn.Module):

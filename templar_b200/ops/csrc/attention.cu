@@ -1,0 +1,630 @@
+// Causal flash attention on tcgen05 (sm_100a): S = Q K^T and O += P V run on the 5th-generation
+// tensor cores with the accumulators in tensor memory; the softmax reads its row of S straight
+// from TMEM (lane = query row, so row max / row sum need no shuffles), writes P back into the
+// same TMEM columns as packed bf16 and the second MMA takes P from TMEM as its A operand.
+//
+// Operands come from the packed projection output [B*S, (H + 2 KV) * 128] (q heads, k heads,
+// v heads; RoPE already applied in place), loaded by TMA with 128-byte swizzle; no copy splits
+// q, k and v.  Head dimension 128, sequence length a multiple of 128, grouped-query heads.
+//
+// CTA = one 128-row query block of one head: warp 0 TMA producer, warp 1 MMA issuer + TMEM
+// owner, warps 2-5 softmax / correction / epilogue.  256 TMEM columns and 97 KB of shared
+// memory per CTA, so two CTAs share an SM and one's softmax overlaps the other's MMAs.
+// The running maximum is only raised when it grows by more than 2^8 (any consistent reference
+// value gives the same result), which keeps the O-rescale off the common path.
+// Every mbarrier wait is bounded; on expiry TPLR_ST_WAIT_TIMEOUT is set and all roles return.
+//
+// Replaces F.scaled_dot_product_attention(is_causal=True) of the reference model
+// (torchtitan models/llama3/model/model.py:203-206, :244-262).
+#include "tcgen05.cuh"
+
+namespace {
+using namespace tplr_tc;
+
+constexpr int BQ = 128, BKV = 128, DH = 128;
+constexpr int TILE_BYTES = 128 * DH * 2;                 // 32 KB: one 128 x 128 bf16 tile
+constexpr int FWD_SMEM = 3 * TILE_BYTES + 1024;          // Q, K, V
+constexpr int FWD_THREADS = 192;
+constexpr float RESCALE_THRESHOLD = 8.0f;                // log2 units
+
+struct AttnFwdParams {
+  CUtensorMap tmQKV;      // [B*S, C] bf16, box 64 x 128, 128-byte swizzle
+  CUtensorMap tmO;        // [B*S, H*128] bf16, box 64 x 32, 128-byte swizzle
+  float* lse;             // [B, H, S] natural-log sum-exp of the scaled scores
+  int B, S, H, KV;
+  float scale_log2;       // softmax scale * log2(e)
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void umma_ts_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+
+// instruction descriptor: fp32 accumulate, bf16 A and B, M = 128, N = 128; b_mn selects an N-contiguous B
+__device__ __forceinline__ uint32_t idesc_128x128(bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_q, bar_k_full, bar_k_empty, bar_v_full, bar_v_empty, bar_s_full, bar_p_full, bar_o_full;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nQ = p.S / BQ;
+  // heavy (late) query blocks first
+  const int hb = p.H * p.B;
+  const int qi = nQ - 1 - (int)(blockIdx.x / hb);
+  const int h = (int)(blockIdx.x % hb) % p.H, b = (int)(blockIdx.x % hb) / p.H;
+  const int g = h / (p.H / p.KV);
+  const int nb = qi + 1;                                   // causal: kv blocks 0..qi
+  const int row0 = b * p.S + qi * BQ;
+  const int qcol = h * DH, kcol = (p.H + g) * DH, vcol = (p.H + p.KV + g) * DH;
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&bar_q), 1);
+    mbar_init(smem_u32(&bar_k_full), 1); mbar_init(smem_u32(&bar_k_empty), 1);
+    mbar_init(smem_u32(&bar_v_full), 1); mbar_init(smem_u32(&bar_v_empty), 1);
+    mbar_init(smem_u32(&bar_s_full), 1); mbar_init(smem_u32(&bar_p_full), 4);
+    mbar_init(smem_u32(&bar_o_full), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(&s_tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const uint32_t tS = tmem_base, tO = tmem_base + 128;     // S / P columns 0..127, O columns 128..255
+  const uint32_t sQ = smem_u32(smem), sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bar_q), TILE_BYTES);
+      tma_load_2d(sQ, &p.tmQKV, smem_u32(&bar_q), qcol, row0);
+      tma_load_2d(sQ + TILE_BYTES / 2, &p.tmQKV, smem_u32(&bar_q), qcol + 64, row0);
+      bool ok = true;
+      for (int j = 0; j < nb && ok; ++j) {
+        const uint32_t ph = j & 1;
+        const int krow = b * p.S + j * BKV;
+        if (!(ok = mbar_wait(smem_u32(&bar_k_empty), ph ^ 1, abort_flag))) break;
+        mbar_expect_tx(smem_u32(&bar_k_full), TILE_BYTES);
+        tma_load_2d(sK, &p.tmQKV, smem_u32(&bar_k_full), kcol, krow);
+        tma_load_2d(sK + TILE_BYTES / 2, &p.tmQKV, smem_u32(&bar_k_full), kcol + 64, krow);
+        if (!(ok = mbar_wait(smem_u32(&bar_v_empty), ph ^ 1, abort_flag))) break;
+        mbar_expect_tx(smem_u32(&bar_v_full), TILE_BYTES);
+        tma_load_2d(sV, &p.tmQKV, smem_u32(&bar_v_full), vcol, krow);
+        tma_load_2d(sV + TILE_BYTES / 2, &p.tmQKV, smem_u32(&bar_v_full), vcol + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_qk = idesc_128x128(false), id_pv = idesc_128x128(true);
+      bool ok = mbar_wait(smem_u32(&bar_q), 0, abort_flag);
+      for (int j = 0; j < nb && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_k_full), ph, abort_flag))) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * (TILE_BYTES / 2) + (uint32_t)(kk & 3) * 32u;
+          umma_bf16(tS, make_desc(sQ + off, 16, 1024), make_desc(sK + off, 16, 1024), id_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bar_s_full));
+        umma_commit(smem_u32(&bar_k_empty));
+        if (!(ok = mbar_wait(smem_u32(&bar_p_full), ph, abort_flag))) break;
+        if (!(ok = mbar_wait(smem_u32(&bar_v_full), ph, abort_flag))) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          umma_ts_bf16(tO, tS + 8 * kk, make_desc(sV + kk * (16 * 128), TILE_BYTES / 2, 1024), id_pv,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&bar_v_empty));
+        if (j == nb - 1) umma_commit(smem_u32(&bar_o_full));
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                        // query row inside the block = TMEM lane
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      ok = mbar_wait(smem_u32(&bar_s_full), j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const bool diag = j == qi;
+      // pass 1: row maximum of the scaled scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32 + lane_off, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float x = __uint_as_float(v[e]);
+          mx = fmaxf(mx, (diag && c * 32 + e > r) ? -INFINITY : x);
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const bool need = m_new > m_used + RESCALE_THRESHOLD;       // true for the first block (m_used = -inf)
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = need ? exp2f(m_used - m_new) : 1.f;   // 0 for the first block
+        if (need) { m_used = m_new; l *= alpha; }
+        if (j > 0) {
+          // S of block j is complete, so every earlier MMA, PV of block j-1 included, has finished with O
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO + c * 32 + lane_off, v);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+            tmem_st32(tO + c * 32 + lane_off, v);
+          }
+        }
+      }
+      // pass 2: P = exp2(S * scale - m) as packed bf16 over the first 64 columns of S
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], pk[16];
+        tmem_ld32(tS + c * 32 + lane_off, v);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float p0 = exp2f(fmaf(__uint_as_float(v[2 * e]), p.scale_log2, -m_used));
+          float p1 = exp2f(fmaf(__uint_as_float(v[2 * e + 1]), p.scale_log2, -m_used));
+          if (diag) {
+            if (c * 32 + 2 * e > r) p0 = 0.f;
+            if (c * 32 + 2 * e + 1 > r) p1 = 0.f;
+          }
+          l += p0 + p1;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        tmem_st16(tS + c * 16 + lane_off, pk);
+      }
+      tmem_wait_st();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p_full));
+    }
+    // epilogue: O / l -> bf16 -> swizzled staging (the Q tile is no longer read) -> TMA store
+    if (ok) ok = mbar_wait(smem_u32(&bar_o_full), 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tcgen05_fence_after();
+      const float inv_l = 1.f / l;
+      const uint32_t stage = sQ + (uint32_t)quad * 8192u;
+      const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tO + c * 32 + lane_off, v);
+        const uint32_t rowaddr = stage + (uint32_t)(c >> 1) * 4096u + (uint32_t)lane * 128u;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t pw[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 2 * e]) * inv_l,
+                                                      __uint_as_float(v[8 * q4 + 2 * e + 1]) * inv_l);
+            pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          const uint32_t jj = (uint32_t)((c & 1) * 4 + q4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((jj ^ sw) << 4)), "r"(pw[0]), "r"(pw[1]),
+                       "r"(pw[2]), "r"(pw[3]) : "memory");
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&p.tmO, stage, qcol, row0 + quad * 32);
+        tma_store_2d(&p.tmO, stage + 4096u, qcol + 64, row0 + quad * 32);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+      if (p.lse) p.lse[((long long)b * p.H + h) * p.S + qi * BQ + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+  }
+  if (threadIdx.x == 0 && s_abort && p.status) atomicOr(p.status, TPLR_ST_WAIT_TIMEOUT);
+}
+
+}  // namespace
+
+// qkv: packed [B*S, (H + 2*KV) * 128] bf16 (row stride ld_qkv elements); out: [B*S, H*128] bf16 (row stride ld_o);
+// lse: [B, H, S] fp32 or null.  S must be a multiple of 128 and H a multiple of KV.
+TPLR_API int tplr_attention_fwd(const void* qkv, void* out, float* lse, int B, int S, int H, int KV, long long ld_qkv,
+                                long long ld_o, float scale, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (B <= 0 || S <= 0) return 0;
+  if (S % BQ || H % KV || (ld_qkv % 8) || (ld_o % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return -201;
+  AttnFwdParams p = {};
+  if (!make_map(&p.tmQKV, qkv, (long long)(H + 2 * KV) * DH, (long long)B * S, ld_qkv, 64, 128)) return -202;
+  if (!make_map(&p.tmO, out, (long long)H * DH, (long long)B * S, ld_o, 64, 32)) return -203;
+  p.lse = lse; p.B = B; p.S = S; p.H = H; p.KV = KV;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+  if (e != cudaSuccess) return (int)e;
+  const unsigned grid = (unsigned)((S / BQ) * H * B);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------ //
+// Backward.  CTA = one 128-row key/value block of one kv head; it walks the query heads of the
+// group and the query blocks at or below the diagonal.  Per step:
+//   S = Q K^T, dP = dO V^T            (tensor cores -> TMEM)
+//   P = exp2(S*scale - lse), dS = P * (dP - delta) * scale   (softmax warps, one query row per thread;
+//                                      P and dS go to shared memory as bf16 in 128-byte-swizzled tiles)
+//   dV += P^T dO, dK += dS^T Q        (accumulated in TMEM over the whole walk)
+//   dQ_partial = dS K                 (into the S columns, then TMA reduce-add into the fp32 dQ buffer)
+// The same swizzled tile serves as a K-major operand of one MMA and an MN-major operand of another,
+// so Q, dO, P and dS are each stored once.  K and V stay resident in shared memory.
+// ------------------------------------------------------------------------------------------ //
+namespace {
+
+constexpr int BWD_SMEM = 6 * TILE_BYTES + 1024;
+constexpr int BWD_THREADS = 192;
+
+struct AttnBwdParams {
+  CUtensorMap tmQKV;    // [B*S, C] bf16, box 64 x 128
+  CUtensorMap tmDO;     // [B*S, H*128] bf16, box 64 x 128
+  CUtensorMap tmDQ;     // [B*S, H*128] fp32, box 32 x 32 (reduce-add target)
+  CUtensorMap tmDQKV;   // [B*S, C] bf16, box 64 x 32 (dK and dV stores)
+  const float* lse;
+  const float* delta;
+  int B, S, H, KV;
+  float scale, scale_log2;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint32_t idesc_bwd(bool a_mn, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+// descriptors of a 128 x 128 bf16 tile stored as two [128 rows x 128 B] swizzled blocks
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {   // contraction along the 128-byte rows
+  return make_desc(base + (uint32_t)(kk >> 2) * (TILE_BYTES / 2) + (uint32_t)(kk & 3) * 32u, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {  // contraction along the tile rows
+  return make_desc(base + (uint32_t)kk * (16 * 128), TILE_BYTES / 2, 1024);
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_kv, bar_qdo_full, bar_qdo_empty, bar_sp_full, bar_pds_full, bar_dq_full, bar_s_free;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nQ = p.S / BQ;
+  const int gb = p.KV * p.B;
+  const int j = (int)(blockIdx.x / gb);                    // kv block; small j (long walks) first
+  const int g = (int)(blockIdx.x % gb) % p.KV, b = (int)(blockIdx.x % gb) / p.KV;
+  const int group = p.H / p.KV;
+  const int n_i = nQ - j;                                  // query blocks j..nQ-1
+  const int n_it = group * n_i;
+  const int kvrow0 = b * p.S + j * BKV;
+  const int kcol = (p.H + g) * DH, vcol = (p.H + p.KV + g) * DH;
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&bar_kv), 1);
+    mbar_init(smem_u32(&bar_qdo_full), 1); mbar_init(smem_u32(&bar_qdo_empty), 1);
+    mbar_init(smem_u32(&bar_sp_full), 1); mbar_init(smem_u32(&bar_pds_full), 4);
+    mbar_init(smem_u32(&bar_dq_full), 1); mbar_init(smem_u32(&bar_s_free), 4);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+  const uint32_t sK = smem_u32(smem), sV = sK + TILE_BYTES, sQ = sV + TILE_BYTES, sdO = sQ + TILE_BYTES,
+                 sP = sdO + TILE_BYTES, sdS = sP + TILE_BYTES;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bar_kv), 2 * TILE_BYTES);
+      tma_load_2d(sK, &p.tmQKV, smem_u32(&bar_kv), kcol, kvrow0);
+      tma_load_2d(sK + TILE_BYTES / 2, &p.tmQKV, smem_u32(&bar_kv), kcol + 64, kvrow0);
+      tma_load_2d(sV, &p.tmQKV, smem_u32(&bar_kv), vcol, kvrow0);
+      tma_load_2d(sV + TILE_BYTES / 2, &p.tmQKV, smem_u32(&bar_kv), vcol + 64, kvrow0);
+      bool ok = true;
+      for (int t = 0; t < n_it && ok; ++t) {
+        const int h = g * group + t / n_i, i = j + t % n_i;
+        const int qrow0 = b * p.S + i * BQ, qcol = h * DH;
+        if (!(ok = mbar_wait(smem_u32(&bar_qdo_empty), (uint32_t)((t & 1) ^ 1), abort_flag))) break;
+        const uint32_t fb = smem_u32(&bar_qdo_full);
+        mbar_expect_tx(fb, 2 * TILE_BYTES);
+        tma_load_2d(sQ, &p.tmQKV, fb, qcol, qrow0);
+        tma_load_2d(sQ + TILE_BYTES / 2, &p.tmQKV, fb, qcol + 64, qrow0);
+        tma_load_2d(sdO, &p.tmDO, fb, qcol, qrow0);
+        tma_load_2d(sdO + TILE_BYTES / 2, &p.tmDO, fb, qcol + 64, qrow0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_kk = idesc_bwd(false, false), id_mm = idesc_bwd(true, true), id_km = idesc_bwd(false, true);
+      bool ok = mbar_wait(smem_u32(&bar_kv), 0, abort_flag);
+      for (int t = 0; t < n_it && ok; ++t) {
+        const uint32_t ph = t & 1;
+        if (!(ok = mbar_wait(smem_u32(&bar_qdo_full), ph, abort_flag))) break;
+        if (t > 0 && !(ok = mbar_wait(smem_u32(&bar_s_free), ph ^ 1, abort_flag))) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tS, desc_kmajor(sQ, kk), desc_kmajor(sK, kk), id_kk, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tdP, desc_kmajor(sdO, kk), desc_kmajor(sV, kk), id_kk, kk > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_sp_full));
+        if (!(ok = mbar_wait(smem_u32(&bar_pds_full), ph, abort_flag))) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // dV[kv, d] += P^T[kv, q] dO[q, d]
+          umma_bf16(tdV, desc_mnmajor(sP, kk), desc_mnmajor(sdO, kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // dK[kv, d] += dS^T[kv, q] Q[q, d]
+          umma_bf16(tdK, desc_mnmajor(sdS, kk), desc_mnmajor(sQ, kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // dQ[q, d] = dS[q, kv] K[kv, d]
+          umma_bf16(tS, desc_kmajor(sdS, kk), desc_mnmajor(sK, kk), id_km, kk > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_dq_full));
+        umma_commit(smem_u32(&bar_qdo_empty));
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    // this warp's two private 4 KB staging buffers: its own rows of the two halves of the P tile
+    const uint32_t stg0 = sP + (uint32_t)quad * 4096u, stg1 = stg0 + TILE_BYTES / 2;
+    uint32_t n_boxes = 0;
+    bool ok = true;
+    for (int t = 0; t < n_it && ok; ++t) {
+      const int h = g * group + t / n_i, i = j + t % n_i;
+      const long long stat = ((long long)b * p.H + h) * p.S + i * BQ + r;
+      const float lse2 = p.lse[stat] * 1.4426950408889634f;
+      const float dl = p.delta[stat];
+      ok = mbar_wait(smem_u32(&bar_sp_full), t & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const bool diag = i == j;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tS + c * 32 + lane_off, sv);
+        tmem_ld32(tdP + c * 32 + lane_off, dv);
+        const uint32_t prow = sP + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
+        const uint32_t drow = sdS + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t pw[4], dw[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = c * 32 + q4 * 8 + 2 * e;
+            float p0 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e]), p.scale_log2, -lse2));
+            float p1 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e + 1]), p.scale_log2, -lse2));
+            if (diag) { if (col > r) p0 = 0.f; if (col + 1 > r) p1 = 0.f; }
+            const float d0 = p0 * (__uint_as_float(dv[q4 * 8 + 2 * e]) - dl) * p.scale;
+            const float d1 = p1 * (__uint_as_float(dv[q4 * 8 + 2 * e + 1]) - dl) * p.scale;
+            __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+            pw[e] = *reinterpret_cast<uint32_t*>(&hp);
+            dw[e] = *reinterpret_cast<uint32_t*>(&hd);
+          }
+          const uint32_t off = (((uint32_t)((c & 1) * 4 + q4)) ^ sw) << 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + off), "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(drow + off), "r"(dw[0]), "r"(dw[1]), "r"(dw[2]), "r"(dw[3]) : "memory");
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_pds_full));
+      // drain dQ_partial (fp32, in the S columns) into the global fp32 dQ with TMA reduce-add
+      ok = mbar_wait(smem_u32(&bar_dq_full), t & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int qrow0 = b * p.S + i * BQ + quad * 32;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32 + lane_off, v);
+        const uint32_t buf = (n_boxes & 1u) ? stg1 : stg0;
+        if (c >= 2) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+        }
+        const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((uint32_t)q8 ^ sw) << 4)), "r"(v[4 * q8]),
+                       "r"(v[4 * q8 + 1]), "r"(v[4 * q8 + 2]), "r"(v[4 * q8 + 3]) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_2d(&p.tmDQ, buf, h * DH + c * 32, qrow0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++n_boxes;
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // P rows may be rewritten
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_s_free));
+    }
+    // dV and dK of this kv block: TMEM -> bf16 -> staging -> TMA store into the packed gradient
+    if (ok) {
+      tcgen05_fence_after();
+      const int orow0 = kvrow0 + quad * 32;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {            // c>>1: 0 = dV, 1 = dK;  c&1: 64-column half
+        const uint32_t tacc = (c >> 1) ? tdK : tdV;
+        const uint32_t buf = (c & 1) ? stg1 : stg0;
+        if (c >= 2) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+        }
+        const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t v[32];
+          tmem_ld32(tacc + (c & 1) * 64 + hf * 32 + lane_off, v);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t pw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 2 * e]), __uint_as_float(v[8 * q4 + 2 * e + 1]));
+              pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((((uint32_t)(hf * 4 + q4)) ^ sw) << 4)),
+                         "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3]) : "memory");
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&p.tmDQKV, buf, ((c >> 1) ? kcol : vcol) + (c & 1) * 64, orow0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+  if (threadIdx.x == 0 && s_abort && p.status) atomicOr(p.status, TPLR_ST_WAIT_TIMEOUT);
+}
+
+// delta[b, h, s] = sum_d dO * O : one warp per (token, head), 4 elements per lane
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                                         float* __restrict__ delta, long long tokens, int S, int H,
+                                                         long long ld_o) {
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= tokens * H) return;
+  const int lane = threadIdx.x & 31;
+  const long long tok = w / H;
+  const int h = (int)(w % H);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + tok * ld_o + h * DH + lane * 4);
+  const uint2 d = *reinterpret_cast<const uint2*>(dout + tok * (long long)H * DH + h * DH + lane * 4);
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 d0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d.x));
+  const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d.y));
+  float s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
+  s = warp_sum(s);
+  if (lane == 0) delta[((tok / S) * H + h) * S + tok % S] = s;
+}
+
+// dq32 [tokens, H*128] fp32 -> first H*128 columns of the packed bf16 gradient
+__global__ void __launch_bounds__(256) attn_dq_cast_kernel(const float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv,
+                                                           long long tokens, int width, long long ld) {
+  const long long n4 = tokens * (width / 4);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n4; v += (long long)gridDim.x * blockDim.x) {
+    const long long tok = v / (width / 4);
+    const int c4 = (int)(v % (width / 4));
+    const float4 f = reinterpret_cast<const float4*>(dq32)[v];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dqkv + tok * ld + c4 * 4) = o;
+  }
+}
+
+}  // namespace
+
+// Gradient of tplr_attention_fwd.  qkv / dqkv: packed [B*S, C] bf16 with row stride ld_qkv; out: the forward's
+// output (row stride ld_o); dout: contiguous [B*S, H*128]; lse from the forward; delta: [B,H,S] fp32 scratch;
+// dq32: [B*S, H*128] fp32 scratch that the caller has zeroed.  dqkv receives dq | dk | dv.
+TPLR_API int tplr_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
+                                float scale, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (B <= 0 || S <= 0) return 0;
+  if (S % BQ || H % KV || (ld_qkv % 8) || (ld_o % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)dqkv & 15) ||
+      ((uintptr_t)dout & 15) || ((uintptr_t)out & 7) || ((uintptr_t)dq32 & 15))
+    return -201;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long tokens = (long long)B * S;
+  const int C = (H + 2 * KV) * DH;
+  AttnBwdParams p = {};
+  if (!make_map(&p.tmQKV, qkv, C, tokens, ld_qkv, 64, 128)) return -202;
+  if (!make_map(&p.tmDO, dout, (long long)H * DH, tokens, (long long)H * DH, 64, 128)) return -203;
+  if (!make_map(&p.tmDQ, dq32, (long long)H * DH, tokens, (long long)H * DH, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B, true)) return -204;
+  if (!make_map(&p.tmDQKV, dqkv, C, tokens, ld_qkv, 64, 32)) return -205;
+  p.lse = lse; p.delta = delta; p.B = B; p.S = S; p.H = H; p.KV = KV;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  attn_delta_kernel<<<(unsigned)((tokens * H + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
+                                                                       delta, tokens, S, H, ld_o);
+  cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+  if (e != cudaSuccess) return (int)e;
+  attn_bwd_kernel<<<(unsigned)((S / BKV) * KV * B), BWD_THREADS, BWD_SMEM, st>>>(p);
+  attn_dq_cast_kernel<<<tplr_sm_count() * 8, 256, 0, st>>>(dq32, (__nv_bfloat16*)dqkv, tokens, H * DH, ld_qkv);
+  return (int)cudaGetLastError();
+}

@@ -13,10 +13,10 @@
 //           time, and release one flag per 128 rows; the TMA producer of a compute CTA waits
 //           (bounded) for the flags of the rows it is about to load.  Every remote byte crosses
 //           NVLink once and the tiles of the local shard start at once.
-//   scatter (GEMM -> reduce-scatter): compute CTAs store the bf16 partial tile into this GPU's
-//           staging buffer and write one flag into the memory of the rank that owns those rows;
-//           that rank's comm CTAs wait (bounded) for the flags of all ranks, pull the partial
-//           tiles with TMA, sum them in fp32 and store the owned rows.
+//   scatter (GEMM -> reduce-scatter): the epilogue of every tile reduce-adds its 32 x 128-byte boxes
+//           (bf16 or fp32) with TMA straight into the buffer of the rank that owns those rows, over
+//           NVLink for a peer and in the local L2 for itself; tile rows are visited so that all
+//           owners receive traffic all the time.  No staging buffer, no second pass.
 // No load in this file carries a cluster-multicast qualifier; only tcgen05.commit does.
 // Every wait is bounded by wall time; on expiry TPLR_ST_WAIT_TIMEOUT is set and all roles return.
 //
@@ -36,14 +36,12 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_RANKS = 8;
 constexpr int CHUNK_ROWS = 128;                    // gather / scatter flag granularity (rows)
-constexpr int RS_ROWS_MIN = 16;                    // rows per reducer step at 8 ranks (more with fewer ranks)
-constexpr int RS_STAGES = 3, RS_STAGE_BYTES = 2 * STAGE_BYTES;   // 3 x 64 KB
 
 struct Gemm2Params {
   CUtensorMap tmA, tmB;
   CUtensorMap tmC;                   // output: box 64 x 32 bf16 or 32 x 32 fp32, 128-byte swizzle
   int c_tma;                         // 1: epilogue through TMA, 0: direct stores (unaligned C)
-  CUtensorMap tmPart[MAX_RANKS];     // scatter: every rank's staging buffer, box 256 x rs_rows, no swizzle
+  CUtensorMap tmCr[MAX_RANKS];       // scatter: rank o's owned rows [rows_per_rank, N], same box as tmC
   void* C;
   long long ldc;
   int M, N, K;
@@ -63,12 +61,7 @@ struct Gemm2Params {
   unsigned int* ag_flags;            // one per CHUNK_ROWS rows of the full buffer (local memory)
   // scatter
   int rs_on;
-  int rs_rows;                       // rows per reducer step: world * rs_rows * 512 B fill one 64 KB stage
   int rs_rows_per_rank;
-  unsigned int* rs_flag_dst[MAX_RANKS];   // rank o's flag array [world][chunks_per_rank][tiles_n], as mapped here
-  unsigned int* rs_flags;            // this rank's flag array
-  __nv_bfloat16* rs_out;             // [rs_rows_per_rank, N] owned rows of the reduced result
-  long long rs_ld_out;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -131,33 +124,12 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 // Bounded wait for *flag == want (flags carry the call's epoch).  SYS selects the scope of the acquire.
 template <bool SYS>
 __device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int want, volatile int* abort_flag) {
   unsigned long long t0 = 0;
   for (uint32_t i = 0;; ++i) {
     const unsigned int v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
-    if (v == want) return true;
-    if ((i & 7u) == 7u) {
-      if (*abort_flag) return false;
-      const unsigned long long now = gtimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) break;
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-// Bounded wait with relaxed polls (the flag lives in local memory); the caller issues the acquire fence.
-__device__ __forceinline__ bool flag_wait_relaxed(const unsigned int* flag, unsigned int want, volatile int* abort_flag) {
-  unsigned long long t0 = 0;
-  for (uint32_t i = 0;; ++i) {
-    unsigned int v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v == want) return true;
     if ((i & 7u) == 7u) {
       if (*abort_flag) return false;
@@ -225,6 +197,13 @@ __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem
   constexpr int COLS = EPI == 0 ? 64 : 32;
   const int row0 = m0 + quad * 32;
   const uint32_t sw = (uint32_t)(lane & 7);
+  const CUtensorMap* map = &p.tmC;
+  int y = row0;
+  if (p.rs_on && row0 < p.M) {                       // the 32 rows of a warp have one owner (128 | rows per rank)
+    const int owner = row0 / p.rs_rows_per_rank;
+    map = &p.tmCr[owner];
+    y = row0 - owner * p.rs_rows_per_rank;
+  }
 #pragma unroll 1
   for (int c = 0; c < TILE_N / COLS; ++c) {
     const int col0 = n0 + c * COLS;
@@ -264,8 +243,8 @@ __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0) {
-      if (EPI == 1) tma_reduce_add_2d(&p.tmC, buf, col0, row0);
-      else          tma_store_2d(&p.tmC, buf, col0, row0);
+      if (EPI == 1 || p.rs_on) tma_reduce_add_2d(map, buf, col0, y);
+      else                     tma_store_2d(map, buf, col0, y);
       bulk_commit();
     }
     ++n_boxes;
@@ -278,7 +257,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2], bar_epi[2];
+  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ uint32_t s_ready[32];   // gather: bit c set once chunk c was seen ready (1024 chunks)
@@ -287,7 +266,6 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
   const uint32_t cr = cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const bool is_compute = pair < p.n_compute_pairs;
-  const bool is_reducer = !is_compute && p.rs_on;
   const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + TILE_N - 1) / TILE_N;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
@@ -297,9 +275,9 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), is_reducer ? 4 : 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 8); mbar_init(smem_u32(&bar_epi[s]), 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_tfull[s]), 1); mbar_init(smem_u32(&bar_tempty[s]), 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -415,7 +393,6 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
       const int quad = warp & 3;
       uint32_t tile_i = 0, n_boxes = 0;
       bool ok = true;
-      const int chunks_per_rank = p.rs_on ? p.rs_rows_per_rank / CHUNK_ROWS : 1;
       for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
         int tm, tn;
         tile_coords(p, t, tiles_m, tiles_n, tm, tn);
@@ -430,22 +407,12 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         else         epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
         tcgen05_fence_before();
         __syncwarp();
-        if (EPI == 0 && p.rs_on && lane == 0) {
-          bulk_wait0();            // this warp's rows of the partial tile are written
-          __threadfence();
-          mbar_arrive(smem_u32(&bar_epi[acc]));
-        }
         if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[acc]), 0));
-        if (EPI == 0 && p.rs_on && warp == 2 && lane == 0) {
-          // once all four warps stored their rows (bounded wait), tell the rank that owns them
-          if (mbar_wait(smem_u32(&bar_epi[acc]), acc_ph, abort_flag) && m0 < p.M) {
-            const int chunk = m0 / CHUNK_ROWS, owner = chunk / chunks_per_rank, cl = chunk - owner * chunks_per_rank;
-            __threadfence_system();
-            st_release_sys(p.rs_flag_dst[owner] + ((long long)p.rank * chunks_per_rank + cl) * tiles_n + tn, p.epoch);
-          }
-        }
       }
-      if (lane == 0) bulk_wait0();   // staging buffers are read out before the CTA retires
+      if (lane == 0) {
+        bulk_wait0();                // staging buffers are read out and the stores / reductions are performed
+        if (p.rs_on) __threadfence_system();
+      }
     }
   } else if (p.ag_operand) {
     // ----------------------------- comm CTA: pull the peers' row shards -----------------
@@ -499,94 +466,6 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
       // loads that were issued but never stored (abort path) must land before the CTA retires
       for (long long g = stored; g < issued; ++g)
         mbar_wait(smem_u32(&bar_full[g % STAGES]), (uint32_t)((g / STAGES) & 1), abort_flag);
-    }
-  } else if (p.rs_on) {
-    // ----------------------------- comm CTA: reduce the rows this rank owns -------------
-    const int ci = (pair - p.n_compute_pairs) * 2 + (int)cr, n_comm = (n_pairs - p.n_compute_pairs) * 2;
-    const int chunks_per_rank = p.rs_rows_per_rank / CHUNK_ROWS;
-    const int RS_ROWS = p.rs_rows, SUBS = CHUNK_ROWS / RS_ROWS;
-    const uint32_t SRC_BYTES = (uint32_t)(TILE_N * RS_ROWS * 2);   // bytes per source per step
-    if (warp == 0) {
-      if (lane == 0) {
-        uint32_t it = 0;
-        bool ok = true;
-        int cnt = 0;
-        for (int u = 0; u < 2 * num_tiles && ok; ++u) {
-          int tm, tn;
-          tile_coords(p, u >> 1, tiles_m, tiles_n, tm, tn);
-          const int chunk = tm * 2 + (u & 1);
-          if (chunk / chunks_per_rank != p.rank) continue;
-          if ((cnt++) % n_comm != ci) continue;
-          const int cl = chunk - p.rank * chunks_per_rank;
-          for (int s = 0; s < p.world && ok; ++s)
-            ok = flag_wait_relaxed(p.rs_flags + ((long long)s * chunks_per_rank + cl) * tiles_n + tn, p.epoch, abort_flag);
-          if (!ok) break;
-          asm volatile("fence.acq_rel.sys;" ::: "memory");   // one acquire for all the flags of the unit
-          fence_proxy_async();
-          for (int sub = 0; sub < SUBS; ++sub, ++it) {
-            const int st = it % RS_STAGES;
-            const uint32_t ph = (it / RS_STAGES) & 1;
-            if (!(ok = mbar_wait(smem_u32(&bar_empty[st]), ph ^ 1, abort_flag))) break;
-            const uint32_t fb = smem_u32(&bar_full[st]);
-            mbar_expect_tx(fb, SRC_BYTES * p.world);
-            const int y = p.rank * p.rs_rows_per_rank + cl * CHUNK_ROWS + sub * RS_ROWS;
-            for (int j = 0; j < p.world; ++j) {
-              const int s = (p.rank + 1 + j) % p.world;
-              tma_load_2d(sbase + st * RS_STAGE_BYTES + s * SRC_BYTES, &p.tmPart[s], fb, tn * TILE_N, y);
-            }
-          }
-        }
-        for (uint32_t back = 0; back < RS_STAGES && back < it; ++back) {
-          const uint32_t j = it - 1 - back;
-          mbar_wait(smem_u32(&bar_full[j % RS_STAGES]), (j / RS_STAGES) & 1, abort_flag);
-        }
-      }
-    } else if (warp >= 2) {
-      const int tid = threadIdx.x - 64;   // 0..127
-      uint32_t it = 0;
-      bool ok = true;
-      int cnt = 0;
-      for (int u = 0; u < 2 * num_tiles && ok; ++u) {
-        int tm, tn;
-        tile_coords(p, u >> 1, tiles_m, tiles_n, tm, tn);
-        const int chunk = tm * 2 + (u & 1);
-        if (chunk / chunks_per_rank != p.rank) continue;
-        if ((cnt++) % n_comm != ci) continue;
-        const int cl = chunk - p.rank * chunks_per_rank;
-        for (int sub = 0; sub < SUBS; ++sub, ++it) {
-          const int st = it % RS_STAGES;
-          ok = mbar_wait(smem_u32(&bar_full[st]), (it / RS_STAGES) & 1, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          const uint8_t* sb = smem + st * RS_STAGE_BYTES;
-#pragma unroll 4
-          for (int j = 0; j < (RS_ROWS * TILE_N / 8) / 128; ++j) {
-            const int v = tid + 128 * j, r = v >> 5, cv = v & 31;
-            float acc[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            for (int s = 0; s < p.world; ++s) {
-              const uint4 q = *reinterpret_cast<const uint4*>(sb + s * SRC_BYTES + r * (TILE_N * 2) + cv * 16);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(h[e]);
-                acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
-              }
-            }
-            const int orow = cl * CHUNK_ROWS + sub * RS_ROWS + r, ocol = tn * TILE_N + cv * 8;
-            if (ocol < p.N) {
-              uint4 o;
-              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-              *reinterpret_cast<uint4*>(p.rs_out + (long long)orow * p.rs_ld_out + ocol) = o;
-            }
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_empty[st]));
-        }
-      }
     }
   }
   __syncwarp();
@@ -709,35 +588,35 @@ TPLR_API int tplr_gemm2_gather(const void* A, const void* B, void* C, int M, int
 }
 
 // GEMM fused with a reduce-scatter over the rows of C.  Every rank computes its partial
-// [M,N] = op(A) op(B) over its own K shard into its bf16 staging buffer `stage` (leading dimension
-// ldc); rank o owns rows [o*rows_per_rank, (o+1)*rows_per_rank) and receives their fp32-accumulated
-// sum over all ranks in `out` [rows_per_rank, N].  `peer_stage[r]` / `peer_flags[r]` are rank r's
-// staging buffer / flag array as mapped in this process (own entries are the local ones); the flag
-// array holds world * (rows_per_rank/128) * ceil(N/256) zero-initialised words.
-TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, void* stage, int M, int N, int K, long long lda,
-                                long long ldb, long long ldc, int a_mn, int b_mn, int world, int rank,
-                                int rows_per_rank, const void* const* peer_stage, void* const* peer_flags,
-                                void* out, long long ld_out, unsigned int epoch, int n_comm_pairs,
-                                unsigned int* status, void* stream) {
+// [M,N] = op(A) op(B) over its own K shard; rank o owns rows [o*rows_per_rank, (o+1)*rows_per_rank)
+// and `peer_out[o]` is its [rows_per_rank, N] result buffer (leading dimension ld_out, bf16 or fp32
+// by `out_fp32`) as mapped in this process.  The partial tiles are reduce-added into those buffers by
+// the epilogue, so every buffer must be zero and all ranks past a barrier when the kernel starts,
+// and the sums are complete once all ranks' kernels have finished (a barrier after it).
+TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                int a_mn, int b_mn, int world, int rank, int rows_per_rank,
+                                void* const* peer_out, long long ld_out, int out_fp32, unsigned int* status,
+                                void* stream) {
   TPLR_ENTER();
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || n_comm_pairs < 1) return -107;
-  if (rows_per_rank % CHUNK_ROWS || M != world * rows_per_rank || (N % 8) || (ldc % 8) || (ld_out % 8)) return -108;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -107;
+  const int esz = out_fp32 ? 4 : 2;
+  if (rows_per_rank % CHUNK_ROWS || M != world * rows_per_rank || (ld_out * esz) % 16) return -108;
   Gemm2Params p = {};
-  if (int r = fill_common(p, A, B, stage, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, status)) return r;
-  p.world = world; p.rank = rank; p.epoch = epoch;
+  const int epi = out_fp32 ? 1 : 0;
+  if (int r = fill_common(p, A, B, peer_out[rank], rows_per_rank, N, K, lda, ldb, ld_out, a_mn, b_mn, epi, status)) return r;
+  if (!p.c_tma) return -108;
+  p.M = M;                                 // fill_common built tmC over the owned rows only
+  if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
+  p.world = world; p.rank = rank;
   p.rs_on = 1; p.rs_rows_per_rank = rows_per_rank;
-  p.rs_rows = RS_ROWS_MIN;
-  while (p.rs_rows * 2 * world * TILE_N * 2 <= RS_STAGE_BYTES && p.rs_rows * 2 <= CHUNK_ROWS) p.rs_rows *= 2;
   for (int r = 0; r < world; ++r) {
-    if (!make_map(&p.tmPart[r], peer_stage[r], N, M, ldc, TILE_N, p.rs_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return -109;
-    p.rs_flag_dst[r] = static_cast<unsigned int*>(peer_flags[r]);
+    if ((uintptr_t)peer_out[r] & 15) return -108;
+    if (!make_map(&p.tmCr[r], peer_out[r], N, rows_per_rank, ld_out, out_fp32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B,
+                  out_fp32 != 0)) return -109;
   }
-  p.rs_flags = static_cast<unsigned int*>(peer_flags[rank]);
-  p.rs_out = static_cast<__nv_bfloat16*>(out);
-  p.rs_ld_out = ld_out;
-  // every band of tile rows touches every owner, so all ranks' reducers work throughout the GEMM
+  // every band of tile rows touches every owner, so all links carry traffic throughout the GEMM
   const int tiles_m = (M + TILE_M - 1) / TILE_M;
   if (world > 1 && tiles_m % world == 0) p.m_inter = world;
-  return dispatch2(p, a_mn, b_mn, 0, n_comm_pairs, 0, (cudaStream_t)stream);
+  return dispatch2(p, a_mn, b_mn, epi, 0, 0, (cudaStream_t)stream);
 }

@@ -417,6 +417,72 @@ def attention(q, k, v):
     return o.transpose(1, 2)
 
 
+_ATTN_BACKEND = "tcgen05"      # "tcgen05": own flash-attention kernels; "sdpa": torch SDPA (library)
+
+
+def set_attention_backend(name: str) -> None:
+    global _ATTN_BACKEND
+    if name not in ("tcgen05", "sdpa"):
+        raise ValueError(name)
+    _ATTN_BACKEND = name
+
+
+def attention_backend() -> str:
+    return _ATTN_BACKEND
+
+
+def _split_qkv(qkv, n_heads, n_kv, hd):
+    B, S, _ = qkv.shape
+    nq, nk = n_heads * hd, n_kv * hd
+    return (qkv[..., :nq].view(B, S, n_heads, hd), qkv[..., nq:nq + nk].view(B, S, n_kv, hd),
+            qkv[..., nq + nk:].view(B, S, n_kv, hd))
+
+
+class _AttentionPacked(torch.autograd.Function):
+    """Causal GQA attention on the packed projection output [B, S, (H + 2 KV) * 128]; the backward
+    returns the gradient in the same packed layout, so nothing splits or concatenates q, k and v."""
+
+    @staticmethod
+    def forward(ctx, qkv, n_heads, n_kv, hd):
+        B, S, C = qkv.shape
+        out = torch.empty(B, S, n_heads * hd, dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty(B, n_heads, S, dtype=torch.float32, device=qkv.device)
+        native.check(native.lib().tplr_attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, n_heads, n_kv,
+                                                     qkv.stride(1), out.stride(1), hd ** -0.5,
+                                                     status_word(qkv.device).data_ptr(), native.stream_ptr()),
+                     "attention_fwd")
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.dims = (n_heads, n_kv, hd)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        n_heads, n_kv, hd = ctx.dims
+        B, S, C = qkv.shape
+        do = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq32 = torch.zeros(B, S, n_heads * hd, dtype=torch.float32, device=qkv.device)
+        delta = torch.empty(B, n_heads, S, dtype=torch.float32, device=qkv.device)
+        native.check(native.lib().tplr_attention_bwd(qkv.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                                     delta.data_ptr(), dq32.data_ptr(), dqkv.data_ptr(), B, S, n_heads, n_kv,
+                                                     qkv.stride(1), out.stride(1), hd ** -0.5,
+                                                     status_word(qkv.device).data_ptr(), native.stream_ptr()),
+                     "attention_bwd")
+        return dqkv, None, None, None
+
+
+def attention_packed(qkv, n_heads: int, n_kv: int, hd: int):
+    """Causal attention of ``qkv`` [B, S, (H + 2 KV) * hd] (q heads, k heads, v heads); returns [B, S, H * hd]."""
+    B, S, C = qkv.shape
+    if (_ATTN_BACKEND == "tcgen05" and qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd == 128 and S % 128 == 0
+            and n_heads % n_kv == 0 and qkv.stride(2) == 1 and qkv.stride(0) == S * qkv.stride(1)
+            and qkv.stride(1) % 8 == 0 and qkv.data_ptr() % 16 == 0):
+        return _AttentionPacked.apply(qkv, n_heads, n_kv, hd)
+    q, k, v = _split_qkv(qkv, n_heads, n_kv, hd)
+    return attention(q, k, v).reshape(B, S, n_heads * hd)
+
+
 # --------------------------------------------------------------------------- #
 # Cross entropy with the logit gradient produced in the forward pass
 # --------------------------------------------------------------------------- #

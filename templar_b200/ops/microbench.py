@@ -84,6 +84,29 @@ def bench_gemm(a):
     print(json.dumps(rec))
 
 
+def bench_attention(a):
+    """Own flash attention (forward, forward+backward) vs torch SDPA on the packed layout of one layer."""
+    B, S, H, KV, hd = a.batch, a.seq, a.heads, a.kv_heads, 128
+    qkv = torch.randn(B, S, (H + 2 * KV) * hd, device="cuda").to(torch.bfloat16).requires_grad_()
+    dout = torch.randn(B, S, H * hd, device="cuda").to(torch.bfloat16)
+    fl_fwd = 4.0 * B * H * S * S * hd / 2
+    rec = {"case": "attention", "B": B, "S": S, "H": H, "KV": KV, "status": 0}
+    for be in ("tcgen05", "sdpa"):
+        OF.set_attention_backend(be)
+        with torch.no_grad():
+            med_f, _ = time_ms(lambda: OF.attention_packed(qkv, H, KV, hd), a.iters)
+
+        def fb():
+            qkv.grad = None
+            OF.attention_packed(qkv, H, KV, hd).backward(dout)
+        med_fb, _ = time_ms(fb, a.iters)
+        rec[f"{be}_fwd_ms"], rec[f"{be}_fwd_tflops"] = med_f, fl_fwd / med_f / 1e9
+        rec[f"{be}_fwdbwd_ms"], rec[f"{be}_fwdbwd_tflops"] = med_fb, 3.5 * fl_fwd / med_fb / 1e9
+    OF.set_attention_backend("tcgen05")
+    rec["status"] = int(OF.status_word("cuda").item())
+    print(json.dumps(rec))
+
+
 def _engine(model_name, topk, peers):
     from ..models.llama import PRESETS, build_model
     from ..parallel.window_engine import EngineConfig, WindowEngine
@@ -142,7 +165,7 @@ def bench_elementwise(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "compress", "aggregate", "elementwise"])
+    ap.add_argument("case", choices=["gemm", "compress", "aggregate", "elementwise", "attention"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=2048)
@@ -154,9 +177,13 @@ def main():
     ap.add_argument("--peers", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=8)
     a = ap.parse_args()
     {"gemm": bench_gemm, "compress": bench_compress, "aggregate": bench_aggregate,
-     "elementwise": bench_elementwise}[a.case](a)
+     "elementwise": bench_elementwise, "attention": bench_attention}[a.case](a)
 
 
 if __name__ == "__main__":

@@ -73,10 +73,12 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_sumsq": [vp, ll, vp, vp, vp],
         "tplr_adamw": [vp, vp, vp, vp, vp, i, ll, f, f, f, f, f, i, f, f, vp, i, vp],
         "tplr_cast_bf16": [vp, vp, ll, vp],
+        "tplr_attention_fwd": [vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
+        "tplr_attention_bwd": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_gemm_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, vp, i, vp],
         "tplr_gemm2_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, vp, i, vp],
         "tplr_gemm2_gather": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, i, i, i, i, vp, vp, ctypes.c_uint, i, vp, vp],
-        "tplr_gemm2_scatter": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, i, i, vp, vp, vp, ll, ctypes.c_uint, i, vp, vp],
+        "tplr_gemm2_scatter": [vp, vp, i, i, i, ll, ll, i, i, i, i, i, vp, ll, i, vp, vp],
         "tplr_heap_alloc": [ctypes.c_ulonglong, ctypes.POINTER(c_void_p)],
         "tplr_heap_free": [vp],
         "tplr_ipc_handle_size": [],

@@ -8,10 +8,11 @@ kernel for each pair (``tplr_gemm2_gather`` / ``tplr_gemm2_scatter``): the colle
 NVLink peer memory inside the GEMM launch, tile by tile.
 
 Buffers live on the symmetric heap: two gather buffers (alternated so that a rank may refill one
-while a slower peer still copies the other), one staging buffer for partial sums and one flag
-array.  Every fused call is preceded by one stream-ordered heap barrier, which both publishes the
-caller's rows to its peers and proves that all peers are done with the buffers of the call before
-the previous one.
+while a slower peer still copies the other) and one buffer for the rows a rank owns of a
+reduce-scattered product, into which all ranks' GEMM epilogues reduce-add their partial tiles.
+Every fused call is preceded by one stream-ordered heap barrier, which both publishes the caller's
+rows to its peers and proves that all peers are done with the buffers of the call before the
+previous one; the reduce-scatter is followed by a second one, after which the sums are complete.
 """
 
 from __future__ import annotations
@@ -33,7 +34,8 @@ class TensorParallel:
     ``rows`` is the number of tokens of the full (gathered) activation, ``width`` the widest
     activation that is gathered or reduce-scattered (the model dimension)."""
 
-    def __init__(self, heap: SymmetricHeap, rows: int, width: int, n_comm_pairs: int | None = None):
+    def __init__(self, heap: SymmetricHeap, rows: int, width: int, n_comm_pairs: int | None = None,
+                 reduce_dtype: torch.dtype = torch.bfloat16):
         self.heap, self.rank, self.world = heap, heap.rank, heap.world_size
         native.require(rows % (128 * self.world) == 0, "tensor parallel: rows must be a multiple of 128 * world")
         native.require(rows // 128 <= _MAX_CHUNKS, "tensor parallel: too many rows")
@@ -42,10 +44,9 @@ class TensorParallel:
         self.n_comm_pairs = n_comm_pairs
         self.device = heap.device
         self._g = [heap.alloc(rows * width, torch.bfloat16) for _ in range(2)]
-        self._s = heap.alloc(rows * width, torch.bfloat16)
-        tiles_n = -(-width // 256)
-        self._sflags = heap.alloc(self.world * (self.rows_per_rank // 128) * tiles_n, torch.int32)
-        self._sflags.zero_()
+        # reduce-scatter target: bf16 sums like NCCL's bf16 reduce-scatter, or fp32 sums at twice the NVLink bytes
+        self.reduce_dtype = reduce_dtype
+        self._r = heap.alloc(self.rows_per_rank * width, reduce_dtype)
         self._gflags = [torch.zeros(_MAX_CHUNKS, dtype=torch.int32, device=self.device) for _ in range(2)]
         self._g_next = 0
         self._epoch = 0
@@ -115,19 +116,19 @@ class TensorParallel:
         M, K = a.shape
         N = b.shape[1] if b_mn else b.shape[0]
         native.require(M == self.rows and N <= self.width, "gemm_rs: shape outside the workspace")
-        if out is None:
-            out = torch.empty((self.rows_per_rank, N), dtype=torch.bfloat16, device=self.device)
-        stage = self._s[: M * N].view(M, N)
+        ws = self._r[: self.rows_per_rank * N].view(self.rows_per_rank, N)
+        ws.zero_()
         self.heap.barrier()
-        stages = [self.heap.peer_ptr(self._s, r) for r in range(self.world)]
-        flags = [self.heap.peer_ptr(self._sflags, r) for r in range(self.world)]
+        outs = [self.heap.peer_ptr(self._r, r) for r in range(self.world)]
         err = native.lib().tplr_gemm2_scatter(
-            a.data_ptr(), b.data_ptr(), stage.data_ptr(), M, N, K, a.stride(0), b.stride(0), stage.stride(0),
-            0, int(b_mn), self.world, self.rank, self.rows_per_rank, native.ptr_array(stages),
-            native.ptr_array(flags), out.data_ptr(), out.stride(0), ctypes.c_uint(self._next_epoch()),
-            self._comm_pairs(2.0 * M * N * K, (self.world - 1) * self.rows_per_rank * N * 2),
+            a.data_ptr(), b.data_ptr(), M, N, K, a.stride(0), b.stride(0), 0, int(b_mn), self.world, self.rank,
+            self.rows_per_rank, native.ptr_array(outs), N, int(self.reduce_dtype == torch.float32),
             OF.status_word(self.device).data_ptr(), native.stream_ptr())
         native.check(err, "tplr_gemm2_scatter")
+        self.heap.barrier()
+        if out is None:
+            return ws.to(torch.bfloat16, copy=True)
+        out.copy_(ws)
         return out
 
     def check(self) -> None:

@@ -152,7 +152,7 @@ def test_add_rmsnorm_fwd_bwd():
         dh, dy = torch.randn_like(h), torch.randn_like(y)
         torch.autograd.backward([h, y], [dh, dy])
         rf, df, wf = (t.detach().float().requires_grad_() for t in (res, delta, w))
-        hr = (rf + df).to(torch.bfloat16).float() + (rf + df - (rf + df).detach())   # bf16-rounded sum, identity gradient
+        hr = (rf + df).detach().to(torch.bfloat16).float() + (rf + df - (rf + df).detach())   # bf16-rounded sum, identity gradient
         yr = F.rms_norm(hr, (D,), wf, 1e-5)
         torch.autograd.backward([hr, yr], [dh.float(), dy.float()])
         assert torch.equal(h, (res.detach().float() + delta.detach().float()).to(torch.bfloat16))
