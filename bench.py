@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="also print per-phase device times of one extra window (stderr; not part of the timed region)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -187,7 +189,39 @@ def run_ours(a):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), native.launch_count - l0, clocks
 
+    def breakdown():
+        marks = []
+
+        def mark(name):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e))
+
+        mark("start")
+        eng.snapshot(); mark("snapshot")
+        for m in range(A):
+            tok = dev_tokens[m % n_pool]
+            eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0 / A)
+        mark("micro_steps")
+        eng.optimizer_step(); mark("optimizer_step")
+        own_ptrs = None
+        if heap is not None:
+            own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
+        eng.compress(own_slot_ptrs=own_ptrs); mark("compress")
+        for j in hosted:
+            eng.load_peer_payload(j // world, host_payload[j])
+        mark("peer_payload_h2d")
+        if world > 1:
+            eng._barrier()
+        eng.outer_step(a.peers); mark("outer_step")
+        torch.cuda.synchronize()
+        return {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 3) for i in range(1, len(marks))}
+
     ms_total, launches, clocks = timed(False, a.steps, a.warmup)
+    if a.breakdown and rank == 0:
+        print("breakdown_ms " + json.dumps(breakdown()), file=sys.stderr)
+    elif a.breakdown:
+        breakdown()
     tokens_per_step = B * S * A * world
     value = tokens_per_step * a.steps / (ms_total / 1e3)
     e2e = None

@@ -50,6 +50,7 @@ struct Gemm2Params {
   int group_m;                       // tile order: bands of group_m tile rows, tile row fastest inside a band
   int m_rot;                         // rotation of the tile-row order (in 256-row tiles)
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
+  int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
   int world, rank;
   unsigned int epoch;
   // gather
@@ -267,8 +268,9 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const bool is_compute = pair < p.n_compute_pairs;
   const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + TILE_N - 1) / TILE_N;
-  const int num_tiles = tiles_m * tiles_n;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int k_blocks_all = (p.K + BK - 1) / BK;
+  const int k_per = (k_blocks_all + p.k_splits - 1) / p.k_splits;   // k blocks per work unit
+  const int num_tiles = tiles_m * tiles_n * p.k_splits;             // work units: (tile, k split), k split fastest
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
@@ -315,15 +317,17 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs) {
           int tm, tn;
-          tile_coords(p, t, tiles_m, tiles_n, tm, tn);
+          tile_coords(p, t / p.k_splits, tiles_m, tiles_n, tm, tn);
+          const int kb0 = (t % p.k_splits) * k_per;
+          const int k_blocks = min(k_per, k_blocks_all - kb0);
           const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N + (int)cr * CTA_N;
           if (p.ag_operand == 1 && !A_MN) ok = rows_ready(m0, CTA_M);
           if (p.ag_operand == 2 && !B_MN) ok = ok && rows_ready(n0, CTA_N);
           for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
             // k order rotated so that the rows of the local shard come first when k is the gathered dimension
-            int kbr = kb;
+            int kbr = kb0 + kb;
             if ((p.ag_operand == 1 && A_MN) || (p.ag_operand == 2 && B_MN)) {
-              kbr = kb + p.rank * (p.ag_rows_per_rank / BK);
+              kbr = kb + p.rank * (p.ag_rows_per_rank / BK);       // gathered k: never split
               if (kbr >= k_blocks) kbr -= k_blocks;
               if (!(ok = rows_ready(kbr * BK, BK))) break;
             }
@@ -365,6 +369,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         uint32_t it = 0, tile_i = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
+          const int k_blocks = min(k_per, k_blocks_all - (t % p.k_splits) * k_per);
           const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
           if (!(ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_ph ^ 1, abort_flag))) break;
           tcgen05_fence_after();
@@ -395,7 +400,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
         int tm, tn;
-        tile_coords(p, t, tiles_m, tiles_n, tm, tn);
+        tile_coords(p, t / p.k_splits, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N;
         const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_tfull[acc]), acc_ph, abort_flag);
@@ -526,6 +531,24 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
   return -104;
 }
 
+// Accumulating GEMMs (C += ...) reduce-add their tiles, so K may be cut to fill the last wave:
+// the number of splits (1, 2, 4 or 8, at least 16 k blocks each) that wastes the fewest CTA-pair slots.
+int pick_k_splits(int M, int N, int K, int max_pairs) {
+  int pairs = tplr_sm_count() / 2;
+  if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
+  const long long tiles = (long long)((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
+  const int k_blocks = (K + BK - 1) / BK;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 8; s *= 2) {
+    if (s > 1 && k_blocks / s < 16) break;
+    const long long units = tiles * s;
+    const double eff = (double)units / (double)(((units + pairs - 1) / pairs) * pairs);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
 // Fills the operand maps and the plain fields; returns 0 or a negative argument error.
 int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                 long long ldb, long long ldc, int a_mn, int b_mn, int epi, unsigned int* status) {
@@ -533,7 +556,7 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
   if (!(b_mn ? make_map(&p.tmB, B, N, K, ldb, 64, BK) : make_map(&p.tmB, B, K, N, ldb, BK, CTA_N))) return -103;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
-  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = 8; p.m_rot = 0; p.m_inter = 1;
+  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = 8; p.m_rot = 0; p.m_inter = 1; p.k_splits = 1;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
@@ -551,6 +574,7 @@ TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   Gemm2Params p = {};
   if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
+  if (epi == 1 && p.c_tma) p.k_splits = pick_k_splits(M, N, K, max_pairs);
   return dispatch2(p, a_mn, b_mn, epi, 0, max_pairs, (cudaStream_t)stream);
 }
 

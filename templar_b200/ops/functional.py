@@ -214,13 +214,22 @@ class _AddRMSNorm(torch.autograd.Function):
             native.check(native.lib().tplr_add_rmsnorm_fwd(res.data_ptr(), delta.data_ptr(), w.data_ptr(), h.data_ptr(),
                                                            y.data_ptr(), rstd.data_ptr(), T, D, eps, native.stream_ptr()),
                          "add_rmsnorm_fwd")
-            ctx.native = True
+            ctx.native = 1
+        elif _native_ok(res, delta, w) and D % 8 == 0 and D <= 8192:
+            # wide rows: eager add, then the one-CTA-per-row norm kernels
+            h = res + delta
+            T = h.numel() // D
+            y = torch.empty_like(h)
+            rstd = torch.empty(T, dtype=torch.float32, device=res.device)
+            native.check(native.lib().tplr_rmsnorm_fwd(h.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(),
+                                                       T, D, eps, native.stream_ptr()), "rmsnorm_fwd")
+            ctx.native = 2
         else:
             h = res + delta
             hf = h.float()
             rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
             y = (hf * rstd * w.float()).to(res.dtype)
-            ctx.native = False
+            ctx.native = 0
         ctx.save_for_backward(h, w, rstd)
         return h, y
 
@@ -229,6 +238,17 @@ class _AddRMSNorm(torch.autograd.Function):
         h, w, rstd = ctx.saved_tensors
         mg = ctx.main_grad
         D = h.shape[-1]
+        if ctx.native == 2:
+            T = h.numel() // D
+            dyc = dy.contiguous()
+            dx = torch.empty_like(h)
+            dw_buf = mg if mg is not None else torch.zeros(D, dtype=torch.float32, device=h.device)
+            native.check(native.lib().tplr_rmsnorm_bwd(dyc.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                                       dx.data_ptr(), dw_buf.data_ptr(), T, D, native.stream_ptr()),
+                         "rmsnorm_bwd")
+            if dh is not None:
+                dx += dh
+            return dx, dx, (None if mg is not None else dw_buf.to(w.dtype)), None, None
         if ctx.native:
             T = h.numel() // D
             dyc = dy.contiguous()

@@ -68,16 +68,17 @@ class TensorParallel:
         return self._epoch
 
     def _comm_pairs(self, flops: float, link_bytes: float) -> int:
-        """CTA pairs set aside for the collective: enough to move ``link_bytes`` within the GEMM's
-        own time (about 50 GB/s per CTA with its shared memory full of loads in flight), no more
-        than what saturates one NVLink direction."""
+        """CTA pairs set aside for the gather.  The tiles of the local shard need no peer data, so the
+        peers' rows have to arrive within the remaining (world-1)/world of the GEMM's time; one copier
+        CTA sustains about 45 GB/s (160 KB of loads in flight over NVLink), and more than 16 of them
+        only saturate the link."""
         if self.n_comm_pairs is not None:
             return self.n_comm_pairs
         if self.world == 1:
             return 1
-        t_gemm = flops / 1.4e15
-        need_gbs = min(link_bytes / max(t_gemm, 1e-6) / 1e9, 800.0)
-        return max(1, min(8, -(-int(need_gbs / 50.0 + 0.999) // 2)))
+        t_remote = flops / 1.4e15 * (self.world - 1) / self.world
+        need_gbs = min(link_bytes / max(t_remote, 1e-6) / 1e9, 720.0)
+        return max(1, min(8, -(-int(need_gbs / 45.0 + 0.999) // 2)))
 
     # -- fused kernels ----------------------------------------------------------------------------
     def ag_gemm(self, slot: int, width: int, other: torch.Tensor, *, gathered: str = "A", a_mn: bool = False,

@@ -1,0 +1,65 @@
+"""Worker launched by test_gpu_multi.py under torchrun: tensor-parallel LLaMA vs the unsharded model on one GPU."""
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from templar_b200.models.llama import ModelArgs, build_model  # noqa: E402
+from templar_b200.models.llama_tp import TPLlamaModel  # noqa: E402
+from templar_b200.ops import functional as OF  # noqa: E402
+from templar_b200.parallel.symmetric import SymmetricHeap  # noqa: E402
+from templar_b200.parallel.tensor_parallel import TensorParallel  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    heap = SymmetricHeap.create(dev, rank, world, timeout_s=20.0)
+    args = ModelArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, intermediate_size=1024, max_seq_len=256)
+    B, S = 2, 256
+    full = build_model(args, device=dev, dtype=torch.bfloat16, seed=9)
+    model = TPLlamaModel(args, rank, world).to(device=dev, dtype=torch.bfloat16)
+    model.freqs_cis = full.freqs_cis
+    model.load_from_full(full)
+    model.attach(TensorParallel(heap, rows=B * S, width=args.dim))
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, args.vocab_size, (B, S + 1), generator=g).to(dev)
+    loss = model.loss(toks[:, :-1], toks[:, 1:])
+    loss.backward()
+    model.reduce_replicated_grads()
+    ref = full.loss(toks[:, :-1], toks[:, 1:])
+    ref.backward()
+    torch.cuda.synchronize()
+    model.tp.check()
+    out = {"loss": float(loss), "ref_loss": float(ref), "status": int(OF.status_word(dev).item())}
+    fg = {n: p.grad for n, p in full.named_parameters()}
+    n_sh, worst = world, 0.0
+    for name, p in model.named_parameters():
+        f = fg[name].float()
+        if name.endswith(("wq.weight", "wk.weight", "wv.weight", "w1.weight", "w3.weight")) or name in ("tok_embeddings.weight", "output.weight"):
+            n = f.shape[0] // n_sh
+            f = f[rank * n:(rank + 1) * n]
+        elif name.endswith(("wo.weight", "w2.weight")):
+            n = f.shape[1] // n_sh
+            f = f[:, rank * n:(rank + 1) * n]
+        rel = ((p.grad.float() - f).norm() / (f.norm() + 1e-12)).item()
+        worst = max(worst, rel)
+        out.setdefault("rel", {})[name] = rel
+    out["worst_rel"] = worst
+    res = [None] * world
+    dist.all_gather_object(res, out)
+    if rank == 0:
+        print("RESULT " + json.dumps(res))
+    heap.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

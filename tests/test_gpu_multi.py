@@ -47,3 +47,13 @@ def test_fused_tensor_parallel_linears():
         assert r["status"] == 0, r
         for k in ("h", "y", "dx", "dw1", "dw2"):
             assert r[k] < 2e-2, (k, r)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_model_matches_unsharded():
+    """Loss and every parameter gradient of the 2-way tensor-parallel model against the same model on one GPU."""
+    res = _run(2, worker="_tp_model_worker.py")
+    for r in res:
+        assert r["status"] == 0, r
+        assert abs(r["loss"] - r["ref_loss"]) < 3e-2, r
+        assert r["worst_rel"] < 0.12, r   # two bf16 pipelines with different summation orders
