@@ -23,6 +23,7 @@
 // Replaces cuBLAS + NCCL behind the reference's tensor-parallel plan: colwise q/k/v/w1/w3,
 // rowwise wo/w2 with sequence-sharded activations (torchtitan models/llama3/infra/parallelize.py:151-219).
 #include "tcgen05.cuh"
+#include <stdlib.h>
 
 namespace {
 using namespace tplr_tc;
@@ -531,22 +532,18 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
   return -104;
 }
 
-// Accumulating GEMMs (C += ...) reduce-add their tiles, so K may be cut to fill the last wave:
-// the number of splits (1, 2, 4 or 8, at least 16 k blocks each) that wastes the fewest CTA-pair slots.
+// Accumulating GEMMs (C += ...) reduce-add their tiles, so K may be cut in two to fill the last wave.
+// Every split costs another M*N*4 bytes of L2 reductions (measured: 4 and 8 splits lose more than the
+// fuller waves win), so K is halved only when that lifts the wave efficiency by more than 10 points.
 int pick_k_splits(int M, int N, int K, int max_pairs) {
+  static const int forced = [] { const char* e = getenv("TPLR_GEMM_KSPLITS"); return e ? atoi(e) : 0; }();
+  if (forced > 0) return (K + BK - 1) / BK / forced >= 1 ? forced : 1;   // tuning override
   int pairs = tplr_sm_count() / 2;
   if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
   const long long tiles = (long long)((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
-  const int k_blocks = (K + BK - 1) / BK;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; s *= 2) {
-    if (s > 1 && k_blocks / s < 16) break;
-    const long long units = tiles * s;
-    const double eff = (double)units / (double)(((units + pairs - 1) / pairs) * pairs);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
-  }
-  return best;
+  if ((K + BK - 1) / BK < 128) return 1;
+  auto eff = [&](long long units) { return (double)units / (double)(((units + pairs - 1) / pairs) * pairs); };
+  return eff(2 * tiles) > eff(tiles) + 0.10 ? 2 : 1;
 }
 
 // Fills the operand maps and the plain fields; returns 0 or a negative argument error.
