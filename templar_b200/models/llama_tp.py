@@ -130,9 +130,12 @@ class _VocabParallelCE(torch.autograd.Function):
     single-GPU loss, the logit gradient (times ``grad_scale``) is produced in the forward."""
 
     @staticmethod
-    def forward(ctx, logits, labels, rank, group, grad_scale, ignore_index):
+    def forward(ctx, logits, labels, rank, group, grad_scale, ignore_index, vocab):
         vl = logits.shape[-1]
         lf = logits.float()
+        n_real = min(max(vocab - rank * vl, 0), vl)         # columns of this rank that are real vocabulary entries
+        if n_real < vl:
+            lf[:, n_real:] = float("-inf")
         m = lf.max(-1).values
         dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
         e = torch.exp(lf - m.unsqueeze(-1))
@@ -155,7 +158,7 @@ class _VocabParallelCE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         (g,) = ctx.saved_tensors
-        return g, None, None, None, None, None
+        return g, None, None, None, None, None, None
 
 
 class TPLlamaModel(LlamaModel):
@@ -163,13 +166,16 @@ class TPLlamaModel(LlamaModel):
 
     def __init__(self, args: ModelArgs, tp_rank: int, tp_world: int):
         nn.Module.__init__(self)
-        assert args.vocab_size % (64 * tp_world) == 0, "vocabulary must divide by 64 * TP degree"
         self.args = self.model_args = args
         self.tp_rank, self.tp_world = tp_rank, tp_world
-        self.tok_embeddings = nn.Embedding(args.vocab_size // tp_world, args.dim)
+        # the vocabulary is padded so that every rank's rows are whole 64-row chunks; padded rows are zero,
+        # never indexed by a token and masked out of the softmax
+        step = 64 * tp_world
+        self.vocab_padded = -(-args.vocab_size // step) * step
+        self.tok_embeddings = nn.Embedding(self.vocab_padded // tp_world, args.dim)
         self.layers = nn.ModuleDict({str(i): TPTransformerBlock(i, args, tp_world) for i in range(args.n_layers)})
         self.norm = RMSNorm(args.dim, args.norm_eps)
-        self.output = _Weight(args.vocab_size // tp_world, args.dim)
+        self.output = _Weight(self.vocab_padded // tp_world, args.dim)
         self.register_buffer("freqs_cis", self._freqs_cis(), persistent=True)
         self._rope_cache: dict = {}
         self.activation_checkpointing = False
@@ -207,14 +213,23 @@ class TPLlamaModel(LlamaModel):
             n = t.shape[0] // w
             return t[r * n:(r + 1) * n]
 
+        def vocab_rows(t):
+            n = self.vocab_padded // w
+            out = torch.zeros(n, t.shape[1], dtype=t.dtype, device=t.device)
+            lo, hi = r * n, min((r + 1) * n, t.shape[0])
+            if hi > lo:
+                out[: hi - lo] = t[lo:hi]
+            return out
+
         def cols(t):
             n = t.shape[1] // w
             return t[:, r * n:(r + 1) * n]
 
         for name, p in self.named_parameters():
             src = sd[name]
-            if name.endswith(("wq.weight", "wk.weight", "wv.weight", "w1.weight", "w3.weight")) or name in (
-                    "tok_embeddings.weight", "output.weight"):
+            if name in ("tok_embeddings.weight", "output.weight"):
+                p.copy_(vocab_rows(src))
+            elif name.endswith(("wq.weight", "wk.weight", "wv.weight", "w1.weight", "w3.weight")):
                 p.copy_(rows(src))
             elif name.endswith(("wo.weight", "w2.weight")):
                 p.copy_(cols(src))
@@ -237,4 +252,5 @@ class TPLlamaModel(LlamaModel):
 
     def loss(self, tokens: torch.Tensor, labels: torch.Tensor, grad_scale: float = 1.0,
              ignore_index: int = -100) -> torch.Tensor:
-        return _VocabParallelCE.apply(self.forward(tokens), labels, self.tp_rank, self.group, grad_scale, ignore_index)
+        return _VocabParallelCE.apply(self.forward(tokens), labels, self.tp_rank, self.group, grad_scale, ignore_index,
+                                      self.args.vocab_size)

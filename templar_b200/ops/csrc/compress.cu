@@ -22,7 +22,7 @@
 // Semantics follow the reference's src/tplr/compress.py:225-292 (chunking + DCT),
 // :385-481 (top-k, scatter-mean over contributors), :526-556 (median-norm clip) and
 // src/tplr/neurons.py:138-173 (error feedback), :342-450 (outer step).
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define NT 256
 #define LD 64
@@ -582,6 +582,299 @@ TPLR_API int tplr_aggregate_apply(const void* descs, int n_desc, int total_chunk
   int grid = tplr_sm_count() * 2;
   if (grid > total_chunks) grid = total_chunks;
   aggregate_kernel<<<grid, NT, smem, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// Tensor-core path of the inverse chunk DCT (all chunks 64 x 64, one shared basis F).
+//
+// g = F^T S F for two chunks at a time as two tcgen05 GEMMs of shape 128 x 64 x 64 against the basis:
+//   Z[(c,j)][r]   = sum_n S_c[n][j] F[n][r]     A = S^T rows (K-major),        B = F read N-contiguous
+//   g[(c,r)][col] = sum_j Z_c[j][r] F[j][col]   A = Z read M-contiguous (no transpose pass), B = F again
+// fp32 operands are split into three bf16 terms (x = b1 + b2 + b3, 24 mantissa bits) and the six
+// products whose weight is above 2^-24 are accumulated in fp32 in tensor memory, so the result has
+// fp32-grade accuracy.  The 128-byte-swizzled tile that holds Z is written once and read by the second
+// GEMM through an M-major descriptor; the basis tile is shared by both GEMMs.
+// ------------------------------------------------------------------------------------- //
+namespace {
+using namespace tplr_tc;
+
+constexpr int TC_A_TILE = 128 * 128;          // bytes: 128 rows x 64 bf16
+constexpr int TC_B_TILE = 64 * 128;           // bytes: 64 rows x 64 bf16
+constexpr int TC_SMEM = 3 * TC_A_TILE + 3 * TC_B_TILE + 1024;   // S/Cnt accumulators alias the A tiles + extra
+constexpr int TC_ACC_BYTES = 2 * 4096 * 8;    // two chunks: fp32 sums + int counts = 64 KB
+constexpr int TC_SMEM_AGG = TC_ACC_BYTES + 3 * TC_B_TILE + 1024;
+
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& b1, __nv_bfloat16& b2, __nv_bfloat16& b3) {
+  b1 = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(b1);
+  b2 = __float2bfloat16_rn(r1);
+  b3 = __float2bfloat16_rn(r1 - __bfloat162float(b2));
+}
+
+// Writes 32 consecutive fp32 values of one tile row (columns 32*hf .. 32*hf+31) as three bf16 split tiles.
+// row: 128-byte row index inside the tile whose three term copies start at base, base + stride, base + 2*stride.
+__device__ __forceinline__ void store_split_row(uint32_t base, uint32_t stride, int row, int hf, const float* v) {
+  const uint32_t rowaddr = base + (uint32_t)row * 128u;
+  const uint32_t sw = (uint32_t)(row & 7);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w1[4], w2[4], w3[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat16 a1, a2, a3, c1, c2, c3;
+      split3(v[8 * q + 2 * e], a1, a2, a3);
+      split3(v[8 * q + 2 * e + 1], c1, c2, c3);
+      __nv_bfloat162 h1 = __halves2bfloat162(a1, c1), h2 = __halves2bfloat162(a2, c2), h3 = __halves2bfloat162(a3, c3);
+      w1[e] = *reinterpret_cast<uint32_t*>(&h1);
+      w2[e] = *reinterpret_cast<uint32_t*>(&h2);
+      w3[e] = *reinterpret_cast<uint32_t*>(&h3);
+    }
+    const uint32_t off = (((uint32_t)(hf * 4 + q)) ^ sw) << 4;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + off), "r"(w1[0]), "r"(w1[1]), "r"(w1[2]), "r"(w1[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + stride + off), "r"(w2[0]), "r"(w2[1]), "r"(w2[2]), "r"(w2[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + 2 * stride + off), "r"(w3[0]), "r"(w3[1]), "r"(w3[2]), "r"(w3[3]) : "memory");
+  }
+}
+
+// The 64 x 64 basis (row-major fp32 in global memory) as three swizzled bf16 tiles [64 rows x 128 B].
+__device__ __forceinline__ void load_basis_split(const float* __restrict__ g, uint32_t sB) {
+  // 256 threads: row = tid / 4, 16 columns each
+  const int row = threadIdx.x >> 2, c0 = (threadIdx.x & 3) * 16;
+  const uint32_t rowaddr = sB + (uint32_t)row * 128u;
+  const uint32_t sw = (uint32_t)(row & 7);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t w1[4], w2[4], w3[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat16 a1, a2, a3, c1, c2, c3;
+      split3(__ldg(g + row * 64 + c0 + 8 * q + 2 * e), a1, a2, a3);
+      split3(__ldg(g + row * 64 + c0 + 8 * q + 2 * e + 1), c1, c2, c3);
+      __nv_bfloat162 h1 = __halves2bfloat162(a1, c1), h2 = __halves2bfloat162(a2, c2), h3 = __halves2bfloat162(a3, c3);
+      w1[e] = *reinterpret_cast<uint32_t*>(&h1);
+      w2[e] = *reinterpret_cast<uint32_t*>(&h2);
+      w3[e] = *reinterpret_cast<uint32_t*>(&h3);
+    }
+    const uint32_t off = (((uint32_t)(c0 / 8 + q)) ^ sw) << 4;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + off), "r"(w1[0]), "r"(w1[1]), "r"(w1[2]), "r"(w1[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + TC_B_TILE + off), "r"(w2[0]), "r"(w2[1]), "r"(w2[2]), "r"(w2[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + 2 * TC_B_TILE + off), "r"(w3[0]), "r"(w3[1]), "r"(w3[2]), "r"(w3[3]) : "memory");
+  }
+}
+
+// D[128 x 64] = A B with the six significant products of the 3-term splits.  a_mn: A tile holds K rows of
+// 128 bytes of M (two 64-wide M blocks 8 KB apart); otherwise A tile holds 128 M rows of 128 bytes of K.
+// b_mn: the basis tile is read with its rows as K (B = F); otherwise with its rows as N (B = F^T).
+__device__ __forceinline__ void issue_split_gemm(uint32_t tD, uint32_t sA, uint32_t sB, bool a_mn, bool b_mn) {
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+                         ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  const int ta[6] = {0, 0, 1, 0, 1, 2}, tb[6] = {0, 1, 0, 2, 1, 0};
+  uint32_t first = 1;
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+    for (int t = 0; t < 6; ++t) {
+      const uint32_t a0 = sA + (uint32_t)ta[t] * TC_A_TILE, b0 = sB + (uint32_t)tb[t] * TC_B_TILE;
+      const uint64_t da = a_mn ? make_desc(a0 + kk * 2048u, 8192, 1024) : make_desc(a0 + kk * 32u, 16, 1024);
+      const uint64_t db = b_mn ? make_desc(b0 + kk * 2048u, 8192, 1024) : make_desc(b0 + kk * 32u, 16, 1024);
+      umma_bf16(tD, da, db, idesc, first ? 0u : 1u);
+      first = 0;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
+  extern __shared__ uint8_t smem_raw_tc[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_tc) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_mma;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  float* S = reinterpret_cast<float*>(smem);                       // [2][4096] sums, later the A tiles
+  int* Cnt = reinterpret_cast<int*>(smem + 2 * 4096 * 4);          // [2][4096] contributor counts
+  const uint32_t sA = smem_u32(smem), sB = sA + TC_ACC_BYTES;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qd = warp & 3, hf = warp >> 2;                         // TMEM lane quadrant, column half
+  const int ch = qd >> 1, rin = (qd & 1) * 32 + lane;              // chunk of the pair, row inside the chunk
+  const int trow = ch * 64 + rin;                                  // row of the stacked 128-row tiles
+  const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+  volatile int* abort_flag = &s_abort;
+  int cur_f = -1;
+  uint32_t phase = 0;
+
+  if (tid == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&bar_mma), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(smem_u32(&s_tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tZ = s_tmem_base, tG = s_tmem_base + 64;
+  const int n_pairs = (a.total_chunks + 1) / 2;
+  bool ok = true;
+
+  for (int q = blockIdx.x; q < n_pairs && ok; q += gridDim.x) {
+    // this thread's chunk of the pair
+    const int c = 2 * q + ch;
+    const bool active = c < a.total_chunks;
+    TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, active ? c : a.total_chunks - 1)];
+    const int cl = c - d.chunk_begin;
+    const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
+    const long long base = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64;
+    const bool skipped = a.skip && a.skip[d.param_id];
+    __syncthreads();                                   // previous pair's tiles and accumulators are free
+    if (d.fh_off != cur_f) {                           // uniform: every 64 x 64 chunk uses the same basis
+      load_basis_split(a.basis + d.fh_off, sB);
+      cur_f = d.fh_off;
+    }
+    for (int i = tid; i < TC_ACC_BYTES / 16; i += NT) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    // ---- pull + unpack + scale + scatter-add, both chunks --------------------------------
+    {
+      const int pairs = d.k / 2;                       // k is the same for all 64 x 64 chunks of a layout
+      for (int t = tid; t < 2 * a.n_peers * pairs; t += NT) {
+        const int c2 = t / (a.n_peers * pairs), rem = t - c2 * (a.n_peers * pairs);
+        const int cc = 2 * q + c2;
+        if (cc >= a.total_chunks) continue;
+        const TplrParamDesc d2 = a.descs[find_desc(a.descs, a.n_desc, cc)];
+        if (a.skip && a.skip[d2.param_id]) continue;
+        const int cl2 = cc - d2.chunk_begin;
+        const int peer = rem / pairs, pr = rem - peer * pairs;
+        const uint8_t* ip = a.pp.idx[peer] + d2.idx_off + ((long long)cl2 * pairs + pr) * 3;
+        const unsigned b0 = ip[0], b1 = ip[1], b2 = ip[2];
+        const int i0 = (int)(b0 | ((b1 & 0xfu) << 8));
+        const int i1 = (int)(((b1 >> 4) & 0xfu) | (b2 << 4));
+        const long long vo = d2.val_off + (long long)cl2 * d2.k + 2 * pr;
+        const float* qt = a.qtable ? a.qtable + ((long long)peer * a.n_params + d2.param_id) * (a.n_bins + 1) : nullptr;
+        const float sc = a.clip ? a.clip[(long long)peer * a.n_params + d2.param_id] : 1.f;
+        const float v0 = load_val(a.pp.val[peer], vo, a.val_dtype, qt, a.n_bins) * sc;
+        const float v1 = load_val(a.pp.val[peer], vo + 1, a.val_dtype, qt, a.n_bins) * sc;
+        atomicAdd(&S[c2 * 4096 + i0], v0); atomicAdd(&Cnt[c2 * 4096 + i0], 1);   // 12-bit indices: always < 4096
+        atomicAdd(&S[c2 * 4096 + i1], v1); atomicAdd(&Cnt[c2 * 4096 + i1], 1);
+      }
+    }
+    __syncthreads();
+    // ---- mean, transposed read: row j of S_c^T, columns n = 32*hf .. ------------------------
+    float v[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const int n = hf * 32 + e;
+      const float s = S[ch * 4096 + n * 64 + rin];
+      const int cnt = Cnt[ch * 4096 + n * 64 + rin];
+      v[e] = cnt > 1 ? s / (float)cnt : s;
+    }
+    __syncthreads();                                   // accumulators are read out: their bytes become the A tiles
+    store_split_row(sA, TC_A_TILE, trow, hf, v);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tcgen05_fence_after();
+      issue_split_gemm(tZ, sA, sB, /*a_mn=*/false, /*b_mn=*/true);      // Z = S^T F
+      umma_commit(smem_u32(&bar_mma));
+    }
+    ok = mbar_wait(smem_u32(&bar_mma), phase, abort_flag);
+    phase ^= 1;
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tcgen05_fence_after();
+    {
+      uint32_t r[32];
+      tmem_ld32(tZ + hf * 32 + lane_off, r);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+    }
+    // Z_c rows (index j) into block c of the tiles: read back M-contiguous by the second GEMM
+    store_split_row(sA + (uint32_t)ch * 8192u, TC_A_TILE, rin, hf, v);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tcgen05_fence_after();
+      issue_split_gemm(tG, sA, sB, /*a_mn=*/true, /*b_mn=*/true);       // g = Z^T F
+      umma_commit(smem_u32(&bar_mma));
+    }
+    ok = mbar_wait(smem_u32(&bar_mma), phase, abort_flag);
+    phase ^= 1;
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    tcgen05_fence_after();
+    uint32_t gr[32];
+    tmem_ld32(tG + hf * 32 + lane_off, gr);
+    tcgen05_fence_before();
+    // ---- outer update of row `rin`, columns 32*hf .. of chunk c -------------------------------
+    if (active) {
+      const float lr = skipped ? 0.f : a.lr;
+      const float decay = skipped ? 1.f : (1.f - a.lr * a.weight_decay);
+      const long long g0 = base + (long long)rin * d.cols + hf * 32;
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        float gv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) gv[e] = skipped ? 0.f : __uint_as_float(gr[4 * q4 + e]);
+        if (a.grad_out) *reinterpret_cast<float4*>(a.grad_out + g0 + 4 * q4) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+        if (a.update_mode != 2) {
+          const float4 t0 = *reinterpret_cast<const float4*>(a.theta0 + g0 + 4 * q4);
+          const float tv[4] = {t0.x, t0.y, t0.z, t0.w};
+          float o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float step = (a.update_mode == 1) ? (gv[e] > 0.f ? 1.f : (gv[e] < 0.f ? -1.f : 0.f)) : gv[e];
+            o[e] = tv[e] * decay - lr * step;
+          }
+          *reinterpret_cast<float4*>(a.theta + g0 + 4 * q4) = make_float4(o[0], o[1], o[2], o[3]);
+          if (a.theta_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned int*>(&lo);
+            pk.y = *reinterpret_cast<unsigned int*>(&hi);
+            *reinterpret_cast<uint2*>(a.theta_bf16 + g0 + 4 * q4) = pk;
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(s_tmem_base) : "memory");
+  }
+  if (tid == 0 && s_abort && a.status) atomicOr(a.status, TPLR_ST_WAIT_TIMEOUT);
+}
+
+}  // namespace
+
+// Same contract as tplr_aggregate_apply with use_dct = 1 and one shared basis, for descriptor tables in
+// which every chunk is 64 x 64 (element offsets and column counts multiples of 4).
+TPLR_API int tplr_aggregate_apply_tc(const void* descs, int n_desc, int total_chunks, const float* basis,
+                                     int n_peers, const void* const* idx_ptrs, const void* const* val_ptrs,
+                                     int val_dtype, const float* qtable, int n_bins, int n_params,
+                                     const float* clip, const int* skip, const float* theta0, float* theta,
+                                     void* theta_bf16, float* grad_out, float lr, float weight_decay,
+                                     int update_mode, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (total_chunks <= 0) return 0;
+  if (n_peers > TPLR_MAX_PEERS || n_peers <= 0) return (int)cudaErrorInvalidValue;
+  AggArgs a;
+  a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.clip = clip; a.skip = skip; a.qtable = qtable;
+  a.theta0 = theta0; a.theta = theta; a.theta_bf16 = (__nv_bfloat16*)theta_bf16; a.grad_out = grad_out;
+  a.status = status; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_peers = n_peers;
+  a.n_params = n_params; a.n_bins = n_bins; a.lr = lr; a.weight_decay = weight_decay; a.use_dct = 1;
+  a.update_mode = update_mode; a.val_dtype = val_dtype; a.distinct = 0;
+  for (int i = 0; i < n_peers; ++i) { a.pp.idx[i] = (const uint8_t*)idx_ptrs[i]; a.pp.val[i] = val_ptrs[i]; }
+  cudaError_t err = cudaFuncSetAttribute(aggregate_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_AGG);
+  if (err != cudaSuccess) return (int)err;
+  int grid = tplr_sm_count() * 2;
+  const int n_pairs = (total_chunks + 1) / 2;
+  if (grid > n_pairs) grid = n_pairs;
+  aggregate_tc_kernel<<<grid, NT, TC_SMEM_AGG, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
 

@@ -67,7 +67,7 @@ class TensorParallel:
         self._epoch += 1
         return self._epoch
 
-    def _comm_pairs(self, flops: float, link_bytes: float) -> int:
+    def _comm_pairs(self, flops: float, link_bytes: float, tiles: int) -> int:
         """CTA pairs set aside for the gather.  The tiles of the local shard need no peer data, so the
         peers' rows have to arrive within the remaining (world-1)/world of the GEMM's time; one copier
         CTA sustains about 45 GB/s (160 KB of loads in flight over NVLink), and more than 16 of them
@@ -78,7 +78,11 @@ class TensorParallel:
             return 1
         t_remote = flops / 1.4e15 * (self.world - 1) / self.world
         need_gbs = min(link_bytes / max(t_remote, 1e-6) / 1e9, 720.0)
-        return max(1, min(8, -(-int(need_gbs / 45.0 + 0.999) // 2)))
+        pairs = max(1, min(8, -(-int(need_gbs / 45.0 + 0.999) // 2)))
+        if tiles <= 2 * 74:
+            # a GEMM of at most two waves leaves CTA pairs idle anyway: spend them on the gather
+            pairs = max(pairs, min(12, 74 - -(-tiles // 2)))
+        return pairs
 
     # -- fused kernels ----------------------------------------------------------------------------
     def ag_gemm(self, slot: int, width: int, other: torch.Tensor, *, gathered: str = "A", a_mn: bool = False,
@@ -106,7 +110,8 @@ class TensorParallel:
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             int(a_mn), int(b_mn), epi, 1 if gathered == "A" else 2, self.world, self.rank, self.rows_per_rank,
             native.ptr_array(bases), self._gflags[slot].data_ptr(), ctypes.c_uint(self._next_epoch()),
-            self._comm_pairs(2.0 * M * N * K, (self.world - 1) * self.rows_per_rank * width * 2),
+            self._comm_pairs(2.0 * M * N * K, (self.world - 1) * self.rows_per_rank * width * 2,
+                             -(-M // 256) * -(-N // 256)),
             OF.status_word(self.device).data_ptr(), native.stream_ptr())
         native.check(err, "tplr_gemm2_gather")
         return out

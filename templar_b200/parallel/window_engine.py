@@ -90,6 +90,13 @@ class WindowEngine:
             arr = L.descriptors(rank if world_size > 1 else None, square=square)
             self._desc[square] = (torch.from_numpy(arr.view(np.uint8).reshape(-1).copy()).to(self.device), len(arr),
                                   int(arr["n_chunks"].sum()) if len(arr) else 0)
+        # the tensor-core DCT kernels need every chunk of the square table to be 64 x 64 with 16-byte aligned rows
+        import os
+        sq = L.descriptors(rank if world_size > 1 else None, square=True)
+        self._dct_on_tensor_cores = bool(
+            self.cuda and len(sq) and (sq["h"] == 64).all() and (sq["w"] == 64).all()
+            and (sq["cols"] % 4 == 0).all() and (sq["elem_off"] % 4 == 0).all()
+            and os.environ.get("TPLR_DCT_BACKEND", "tcgen05") == "tcgen05")
         full = L.descriptors(None, square=None)
         self._desc_full = (torch.from_numpy(full.view(np.uint8).reshape(-1).copy()).to(self.device), len(full))
         P = cfg.max_peers
@@ -393,6 +400,16 @@ class WindowEngine:
         for square in (True, False):
             desc, n_desc, n_chunks = self._desc[square]
             if n_chunks == 0:
+                continue
+            if square and cfg.use_dct and self._dct_on_tensor_cores:
+                # every chunk of this table is 64 x 64: inverse DCT as tcgen05 GEMMs against the basis
+                native.check(L.tplr_aggregate_apply_tc(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(), n_peers,
+                                                       native.ptr_array(idx_ptrs), native.ptr_array(val_ptrs), vdt, None, 0,
+                                                       np_, self.clip.data_ptr() if use_clip else None,
+                                                       self.skip.data_ptr() if use_clip else None,
+                                                       base_buf.data_ptr() - bias, st.master_shard.data_ptr() - bias,
+                                                       shadow, None, lr, cfg.outer_weight_decay, mode,
+                                                       self.status.data_ptr(), stream), "aggregate_apply_tc")
                 continue
             native.check(L.tplr_aggregate_apply(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(), n_peers,
                                                 native.ptr_array(idx_ptrs), native.ptr_array(val_ptrs), vdt, None, 0, np_,

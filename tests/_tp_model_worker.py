@@ -22,7 +22,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     heap = SymmetricHeap.create(dev, rank, world, timeout_s=20.0)
-    args = ModelArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, intermediate_size=1024, max_seq_len=256)
+    args = ModelArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1000, intermediate_size=1024, max_seq_len=256)
     B, S = 2, 256
     full = build_model(args, device=dev, dtype=torch.bfloat16, seed=9)
     model = TPLlamaModel(args, rank, world).to(device=dev, dtype=torch.bfloat16)
@@ -43,7 +43,12 @@ def main():
     n_sh, worst = world, 0.0
     for name, p in model.named_parameters():
         f = fg[name].float()
-        if name.endswith(("wq.weight", "wk.weight", "wv.weight", "w1.weight", "w3.weight")) or name in ("tok_embeddings.weight", "output.weight"):
+        if name in ("tok_embeddings.weight", "output.weight"):
+            n = model.vocab_padded // n_sh
+            pad = torch.zeros(model.vocab_padded, f.shape[1], device=f.device)
+            pad[: f.shape[0]] = f
+            f = pad[rank * n:(rank + 1) * n]
+        elif name.endswith(("wq.weight", "wk.weight", "wv.weight", "w1.weight", "w3.weight")):
             n = f.shape[0] // n_sh
             f = f[rank * n:(rank + 1) * n]
         elif name.endswith(("wo.weight", "w2.weight")):
