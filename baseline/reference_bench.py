@@ -198,7 +198,9 @@ def main(a) -> None:
             for n, _ in shapes:
                 idxs = [own[n + "idxs"].to(dev, non_blocking=True)]
                 vals = [own[n + "vals"].to(dev, non_blocking=True)]
-                qps = [own[n + "quant_params"]]
+                # shards gathered from other ranks arrive with their tensors on the sender's GPU; the
+                # reference reads payloads back through its object store with map_location = its device
+                qps = [tuple(x.to(dev) if torch.is_tensor(x) else x for x in own[n + "quant_params"])]
                 for d in peers_host:
                     i, v, qp = d[n]
                     idxs.append(i.to(dev, non_blocking=True))
@@ -238,9 +240,30 @@ def main(a) -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0]), float(t[1]), clocks, loss
 
+    # Watchdog: a collective of the reference path that never completes must not hold the GPUs.  After
+    # TPLR_REF_TIMEOUT seconds (default 300) rank 0 prints the `unavailable` line and every rank leaves.
+    import faulthandler
+    import threading
+
+    limit = float(os.environ.get("TPLR_REF_TIMEOUT", "300"))
+    if os.environ.get("TPLR_REF_DEBUG_DUMP"):
+        faulthandler.dump_traceback_later(float(os.environ["TPLR_REF_DEBUG_DUMP"]), exit=False)
+
+    def _expired():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              f"reference window did not finish within {limit:.0f} s at world_size={world}: "
+                              "a collective of its prepare_gradient_dict/outer_step path never completed"}), flush=True)
+        os._exit(0)
+
+    watchdog = threading.Timer(limit, _expired)
+    watchdog.daemon = True
+    watchdog.start()
     try:
         ms, wall_ms, clocks, loss = asyncio.run(timed(a.steps, a.warmup))
+        watchdog.cancel()
     except Exception as e:  # noqa: BLE001
+        watchdog.cancel()
         if world > 1 and dist.is_initialized():
             dist.destroy_process_group()
         return _unavailable(f"reference window failed: {type(e).__name__}: {e}")

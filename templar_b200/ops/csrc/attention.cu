@@ -310,7 +310,7 @@ TPLR_API int tplr_attention_fwd(const void* qkv, void* out, float* lse, int B, i
 namespace {
 
 constexpr int BWD_SMEM = 6 * TILE_BYTES + 1024;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;                        // TMA warp, MMA warp, 8 softmax warps (2 per TMEM lane quadrant)
 
 struct AttnBwdParams {
   CUtensorMap tmQKV;    // [B*S, C] bf16, box 64 x 128
@@ -364,8 +364,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
     s_abort = 0;
     mbar_init(smem_u32(&bar_kv), 1);
     mbar_init(smem_u32(&bar_qdo_full), 1); mbar_init(smem_u32(&bar_qdo_empty), 1);
-    mbar_init(smem_u32(&bar_sp_full), 1); mbar_init(smem_u32(&bar_pds_full), 4);
-    mbar_init(smem_u32(&bar_dq_full), 1); mbar_init(smem_u32(&bar_s_free), 4);
+    mbar_init(smem_u32(&bar_sp_full), 1); mbar_init(smem_u32(&bar_pds_full), 8);
+    mbar_init(smem_u32(&bar_dq_full), 1); mbar_init(smem_u32(&bar_s_free), 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -431,13 +431,14 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int ch = (warp - 2) >> 2;            // column half (64 columns) this warp works on
     const int r = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const uint32_t sw = (uint32_t)(lane & 7);
-    // this warp's two private 4 KB staging buffers: its own rows of the two halves of the P tile
-    const uint32_t stg0 = sP + (uint32_t)quad * 4096u, stg1 = stg0 + TILE_BYTES / 2;
-    uint32_t n_boxes = 0;
+    // two private 4 KB staging buffers: the bytes of this warp's own rows and column half in the P and dS tiles
+    const uint32_t stg0 = sP + (uint32_t)ch * (TILE_BYTES / 2) + (uint32_t)quad * 4096u;
+    const uint32_t stg1 = sdS + (uint32_t)ch * (TILE_BYTES / 2) + (uint32_t)quad * 4096u;
     bool ok = true;
     for (int t = 0; t < n_it && ok; ++t) {
       const int h = g * group + t / n_i, i = j + t % n_i;
@@ -450,7 +451,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       tcgen05_fence_after();
       const bool diag = i == j;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld32(tS + c * 32 + lane_off, sv);
         tmem_ld32(tdP + c * 32 + lane_off, dv);
@@ -486,15 +487,12 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       if (!ok) break;
       tcgen05_fence_after();
       const int qrow0 = b * p.S + i * BQ + quad * 32;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * ch + cc;
         uint32_t v[32];
         tmem_ld32(tS + c * 32 + lane_off, v);
-        const uint32_t buf = (n_boxes & 1u) ? stg1 : stg0;
-        if (c >= 2) {
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-        }
+        const uint32_t buf = cc ? stg1 : stg0;
         const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
 #pragma unroll
         for (int q8 = 0; q8 < 8; ++q8)
@@ -506,7 +504,6 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
           tma_reduce_add_2d(&p.tmDQ, buf, h * DH + c * 32, qrow0);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
-        ++n_boxes;
       }
       if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // P rows may be rewritten
       tcgen05_fence_before();
@@ -517,19 +514,15 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
     if (ok) {
       tcgen05_fence_after();
       const int orow0 = kvrow0 + quad * 32;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {            // c>>1: 0 = dV, 1 = dK;  c&1: 64-column half
-        const uint32_t tacc = (c >> 1) ? tdK : tdV;
-        const uint32_t buf = (c & 1) ? stg1 : stg0;
-        if (c >= 2) {
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-        }
+#pragma unroll
+      for (int acc = 0; acc < 2; ++acc) {      // 0 = dV, 1 = dK; this warp stores its 64-column half of each
+        const uint32_t tacc = acc ? tdK : tdV;
+        const uint32_t buf = acc ? stg1 : stg0;
         const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t v[32];
-          tmem_ld32(tacc + (c & 1) * 64 + hf * 32 + lane_off, v);
+          tmem_ld32(tacc + ch * 64 + hf * 32 + lane_off, v);
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint32_t pw[4];
@@ -545,7 +538,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&p.tmDQKV, buf, ((c >> 1) ? kcol : vcol) + (c & 1) * 64, orow0);
+          tma_store_2d(&p.tmDQKV, buf, (acc ? kcol : vcol) + ch * 64, orow0);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
