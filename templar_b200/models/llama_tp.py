@@ -22,7 +22,8 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import functional as OF
-from ..parallel.tensor_parallel import TensorParallel, column_parallel_linear, row_parallel_linear
+from ..parallel.tensor_parallel import (TensorParallel, all_gather_rows, column_parallel_linear,
+                                        reduce_scatter_rows, row_parallel_linear)
 from .llama import Attention, FeedForward, LlamaModel, ModelArgs, RMSNorm, TransformerBlock, _Weight
 
 
@@ -104,8 +105,7 @@ class _VocabParallelEmbedding(torch.autograd.Function):
         ids = tokens.reshape(-1) - rank * vl
         mask = (ids >= 0) & (ids < vl)
         part = weight[ids.clamp(0, vl - 1)] * mask.unsqueeze(-1).to(weight.dtype)
-        out = torch.empty(part.shape[0] // world, part.shape[1], dtype=part.dtype, device=part.device)
-        dist.reduce_scatter_tensor(out, part, group=group)
+        out = reduce_scatter_rows(part, rank, world, group)
         ctx.save_for_backward(ids, mask)
         ctx.meta = (world, group, main_grad, weight.shape, weight.dtype)
         return out
@@ -114,8 +114,7 @@ class _VocabParallelEmbedding(torch.autograd.Function):
     def backward(ctx, dout):
         ids, mask = ctx.saved_tensors
         world, group, mg, shape, dtype = ctx.meta
-        full = torch.empty(dout.shape[0] * world, dout.shape[1], dtype=dout.dtype, device=dout.device)
-        dist.all_gather_into_tensor(full, dout.contiguous(), group=group)
+        full = all_gather_rows(dout, world, group)
         sel = mask.nonzero(as_tuple=True)[0]
         if mg is not None:
             mg.index_add_(0, ids[sel], full[sel].to(mg.dtype))

@@ -147,6 +147,78 @@ class TensorParallel:
             raise TimeoutError(f"tensor-parallel kernel gave up waiting for a peer (status {v:#x})")
 
 
+def reduce_scatter_rows(part: torch.Tensor, rank: int, world: int, group=None) -> torch.Tensor:
+    """Sum ``part`` [rows, n] over ranks and return this rank's block of rows/world rows (NCCL: one
+    reduce-scatter; other backends: all-reduce and slice)."""
+    import torch.distributed as dist
+
+    n = part.shape[0] // world
+    if dist.get_backend(group) == "nccl":
+        out = torch.empty(n, part.shape[1], dtype=part.dtype, device=part.device)
+        dist.reduce_scatter_tensor(out, part.contiguous(), group=group)
+        return out
+    full = part.clone()
+    dist.all_reduce(full, group=group)
+    return full[rank * n:(rank + 1) * n].clone()
+
+
+def all_gather_rows(shard: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """Concatenation over ranks of ``shard`` [rows/world, n] along the rows."""
+    import torch.distributed as dist
+
+    parts = [torch.empty_like(shard) for _ in range(world)]
+    dist.all_gather(parts, shard.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
+class CollectiveTensorParallel:
+    """Same interface as :class:`TensorParallel` on ``torch.distributed`` collectives and plain matmuls
+    (any backend, any dtype).  It is the CPU/gloo stand-in for tests of the sharding logic and the
+    library baseline that the fused kernels are compared with."""
+
+    def __init__(self, rows: int, width: int, rank: int, world: int, group=None, device="cpu",
+                 dtype: torch.dtype = torch.float32):
+        self.rows, self.width, self.rank, self.world, self.group = rows, width, rank, world, group
+        self.rows_per_rank = rows // world
+        self.device = torch.device(device)
+        self._g = [torch.zeros(rows * width, dtype=dtype, device=self.device) for _ in range(2)]
+        self._g_next = 0
+
+    def gather_buffer(self, width: int):
+        slot = self._g_next
+        self._g_next ^= 1
+        full = self._g[slot][: self.rows * width].view(self.rows, width)
+        return slot, full, full[self.rank * self.rows_per_rank:(self.rank + 1) * self.rows_per_rank]
+
+    def ag_gemm(self, slot, width, other, *, gathered="A", a_mn=False, b_mn=False, out=None, accumulate=False,
+                out_dtype=None):
+        full = self._g[slot][: self.rows * width].view(self.rows, width)
+        own = full[self.rank * self.rows_per_rank:(self.rank + 1) * self.rows_per_rank].clone()
+        full.copy_(all_gather_rows(own, self.world, self.group))
+        a, b = (full, other) if gathered == "A" else (other, full)
+        A = a.t() if a_mn else a
+        Bt = b if b_mn else b.t()
+        c = A.float() @ Bt.float()
+        if out is None:
+            return c.to(out_dtype or a.dtype)
+        if accumulate:
+            out.add_(c.to(out.dtype))
+        else:
+            out.copy_(c)
+        return out
+
+    def gemm_rs(self, a, b, *, b_mn=False, out=None):
+        part = (a.float() @ (b.float() if b_mn else b.float().t())).to(a.dtype)
+        res = reduce_scatter_rows(part, self.rank, self.world, self.group)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
+
+    def check(self) -> None:
+        return None
+
+
 # --------------------------------------------------------------------------------------------- #
 # autograd pairs
 # --------------------------------------------------------------------------------------------- #

@@ -10,9 +10,9 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def launch(nproc, args, timeout=900):
+def launch(nproc, args, timeout=900, worker="_gloo_worker.py", port=29641):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "_gloo_worker.py"), *map(str, args)]
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, worker), *map(str, args)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, TPLR_LOG_LEVEL="WARNING"))
     lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
     assert r.returncode == 0 and lines, r.stdout[-2000:] + r.stderr[-4000:]
@@ -27,3 +27,14 @@ def test_two_rank_window_and_checkpoint_roundtrip(tmp_path, update):
         assert r["same_weights"] and r["master_roundtrip"] and r["compute_roundtrip"], r
         assert r["ckpt"] == [7, 3] and r["status"] == 0
         assert r["loss0"] > 0 and abs(r["loss1"] - r["loss0"]) > 1e-6       # the outer step moved the model
+
+
+def test_tensor_parallel_sharding_matches_unsharded_model():
+    """Heads, hidden features and the (padded) vocabulary split over 2 ranks: same loss and the same
+    parameter gradients as the unsharded model, with the projections on torch.distributed collectives."""
+    res = launch(2, [], worker="_gloo_tp_worker.py", port=29643)
+    assert len(res) == 2
+    for r in res:
+        assert r["vocab_padded"] == 512
+        assert abs(r["loss"] - r["ref_loss"]) < 1e-4, r
+        assert r["worst_rel"] < 1e-3, r
