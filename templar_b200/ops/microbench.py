@@ -152,9 +152,30 @@ def bench_elementwise(a):
     h = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
     logits = torch.randn(T, V, device="cuda").to(torch.bfloat16)
     labels = torch.randint(0, V, (T,), device="cuda")
+    res = torch.randn(T, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    delta = torch.randn(T, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    wn = torch.ones(D, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    wn.main_grad = torch.zeros(D, device="cuda")
+    hg = h.clone().requires_grad_()
+    dyh = torch.randn(T, F, device="cuda").to(torch.bfloat16)
+    H, hd = D // 128, 128
+    qkv = torch.randn(1, T, 3 * D, device="cuda").to(torch.bfloat16)
+    cos, sin = OF.rope_tables(T, hd, 10000.0, "cuda")
+
+    def add_norm_fwd_bwd():
+        hh, y = OF.add_rmsnorm(res, delta, wn)
+        torch.autograd.backward([hh, y], [x, x])
+
+    def swiglu_fwd_bwd():
+        hg.grad = None
+        OF.swiglu(hg).backward(dyh)
+
     cases = {
         "rmsnorm_fwd": (lambda: OF.rmsnorm(x, w), T * D * 2 * 2),
+        "add_rmsnorm_fwd_bwd": (add_norm_fwd_bwd, T * D * 2 * (4 + 4)),
+        "rope_inplace": (lambda: OF.rope(qkv, cos, sin, 2 * H, hd), T * 2 * D * 2 * 2),
         "swiglu_fwd": (lambda: OF.swiglu(h), T * F * 2 * 3),
+        "swiglu_fwd_bwd": (swiglu_fwd_bwd, T * F * 2 * (3 + 5)),
         "cross_entropy_fwd_bwd": (lambda: OF.cross_entropy(logits.requires_grad_(), labels), T * V * 2 * 3),
     }
     for name, (fn, byts) in cases.items():

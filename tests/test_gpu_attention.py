@@ -24,8 +24,19 @@ def _reference(qkv, H, KV, hd):
     return (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, H * hd)
 
 
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("B,S,H,KV", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 512, 2, 2), (2, 1024, 4, 1)])
-def test_attention_forward_backward(B, S, H, KV):
+def test_attention_forward_backward(B, S, H, KV, variant):
+    """variant 1: 128 query rows per step; variant 2: pipelined transposed backward (64 query rows per step)."""
+    from templar_b200.ops import native
+    assert native.lib().tplr_attention_set_bwd_variant(variant) == 0
+    try:
+        _run_case(B, S, H, KV)
+    finally:
+        native.lib().tplr_attention_set_bwd_variant(1)
+
+
+def _run_case(B, S, H, KV):
     hd = 128
     torch.manual_seed(S + H)
     qkv = torch.randn(B, S, (H + 2 * KV) * hd, device=DEV).to(torch.bfloat16).requires_grad_()
