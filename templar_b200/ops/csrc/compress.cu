@@ -849,6 +849,297 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
   if (tid == 0 && s_abort && a.status) atomicOr(a.status, TPLR_ST_WAIT_TIMEOUT);
 }
 
+// ------------------------------------------------------------------------------------- //
+// Tensor-core path of the compress kernel (all chunks 64 x 64, one shared basis): the forward DCT
+// Y = F X F^T and the dense inverse of the selected coefficients run as tcgen05 GEMMs (same 3-term
+// split, same tile tricks as aggregate_tc_kernel); top-k selection, packing and the error-feedback
+// update stay on the CUDA cores.  Two chunks per step: the 128 threads whose TMEM lanes hold a chunk
+// select for it.  Thread (chunk ch, row rin, column half hf) owns X[rin][32*hf..] and, after the
+// second GEMM, the coefficients Y[32*hf .. 32*hf+31][rin] (the GEMM pair leaves Y transposed).
+// ------------------------------------------------------------------------------------- //
+constexpr int TC_X_BYTES = 128 * 64 * 4;     // fp32 copy of the two chunks (each thread re-reads only its own part)
+constexpr int TC_SMEM_CMP = 3 * TC_A_TILE + 3 * TC_B_TILE + TC_X_BYTES + 1024;
+
+__global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a) {
+  extern __shared__ uint8_t smem_raw_tc[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_tc) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_mma;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ int s_hist[2][256];
+  __shared__ int s_wsum[8];
+  __shared__ int s_bin[2], s_krem[2];
+  __shared__ int s_sel_idx[2][TPLR_TILE];
+  __shared__ float s_sel_val[2][TPLR_TILE];
+  const uint32_t sA = smem_u32(smem), sB = sA + 3 * TC_A_TILE, sX = sB + 3 * TC_B_TILE;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qd = warp & 3, hf = warp >> 2;
+  const int ch = qd >> 1, rin = (qd & 1) * 32 + lane;
+  const int trow = ch * 64 + rin;
+  const int lt = rin + hf * 64;                          // thread index inside the chunk's group of 128
+  const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+  const uint32_t xaddr = sX + (uint32_t)trow * 256u + (uint32_t)hf * 128u;
+  const uint32_t xsw = (uint32_t)(lane & 7);
+  volatile int* abort_flag = &s_abort;
+  int cur_f = -1;
+  uint32_t phase = 0;
+
+  if (tid == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&bar_mma), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(smem_u32(&s_tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tZ = s_tmem_base, tY = s_tmem_base + 64;
+  const int n_pairs = (a.total_chunks + 1) / 2;
+  bool ok = true;
+
+  auto run_gemm = [&](uint32_t tD, bool a_mn, bool b_mn) -> bool {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tcgen05_fence_after();
+      issue_split_gemm(tD, sA, sB, a_mn, b_mn);
+      umma_commit(smem_u32(&bar_mma));
+    }
+    bool o = mbar_wait(smem_u32(&bar_mma), phase, abort_flag);
+    phase ^= 1;
+    o = __syncthreads_and(o);
+    tcgen05_fence_after();
+    return o;
+  };
+
+  for (int q = blockIdx.x; q < n_pairs && ok; q += gridDim.x) {
+    const int c = 2 * q + ch;
+    const bool active = c < a.total_chunks;
+    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, active ? c : a.total_chunks - 1)];
+    const int k = d.k;
+    const int cl = c - d.chunk_begin;
+    const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
+    const long long g0 = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64 + (long long)rin * d.cols + hf * 32;
+    __syncthreads();
+    if (d.fh_off != cur_f) {
+      load_basis_split(a.basis + d.fh_off, sB);
+      cur_f = d.fh_off;
+    }
+    // ---- X = gamma*e + delta: this thread's 32 values; fp32 copy kept in shared memory --------
+    float v[32];
+#pragma unroll
+    for (int q4 = 0; q4 < 8; ++q4) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (active && !a.null_round) {
+        const float4 e = *reinterpret_cast<const float4*>(a.ef + g0 + 4 * q4);
+        float4 dl = *reinterpret_cast<const float4*>(a.theta0 + g0 + 4 * q4);
+        if (a.delta_mode) {
+          const float4 t = *reinterpret_cast<const float4*>(a.theta + g0 + 4 * q4);
+          dl.x -= t.x; dl.y -= t.y; dl.z -= t.z; dl.w -= t.w;
+        }
+        x.x = fmaf(a.gamma, e.x, dl.x); x.y = fmaf(a.gamma, e.y, dl.y);
+        x.z = fmaf(a.gamma, e.z, dl.z); x.w = fmaf(a.gamma, e.w, dl.w);
+      }
+      v[4 * q4] = x.x; v[4 * q4 + 1] = x.y; v[4 * q4 + 2] = x.z; v[4 * q4 + 3] = x.w;
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(xaddr + (((uint32_t)q4 ^ xsw) << 4)), "f"(x.x), "f"(x.y),
+                   "f"(x.z), "f"(x.w) : "memory");
+    }
+    store_split_row(sA, TC_A_TILE, trow, hf, v);
+    if (!(ok = run_gemm(tZ, /*a_mn=*/false, /*b_mn=*/false))) break;          // Z = X F^T
+    {
+      uint32_t r[32];
+      tmem_ld32(tZ + hf * 32 + lane_off, r);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+    }
+    store_split_row(sA + (uint32_t)ch * 8192u, TC_A_TILE, rin, hf, v);
+    if (!(ok = run_gemm(tY, /*a_mn=*/true, /*b_mn=*/false))) break;           // Y^T = Z^T F^T
+    {
+      uint32_t r[32];
+      tmem_ld32(tY + hf * 32 + lane_off, r);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);             // v[e] = Y[32*hf + e][rin]
+    }
+    tcgen05_fence_before();
+    // ---- radix select of the k largest |Y| of each chunk (its 128 threads, 32 keys each) ------
+    unsigned int prefix = 0u, mask = 0u;
+    int krem = k;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      s_hist[0][tid] = 0; s_hist[1][tid] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const unsigned int key = __float_as_uint(v[i]) & 0x7fffffffu;
+        if ((key & mask) == prefix) atomicAdd(&s_hist[ch][(key >> shift) & 255u], 1);
+      }
+      __syncthreads();
+      if (warp < 2) {                                     // warp w scans the histogram of chunk w
+        // every thread of a chunk carries the same (prefix, krem); warp w reads chunk w's from shared memory
+        const int kr = pass == 0 ? k : s_krem[warp];
+        const int hi = 255 - 8 * lane;
+        int sum = 0;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) sum += s_hist[warp][hi - jj];
+        int incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const int excl = incl - sum;
+        int bin = -1, rem = 0;
+        if (excl < kr && kr <= incl) {
+          int run = excl;
+          for (int jj = 0; jj < 8; ++jj) {
+            const int cnt = s_hist[warp][hi - jj];
+            if (run + cnt >= kr) { bin = hi - jj; rem = kr - run; break; }
+            run += cnt;
+          }
+        }
+        __syncwarp();
+        if (bin >= 0) { s_bin[warp] = bin; s_krem[warp] = rem; }
+      }
+      __syncthreads();
+      prefix |= ((unsigned int)s_bin[ch]) << shift;
+      mask |= 255u << shift;
+      krem = s_krem[ch];
+      __syncthreads();
+    }
+    // ---- ordered compaction inside each chunk's four warps -----------------------------------
+    int gcnt = 0, qcnt = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const unsigned int key = __float_as_uint(v[i]) & 0x7fffffffu;
+      gcnt += key > prefix; qcnt += key == prefix;
+    }
+    const int packed = gcnt | (qcnt << 16);
+    int incl = packed;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_wsum[warp] = incl;
+    __syncthreads();
+    int woff = 0;
+    {
+      // warps of chunk ch in order: 2ch, 2ch+1, 2ch+4, 2ch+5
+      const int order[4] = {2 * ch, 2 * ch + 1, 2 * ch + 4, 2 * ch + 5};
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) if (order[jj] != warp && ((order[jj] < warp && (order[jj] >> 2) == (warp >> 2)) || (order[jj] >> 2) < (warp >> 2))) woff += s_wsum[order[jj]];
+    }
+    const int excl = incl - packed + woff;
+    int gb = excl & 0xffff, qb = excl >> 16;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const unsigned int key = __float_as_uint(v[i]) & 0x7fffffffu;
+      int pos = -1;
+      if (key > prefix) { pos = gb + min(qb, krem); ++gb; }
+      else if (key == prefix) { if (qb < krem) pos = gb + qb; ++qb; }
+      if (pos >= 0 && pos < TPLR_TILE) {
+        s_sel_idx[ch][pos] = (hf * 32 + i) * 64 + rin;     // row-major index of Y[32*hf + i][rin]
+        s_sel_val[ch][pos] = v[i];
+      }
+    }
+    __syncthreads();
+    // ---- payload ------------------------------------------------------------------------------
+    if (active) {
+      uint8_t* ip = a.idx_out + d.idx_off + (long long)cl * (k / 2) * 3;
+      float* vp = a.val_out + d.val_off + (long long)cl * k;
+      if (lt < k / 2) {
+        const int i0 = s_sel_idx[ch][2 * lt], i1 = s_sel_idx[ch][2 * lt + 1];
+        ip[3 * lt + 0] = (uint8_t)(i0 & 0xff);
+        ip[3 * lt + 1] = (uint8_t)(((i0 >> 8) & 0xf) | ((i1 & 0xf) << 4));
+        ip[3 * lt + 2] = (uint8_t)((i1 >> 4) & 0xff);
+      }
+      if (lt >= 64 && lt < 64 + k) vp[lt - 64] = s_sel_val[ch][lt - 64];
+    }
+    // ---- residual e <- X - F^T S F with S the selected coefficients ------------------------------
+    float t32[32];
+    if (a.write_residual) {
+      for (int i = tid; i < 3 * TC_A_TILE / 16; i += NT) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+      __syncthreads();
+      if (lt < k) {
+        const int e = s_sel_idx[ch][lt];
+        const int n = e >> 6, jx = e & 63;                 // S[n][jx] goes to row jx, column n of the S^T tile
+        const int row = ch * 64 + jx;
+        const uint32_t addr = (uint32_t)row * 128u + ((((uint32_t)(n >> 3)) ^ (uint32_t)(row & 7)) << 4) + (uint32_t)(n & 7) * 2u;
+        __nv_bfloat16 b1, b2, b3;
+        split3(s_sel_val[ch][lt], b1, b2, b3);
+        *reinterpret_cast<__nv_bfloat16*>(smem + addr) = b1;
+        *reinterpret_cast<__nv_bfloat16*>(smem + TC_A_TILE + addr) = b2;
+        *reinterpret_cast<__nv_bfloat16*>(smem + 2 * TC_A_TILE + addr) = b3;
+      }
+      if (!(ok = run_gemm(tZ, /*a_mn=*/false, /*b_mn=*/true))) break;        // Z' = S^T F
+      {
+        uint32_t r[32];
+        tmem_ld32(tZ + hf * 32 + lane_off, r);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) t32[e] = __uint_as_float(r[e]);
+      }
+      store_split_row(sA + (uint32_t)ch * 8192u, TC_A_TILE, rin, hf, t32);
+      if (!(ok = run_gemm(tY, /*a_mn=*/true, /*b_mn=*/true))) break;         // transmit = Z'^T F
+      uint32_t r[32];
+      tmem_ld32(tY + hf * 32 + lane_off, r);
+      tcgen05_fence_before();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) t32[e] = __uint_as_float(r[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) t32[e] = 0.f;
+    }
+    if (active) {
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        float4 x;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                     : "r"(xaddr + (((uint32_t)q4 ^ xsw) << 4)) : "memory");
+        *reinterpret_cast<float4*>(a.ef + g0 + 4 * q4) =
+            make_float4(x.x - t32[4 * q4], x.y - t32[4 * q4 + 1], x.z - t32[4 * q4 + 2], x.w - t32[4 * q4 + 3]);
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(s_tmem_base) : "memory");
+  }
+  if (tid == 0 && s_abort && a.status) atomicOr(a.status, TPLR_ST_WAIT_TIMEOUT);
+}
+
+}  // namespace
+
+// Same contract as tplr_compress_chunks with use_dct = 1 and one shared basis, for descriptor tables in which
+// every chunk is 64 x 64 (element offsets and column counts multiples of 4).
+TPLR_API int tplr_compress_chunks_tc(const void* descs, int n_desc, int total_chunks, const float* basis,
+                                     float* ef, const float* theta0, const float* theta,
+                                     uint8_t* idx_out, float* val_out, unsigned int* status,
+                                     float gamma, int delta_mode, int null_round, int write_residual, void* stream) {
+  TPLR_ENTER();
+  if (total_chunks <= 0) return 0;
+  CompressArgs a;
+  a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.theta0 = theta0; a.theta = theta;
+  a.idx_out = idx_out; a.val_out = val_out; a.status = status; a.n_desc = n_desc;
+  a.total_chunks = total_chunks; a.gamma = gamma; a.use_dct = 1; a.delta_mode = delta_mode;
+  a.null_round = null_round; a.write_residual = write_residual; a.distinct = 0;
+  cudaError_t err = cudaFuncSetAttribute(compress_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_CMP);
+  if (err != cudaSuccess) return (int)err;
+  int grid = tplr_sm_count() * 2;
+  const int n_pairs = (total_chunks + 1) / 2;
+  if (grid > n_pairs) grid = n_pairs;
+  compress_tc_kernel<<<grid, NT, TC_SMEM_CMP, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+namespace {
 }  // namespace
 
 // Same contract as tplr_aggregate_apply with use_dct = 1 and one shared basis, for descriptor tables in

@@ -97,6 +97,7 @@ class WindowEngine:
             self.cuda and len(sq) and (sq["h"] == 64).all() and (sq["w"] == 64).all()
             and (sq["cols"] % 4 == 0).all() and (sq["elem_off"] % 4 == 0).all()
             and os.environ.get("TPLR_DCT_BACKEND", "tcgen05") == "tcgen05")
+        self._compress_on_tensor_cores = os.environ.get("TPLR_COMPRESS_BACKEND", "tcgen05") == "tcgen05"
         full = L.descriptors(None, square=None)
         self._desc_full = (torch.from_numpy(full.view(np.uint8).reshape(-1).copy()).to(self.device), len(full))
         P = cfg.max_peers
@@ -248,6 +249,13 @@ class WindowEngine:
         for square in (True, False):
             desc, n_desc, n_chunks = self._desc[square]
             if n_chunks == 0:
+                continue
+            if square and cfg.use_dct and self._dct_on_tensor_cores and self._compress_on_tensor_cores:
+                native.check(L.tplr_compress_chunks_tc(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(),
+                                                       self.ef.data_ptr() - bias, self.theta0.data_ptr() - bias,
+                                                       st.master_shard.data_ptr() - bias, idx_ptr, val_ptr,
+                                                       self.status.data_ptr(), cfg.momentum_decay, 1, int(null_round), 1,
+                                                       native.stream_ptr()), "compress_tc")
                 continue
             native.check(L.tplr_compress_chunks(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(),
                                                 self.ef.data_ptr() - bias, self.theta0.data_ptr() - bias,
