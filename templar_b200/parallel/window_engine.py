@@ -290,13 +290,45 @@ class WindowEngine:
             self.own_idx[io: io + idx.numel()].copy_(idx)
             self.own_val[vo: vo + val.numel()].copy_(val.reshape(-1))
 
-    def own_payload(self) -> dict:
+    def own_payload(self, quantize: bool = False, n_bins: int = 256, range_in_sigmas: float = 6.0) -> dict:
         """Reference-format gradient dict (``<name>idxs`` / ``<name>vals`` / ``<name>quant_params``)
-        as views of the flat payload buffers, in named_parameters() order."""
+        as views of the flat payload buffers, in named_parameters() order.
+
+        ``quantize``: values as uint8 codes with the reference's per-tensor ``(shift, scale, offset, lookup,
+        dtype)`` tuples (src/tplr/compress.py:585-636).  On CUDA with an unsharded engine the whole payload is
+        encoded by one group of kernels (``tplr_quantize_values``); otherwise tensor by tensor through
+        :class:`templar_b200.compress.TopKCompressor`."""
+        specs = sorted(self.layout.specs, key=lambda s: s.index)
         out = {}
-        for s in sorted(self.layout.specs, key=lambda s: s.index):
+        if not quantize:
+            for s in specs:
+                idx, val = self.layout.payload_views(self.own_idx, self.own_val, s.name)
+                out[s.name + "idxs"], out[s.name + "vals"], out[s.name + "quant_params"] = idx, val, None
+            return out
+        if self.cuda and self.world_size == 1 and n_bins <= 256:
+            np_ = self.layout.n_params
+            if getattr(self, "_q_codes", None) is None or self._q_table.shape[1] != n_bins + 2:
+                self._q_codes = torch.empty(self.own_val.numel(), dtype=torch.uint8, device=self.device)
+                self._q_table = torch.zeros(np_, n_bins + 2, dtype=torch.float32, device=self.device)
+                self._q_scratch = torch.zeros(np_ * (16 + 2 * n_bins), dtype=torch.float32, device=self.device)
+            desc_full, n_full = self._desc_full
+            native.check(native.lib().tplr_quantize_values(desc_full.data_ptr(), n_full, self.own_val.data_ptr(),
+                                                           self._q_codes.data_ptr(), self._q_table.data_ptr(),
+                                                           self._q_scratch.data_ptr(), np_, n_bins, range_in_sigmas,
+                                                           native.stream_ptr()), "quantize_values")
+            tab = self._q_table.cpu()                       # one small D2H copy for all tensors
+            for s in specs:
+                idx, codes = self.layout.payload_views(self.own_idx, self._q_codes, s.name)
+                row = tab[s.index]
+                out[s.name + "idxs"], out[s.name + "vals"] = idx, codes
+                out[s.name + "quant_params"] = (row[n_bins].clone(), float(row[n_bins + 1]), n_bins // 2,
+                                                row[:n_bins].clone(), torch.float32)
+            return out
+        comp = C.TopKCompressor(use_quantization=True, quantization_bins=n_bins, quantization_range=int(range_in_sigmas))
+        for s in specs:
             idx, val = self.layout.payload_views(self.own_idx, self.own_val, s.name)
-            out[s.name + "idxs"], out[s.name + "vals"], out[s.name + "quant_params"] = idx, val, None
+            q, qp = comp._quantize_values(val.float())
+            out[s.name + "idxs"], out[s.name + "vals"], out[s.name + "quant_params"] = idx, q, qp
         return out
 
     # ------------------------------------------------------------------------------------ #

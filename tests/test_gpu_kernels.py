@@ -276,3 +276,34 @@ def test_model_step_native_vs_torch_reference(backend):
             assert float(rel) < 0.08, (n, float(rel))
     finally:
         OF.set_gemm_backend(prev)
+
+
+def test_payload_value_quantisation_matches_reference_format():
+    """uint8 codes + per-tensor lookup produced by the kernels against the torch implementation of the
+    reference's wire format, tensor by tensor."""
+    from templar_b200 import compress as C
+
+    args = ModelArgs(dim=256, n_layers=1, n_heads=2, vocab_size=512, intermediate_size=512, max_seq_len=128)
+    model = build_model(args, device=DEV, dtype=torch.bfloat16, seed=1)
+    eng = WindowEngine(model, EngineConfig(topk=8), device=DEV)
+    eng.snapshot()
+    eng.store.master_shard.add_(torch.randn_like(eng.store.master_shard) * 1e-3)
+    eng.compress()
+    plain = eng.own_payload()
+    quant = eng.own_payload(quantize=True)
+    comp = C.TopKCompressor(use_quantization=True, quantization_bins=256, quantization_range=6)
+    for s in eng.layout.specs:
+        val = plain[s.name + "vals"].float()
+        q_ref, qp_ref = comp._quantize_values(val)
+        q, qp = quant[s.name + "vals"], quant[s.name + "quant_params"]
+        assert q.dtype == torch.uint8 and q.shape == val.shape
+        assert torch.equal(plain[s.name + "idxs"], quant[s.name + "idxs"])
+        assert abs(float(qp[0]) - float(qp_ref[0])) <= 1e-6 + 1e-4 * abs(float(qp_ref[0]))
+        assert abs(qp[1] - qp_ref[1]) <= 1e-5 * qp_ref[1]
+        assert qp[2] == qp_ref[2]
+        mism = (q.int() - q_ref.int()).abs()
+        assert int(mism.max()) <= 1 and float((mism > 0).float().mean()) < 0.01      # ties at bin edges only
+        deq = comp._dequantize_values(q, qp)
+        deq_ref = comp._dequantize_values(q_ref, qp_ref)
+        assert float((deq.cpu() - deq_ref.cpu()).abs().max()) <= 2.0 * qp_ref[1]
+        assert float((deq.cpu() - val.cpu()).abs().max()) <= 1.01 * qp_ref[1] * 256 / 2 + 1e-6
