@@ -553,7 +553,8 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
   if (!(b_mn ? make_map(&p.tmB, B, N, K, ldb, 64, BK) : make_map(&p.tmB, B, K, N, ldb, BK, CTA_N))) return -103;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
-  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = 8; p.m_rot = 0; p.m_inter = 1; p.k_splits = 1;
+  static const int group_m = [] { const char* e = getenv("TPLR_GEMM_GROUP_M"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
+  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.m_inter = 1; p.k_splits = 1;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
