@@ -601,7 +601,6 @@ using namespace tplr_tc;
 
 constexpr int TC_A_TILE = 128 * 128;          // bytes: 128 rows x 64 bf16
 constexpr int TC_B_TILE = 64 * 128;           // bytes: 64 rows x 64 bf16
-constexpr int TC_SMEM = 3 * TC_A_TILE + 3 * TC_B_TILE + 1024;   // S/Cnt accumulators alias the A tiles + extra
 constexpr int TC_ACC_BYTES = 2 * 4096 * 8;    // two chunks: fp32 sums + int counts = 64 KB
 constexpr int TC_SMEM_AGG = TC_ACC_BYTES + 3 * TC_B_TILE + 1024;
 
@@ -1138,9 +1137,6 @@ TPLR_API int tplr_compress_chunks_tc(const void* descs, int n_desc, int total_ch
   compress_tc_kernel<<<grid, NT, TC_SMEM_CMP, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
-
-namespace {
-}  // namespace
 
 // Same contract as tplr_aggregate_apply with use_dct = 1 and one shared basis, for descriptor tables in
 // which every chunk is 64 x 64 (element offsets and column counts multiples of 4).
