@@ -689,6 +689,7 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
   __shared__ __align__(8) uint64_t bar_mma;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ TplrParamDesc s_desc[2];
   float* S = reinterpret_cast<float*>(smem);                       // [2][4096] sums, later the A tiles
   int* Cnt = reinterpret_cast<int*>(smem + 2 * 4096 * 4);          // [2][4096] contributor counts
   const uint32_t sA = smem_u32(smem), sB = sA + TC_ACC_BYTES;
@@ -717,17 +718,23 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
   const uint32_t tZ = s_tmem_base, tG = s_tmem_base + 64;
   const int n_pairs = (a.total_chunks + 1) / 2;
   bool ok = true;
+  TplrParamDesc d = a.descs[0];
 
   for (int q = blockIdx.x; q < n_pairs && ok; q += gridDim.x) {
     // this thread's chunk of the pair
     const int c = 2 * q + ch;
     const bool active = c < a.total_chunks;
-    TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, active ? c : a.total_chunks - 1)];
+    {
+      // consecutive chunks mostly belong to the same tensor: search the table only when the cached entry misses
+      const int cc = active ? c : a.total_chunks - 1;
+      if (!(cc >= d.chunk_begin && cc < d.chunk_begin + d.n_chunks)) d = a.descs[find_desc(a.descs, a.n_desc, cc)];
+    }
     const int cl = c - d.chunk_begin;
     const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
     const long long base = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64;
     const bool skipped = a.skip && a.skip[d.param_id];
     __syncthreads();                                   // previous pair's tiles and accumulators are free
+    if (rin == 0 && hf == 0) s_desc[ch] = d;           // the scatter below works on both chunks of the pair
     if (d.fh_off != cur_f) {                           // uniform: every 64 x 64 chunk uses the same basis
       load_basis_split(a.basis + d.fh_off, sB);
       cur_f = d.fh_off;
@@ -741,7 +748,7 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
         const int c2 = t / (a.n_peers * pairs), rem = t - c2 * (a.n_peers * pairs);
         const int cc = 2 * q + c2;
         if (cc >= a.total_chunks) continue;
-        const TplrParamDesc d2 = a.descs[find_desc(a.descs, a.n_desc, cc)];
+        const TplrParamDesc& d2 = s_desc[c2];
         if (a.skip && a.skip[d2.param_id]) continue;
         const int cl2 = cc - d2.chunk_begin;
         const int peer = rem / pairs, pr = rem - peer * pairs;
@@ -900,6 +907,7 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
   const int n_pairs = (a.total_chunks + 1) / 2;
   bool ok = true;
 
+  TplrParamDesc d = a.descs[0];
   auto run_gemm = [&](uint32_t tD, bool a_mn, bool b_mn) -> bool {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tcgen05_fence_before();
@@ -919,7 +927,10 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
   for (int q = blockIdx.x; q < n_pairs && ok; q += gridDim.x) {
     const int c = 2 * q + ch;
     const bool active = c < a.total_chunks;
-    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, active ? c : a.total_chunks - 1)];
+    {
+      const int cc = active ? c : a.total_chunks - 1;
+      if (!(cc >= d.chunk_begin && cc < d.chunk_begin + d.n_chunks)) d = a.descs[find_desc(a.descs, a.n_desc, cc)];
+    }
     const int k = d.k;
     const int cl = c - d.chunk_begin;
     const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
