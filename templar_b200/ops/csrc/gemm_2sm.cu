@@ -50,6 +50,7 @@ struct Gemm2Params {
   int n_compute_pairs;               // CTA pairs [0, n_compute_pairs) compute, the rest are comm CTAs
   int group_m;                       // tile order: bands of group_m tile rows, tile row fastest inside a band
   int m_rot;                         // rotation of the tile-row order (in 256-row tiles)
+  int n_rot;                         // rotation of the tile-column order (in 256-column tiles)
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
   int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
   int world, rank;
@@ -155,6 +156,8 @@ __device__ __forceinline__ void tile_coords(const Gemm2Params& p, int t, int til
   if (p.m_inter > 1) tml = (tml % p.m_inter) * (tiles_m / p.m_inter) + tml / p.m_inter;
   tm = tml + p.m_rot;
   if (tm >= tiles_m) tm -= tiles_m;
+  tn += p.n_rot;
+  if (tn >= tiles_n) tn -= tiles_n;
 }
 
 // Epilogue without TMA (C not 16-byte aligned or odd leading dimension): each lane stores its own row.
@@ -554,7 +557,7 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   if (!(b_mn ? make_map(&p.tmB, B, N, K, ldb, 64, BK) : make_map(&p.tmB, B, K, N, ldb, BK, CTA_N))) return -103;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
   static const int group_m = [] { const char* e = getenv("TPLR_GEMM_GROUP_M"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
-  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.m_inter = 1; p.k_splits = 1;
+  p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.n_rot = 0; p.m_inter = 1; p.k_splits = 1;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
@@ -605,6 +608,10 @@ TPLR_API int tplr_gemm2_gather(const void* A, const void* B, void* C, int M, int
   if (!mn && ag_operand == 1) {           // tiles of the local row shard first, then the peers in ring order
     p.group_m = 1;
     p.m_rot = (int)(((long long)rank * rows_per_rank) / TILE_M);
+  }
+  if (!mn && ag_operand == 2) {           // gathered weight rows (FSDP shards): all tile rows of the local columns first
+    p.group_m = (M + TILE_M - 1) / TILE_M;
+    p.n_rot = (int)(((long long)rank * rows_per_rank) / TILE_N);
   }
   return dispatch2(p, a_mn, b_mn, epi, world > 1 ? n_comm_pairs : 0, 0, (cudaStream_t)stream);
 }

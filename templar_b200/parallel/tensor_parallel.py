@@ -147,6 +147,49 @@ class TensorParallel:
             raise TimeoutError(f"tensor-parallel kernel gave up waiting for a peer (status {v:#x})")
 
 
+class GatheredWeight:
+    """A weight [N, K] whose rows are sharded over the ranks (the FSDP layout) and whose all-gather is fused
+    into the first GEMM that consumes it: ``linear(x)`` returns ``x W^T`` while copier CTAs of the same
+    launch pull the peers' row shards into this rank's full-size buffer, tile columns of the local shard
+    first.  After the call the buffer holds the whole weight, so the backward GEMMs of the same layer need
+    no communication.  Replaces FSDP2's per-block all-gather + cuBLAS (the reference's
+    torchtitan models/llama3/infra/parallelize.py:325-375 applied by src/tplr/model_factory.py:286-331)."""
+
+    def __init__(self, heap: SymmetricHeap, n_rows: int, k: int, n_comm_pairs: int | None = None):
+        self.heap, self.rank, self.world = heap, heap.rank, heap.world_size
+        native.require(n_rows % (128 * self.world) == 0, "gathered weight: rows must be a multiple of 128 * world")
+        native.require(n_rows // 128 <= _MAX_CHUNKS and k % 8 == 0, "gathered weight: shape not supported")
+        self.n_rows, self.k, self.rows_per_rank = n_rows, k, n_rows // self.world
+        self.device = heap.device
+        self.n_comm_pairs = n_comm_pairs
+        self._full = heap.alloc(n_rows * k, torch.bfloat16)
+        self.full = self._full.view(n_rows, k)
+        self.own = self.full[self.rank * self.rows_per_rank:(self.rank + 1) * self.rows_per_rank]
+        self._flags = torch.zeros(_MAX_CHUNKS, dtype=torch.int32, device=self.device)
+        self._epoch = 0
+
+    def linear(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``y[M, N] = x[M, K] W^T`` with the gather of W inside the launch (x: bf16, rows contiguous)."""
+        M, K = x.shape
+        native.require(K == self.k, "gathered weight: inner dimensions differ")
+        if out is None:
+            out = torch.empty(M, self.n_rows, dtype=torch.bfloat16, device=self.device)
+        self._epoch += 1
+        link = (self.world - 1) * self.rows_per_rank * K * 2
+        pairs = self.n_comm_pairs
+        if pairs is None:
+            t_remote = 2.0 * M * self.n_rows * K / 1.4e15 * (self.world - 1) / max(self.world, 1)
+            pairs = max(1, min(8, -(-int(min(link / max(t_remote, 1e-6) / 1e9, 720.0) / 45.0 + 0.999) // 2)))
+        self.heap.barrier()
+        bases = [self.heap.peer_ptr(self._full, r) for r in range(self.world)]
+        err = native.lib().tplr_gemm2_gather(
+            x.data_ptr(), self.full.data_ptr(), out.data_ptr(), M, self.n_rows, K, x.stride(0), K, out.stride(0),
+            0, 0, 0, 2, self.world, self.rank, self.rows_per_rank, native.ptr_array(bases), self._flags.data_ptr(),
+            ctypes.c_uint(self._epoch), pairs, OF.status_word(self.device).data_ptr(), native.stream_ptr())
+        native.check(err, "tplr_gemm2_gather")
+        return out
+
+
 def reduce_scatter_rows(part: torch.Tensor, rank: int, world: int, group=None) -> torch.Tensor:
     """Sum ``part`` [rows, n] over ranks and return this rank's block of rows/world rows (NCCL: one
     reduce-scatter; other backends: all-reduce and slice)."""

@@ -8,6 +8,7 @@ Run under torchrun, one process per GPU::
 Cases (shapes of the 18B tensor-parallel preset by default):
   ag_gemm   y[T, F/w]   = all_gather(x)[T, D] W1^T     vs  all_gather_into_tensor + matmul
   gemm_rs   y[T/w, D]   = reduce_scatter(h[T, F/w] W2^T) vs matmul + reduce_scatter_tensor
+  fsdp_ag_gemm y[T, D]  = x[T, D] all_gather(W)[D, D]^T   vs all_gather_into_tensor + matmul (row-sharded weight)
 Times are CUDA-event times on the launching stream, max over ranks, median over iterations; a
 buffer larger than L2 is rewritten between iterations.  Prints one JSON line per case with the
 roofline: the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s.
@@ -25,7 +26,7 @@ import torch.distributed as dist
 from ..ops import functional as OF
 from ..ops.microbench import peaks
 from .symmetric import SymmetricHeap
-from .tensor_parallel import TensorParallel
+from .tensor_parallel import GatheredWeight, TensorParallel
 
 NVLINK_GBS = 770.0   # measured peer-copy bandwidth per direction per GPU
 
@@ -95,17 +96,33 @@ def main():
         torch.matmul(h, w2.t(), out=part)
         dist.reduce_scatter_tensor(y2, part)
 
+    gw = GatheredWeight(heap, D, D, n_comm_pairs=a.comm_pairs or None)
+    w_shard = (torch.randn(D // world, D, device=dev) * 0.02).to(torch.bfloat16)
+    gw.own.copy_(w_shard)
+    xfull = (torch.randn(T, D, device=dev) * 0.5).to(torch.bfloat16)
+    wg = torch.empty(D, D, dtype=torch.bfloat16, device=dev)
+    y3 = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+
+    def fused_fsdp():
+        gw.linear(xfull, out=y3)
+
+    def lib_fsdp():
+        dist.all_gather_into_tensor(wg, w_shard)
+        torch.matmul(xfull, wg.t(), out=y3)
+
     rows = []
     for name, fused, lib, flops, link_bytes in (
+            ("fsdp_ag_gemm", fused_fsdp, lib_fsdp, 2.0 * T * D * D, (world - 1) * (D // world) * D * 2),
             ("ag_gemm", fused_ag, lib_ag, 2.0 * T * fl * D, (world - 1) * tr * D * 2),
             ("gemm_rs", fused_rs, lib_rs, 2.0 * T * D * fl, (world - 1) * tr * D * 2)):
         # correctness of the fused result against the library path on the same inputs
         lib()
-        ref = (y1 if name == "ag_gemm" else y2).float().clone()
-        (y1 if name == "ag_gemm" else y2).zero_()
+        buf = {"ag_gemm": y1, "gemm_rs": y2, "fsdp_ag_gemm": y3}[name]
+        ref = buf.float().clone()
+        buf.zero_()
         fused()
         torch.cuda.synchronize()
-        got = (y1 if name == "ag_gemm" else y2).float()
+        got = buf.float()
         err = ((got - ref).abs().max() / ref.abs().max().clamp_min(1e-6)).item()
         med_f, best_f = _time(fused, a.iters, flush, world)
         med_l, best_l = _time(lib, a.iters, flush, world)

@@ -11,7 +11,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from templar_b200.ops import functional as OF  # noqa: E402
 from templar_b200.parallel.symmetric import SymmetricHeap  # noqa: E402
-from templar_b200.parallel.tensor_parallel import (TensorParallel, column_parallel_linear,  # noqa: E402
+from templar_b200.parallel.tensor_parallel import (GatheredWeight, TensorParallel, column_parallel_linear,  # noqa: E402
                                                    row_parallel_linear)
 
 
@@ -63,6 +63,16 @@ def main():
     out["dx"] = rel(x_shard.grad, Xr.grad[rank * tr:(rank + 1) * tr])
     out["dw1"] = rel(mg1, W1r.grad[rank * fl:(rank + 1) * fl])
     out["dw2"] = rel(mg2, W2r.grad[:, rank * fl:(rank + 1) * fl])
+    # FSDP-style row-sharded weight gathered inside the GEMM that consumes it
+    Wf = (torch.randn(256 * world, D, generator=g) * 0.05).to(dev).to(torch.bfloat16)
+    gw = GatheredWeight(heap, 256 * world, D)
+    gw.own.copy_(Wf[rank * 256:(rank + 1) * 256])
+    xa = X.to(torch.bfloat16)
+    for rep in range(2):
+        yg = gw.linear(xa)
+    torch.cuda.synchronize()
+    out["fsdp_y"] = rel(yg, xa.float() @ Wf.float().t())
+    out["fsdp_w"] = float((gw.full.float() - Wf.float()).abs().max())
     out["status"] = int(OF.status_word(dev).item())
     res = [None] * world
     dist.all_gather_object(res, out)

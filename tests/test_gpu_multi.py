@@ -45,8 +45,9 @@ def test_fused_tensor_parallel_linears():
     res = _run(min(torch.cuda.device_count(), 4) // 2 * 2, worker="_tp_worker.py")
     for r in res:
         assert r["status"] == 0, r
-        for k in ("h", "y", "dx", "dw1", "dw2"):
+        for k in ("h", "y", "dx", "dw1", "dw2", "fsdp_y"):
             assert r[k] < 2e-2, (k, r)
+        assert r["fsdp_w"] == 0.0, r          # the gathered weight buffer is complete after the call
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
