@@ -1,0 +1,51 @@
+"""CPU checks of engine-level helpers that have a GPU fast path elsewhere."""
+
+import torch
+
+from templar_b200 import compress as C
+from templar_b200.models.llama import ModelArgs, build_model
+from templar_b200.parallel.tensor_parallel import TensorParallel
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+
+
+def _engine():
+    args = ModelArgs(dim=128, n_layers=1, n_heads=2, vocab_size=256, intermediate_size=256, max_seq_len=32)
+    model = build_model(args, device="cpu", dtype=torch.float32, seed=2)
+    eng = WindowEngine(model, EngineConfig(topk=8), device="cpu")
+    eng.snapshot()
+    eng.store.master_shard.add_(torch.randn_like(eng.store.master_shard) * 1e-3)
+    eng.compress()
+    return eng
+
+
+def test_own_payload_quantised_roundtrip():
+    """own_payload(quantize=True) is the reference wire format: uint8 codes whose lookup decodes to within one bin."""
+    eng = _engine()
+    plain, quant = eng.own_payload(), eng.own_payload(quantize=True)
+    comp = C.TopKCompressor(use_quantization=True)
+    assert set(plain) == set(quant)
+    for s in eng.layout.specs:
+        q, qp = quant[s.name + "vals"], quant[s.name + "quant_params"]
+        assert q.dtype == torch.uint8 and q.shape == plain[s.name + "vals"].shape
+        assert torch.equal(quant[s.name + "idxs"], plain[s.name + "idxs"])
+        deq = comp._dequantize_values(q, qp)
+        err = (deq - plain[s.name + "vals"].float()).abs().max()
+        assert float(err) <= 1.01 * qp[1] * 128 + 1e-9
+        inner = (q > 0) & (q < 255)                          # values not clamped to the outer bins
+        if inner.any():
+            assert float((deq - plain[s.name + "vals"].float()).abs()[inner].max()) <= 1.01 * qp[1]
+
+
+def test_gather_cta_budget_grows_with_link_pressure():
+    """More copier CTA pairs when the peers' rows must arrive faster; bounded by the link; idle pairs are used."""
+    tp = TensorParallel.__new__(TensorParallel)
+    tp.n_comm_pairs, tp.world = None, 8
+    small = tp._comm_pairs(2.0 * 8192 * 28672 * 8192, 7 * 1024 * 8192 * 2, 4096)       # compute-heavy
+    large = tp._comm_pairs(2.0 * 8192 * 1024 * 8192, 7 * 1024 * 8192 * 2, 128 * 4)     # communication-heavy
+    tiny = tp._comm_pairs(2.0 * 2048 * 3584 * 8192, 7 * 256 * 8192 * 2, 8 * 14)        # two waves: idle pairs copy
+    assert 1 <= small <= large <= 8
+    assert tiny >= large
+    tp.n_comm_pairs = 3
+    assert tp._comm_pairs(1.0, 1.0, 1) == 3
+    tp.n_comm_pairs, tp.world = None, 1
+    assert tp._comm_pairs(1e12, 0.0, 100) == 1
