@@ -241,11 +241,11 @@ def main(a) -> None:
         return float(t[0]), float(t[1]), clocks, loss
 
     # Watchdog: a collective of the reference path that never completes must not hold the GPUs.  After
-    # TPLR_REF_TIMEOUT seconds (default 300) rank 0 prints the `unavailable` line and every rank leaves.
+    # TPLR_REF_TIMEOUT seconds (default 600) rank 0 prints the `unavailable` line and every rank leaves.
     import faulthandler
     import threading
 
-    limit = float(os.environ.get("TPLR_REF_TIMEOUT", "300"))
+    limit = float(os.environ.get("TPLR_REF_TIMEOUT", "600"))
     if os.environ.get("TPLR_REF_DEBUG_DUMP"):
         faulthandler.dump_traceback_later(float(os.environ["TPLR_REF_DEBUG_DUMP"]), exit=False)
 

@@ -256,9 +256,8 @@ def build_model(args: ModelArgs | str, device=None, dtype=None, seed: int | None
     with torch.device(device or "cpu"):
         model = LlamaModel(args)
     if dtype is not None:
-        fc = model.freqs_cis
-        model = model.to(dtype)
-        model.freqs_cis = fc  # complex buffer keeps its dtype
+        # floating-point tensors only: the complex rotary buffer keeps its dtype (checkpoint compatibility)
+        model = model._apply(lambda t: t.to(dtype) if t.is_floating_point() else t)
     if seed is not None:
         model.init_weights(seed)
     return model
