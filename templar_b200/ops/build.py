@@ -78,7 +78,9 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                     print(out, file=sys.stderr)
     lib = lib_path()
     if jobs or not lib.exists():
-        run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"])
+        tmp = lib.with_suffix(".so.tmp")          # link beside the target, then rename: readers never see a partial file
+        run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"])
+        os.replace(tmp, lib)
     return lib
 
 

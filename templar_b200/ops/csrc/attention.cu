@@ -17,6 +17,7 @@
 // Replaces F.scaled_dot_product_attention(is_causal=True) of the reference model
 // (torchtitan models/llama3/model/model.py:203-206, :244-262).
 #include "tcgen05.cuh"
+#include <cuda/std/type_traits>
 #include <stdlib.h>
 
 namespace {
@@ -36,15 +37,6 @@ struct AttnFwdParams {
   float scale_log2;       // softmax scale * log2(e)
   unsigned int* status;
 };
-
-__device__ __forceinline__ void umma_ts_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
@@ -74,6 +66,50 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 __device__ __forceinline__ uint32_t idesc_128x128(bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
+}
+
+// Softmax passes over one row of S (128 fp32 columns in tensor memory, lane = query row).  DIAG = the block
+// on the diagonal (columns above the row are masked); the other blocks run the variant without the per-element
+// compare and select, which is a third of the instructions of the issue-bound softmax warps.
+template <bool DIAG>
+__device__ __forceinline__ float attn_row_max(uint32_t ts_lane, int r) {
+  float mx = -INFINITY;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(ts_lane + c * 32, v);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float x = __uint_as_float(v[e]);
+      if (DIAG) mx = fmaxf(mx, (c * 32 + e > r) ? -INFINITY : x);
+      else      mx = fmaxf(mx, x);
+    }
+  }
+  return mx;
+}
+// P = exp2(S * scale - m) written as packed bf16 over the first 64 columns of S; returns the row sum of P.
+template <bool DIAG>
+__device__ __forceinline__ float attn_row_exp(uint32_t ts_lane, int r, float sl2, float m_used) {
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32], pk[16];
+    tmem_ld32(ts_lane + c * 32, v);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      float p0 = exp2f(fmaf(__uint_as_float(v[2 * e]), sl2, -m_used));
+      float p1 = exp2f(fmaf(__uint_as_float(v[2 * e + 1]), sl2, -m_used));
+      if (DIAG) {
+        if (c * 32 + 2 * e > r) p0 = 0.f;
+        if (c * 32 + 2 * e + 1 > r) p1 = 0.f;
+      }
+      sum0 += p0; sum1 += p1;
+      __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+      pk[e] = *reinterpret_cast<uint32_t*>(&hh);
+    }
+    tmem_st16(ts_lane + c * 16, pk);
+  }
+  return sum0 + sum1;
 }
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
@@ -139,6 +175,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_qk = idesc_128x128(false), id_pv = idesc_128x128(true);
+      const DescBase bQ = desc_base(sQ, 16, 1024), bK = desc_base(sK, 16, 1024), bV = desc_base(sV, TILE_BYTES / 2, 1024);
       bool ok = mbar_wait(smem_u32(&bar_q), 0, abort_flag);
       for (int j = 0; j < nb && ok; ++j) {
         const uint32_t ph = j & 1;
@@ -146,8 +183,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * (TILE_BYTES / 2) + (uint32_t)(kk & 3) * 32u;
-          umma_bf16(tS, make_desc(sQ + off, 16, 1024), make_desc(sK + off, 16, 1024), id_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off = (uint32_t)(kk >> 2) * (TILE_BYTES / 32) + (uint32_t)(kk & 3) * 2u;    // 16-byte units
+          umma_bf16_b(tS, bQ, off, bK, off, id_qk, kk > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&bar_s_full));
         umma_commit(smem_u32(&bar_k_empty));
@@ -156,8 +193,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_ts_bf16(tO, tS + 8 * kk, make_desc(sV + kk * (16 * 128), TILE_BYTES / 2, 1024), id_pv,
-                       (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_bf16_b(tO, tS + 8 * kk, bV, (uint32_t)kk * 128u, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(smem_u32(&bar_v_empty));
         if (j == nb - 1) umma_commit(smem_u32(&bar_o_full));
       }
@@ -174,18 +210,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       if (!ok) break;
       tcgen05_fence_after();
       const bool diag = j == qi;
-      // pass 1: row maximum of the scaled scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32 + lane_off, v);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float x = __uint_as_float(v[e]);
-          mx = fmaxf(mx, (diag && c * 32 + e > r) ? -INFINITY : x);
-        }
-      }
+      // pass 1: row maximum of the scores
+      const float mx = diag ? attn_row_max<true>(tS + lane_off, r) : attn_row_max<false>(tS + lane_off, r);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + RESCALE_THRESHOLD;       // true for the first block (m_used = -inf)
       if (__any_sync(0xffffffffu, need)) {
@@ -203,25 +229,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
           }
         }
       }
-      // pass 2: P = exp2(S * scale - m) as packed bf16 over the first 64 columns of S
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], pk[16];
-        tmem_ld32(tS + c * 32 + lane_off, v);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float p0 = exp2f(fmaf(__uint_as_float(v[2 * e]), p.scale_log2, -m_used));
-          float p1 = exp2f(fmaf(__uint_as_float(v[2 * e + 1]), p.scale_log2, -m_used));
-          if (diag) {
-            if (c * 32 + 2 * e > r) p0 = 0.f;
-            if (c * 32 + 2 * e + 1 > r) p1 = 0.f;
-          }
-          l += p0 + p1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          pk[e] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        tmem_st16(tS + c * 16 + lane_off, pk);
-      }
+      // pass 2: P as packed bf16 over the first 64 columns of S
+      l += diag ? attn_row_exp<true>(tS + lane_off, r, p.scale_log2, m_used)
+                : attn_row_exp<false>(tS + lane_off, r, p.scale_log2, m_used);
       tmem_wait_st();
       tcgen05_fence_before();
       __syncwarp();
@@ -333,13 +343,6 @@ __device__ __forceinline__ uint32_t idesc_bwd(bool a_mn, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
          ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-// descriptors of a 128 x 128 bf16 tile stored as two [128 rows x 128 B] swizzled blocks
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {   // contraction along the 128-byte rows
-  return make_desc(base + (uint32_t)(kk >> 2) * (TILE_BYTES / 2) + (uint32_t)(kk & 3) * 32u, 16, 1024);
-}
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {  // contraction along the tile rows
-  return make_desc(base + (uint32_t)kk * (16 * 128), TILE_BYTES / 2, 1024);
-}
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
@@ -405,6 +408,14 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_kk = idesc_bwd(false, false), id_mm = idesc_bwd(true, true), id_km = idesc_bwd(false, true);
+      // descriptor bases: "k" = contraction along the 128-byte rows, "m" = contraction along the tile rows
+      const DescBase kQ = desc_base(sQ, 16, 1024), kK = desc_base(sK, 16, 1024), kdO = desc_base(sdO, 16, 1024),
+                     kV = desc_base(sV, 16, 1024), kdS = desc_base(sdS, 16, 1024);
+      const DescBase mP = desc_base(sP, TILE_BYTES / 2, 1024), mdO = desc_base(sdO, TILE_BYTES / 2, 1024),
+                     mdS = desc_base(sdS, TILE_BYTES / 2, 1024), mQ = desc_base(sQ, TILE_BYTES / 2, 1024),
+                     mK = desc_base(sK, TILE_BYTES / 2, 1024);
+#define TPLR_KOFF(kk) ((uint32_t)((kk) >> 2) * (TILE_BYTES / 32) + (uint32_t)((kk) & 3) * 2u)
+#define TPLR_MOFF(kk) ((uint32_t)(kk) * 128u)
       bool ok = mbar_wait(smem_u32(&bar_kv), 0, abort_flag);
       for (int t = 0; t < n_it && ok; ++t) {
         const uint32_t ph = t & 1;
@@ -412,21 +423,21 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         if (t > 0 && !(ok = mbar_wait(smem_u32(&bar_s_free), ph ^ 1, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(tS, desc_kmajor(sQ, kk), desc_kmajor(sK, kk), id_kk, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) umma_bf16_b(tS, kQ, TPLR_KOFF(kk), kK, TPLR_KOFF(kk), id_kk, kk > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(tdP, desc_kmajor(sdO, kk), desc_kmajor(sV, kk), id_kk, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) umma_bf16_b(tdP, kdO, TPLR_KOFF(kk), kV, TPLR_KOFF(kk), id_kk, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_sp_full));
         if (!(ok = mbar_wait(smem_u32(&bar_pds_full), ph, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // dV[kv, d] += P^T[kv, q] dO[q, d]
-          umma_bf16(tdV, desc_mnmajor(sP, kk), desc_mnmajor(sdO, kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_b(tdV, mP, TPLR_MOFF(kk), mdO, TPLR_MOFF(kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // dK[kv, d] += dS^T[kv, q] Q[q, d]
-          umma_bf16(tdK, desc_mnmajor(sdS, kk), desc_mnmajor(sQ, kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_b(tdK, mdS, TPLR_MOFF(kk), mQ, TPLR_MOFF(kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // dQ[q, d] = dS[q, kv] K[kv, d]
-          umma_bf16(tS, desc_kmajor(sdS, kk), desc_mnmajor(sK, kk), id_km, kk > 0 ? 1u : 0u);
+          umma_bf16_b(tS, kdS, TPLR_KOFF(kk), mK, TPLR_MOFF(kk), id_km, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_dq_full));
         umma_commit(smem_u32(&bar_qdo_empty));
       }
@@ -450,34 +461,44 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const bool diag = i == j;
+      // P and dS of this warp's two 32-column chunks; the diagonal block runs the variant with the causal mask,
+      // the others the one without the per-element compare (the softmax warps are issue-bound).  dS carries the
+      // softmax scale: d = p * (dp - delta) * scale = p * fma(dp, scale, -delta * scale).
+      const float dls = dl * p.scale;
+      auto chunk_pair = [&](auto DIAG) {
+        constexpr bool kDiag = decltype(DIAG)::value;
 #pragma unroll 1
-      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tS + c * 32 + lane_off, sv);
-        tmem_ld32(tdP + c * 32 + lane_off, dv);
-        const uint32_t prow = sP + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
-        const uint32_t drow = sdS + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
+        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+          uint32_t sv[32], dv[32];
+          tmem_ld32(tS + c * 32 + lane_off, sv);
+          tmem_ld32(tdP + c * 32 + lane_off, dv);
+          const uint32_t prow = sP + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
+          const uint32_t drow = sdS + (uint32_t)(c >> 1) * (TILE_BYTES / 2) + (uint32_t)r * 128u;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t pw[4], dw[4];
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t pw[4], dw[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = c * 32 + q4 * 8 + 2 * e;
-            float p0 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e]), p.scale_log2, -lse2));
-            float p1 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e + 1]), p.scale_log2, -lse2));
-            if (diag) { if (col > r) p0 = 0.f; if (col + 1 > r) p1 = 0.f; }
-            const float d0 = p0 * (__uint_as_float(dv[q4 * 8 + 2 * e]) - dl) * p.scale;
-            const float d1 = p1 * (__uint_as_float(dv[q4 * 8 + 2 * e + 1]) - dl) * p.scale;
-            __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
-            pw[e] = *reinterpret_cast<uint32_t*>(&hp);
-            dw[e] = *reinterpret_cast<uint32_t*>(&hd);
+            for (int e = 0; e < 4; ++e) {
+              float p0 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e]), p.scale_log2, -lse2));
+              float p1 = exp2f(fmaf(__uint_as_float(sv[q4 * 8 + 2 * e + 1]), p.scale_log2, -lse2));
+              if (kDiag) {
+                const int col = c * 32 + q4 * 8 + 2 * e;
+                if (col > r) p0 = 0.f;
+                if (col + 1 > r) p1 = 0.f;
+              }
+              const float d0 = p0 * fmaf(__uint_as_float(dv[q4 * 8 + 2 * e]), p.scale, -dls);
+              const float d1 = p1 * fmaf(__uint_as_float(dv[q4 * 8 + 2 * e + 1]), p.scale, -dls);
+              __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+              pw[e] = *reinterpret_cast<uint32_t*>(&hp);
+              dw[e] = *reinterpret_cast<uint32_t*>(&hd);
+            }
+            const uint32_t off = (((uint32_t)((c & 1) * 4 + q4)) ^ sw) << 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + off), "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(drow + off), "r"(dw[0]), "r"(dw[1]), "r"(dw[2]), "r"(dw[3]) : "memory");
           }
-          const uint32_t off = (((uint32_t)((c & 1) * 4 + q4)) ^ sw) << 4;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + off), "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3]) : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(drow + off), "r"(dw[0]), "r"(dw[1]), "r"(dw[2]), "r"(dw[3]) : "memory");
         }
-      }
+      };
+      if (i == j) chunk_pair(cuda::std::true_type{}); else chunk_pair(cuda::std::false_type{});
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tcgen05_fence_before();
       __syncwarp();
@@ -631,19 +652,9 @@ __device__ __forceinline__ uint32_t idesc_mn(int n, bool a_mn, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-// 64-row tile (Q, dO): two blocks of [64 rows x 128 B]
-__device__ __forceinline__ uint64_t desc64_kmajor(uint32_t base, int kk) {    // contraction along d (row bytes)
-  return make_desc(base + (uint32_t)(kk >> 2) * 8192u + (uint32_t)(kk & 3) * 32u, 16, 1024);
-}
-__device__ __forceinline__ uint64_t desc64_mnmajor(uint32_t base, int kk) {   // contraction along the 64 rows
-  return make_desc(base + (uint32_t)kk * 2048u, 8192, 1024);
-}
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  umma_ts_bf16(tmem_d, tmem_a, desc_b, idesc, accumulate);
 }
 
 __global__ void __launch_bounds__(B2_THREADS, 1)
@@ -721,17 +732,27 @@ attn_bwd2_kernel(const __grid_constant__ AttnBwd2Params p) {
       const uint32_t id_st = idesc_mn(64, false, false);     // S^T, dP^T : K-major A and B, N = 64
       const uint32_t id_dv = idesc_mn(128, false, true);     // dV, dK   : A from TMEM, B N-contiguous, N = 128
       const uint32_t id_dq = idesc_mn(64, true, true);       // dQ^T     : A M-contiguous (K^T), B N-contiguous
+      // descriptor bases, built once ("k": contraction along the 128-byte rows, "m": along the tile rows)
+      const DescBase kK = desc_base(sK, 16, 1024), kV = desc_base(sV, 16, 1024), mK = desc_base(sK, TILE_BYTES / 2, 1024);
+      DescBase kQ[2], kdO[2], mQ[2], mdO[2], mdS[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        kQ[s] = desc_base(sQ0 + s * B2_QTILE, 16, 1024);    kdO[s] = desc_base(sdO0 + s * B2_QTILE, 16, 1024);
+        mQ[s] = desc_base(sQ0 + s * B2_QTILE, 8192, 1024);  mdO[s] = desc_base(sdO0 + s * B2_QTILE, 8192, 1024);
+        mdS[s] = desc_base(sdS0 + s * B2_DS_TILE, 8192, 1024);
+      }
+#define TPLR_K128(kk) ((uint32_t)((kk) >> 2) * (TILE_BYTES / 32) + (uint32_t)((kk) & 3) * 2u)   /* 128-row tile, 16-byte units */
+#define TPLR_K64(kk) ((uint32_t)((kk) >> 2) * 512u + (uint32_t)((kk) & 3) * 2u)                /* 64-row tile */
+#define TPLR_M(kk) ((uint32_t)(kk) * 128u)
       auto issue_st = [&](int t) {                            // S^T(t) = K Q^T into S buffer t & 1
-        const uint32_t q = sQ0 + (t & 1) * B2_QTILE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tS0 + (t & 1) * 64, desc_kmajor(sK, kk), desc64_kmajor(q, kk), id_st, kk > 0 ? 1u : 0u);
+          umma_bf16_b(tS0 + (t & 1) * 64, kK, TPLR_K128(kk), kQ[t & 1], TPLR_K64(kk), id_st, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_s_full[t & 1]));
       };
       auto issue_dp = [&](int t) {                            // dP^T(t) = V dO^T
-        const uint32_t d = sdO0 + (t & 1) * B2_QTILE;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(tdP, desc_kmajor(sV, kk), desc64_kmajor(d, kk), id_st, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) umma_bf16_b(tdP, kV, TPLR_K128(kk), kdO[t & 1], TPLR_K64(kk), id_st, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_dp_full));
       };
       bool ok = mbar_wait(smem_u32(&bar_kv), 0, abort_flag);
@@ -748,22 +769,21 @@ attn_bwd2_kernel(const __grid_constant__ AttnBwd2Params p) {
       for (int t = 0; t < n_it && ok; ++t) {
         const int s = t & 1;
         const uint32_t ph = t & 1;
-        const uint32_t q = sQ0 + s * B2_QTILE, d = sdO0 + s * B2_QTILE, ds = sdS0 + s * B2_DS_TILE;
         if (!(ok = mbar_wait(smem_u32(&bar_p_ready), ph, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)          // dV += P^T dO ; P^T packed at columns 0-15 and 32-47 of the S buffer
-          umma_ts(tdV, tS0 + s * 64 + (kk >> 1) * 32 + (kk & 1) * 8, desc64_mnmajor(d, kk), id_dv, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_bf16_b(tdV, tS0 + s * 64 + (kk >> 1) * 32 + (kk & 1) * 8, mdO[s], TPLR_M(kk), id_dv, (t > 0 || kk > 0) ? 1u : 0u);
         if (!(ok = mbar_wait(smem_u32(&bar_ds_ready), ph, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)          // dK += dS^T Q
-          umma_ts(tdK, tdP + (kk >> 1) * 32 + (kk & 1) * 8, desc64_mnmajor(q, kk), id_dv, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_bf16_b(tdK, tdP + (kk >> 1) * 32 + (kk & 1) * 8, mQ[s], TPLR_M(kk), id_dv, (t > 0 || kk > 0) ? 1u : 0u);
         if (t > 0 && !(ok = mbar_wait(smem_u32(&bar_dq_free), (uint32_t)((t - 1) & 1), abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)          // dQ^T = K^T dS^T
-          umma_bf16(tdQ, desc_mnmajor(sK, kk), make_desc(ds + kk * 2048u, 8192, 1024), id_dq, kk > 0 ? 1u : 0u);
+          umma_bf16_b(tdQ, mK, TPLR_M(kk), mdS[s], TPLR_M(kk), id_dq, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_dq_full));
         umma_commit(smem_u32(&bar_q_empty[s]));
         if (t + 1 < n_it) issue_dp(t + 1);

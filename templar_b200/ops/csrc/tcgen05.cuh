@@ -83,6 +83,37 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// A descriptor whose start address is advanced by adding to its low word (the address field holds
+// bytes >> 4 in bits 0-13, so offsets are given in units of 16 bytes and must not carry past 256 KB).
+// Built once outside the issue loop: the MMA-issuing thread then spends one add per operand instead of
+// rebuilding a 64-bit descriptor for every instruction.
+struct DescBase { uint32_t lo, hi; };
+__device__ __forceinline__ DescBase desc_base(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = make_desc(saddr, lbo_bytes, sbo_bytes);
+  DescBase b; b.lo = (uint32_t)d; b.hi = (uint32_t)(d >> 32);
+  return b;
+}
+__device__ __forceinline__ void umma_bf16_b(uint32_t tmem_d, DescBase a, uint32_t a_off16, DescBase b, uint32_t b_off16,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// same with the A operand in tensor memory
+__device__ __forceinline__ void umma_ts_bf16_b(uint32_t tmem_d, uint32_t tmem_a, DescBase b, uint32_t b_off16, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
