@@ -71,6 +71,31 @@ __device__ __forceinline__ uint32_t idesc_128x128(bool b_mn) {
 // Softmax passes over one row of S (128 fp32 columns in tensor memory, lane = query row).  DIAG = the block
 // on the diagonal (columns above the row are masked); the other blocks run the variant without the per-element
 // compare and select, which is a third of the instructions of the issue-bound softmax warps.
+// packed fp32 pairs (sm_100): one instruction for two lanes of fma / add, and the three-input max
+__device__ __forceinline__ unsigned long long pack_f32x2(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool DIAG>
 __device__ __forceinline__ float attn_row_max(uint32_t ts_lane, int r) {
   float mx = -INFINITY;
@@ -78,11 +103,12 @@ __device__ __forceinline__ float attn_row_max(uint32_t ts_lane, int r) {
   for (int c = 0; c < 4; ++c) {
     uint32_t v[32];
     tmem_ld32(ts_lane + c * 32, v);
+    if (DIAG) {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const float x = __uint_as_float(v[e]);
-      if (DIAG) mx = fmaxf(mx, (c * 32 + e > r) ? -INFINITY : x);
-      else      mx = fmaxf(mx, x);
+      for (int e = 0; e < 32; ++e) mx = fmaxf(mx, (c * 32 + e > r) ? -INFINITY : __uint_as_float(v[e]));
+    } else {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) mx = max3(mx, __uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
     }
   }
   return mx;
@@ -90,26 +116,31 @@ __device__ __forceinline__ float attn_row_max(uint32_t ts_lane, int r) {
 // P = exp2(S * scale - m) written as packed bf16 over the first 64 columns of S; returns the row sum of P.
 template <bool DIAG>
 __device__ __forceinline__ float attn_row_exp(uint32_t ts_lane, int r, float sl2, float m_used) {
-  float sum0 = 0.f, sum1 = 0.f;
+  const unsigned long long sl2x2 = pack_f32x2(__float_as_uint(sl2), __float_as_uint(sl2));
+  const unsigned long long negm = pack_f32x2(__float_as_uint(-m_used), __float_as_uint(-m_used));
+  unsigned long long sum = 0ull;                         // (0.f, 0.f)
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     uint32_t v[32], pk[16];
     tmem_ld32(ts_lane + c * 32, v);
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
-      float p0 = exp2f(fmaf(__uint_as_float(v[2 * e]), sl2, -m_used));
-      float p1 = exp2f(fmaf(__uint_as_float(v[2 * e + 1]), sl2, -m_used));
+      float a0, a1;
+      unpack_f32x2(fma_f32x2(pack_f32x2(v[2 * e], v[2 * e + 1]), sl2x2, negm), a0, a1);
+      float p0 = exp2f(a0), p1 = exp2f(a1);
       if (DIAG) {
         if (c * 32 + 2 * e > r) p0 = 0.f;
         if (c * 32 + 2 * e + 1 > r) p1 = 0.f;
       }
-      sum0 += p0; sum1 += p1;
+      sum = add_f32x2(sum, pack_f32x2(__float_as_uint(p0), __float_as_uint(p1)));
       __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
       pk[e] = *reinterpret_cast<uint32_t*>(&hh);
     }
     tmem_st16(ts_lane + c * 16, pk);
   }
-  return sum0 + sum1;
+  float s0, s1;
+  unpack_f32x2(sum, s0, s1);
+  return s0 + s1;
 }
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
@@ -348,7 +379,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t bar_kv, bar_qdo_full, bar_qdo_empty, bar_sp_full, bar_pds_full, bar_dq_full, bar_s_free;
+  __shared__ __align__(8) uint64_t bar_kv, bar_q_full, bar_q_empty, bar_do_full, bar_do_empty, bar_sp_full, bar_pds_full, bar_dq_full, bar_s_free;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -367,7 +398,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(smem_u32(&bar_kv), 1);
-    mbar_init(smem_u32(&bar_qdo_full), 1); mbar_init(smem_u32(&bar_qdo_empty), 1);
+    mbar_init(smem_u32(&bar_q_full), 1); mbar_init(smem_u32(&bar_q_empty), 1);
+    mbar_init(smem_u32(&bar_do_full), 1); mbar_init(smem_u32(&bar_do_empty), 1);
     mbar_init(smem_u32(&bar_sp_full), 1); mbar_init(smem_u32(&bar_pds_full), 8);
     mbar_init(smem_u32(&bar_dq_full), 1); mbar_init(smem_u32(&bar_s_free), 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -396,13 +428,18 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       for (int t = 0; t < n_it && ok; ++t) {
         const int h = g * group + t / n_i, i = j + t % n_i;
         const int qrow0 = b * p.S + i * BQ, qcol = h * DH;
-        if (!(ok = mbar_wait(smem_u32(&bar_qdo_empty), (uint32_t)((t & 1) ^ 1), abort_flag))) break;
-        const uint32_t fb = smem_u32(&bar_qdo_full);
-        mbar_expect_tx(fb, 2 * TILE_BYTES);
-        tma_load_2d(sQ, &p.tmQKV, fb, qcol, qrow0);
-        tma_load_2d(sQ + TILE_BYTES / 2, &p.tmQKV, fb, qcol + 64, qrow0);
-        tma_load_2d(sdO, &p.tmDO, fb, qcol, qrow0);
-        tma_load_2d(sdO + TILE_BYTES / 2, &p.tmDO, fb, qcol + 64, qrow0);
+        // Q is released by the dK MMAs and dO by the dV MMAs of the previous step, both before its dQ MMAs and the
+        // dQ drain: the next tiles are in flight while those run
+        if (!(ok = mbar_wait(smem_u32(&bar_q_empty), (uint32_t)((t & 1) ^ 1), abort_flag))) break;
+        const uint32_t fq = smem_u32(&bar_q_full);
+        mbar_expect_tx(fq, TILE_BYTES);
+        tma_load_2d(sQ, &p.tmQKV, fq, qcol, qrow0);
+        tma_load_2d(sQ + TILE_BYTES / 2, &p.tmQKV, fq, qcol + 64, qrow0);
+        if (!(ok = mbar_wait(smem_u32(&bar_do_empty), (uint32_t)((t & 1) ^ 1), abort_flag))) break;
+        const uint32_t fd = smem_u32(&bar_do_full);
+        mbar_expect_tx(fd, TILE_BYTES);
+        tma_load_2d(sdO, &p.tmDO, fd, qcol, qrow0);
+        tma_load_2d(sdO + TILE_BYTES / 2, &p.tmDO, fd, qcol + 64, qrow0);
       }
     }
   } else if (warp == 1) {
@@ -419,27 +456,29 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       bool ok = mbar_wait(smem_u32(&bar_kv), 0, abort_flag);
       for (int t = 0; t < n_it && ok; ++t) {
         const uint32_t ph = t & 1;
-        if (!(ok = mbar_wait(smem_u32(&bar_qdo_full), ph, abort_flag))) break;
+        if (!(ok = mbar_wait(smem_u32(&bar_q_full), ph, abort_flag))) break;
         if (t > 0 && !(ok = mbar_wait(smem_u32(&bar_s_free), ph ^ 1, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_bf16_b(tS, kQ, TPLR_KOFF(kk), kK, TPLR_KOFF(kk), id_kk, kk > 0 ? 1u : 0u);
+        if (!(ok = mbar_wait(smem_u32(&bar_do_full), ph, abort_flag))) break;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_bf16_b(tdP, kdO, TPLR_KOFF(kk), kV, TPLR_KOFF(kk), id_kk, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_sp_full));
         if (!(ok = mbar_wait(smem_u32(&bar_pds_full), ph, abort_flag))) break;
         tcgen05_fence_after();
 #pragma unroll
+        for (int kk = 0; kk < 8; ++kk)      // dK[kv, d] += dS^T[kv, q] Q[q, d]   (first: Q is what the next step needs first)
+          umma_bf16_b(tdK, mdS, TPLR_MOFF(kk), mQ, TPLR_MOFF(kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&bar_q_empty));
+#pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // dV[kv, d] += P^T[kv, q] dO[q, d]
           umma_bf16_b(tdV, mP, TPLR_MOFF(kk), mdO, TPLR_MOFF(kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)      // dK[kv, d] += dS^T[kv, q] Q[q, d]
-          umma_bf16_b(tdK, mdS, TPLR_MOFF(kk), mQ, TPLR_MOFF(kk), id_mm, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&bar_do_empty));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)      // dQ[q, d] = dS[q, kv] K[kv, d]
           umma_bf16_b(tS, kdS, TPLR_KOFF(kk), mK, TPLR_MOFF(kk), id_km, kk > 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_dq_full));
-        umma_commit(smem_u32(&bar_qdo_empty));
       }
     }
   } else {
