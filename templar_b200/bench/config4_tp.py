@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--topk", type=int, default=32)
+    ap.add_argument("--activation-checkpointing", action="store_true")
     a = ap.parse_args()
 
     import dataclasses
@@ -56,6 +57,7 @@ def main():
         model = TPLlamaModel(args, rank, world).to(torch.bfloat16)
     model.init_weights(seed=1 + rank, buffer_device=dev)
     model.attach(TensorParallel(heap, rows=B * S, width=args.dim))
+    model.activation_checkpointing = a.activation_checkpointing
     eng = WindowEngine(model, EngineConfig(topk=a.topk, use_dct=True, max_peers=1), device=dev)
     g = torch.Generator().manual_seed(77)                       # every TP rank sees the same tokens
     toks = [torch.randint(0, args.vocab_size, (B, S + 1), generator=g).to(dev) for _ in range(A)]
@@ -99,7 +101,7 @@ def main():
             "loss": float(loss), "peak_mem_gib": mem, "own_kernel_launches": native.launch_count - l0,
             "kernel_status": status, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"micro_batch": B, "seq_len": S, "accum": A, "topk": a.topk, "peers": 1,
-                       "activation_checkpointing": False}}))
+                       "activation_checkpointing": bool(a.activation_checkpointing)}}))
     heap.close()
     dist.destroy_process_group()
 

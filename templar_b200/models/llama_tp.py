@@ -242,7 +242,12 @@ class TPLlamaModel(LlamaModel):
         h = _VocabParallelEmbedding.apply(tokens, self.tok_embeddings.weight, self.tp_rank, self.tp_world, self.group, mg)
         delta = None
         for layer in self.layers.values():
-            h, delta = layer.forward_tp(h, delta, cos, sin, B, S)
+            if self.activation_checkpointing and torch.is_grad_enabled() and delta is not None:
+                # the block is re-run in the backward pass, collectives included (every rank recomputes the same block)
+                from torch.utils.checkpoint import checkpoint
+                h, delta = checkpoint(layer.forward_tp, h, delta, cos, sin, B, S, use_reentrant=False)
+            else:
+                h, delta = layer.forward_tp(h, delta, cos, sin, B, S)
         return OF.add_rmsnorm(h, delta, self.norm.weight, self.norm.eps)[1]
 
     def forward(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:

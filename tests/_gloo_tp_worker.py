@@ -51,7 +51,17 @@ def main():
             n = f.shape[1] // world
             f = f[:, rank * n:(rank + 1) * n]
         worst = max(worst, ((p.grad - f).norm() / (f.norm() + 1e-12)).item())
-    out = {"loss": float(loss), "ref_loss": float(ref), "worst_rel": worst, "vocab_padded": model.vocab_padded}
+    # the same step with activation checkpointing: identical loss and gradients
+    g1 = {n: p.grad.clone() for n, p in model.named_parameters()}
+    for p in model.parameters():
+        p.grad = None
+    model.activation_checkpointing = True
+    loss2 = model.loss(toks[:, :-1], labels)
+    loss2.backward()
+    model.reduce_replicated_grads()
+    ckpt_diff = max(float((p.grad - g1[n]).abs().max()) for n, p in model.named_parameters())
+    out = {"loss": float(loss), "ref_loss": float(ref), "worst_rel": worst, "vocab_padded": model.vocab_padded,
+           "ckpt_loss_diff": abs(float(loss2) - float(loss)), "ckpt_grad_diff": ckpt_diff}
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

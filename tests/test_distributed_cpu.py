@@ -38,3 +38,4 @@ def test_tensor_parallel_sharding_matches_unsharded_model():
         assert r["vocab_padded"] == 512
         assert abs(r["loss"] - r["ref_loss"]) < 1e-4, r
         assert r["worst_rel"] < 1e-3, r
+        assert r["ckpt_loss_diff"] < 1e-6 and r["ckpt_grad_diff"] < 1e-5, r      # activation checkpointing changes nothing
