@@ -680,6 +680,7 @@ class Validator(BaseNode, Trainer):
                                           if not k.endswith("quant_params")})
         else:
             eng.distribute_peer_payloads(sd, n)
+        self.staged_peers = n                       # slot j holds uids[j]: the overlap check reads the slots
         return n
 
     async def score_peers(self, gather_result, n_peers: int) -> list[dict]:

@@ -620,7 +620,18 @@ async def check_uid_index_overlap(neuron, gather_result, window: int, *, overlap
     acc: dict[tuple[int, int], list[float]] = defaultdict(lambda: [0.0, 0.0])
     tot_w = tot = 0.0
     device = neuron.config.device
-    for pname, _ in neuron.model.named_parameters():
+    eng = getattr(neuron, "engine", None)
+    staged = getattr(neuron, "staged_peers", None)
+    if eng is not None and eng.cuda and eng.world_size == 1 and staged == n:
+        # the gathered payloads already sit in the engine's peer slots (slot j = uids[j]): one kernel over the
+        # packed indices gives every pair's overlap
+        m = eng.index_overlap(n).cpu()
+        for i in range(n):
+            for j in range(i + 1, n):
+                acc[(i, j)] = [float(m[i, j]), 1.0]
+                tot_w += float(m[i, j])
+                tot += 1.0
+    for pname, _ in (neuron.model.named_parameters() if not acc else ()):
         idxs_all = getattr(gather_result.state_dict, pname + "idxs", None)
         vals_all = getattr(gather_result.state_dict, pname + "vals", None)
         if idxs_all is None or vals_all is None:

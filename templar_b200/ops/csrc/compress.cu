@@ -1279,4 +1279,67 @@ TPLR_API int tplr_quantize_values(const void* descs, int n_desc, const float* va
   return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------- //
+// Index-overlap check: for every pair of peers (i < j), the number of (chunk, index) selections they share,
+// summed over all chunks of the payload.  One CTA per chunk (grid-stride): a 4096-bit membership bitmap per
+// peer in shared memory, then popcount(AND) per pair.  counts[i * n_peers + j] (i < j) accumulates with 64-bit
+// atomics.  Replaces the per-tensor torch scatter / gather of the reference's check
+// (neurons/validator.py:3860-3990) with one launch over the packed payloads.
+// ------------------------------------------------------------------------------------- //
+__global__ void __launch_bounds__(256) index_overlap_kernel(const TplrParamDesc* __restrict__ descs, int n_desc, int total_chunks,
+                                                            PeerPtrs pp, int n_peers, unsigned long long* __restrict__ counts) {
+  extern __shared__ unsigned int s_bits[];               // [n_peers][128] words, then [n_peers * n_peers] partial counts
+  unsigned int* s_cnt = s_bits + n_peers * 128;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < n_peers * n_peers; i += blockDim.x) s_cnt[i] = 0u;
+  TplrParamDesc d = descs[0];
+  for (int c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+    if (!(c >= d.chunk_begin && c < d.chunk_begin + d.n_chunks)) d = descs[find_desc(descs, n_desc, c)];
+    const int cl = c - d.chunk_begin, pairs = d.k / 2;
+    __syncthreads();
+    for (int i = tid; i < n_peers * 128; i += blockDim.x) s_bits[i] = 0u;
+    __syncthreads();
+    for (int t = tid; t < n_peers * pairs; t += blockDim.x) {
+      const int peer = t / pairs, pr = t - peer * pairs;
+      const uint8_t* ip = pp.idx[peer] + d.idx_off + ((long long)cl * pairs + pr) * 3;
+      const unsigned b0 = ip[0], b1 = ip[1], b2 = ip[2];
+      const unsigned i0 = b0 | ((b1 & 0xfu) << 8), i1 = ((b1 >> 4) & 0xfu) | (b2 << 4);
+      atomicOr(&s_bits[peer * 128 + (i0 >> 5)], 1u << (i0 & 31));
+      atomicOr(&s_bits[peer * 128 + (i1 >> 5)], 1u << (i1 & 31));
+    }
+    __syncthreads();
+    const int n_pairs = n_peers * (n_peers - 1) / 2;
+    for (int q = warp; q < n_pairs; q += blockDim.x / 32) {
+      int i = 0, rem = q;                               // q-th pair (i < j) in row-major order
+      while (rem >= n_peers - 1 - i) { rem -= n_peers - 1 - i; ++i; }
+      const int j = i + 1 + rem;
+      unsigned int n = 0;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) n += __popc(s_bits[i * 128 + lane * 4 + w] & s_bits[j * 128 + lane * 4 + w]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+      if (lane == 0) s_cnt[i * n_peers + j] += n;       // one warp owns a pair for the whole kernel
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < n_peers * n_peers; i += blockDim.x)
+    if (s_cnt[i]) atomicAdd(counts + i, (unsigned long long)s_cnt[i]);
+}
+
+// counts: [n_peers * n_peers] uint64, zeroed by the caller.
+TPLR_API int tplr_index_overlap(const void* descs, int n_desc, int total_chunks, int n_peers,
+                                const void* const* idx_ptrs, unsigned long long* counts, void* stream) {
+  TPLR_ENTER();
+  if (total_chunks <= 0 || n_peers < 2) return 0;
+  if (n_peers > TPLR_MAX_PEERS) return (int)cudaErrorInvalidValue;
+  PeerPtrs pp;
+  for (int i = 0; i < n_peers; ++i) { pp.idx[i] = (const uint8_t*)idx_ptrs[i]; pp.val[i] = nullptr; }
+  const int smem = (n_peers * 128 + n_peers * n_peers) * (int)sizeof(unsigned int);
+  int grid = tplr_sm_count() * 4;
+  if (grid > total_chunks) grid = total_chunks;
+  index_overlap_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>((const TplrParamDesc*)descs, n_desc, total_chunks, pp,
+                                                                 n_peers, counts);
+  return (int)cudaGetLastError();
+}
+
 TPLR_API int tplr_param_desc_size() { return (int)sizeof(TplrParamDesc); }

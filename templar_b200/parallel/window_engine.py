@@ -511,6 +511,23 @@ class WindowEngine:
     # validator: single-peer apply and restore
     # ------------------------------------------------------------------------------------ #
     @torch.no_grad()
+    @torch.no_grad()
+    def index_overlap(self, n_peers: int) -> torch.Tensor:
+        """[n_peers, n_peers] matrix whose (i, j), i < j, entry is the fraction of (chunk, index) selections that
+        the staged peers i and j share over the whole payload (one kernel over the packed indices; CUDA,
+        unsharded engine).  Equals the size-weighted mean over tensors of the per-chunk overlap fraction."""
+        native.require(self.cuda and self.world_size == 1, "index_overlap needs the CUDA engine with all payloads local")
+        ids = list(range(n_peers))
+        idx_ptrs, _ = self._peer_ptrs(ids)
+        counts = torch.zeros(n_peers * n_peers, dtype=torch.int64, device=self.device)
+        desc_full, n_full = self._desc_full
+        total_chunks = sum(s.n_chunks for s in self.layout.specs)
+        native.check(native.lib().tplr_index_overlap(desc_full.data_ptr(), n_full, total_chunks, n_peers,
+                                                     native.ptr_array(idx_ptrs), counts.data_ptr(),
+                                                     native.stream_ptr()), "index_overlap")
+        total = sum(s.n_chunks * s.topk(self.layout.topk) for s in self.layout.specs)
+        return counts.view(n_peers, n_peers).double() / float(total)
+
     def apply_single_peer(self, peer: int, lr: float, median: torch.Tensor | None = None) -> None:
         """theta <- theta0 - lr * decode(peer's payload), the peer's values clipped per tensor to
         ``min(1, median / (norm + 1e-8))`` where ``median`` is the per-tensor median norm over the

@@ -307,3 +307,37 @@ def test_payload_value_quantisation_matches_reference_format():
         deq_ref = comp._dequantize_values(q_ref, qp_ref)
         assert float((deq.cpu() - deq_ref.cpu()).abs().max()) <= 2.0 * qp_ref[1]
         assert float((deq.cpu() - val.cpu()).abs().max()) <= 1.01 * qp_ref[1] * 256 / 2 + 1e-6
+
+
+def test_index_overlap_kernel_matches_bitmap_count():
+    """Pairwise shared (chunk, index) selections of staged peers: kernel over the packed payloads vs torch bitmaps."""
+    from templar_b200.compress import unpack_12bit_indices
+
+    args = ModelArgs(dim=256, n_layers=1, n_heads=2, vocab_size=512, intermediate_size=512, max_seq_len=128)
+    model = build_model(args, device=DEV, dtype=torch.bfloat16, seed=1)
+    eng = WindowEngine(model, EngineConfig(topk=8, max_peers=4), device=DEV)
+    n = 4
+    payloads = [synthetic_payload(eng.layout, 70 + j, device=DEV) for j in range(n)]
+    payloads[2] = (payloads[0][0].clone(), payloads[2][1])          # peer 2 copies peer 0's indices: overlap 1.0
+    for j, pl in enumerate(payloads):
+        eng.load_peer_payload(j, pl)
+    m = eng.index_overlap(n).cpu()
+    assert abs(float(m[0, 2]) - 1.0) < 1e-12
+    shared = torch.zeros(n, n, dtype=torch.float64)
+    total = 0
+    for s in eng.layout.specs:
+        k = s.topk(eng.layout.topk)
+        sets = []
+        for j in range(n):
+            ib, vb = eng.layout.payload_views(payloads[j][0], payloads[j][1], s.name)
+            idx = unpack_12bit_indices(ib, vb.shape).reshape(-1, k)
+            member = torch.zeros(idx.shape[0], 4096, dtype=torch.bool, device=idx.device)
+            member.scatter_(-1, idx, True)
+            sets.append(member)
+        total += sets[0].shape[0] * k
+        for i in range(n):
+            for j in range(i + 1, n):
+                shared[i, j] += float((sets[i] & sets[j]).sum())
+    for i in range(n):
+        for j in range(i + 1, n):
+            assert abs(float(m[i, j]) - shared[i, j] / total) < 1e-9, (i, j)
