@@ -37,6 +37,7 @@ from neurons.trainer import Trainer  # noqa: E402
 from templar_b200.backends.chain import StaticWallet, make_subtensor  # noqa: E402
 from templar_b200.distributed import dist_helper  # noqa: E402
 from templar_b200.metrics import MetricsLogger  # noqa: E402
+from templar_b200.parallel.window_engine import peer_slice  # noqa: E402
 from templar_b200.utils.rating import PlackettLuce  # noqa: E402
 from templar_b200.wandb_ops import initialize_wandb  # noqa: E402
 
@@ -676,8 +677,7 @@ class Validator(BaseNode, Trainer):
         n = int(t.item())
         if eng.world_size == 1:
             for j in range(n):
-                eng.load_peer_payload(j, {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in sd.items()
-                                          if not k.endswith("quant_params")})
+                eng.load_peer_payload(j, peer_slice(sd, j))
         else:
             eng.distribute_peer_payloads(sd, n)
         self.staged_peers = n                       # slot j holds uids[j]: the overlap check reads the slots

@@ -298,8 +298,8 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
         return None
     if engine.world_size == 1:
         for j in range(n_peers):
-            engine.load_peer_payload(j, {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in sd.items()
-                                         if not k.endswith("quant_params")})
+            from .parallel.window_engine import peer_slice
+            engine.load_peer_payload(j, peer_slice(sd, j))
     else:
         engine.distribute_peer_payloads(sd if is_master else None, n_peers)
     if not engine.window_open:

@@ -51,6 +51,11 @@ class EngineConfig:
     val_dtype: torch.dtype = torch.float32
 
 
+def peer_slice(state_dict: dict, j: int) -> dict:
+    """Peer ``j``'s entries of a gathered state dict whose values are per-peer lists."""
+    return {k: (v[j] if isinstance(v, list) else v) for k, v in state_dict.items()}
+
+
 class WindowEngine:
     def __init__(self, model: torch.nn.Module, cfg: EngineConfig, *, device=None, rank: int = 0,
                  world_size: int = 1, group=None, heap=None, compute_dtype: torch.dtype | None = None):
@@ -341,11 +346,27 @@ class WindowEngine:
             for s in self.layout.specs:
                 idx, val = self.layout.payload_views(self.peer_idx[slot], self.peer_val[slot], s.name)
                 idx.copy_(payload[s.name + "idxs"].reshape(-1), non_blocking=non_blocking)
-                val.copy_(payload[s.name + "vals"].reshape(val.shape), non_blocking=non_blocking)
+                val.copy_(self._payload_values(payload, s.name).reshape(val.shape), non_blocking=non_blocking)
             return
         idx_flat, val_flat = payload
         self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
         self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
+
+    @staticmethod
+    def _payload_values(payload: dict, name: str) -> torch.Tensor:
+        """The values of one tensor of a reference-format payload; uint8 codes are decoded with the payload's
+        ``<name>quant_params`` = (shift, scale, offset, lookup, dtype), as the reference does before it
+        decompresses (src/tplr/compress.py:624-644)."""
+        vals = payload[name + "vals"]
+        if vals.dtype != torch.uint8:
+            return vals
+        qp = payload.get(name + "quant_params")
+        if qp is None:
+            raise ValueError(f"{name}vals holds 8-bit codes but the payload has no {name}quant_params")
+        shift, _, _, lookup, _ = qp
+        lookup = torch.as_tensor(lookup).to(vals.device, torch.float32)
+        shift = torch.as_tensor(shift).to(vals.device, torch.float32)
+        return lookup[vals.long()] + shift
 
     def _peer_list(self, n_peers, include_own: bool, peers=None) -> list[int]:
         """Peer ids taking part: ``peers`` when given, else 0..n_peers-1; id -1 denotes this node's own payload."""
@@ -570,7 +591,7 @@ class WindowEngine:
         for s in L.specs:
             i, v = L.payload_views(idx, val, s.name)
             i.copy_(payload[s.name + "idxs"].reshape(-1))
-            v.copy_(payload[s.name + "vals"].reshape(v.shape))
+            v.copy_(self._payload_values(payload, s.name).reshape(v.shape))
         return idx, val
 
     @torch.no_grad()
@@ -583,8 +604,7 @@ class WindowEngine:
             owner, slot = self.slot_of(j)
             if self.heap is not None:
                 if self.rank == 0:
-                    one = {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in state_dict.items()
-                           if not k.endswith("quant_params")}
+                    one = peer_slice(state_dict, j)
                     idx, val = self.pack_payload(one, device=self.device)
                     for src, dst in ((idx, self.peer_idx[slot]), (val, self.peer_val[slot])):
                         native.check(native.lib().tplr_push_copy(
@@ -592,8 +612,7 @@ class WindowEngine:
                             -(-src.numel() * src.element_size() // 16) * 16, native.stream_ptr()), "push_copy")
             else:
                 if self.rank == 0:
-                    one = {k: (v[j] if isinstance(v, (list, tuple)) else v) for k, v in state_dict.items()
-                           if not k.endswith("quant_params")}
+                    one = peer_slice(state_dict, j)
                     idx, val = self.pack_payload(one, device=self.device)
                     self.peer_idx[slot].copy_(idx)
                     self.peer_val[slot].copy_(val)

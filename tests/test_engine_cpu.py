@@ -36,6 +36,31 @@ def test_own_payload_quantised_roundtrip():
             assert float((deq - plain[s.name + "vals"].float()).abs()[inner].max()) <= 1.01 * qp[1]
 
 
+def test_quantised_peer_payload_is_decoded_when_staged():
+    """A peer that sends 8-bit codes (the reference miner's default) lands in the slot as decoded values,
+    through the single-payload path and through the per-peer slice of a gathered state dict."""
+    from templar_b200.parallel.window_engine import peer_slice
+
+    eng = _engine()
+    plain, quant = eng.own_payload(), eng.own_payload(quantize=True)
+    gathered = {k: [v, v] for k, v in quant.items()}
+    eng.load_peer_payload(0, peer_slice(gathered, 1), non_blocking=False)
+    _, val = eng.pack_payload(quant)
+    for s in eng.layout.specs:
+        _, slot_val = eng.layout.payload_views(eng.peer_idx[0], eng.peer_val[0], s.name)
+        _, packed_val = eng.layout.payload_views(eng.peer_idx[0], val, s.name)
+        ref = plain[s.name + "vals"].float().reshape(slot_val.shape)
+        tol = 1.01 * float(quant[s.name + "quant_params"][1]) * 128 + 1e-6
+        assert float((slot_val.float() - ref).abs().max()) <= tol
+        assert torch.equal(packed_val, slot_val)
+    bad = {k: v for k, v in quant.items() if not k.endswith("quant_params")}
+    try:
+        eng.load_peer_payload(0, bad)
+        raise AssertionError("8-bit codes without parameters must be refused")
+    except ValueError:
+        pass
+
+
 def test_gather_cta_budget_grows_with_link_pressure():
     """More copier CTA pairs when the peers' rows must arrive faster; bounded by the link; idle pairs are used."""
     tp = TensorParallel.__new__(TensorParallel)
