@@ -17,5 +17,6 @@ from .hparams import load_hparams  # noqa: E402,F401
 from .logging import P, T, debug, log_with_context, logger, setup_loki_logger, trace_on  # noqa: E402,F401
 from .neurons import *  # noqa: E402,F401,F403
 from .schemas import Bucket, CommsGetResult  # noqa: E402,F401
+from .dataset import DatasetLoader, SubsetLoader  # noqa: E402,F401
 from .sharded_dataset import SharedShardedDataset, ShardedDatasetManager, SyntheticDataset, compute_shard_state  # noqa: E402,F401
 from .sharded_sampler import EvalSampler, MinerSampler  # noqa: E402,F401

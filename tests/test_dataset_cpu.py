@@ -1,0 +1,76 @@
+"""Page-addressed streaming dataset on an in-memory row source (no network)."""
+
+import asyncio
+
+import numpy as np
+
+from templar_b200.dataset import DatasetLoader, MemoryRowSource, SubsetLoader
+
+
+class _Tok:
+    """One token per word (its length), EOS = 0."""
+
+    eos_token_id = 0
+
+    def encode(self, text, truncation=True, max_length=None):
+        ids = [len(w) for w in text.split()]
+        return ids[:max_length] if (truncation and max_length) else ids
+
+
+def _source(n_cfg=3, n_rows=400):
+    rng = np.random.default_rng(0)
+    docs = {f"cfg{c}": [" ".join("x" * int(k) for k in rng.integers(1, 9, size=int(rng.integers(3, 40))))
+                        for _ in range(n_rows)] for c in range(n_cfg)}
+    return MemoryRowSource(docs)
+
+
+def test_next_pages_is_deterministic_and_offset_dependent():
+    src = _source()
+    a = asyncio.run(DatasetLoader.next_pages(offset=5, n_pages=4, seed="miner-7", source=src))
+    b = asyncio.run(DatasetLoader.next_pages(offset=5, n_pages=4, seed="miner-7", source=src))
+    c = asyncio.run(DatasetLoader.next_pages(offset=6, n_pages=4, seed="miner-7", source=src))
+    assert a == b and a != c
+    for cfg, row, split in a:
+        assert cfg in src.docs and split == "train" and 0 <= row < 400 - 1 - 100
+
+
+def test_padded_batches_hold_one_document_per_sequence_group():
+    src, tok = _source(), _Tok()
+    pages = asyncio.run(DatasetLoader.next_pages(0, 2, 3, source=src))
+    ds = asyncio.run(DatasetLoader.create(batch_size=4, sequence_length=16, pages_info=pages, tokenizer=tok,
+                                          source=src))
+    assert ds.get_page_names() == [f"{c}_{r}_{s}" for c, r, s in pages]
+    first = [b.copy() for b in ds]
+    assert first and all(b.shape == (4, 16) and b.dtype == np.int64 for b in first)
+    flat = np.concatenate([b.reshape(-1) for b in first])
+    # documents in page order, each padded with EOS to a multiple of 16 (their own EOS dropped)
+    expect = []
+    for page in pages:
+        for text in asyncio.run(src.rows(page, 100)):
+            body = tok.encode(text, max_length=16)
+            expect += body + [0] * ((-len(body)) % 16)
+    assert np.array_equal(flat, np.asarray(expect[: flat.size]))
+    again = [b.copy() for b in ds]                       # a second pass replays the same documents
+    assert len(again) == len(first) and all(np.array_equal(x, y) for x, y in zip(first, again))
+
+
+def test_packed_batches_join_documents_with_one_eos():
+    tok = _Tok()
+    sl = SubsetLoader(batch_size=2, sequence_length=8, tokenizer=tok, pack_samples=True)
+    sl.add_documents([[1, 2, 3], [4, 5, 0], [6] * 9, [7] * 20])
+    out = np.concatenate([b.reshape(-1) for b in sl])
+    stream = [1, 2, 3, 0, 4, 5, 0] + [6] * 9 + [0] + [7] * 20 + [0]
+    assert out.size == 32 and np.array_equal(out, np.asarray(stream[:32]))
+    assert sl._get_pad_size([1, 2, 3]) == 1
+    sl.pack_samples = False
+    assert sl._get_pad_size([1] * 8) == 0 and sl._get_pad_size([1] * 9) == 7
+
+
+def test_random_pages_and_raw_rows():
+    src, tok = _source(), _Tok()
+    ds = asyncio.run(DatasetLoader.create(batch_size=2, sequence_length=8, num_pages=2, tokenizer=tok, source=src))
+    assert len(ds.pages) == 2 and len(ds.buffer) > 0
+    rows = asyncio.run(ds.fetch_data_to_rows(3))
+    assert len(rows) == 300 and all(isinstance(r, str) for r in rows)
+    cfgs = asyncio.run(DatasetLoader.fetch_dataset_configs(source=src))
+    assert cfgs == {f"cfg{c}": {"num_rows": 400, "split": "train"} for c in range(3)}
