@@ -39,6 +39,7 @@ from templar_b200.distributed import dist_helper  # noqa: E402
 from templar_b200.metrics import MetricsLogger  # noqa: E402
 from templar_b200.parallel.window_engine import peer_slice  # noqa: E402
 from templar_b200.utils.rating import PlackettLuce  # noqa: E402
+from templar_b200.utils.tree import map_tensors, tensor_bytes, to_pinned_cpu  # noqa: E402
 from templar_b200.wandb_ops import initialize_wandb  # noqa: E402
 
 N_UIDS = 256
@@ -635,6 +636,7 @@ class Validator(BaseNode, Trainer):
                 await self.slash_for_poor_sync()
                 self.slash_for_missing_gradients(list(gather_result.skipped_uids), float(gather_result.success_rate))
                 self.note_delivered(list(gather_result.uids))
+                self.offload_gather_results(gather_result, log=False)
             scored = await self.score_peers(gather_result, n_peers)
             if self.is_master:
                 self.apply_negative_evaluation_penalties()
@@ -665,6 +667,41 @@ class Validator(BaseNode, Trainer):
                                             "n_gathered": len(out["gathered"])}, with_system_metrics=True, with_gpu_metrics=True)
         dist_helper.safe_barrier("validator_end_window", self.local_rank)
         return out
+
+    def offload_gather_results(self, gather_result, *, log: bool = True) -> None:
+        """Move the gathered state dict to pinned host memory (reference neurons/validator.py:92-156).  The
+        engine keeps its own packed copy of every staged peer in device slots, so after ``_stage_gather``
+        the dict is only needed again for uploads and per-UID bookkeeping."""
+        if gather_result is None or not getattr(self.hparams, "offload_gather_results", True):
+            return
+        state = getattr(gather_result, "state_dict", None)
+        if state is None or getattr(gather_result, "_offloaded", None) == "cpu":
+            return
+        t0 = time.time()
+        on_device = tensor_bytes(map_tensors(state, lambda t: t)) if log else 0
+        map_tensors(state, to_pinned_cpu)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        gather_result._offloaded = "cpu"
+        if log:
+            tplr.logger.info(f"[GatherOffload] gathered payloads -> pinned host | {on_device / 1e6:.1f} MB "
+                             f"in {time.time() - t0:.3f}s")
+
+    def load_gather_results_to_device(self, gather_result, device, *, log: bool = True) -> None:
+        """Inverse of :meth:`offload_gather_results` (reference neurons/validator.py:158-219)."""
+        if gather_result is None or getattr(gather_result, "_offloaded", None) != "cpu":
+            return
+        state = getattr(gather_result, "state_dict", None)
+        if state is None:
+            return
+        device, t0 = torch.device(device), time.time()
+        map_tensors(state, lambda t: t if t.device == device else t.to(device, non_blocking=True))
+        if device.type == "cuda":
+            torch.cuda.synchronize(device)
+        gather_result._offloaded = None
+        if log:
+            tplr.logger.info(f"[GatherOffload] gathered payloads -> {device.type} | "
+                             f"{tensor_bytes(state) / 1e6:.1f} MB in {time.time() - t0:.3f}s")
 
     def _stage_gather(self, gather_result) -> int:
         """Put the gathered payloads into the engine's device slots (all ranks); returns the peer count."""

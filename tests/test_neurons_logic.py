@@ -273,3 +273,29 @@ def test_handle_checkpoint_catchup_replays_scheduler(monkeypatch):
     sched.n = 0
     run(tplr.handle_checkpoint_catchup(inst, True, 20, 6, False))
     assert sched.n == 6 and inst.warmup_steps_taken == 2
+
+
+def test_validator_gather_offload_round_trip():
+    """offload / reload of a gathered state dict keeps values and structure (lists, tuples with non-tensor leaves)."""
+    from neurons.validator import Validator
+
+    v = Validator.__new__(Validator)
+    v.hparams = SimpleNamespace(offload_gather_results=True)
+    lookup = torch.arange(4.0)
+    sd = SimpleNamespace(**{"w.idxs": [torch.arange(6, dtype=torch.uint8), torch.ones(6, dtype=torch.uint8)],
+                            "w.vals": [torch.randn(4), torch.randn(4)],
+                            "w.quant_params": [(0.5, 0.1, 128, lookup, torch.float32), None]})
+    keep = [t.clone() for t in sd.__dict__["w.vals"]]
+    res = SimpleNamespace(state_dict=sd, uids=[3, 4])
+    v.offload_gather_results(res, log=False)
+    assert res._offloaded == "cpu" and res.state_dict is sd
+    assert all(t.device.type == "cpu" for t in sd.__dict__["w.vals"])
+    qp = sd.__dict__["w.quant_params"]
+    assert qp[1] is None and qp[0][0] == 0.5 and qp[0][4] is torch.float32 and torch.equal(qp[0][3], lookup)
+    v.offload_gather_results(res, log=False)                       # second call is a no-op
+    v.load_gather_results_to_device(res, torch.device("cpu"), log=False)
+    assert res._offloaded is None
+    assert all(torch.equal(a, b) for a, b in zip(sd.__dict__["w.vals"], keep))
+    v.hparams.offload_gather_results = False
+    v.offload_gather_results(res, log=False)
+    assert res._offloaded is None
