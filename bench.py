@@ -39,6 +39,9 @@ def parse():
     ap.add_argument("--peers", type=int, default=8)
     ap.add_argument("--topk", type=int, default=32)
     ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
+    ap.add_argument("--values", default="fp32", choices=["fp32", "uint8"],
+                    help="wire format of this node's payload values: fp32, or the reference miner's 8-bit codes "
+                         "(256 bins, 6 sigma) with the quantisation error kept in the error feedback")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--breakdown", action="store_true",
@@ -116,7 +119,8 @@ def run_ours(a):
         OF.set_gemm_backend(a.gemm)
     args = PRESETS[a.model]
     model = build_model(args, device=dev, dtype=torch.bfloat16, seed=0)
-    cfg = EngineConfig(topk=a.topk, use_dct=True, outer_update=a.outer_update, max_peers=a.peers)
+    cfg = EngineConfig(topk=a.topk, use_dct=True, outer_update=a.outer_update, max_peers=a.peers,
+                       quantize=a.values == "uint8", quant_bins=256, quant_range=6.0)
     eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
     L = eng.layout
     B, S, A = a.micro_batch, a.seq_len, a.accum
@@ -243,7 +247,7 @@ def run_ours(a):
                           "global_batch": B * A * world, "micro_batch": B, "accum": A, "seq_len": S,
                           "parallelism": f"zero-shard{world}" if world > 1 else "single",
                           "peers": a.peers, "topk": a.topk, "use_dct": True, "outer_update": a.outer_update,
-                          "payload_values": "fp32", "l2": "inputs larger than L2 (2.4 GB bf16 weights, 134 MB activations per layer)"}}
+                          "payload_values": a.values, "l2": "inputs larger than L2 (2.4 GB bf16 weights, 134 MB activations per layer)"}}
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -1280,6 +1280,119 @@ TPLR_API int tplr_quantize_values(const void* descs, int n_desc, const float* va
 }
 
 // ------------------------------------------------------------------------------------- //
+// Error feedback under quantisation.  The reference subtracts from the error feedback what a receiver will
+// decode, i.e. the *dequantised* top-k values (src/tplr/neurons.py:157-171), so the quantisation error stays
+// in the buffer and is sent later.  compress_kernel has already subtracted the exact values; this kernel
+// adds back decode(v - deq(v)) per chunk (a rank-k product against the DCT basis, as in compress_kernel's
+// residual) and overwrites the stored values with deq(v), so that the node's own payload is applied with the
+// numbers every receiver sees.  idx / val / codes / table may live in a peer's memory (plain loads/stores).
+// ------------------------------------------------------------------------------------- //
+struct RequantArgs {
+  const TplrParamDesc* descs;
+  const float* basis;
+  float* ef;
+  const uint8_t* idx;
+  float* val;
+  const uint8_t* codes;
+  const float* table;
+  int n_desc, total_chunks, n_bins, use_dct, distinct;
+};
+
+__global__ void __launch_bounds__(NT, 2) requant_residual_kernel(const RequantArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  float* Y = smem;
+  float* U = Y + TPLR_TILE_ELEMS;
+  float* Fh = U + TPLR_TILE_ELEMS;
+  float* Fht = Fh + TPLR_TILE_ELEMS;
+  float* Fw = a.distinct ? Fht + TPLR_TILE_ELEMS : Fh;
+  float* Fwt = a.distinct ? Fw + TPLR_TILE_ELEMS : Fht;
+  __shared__ int s_idx[TPLR_TILE];
+  __shared__ float s_diff[TPLR_TILE];
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  int cur_fh = -1, cur_fw = -1;
+  for (int c = blockIdx.x; c < a.total_chunks; c += gridDim.x) {
+    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, c)];
+    const int h = d.h, w = d.w, k = d.k;
+    const int cl = c - d.chunk_begin;
+    const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
+    const long long base = d.elem_off + (long long)cy * h * d.cols + (long long)cx * w;
+    __syncthreads();  // previous chunk's shared memory fully consumed
+    if (a.use_dct && (d.fh_off != cur_fh || d.fw_off != cur_fw)) {
+      load_basis(a.basis + d.fh_off, h, Fh, Fht);
+      if (a.distinct) load_basis(a.basis + d.fw_off, w, Fw, Fwt);
+      cur_fh = d.fh_off;
+      cur_fw = d.fw_off;
+    }
+    if (tid < k) {
+      const uint8_t* ip = a.idx + d.idx_off + ((long long)cl * (k / 2) + (tid >> 1)) * 3;
+      const unsigned b0 = ip[0], b1 = ip[1], b2 = ip[2];
+      const int e = (tid & 1) ? (int)(((b1 >> 4) & 0xfu) | (b2 << 4)) : (int)(b0 | ((b1 & 0xfu) << 8));
+      const long long vi = d.val_off + (long long)cl * k + tid;
+      const float* row = a.table + (long long)d.param_id * (a.n_bins + 2);
+      const float v = a.val[vi];
+      const float deq = row[min((int)a.codes[vi], a.n_bins - 1)] + row[a.n_bins];
+      a.val[vi] = deq;
+      s_idx[tid] = min(e, h * w - 1);
+      s_diff[tid] = v - deq;
+    }
+    __syncthreads();
+    if (!a.use_dct) {
+      if (tid < k) {
+        const int e = s_idx[tid];
+        a.ef[base + (long long)(e / w) * d.cols + (e % w)] += s_diff[tid];
+      }
+      continue;
+    }
+    for (int i = tid; i < k * LD; i += NT) {
+      const int j = i >> 6, r = i & 63;
+      const int e = s_idx[j];
+      Y[i] = Fh[(e / w) * LD + r];
+      U[i] = s_diff[j] * Fw[(e % w) * LD + r];
+    }
+    __syncthreads();
+    float acc[4][4];
+    mm_tile(Y, U, k, acc);
+    const bool vec = (w == 64) && ((d.cols & 3) == 0) && ((base & 3) == 0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * ty + i;
+      if (r >= h) continue;
+      const long long g0 = base + (long long)r * d.cols + 4 * tx;
+      if (vec) {
+        float4 x = *reinterpret_cast<const float4*>(a.ef + g0);
+        x.x += acc[i][0]; x.y += acc[i][1]; x.z += acc[i][2]; x.w += acc[i][3];
+        *reinterpret_cast<float4*>(a.ef + g0) = x;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (4 * tx + j < w) a.ef[g0 + j] += acc[i][j];
+      }
+    }
+  }
+}
+
+// descs: the launch's chunk table (same as for tplr_compress_chunks); ef biased like there; table as written by
+// tplr_quantize_values.  Chunks must be disjoint between concurrent launches (they update ef and val in place).
+TPLR_API int tplr_requant_residual(const void* descs, int n_desc, int total_chunks, const float* basis, float* ef,
+                                   const uint8_t* idx, float* val, const uint8_t* codes, const float* table,
+                                   int n_bins, int use_dct, int distinct, void* stream) {
+  TPLR_ENTER();
+  if (total_chunks <= 0) return 0;
+  if (n_bins <= 0 || n_bins > 256) return (int)cudaErrorInvalidValue;
+  RequantArgs a;
+  a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.idx = idx; a.val = val; a.codes = codes;
+  a.table = table; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_bins = n_bins; a.use_dct = use_dct;
+  a.distinct = distinct;
+  const int smem = (distinct ? 6 : 4) * TPLR_TILE_ELEMS * (int)sizeof(float);
+  cudaError_t err = cudaFuncSetAttribute(requant_residual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return (int)err;
+  int grid = tplr_sm_count() * 2;
+  if (grid > total_chunks) grid = total_chunks;
+  requant_residual_kernel<<<grid, NT, smem, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
 // Index-overlap check: for every pair of peers (i < j), the number of (chunk, index) selections they share,
 // summed over all chunks of the payload.  One CTA per chunk (grid-stride): a 4096-bit membership bitmap per
 // peer in shared memory, then popcount(AND) per pair.  counts[i * n_peers + j] (i < j) accumulates with 64-bit

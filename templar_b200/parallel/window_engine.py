@@ -49,6 +49,9 @@ class EngineConfig:
     max_grad_norm: float = 1.0
     max_peers: int = 8
     val_dtype: torch.dtype = torch.float32
+    quantize: bool = False             # 8-bit value codes on the wire (the reference miner's format)
+    quant_bins: int = 256
+    quant_range: float = 6.0
 
 
 def peer_slice(state_dict: dict, j: int) -> dict:
@@ -267,12 +270,66 @@ class WindowEngine:
                                                 st.master_shard.data_ptr() - bias, idx_ptr, val_ptr,
                                                 self.status.data_ptr(), cfg.momentum_decay, int(cfg.use_dct), 1,
                                                 int(null_round), 1, int(not square), native.stream_ptr()), "compress")
+        if cfg.quantize:
+            self._quantize_own(on_rank0=own_slot_ptrs is not None)
+
+    def _quant_buffers(self, n_bins: int | None = None):
+        """codes [val_elems] uint8, table [n_params, bins + 2] fp32 (lookup | shift | scale), scratch."""
+        nb, np_ = (self.cfg.quant_bins if n_bins is None else n_bins), self.layout.n_params
+        if getattr(self, "_q_codes", None) is None or self._q_table.shape[1] != nb + 2:
+            z = lambda n, dt: (self.heap.alloc(n, dt) if self.heap is not None
+                               else torch.zeros(n, dtype=dt, device=self.device))
+            self._q_codes = z(self.layout.val_elems, torch.uint8)
+            self._q_table = z(np_ * (nb + 2), torch.float32).view(np_, nb + 2)
+            self._q_scratch = torch.zeros(np_ * (16 + 2 * nb), dtype=torch.float32, device=self.device)
+        return self._q_codes, self._q_table, self._q_scratch
+
+    def _quantize_own(self, on_rank0: bool) -> None:
+        """Encode the node's payload values as 8-bit codes with per-tensor tables (``tplr_quantize_values``),
+        add the quantisation error back into the error feedback and leave the dequantised values in the
+        payload, which is what the reference's miner does by decompressing with its quantisation parameters
+        before it forms the residual (src/tplr/neurons.py:157-171).
+
+        Sharded: every rank has written its chunks into rank 0's payload (``on_rank0``); rank 0 encodes the
+        whole payload (the statistics are per tensor), then every rank corrects its own chunks, reading the
+        codes and tables from rank 0's memory."""
+        cfg, st = self.cfg, self.store
+        native.require(cfg.quant_bins <= 256, "at most 256 quantisation bins")
+        native.require(self.world_size == 1 or (on_rank0 and self.heap is not None),
+                       "a sharded engine quantises the payload assembled in rank 0's symmetric buffers")
+        codes, table, scratch = self._quant_buffers()
+        L = native.lib()
+        if self.world_size > 1:
+            self._barrier()                        # every rank's chunks have landed on rank 0
+        if self.rank == 0:
+            desc_full, n_full = self._desc_full
+            native.check(L.tplr_quantize_values(desc_full.data_ptr(), n_full, self.own_val.data_ptr(), codes.data_ptr(),
+                                                table.data_ptr(), scratch.data_ptr(), self.layout.n_params,
+                                                cfg.quant_bins, float(cfg.quant_range), native.stream_ptr()),
+                         "quantize_values")
+        if self.world_size > 1:
+            self._barrier()                        # codes and tables are complete
+        at0 = (lambda t: self.heap.peer_ptr(t, 0)) if self.world_size > 1 else (lambda t: t.data_ptr())
+        bias = st.lo * 4
+        for square in (True, False):
+            desc, n_desc, n_chunks = self._desc[square]
+            if n_chunks == 0:
+                continue
+            native.check(L.tplr_requant_residual(desc.data_ptr(), n_desc, n_chunks, self.basis.data_ptr(),
+                                                 self.ef.data_ptr() - bias, at0(self.own_idx), at0(self.own_val),
+                                                 at0(codes), at0(table), cfg.quant_bins, int(cfg.use_dct),
+                                                 int(not square), native.stream_ptr()), "requant_residual")
 
     def _compress_torch(self, null_round: bool) -> None:
         """CPU oracle path: the same arithmetic through :mod:`templar_b200.compress`, tensor by tensor."""
         cfg, st, L = self.cfg, self.store, self.layout
+        if cfg.quantize and self.world_size > 1:
+            raise NotImplementedError("the CPU path quantises whole tensors: run it unsharded")
         tr = C.ChunkingTransformer(None, cfg.target_chunk)
-        comp = C.TopKCompressor(use_quantization=False)
+        comp = C.TopKCompressor(use_quantization=cfg.quantize, quantization_bins=cfg.quant_bins,
+                                quantization_range=int(cfg.quant_range))
+        if cfg.quantize:
+            codes, table, _ = self._quant_buffers()
         for s, r0, nrows in (L.shard_entries(self.rank) if self.world_size > 1
                              else [(s, 0, s.chunk_rows) for s in L.specs]):
             a = s.offset + r0 * s.h * s.cols - st.lo
@@ -285,24 +342,38 @@ class WindowEngine:
             else:
                 e.mul_(cfg.momentum_decay).add_((self.theta0[a:b] - st.master_shard[a:b]).view(shape))
             enc = tr.encode(e, use_dct=cfg.use_dct)
-            idx, val, xshape, totalk = comp.compress(enc, cfg.topk)
-            dec = tr.decode(comp.decompress(e, idx, val, xshape, totalk), use_dct=cfg.use_dct)
+            out = comp.compress(enc, cfg.topk)
+            idx, val, xshape, totalk = out[:4]
+            qp = out[4] if len(out) == 5 else None
+            dec = tr.decode(comp.decompress(e, idx, val, xshape, totalk, qp), use_dct=cfg.use_dct)
             e.sub_(dec)
             k = s.topk(cfg.topk)
             c0 = r0 * s.chunks_x
             io = L.idx_off[s.name] + c0 * (k // 2) * 3
             vo = L.val_off[s.name] + c0 * k
             self.own_idx[io: io + idx.numel()].copy_(idx)
+            if qp is not None:                      # the payload keeps what a receiver decodes
+                codes[vo: vo + val.numel()].copy_(val.reshape(-1))
+                shift, scale, _, lookup, _ = qp
+                table[s.index, : cfg.quant_bins] = lookup
+                table[s.index, cfg.quant_bins], table[s.index, cfg.quant_bins + 1] = float(shift), float(scale)
+                val = comp._dequantize_values(val, qp)
             self.own_val[vo: vo + val.numel()].copy_(val.reshape(-1))
 
-    def own_payload(self, quantize: bool = False, n_bins: int = 256, range_in_sigmas: float = 6.0) -> dict:
+    def own_payload(self, quantize: bool | None = None, n_bins: int | None = None,
+                    range_in_sigmas: float | None = None) -> dict:
         """Reference-format gradient dict (``<name>idxs`` / ``<name>vals`` / ``<name>quant_params``)
         as views of the flat payload buffers, in named_parameters() order.
 
-        ``quantize``: values as uint8 codes with the reference's per-tensor ``(shift, scale, offset, lookup,
-        dtype)`` tuples (src/tplr/compress.py:585-636).  On CUDA with an unsharded engine the whole payload is
-        encoded by one group of kernels (``tplr_quantize_values``); otherwise tensor by tensor through
-        :class:`templar_b200.compress.TopKCompressor`."""
+        ``quantize`` (default: the engine's ``cfg.quantize``): values as uint8 codes with the reference's
+        per-tensor ``(shift, scale, offset, lookup, dtype)`` tuples (src/tplr/compress.py:585-636).  An engine
+        configured with ``quantize`` returns the codes that :meth:`compress` computed; otherwise the payload is
+        encoded here, on CUDA (unsharded) by one group of kernels (``tplr_quantize_values``), else tensor by
+        tensor through :class:`templar_b200.compress.TopKCompressor`."""
+        cfg = self.cfg
+        quantize = cfg.quantize if quantize is None else quantize
+        n_bins = cfg.quant_bins if n_bins is None else n_bins
+        range_in_sigmas = cfg.quant_range if range_in_sigmas is None else range_in_sigmas
         specs = sorted(self.layout.specs, key=lambda s: s.index)
         out = {}
         if not quantize:
@@ -310,17 +381,15 @@ class WindowEngine:
                 idx, val = self.layout.payload_views(self.own_idx, self.own_val, s.name)
                 out[s.name + "idxs"], out[s.name + "vals"], out[s.name + "quant_params"] = idx, val, None
             return out
-        if self.cuda and self.world_size == 1 and n_bins <= 256:
-            np_ = self.layout.n_params
-            if getattr(self, "_q_codes", None) is None or self._q_table.shape[1] != n_bins + 2:
-                self._q_codes = torch.empty(self.own_val.numel(), dtype=torch.uint8, device=self.device)
-                self._q_table = torch.zeros(np_, n_bins + 2, dtype=torch.float32, device=self.device)
-                self._q_scratch = torch.zeros(np_ * (16 + 2 * n_bins), dtype=torch.float32, device=self.device)
-            desc_full, n_full = self._desc_full
-            native.check(native.lib().tplr_quantize_values(desc_full.data_ptr(), n_full, self.own_val.data_ptr(),
-                                                           self._q_codes.data_ptr(), self._q_table.data_ptr(),
-                                                           self._q_scratch.data_ptr(), np_, n_bins, range_in_sigmas,
-                                                           native.stream_ptr()), "quantize_values")
+        computed = cfg.quantize and n_bins == cfg.quant_bins and getattr(self, "_q_codes", None) is not None
+        if computed or (self.cuda and self.world_size == 1 and n_bins <= 256):
+            if not computed:
+                codes, table, scratch = self._quant_buffers(n_bins)
+                desc_full, n_full = self._desc_full
+                native.check(native.lib().tplr_quantize_values(desc_full.data_ptr(), n_full, self.own_val.data_ptr(),
+                                                               codes.data_ptr(), table.data_ptr(), scratch.data_ptr(),
+                                                               self.layout.n_params, n_bins, float(range_in_sigmas),
+                                                               native.stream_ptr()), "quantize_values")
             tab = self._q_table.cpu()                       # one small D2H copy for all tensors
             for s in specs:
                 idx, codes = self.layout.payload_views(self.own_idx, self._q_codes, s.name)

@@ -74,3 +74,61 @@ def test_gather_cta_budget_grows_with_link_pressure():
     assert tp._comm_pairs(1.0, 1.0, 1) == 3
     tp.n_comm_pairs, tp.world = None, 1
     assert tp._comm_pairs(1e12, 0.0, 100) == 1
+
+
+def _decode_own(eng):
+    """Dense decode of the engine's own payload, flat in the layout's element order."""
+    L = eng.layout
+    tr = C.ChunkingTransformer(None, eng.cfg.target_chunk)
+    comp = C.TopKCompressor(use_quantization=False)
+    out = torch.zeros(L.total, dtype=torch.float32)
+    for s in L.specs:
+        shape = tuple(s.shape) if len(s.shape) >= 2 else (s.cols,)
+        tr.register_shape(shape)
+        idx, val = L.payload_views(eng.own_idx.cpu(), eng.own_val.float().cpu(), s.name)
+        dense = comp.decompress(torch.zeros(shape), idx, val, L.xshape(s.name), s.totalk)
+        out[s.offset: s.offset + s.numel] = tr.decode(dense, use_dct=eng.cfg.use_dct).reshape(-1)
+    return out
+
+
+def quantised_window_identity(device):
+    """With ``quantize`` the payload holds what a receiver decodes and the error feedback keeps the rest:
+    ef_new + decode(payload) == momentum * ef_old + (theta0 - theta), and own_payload() returns the codes."""
+    args = ModelArgs(dim=128, n_layers=1, n_heads=2, vocab_size=256, intermediate_size=256, max_seq_len=32)
+    model = build_model(args, device=device, dtype=torch.float32 if device == "cpu" else torch.bfloat16, seed=2)
+    eng = WindowEngine(model, EngineConfig(topk=8, quantize=True, quant_bins=16), device=device)
+    g = torch.Generator().manual_seed(5)
+    eng.ef.copy_(torch.randn(eng.ef.shape, generator=g) * 1e-3)
+    ef_old = eng.ef.clone()
+    eng.snapshot()
+    eng.store.master_shard.add_((torch.randn(eng.ef.shape, generator=g) * 1e-3).to(eng.store.master_shard.device))
+    x = (eng.cfg.momentum_decay * ef_old + (eng.theta0 - eng.store.master_shard)).float().cpu()
+    eng.compress()
+    sent = _decode_own(eng)
+    assert float((eng.ef.float().cpu() + sent - x).abs().max()) < 2e-6
+    pl = eng.own_payload()
+    comp = C.TopKCompressor(use_quantization=True, quantization_bins=16)
+    n_codes = 0
+    for s in eng.layout.specs:
+        q, qp = pl[s.name + "vals"], pl[s.name + "quant_params"]
+        assert q.dtype == torch.uint8 and int(q.max()) < 16
+        _, val = eng.layout.payload_views(eng.own_idx, eng.own_val, s.name)
+        assert torch.allclose(comp._dequantize_values(q.cpu(), tuple(t.cpu() if torch.is_tensor(t) else t for t in qp)),
+                              val.float().cpu().reshape(q.shape), atol=1e-7)
+        n_codes += len(torch.unique(q))
+    assert n_codes > len(eng.layout.specs)             # the codes are not all one bin
+    # the quantisation error is in the buffer: it differs from the exact-value residual
+    exact = WindowEngine(build_model(args, device=device, dtype=model.tok_embeddings.weight.dtype, seed=2),
+                         EngineConfig(topk=8), device=device)
+    exact.ef.copy_(ef_old)
+    exact.theta0.copy_(eng.theta0)
+    exact.store.master_shard.copy_(eng.store.master_shard)
+    exact.window_open = True
+    exact.compress()
+    assert torch.equal(exact.own_idx.cpu(), eng.own_idx.cpu())
+    assert float((exact.ef - eng.ef).abs().max()) > 1e-7
+    return eng
+
+
+def test_quantised_window_identity_cpu():
+    quantised_window_identity("cpu")

@@ -341,3 +341,19 @@ def test_index_overlap_kernel_matches_bitmap_count():
     for i in range(n):
         for j in range(i + 1, n):
             assert abs(float(m[i, j]) - shared[i, j] / total) < 1e-9, (i, j)
+
+
+def test_quantised_compress_keeps_quantisation_error_in_error_feedback():
+    """Engine with ``quantize``: codes + tables from the kernels, dequantised values in the payload and
+    ef_new + decode(payload) == momentum * ef_old + delta (the reference's residual under quantisation)."""
+    import importlib.util
+    import os
+
+    spec = importlib.util.spec_from_file_location(
+        "engine_cpu_cases", os.path.join(os.path.dirname(os.path.abspath(__file__)), "test_engine_cpu.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    quantised_window_identity = mod.quantised_window_identity
+
+    eng = quantised_window_identity("cuda")
+    assert eng.check_status() == 0
