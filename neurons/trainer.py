@@ -88,7 +88,12 @@ class Trainer:
             outer_weight_decay=float(getattr(hp, "outer_weight_decay", 0.0)),
             inner_lr=float(adam.get("learning_rate", 2e-4)), betas=tuple(adam.get("betas", [0.9, 0.95])),
             eps=float(adam.get("eps", 1e-8)), weight_decay=float(adam.get("weight_decay", 0.1)), max_grad_norm=1.0,
-            max_peers=max_peers or (getattr(hp, "gather_peer_count", 8) + getattr(hp, "reserve_peer_count", 0)))
+            max_peers=max_peers or (getattr(hp, "gather_peer_count", 8) + getattr(hp, "reserve_peer_count", 0)),
+            # 8-bit value codes on the wire (what the reference's miner always sends); a sharded engine needs
+            # the symmetric heap for it, because the statistics are per whole tensor
+            quantize=bool(getattr(hp, "payload_quantization", False)) and (self.world_size == 1 or heap is not None),
+            quant_bins=min(int(getattr(hp, "quantization_bins", 256)), 256),
+            quant_range=float(getattr(hp, "quantization_range", 6)))
         self.engine = WindowEngine(self.model, cfg, device=self.device, rank=self.rank, world_size=self.world_size, heap=heap)
         return self.engine
 

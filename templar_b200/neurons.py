@@ -160,14 +160,20 @@ def _prepare_gradient_dict_engine(miner, engine, step_window: int, null_round: b
     gradient, xshapes, totalks = {}, {}, {}
     L = engine.layout
     want_payload = engine.rank == 0
+    quant = None
     if want_payload:
-        idx_host, val_host = _to_host_async(engine.own_idx), _to_host_async(engine.own_val)
+        idx_host = _to_host_async(engine.own_idx)
+        if engine.cfg.quantize:                  # codes and tables were computed by engine.compress()
+            quant = engine.own_payload()
+            val_host = _to_host_async(engine._q_codes)
+        else:
+            val_host = _to_host_async(engine.own_val)
     for s in sorted(L.specs, key=lambda s: s.index):
         xshapes[s.name], totalks[s.name] = L.xshape(s.name), s.totalk
         if want_payload:
             idx, val = L.payload_views(idx_host, val_host, s.name)
             gradient[s.name + "idxs"], gradient[s.name + "vals"] = idx, val
-            gradient[s.name + "quant_params"] = None
+            gradient[s.name + "quant_params"] = quant[s.name + "quant_params"] if quant is not None else None
     if engine.cuda:
         torch.cuda.current_stream().synchronize()
     gradient["metadata"] = {"window": step_window}

@@ -299,3 +299,51 @@ def test_validator_gather_offload_round_trip():
     v.hparams.offload_gather_results = False
     v.offload_gather_results(res, log=False)
     assert res._offloaded is None
+
+
+def test_engine_quantised_window_equals_generic_functions():
+    """Engine with ``quantize`` against the reference-semantics functions with a quantising compressor: same
+    codes, same tables, same error feedback, and the same weights after the outer step on the sent payload."""
+    args = ModelArgs(dim=64, n_layers=1, n_heads=2, vocab_size=128, intermediate_size=128, max_seq_len=32)
+    torch.manual_seed(1)
+    tok = torch.randint(0, 128, (2, 33))
+    m1 = build_model(args, seed=3)
+    eng = WindowEngine(m1, EngineConfig(topk=8, use_dct=True, momentum_decay=0.9, outer_lr=0.3, inner_lr=1e-2,
+                                        max_peers=3, quantize=True, quant_bins=16))
+    hp = SimpleNamespace(use_dct=True, topk_compression=8, momentum_decay=0.9)
+    node = SimpleNamespace(model=m1, use_engine=True, hparams=hp)
+    eng.snapshot()
+    eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0)
+    eng.optimizer_step()
+    sent, xs, tk = tplr.prepare_gradient_dict(node, 0)                   # engine path: codes + tables
+    m2 = build_model(args, seed=3)
+    opt = torch.optim.AdamW(m2.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    theta0 = {n: p.detach().clone() for n, p in m2.named_parameters()}
+    m2.loss(tok[:, :-1], tok[:, 1:]).backward()
+    torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+    opt.step()
+    comp = C.TopKCompressor(use_quantization=True, quantization_bins=16, quantization_range=6)
+    miner = SimpleNamespace(model=m2, use_engine=False, hparams=hp, transformer=C.ChunkingTransformer(m2, 64),
+                            compressor=comp, owned_params={n for n, _ in m2.named_parameters()},
+                            error_feedback={n: None for n, _ in m2.named_parameters()}, error_feedback_cpu_buffers={})
+    with torch.no_grad():
+        for n, p in m2.named_parameters():
+            p.grad = theta0[n] - p.detach()
+            p.copy_(theta0[n])
+    grad, _, _ = tplr.prepare_gradient_dict(miner, 0)
+    for n, _ in m2.named_parameters():
+        assert sent[n + "vals"].dtype == torch.uint8 and grad[n + "vals"].dtype == torch.uint8
+        qa, qb = sent[n + "quant_params"], grad[n + "quant_params"]
+        assert abs(float(qa[0]) - float(qb[0])) < 1e-7 and abs(float(qa[1]) / float(qb[1]) - 1) < 1e-5
+        da = comp._dequantize_values(sent[n + "vals"], qa).reshape(-1, sent[n + "vals"].shape[-1])
+        db = comp._dequantize_values(grad[n + "vals"], qb).reshape(da.shape)
+        ia = C.unpack_12bit_indices(sent[n + "idxs"], da.shape)
+        ib = C.unpack_12bit_indices(grad[n + "idxs"], db.shape)
+        oa, ob = ia.argsort(-1), ib.argsort(-1)
+        assert torch.equal(ia.gather(-1, oa), ib.gather(-1, ob)), n
+        assert torch.allclose(da.gather(-1, oa), db.gather(-1, ob), atol=2e-6), n
+        assert torch.allclose(eng.store.view(eng.ef, n), miner.error_feedback[n], atol=2e-6), n
+    # a receiver that stages the sent dict sees exactly the node's own (dequantised) payload
+    from templar_b200.parallel.window_engine import peer_slice
+    eng.load_peer_payload(0, peer_slice({k: [v] for k, v in sent.items() if k != "metadata"}, 0), non_blocking=False)
+    assert torch.allclose(eng.peer_val[0], eng.own_val, atol=1e-7)
