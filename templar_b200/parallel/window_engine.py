@@ -415,17 +415,19 @@ class WindowEngine:
             for s in self.layout.specs:
                 idx, val = self.layout.payload_views(self.peer_idx[slot], self.peer_val[slot], s.name)
                 idx.copy_(payload[s.name + "idxs"].reshape(-1), non_blocking=non_blocking)
-                val.copy_(self._payload_values(payload, s.name).reshape(val.shape), non_blocking=non_blocking)
+                val.copy_(self._payload_values(payload, s.name, val.device).reshape(val.shape),
+                          non_blocking=non_blocking)
             return
         idx_flat, val_flat = payload
         self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
         self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
 
     @staticmethod
-    def _payload_values(payload: dict, name: str) -> torch.Tensor:
+    def _payload_values(payload: dict, name: str, device=None) -> torch.Tensor:
         """The values of one tensor of a reference-format payload; uint8 codes are decoded with the payload's
         ``<name>quant_params`` = (shift, scale, offset, lookup, dtype), as the reference does before it
-        decompresses (src/tplr/compress.py:624-644)."""
+        decompresses (src/tplr/compress.py:624-644).  With ``device`` the codes are moved there first, so a
+        quantised payload crosses the host link as one byte per value and is decoded on the device."""
         vals = payload[name + "vals"]
         if vals.dtype != torch.uint8:
             return vals
@@ -433,6 +435,8 @@ class WindowEngine:
         if qp is None:
             raise ValueError(f"{name}vals holds 8-bit codes but the payload has no {name}quant_params")
         shift, _, _, lookup, _ = qp
+        if device is not None:
+            vals = vals.to(device, non_blocking=True)
         lookup = torch.as_tensor(lookup).to(vals.device, torch.float32)
         shift = torch.as_tensor(shift).to(vals.device, torch.float32)
         return lookup[vals.long()] + shift
@@ -660,7 +664,7 @@ class WindowEngine:
         for s in L.specs:
             i, v = L.payload_views(idx, val, s.name)
             i.copy_(payload[s.name + "idxs"].reshape(-1))
-            v.copy_(self._payload_values(payload, s.name).reshape(v.shape))
+            v.copy_(self._payload_values(payload, s.name, v.device).reshape(v.shape))
         return idx, val
 
     @torch.no_grad()
