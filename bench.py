@@ -135,7 +135,11 @@ def run_ours(a):
     from templar_b200.utils.synthetic import synthetic_payload
     for j in hosted:
         idx, val = synthetic_payload(L, 99 + j, device=dev)
-        host_payload[j] = (idx.cpu().pin_memory(), val.cpu().pin_memory())
+        if a.values == "uint8":                  # peers send 8-bit codes with per-tensor tables, decoded on the device
+            codes, table = eng.encode_values(val)
+            host_payload[j] = (idx.cpu().pin_memory(), codes.cpu().pin_memory(), table.cpu().pin_memory())
+        else:
+            host_payload[j] = (idx.cpu().pin_memory(), val.cpu().pin_memory())
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
 
     def window(e2e: bool, w: int):
@@ -232,7 +236,7 @@ def run_ours(a):
     if not a.no_e2e:
         ms_e2e, _, _ = timed(True, a.steps, 1)
         e2e = {"value": tokens_per_step * a.steps / (ms_e2e / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": int(A * B * (S + 1) * 8 + sum(i.numel() + v.numel() * 4 for i, v in host_payload.values())),
+               "h2d_bytes_per_step": int(A * B * (S + 1) * 8 + sum(t.numel() * t.element_size() for pl in host_payload.values() for t in pl)),
                "d2h_bytes_per_step": 4}
     status = eng.check_status()
     if rank == 0:

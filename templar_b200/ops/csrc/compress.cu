@@ -1279,6 +1279,33 @@ TPLR_API int tplr_quantize_values(const void* descs, int n_desc, const float* va
   return (int)cudaGetLastError();
 }
 
+// Decode of a whole payload: out[i] = lookup[code[i]] + shift with the table written by tplr_quantize_values
+// (or filled from a received payload's per-tensor parameters).  One launch over all tensors.
+__global__ void __launch_bounds__(256) dequant_values_kernel(const TplrParamDesc* __restrict__ descs, const uint8_t* __restrict__ codes,
+                                                             const float* __restrict__ table, float* __restrict__ out, int n_bins) {
+  __shared__ float s_row[257];
+  const TplrParamDesc d = descs[blockIdx.x];
+  const long long n = (long long)d.n_chunks * d.k;
+  const long long per = ((n + QSPLIT - 1) / QSPLIT + 3) & ~3LL;
+  const long long lo = per * blockIdx.y, hi = min(n, lo + per);
+  const float* row = table + (long long)d.param_id * (n_bins + 2);
+  for (int b = threadIdx.x; b <= n_bins; b += blockDim.x) s_row[b] = row[b];
+  __syncthreads();
+  const float shift = s_row[n_bins];
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x)
+    out[d.val_off + i] = s_row[min((int)codes[d.val_off + i], n_bins - 1)] + shift;
+}
+
+TPLR_API int tplr_dequantize_values(const void* descs, int n_desc, const uint8_t* codes, const float* table, float* out,
+                                    int n_bins, void* stream) {
+  TPLR_ENTER();
+  if (n_desc <= 0) return 0;
+  if (n_bins <= 0 || n_bins > 256) return (int)cudaErrorInvalidValue;
+  dim3 grid(n_desc, QSPLIT);
+  dequant_values_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const TplrParamDesc*)descs, codes, table, out, n_bins);
+  return (int)cudaGetLastError();
+}
+
 // ------------------------------------------------------------------------------------- //
 // Error feedback under quantisation.  The reference subtracts from the error feedback what a receiver will
 // decode, i.e. the *dequantised* top-k values (src/tplr/neurons.py:157-171), so the quantisation error stays
@@ -1298,76 +1325,123 @@ struct RequantArgs {
   int n_desc, total_chunks, n_bins, use_dct, distinct;
 };
 
-__global__ void __launch_bounds__(NT, 2) requant_residual_kernel(const RequantArgs a) {
-  extern __shared__ __align__(16) float smem[];
-  float* Y = smem;
-  float* U = Y + TPLR_TILE_ELEMS;
-  float* Fh = U + TPLR_TILE_ELEMS;
-  float* Fht = Fh + TPLR_TILE_ELEMS;
-  float* Fw = a.distinct ? Fht + TPLR_TILE_ELEMS : Fh;
-  float* Fwt = a.distinct ? Fw + TPLR_TILE_ELEMS : Fht;
-  __shared__ int s_idx[TPLR_TILE];
+// One chunk per CTA iteration.  The k selected entries are fetched by the first k threads (the next chunk's
+// while this one is computed), the tensor's lookup row and the DCT matrices are cached in shared memory, and
+// every thread accumulates a 4 x 4 patch of  sum_j diff_j * F_h[b_j][r] * F_w[d_j][l]  straight from the basis.
+struct RequantEntry {
+  unsigned b0, b1, b2;
+  float v;
+  int code;
+};
+
+static __device__ __forceinline__ RequantEntry requant_fetch(const RequantArgs& a, const TplrParamDesc& d, int cl, int tid) {
+  RequantEntry e;
+  const uint8_t* ip = a.idx + d.idx_off + ((long long)cl * (d.k / 2) + (tid >> 1)) * 3;
+  const long long vi = d.val_off + (long long)cl * d.k + tid;
+  e.b0 = ip[0]; e.b1 = ip[1]; e.b2 = ip[2];
+  e.v = a.val[vi];
+  e.code = a.codes[vi];
+  return e;
+}
+
+__global__ void __launch_bounds__(NT, 4) requant_residual_kernel(const RequantArgs a) {
+  __shared__ __align__(16) float Fh[TPLR_TILE_ELEMS];
+  __shared__ __align__(16) float Fw2[TPLR_TILE_ELEMS];
+  __shared__ float s_row[258];
+  __shared__ int s_b[TPLR_TILE], s_d[TPLR_TILE];
   __shared__ float s_diff[TPLR_TILE];
+  const float* Fw = a.distinct ? Fw2 : Fh;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  int cur_fh = -1, cur_fw = -1;
-  for (int c = blockIdx.x; c < a.total_chunks; c += gridDim.x) {
-    const TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, c)];
+  int cur_fh = -1, cur_fw = -1, cur_param = -1;
+  int c = blockIdx.x;
+  if (c >= a.total_chunks) return;
+  TplrParamDesc d = a.descs[find_desc(a.descs, a.n_desc, c)];
+  RequantEntry ent;
+  if (tid < d.k) ent = requant_fetch(a, d, c - d.chunk_begin, tid);
+  while (c < a.total_chunks) {
     const int h = d.h, w = d.w, k = d.k;
     const int cl = c - d.chunk_begin;
     const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
     const long long base = d.elem_off + (long long)cy * h * d.cols + (long long)cx * w;
     __syncthreads();  // previous chunk's shared memory fully consumed
     if (a.use_dct && (d.fh_off != cur_fh || d.fw_off != cur_fw)) {
-      load_basis(a.basis + d.fh_off, h, Fh, Fht);
-      if (a.distinct) load_basis(a.basis + d.fw_off, w, Fw, Fwt);
+      for (int i = tid; i < TPLR_TILE_ELEMS; i += NT) {
+        const int r = i >> 6, cc = i & 63;
+        Fh[i] = (r < h && cc < h) ? __ldg(a.basis + d.fh_off + r * h + cc) : 0.f;
+        if (a.distinct) Fw2[i] = (r < w && cc < w) ? __ldg(a.basis + d.fw_off + r * w + cc) : 0.f;
+      }
       cur_fh = d.fh_off;
       cur_fw = d.fw_off;
     }
-    if (tid < k) {
-      const uint8_t* ip = a.idx + d.idx_off + ((long long)cl * (k / 2) + (tid >> 1)) * 3;
-      const unsigned b0 = ip[0], b1 = ip[1], b2 = ip[2];
-      const int e = (tid & 1) ? (int)(((b1 >> 4) & 0xfu) | (b2 << 4)) : (int)(b0 | ((b1 & 0xfu) << 8));
-      const long long vi = d.val_off + (long long)cl * k + tid;
+    if (d.param_id != cur_param) {
       const float* row = a.table + (long long)d.param_id * (a.n_bins + 2);
-      const float v = a.val[vi];
-      const float deq = row[min((int)a.codes[vi], a.n_bins - 1)] + row[a.n_bins];
-      a.val[vi] = deq;
-      s_idx[tid] = min(e, h * w - 1);
-      s_diff[tid] = v - deq;
+      for (int i = tid; i <= a.n_bins; i += NT) s_row[i] = row[i];
+      cur_param = d.param_id;
+      __syncthreads();
+    }
+    if (tid < k) {
+      const int e = min((tid & 1) ? (int)(((ent.b1 >> 4) & 0xfu) | (ent.b2 << 4)) : (int)(ent.b0 | ((ent.b1 & 0xfu) << 8)),
+                        h * w - 1);
+      const float deq = s_row[min(ent.code, a.n_bins - 1)] + s_row[a.n_bins];
+      a.val[d.val_off + (long long)cl * k + tid] = deq;
+      s_b[tid] = e / w;
+      s_d[tid] = e % w;
+      s_diff[tid] = ent.v - deq;
     }
     __syncthreads();
+    // the next chunk's entries travel while this chunk is computed
+    const int cn = c + gridDim.x;
+    TplrParamDesc dn = d;
+    if (cn < a.total_chunks) {
+      if (!(cn >= d.chunk_begin && cn < d.chunk_begin + d.n_chunks)) dn = a.descs[find_desc(a.descs, a.n_desc, cn)];
+      if (tid < dn.k) ent = requant_fetch(a, dn, cn - dn.chunk_begin, tid);
+    }
     if (!a.use_dct) {
-      if (tid < k) {
-        const int e = s_idx[tid];
-        a.ef[base + (long long)(e / w) * d.cols + (e % w)] += s_diff[tid];
-      }
-      continue;
-    }
-    for (int i = tid; i < k * LD; i += NT) {
-      const int j = i >> 6, r = i & 63;
-      const int e = s_idx[j];
-      Y[i] = Fh[(e / w) * LD + r];
-      U[i] = s_diff[j] * Fw[(e % w) * LD + r];
-    }
-    __syncthreads();
-    float acc[4][4];
-    mm_tile(Y, U, k, acc);
-    const bool vec = (w == 64) && ((d.cols & 3) == 0) && ((base & 3) == 0);
+      if (tid < k) a.ef[base + (long long)s_b[tid] * d.cols + s_d[tid]] += s_diff[tid];
+    } else {
+      const bool vec = (w == 64) && ((d.cols & 3) == 0) && ((base & 3) == 0);
+      // this thread's patch of the error feedback is loaded before the product and stored after it
+      float4 x[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = 4 * ty + i;
-      if (r >= h) continue;
-      const long long g0 = base + (long long)r * d.cols + 4 * tx;
-      if (vec) {
-        float4 x = *reinterpret_cast<const float4*>(a.ef + g0);
-        x.x += acc[i][0]; x.y += acc[i][1]; x.z += acc[i][2]; x.w += acc[i][3];
-        *reinterpret_cast<float4*>(a.ef + g0) = x;
-      } else {
+      for (int i = 0; i < 4; ++i) {
+        x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int r = 4 * ty + i;
+        if (vec && r < h) x[i] = *reinterpret_cast<const float4*>(a.ef + base + (long long)r * d.cols + 4 * tx);
+      }
+      float acc[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (4 * tx + j < w) a.ef[g0 + j] += acc[i][j];
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+      for (int j = 0; j < k; ++j) {
+        const float df = s_diff[j];
+        const float4 fh = *reinterpret_cast<const float4*>(Fh + s_b[j] * LD + 4 * ty);
+        const float4 fw = *reinterpret_cast<const float4*>(Fw + s_d[j] * LD + 4 * tx);
+        const float av[4] = {fh.x * df, fh.y * df, fh.z * df, fh.w * df};
+        const float bv[4] = {fw.x, fw.y, fw.z, fw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) acc[i][jj] = fmaf(av[i], bv[jj], acc[i][jj]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = 4 * ty + i;
+        if (r >= h) continue;
+        const long long g0 = base + (long long)r * d.cols + 4 * tx;
+        if (vec) {
+          *reinterpret_cast<float4*>(a.ef + g0) =
+              make_float4(x[i].x + acc[i][0], x[i].y + acc[i][1], x[i].z + acc[i][2], x[i].w + acc[i][3]);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            if (4 * tx + jj < w) a.ef[g0 + jj] += acc[i][jj];
+        }
       }
     }
+    c = cn;
+    d = dn;
   }
 }
 
@@ -1383,12 +1457,9 @@ TPLR_API int tplr_requant_residual(const void* descs, int n_desc, int total_chun
   a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.idx = idx; a.val = val; a.codes = codes;
   a.table = table; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_bins = n_bins; a.use_dct = use_dct;
   a.distinct = distinct;
-  const int smem = (distinct ? 6 : 4) * TPLR_TILE_ELEMS * (int)sizeof(float);
-  cudaError_t err = cudaFuncSetAttribute(requant_residual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (err != cudaSuccess) return (int)err;
-  int grid = tplr_sm_count() * 2;
+  int grid = tplr_sm_count() * 4;
   if (grid > total_chunks) grid = total_chunks;
-  requant_residual_kernel<<<grid, NT, smem, (cudaStream_t)stream>>>(a);
+  requant_residual_kernel<<<grid, NT, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
 

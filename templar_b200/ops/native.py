@@ -61,6 +61,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_aggregate_apply": [vp, i, i, vp, i, vp, vp, i, vp, i, i, vp, vp, vp, vp, vp, vp, f, f, i, i, i, vp, vp],
         "tplr_index_overlap": [vp, i, i, i, vp, vp, vp],
         "tplr_quantize_values": [vp, i, vp, vp, vp, vp, i, i, f, vp],
+        "tplr_dequantize_values": [vp, i, vp, vp, vp, i, vp],
         "tplr_requant_residual": [vp, i, i, vp, vp, vp, vp, vp, vp, i, i, i, vp],
         "tplr_compress_chunks_tc": [vp, i, i, vp, vp, vp, vp, vp, vp, vp, f, i, i, i, vp],
         "tplr_aggregate_apply_tc": [vp, i, i, vp, i, vp, vp, i, vp, i, i, vp, vp, vp, vp, vp, vp, f, f, i, vp, vp],

@@ -410,7 +410,8 @@ class WindowEngine:
     # ------------------------------------------------------------------------------------ #
     @torch.no_grad()
     def load_peer_payload(self, slot: int, payload, non_blocking: bool = True) -> None:
-        """``payload``: (idx_flat uint8, val_flat) in this layout, or a reference-format dict."""
+        """``payload``: (idx_flat uint8, val_flat) or (idx_flat uint8, codes uint8, table) in this layout, or a
+        reference-format dict."""
         if isinstance(payload, dict):
             for s in self.layout.specs:
                 idx, val = self.layout.payload_views(self.peer_idx[slot], self.peer_val[slot], s.name)
@@ -418,9 +419,55 @@ class WindowEngine:
                 val.copy_(self._payload_values(payload, s.name, val.device).reshape(val.shape),
                           non_blocking=non_blocking)
             return
+        if len(payload) == 3:                     # quantised flat form: indices, 8-bit codes, per-tensor tables
+            idx_flat, codes, table = payload
+            self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
+            self._decode_flat(codes, table, self.peer_val[slot], non_blocking)
+            return
         idx_flat, val_flat = payload
         self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
         self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
+
+    def _decode_flat(self, codes: torch.Tensor, table: torch.Tensor, out: torch.Tensor, non_blocking: bool) -> None:
+        """out <- lookup[code] + shift per tensor.  ``codes`` [val_elems] uint8 and ``table`` [n_params, bins + 2]
+        (lookup | shift | scale) may live on the host: they cross the link as they are (one byte per value) and
+        are decoded on the device by one kernel."""
+        n_bins = table.shape[1] - 2
+        if not self.cuda or out.dtype != torch.float32:
+            lut = table.to(out.device, torch.float32)
+            codes = codes.to(out.device)
+            for s in self.layout.specs:
+                _, c = self.layout.payload_views(self.own_idx, codes, s.name)
+                _, o = self.layout.payload_views(self.own_idx, out, s.name)
+                o.copy_((lut[s.index, :n_bins][c.long().clamp(max=n_bins - 1)] + lut[s.index, n_bins]).reshape(o.shape))
+            return
+        if getattr(self, "_stage_codes", None) is None or self._stage_table.shape != table.shape:
+            self._stage_codes = torch.empty(self.layout.val_elems, dtype=torch.uint8, device=self.device)
+            self._stage_table = torch.empty(table.shape, dtype=torch.float32, device=self.device)
+        self._stage_codes[: codes.numel()].copy_(codes, non_blocking=non_blocking)
+        self._stage_table.copy_(table, non_blocking=non_blocking)
+        desc_full, n_full = self._desc_full
+        native.check(native.lib().tplr_dequantize_values(desc_full.data_ptr(), n_full, self._stage_codes.data_ptr(),
+                                                         self._stage_table.data_ptr(), out.data_ptr(), n_bins,
+                                                         native.stream_ptr()), "dequantize_values")
+
+    @torch.no_grad()
+    def encode_values(self, val_flat: torch.Tensor, n_bins: int | None = None,
+                      range_in_sigmas: float | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """8-bit codes and per-tensor tables ([n_params, bins + 2]: lookup | shift | scale) of any value buffer
+        in this layout (CUDA, full layout); the inverse is the 3-tuple form of :meth:`load_peer_payload`."""
+        native.require(self.cuda and val_flat.is_cuda and val_flat.dtype == torch.float32, "encode_values runs on CUDA fp32")
+        n_bins = self.cfg.quant_bins if n_bins is None else n_bins
+        range_in_sigmas = self.cfg.quant_range if range_in_sigmas is None else range_in_sigmas
+        np_ = self.layout.n_params
+        codes = torch.empty(self.layout.val_elems, dtype=torch.uint8, device=self.device)
+        table = torch.zeros(np_, n_bins + 2, dtype=torch.float32, device=self.device)
+        scratch = torch.zeros(np_ * (16 + 2 * n_bins), dtype=torch.float32, device=self.device)
+        desc_full, n_full = self._desc_full
+        native.check(native.lib().tplr_quantize_values(desc_full.data_ptr(), n_full, val_flat.data_ptr(), codes.data_ptr(),
+                                                       table.data_ptr(), scratch.data_ptr(), np_, n_bins,
+                                                       float(range_in_sigmas), native.stream_ptr()), "quantize_values")
+        return codes, table
 
     @staticmethod
     def _payload_values(payload: dict, name: str, device=None) -> torch.Tensor:

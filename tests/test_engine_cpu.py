@@ -117,6 +117,9 @@ def quantised_window_identity(device):
                               val.float().cpu().reshape(q.shape), atol=1e-7)
         n_codes += len(torch.unique(q))
     assert n_codes > len(eng.layout.specs)             # the codes are not all one bin
+    # the flat quantised form (indices, codes, tables) staged as a peer decodes to the same values
+    eng.load_peer_payload(0, (eng.own_idx, eng._q_codes, eng._q_table), non_blocking=False)
+    assert torch.allclose(eng.peer_val[0].float(), eng.own_val.float(), atol=1e-7)
     # the quantisation error is in the buffer: it differs from the exact-value residual
     exact = WindowEngine(build_model(args, device=device, dtype=model.tok_embeddings.weight.dtype, seed=2),
                          EngineConfig(topk=8), device=device)

@@ -357,3 +357,27 @@ def test_quantised_compress_keeps_quantisation_error_in_error_feedback():
 
     eng = quantised_window_identity("cuda")
     assert eng.check_status() == 0
+
+
+def test_encode_values_and_flat_quantised_staging():
+    """encode_values -> (codes, tables); the 3-tuple staged from pinned host memory decodes to lookup[code] + shift,
+    within half a bin of the original values where they were not clamped."""
+    model = _Bag([(128, 192), (256,), (96, 40), (64, 64)]).to(DEV)
+    eng = WindowEngine(model, EngineConfig(topk=16, max_peers=2, quant_bins=64), device=DEV, compute_dtype=torch.float32)
+    idx, val = synthetic_payload(eng.layout, 3, device=DEV, scale=1e-2)
+    codes, table = eng.encode_values(val)
+    eng.load_peer_payload(1, (idx.cpu().pin_memory(), codes.cpu().pin_memory(), table.cpu().pin_memory()))
+    torch.cuda.synchronize()
+    assert torch.equal(eng.peer_idx[1][: idx.numel()], idx)
+    for s in eng.layout.specs:
+        _, c = eng.layout.payload_views(idx, codes, s.name)
+        _, got = eng.layout.payload_views(idx, eng.peer_val[1], s.name)
+        _, v = eng.layout.payload_views(idx, val, s.name)
+        row = table[s.index]
+        assert torch.equal(got, (row[:64][c.long()] + row[64]).reshape(got.shape))
+        inner = (c > 0) & (c < 63)
+        assert float((got - v).abs()[inner.reshape(got.shape)].max()) <= 1.01 * float(row[65])
+        comp = C.TopKCompressor(use_quantization=True, quantization_bins=64, quantization_range=6)
+        q, qp = comp._quantize_values(v.cpu().float())
+        assert float((q.long() - c.cpu().long().reshape(q.shape)).abs().max()) <= 1     # same bins up to rounding ties
+        assert abs(float(qp[1]) / float(row[65]) - 1) < 1e-4
