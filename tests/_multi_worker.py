@@ -96,6 +96,26 @@ def main():
     out["master_max_diff"], out["compute_max_diff"], out["scale"] = diff, cdiff, scale
     moved = (ref.store.master_shard - ref.theta0).abs().max().item()
     out["moved"] = moved
+
+    # 4. the same with 8-bit payload values: rank 0 encodes the assembled payload, every rank corrects its chunks
+    import dataclasses
+    qcfg = dataclasses.replace(cfg, quantize=True, quant_bins=256)
+    qeng = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), qcfg, device=dev, rank=rank,
+                        world_size=world, heap=heap)
+    run(qeng, [rank], heap)
+    heap.check()
+    qref = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), qcfg, device=dev)
+    run(qref, list(range(world)), None)
+    lo, hi = qeng.store.lo, qeng.store.hi
+    out["q_status"] = qeng.check_status()
+    out["q_master_max_diff"] = (qeng.store.master_shard - qref.store.master_shard[lo:hi]).abs().max().item()
+    out["q_ef_max_diff"] = (qeng.ef - qref.ef[lo:hi]).abs().max().item()
+    out["q_ef_scale"] = qref.ef.abs().max().item()
+    out["q_ef_vs_exact"] = (qref.ef - ref.ef).abs().max().item()       # the quantisation error is in the buffer
+    if rank == 0:
+        out["q_val_max_diff"] = (qeng.own_val - qref.own_val).abs().max().item()
+        out["q_val_scale"] = qref.own_val.abs().max().item()
+        out["q_codes_equal"] = float((qeng._q_codes == qref._q_codes).float().mean().item())
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

@@ -37,6 +37,14 @@ def test_two_rank_runtime_and_window():
         assert r["moved"] > 1e-4, r
         assert r["master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
         assert r["compute_max_diff"] < 2e-2 * max(r["scale"], 1.0), r
+        # quantised payload values: sharded == single rank up to the bf16 summation order of the gradients
+        assert r["q_status"] == 0, r
+        assert r["q_master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
+        assert r["q_ef_max_diff"] < 0.05 * r["q_ef_scale"], r
+        assert r["q_ef_vs_exact"] > 0, r
+        if "q_val_max_diff" in r:
+            assert r["q_val_max_diff"] < 0.05 * r["q_val_scale"], r
+            assert r["q_codes_equal"] > 0.9, r
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
