@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--peers", type=int, default=8)
     ap.add_argument("--topk", type=int, default=32)
     ap.add_argument("--outer-update", default="sgd", choices=["sgd", "sign"])
-    ap.add_argument("--values", default="fp32", choices=["fp32", "uint8"],
+    ap.add_argument("--values", default="uint8", choices=["fp32", "uint8"],
                     help="wire format of this node's payload values: fp32, or the reference miner's 8-bit codes "
                          "(256 bins, 6 sigma) with the quantisation error kept in the error feedback")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
