@@ -74,3 +74,47 @@ def test_random_pages_and_raw_rows():
     assert len(rows) == 300 and all(isinstance(r, str) for r in rows)
     cfgs = asyncio.run(DatasetLoader.fetch_dataset_configs(source=src))
     assert cfgs == {f"cfg{c}": {"num_rows": 400, "split": "train"} for c in range(3)}
+
+
+def test_dataset_prep_shards_ids_and_reader(tmp_path):
+    """pretokenize -> fixed-size shards with documents split across shard ends; ids = BLAKE2b-8 of each sequence;
+    the sharded dataset reads what was written."""
+    import hashlib
+    import struct
+
+    import templar_b200 as tplr
+    from templar_b200 import dataset_prep as P
+
+    tok = _Tok()
+    docs = [" ".join("y" * (1 + (i * 7 + j) % 9) for j in range(5 + i % 11)) for i in range(200)]
+    stream = []
+    for d in docs:
+        stream += tok.encode(d) + [0]
+    paths = P.pretokenize(docs, tok, str(tmp_path), shard_size=512, seq_len=16)
+    assert len(paths) == len(stream) // 512 and len(paths) >= 3
+    for i, path in enumerate(paths):
+        arr = np.load(path)
+        assert arr.dtype == np.uint32 and arr.shape == (512,)
+        assert np.array_equal(arr, np.asarray(stream[i * 512: (i + 1) * 512], dtype=np.uint32))
+        ids = np.load(tmp_path / f"sample_ids_{i:06d}.npy")
+        assert ids.dtype == np.uint64 and ids.shape == (32,)
+        want = struct.unpack("<Q", hashlib.blake2b(arr[16:32].tobytes(), digest_size=8).digest())[0]
+        assert int(ids[1]) == want == P.sample_id(arr[16:32])
+    ds = tplr.SharedShardedDataset(1, 16, 0, 1, custom_path=str(tmp_path))
+    assert len(ds) == 32
+    assert np.array_equal(np.asarray(ds[3]), np.asarray(stream[512 + 48: 512 + 64]))
+    assert int(ds.sample_id(3)) == P.sample_id(np.load(paths[1])[48:64])
+
+
+def test_dataset_prep_cli_synthetic_and_ids(tmp_path, capsys):
+    from templar_b200 import dataset_prep as P
+
+    assert P.main(["synthetic", "--dir", str(tmp_path), "--shards", "2", "--tokens", "4096", "--seq-len", "64",
+                   "--vocab-size", "1000"]) == 0
+    a = np.load(tmp_path / "train_000001.npy")
+    assert a.shape == (4096,) and int(a.max()) < 1000
+    ids = np.load(tmp_path / "sample_ids_000001.npy").copy()
+    (tmp_path / "sample_ids_000001.npy").unlink()
+    assert P.main(["ids", "--dir", str(tmp_path), "--seq-len", "64", "--workers", "3"]) == 0
+    assert np.array_equal(np.load(tmp_path / "sample_ids_000001.npy"), ids)
+    assert P.shard_names(5, "anneal") == ("anneal_000005.npy", "sample_ids_anneal_000005.npy")
