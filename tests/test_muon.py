@@ -1,0 +1,148 @@
+"""Muon: Newton-Schulz orthogonalisation, the single-device optimizer with auxiliary Adam, the sharded variant."""
+
+import copy
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from templar_b200.muon import (Muon, SingleDeviceMuonWithAuxAdam, adam_update, muon_update, newton_schulz,
+                               zeropower_via_newtonschulz5)
+from templar_b200.muon.newton_schulz import NS_CONSTS
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _ns_reference(G: torch.Tensor) -> torch.Tensor:
+    """The same five quintic iterations in fp32 matmuls."""
+    X = G.float()
+    t = X.size(-2) > X.size(-1)
+    if t:
+        X = X.mT
+    X = X / (X.norm() + 1e-7)
+    for a, b, c in NS_CONSTS:
+        A = X @ X.mT
+        X = a * X + (b * A + c * A @ A) @ X
+    return X.mT if t else X
+
+
+@pytest.mark.parametrize("shape", [(64, 64), (128, 64), (64, 192), (3, 64, 128)])
+def test_newton_schulz_pushes_singular_values_to_one(shape):
+    torch.manual_seed(0)
+    G = torch.randn(*shape)
+    X = newton_schulz(G).float()
+    assert X.shape == G.shape
+    sv = torch.linalg.svdvals(X)
+    # all but the near-singular directions of a random matrix end close to 1
+    assert float(sv.max()) < 1.3 and 0.9 < float(sv.median()) < 1.1 and float((sv > 0.5).float().mean()) > 0.9
+    flatG, flatX = G.reshape(-1, *shape[-2:]), X.reshape(-1, *shape[-2:])
+    for g, x in zip(flatG, flatX):
+        U, _, Vh = torch.linalg.svd(g, full_matrices=False)
+        polar = U @ Vh
+        assert float((x * polar).sum() / (x.norm() * polar.norm())) > 0.95      # aligned with U V^T
+        ref = _ns_reference(g)
+        assert float((x - ref).norm() / ref.norm()) < 3e-2                      # bf16 operands vs fp32 matmuls
+
+
+def test_fixed_coefficient_variant_and_errors():
+    torch.manual_seed(1)
+    G = torch.randn(48, 96)
+    sv = torch.linalg.svdvals(zeropower_via_newtonschulz5(G).float())
+    assert float(sv.max()) < 1.3 and float(sv.min()) > 0.3                   # 48 x 96: well conditioned
+    with pytest.raises(ValueError):
+        newton_schulz(torch.randn(7))
+
+
+@pytest.mark.parametrize("nesterov,rms", [(True, False), (False, False), (True, True)])
+def test_muon_update_formula(nesterov, rms):
+    torch.manual_seed(2)
+    g, m = torch.randn(96, 32), torch.randn(96, 32) * 0.1
+    g0, m0 = g.clone(), m.clone()
+    upd = muon_update(g, m, beta=0.9, nesterov=nesterov, rms_scale=rms)
+    m_ref = m0 + (g0 - m0) * 0.1
+    assert torch.allclose(m, m_ref, atol=1e-6)
+    direction = g0 + (m_ref - g0) * 0.9 if nesterov else m_ref
+    scale = 0.2 * 96 ** 0.5 if rms else (96 / 32) ** 0.5
+    want = newton_schulz(direction).float() * scale
+    assert torch.allclose(upd.float(), want, atol=1e-5)
+    g4, m4 = torch.randn(8, 4, 3, 3), torch.zeros(8, 4, 3, 3)              # conv-style weights are flattened
+    assert muon_update(g4, m4).shape == (8, 36)
+
+
+def test_adam_update_matches_torch_adamw():
+    torch.manual_seed(3)
+    p = torch.nn.Parameter(torch.randn(10, 6))
+    q = torch.nn.Parameter(p.detach().clone())
+    ours = SingleDeviceMuonWithAuxAdam([dict(params=[p], use_muon=False, lr=1e-2, betas=(0.9, 0.95), eps=1e-10,
+                                             weight_decay=0.1)])
+    ref = torch.optim.AdamW([q], lr=1e-2, betas=(0.9, 0.95), eps=1e-10, weight_decay=0.1)
+    for _ in range(3):
+        g = torch.randn(10, 6)
+        p.grad, q.grad = g.clone(), g.clone()
+        ours.step()
+        ref.step()
+    assert torch.allclose(p, q, atol=1e-6)
+    b1, b2 = torch.zeros(3), torch.zeros(3)
+    u = adam_update(torch.ones(3), b1, b2, 1, (0.9, 0.95), 1e-10)
+    assert torch.allclose(u, torch.ones(3), atol=1e-6)                       # bias-corrected first step
+
+
+def test_single_device_muon_step_and_defaults():
+    torch.manual_seed(4)
+    w = torch.nn.Parameter(torch.randn(64, 32))
+    b = torch.nn.Parameter(torch.randn(32))
+    opt = SingleDeviceMuonWithAuxAdam([dict(params=[w], use_muon=True, lr=0.05, weight_decay=0.01),
+                                       dict(params=[b], use_muon=False)])
+    assert opt.param_groups[0]["momentum"] == 0.95 and opt.param_groups[1]["lr"] == 3e-4
+    w0, g = w.detach().clone(), torch.randn(64, 32)
+    w.grad, b.grad = g.clone(), torch.randn(32)
+    loss = opt.step(lambda: torch.tensor(1.5))
+    assert float(loss) == 1.5
+    want = w0 * (1 - 0.05 * 0.01) - 0.05 * muon_update(g.clone(), torch.zeros(64, 32), beta=0.95)
+    assert torch.allclose(w.detach(), want, atol=1e-5)
+    with pytest.raises(AssertionError):
+        SingleDeviceMuonWithAuxAdam([dict(params=[w])])
+
+
+def test_sharded_muon_on_plain_tensors_equals_local_formula():
+    """Without DTensor parameters the sharded class takes the single-device path (with its own defaults)."""
+    torch.manual_seed(5)
+    w = torch.nn.Parameter(torch.randn(32, 64))
+    opt = Muon([dict(params=[w], use_muon=True, lr=0.02)])
+    assert opt.param_groups[0]["rms_scale"] and opt.param_groups[0]["nesterov"]
+    w0, g = w.detach().clone(), torch.randn(32, 64)
+    w.grad = g.clone()
+    opt.step()
+    want = w0 - 0.02 * muon_update(g.clone(), torch.zeros(32, 64), 0.95, True, True)
+    assert torch.allclose(w.detach(), want, atol=1e-5)
+
+
+def test_sharded_muon_two_ranks_gloo():
+    """dim-0 sharded DTensor parameters over 2 gloo ranks: same weights as the full-matrix update on one rank."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29647", os.path.join(HERE, "_gloo_muon_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert r.returncode == 0 and lines, r.stdout[-2000:] + r.stderr[-4000:]
+    for res in json.loads(lines[-1][7:]):
+        assert res["max_diff"] < 1e-5, res
+        assert res["moved"] > 1e-3, res
+        assert res["aux_diff"] < 1e-6, res
+
+
+@pytest.mark.gpu
+def test_newton_schulz_on_own_gemm_matches_fp32_iterations():
+    from templar_b200.ops import functional as OF
+
+    torch.manual_seed(6)
+    for shape in [(256, 256), (512, 256), (256, 1024)]:
+        G = torch.randn(*shape, device="cuda")
+        X = newton_schulz(G).float()
+        ref = _ns_reference(G)
+        assert float((X - ref).norm() / ref.norm()) < 4e-2
+        sv = torch.linalg.svdvals(X)
+        assert float(sv.max()) < 1.3 and 0.9 < float(sv.median()) < 1.1
+    assert int(OF.status_word(torch.device("cuda")).item()) == 0
