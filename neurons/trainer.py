@@ -16,7 +16,6 @@ from __future__ import annotations
 import asyncio
 import math
 from contextlib import nullcontext
-from types import SimpleNamespace
 
 import torch
 import torch.distributed as dist

@@ -21,7 +21,7 @@ import os
 import random
 import sys
 import time
-from collections import defaultdict, deque
+from collections import deque
 from datetime import datetime, timedelta, timezone
 from types import SimpleNamespace
 

@@ -18,7 +18,6 @@ from types import SimpleNamespace
 
 import torch
 
-from ..schemas import Bucket
 
 
 class StaticMetagraph:

@@ -20,7 +20,6 @@ import asyncio
 import hashlib
 import os
 import shutil
-import time
 from dataclasses import dataclass
 from datetime import datetime, timezone
 from pathlib import Path

@@ -21,7 +21,6 @@ directory, in-memory with fault injection), so the whole protocol runs offline.
 from __future__ import annotations
 
 import asyncio
-import io
 import json
 import math
 import os

@@ -20,7 +20,6 @@ Behavioural parity with the reference (paths are relative to its project root):
 from __future__ import annotations
 
 import math
-from typing import Sequence
 
 import torch
 

@@ -16,8 +16,7 @@ loss kernel emits the logit gradient during the forward pass.  All of these go t
 
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.nn as nn

@@ -16,7 +16,6 @@ components/loss.py:18-22.
 
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn.functional as F

@@ -20,7 +20,6 @@ from pathlib import Path
 import torch
 
 from . import functional as OF
-from . import native
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 

@@ -13,7 +13,6 @@ from __future__ import annotations
 import ctypes
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from pathlib import Path
 
 import torch
 

@@ -20,8 +20,7 @@ scalar back to the host.
 
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 import torch
@@ -30,7 +29,7 @@ import torch.distributed as dist
 from .. import compress as C
 from ..ops import functional as OF
 from ..ops import native
-from .flat import FlatLayout, FlatParamStore
+from .flat import FlatParamStore
 
 
 @dataclass

@@ -9,7 +9,6 @@ import asyncio
 import json
 import os
 import sys
-import tempfile
 import time
 from types import SimpleNamespace
 

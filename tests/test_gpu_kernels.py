@@ -1,8 +1,5 @@
 """Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
 
-import math
-
-import numpy as np
 import pytest
 import torch
 import torch.nn.functional as F
@@ -11,7 +8,6 @@ from templar_b200 import compress as C
 from templar_b200.models.llama import ModelArgs, build_model
 from templar_b200.ops import functional as OF
 from templar_b200.ops import native
-from templar_b200.parallel.flat import FlatLayout
 from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
 from templar_b200.utils.synthetic import synthetic_payload
 

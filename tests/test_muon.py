@@ -1,6 +1,5 @@
 """Muon: Newton-Schulz orthogonalisation, the single-device optimizer with auxiliary Adam, the sharded variant."""
 
-import copy
 import json
 import os
 import subprocess
