@@ -26,6 +26,7 @@ import templar_b200 as tplr
 from templar_b200 import model_factory
 from templar_b200.distributed import dist_helper
 from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+from templar_b200.utils.ranges import labelled, phase
 
 
 def _opt_cfg(hparams) -> tuple[str, dict, dict]:
@@ -242,15 +243,17 @@ class Trainer:
         batch_count = batch_tokens = inner_step_count = 0
         entry_loss = None
         try:
-            for batch in loader:
+            for batch in labelled(loader, "Data Loading"):
                 if self.stop_event.is_set():
                     break
-                ids = (batch if isinstance(batch, torch.Tensor) else torch.tensor(batch)).to(dev, dtype=torch.long,
-                                                                                         non_blocking=True)
-                labels = self._labels(ids)
+                with phase("Prepare Inputs"):
+                    ids = (batch if isinstance(batch, torch.Tensor) else torch.tensor(batch)).to(
+                        dev, dtype=torch.long, non_blocking=True)
+                    labels = self._labels(ids)
                 batch_tokens += ids.numel()
                 if engine is not None:
-                    loss = engine.micro_step(ids, labels, 1.0 / accum)
+                    with phase("Forward + Backward Pass"):
+                        loss = engine.micro_step(ids, labels, 1.0 / accum)
                 else:
                     ctx = (torch.autocast(device_type=dev.type, dtype=getattr(self, "amp_dtype", torch.bfloat16))
                            if dev.type == "cuda" else nullcontext())
@@ -273,7 +276,8 @@ class Trainer:
                     if not null_round:
                         scale = self._warmup_scale()
                         if engine is not None:
-                            engine.optimizer_step(lr=self._lr_now() * scale)
+                            with phase("Optimizer Step"):
+                                engine.optimizer_step(lr=self._lr_now() * scale)
                         else:
                             torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
                             saved = [g["lr"] for g in self.inner_optimizer.param_groups]

@@ -38,6 +38,7 @@ from templar_b200.backends.chain import StaticWallet, make_subtensor  # noqa: E4
 from templar_b200.distributed import dist_helper  # noqa: E402
 from templar_b200.metrics import MetricsLogger  # noqa: E402
 from templar_b200.parallel.window_engine import peer_slice  # noqa: E402
+from templar_b200.utils.ranges import phase  # noqa: E402
 from templar_b200.utils.rating import PlackettLuce  # noqa: E402
 from templar_b200.utils.tree import map_tensors, tensor_bytes, to_pinned_cpu  # noqa: E402
 from templar_b200.wandb_ops import initialize_wandb  # noqa: E402
@@ -647,7 +648,8 @@ class Validator(BaseNode, Trainer):
                                                uids=torch.nonzero(pos).flatten().tolist(), weights=self.weights[pos].tolist())
             # consensus update for this window
             self.engine.window_open = True          # theta0 already holds the pre-update weights
-            self.engine.outer_step(n_peers, lr=self.lr, include_own=False, base="theta0")
+            with phase("Outer Step"):
+                self.engine.outer_step(n_peers, lr=self.lr, include_own=False, base="theta0")
             self.engine.window_open = False
             self.global_step += 1
             if self.is_master:

@@ -29,6 +29,7 @@ import torch.nn as nn
 from .compress import unpack_12bit_indices
 from .distributed import dist_helper
 from .logging import P, T, logger
+from .utils.ranges import phase
 
 __all__ = ["prepare_gradient_dict", "outer_step", "update_peers", "load_checkpoint_with_fallback",
            "handle_checkpoint_catchup", "catchup_with_aggregation_server", "compare_model_with_debug_dict",
@@ -154,9 +155,10 @@ def _prepare_gradient_dict_engine(miner, engine, step_window: int, null_round: b
     own = None
     if heap is not None and engine.world_size > 1:
         own = (heap.peer_ptr(engine.own_idx, 0), heap.peer_ptr(engine.own_val, 0))
-    engine.compress(null_round=null_round, own_slot_ptrs=own)
-    if engine.world_size > 1:
-        engine._barrier()
+    with phase("Compress"):
+        engine.compress(null_round=null_round, own_slot_ptrs=own)
+        if engine.world_size > 1:
+            engine._barrier()
     gradient, xshapes, totalks = {}, {}, {}
     L = engine.layout
     want_payload = engine.rank == 0
@@ -310,7 +312,8 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
         engine.distribute_peer_payloads(sd if is_master else None, n_peers)
     if not engine.window_open:
         engine.snapshot()           # catch-up / validator flow: apply to the current weights
-    engine.outer_step(n_peers, lr=lr, include_own=False, base="theta0")
+    with phase("Outer Step"):
+        engine.outer_step(n_peers, lr=lr, include_own=False, base="theta0")
     engine.window_open = False
     # fingerprint: the applied update is (theta0 - theta) / lr on every shard
     d = engine.theta0 - engine.store.master_shard

@@ -21,6 +21,9 @@ import torch.distributed as dist
 from ..ops import native
 
 
+GUARD, GUARD_BYTE = 256, 0xA5
+
+
 class _DeviceBlock:
     """Exposes a raw device allocation through ``__cuda_array_interface__``."""
 
@@ -35,6 +38,7 @@ class SymmetricHeap:
         self.timeout_ns = int(timeout_s * 1e9)
         self._allocs: list[tuple[int, int, list[int]]] = []   # (local_ptr, nbytes, [ptr per rank])
         self._blocks = []
+        self._guards: list[torch.Tensor] = []
         self._epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._flags = None
@@ -52,7 +56,9 @@ class SymmetricHeap:
         esz = torch.empty((), dtype=dtype).element_size()
         nbytes = max(-(-numel * esz // 256) * 256, 256)
         out = ctypes.c_void_p()
-        native.check(L.tplr_heap_alloc(ctypes.c_ulonglong(nbytes), ctypes.byref(out)), "heap_alloc")
+        # GUARD bytes behind every block hold a fixed pattern: a store that runs past the end of a buffer (this
+        # rank's or a peer's) lands there and is found by check_guards() instead of corrupting a neighbour
+        native.check(L.tplr_heap_alloc(ctypes.c_ulonglong(nbytes + GUARD), ctypes.byref(out)), "heap_alloc")
         native.launch_count -= 1
         local = out.value
         hsz = L.tplr_ipc_handle_size()
@@ -73,10 +79,22 @@ class SymmetricHeap:
                 raise native.NativeError(f"cudaIpcOpenMemHandle(rank {r}) failed: {err}")
             ptrs.append(p.value)
         self._allocs.append((local, nbytes, ptrs))
-        block = _DeviceBlock(local, nbytes)
+        block = _DeviceBlock(local, nbytes + GUARD)
         self._blocks.append(block)
         t = torch.as_tensor(block, device=self.device)
-        return t.view(dtype)[:numel]
+        guard = t[nbytes:]
+        guard.fill_(GUARD_BYTE)
+        self._guards.append(guard)
+        return t[:nbytes].view(dtype)[:numel]
+
+    def check_guards(self) -> None:
+        """Host sync; raises if the guard bytes behind any block of this rank were overwritten."""
+        if not self._guards:
+            return
+        bad = torch.stack([(g != GUARD_BYTE).any() for g in self._guards])
+        if bool(bad.any().item()):
+            which = [i for i, b in enumerate(bad.tolist()) if b]
+            raise MemoryError(f"symmetric heap: a store ran past the end of block(s) {which} on rank {self.rank}")
 
     def peer_ptr(self, tensor_or_ptr, rank: int) -> int:
         """Address, in this process, of ``tensor``'s memory inside rank ``rank``'s copy of the allocation."""

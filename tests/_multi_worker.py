@@ -116,6 +116,10 @@ def main():
         out["q_val_max_diff"] = (qeng.own_val - qref.own_val).abs().max().item()
         out["q_val_scale"] = qref.own_val.abs().max().item()
         out["q_codes_equal"] = float((qeng._q_codes == qref._q_codes).float().mean().item())
+    heap.barrier()
+    torch.cuda.synchronize()
+    heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank
+    out["guards_ok"] = True
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

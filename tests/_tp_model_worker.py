@@ -58,6 +58,10 @@ def main():
         worst = max(worst, rel)
         out.setdefault("rel", {})[name] = rel
     out["worst_rel"] = worst
+    heap.barrier()
+    torch.cuda.synchronize()
+    heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank
+    out["guards_ok"] = True
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

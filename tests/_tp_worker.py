@@ -74,6 +74,10 @@ def main():
     out["fsdp_y"] = rel(yg, xa.float() @ Wf.float().t())
     out["fsdp_w"] = float((gw.full.float() - Wf.float()).abs().max())
     out["status"] = int(OF.status_word(dev).item())
+    heap.barrier()
+    torch.cuda.synchronize()
+    heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank
+    out["guards_ok"] = True
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

@@ -31,7 +31,7 @@ def _run(nproc, extra_env=None, worker="_multi_worker.py"):
 def test_two_rank_runtime_and_window():
     res = _run(2)
     for r in res:
-        assert r["push_ok"], r
+        assert r["push_ok"] and r["guards_ok"], r
         assert r["timeout_detected"], r
         assert r["status"] == 0, r
         assert r["moved"] > 1e-4, r
@@ -55,6 +55,7 @@ def test_fused_tensor_parallel_linears():
         assert r["status"] == 0, r
         for k in ("h", "y", "dx", "dw1", "dw2", "fsdp_y"):
             assert r[k] < 2e-2, (k, r)
+        assert r["guards_ok"], r
         assert r["fsdp_w"] == 0.0, r          # the gathered weight buffer is complete after the call
 
 
@@ -64,5 +65,5 @@ def test_tensor_parallel_model_matches_unsharded():
     res = _run(2, worker="_tp_model_worker.py")
     for r in res:
         assert r["status"] == 0, r
-        assert abs(r["loss"] - r["ref_loss"]) < 3e-2, r
+        assert abs(r["loss"] - r["ref_loss"]) < 3e-2 and r["guards_ok"], r
         assert r["worst_rel"] < 0.12, r   # two bf16 pipelines with different summation orders

@@ -381,3 +381,19 @@ def test_small_modules(tmp_path, monkeypatch):
     a, b = m.rate([[m.rating()], [m.rating()]], scores=[1.0, 0.0])
     assert a[0].mu > 25 > b[0].mu and a[0].sigma < 25 / 3
     tplr.log_with_context("info", "hello", window=3, uid=1)
+
+
+def test_phase_ranges_show_up_in_a_profiler_trace():
+    """Phases are record_function scopes: a torch.profiler run lists them by name; iteration is labelled too."""
+    import torch.profiler as tp
+
+    from templar_b200.utils.ranges import labelled, nvtx_enabled, phase
+
+    with tp.profile(activities=[tp.ProfilerActivity.CPU]) as prof:
+        seen = []
+        for x in labelled([1, 2, 3], "Data Loading"):
+            with phase("Forward + Backward Pass"):
+                seen.append(torch.ones(4) * x)
+    names = {e.key for e in prof.key_averages()}
+    assert "Data Loading" in names and "Forward + Backward Pass" in names
+    assert len(seen) == 3 and not nvtx_enabled()
