@@ -127,6 +127,32 @@ def bench_compress(a):
                       "peaks": pk["source"], "status": eng.check_status()}))
 
 
+def bench_quantize(a):
+    """The two steps that the 8-bit payload mode adds after compress: encode (codes + tables) and the
+    error-feedback correction with the dequantised values written back."""
+    eng = _engine(a.model, a.topk, 1)
+    eng.snapshot()
+    eng.store.master_shard.add_(torch.randn_like(eng.store.master_shard) * 1e-3)
+    eng.compress()
+    exact = eng.own_val.clone()
+    eng.cfg.quantize = True
+
+    def both():
+        eng.own_val.copy_(exact)
+        eng._quantize_own(on_rank0=False)
+
+    copy_med, _ = time_ms(lambda: eng.own_val.copy_(exact), a.iters)
+    med, best = time_ms(both, a.iters)
+    enc_med, _ = time_ms(lambda: eng.encode_values(exact), a.iters)
+    n = eng.layout.total
+    byts = n * 4 * 2                      # error feedback read and written
+    pk = peaks()
+    print(json.dumps({"case": "quantize", "model": a.model, "topk": a.topk, "values": int(eng.layout.val_elems),
+                      "ms_median": med - copy_med, "ms_best": best - copy_med, "encode_ms": enc_med,
+                      "gbs": byts / (med - copy_med) / 1e6, "frac_of_hbm": byts / (med - copy_med) / 1e6 / pk["hbm_gbs"],
+                      "peaks": pk["source"], "status": eng.check_status()}))
+
+
 def bench_aggregate(a):
     from ..utils.synthetic import synthetic_payload
 
@@ -185,7 +211,7 @@ def bench_elementwise(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "compress", "aggregate", "elementwise", "attention"])
+    ap.add_argument("case", choices=["gemm", "compress", "quantize", "aggregate", "elementwise", "attention"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=2048)
@@ -202,7 +228,7 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=8)
     a = ap.parse_args()
-    {"gemm": bench_gemm, "compress": bench_compress, "aggregate": bench_aggregate,
+    {"gemm": bench_gemm, "compress": bench_compress, "quantize": bench_quantize, "aggregate": bench_aggregate,
      "elementwise": bench_elementwise, "attention": bench_attention}[a.case](a)
 
 
