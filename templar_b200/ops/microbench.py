@@ -203,6 +203,20 @@ def bench_elementwise(a):
         "swiglu_fwd_bwd": (swiglu_fwd_bwd, T * F * 2 * (3 + 5)),
         "cross_entropy_fwd_bwd": (lambda: OF.cross_entropy(logits.requires_grad_(), labels), T * V * 2 * 3),
     }
+    # fused AdamW on a flat shard: fp32 master / moments / gradient in, master / moments / bf16 copy out
+    from . import native
+    n = (8 if a.small else 64) * 1024 * 1024
+    master, m1, m2 = (torch.zeros(n, device="cuda") for _ in range(3))
+    grad = torch.randn(n, device="cuda") * 1e-3
+    shadow = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    gsq = (grad * grad).sum().reshape(1)
+
+    def adamw():
+        native.check(native.lib().tplr_adamw(master.data_ptr(), m1.data_ptr(), m2.data_ptr(), grad.data_ptr(),
+                                             native.ptr_array([shadow.data_ptr()]), 1, n, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1,
+                                             1.0, 1.0, gsq.data_ptr(), 1, native.stream_ptr()), "adamw")
+
+    cases["adamw"] = (adamw, n * (4 * 4 + 4 * 3 + 4 + 2))      # the gradient is zeroed in the same pass
     for name, (fn, byts) in cases.items():
         med, best = time_ms(fn, a.iters)
         print(json.dumps({"case": name, "ms_median": med, "gbs": byts / med / 1e6,
