@@ -514,7 +514,6 @@ class WindowEngine:
         return idx_ptrs, val_ptrs
 
     @torch.no_grad()
-    @torch.no_grad()
     def compute_peer_norms(self, n_peers: int | None = None, *, include_own: bool = False, peers=None) -> torch.Tensor:
         """Per-(peer, tensor) value norms, their per-tensor lower median, clip factors and skip flags
         (all left on the device in ``peer_norms`` / ``median`` / ``clip`` / ``skip``).  Returns the medians."""
@@ -648,9 +647,8 @@ class WindowEngine:
         self._publish_compute()
 
     # ------------------------------------------------------------------------------------ #
-    # validator: single-peer apply and restore
+    # validator: index overlap, single-peer apply and restore
     # ------------------------------------------------------------------------------------ #
-    @torch.no_grad()
     @torch.no_grad()
     def index_overlap(self, n_peers: int) -> torch.Tensor:
         """[n_peers, n_peers] matrix whose (i, j), i < j, entry is the fraction of (chunk, index) selections that
@@ -668,6 +666,7 @@ class WindowEngine:
         total = sum(s.n_chunks * s.topk(self.layout.topk) for s in self.layout.specs)
         return counts.view(n_peers, n_peers).double() / float(total)
 
+    @torch.no_grad()
     def apply_single_peer(self, peer: int, lr: float, median: torch.Tensor | None = None) -> None:
         """theta <- theta0 - lr * decode(peer's payload), the peer's values clipped per tensor to
         ``min(1, median / (norm + 1e-8))`` where ``median`` is the per-tensor median norm over the
