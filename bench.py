@@ -235,9 +235,14 @@ def run_ours(a):
     e2e = None
     if not a.no_e2e:
         ms_e2e, _, _ = timed(True, a.steps, 1)
+        # bytes of the whole job, like the value: every rank copies its token batches and the payloads of the
+        # peers it hosts from pinned host memory and reads its loss back
+        io = torch.tensor([A * B * (S + 1) * 8 + sum(t.numel() * t.element_size() for pl in host_payload.values() for t in pl),
+                           4], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(io)
         e2e = {"value": tokens_per_step * a.steps / (ms_e2e / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": int(A * B * (S + 1) * 8 + sum(t.numel() * t.element_size() for pl in host_payload.values() for t in pl)),
-               "d2h_bytes_per_step": 4}
+               "h2d_bytes_per_step": int(io[0]), "d2h_bytes_per_step": int(io[1])}
     status = eng.check_status()
     if rank == 0:
         mfu = value / world * args.flops_per_token(S) / 1e12
