@@ -81,7 +81,7 @@ class Trainer:
         hp = self.hparams
         kind, spec, _ = _opt_cfg(hp)
         adam = (getattr(hp, "optimizer", {}) or {}).get("adamw", {}) or {}
-        cfg = EngineConfig(
+        kw = dict(
             topk=getattr(hp, "topk_compression", 32), target_chunk=getattr(hp, "target_chunk", 64),
             use_dct=getattr(hp, "use_dct", False), momentum_decay=getattr(hp, "momentum_decay", 0.95),
             outer_lr=float(getattr(hp, "outer_learning_rate", 0.4)), outer_update=getattr(hp, "outer_update", "sgd"),
@@ -94,8 +94,22 @@ class Trainer:
             quantize=bool(getattr(hp, "payload_quantization", False)) and (self.world_size == 1 or heap is not None),
             quant_bins=min(int(getattr(hp, "quantization_bins", 256)), 256),
             quant_range=float(getattr(hp, "quantization_range", 6)))
+        kw.update(self._muon_engine_args(kind, spec))
+        cfg = EngineConfig(**kw)
         self.engine = WindowEngine(self.model, cfg, device=self.device, rank=self.rank, world_size=self.world_size, heap=heap)
         return self.engine
+
+    def _muon_engine_args(self, kind: str, spec: dict) -> dict:
+        """Engine settings for ``optimizer.type == "muon"``: the same groups, LR scales and decays that
+        :meth:`get_inner_optimizer` builds for the unfused path."""
+        if kind != "muon":
+            return {}
+        return dict(inner_optimizer="muon", inner_lr=float(spec.get("learning_rate", 0.02)),
+                    muon_momentum=float(spec.get("momentum", 0.95)), muon_weight_decay=float(spec.get("weight_decay", 0.01)),
+                    muon_aux_lr_scale=(("head", float(spec.get("head_lr_scale", 0.5))),
+                                       ("embed", float(spec.get("embed_lr_scale", 0.5))),
+                                       ("scalar", float(spec.get("scalar_lr_scale", 0.2)))),
+                    betas=(0.9, 0.95), eps=1e-8, weight_decay=float(getattr(self.hparams, "weight_decay", 0.1)))
 
     def init_optimizers_schedulers(self, validator: bool = False):
         self.lr = float(self.hparams.outer_learning_rate)
@@ -111,8 +125,9 @@ class Trainer:
     def get_inner_optimizer(self, validator: bool):
         kind, spec, _ = _opt_cfg(self.hparams)
         lr = spec.get("learning_rate", 2e-4 if kind == "adamw" else 0.02)
-        if validator or getattr(self, "engine", None) is not None and kind == "adamw":
-            # the engine owns the AdamW state; this stand-in carries the LR for the scheduler
+        if validator or getattr(self, "engine", None) is not None:
+            # the engine owns the optimizer state (fused AdamW, or Muon with auxiliary Adam on the flat
+            # buffers); this stand-in carries the LR for the scheduler
             dummy = torch.nn.Parameter(torch.zeros(1), requires_grad=False)
             return torch.optim.SGD([dummy], lr=lr)
         if kind == "adamw":

@@ -48,6 +48,11 @@ class EngineConfig:
     max_grad_norm: float = 1.0
     max_peers: int = 8
     val_dtype: torch.dtype = torch.float32
+    inner_optimizer: str = "adamw"     # "adamw" (fused kernel) or "muon" (Newton-Schulz on the own GEMM + auxiliary Adam)
+    muon_momentum: float = 0.95
+    muon_nesterov: bool = True
+    muon_weight_decay: float = 0.01
+    muon_aux_lr_scale: tuple = (("head", 0.5), ("embed", 0.5), ("scalar", 0.2))
     quantize: bool = False             # 8-bit value codes on the wire (the reference miner's format)
     quant_bins: int = 256
     quant_range: float = 6.0
@@ -157,6 +162,8 @@ class WindowEngine:
         self.adam_step += 1
         if self.world_size > 1:
             self._reduce_grads()
+        if cfg.inner_optimizer == "muon":
+            return self._muon_step(lr)
         gshard = st.grad[st.lo:st.hi]
         n = st.hi - st.lo
         if self.cuda:
@@ -190,6 +197,109 @@ class WindowEngine:
         p.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + cfg.eps, value=-lr)
         st.grad.zero_()
         self._publish_compute()
+
+    # -- Muon as the inner optimizer ------------------------------------------------------------- #
+    @staticmethod
+    def muon_class(name: str, ndim: int) -> str:
+        """Parameter classes of the reference's Muon set-up (neurons/trainer.py:338-390): matrices of the
+        blocks are orthogonalised, embeddings / the output head / vectors get Adam with their own LR scale."""
+        if "embed" in name:
+            return "embed"
+        if "lm_head" in name or name == "output.weight":
+            return "head"
+        return "muon" if ndim >= 2 else "scalar"
+
+    def _segments(self):
+        """[(spec, class, a, b)]: the part [a, b) (flat element range) of every tensor inside this rank's shard."""
+        st = self.store
+        out = []
+        for s in self.layout.specs:
+            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
+            if a < b:
+                out.append((s, self.muon_class(s.name, len(s.shape)), a, b))
+        return out
+
+    @torch.no_grad()
+    def _muon_step(self, lr: float) -> None:
+        """One inner step with Muon on the hidden matrices and Adam on the rest, on the flat sharded state.
+
+        Gradient clipping by the global norm first, as for AdamW.  ``exp_avg`` is the Muon momentum for the
+        matrices and Adam's first moment for the others.  The momentum-blended direction is written back into
+        the gradient shard, the shards are exchanged so that every rank holds whole matrices, and each rank
+        orthogonalises the matrices that intersect its shard (Newton-Schulz on the own GEMM) and updates its
+        part of the fp32 master weights.  Scaling ``max(1, rows / cols) ** 0.5`` and decoupled weight decay as in
+        the reference's single-device Muon (src/tplr/muon/muon.py:25-186)."""
+        from ..muon.muon import adam_update
+        from ..muon.newton_schulz import newton_schulz
+
+        cfg, st = self.cfg, self.store
+        g = st.grad[st.lo:st.hi]
+        g.mul_(1.0 / self.world_size)
+        self.gnorm_sq.copy_((g * g).sum().reshape(1))
+        if self.world_size > 1:
+            dist.all_reduce(self.gnorm_sq, group=self.group)
+        if cfg.max_grad_norm > 0:
+            g.mul_(torch.clamp(cfg.max_grad_norm / (self.gnorm_sq.sqrt() + 1e-6), max=1.0))
+        segs = self._segments()
+        beta = cfg.muon_momentum
+        for s, cls, a, b in segs:
+            if cls != "muon":
+                continue
+            gs, ms = g[a - st.lo: b - st.lo], self.exp_avg[a - st.lo: b - st.lo]
+            ms.lerp_(gs, 1 - beta)
+            if cfg.muon_nesterov:
+                gs.lerp_(ms, beta)
+            else:
+                gs.copy_(ms)
+        if self.world_size > 1:
+            self._allgather_grad()                  # every rank now holds the whole direction of every matrix
+        scale = dict(cfg.muon_aux_lr_scale)
+        for s, cls, a, b in segs:
+            p = st.master_shard[a - st.lo: b - st.lo]
+            if cls == "muon":
+                u = st.grad[s.offset: s.offset + s.numel].view(s.shape)
+                if u.ndim > 2:
+                    u = u.reshape(u.shape[0], -1)
+                rows, cols = u.shape
+                o = newton_schulz(u).float() * max(1.0, rows / cols) ** 0.5
+                p.mul_(1 - lr * cfg.muon_weight_decay)
+                p.add_(o.reshape(-1)[a - s.offset: b - s.offset], alpha=-lr)
+            else:
+                lo_, hi_ = a - st.lo, b - st.lo
+                upd = adam_update(g[lo_:hi_], self.exp_avg[lo_:hi_], self.exp_avg_sq[lo_:hi_], self.adam_step,
+                                  cfg.betas, cfg.eps)
+                lr_c = lr * scale.get(cls, 1.0)
+                p.mul_(1 - lr_c * cfg.weight_decay)
+                p.add_(upd, alpha=-lr_c)
+        if self.cuda and st.compute is not st.master_shard:
+            native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(),
+                                                     st.compute.data_ptr() + st.lo * st.compute.element_size(),
+                                                     st.hi - st.lo, native.stream_ptr()), "cast_bf16")
+            if self.world_size > 1:
+                self._barrier()
+                self._allgather_compute_native()
+        else:
+            self._publish_compute()
+        if self.world_size > 1:
+            self._barrier()
+        st.grad.zero_()
+
+    def _allgather_grad(self) -> None:
+        """Every rank's gradient shard to every other rank's full-size gradient buffer."""
+        st = self.store
+        if self.cuda and self.heap is not None:
+            self._barrier()                         # nobody still reads the ranges that are overwritten now
+            n = st.hi - st.lo
+            src = st.grad.data_ptr() + st.lo * 4
+            dsts = [self.heap.peer_ptr(st.grad, r) + st.lo * 4 for r in range(self.world_size) if r != self.rank]
+            native.check(native.lib().tplr_push_copy(src, native.ptr_array(dsts), len(dsts), n * 4, native.stream_ptr()),
+                         "push_copy")
+            self._barrier()
+            return
+        for r in range(self.world_size):
+            a, b = self.layout.shard_range(r)
+            dist.broadcast(st.grad[a:b], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                           group=self.group)
 
     def _compute_shadow_ptrs(self) -> list[int]:
         st = self.store

@@ -48,6 +48,33 @@ def main():
         worst = max(worst, float((got - q.detach()).abs().max()))
         moved = max(moved, float((got - w).abs().max()))
     out = {"max_diff": worst, "moved": moved, "aux_diff": float((aux.detach() - ref_aux.detach()).abs().max())}
+
+    # window engine with Muon as the inner optimizer: 2 ranks (each its own micro-batch) == 1 rank (both)
+    from templar_b200.models.llama import ModelArgs, build_model
+    from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+
+    args = ModelArgs(dim=64, n_layers=2, n_heads=2, vocab_size=128, intermediate_size=128, max_seq_len=32)
+    cfg = EngineConfig(inner_optimizer="muon", inner_lr=0.02, muon_momentum=0.9)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, 128, (2, world, 2, 33), generator=g)          # [step, rank, batch, seq + 1]
+    eng = WindowEngine(build_model(args, seed=3), cfg, rank=rank, world_size=world)
+    one = WindowEngine(build_model(args, seed=3), cfg)
+    for step in range(2):
+        t = toks[step, rank]
+        eng.micro_step(t[:, :-1], t[:, 1:], 1.0)
+        eng.optimizer_step()
+        for r in range(world):
+            t = toks[step, r]
+            one.micro_step(t[:, :-1], t[:, 1:], 1.0 / world)
+        one.optimizer_step()
+    full, ref = eng.full_state_dict(), one.full_state_dict()             # fp32 master weights by name (collective)
+    d = torch.cat([(full[k] - ref[k]).abs().reshape(-1) for k in ref])
+    out["engine_exact_frac"] = float((d < 1e-6).float().mean())
+    out["engine_max_diff"] = float(d.max())
+    mine, theirs = dict(eng.model.named_parameters()), dict(one.model.named_parameters())
+    out["engine_compute_diff"] = max(float((mine[k].detach().float() - theirs[k].detach().float()).abs().max()) for k in theirs)
+    start = dict(build_model(args, seed=3).named_parameters())
+    out["engine_moved"] = max(float((ref[k] - start[k].detach()).abs().max()) for k in start)
     res = [None] * world
     dist.all_gather_object(res, out)
     if rank == 0:

@@ -116,6 +116,22 @@ def main():
         out["q_val_max_diff"] = (qeng.own_val - qref.own_val).abs().max().item()
         out["q_val_scale"] = qref.own_val.abs().max().item()
         out["q_codes_equal"] = float((qeng._q_codes == qref._q_codes).float().mean().item())
+
+    # 5. Muon as the inner optimizer: direction shards exchanged over NVLink, Newton-Schulz on the own GEMM
+    mcfg = dataclasses.replace(cfg, inner_optimizer="muon", inner_lr=0.02)
+    meng = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), mcfg, device=dev, rank=rank,
+                        world_size=world, heap=heap)
+    start = meng.store.master_shard.clone()
+    run(meng, [rank], heap)
+    heap.check()
+    mref = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), mcfg, device=dev)
+    run(mref, list(range(world)), None)
+    lo, hi = meng.store.lo, meng.store.hi
+    md = (meng.store.master_shard - mref.store.master_shard[lo:hi]).abs()
+    out["m_status"] = meng.check_status()
+    out["m_mean_diff"], out["m_max_diff"] = md.mean().item(), md.max().item()
+    out["m_moved_mean"] = (mref.store.master_shard[lo:hi] - start).abs().mean().item()
+    out["m_vs_adamw"] = (mref.store.master_shard - ref.store.master_shard).abs().mean().item()
     heap.barrier()
     torch.cuda.synchronize()
     heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank

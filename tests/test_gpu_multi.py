@@ -42,6 +42,9 @@ def test_two_rank_runtime_and_window():
         assert r["q_master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
         assert r["q_ef_max_diff"] < 0.05 * r["q_ef_scale"], r
         assert r["q_ef_vs_exact"] > 0, r
+        # Muon inner optimizer: sharded == single rank up to the bf16 roundings inside Newton-Schulz
+        assert r["m_status"] == 0 and r["m_vs_adamw"] > 0, r
+        assert r["m_mean_diff"] < 0.1 * r["m_moved_mean"] and r["m_max_diff"] < 0.1, r
         if "q_val_max_diff" in r:
             assert r["q_val_max_diff"] < 0.05 * r["q_val_scale"], r
             assert r["q_codes_equal"] > 0.9, r

@@ -130,6 +130,9 @@ def test_sharded_muon_two_ranks_gloo():
         assert res["max_diff"] < 1e-5, res
         assert res["moved"] > 1e-3, res
         assert res["aux_diff"] < 1e-6, res
+        # sharded window engine with Muon: same master weights as one rank, up to bf16 rounding flips in Newton-Schulz
+        assert res["engine_exact_frac"] > 0.9 and res["engine_max_diff"] < 2e-3, res
+        assert res["engine_compute_diff"] < 2e-3 and res["engine_moved"] > 1e-3, res
 
 
 @pytest.mark.gpu
@@ -145,3 +148,52 @@ def test_newton_schulz_on_own_gemm_matches_fp32_iterations():
         sv = torch.linalg.svdvals(X)
         assert float(sv.max()) < 1.3 and 0.9 < float(sv.median()) < 1.1
     assert int(OF.status_word(torch.device("cuda")).item()) == 0
+
+
+def test_engine_muon_step_equals_single_device_muon_with_aux_adam():
+    """The window engine's Muon inner step (flat fp32 state) against the optimizer class on the module tree,
+    with the groups, LR scales and decays the trainer builds for ``optimizer.type == "muon"``."""
+    from templar_b200.models.llama import ModelArgs, build_model
+    from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+
+    args = ModelArgs(dim=64, n_layers=2, n_heads=2, vocab_size=128, intermediate_size=128, max_seq_len=32)
+    torch.manual_seed(0)
+    toks = torch.randint(0, 128, (2, 2, 33))
+    m1 = build_model(args, seed=3)
+    eng = WindowEngine(m1, EngineConfig(inner_optimizer="muon", inner_lr=0.02, muon_momentum=0.9, muon_weight_decay=0.01,
+                                        weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8, max_grad_norm=1.0))
+    m2 = build_model(args, seed=3)
+    groups = {"head": [], "embed": [], "scalar": [], "muon": []}
+    for n, p in m2.named_parameters():
+        groups[WindowEngine.muon_class(n, p.ndim)].append(p)
+    assert groups["muon"] and groups["embed"] and groups["head"] and groups["scalar"]
+    opt = SingleDeviceMuonWithAuxAdam(
+        [dict(params=groups[k], lr=0.02 * sc, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-8, use_muon=False)
+         for k, sc in (("head", 0.5), ("embed", 0.5), ("scalar", 0.2))]
+        + [dict(params=groups["muon"], lr=0.02, momentum=0.9, weight_decay=0.01, use_muon=True)])
+    for step in range(2):
+        t = toks[step]
+        eng.micro_step(t[:, :-1], t[:, 1:], 1.0)
+        eng.optimizer_step(lr=0.02)
+        opt.zero_grad(set_to_none=True)
+        m2.loss(t[:, :-1], t[:, 1:]).backward()
+        torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+        opt.step()
+    diffs = [float((p.detach() - dict(m1.named_parameters())[n].detach()).abs().max()) for n, p in m2.named_parameters()]
+    # identical arithmetic; a last-bit difference in a gradient can flip a bf16 rounding inside Newton-Schulz,
+    # which moves single entries of one matrix by about lr * 1e-2
+    assert sum(d < 1e-6 for d in diffs) >= len(diffs) - 2 and max(diffs) < 1e-3, diffs
+    assert float(eng.store.grad.abs().max()) == 0.0
+
+
+def test_trainer_maps_muon_hparams_to_the_engine():
+    from types import SimpleNamespace
+
+    from neurons.trainer import Trainer
+
+    t = Trainer.__new__(Trainer)
+    t.hparams = SimpleNamespace(weight_decay=0.05)
+    kw = t._muon_engine_args("muon", {"learning_rate": 0.03, "momentum": 0.9, "head_lr_scale": 0.4})
+    assert kw["inner_optimizer"] == "muon" and kw["inner_lr"] == 0.03 and kw["muon_momentum"] == 0.9
+    assert dict(kw["muon_aux_lr_scale"]) == {"head": 0.4, "embed": 0.5, "scalar": 0.2} and kw["weight_decay"] == 0.05
+    assert t._muon_engine_args("adamw", {}) == {}
