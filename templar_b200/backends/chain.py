@@ -18,6 +18,7 @@ from types import SimpleNamespace
 
 import torch
 
+from ..logging import logger
 
 
 class StaticMetagraph:
@@ -77,8 +78,8 @@ class StaticChain:
             try:
                 d = json.loads(self.state_file.read_text())
                 self._commit.update({int(k): v for k, v in d.get("commitments", {}).items()})
-            except Exception:  # noqa: BLE001
-                pass
+            except Exception as e:  # noqa: BLE001
+                logger.warning(f"static chain: state file {self.state_file} is unreadable ({e}); starting empty")
 
     def commit(self, wallet, netuid: int, data: str) -> None:
         uid = self._metagraph.hotkeys.index(wallet.hotkey.ss58_address)

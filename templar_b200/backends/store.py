@@ -307,8 +307,8 @@ class S3Store(ObjectStore):
             except Exception as e:  # noqa: BLE001
                 try:
                     await client.abort_multipart_upload(Bucket=bucket.name, Key=key, UploadId=upload_id)
-                except Exception:  # noqa: BLE001
-                    pass
+                except Exception as abort_err:  # noqa: BLE001
+                    logger.debug(f"abort of multipart upload {upload_id} failed: {abort_err}")
                 if attempt == self.max_retries - 1 or not (restart or _is_named(e, "ClientError", "ConnectionClosedError")):
                     raise
                 logger.warning(f"multipart upload of {key} restarting ({e})")

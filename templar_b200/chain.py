@@ -89,8 +89,8 @@ class ChainManager:
             try:
                 sub.close()
                 sub.initialize()
-            except Exception:  # noqa: BLE001
-                pass
+            except Exception as e:  # noqa: BLE001
+                logger.debug(f"substrate reconnect failed: {e}")
 
     # -- commitments ----------------------------------------------------------------------------
     def get_bucket(self, uid: int) -> Bucket | None:

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 from pathlib import Path
 
 REQUIRED_VARS = [
@@ -66,8 +67,8 @@ def load_bucket_secrets(strict: bool | None = None) -> dict:
             cfgs = json.loads(raw.strip())
             if isinstance(cfgs, list) and cfgs:
                 secrets["dataset"] = {"multiple": cfgs}
-        except Exception:
-            pass
+        except Exception as e:  # noqa: BLE001
+            print(f"R2_DATASET_BUCKET_LIST is not valid JSON ({e}); using the single dataset bucket", file=sys.stderr)
     if strict is None:
         strict = os.environ.get("TPLR_STRICT_ENV", "0") == "1"
     miss = missing_env()

@@ -292,8 +292,8 @@ class DCPCheckpointer:
                         next(local_dir.iterdir())
                     except StopIteration:
                         local_dir.rmdir()
-                    except Exception:  # noqa: BLE001
-                        pass
+                    except OSError as e:
+                        logger.debug(f"[DCP] could not inspect {local_dir}: {e}")
 
         if background:
             t = asyncio.create_task(_do())
@@ -314,8 +314,8 @@ class DCPCheckpointer:
                 bucket, _ = await self.comms._get_highest_stake_validator_bucket()
                 if bucket is not None:
                     return bucket
-            except Exception:  # noqa: BLE001
-                pass
+            except Exception as e:  # noqa: BLE001
+                logger.debug(f"[DCP] highest-stake validator bucket not available ({e}); reading from the own bucket")
         return self.comms.bucket
 
     async def _discover_latest(self, *, prefer_highest_staked: bool = True) -> int | None:
@@ -324,8 +324,8 @@ class DCPCheckpointer:
             obj = await self.comms.s3_get_object(key=f"checkpoints/{self.version}/_LATEST.json", bucket=bucket)
             if isinstance(obj, dict) and "latest_window" in obj:
                 return int(obj["latest_window"])
-        except Exception:  # noqa: BLE001
-            pass
+        except Exception as e:  # noqa: BLE001
+            logger.debug(f"[DCP] no readable _LATEST.json ({e}); listing the checkpoint prefix instead")
         prefix = Layout(self.version).prefix + "/"
         windows = set()
         for o in await self.comms.store.list(bucket, prefix):
