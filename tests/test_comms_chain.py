@@ -294,3 +294,69 @@ def test_decorators_and_config(monkeypatch):
     assert config.load_bucket_secrets(strict=False)["dataset"]["multiple"][1]["name"] == "d2"
     r = tplr.CommsGetResult(status="OK")
     assert not r.success and tplr.CommsGetResult(data={}, status="OK").success
+
+
+class _RangeBody:
+    def __init__(self, data):
+        self.data = data
+
+    async def __aenter__(self):
+        return self
+
+    async def __aexit__(self, *exc):
+        return None
+
+    async def read(self):
+        return self.data
+
+
+class _FakeRangedS3:
+    """get_object with Range; the first ``flaky`` requests of chunk 1 return short data, ``dead`` chunks always fail."""
+
+    def __init__(self, data, flaky=0, dead=()):
+        self.data, self.flaky, self.dead, self.requests = data, flaky, set(dead), []
+
+    async def head_object(self, Bucket, Key):
+        from datetime import datetime, timezone
+        return {"ContentLength": len(self.data), "LastModified": datetime.now(timezone.utc)}
+
+    async def get_object(self, Bucket, Key, Range=None):
+        lo, hi = (int(x) for x in Range.split("=")[1].split("-"))
+        self.requests.append((lo, hi))
+        if lo in self.dead:
+            raise IOError("connection reset")
+        if self.flaky > 0 and lo > 0:
+            self.flaky -= 1
+            return {"Body": _RangeBody(self.data[lo: hi])}            # one byte short
+        return {"Body": _RangeBody(self.data[lo: hi + 1])}
+
+
+def test_ranged_download_retries_short_chunks_and_resumes(tmp_path, monkeypatch):
+    monkeypatch.setattr(asyncio, "sleep", _fast_sleep(asyncio.sleep))
+    data = os.urandom(10_000)
+    b = Bucket(name="bkt", account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+    out = tmp_path / "big.bin"
+
+    # 1. short reads are retried; the file is complete and the progress file is gone
+    fake = _FakeRangedS3(data, flaky=2)
+    st = S3Store(client_factory=lambda bk: fake, max_retries=4)
+    monkeypatch.setattr(st, "download_plan", lambda size, workers=None: (3000, 2))
+    assert run(st.download_large_file(b, "big.bin", len(data), str(out)))
+    assert out.read_bytes() == data and not (tmp_path / "big.bin.progress").exists()
+    assert len(fake.requests) == 4 + 2
+
+    # 2. a chunk that never arrives: the call reports failure and records the finished chunks
+    out.unlink()
+    fake = _FakeRangedS3(data, dead=(6000,))
+    st = S3Store(client_factory=lambda bk: fake, max_retries=2)
+    monkeypatch.setattr(st, "download_plan", lambda size, workers=None: (3000, 2))
+    assert not run(st.download_large_file(b, "big.bin", len(data), str(out)))
+    done = {int(x) for x in (tmp_path / "big.bin.progress").read_text().split()}
+    assert done == {0, 1, 3}
+
+    # 3. the next attempt fetches only the missing chunk
+    fake = _FakeRangedS3(data)
+    st = S3Store(client_factory=lambda bk: fake, max_retries=2)
+    monkeypatch.setattr(st, "download_plan", lambda size, workers=None: (3000, 2))
+    assert run(st.download_large_file(b, "big.bin", len(data), str(out)))
+    assert fake.requests == [(6000, 8999)] and out.read_bytes() == data
