@@ -344,11 +344,11 @@ class DCPCheckpointer:
             if window is None:
                 return None
         layout = Layout(self.version, window)
-        local_dir = self._local_dir(layout)
         bucket = await self._choose_read_bucket(prefer_highest_staked)
         objs = await _retry_n(lambda: self.comms.store.list(bucket, f"{layout.prefix}/"), desc=f"LIST {layout.prefix}/")
         if not objs:
-            return None
+            return None                 # no local directory is made for a window that does not exist remotely
+        local_dir = self._local_dir(layout)
         await asyncio.gather(*(self._fetch(bucket, o.key, local_dir) for o in objs))
         return local_dir
 
@@ -361,12 +361,12 @@ class DCPCheckpointer:
             if window is None:
                 return None
         layout = Layout(self.version, window)
-        local_dir = self._local_dir(layout)
         bucket = await self._choose_read_bucket(prefer_highest_staked)
         world, r = _world(process_group), _rank(process_group)
         objs = await _retry_n(lambda: self.comms.store.list(bucket, f"{layout.prefix}/"), desc=f"LIST {layout.prefix}/")
         if not objs:
             return None
+        local_dir = self._local_dir(layout)
         mine = []
         for o in objs:
             if _is_meta(o.key):
@@ -434,6 +434,16 @@ class DCPCheckpointer:
         base = self.repo_root / Layout(self.version).prefix
         if not base.is_dir():
             return
-        wins = sorted((int(p.name) for p in base.iterdir() if p.is_dir() and p.name.isdigit()), reverse=True)
-        for w in wins[keep_latest:]:
-            shutil.rmtree(base / str(w), ignore_errors=True)
+        dirs = [p for p in base.iterdir() if p.is_dir() and p.name.isdigit()]
+        # only directories that hold a finished checkpoint count as "latest".  Empty directories go; a partial
+        # one goes when a newer finished checkpoint exists, otherwise it may be a save in progress and stays
+        whole = sorted((int(p.name) for p in dirs if (p / ".metadata").exists()), reverse=True)
+        keep = set(whole[:keep_latest])
+        for p in dirs:
+            n = int(p.name)
+            if n in keep:
+                continue
+            finished = (p / ".metadata").exists()
+            empty = not any(p.iterdir())
+            if finished or empty or (whole and n < whole[0]):
+                shutil.rmtree(p, ignore_errors=True)
