@@ -347,3 +347,81 @@ def test_engine_quantised_window_equals_generic_functions():
     from templar_b200.parallel.window_engine import peer_slice
     eng.load_peer_payload(0, peer_slice({k: [v] for k, v in sent.items() if k != "metadata"}, 0), non_blocking=False)
     assert torch.allclose(eng.peer_val[0], eng.own_val, atol=1e-7)
+
+
+class _CatchupComms:
+    """Serves the leader's aggregated gradients / debug dicts per window; records what was asked for."""
+
+    def __init__(self, aggregated: dict, debug: dict, live=None):
+        self.aggregated, self.debug, self.live = aggregated, debug, live
+        self.metagraph = SimpleNamespace(S=torch.tensor([1.0, 9.0, 2.0]))       # leader = uid 1
+        self.peers, self.asked, self.gathers = [0, 2], [], []
+
+    async def get(self, uid, window, key, **kw):
+        self.asked.append((uid, window, key))
+        src = self.aggregated if key == "aggregator" else self.debug
+        data = src.get(window)
+        return SimpleNamespace(success=data is not None, data=data)
+
+    async def gather(self, **kw):
+        self.gathers.append(kw["window"])
+        return self.live
+
+
+def _catchup_instance(model, comms, current_window, tr, comp, xs, tk, lr=0.5):
+    sched_steps = []
+    inst = SimpleNamespace(
+        model=model, comms=comms, start_window=10, current_window=current_window, is_master=True, world_size=1, uid=0,
+        config=SimpleNamespace(device="cpu"), hparams=SimpleNamespace(blocks_per_window=4, inner_steps=3, use_dct=True,
+                                                                      time_window_delta_seconds=12),
+        outer_optimizer=torch.optim.SGD(model.parameters(), lr=lr), transformer=tr, compressor=comp, xshapes=xs, totalks=tk,
+        global_step=0, inner_scheduler=SimpleNamespace(step=lambda: sched_steps.append(1)), inner_scheduler_step_count=0,
+        should_skip_scheduler_step=lambda: False, query_block_timestamp=lambda b: 1000.0 + b, local_rank=0)
+    return inst, sched_steps
+
+
+def _as_payload(gr):
+    return {"state_dict": vars(gr.state_dict), "uids": gr.uids, "skipped_uids": [], "success_rate": 1.0}
+
+
+def test_catchup_replays_available_windows_skips_gaps_and_falls_back_to_a_live_gather():
+    model, ref = Tiny(), Tiny()
+    ref.load_state_dict(model.state_dict())
+    g11, tr, comp, xs, tk = _gather_result(model, 2, seed=11)
+    g13 = _gather_result(model, 2, seed=13)[0]
+    g14 = _gather_result(model, 2, seed=14)[0]
+    # windows 11 and 13 were aggregated by the leader, 12 is missing, 14 (the last one) only exists as live gradients
+    comms = _CatchupComms({11: _as_payload(g11), 13: _as_payload(g13)}, {}, live=g14)
+    inst, sched = _catchup_instance(model, comms, current_window=15, tr=tr, comp=comp, xs=xs, tk=tk)
+    asyncio.run(tplr.neurons.catchup_with_aggregation_server(inst, 10))
+    opt = torch.optim.SGD(ref.parameters(), lr=0.5)
+    for gr in (g11, g13, g14):
+        tplr.outer_step(ref, opt, gather_result=gr, transformer=tr, compressor=comp, xshapes=xs, totalks=tk, device="cpu",
+                        is_master=True, world_size=1, use_dct=True)
+    for (n, a), (_, b) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(a.detach(), b.detach(), atol=1e-6), n
+    assert inst.global_step == 3 and len(sched) == 9 and inst.inner_scheduler_step_count == 9       # 3 applied windows x 3
+    assert comms.gathers == [14]                                # live gather only for the last window
+    assert [w for (_, w, k) in comms.asked if k == "aggregator"] == [11, 12, 13, 14]
+    assert all(uid == "1" for uid, _, _ in comms.asked)
+
+
+def test_catchup_follows_the_chain_head_and_survives_a_failed_fallback():
+    model = Tiny()
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    g11, tr, comp, xs, tk = _gather_result(model, 2, seed=21)
+    g12 = _gather_result(model, 2, seed=22)[0]
+    comms = _CatchupComms({11: _as_payload(g11), 12: _as_payload(g12)}, {}, live=None)
+    inst, _ = _catchup_instance(model, comms, current_window=12, tr=tr, comp=comp, xs=xs, tk=tk)
+    real_get = comms.get
+
+    async def get_and_advance(uid, window, key, **kw):
+        if key == "aggregator" and window == 11:
+            inst.current_window = 14                           # the chain moved on while we were replaying
+        return await real_get(uid, window, key, **kw)
+
+    comms.get = get_and_advance
+    asyncio.run(tplr.neurons.catchup_with_aggregation_server(inst, 10))
+    # 11 and 12 applied; 13 has neither aggregated nor live gradients and is skipped without an error
+    assert inst.global_step == 2 and comms.gathers == [13]
+    assert any(not torch.equal(p.detach(), before[n]) for n, p in model.named_parameters())
