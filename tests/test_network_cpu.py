@@ -397,3 +397,62 @@ def test_phase_ranges_show_up_in_a_profiler_trace():
     names = {e.key for e in prof.key_averages()}
     assert "Data Loading" in names and "Forward + Backward Pass" in names
     assert len(seen) == 3 and not nvtx_enabled()
+
+
+def test_quantised_payloads_travel_through_the_store_and_keep_nodes_in_sync(cwd_tmp):
+    """Miners send 8-bit codes with per-tensor tables (the reference wire format); peers and the validator decode
+    them when they stage the gathered payloads and end with the same weights."""
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        miners = [_node(Miner, Miner.miner_config, ["--uid", str(u), "--peers", "2", "3"], store, chain) for u in (2, 3)]
+        for n in miners + [v]:
+            n.loop = asyncio.get_running_loop()
+            n.comms.commitments = await n.comms.get_commitments()
+            n.comms.peers = [2, 3]
+            n.gather_timeout = 5
+            await n.dataset_manager.initialize_datasets(0)
+        for m in miners:
+            m.set_dataloader()
+            m.engine.cfg.quantize, m.engine.cfg.quant_bins = True, 64
+        v.set_dataloader(validator=True)
+        for w in range(1, 3):
+            for m in miners:
+                m.current_window = m.comms.current_window = w
+            res = await asyncio.gather(*(m.run_window(w) for m in miners))
+            assert all(r["gather_success_rate"] == 1.0 for r in res)
+            got = await v.comms.get(uid="2", window=w, key="gradient", local=False, stale_retention=10)
+            vals = [t for k, t in got.data.items() if k.endswith("vals")]
+            assert vals and all(t.dtype == torch.uint8 and int(t.max()) < 64 for t in vals)
+            assert all(got.data[k] is not None for k in got.data if k.endswith("quant_params"))
+            v.current_window, v.comms.current_window, v.sync_window = w + 1, w, w
+            out = await v.run_window()
+            assert sorted(out["gathered"]) == [2, 3]
+        await v.ckpt.flush_background_uploads()
+        pm = [dict(m.model.named_parameters()) for m in miners]
+        pv = dict(v.model.named_parameters())
+        for n in pm[0]:
+            assert torch.allclose(pm[0][n], pm[1][n], atol=1e-6), n
+            assert torch.allclose(pm[0][n], pv[n], atol=1e-5), n
+    run(go())
+
+
+def test_miner_window_with_muon_as_the_inner_optimizer(cwd_tmp):
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        m = _node(Miner, Miner.miner_config, ["--uid", "2", "--peers", "2"], store, chain)
+        m.loop = asyncio.get_running_loop()
+        m.comms.commitments = await m.comms.get_commitments()
+        m.comms.peers = [2]
+        m.gather_timeout = 5
+        await m.dataset_manager.initialize_datasets(0)
+        m.set_dataloader()
+        m.engine.cfg.inner_optimizer = "muon"
+        before = {n: p.detach().clone() for n, p in m.model.named_parameters()}
+        m.current_window = m.comms.current_window = 1
+        res = await m.run_window(1)
+        assert res["global_step"] == 1 and res["gather_success_rate"] == 1.0
+        moved = [float((p.detach() - before[n]).abs().max()) for n, p in m.model.named_parameters()]
+        assert all(x == x for x in moved) and max(moved) > 0            # finite, and the model changed
+        assert float(m.engine.exp_avg.abs().max()) > 0                  # Muon momentum / Adam moment were written
+    run(go())
