@@ -360,3 +360,37 @@ def test_ranged_download_retries_short_chunks_and_resumes(tmp_path, monkeypatch)
     monkeypatch.setattr(st, "download_plan", lambda size, workers=None: (3000, 2))
     assert run(st.download_large_file(b, "big.bin", len(data), str(out)))
     assert fake.requests == [(6000, 8999)] and out.read_bytes() == data
+
+
+def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
+    store, chain, comms = net
+    totalks, xshapes = {"w.": 4096}, {"w.": (2, 2, 64, 64)}
+    comp = C.TopKCompressor(use_quantization=True, quantization_bins=16)
+
+    def qpayload(seed, *, shift=None, scale=None, lookup_nan=False, drop_params=False):
+        g = torch.Generator().manual_seed(seed)
+        idx, q, xshape, totalk, qp = comp.compress(torch.randn(2, 2, 64, 64, generator=g), 4)
+        sh, sc, off, lut, dt = qp
+        lut = lut.clone()
+        if lookup_nan:
+            lut[3] = float("nan")
+        qp = (sh if shift is None else torch.tensor(shift), sc if scale is None else scale, off, lut, dt)
+        return {"w.idxs": idx, "w.vals": q, "w.quant_params": None if drop_params else qp}
+
+    async def go():
+        await comms[0].put(qpayload(0), window=5, key="gradient", uid="0", local=False)
+        await comms[1].put(qpayload(1, shift=float("inf")), window=5, key="gradient", uid="1", local=False)
+        await comms[2].put(qpayload(2, scale=0.0), window=5, key="gradient", uid="2", local=False)
+        await comms[3].put(qpayload(3, lookup_nan=True), window=5, key="gradient", uid="3", local=False)
+        res = await comms[0].gather(my_uid=0, uids=[0, 1, 2, 3], window=5, key="gradient", timeout=2, device="cpu",
+                                    totalks=totalks, local=False, xshapes=xshapes, compressor=comp)
+        assert res.uids == [0] and sorted(res.skipped_uids) == [1, 2, 3]
+        sd = vars(res.state_dict)
+        assert sd["w.vals"][0].dtype == torch.uint8 and len(sd["w.quant_params"]) == 1      # codes kept, tables beside them
+        deq = comp.maybe_dequantize_values(sd["w.vals"], sd["w.quant_params"], "cpu")
+        assert deq[0].dtype == torch.float32 and torch.isfinite(deq[0]).all()
+        # codes without their table are refused
+        await comms[1].put(qpayload(4, drop_params=True), window=6, key="gradient", uid="1", local=False)
+        assert await comms[0].gather(my_uid=0, uids=[1], window=6, key="gradient", timeout=1, device="cpu", totalks=totalks,
+                                     local=False, xshapes=xshapes, compressor=comp) is None
+    run(go())
