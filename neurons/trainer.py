@@ -89,9 +89,11 @@ class Trainer:
             inner_lr=float(adam.get("learning_rate", 2e-4)), betas=tuple(adam.get("betas", [0.9, 0.95])),
             eps=float(adam.get("eps", 1e-8)), weight_decay=float(adam.get("weight_decay", 0.1)), max_grad_norm=1.0,
             max_peers=max_peers or (getattr(hp, "gather_peer_count", 8) + getattr(hp, "reserve_peer_count", 0)),
-            # 8-bit value codes on the wire (what the reference's miner always sends); a sharded engine needs
-            # the symmetric heap for it, because the statistics are per whole tensor
-            quantize=bool(getattr(hp, "payload_quantization", False)) and (self.world_size == 1 or heap is not None),
+            # 8-bit value codes on the wire (what the reference's miner always sends); the statistics are per
+            # whole tensor, so a sharded CUDA engine needs the symmetric heap for it (the CPU path merges the
+            # payload with a collective)
+            quantize=bool(getattr(hp, "payload_quantization", False))
+            and (self.world_size == 1 or heap is not None or torch.device(self.device).type == "cpu"),
             quant_bins=min(int(getattr(hp, "quantization_bins", 256)), 256),
             quant_range=float(getattr(hp, "quantization_range", 6)))
         kw.update(self._muon_engine_args(kind, spec))

@@ -158,6 +158,7 @@ def _prepare_gradient_dict_engine(miner, engine, step_window: int, null_round: b
     with phase("Compress"):
         engine.compress(null_round=null_round, own_slot_ptrs=own)
         if engine.world_size > 1:
+            engine.merge_own_payload()              # no-op with a heap: the ranks wrote into rank 0's buffers
             engine._barrier()
     gradient, xshapes, totalks = {}, {}, {}
     L = engine.layout

@@ -357,9 +357,13 @@ class WindowEngine:
         (or into ``own_slot_ptrs``, e.g. the hosting rank's buffers in peer memory).
         """
         cfg, st = self.cfg, self.store
+        self._own_merged = False
         if not self.cuda:
             return self._compress_torch(null_round)
         idx_ptr, val_ptr = own_slot_ptrs or (self.own_idx.data_ptr(), self.own_val.data_ptr())
+        if self.world_size > 1 and own_slot_ptrs is None:
+            self.own_idx.zero_()                    # only this rank's chunks are written: the rest must read as
+            self.own_val.zero_()                    # zero for merge_own_payload()
         # flat pointers are biased so that descriptor offsets (full-model) address the shard arrays
         bias = st.lo * 4
         L = native.lib()
@@ -429,18 +433,38 @@ class WindowEngine:
                                                  at0(codes), at0(table), cfg.quant_bins, int(cfg.use_dct),
                                                  int(not square), native.stream_ptr()), "requant_residual")
 
+    def merge_own_payload(self) -> None:
+        """Sharded engine without a symmetric heap: every rank has written only its own chunks of the node's
+        payload (the rest of the buffers is zero), so the sum over ranks is the whole payload on every rank.
+        With a heap the ranks write straight into rank 0's buffers and nothing is left to merge."""
+        if self.world_size == 1 or self.heap is not None or getattr(self, "_own_merged", False):
+            return
+        self._own_merged = True                       # once per compress(): a second sum would scale the values
+        dist.all_reduce(self.own_val, group=self.group)
+        idx32 = self.own_idx.to(torch.int32)          # the byte ranges are disjoint: a sum is a merge
+        dist.all_reduce(idx32, group=self.group)
+        self.own_idx.copy_(idx32.to(torch.uint8))
+
     def _compress_torch(self, null_round: bool) -> None:
-        """CPU oracle path: the same arithmetic through :mod:`templar_b200.compress`, tensor by tensor."""
+        """CPU oracle path: the same arithmetic through :mod:`templar_b200.compress`, tensor by tensor.
+
+        Unsharded with ``quantize``: the reference's literal flow (compress with a quantising compressor,
+        residual against the dequantised values).  Sharded with ``quantize``: exact values first, merge of the
+        payload over the ranks, the per-tensor statistics on the whole tensors (the same on every rank), then
+        each rank adds decode(exact - dequantised) of its own chunks back into its error feedback."""
         cfg, st, L = self.cfg, self.store, self.layout
-        if cfg.quantize and self.world_size > 1:
-            raise NotImplementedError("the CPU path quantises whole tensors: run it unsharded")
+        sharded = self.world_size > 1
         tr = C.ChunkingTransformer(None, cfg.target_chunk)
-        comp = C.TopKCompressor(use_quantization=cfg.quantize, quantization_bins=cfg.quant_bins,
+        comp = C.TopKCompressor(use_quantization=cfg.quantize and not sharded, quantization_bins=cfg.quant_bins,
                                 quantization_range=int(cfg.quant_range))
         if cfg.quantize:
             codes, table, _ = self._quant_buffers()
-        for s, r0, nrows in (L.shard_entries(self.rank) if self.world_size > 1
-                             else [(s, 0, s.chunk_rows) for s in L.specs]):
+        if sharded:
+            self.own_idx.zero_()
+            self.own_val.zero_()
+        entries = L.shard_entries(self.rank) if sharded else [(s, 0, s.chunk_rows) for s in L.specs]
+        parts = []
+        for s, r0, nrows in entries:
             a = s.offset + r0 * s.h * s.cols - st.lo
             b = a + nrows * s.h * s.cols
             shape = (nrows * s.h, s.cols) if len(s.shape) >= 2 else (s.cols,)
@@ -461,6 +485,7 @@ class WindowEngine:
             io = L.idx_off[s.name] + c0 * (k // 2) * 3
             vo = L.val_off[s.name] + c0 * k
             self.own_idx[io: io + idx.numel()].copy_(idx)
+            parts.append((s, e, shape, idx, val, xshape, totalk, vo))
             if qp is not None:                      # the payload keeps what a receiver decodes
                 codes[vo: vo + val.numel()].copy_(val.reshape(-1))
                 shift, scale, _, lookup, _ = qp
@@ -468,6 +493,24 @@ class WindowEngine:
                 table[s.index, cfg.quant_bins], table[s.index, cfg.quant_bins + 1] = float(shift), float(scale)
                 val = comp._dequantize_values(val, qp)
             self.own_val[vo: vo + val.numel()].copy_(val.reshape(-1))
+        if not (cfg.quantize and sharded):
+            return
+        self.merge_own_payload()
+        qcomp = C.TopKCompressor(use_quantization=True, quantization_bins=cfg.quant_bins,
+                                 quantization_range=int(cfg.quant_range))
+        for s in L.specs:                           # whole tensors: identical statistics on every rank
+            _, v = L.payload_views(self.own_idx, self.own_val, s.name)
+            _, c = L.payload_views(self.own_idx, codes, s.name)
+            q, (shift, scale, _, lookup, _) = qcomp._quantize_values(v.float())
+            c.copy_(q.reshape(c.shape))
+            table[s.index, : cfg.quant_bins] = lookup
+            table[s.index, cfg.quant_bins], table[s.index, cfg.quant_bins + 1] = float(shift), float(scale)
+            v.copy_((lookup[q.long()] + shift).reshape(v.shape))
+        plain = C.TopKCompressor(use_quantization=False)
+        for s, e, shape, idx, val, xshape, totalk, vo in parts:
+            tr.register_shape(shape)
+            diff = val - self.own_val[vo: vo + val.numel()].view(val.shape)
+            e.add_(tr.decode(plain.decompress(e, idx, diff, xshape, totalk), use_dct=cfg.use_dct))
 
     def own_payload(self, quantize: bool | None = None, n_bins: int | None = None,
                     range_in_sigmas: float | None = None) -> dict:

@@ -45,10 +45,7 @@ def main():
     t0 = time.perf_counter()
     eng.compress()
     # exchange: every rank's payload part is summed into the full node payload (parts are disjoint)
-    dist.all_reduce(eng.own_val)
-    idx32 = eng.own_idx.to(torch.int32)
-    dist.all_reduce(idx32)
-    eng.own_idx.copy_(idx32.to(torch.uint8))
+    eng.merge_own_payload()
     # the "two peers": this node's payload and a second, perturbed copy standing for the other peer
     eng.peer_idx[1].copy_(eng.own_idx)
     eng.peer_val[1].copy_(eng.own_val * 0.5)

@@ -39,3 +39,13 @@ def test_tensor_parallel_sharding_matches_unsharded_model():
         assert abs(r["loss"] - r["ref_loss"]) < 1e-4, r
         assert r["worst_rel"] < 1e-3, r
         assert r["ckpt_loss_diff"] < 1e-6 and r["ckpt_grad_diff"] < 1e-5, r      # activation checkpointing changes nothing
+
+
+def test_sharded_quantised_compress_matches_unsharded():
+    """2 gloo ranks: payload merged over the ranks, per-tensor statistics on whole tensors, every rank corrects the
+    error feedback of its own chunks; same codes, tables, values and error feedback as one rank."""
+    res = launch(2, [], worker="_gloo_quant_worker.py", port=29645)
+    assert len(res) == 2
+    for r in res:
+        assert r["codes_equal"] == 1.0 and r["table"] < 1e-9 and r["val"] < 1e-9, r
+        assert r["ef"] < 1e-6 * max(r["ef_scale"], 1e-3) + 2e-9, r
