@@ -427,6 +427,12 @@ class Validator(BaseNode, Trainer):
     async def slash_for_poor_sync(self) -> None:
         res = await asyncio.gather(*(self.evaluate_miner_sync(u) for u in self.comms.peers))
         for info, uid in zip(res, self.comms.peers):
+            if info.get("success", False) and self.metrics_logger is not None:
+                self.metrics_logger.log("validator_sync_score",
+                                        tags={"uid": str(uid), "window": int(self.sync_window), "global_step": int(self.global_step)},
+                                        fields={k: float(info.get(k, 0.0)) for k in
+                                                ("l2_norm", "avg_l2_norm", "avg_abs_diff", "max_diff", "avg_steps_behind",
+                                                 "max_steps_behind", "sync_score")})
             if not info.get("success", False) or info.get("avg_steps_behind", 99.0) > self.hparams.sync_max_steps_behind:
                 if self.final_scores[uid] > 0:
                     self.final_scores[uid] *= self.sync_score_slash_rate
@@ -446,8 +452,15 @@ class Validator(BaseNode, Trainer):
                 self.reset_peer(uid)
                 continue
             if self.final_scores[uid] > 0:
+                before = float(self.final_scores[uid])
                 self.final_scores[uid] *= (1.0 - self.inactivity_slash_rate)
                 self.binary_moving_averages[uid] *= (1.0 - self.inactivity_slash_rate)
+                if self.metrics_logger is not None:
+                    self.metrics_logger.log("validator_inactivity",
+                                            tags={"uid": str(uid), "window": int(self.current_window),
+                                                  "global_step": int(self.global_step)},
+                                            fields={"score_before": before, "score_after": float(self.final_scores[uid])},
+                                            with_system_metrics=True, with_gpu_metrics=True)
 
     # ------------------------------------------------------------------------------------ #
     # peer lists and evaluation bins
@@ -614,11 +627,13 @@ class Validator(BaseNode, Trainer):
             if self.config.local:
                 tmin = tmax = None
             if self.comms.peers:
+                t_gather = tplr.T()
                 gather_result = await self.comms.gather_with_reserve(
                     my_uid=self.uid, gather_uids=list(self.comms.peers), reserve_uids=list(self.comms.reserve_peers),
                     window=self.sync_window, key="gradient", timeout=getattr(self, "gather_timeout", 75), device="cpu",
                     local=False, totalks=self.totalks, xshapes=self.xshapes, compressor=self.compressor, time_min=tmin,
                     time_max=tmax, expected_compressed_params=self.expected_compressed_params)
+                self.log_timing("gather", tplr.T() - t_gather)
         skip = torch.tensor([0 if (not self.is_master or gather_result is not None) else 1], dtype=torch.int32, device=self.device)
         dist_helper.broadcast(skip, src=0)
         for _ in range(hp.inner_steps):            # LR bookkeeping only
@@ -638,7 +653,9 @@ class Validator(BaseNode, Trainer):
                 self.slash_for_missing_gradients(list(gather_result.skipped_uids), float(gather_result.success_rate))
                 self.note_delivered(list(gather_result.uids))
                 self.offload_gather_results(gather_result, log=False)
+            t_eval = tplr.T()
             scored = await self.score_peers(gather_result, n_peers)
+            self.log_timing("evaluation", tplr.T() - t_eval)
             if self.is_master:
                 self.apply_negative_evaluation_penalties()
                 self.update_and_log_evals()
@@ -648,11 +665,14 @@ class Validator(BaseNode, Trainer):
                                                uids=torch.nonzero(pos).flatten().tolist(), weights=self.weights[pos].tolist())
             # consensus update for this window
             self.engine.window_open = True          # theta0 already holds the pre-update weights
+            t_outer = tplr.T()
             with phase("Outer Step"):
                 self.engine.outer_step(n_peers, lr=self.lr, include_own=False, base="theta0")
+            self.log_timing("outer_step", tplr.T() - t_outer)
             self.engine.window_open = False
             self.global_step += 1
             if self.is_master:
+                self._log_gradient_stats(n_peers)
                 self._track_param_change()
                 await self._publish_debug()
             if self.global_step % max(getattr(hp, "checkpoint_frequency", 10), 1) == 0:
@@ -785,6 +805,32 @@ class Validator(BaseNode, Trainer):
                         "loss_after_random": loss_after_random, "seconds": time.time() - t0})
         eng.window_open = False
         return out
+
+    def _log_gradient_stats(self, n_peers: int) -> None:
+        """``validator_gradient_stats`` (reference neurons/validator.py:2466-2545): statistics of the gathered
+        peers' whole-payload norms, read from the per-(peer, tensor) norms the clip computation left on the
+        device (one small read-back per window)."""
+        if self.metrics_logger is None or n_peers <= 0:
+            return
+        eng = self.engine
+        np_ = eng.layout.n_params
+        per_peer = eng.peer_norms[: n_peers * np_].view(n_peers, np_).double().pow(2).sum(dim=1).sqrt().cpu()
+        finite = per_peer[torch.isfinite(per_peer)]
+        if finite.numel() == 0:
+            return
+        w = float(eng.store.master_shard.double().pow(2).sum().sqrt())
+        mean = float(finite.mean())
+        self.metrics_logger.log("validator_gradient_stats",
+                                tags={"window": int(self.sync_window), "global_step": int(self.global_step)},
+                                fields={"mean_grad_norm": mean, "max_grad_norm": float(finite.max()),
+                                        "min_grad_norm": float(finite.min()), "median_grad_norm": float(finite.median()),
+                                        "grad_norm_std": float(finite.std()) if finite.numel() > 1 else 0.0,
+                                        "mean_weight_norm": w, "grad_to_weight_ratio": mean / w if w > 0 else 0.0})
+
+    def log_timing(self, name: str, seconds: float) -> None:
+        """``timing`` measurement for one phase of the window (reference neurons/validator.py:76-87)."""
+        if self.metrics_logger is not None:
+            self.metrics_logger.log("timing", tags={"window": int(self.sync_window)}, fields={name: float(seconds)})
 
     def _track_param_change(self) -> None:
         a = self.param_change_alpha

@@ -70,6 +70,20 @@ def test_two_miners_and_a_validator_stay_in_sync(cwd_tmp):
             assert not torch.equal(pm[0][n], start[n]) or pm[0][n].numel() < 4
         assert v.evaluated_uids == {2, 3} and float(v.weights.sum()) == pytest.approx(1.0, abs=1e-5)
         assert os.path.exists(v.state_path)
+        # the measurements of a validator window reached the metrics sink
+        for n in miners + [v]:
+            n.metrics_logger.close()                      # drains the writer thread's queue into the sink
+        import json as _json
+        seen = {}
+        for line in (cwd_tmp / "metrics.jsonl").read_text().splitlines():
+            rec = _json.loads(line)
+            seen.setdefault(rec["measurement"].split("_", 0)[-1], rec)
+        names = {k for k in seen}
+        want = {"validator_window_v2", "validator_gradient_stats", "timing", "validator_scores", "training_step_v2"}
+        assert all(any(n.endswith(w) for n in names) for w in want), sorted(names)
+        stats = next(r for n, r in seen.items() if n.endswith("validator_gradient_stats"))["fields"]
+        assert stats["mean_grad_norm"] > 0 and stats["min_grad_norm"] <= stats["median_grad_norm"] <= stats["max_grad_norm"]
+        assert stats["mean_weight_norm"] > 0 and stats["grad_to_weight_ratio"] > 0
         # checkpoint published at global_step 2 is complete and loadable by a fresh evaluator
         assert await v.ckpt.check_checkpoint_exists(window=2)
         e = _node(Evaluator, Evaluator.evaluator_config, ["--uid", "1", "--skip-lm-eval", "--custom-eval-batches", "1"], store, chain)
