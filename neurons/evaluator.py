@@ -73,14 +73,24 @@ class Evaluator(BaseNode, Trainer):
     def evaluator_config(argv=None) -> SimpleNamespace:
         p = argparse.ArgumentParser(description="Evaluator script")
         common_args(p)
-        p.add_argument("--eval-interval", type=int, default=600)
+        # both spellings of every option: dashes, and the reference's underscores (neurons/evaluator.py:1234-1298)
+        p.add_argument("--eval-interval", "--eval_interval", dest="eval_interval", type=int, default=600)
         p.add_argument("--tasks", type=str, default=DEFAULT_TASKS)
+        p.add_argument("--batch-size", "--batch_size", dest="batch_size", type=int, default=4)
+        p.add_argument("--custom-eval-path", "--custom_eval_path", dest="custom_eval_path", type=str, default=None,
+                       help="directory of pre-tokenised shards (val_/eval_/test_/train_000000.npy) for the perplexity run")
         p.add_argument("--custom-eval-batches", type=int, default=16)
         p.add_argument("--skip-lm-eval", action="store_true")
-        p.add_argument("--cache-dir", type=str, default="./eval_model_cache")
+        p.add_argument("--cache-dir", "--cache_dir", dest="cache_dir", type=str, default="./eval_model_cache")
         p.add_argument("--version", type=str, default=None, help="checkpoint version to follow (default: this build)")
-        p.add_argument("--backfill-start", type=int, default=None)
-        p.add_argument("--backfill-end", type=int, default=None)
+        p.add_argument("--from-window", "--from_window", "--backfill-start", dest="backfill_start", type=int, default=None,
+                       help="backfill: first window (inclusive); with only --to-window the network's start window is used")
+        p.add_argument("--to-window", "--to_window", "--backfill-end", dest="backfill_end", type=int, default=None,
+                       help="backfill: last window (inclusive); with only --from-window the newest complete checkpoint")
+        p.add_argument("--no-follow", "--no_follow", dest="no_follow", action="store_true",
+                       help="one shot: stop after the first evaluation / the backfill instead of following new checkpoints")
+        p.add_argument("--force-reval", "--force_reval", dest="force_reval", action="store_true",
+                       help="evaluate windows again even if this process has evaluated them")
         return finish_config(p.parse_args(argv))
 
     def __init__(self, config=None, hparams=None, store=None, subtensor=None):
@@ -136,33 +146,72 @@ class Evaluator(BaseNode, Trainer):
         return self.cache.path
 
     # -- custom eval ---------------------------------------------------------------------------
-    async def run_custom_eval(self, n_batches: int | None = None) -> dict[str, float]:
-        """Mean token cross entropy on held-out rows → loss, perplexity and bits per byte
-        (bytes estimated at 4 per token for synthetic data, measured by decoding otherwise)."""
+    def _custom_eval_rows(self, n_batches: int):
+        """(dataset, row indices of this rank, batch size, exact-bytes flag).  With ``--custom-eval-path`` the rows
+        come from pre-tokenised shards (prefix val / eval / test / train, first shard, at most 1024 sequences split
+        over the ranks, as the reference neurons/evaluator.py:697-745); otherwise seeded synthetic tokens."""
         hp = self.hparams
-        n_batches = n_batches or self.config.custom_eval_batches
+        path = getattr(self.config, "custom_eval_path", None)
+        if path:
+            prefix = next((p for p in ("val", "eval", "test") if (Path(path) / f"{p}_000000.npy").exists()), "train")
+            ds = tplr.SharedShardedDataset(0, hp.sequence_length, self.rank, self.world_size, file_prefix=prefix,
+                                           custom_path=path)
+            total = min(1024, len(ds))
+            per = total // self.world_size
+            lo = self.rank * per
+            hi = lo + per if self.rank < self.world_size - 1 else total
+            return ds, list(range(lo, hi)), max(int(getattr(self.config, "batch_size", 4)), 1), True
         ds = tplr.SyntheticDataset(max(n_batches * hp.micro_batch_size * self.world_size, 8), hp.sequence_length,
                                    hp.model_config.vocab_size, seed=4242)
         rows = list(range(self.rank, len(ds), self.world_size))[: n_batches * hp.micro_batch_size]
-        nll, toks = torch.zeros((), dtype=torch.float64, device=self.device), 0
+        return ds, rows, hp.micro_batch_size, False
+
+    def _decoded_bytes(self, ids: torch.Tensor) -> int | None:
+        """UTF-8 bytes of the evaluated sequences (exact bits per byte), when the tokenizer can decode."""
+        tok = getattr(self, "tokenizer", None)
+        if tok is None or not hasattr(tok, "batch_decode"):
+            return None
+        try:
+            texts = tok.batch_decode(ids.detach().cpu().tolist(), skip_special_tokens=True,
+                                     clean_up_tokenization_spaces=False)
+            return sum(len(t.encode("utf-8")) for t in texts)
+        except Exception as e:  # noqa: BLE001
+            tplr.logger.debug(f"[eval] decode for byte counts failed: {e}")
+            return None
+
+    async def run_custom_eval(self, n_batches: int | None = None) -> dict[str, float]:
+        """Mean token cross entropy on held-out rows -> loss, perplexity and bits per byte.  Bytes are counted by
+        decoding the evaluated sequences when a dataset path and a tokenizer are given, else taken as 4 per token."""
+        n_batches = n_batches or self.config.custom_eval_batches
+        ds, rows, bs, want_bytes = self._custom_eval_rows(n_batches)
+        nll, toks, nbytes, exact = torch.zeros((), dtype=torch.float64, device=self.device), 0, 0, want_bytes
         self.model.eval()
         with torch.no_grad():
-            for i in range(0, len(rows), hp.micro_batch_size):
-                ids = torch.stack([ds[r] for r in rows[i:i + hp.micro_batch_size]]).to(self.device)
+            for i in range(0, len(rows), bs):
+                ids = torch.stack([torch.as_tensor(ds[r]) for r in rows[i:i + bs]]).to(self.device, dtype=torch.long)
                 labels = self._labels(ids)
                 loss = self.model.loss(ids, labels)
                 n = int((labels != -100).sum())
                 nll += loss.double() * n
                 toks += n
+                if exact:
+                    got = self._decoded_bytes(ids)
+                    exact = got is not None
+                    nbytes += got or 0
                 await asyncio.sleep(0)
         self.model.train()
-        t = torch.tensor([float(nll), float(toks)], dtype=torch.float64, device=self.device)
+        # fp32 on CUDA (NCCL has no fp64 sum on every build); the reduced tensor is the one that is read
+        t = torch.tensor([float(nll), float(toks), float(nbytes), 1.0 if exact else 0.0],
+                         dtype=torch.float32 if self.device.type == "cuda" else torch.float64, device=self.device)
         if dist_helper.is_distributed():
-            torch.distributed.all_reduce(t.float() if self.device.type == "cuda" else t)
-        total_nll, total_tok = float(t[0]), max(float(t[1]), 1.0)
+            torch.distributed.all_reduce(t)
+        total_nll, total_tok, total_bytes = float(t[0]), max(float(t[1]), 1.0), float(t[2])
+        all_exact = float(t[3]) >= (self.world_size if dist_helper.is_distributed() else 1) and total_bytes > 0
         loss = total_nll / total_tok
-        return {"loss": loss, "perplexity": math.exp(min(loss, 50.0)), "bits_per_byte": compute_bpb(total_nll, int(total_tok * 4)),
-                "tokens": total_tok}
+        return {"loss": loss, "perplexity": math.exp(min(loss, 50.0)),
+                "bits_per_byte": compute_bpb(total_nll, int(total_bytes) if all_exact else int(total_tok * 4)),
+                "tokens": total_tok, "bytes": total_bytes if all_exact else total_tok * 4.0,
+                "bytes_exact": 1.0 if all_exact else 0.0}
 
     # -- lm_eval ---------------------------------------------------------------------------------
     def lm_eval_command(self, model_path: Path, tasks: list[str], output_dir: Path, num_fewshot: int = 0) -> list[str] | None:
@@ -243,23 +292,45 @@ class Evaluator(BaseNode, Trainer):
                          f"bpb={custom['bits_per_byte']:.4f} tasks={tasks}")
         return {"window": window, "global_step": global_step, **custom, "tasks": tasks}
 
+    async def _backfill_range(self) -> tuple[int, int] | None:
+        """Window range of a backfill run; an open end is resolved from the network (start window / newest
+        complete checkpoint)."""
+        lo, hi = self.config.backfill_start, self.config.backfill_end
+        if lo is None and hi is None:
+            return None
+        if lo is None:
+            lo = await self.comms.get_start_window()
+        if hi is None:
+            hi = await self.ckpt._discover_latest(prefer_highest_staked=True)
+        if lo is None or hi is None:
+            tplr.logger.warning("[eval] backfill range could not be resolved")
+            return None
+        return int(lo), int(hi)
+
     async def run(self):
         self.loop = asyncio.get_running_loop()
         self.comms.commitments = await self.comms.get_commitments()
-        if self.config.backfill_start is not None:
-            for w in range(self.config.backfill_start, (self.config.backfill_end or self.config.backfill_start) + 1):
+        done: set[int] = set()
+        rng = await self._backfill_range()
+        if rng is not None:
+            for w in range(rng[0], rng[1] + 1):
                 if self.stop_event.is_set():
                     break
-                if await self.ckpt.check_checkpoint_exists(window=w):
-                    await self.evaluate_window(w)
-            return
+                if (w in done and not self.config.force_reval) or not await self.ckpt.check_checkpoint_exists(window=w):
+                    continue
+                if await self.evaluate_window(w) is not None:
+                    done.add(w)
+            if self.config.no_follow or (self.config.backfill_start is not None and self.config.backfill_end is not None):
+                return
         while not self.stop_event.is_set():
             w = await self.check_latest_checkpoint() if self.is_master else None
             t = torch.tensor([w if w is not None else -1], dtype=torch.long, device=self.device)
             dist_helper.broadcast(t, src=0)
-            if int(t.item()) >= 0:
-                await self.evaluate_window(int(t.item()))
-            if self.config.max_windows and self.eval_counter >= self.config.max_windows:
+            w = int(t.item())
+            if w >= 0 and (w not in done or self.config.force_reval):
+                if await self.evaluate_window(w) is not None:
+                    done.add(w)
+            if self.config.no_follow or (self.config.max_windows and self.eval_counter >= self.config.max_windows):
                 break
             try:
                 await asyncio.wait_for(self.stop_event.wait(), timeout=self.config.eval_interval)

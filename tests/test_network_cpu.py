@@ -470,3 +470,32 @@ def test_miner_window_with_muon_as_the_inner_optimizer(cwd_tmp):
         assert all(x == x for x in moved) and max(moved) > 0            # finite, and the model changed
         assert float(m.engine.exp_avg.abs().max()) > 0                  # Muon momentum / Adam moment were written
     run(go())
+
+
+def test_evaluator_cli_spellings_and_dataset_path_evaluation(cwd_tmp):
+    from templar_b200 import dataset_prep
+
+    a = Evaluator.evaluator_config(["--local", "--device", "cpu", "--eval_interval", "5", "--from_window", "3", "--to_window", "4",
+                                    "--no_follow", "--force_reval", "--custom_eval_path", "/x", "--cache_dir", "c", "--batch_size", "2"])
+    b = Evaluator.evaluator_config(["--local", "--device", "cpu", "--eval-interval", "5", "--backfill-start", "3", "--backfill-end", "4",
+                                    "--no-follow", "--force-reval", "--custom-eval-path", "/x", "--cache-dir", "c", "--batch-size", "2"])
+    for k in ("eval_interval", "backfill_start", "backfill_end", "no_follow", "force_reval", "custom_eval_path", "cache_dir", "batch_size"):
+        assert getattr(a, k) == getattr(b, k), k
+    assert (a.backfill_start, a.backfill_end, a.no_follow, a.force_reval, a.batch_size) == (3, 4, True, True, 2)
+
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        e = _node(Evaluator, Evaluator.evaluator_config, ["--uid", "1", "--skip-lm-eval", "--batch_size", "2"], store, chain)
+        seq, vocab = e.hparams.sequence_length, e.hparams.model_config.vocab_size
+        dataset_prep.synthetic_shard(str(cwd_tmp / "evalset"), 0, seq * 6, seq, vocab, seed=3, prefix="val")
+        e.config.custom_eval_path = str(cwd_tmp / "evalset")
+        synth = await e.run_custom_eval(1)                                   # no tokenizer: 4 bytes per token assumed
+        assert synth["bytes_exact"] == 0.0 and 0.9 * 6 * (seq - 1) < synth["tokens"] <= 6 * (seq - 1)   # pad ids are masked
+        e.tokenizer = SimpleNamespace(batch_decode=lambda ids, **kw: ["ab" * len(row) for row in ids],
+                                      pad_token_id=getattr(e.tokenizer, "pad_token_id", 0),
+                                      eos_token_id=getattr(e.tokenizer, "eos_token_id", 0))
+        rep = await e.run_custom_eval(1)
+        assert rep["bytes_exact"] == 1.0 and rep["bytes"] == 6 * seq * 2     # two bytes per token of every sequence
+        assert rep["loss"] == pytest.approx(synth["loss"]) and rep["perplexity"] > 1
+        assert rep["bits_per_byte"] == pytest.approx(compute_bpb(rep["loss"] * rep["tokens"], 6 * seq * 2))
+    run(go())
