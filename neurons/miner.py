@@ -217,7 +217,17 @@ class Miner(BaseNode, Trainer):
             await tplr.neurons.update_peers(instance=self, window=step_window, peer_start=tplr.T())
         self.sampler.set_window_uid(self.uid, step_window)
         saved, specs = dist_helper.get_offloaded_params(self.model)
-        null_round = dist_helper.all_agree(False, self.device, "null_round")
+        # null rounds (reference neurons/miner.py:542-568): no training signal is sent while the validators have
+        # not published a peer list for this miner yet (the first validator_offset + peer_list_window_margin
+        # windows after the start window) or while there is nobody to gather from; local runs start at once
+        warmup = 0 if (self.config.local or self.config.test) else (
+            getattr(hp, "validator_offset", 1) + getattr(hp, "peer_list_window_margin", 2))
+        warmup_null = step_window - (self.start_window or step_window) < warmup
+        no_peers_null = len(self.comms.peers) == 0 and not self.config.test
+        null_round = dist_helper.all_agree(warmup_null or no_peers_null, self.device, "null_round")
+        if null_round:
+            tplr.logger.info("null round: " + ("warm-up" if warmup_null else "no gather peers" if no_peers_null
+                                               else "requested by another rank"))
         t0 = tplr.T()
         res = await self.inner_steps(loader=self.loader, step_window=step_window, null_round=null_round)
         train_time = tplr.T() - t0

@@ -499,3 +499,31 @@ def test_evaluator_cli_spellings_and_dataset_path_evaluation(cwd_tmp):
         assert rep["loss"] == pytest.approx(synth["loss"]) and rep["perplexity"] > 1
         assert rep["bits_per_byte"] == pytest.approx(compute_bpb(rep["loss"] * rep["tokens"], 6 * seq * 2))
     run(go())
+
+
+def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
+    """Outside local mode the first validator_offset + peer_list_window_margin windows after the start window, and
+    windows without gather peers, are null rounds: no inner update is kept and nothing is fed into the error feedback."""
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        m = _node(Miner, Miner.miner_config, ["--uid", "2", "--peers", "2"], store, chain)
+        m.loop = asyncio.get_running_loop()
+        m.comms.commitments = await m.comms.get_commitments()
+        m.comms.peers = [2]
+        m.gather_timeout = 2
+        await m.dataset_manager.initialize_datasets(0)
+        m.set_dataloader()
+        m.config.local, m.start_window = False, 10
+        before = {n: p.detach().clone() for n, p in m.model.named_parameters()}
+        m.current_window = m.comms.current_window = 11                 # offset 1 < warm-up of 3 windows
+        await m.run_window(11)
+        assert float(m.engine.ef.abs().max()) == 0.0 and float(m.engine.own_val.abs().max()) == 0.0
+        for n, p in m.model.named_parameters():
+            assert torch.equal(p.detach(), before[n]), n
+        m.comms.peers = []                                             # warm-up over, but nobody to gather from
+        m.current_window = m.comms.current_window = 14
+        await m.run_window(14)
+        assert float(m.engine.ef.abs().max()) == 0.0
+        for n, p in m.model.named_parameters():
+            assert torch.equal(p.detach(), before[n]), n
+    run(go())
