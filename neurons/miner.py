@@ -194,10 +194,11 @@ class Miner(BaseNode, Trainer):
         ok, win, step, boot = await tplr.neurons.load_checkpoint_with_fallback(self)
         if ok or self.current_window > self.start_window:
             await tplr.neurons.handle_checkpoint_catchup(self, ok, win, step, boot)
-        shard_epoch, shard_idx = tplr.compute_shard_state(self.global_step, getattr(self.hparams, "outer_steps_per_shard", 455),
-                                                          getattr(self.hparams, "shard_reset_outer_step", None))
-        await self.dataset_manager.initialize_datasets(shard_idx)
-        self.set_dataloader()
+        await self.init_shard_schedule()
+        if self.is_master:
+            # an (empty) object under this window's gradient key marks the miner as active for the validators
+            await self.comms.put(state_dict={"metadata": {"window": self.current_window, "dummy": True}}, uid=str(self.uid),
+                                 window=self.current_window, key="gradient", local=False)
         windows_done = 0
         while not self.stop_event.is_set():
             step_window = self.current_window
@@ -215,6 +216,7 @@ class Miner(BaseNode, Trainer):
         t_win = tplr.T()
         if self.is_master and self.config.peers is None and self.peers_update_window >= 0:
             await tplr.neurons.update_peers(instance=self, window=step_window, peer_start=tplr.T())
+        await self.maybe_switch_shard(step_window)
         self.sampler.set_window_uid(self.uid, step_window)
         saved, specs = dist_helper.get_offloaded_params(self.model)
         # null rounds (reference neurons/miner.py:542-568): no training signal is sent while the validators have

@@ -57,6 +57,40 @@ class Trainer:
                                                   batch_size=hp.micro_batch_size, pin_memory=torch.cuda.is_available())
         tplr.logger.info("[Run] dataset + sampler ready")
 
+    async def init_shard_schedule(self, validator: bool = False) -> None:
+        """Open the dataset shard that belongs to ``global_step`` and remember it (reference neurons/miner.py:
+        425-456, neurons/validator.py:1261-1275)."""
+        hp = self.hparams
+        epoch, shard = tplr.compute_shard_state(self.global_step, getattr(hp, "outer_steps_per_shard", 455),
+                                                getattr(hp, "shard_reset_outer_step", None))
+        await self.dataset_manager.initialize_datasets(shard)
+        dist_helper.safe_barrier("dataset_init_complete", getattr(self, "local_rank", 0))
+        self.set_dataloader(validator=validator)
+        self._shard_epoch, self._shard_index = epoch, shard
+
+    async def maybe_switch_shard(self, window: int, validator: bool = False) -> bool:
+        """At the start of a window: move to the next shard when ``global_step`` has crossed a shard boundary, or
+        re-open the schedule when the reset step was passed (reference neurons/miner.py:497-527).  Anneal mode
+        stays on its single shard.  Returns whether the dataset changed."""
+        hp = self.hparams
+        if (getattr(hp, "anneal_mode", {}) or {}).get("enabled", False):
+            return False
+        epoch, shard = tplr.compute_shard_state(self.global_step, getattr(hp, "outer_steps_per_shard", 455),
+                                                getattr(hp, "shard_reset_outer_step", None))
+        last_epoch, last_shard = getattr(self, "_shard_epoch", 0), getattr(self, "_shard_index", 0)
+        if epoch != last_epoch:
+            tplr.logger.info(f"Resetting shard schedule at outer_step {self.global_step} to shard {shard}")
+            await self.dataset_manager.initialize_datasets(shard)
+        elif shard > last_shard:
+            tplr.logger.info(f"Swapping dataset after {self.global_step} outer steps at window {window}")
+            await self.dataset_manager.swap_datasets()
+        else:
+            return False
+        self.set_dataloader(validator=validator)
+        dist_helper.safe_barrier("sync_shard_switch", getattr(self, "local_rank", 0))
+        self._shard_epoch, self._shard_index = epoch, shard
+        return True
+
     def get_expected_params(self) -> set[str]:
         out = set()
         for name, _ in self.model.named_parameters():

@@ -591,8 +591,7 @@ class Validator(BaseNode, Trainer):
         ok, win, step, boot = await tplr.neurons.load_checkpoint_with_fallback(self)
         if ok:
             await tplr.neurons.handle_checkpoint_catchup(self, ok, win, step, boot)
-        await self.dataset_manager.initialize_datasets(0)
-        self.set_dataloader(validator=True)
+        await self.init_shard_schedule(validator=True)
         self.sync_window = self.current_window - 1
         done = 0
         while not self.stop_event.is_set():
@@ -608,6 +607,7 @@ class Validator(BaseNode, Trainer):
         hp = self.hparams
         t_win = tplr.T()
         await self.save_state()
+        await self.maybe_switch_shard(self.sync_window, validator=True)
         gather_result = None
         if self.is_master:
             await self.comms.refresh_active_peers()

@@ -527,3 +527,40 @@ def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
         for n, p in m.model.named_parameters():
             assert torch.equal(p.detach(), before[n]), n
     run(go())
+
+
+def test_shard_schedule_swaps_and_resets_with_the_global_step():
+    from neurons.trainer import Trainer
+
+    calls = []
+
+    async def init(idx):
+        calls.append(("init", idx))
+
+    async def swap():
+        calls.append(("swap",))
+
+    t = Trainer.__new__(Trainer)
+    t.hparams = SimpleNamespace(outer_steps_per_shard=10, shard_reset_outer_step=35, anneal_mode={})
+    t.dataset_manager = SimpleNamespace(initialize_datasets=init, swap_datasets=swap)
+    t.set_dataloader = lambda validator=False: calls.append(("loader", validator))
+    t.local_rank = 0
+
+    async def go():
+        t.global_step = 12
+        await t.init_shard_schedule()
+        assert calls == [("init", 1), ("loader", False)] and (t._shard_epoch, t._shard_index) == (0, 1)
+        calls.clear()
+        t.global_step = 19
+        assert not await t.maybe_switch_shard(5) and calls == []
+        t.global_step = 20                                             # next shard of the same epoch: swap
+        assert await t.maybe_switch_shard(6) and calls == [("swap",), ("loader", False)] and t._shard_index == 2
+        calls.clear()
+        t.global_step = 36                                             # past the reset step: schedule re-opened at shard 0
+        assert await t.maybe_switch_shard(7, validator=True)
+        assert calls == [("init", 0), ("loader", True)] and (t._shard_epoch, t._shard_index) == (1, 0)
+        calls.clear()
+        t.hparams.anneal_mode = {"enabled": True}
+        t.global_step = 80
+        assert not await t.maybe_switch_shard(8) and calls == []        # anneal mode stays on its shard
+    run(go())
