@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import gc
 import hashlib
 import os
 import sys
@@ -288,8 +289,38 @@ class Miner(BaseNode, Trainer):
         if self.is_master:
             await self._publish_debug(step_window)
             self._log_window(summary, res)
+        await self.cleanup_window()
         dist_helper.safe_barrier("end_window", self.local_rank)
         return summary
+
+    # -- memory hygiene (reference neurons/miner.py:59-81, :986-1008) -------------------------------------- #
+    def log_gpu_memory(self, stage: str) -> None:
+        if self.device.type == "cuda":
+            gib = 1024 ** 3
+            tplr.logger.info(f"[GPU Memory - {stage}] Allocated: {torch.cuda.memory_allocated(self.device) / gib:.2f} GB, "
+                             f"Reserved: {torch.cuda.memory_reserved(self.device) / gib:.2f} GB")
+
+    def check_memory_threshold(self, threshold_gb: float = 0.5) -> bool:
+        """Release the caching allocator's free blocks when less than ``threshold_gb`` is left; True if it did."""
+        if self.device.type != "cuda":
+            return False
+        free, _total = torch.cuda.mem_get_info(self.device)
+        if free / 1024 ** 3 >= threshold_gb:
+            return False
+        tplr.logger.warning(f"Low GPU memory: {free / 1024 ** 3:.2f} GB available")
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize(self.device)
+        self.log_gpu_memory("After emergency cleanup")
+        return True
+
+    async def cleanup_window(self) -> None:
+        """Between windows: drop autograd leftovers of the module tree and host garbage.  The flat buffers of the
+        engine (weights, gradients, optimizer state, error feedback, payload slots) are allocated once and stay."""
+        for p in self.model.parameters():
+            p.grad = None
+        torch.clear_autocast_cache()
+        gc.collect()
+        self.check_memory_threshold()
 
     async def _publish_debug(self, window: int) -> None:
         """Two elements ([10:12]) of every parameter of the local view, used by validators to
