@@ -639,7 +639,27 @@ class Comms(ChainManager):
         return chosen
 
     async def close(self) -> None:
+        task = getattr(self, "_active_task", None)
+        if task is not None:
+            task.cancel()
+            self._active_task = None
         await self.store.close()
+
+    close_all_s3_clients = close          # the reference's name (src/tplr/comms.py:181-189)
+
+    def start_background_tasks(self) -> None:
+        """Start the peer-activity tracker on the running loop (reference src/tplr/comms.py:205-218).  Neurons that
+        refresh the active set themselves once per window do not need it."""
+        if getattr(self, "_active_task", None) is None:
+            self.loop = asyncio.get_running_loop()
+            self._active_task = self.loop.create_task(self.track_active_peers())
+
+    @staticmethod
+    def delete_local_directory(path: str) -> None:
+        """Remove a directory tree of the local store; a missing path is not an error."""
+        import shutil
+
+        shutil.rmtree(path, ignore_errors=True)
 
 
 def _aware(t: datetime) -> datetime:

@@ -394,3 +394,27 @@ def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
         assert await comms[0].gather(my_uid=0, uids=[1], window=6, key="gradient", timeout=1, device="cpu", totalks=totalks,
                                      local=False, xshapes=xshapes, compressor=comp) is None
     run(go())
+
+
+def test_background_activity_tracker_starts_once_and_stops_on_close(net, tmp_path):
+    store, chain, comms = net
+
+    async def go():
+        c = comms[0]
+        c.active_check_interval = 0.01
+        await comms[1].put(payload(1), window=c.current_window, key="gradient", uid="1", local=False)
+        c.start_background_tasks()
+        task = c._active_task
+        c.start_background_tasks()
+        assert c._active_task is task                      # started once
+        await asyncio.sleep(0.1)
+        assert not task.done()
+        await c.close_all_s3_clients()
+        await asyncio.sleep(0)
+        assert task.cancelled() or task.done()
+        d = tmp_path / "x" / "y"
+        d.mkdir(parents=True)
+        c.delete_local_directory(str(tmp_path / "x"))
+        c.delete_local_directory(str(tmp_path / "x"))        # missing path: no error
+        assert not (tmp_path / "x").exists()
+    run(go())
