@@ -120,7 +120,7 @@ class Validator(BaseNode, Trainer):
         self.score_zero_threshold = 1e-4
         self.idx_similarity_slashing_rate = tplr.neurons.instantiate_slashing_multiplier()
         self.naughty_peers: dict[int, int] = {}
-        self.naughty_peer_timeout = 200
+        self.naughty_peer_timeout = 20           # windows a mega-slashed peer stays excluded (reference neurons/validator.py:510-511)
         self.peer_eval_history: dict[int, deque] = {}
         self.eval_history_limit = 20
         self.consecutive_negative_count: dict[int, int] = {}

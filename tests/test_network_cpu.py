@@ -143,7 +143,7 @@ def _bare_validator():
     v.peer_eval_history, v.consecutive_negative_count, v.consecutive_missing_gradient_count = {}, {}, {}
     v.missing_gradient_history, v.excluded_from_gather, v.exclusion_start_window = {}, set(), {}
     v.peers_last_eval_window, v.naughty_peers = {}, {}
-    v.eval_history_limit, v.missing_gradient_history_limit, v.naughty_peer_timeout = 20, 10, 200
+    v.eval_history_limit, v.missing_gradient_history_limit, v.naughty_peer_timeout = 20, 10, 20
     v.missing_gradient_slash_rate, v.sync_score_slash_rate, v.inactivity_slash_rate, v.score_zero_threshold = 0.75, 0.75, 0.25, 1e-4
     v.idx_similarity_slashing_rate = tplr.neurons.instantiate_slashing_multiplier()
     v.burn_uid, v.sync_window, v.current_window, v.start_window, v.is_master = 1, 10, 11, 0, True
