@@ -630,7 +630,7 @@ class Validator(BaseNode, Trainer):
                 t_gather = tplr.T()
                 gather_result = await self.comms.gather_with_reserve(
                     my_uid=self.uid, gather_uids=list(self.comms.peers), reserve_uids=list(self.comms.reserve_peers),
-                    window=self.sync_window, key="gradient", timeout=getattr(self, "gather_timeout", 75), device="cpu",
+                    window=self.sync_window, key="gradient", timeout=getattr(self, "gather_timeout", 90), device="cpu",
                     local=False, totalks=self.totalks, xshapes=self.xshapes, compressor=self.compressor, time_min=tmin,
                     time_max=tmax, expected_compressed_params=self.expected_compressed_params)
                 self.log_timing("gather", tplr.T() - t_gather)
