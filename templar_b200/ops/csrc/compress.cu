@@ -1182,7 +1182,9 @@ TPLR_API int tplr_aggregate_apply_tc(const void* descs, int n_desc, int total_ch
 // code = clamp(rint((v - shift) / scale + n_bins/2), 0, n_bins - 1), lookup[b] = mean of (v - shift) over the
 // values with code b.  Output: codes (uint8, same offsets as the values) and a table [n_params][n_bins + 2]
 // = lookup | shift | scale, whose first n_bins + 1 entries per row are what aggregate_kernel's uint8 decode
-// reads.  Three launches: statistics, encode + per-bin sums, finalise.
+// reads.  Three launches: statistics, encode + per-bin sums, finalise.  The per-bin sums are taken in 64-bit
+// fixed point (2^-20 of a bin width, exact for the fp32 quotient), so the tables do not depend on the order in
+// which the atomics land: the same payload always encodes to the same bytes.
 // ------------------------------------------------------------------------------------- //
 #define QSPLIT 16
 __global__ void __launch_bounds__(256) quant_sum_kernel(const TplrParamDesc* __restrict__ descs, const float* __restrict__ val,
@@ -1204,8 +1206,9 @@ __global__ void __launch_bounds__(256) quant_sum_kernel(const TplrParamDesc* __r
 }
 
 // pass 0: shift = sum / n ; pass 1: scale from the centred sum of squares.  One thread per tensor.
+#define QFIX 1048576.0            // fixed-point unit of the per-bin sums: 2^-20 of a bin width
 __global__ void quant_stat_kernel(const TplrParamDesc* __restrict__ descs, int n_desc, const float* __restrict__ part,
-                                  float* __restrict__ table, float* __restrict__ bins, int pass, int n_bins,
+                                  float* __restrict__ table, unsigned long long* __restrict__ bins, int pass, int n_bins,
                                   float range_in_sigmas) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_desc) return;
@@ -1216,7 +1219,7 @@ __global__ void quant_stat_kernel(const TplrParamDesc* __restrict__ descs, int n
   float* row = table + (long long)d.param_id * (n_bins + 2);
   if (pass == 0) {
     row[n_bins] = n > 0 ? s / (float)n : 0.f;
-    for (int b = 0; b < 2 * n_bins; ++b) bins[(long long)d.param_id * 2 * n_bins + b] = 0.f;
+    for (int b = 0; b < 2 * n_bins; ++b) bins[(long long)d.param_id * 2 * n_bins + b] = 0ull;
   } else {
     const float stdv = sqrtf(s) / sqrtf((float)max(n - 1, 1LL));
     float scale = range_in_sigmas * stdv / (float)n_bins;
@@ -1227,39 +1230,45 @@ __global__ void quant_stat_kernel(const TplrParamDesc* __restrict__ descs, int n
 
 __global__ void __launch_bounds__(256) quant_encode_kernel(const TplrParamDesc* __restrict__ descs, const float* __restrict__ val,
                                                            uint8_t* __restrict__ codes, const float* __restrict__ table,
-                                                           float* __restrict__ bins, int n_bins) {
-  __shared__ float s_sum[256], s_cnt[256];
+                                                           unsigned long long* __restrict__ bins, int n_bins) {
+  __shared__ unsigned long long s_sum[256];       // two's complement sums of (v - shift) / scale in units of 2^-20
+  __shared__ unsigned int s_cnt[256];
   const TplrParamDesc d = descs[blockIdx.x];
   const long long n = (long long)d.n_chunks * d.k;
   const long long per = (n + QSPLIT - 1) / QSPLIT;
   const long long lo = per * blockIdx.y, hi = min(n, lo + per);
   const float* row = table + (long long)d.param_id * (n_bins + 2);
   const float shift = row[n_bins], inv = 1.f / row[n_bins + 1], offset = (float)(n_bins / 2);
-  for (int b = threadIdx.x; b < n_bins; b += blockDim.x) { s_sum[b] = 0.f; s_cnt[b] = 0.f; }
+  for (int b = threadIdx.x; b < n_bins; b += blockDim.x) { s_sum[b] = 0ull; s_cnt[b] = 0u; }
   __syncthreads();
   for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float c = val[d.val_off + i] - shift;
     const int q = (int)fminf(fmaxf(rintf(c * inv + offset), 0.f), (float)(n_bins - 1));
     codes[d.val_off + i] = (uint8_t)q;
-    atomicAdd(&s_sum[q], c);
-    atomicAdd(&s_cnt[q], 1.f);
+    atomicAdd(&s_sum[q], (unsigned long long)__double2ll_rn((double)(c * inv) * QFIX));
+    atomicAdd(&s_cnt[q], 1u);
   }
   __syncthreads();
-  float* bp = bins + (long long)d.param_id * 2 * n_bins;
+  unsigned long long* bp = bins + (long long)d.param_id * 2 * n_bins;
   for (int b = threadIdx.x; b < n_bins; b += blockDim.x)
-    if (s_cnt[b] > 0.f) { atomicAdd(bp + b, s_sum[b]); atomicAdd(bp + n_bins + b, s_cnt[b]); }
+    if (s_cnt[b] > 0u) { atomicAdd(bp + b, s_sum[b]); atomicAdd(bp + n_bins + b, (unsigned long long)s_cnt[b]); }
 }
 
-__global__ void quant_lookup_kernel(const TplrParamDesc* __restrict__ descs, const float* __restrict__ bins,
+__global__ void quant_lookup_kernel(const TplrParamDesc* __restrict__ descs, const unsigned long long* __restrict__ bins,
                                     float* __restrict__ table, int n_bins) {
   const TplrParamDesc d = descs[blockIdx.x];
-  const float* bp = bins + (long long)d.param_id * 2 * n_bins;
+  const unsigned long long* bp = bins + (long long)d.param_id * 2 * n_bins;
   float* row = table + (long long)d.param_id * (n_bins + 2);
-  for (int b = threadIdx.x; b < n_bins; b += blockDim.x) row[b] = bp[n_bins + b] > 0.f ? bp[b] / bp[n_bins + b] : 0.f;
+  const double scale = (double)row[n_bins + 1];
+  for (int b = threadIdx.x; b < n_bins; b += blockDim.x) {
+    const unsigned long long cnt = bp[n_bins + b];
+    row[b] = cnt ? (float)((double)(long long)bp[b] / QFIX / (double)cnt * scale) : 0.f;
+  }
 }
 
 // descs: one descriptor per tensor (full-model table); val / codes: the payload's value buffer and its uint8 image;
-// table: [n_params][n_bins + 2] (lookup | shift | scale); scratch: n_params * (QSPLIT + 2 * n_bins) floats.  n_bins <= 256.
+// table: [n_params][n_bins + 2] (lookup | shift | scale); scratch: n_params * (QSPLIT + 4 * n_bins) floats, 8-byte
+// aligned (QSPLIT partial sums per tensor, then 2 * n_bins 64-bit words per tensor).  n_bins <= 256.
 TPLR_API int tplr_quantize_values(const void* descs, int n_desc, const float* val, uint8_t* codes, float* table,
                                   float* scratch, int n_params, int n_bins, float range_in_sigmas, void* stream) {
   TPLR_ENTER();
@@ -1268,7 +1277,8 @@ TPLR_API int tplr_quantize_values(const void* descs, int n_desc, const float* va
   cudaStream_t st = (cudaStream_t)stream;
   const TplrParamDesc* dd = (const TplrParamDesc*)descs;
   float* part = scratch;
-  float* bins = scratch + (long long)n_params * QSPLIT;
+  unsigned long long* bins = reinterpret_cast<unsigned long long*>(scratch + (long long)n_params * QSPLIT);
+  if (reinterpret_cast<uintptr_t>(bins) & 7u) return (int)cudaErrorInvalidValue;
   dim3 grid(n_desc, QSPLIT);
   quant_sum_kernel<<<grid, 256, 0, st>>>(dd, val, part, 0, table, n_bins);
   quant_stat_kernel<<<(n_desc + 127) / 128, 128, 0, st>>>(dd, n_desc, part, table, bins, 0, n_bins, range_in_sigmas);

@@ -394,7 +394,7 @@ class WindowEngine:
                                else torch.zeros(n, dtype=dt, device=self.device))
             self._q_codes = z(self.layout.val_elems, torch.uint8)
             self._q_table = z(np_ * (nb + 2), torch.float32).view(np_, nb + 2)
-            self._q_scratch = torch.zeros(np_ * (16 + 2 * nb), dtype=torch.float32, device=self.device)
+            self._q_scratch = torch.zeros(np_ * (16 + 4 * nb), dtype=torch.float32, device=self.device)
         return self._q_codes, self._q_table, self._q_scratch
 
     def _quantize_own(self, on_rank0: bool) -> None:
@@ -614,7 +614,7 @@ class WindowEngine:
         np_ = self.layout.n_params
         codes = torch.empty(self.layout.val_elems, dtype=torch.uint8, device=self.device)
         table = torch.zeros(np_, n_bins + 2, dtype=torch.float32, device=self.device)
-        scratch = torch.zeros(np_ * (16 + 2 * n_bins), dtype=torch.float32, device=self.device)
+        scratch = torch.zeros(np_ * (16 + 4 * n_bins), dtype=torch.float32, device=self.device)
         desc_full, n_full = self._desc_full
         native.check(native.lib().tplr_quantize_values(desc_full.data_ptr(), n_full, val_flat.data_ptr(), codes.data_ptr(),
                                                        table.data_ptr(), scratch.data_ptr(), np_, n_bins,

@@ -379,16 +379,17 @@ def test_encode_values_and_flat_quantised_staging():
         assert abs(float(qp[1]) / float(row[65]) - 1) < 1e-4
 
 
-def test_compress_and_aggregate_are_bitwise_repeatable():
-    """The same inputs give the same bytes: payload, error feedback and updated weights.  The top-k compaction
-    is ordered; the scatter-add of the gather uses shared-memory float atomics, which commute for the at most
-    two contributions per coefficient of this case (own payload + one peer).  (The 8-bit encoder averages each
-    bin with float atomics, so its lookup tables repeat only to rounding; it is left out here.)"""
+@pytest.mark.parametrize("quantize", [False, True])
+def test_compress_and_aggregate_are_bitwise_repeatable(quantize):
+    """The same inputs give the same bytes: payload, codes and tables, error feedback and updated weights.  The
+    top-k compaction is ordered, the 8-bit encoder sums its bins in 64-bit fixed point, and the scatter-add of the
+    gather uses shared-memory float atomics, which commute for the at most two contributions per coefficient of
+    this case (own payload + one peer)."""
     args = ModelArgs(dim=256, n_layers=1, n_heads=2, vocab_size=512, intermediate_size=512, max_seq_len=128)
     runs = []
     for _ in range(2):
         model = build_model(args, device=DEV, dtype=torch.bfloat16, seed=4)
-        eng = WindowEngine(model, EngineConfig(topk=16, max_peers=2), device=DEV)
+        eng = WindowEngine(model, EngineConfig(topk=16, max_peers=2, quantize=quantize), device=DEV)
         g = torch.Generator(device=DEV).manual_seed(11)
         eng.ef.copy_(torch.randn(eng.ef.shape, device=DEV, generator=g) * 1e-3)
         eng.snapshot()
@@ -398,7 +399,10 @@ def test_compress_and_aggregate_are_bitwise_repeatable():
         eng.outer_step(2)
         torch.cuda.synchronize()
         assert eng.check_status() == 0
-        runs.append({"idx": eng.own_idx.clone(), "val": eng.own_val.clone(), "ef": eng.ef.clone(),
-                     "master": eng.store.master_shard.clone(), "compute": eng.store.compute.clone()})
+        rec = {"idx": eng.own_idx.clone(), "val": eng.own_val.clone(), "ef": eng.ef.clone(),
+               "master": eng.store.master_shard.clone(), "compute": eng.store.compute.clone()}
+        if quantize:
+            rec["codes"], rec["table"] = eng._q_codes.clone(), eng._q_table.clone()
+        runs.append(rec)
     for name in runs[0]:
         assert torch.equal(runs[0][name], runs[1][name]), name
