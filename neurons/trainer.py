@@ -410,8 +410,8 @@ class Trainer:
         """Mean |m|, mean v and the update-to-weight ratio of the Adam state (empty for other optimizers)."""
         engine = getattr(self, "engine", None)
         if engine is not None:
-            if engine.adam_step == 0:
-                return {}
+            if engine.adam_step == 0 or engine.cfg.inner_optimizer != "adamw":
+                return {}                      # with Muon the first-moment buffer is its momentum and v is unused
             m, v, p = engine.exp_avg, engine.exp_avg_sq, engine.store.master_shard
             upd = m / (v.sqrt() + engine.cfg.eps)
             vals = torch.stack((m.abs().mean(), v.mean(), upd.norm() / (p.norm() + 1e-12))).tolist()
