@@ -564,3 +564,33 @@ def test_shard_schedule_swaps_and_resets_with_the_global_step():
         t.global_step = 80
         assert not await t.maybe_switch_shard(8) and calls == []        # anneal mode stays on its shard
     run(go())
+
+
+def test_validator_state_round_trip(cwd_tmp):
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        v.global_step = 7
+        v.final_scores[2], v.gradient_scores[3], v.weights[2] = 0.25, -0.5, 1.0
+        v.binary_moving_averages[3], v.sync_scores[2], v.binary_indicator_scores[2] = 0.75, 0.9, 1.0
+        v.openskill_ratings[2] = v.openskill_model.rating(mu=31.0, sigma=4.0, name="2")
+        v.naughty_peers, v.consecutive_negative_count = {3: 5}, {2: 1}
+        await v.save_state()
+        w = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        w.state_path = v.state_path
+        w.load_state()
+        assert w.global_step == 7 and w.naughty_peers == {3: 5} and w.consecutive_negative_count == {2: 1}
+        for name in ("final_scores", "gradient_scores", "weights", "binary_moving_averages", "sync_scores",
+                     "binary_indicator_scores"):
+            assert torch.equal(getattr(w, name), getattr(v, name).float()), name
+        assert w.openskill_ratings[2].mu == pytest.approx(31.0) and w.openskill_ratings[2].sigma == pytest.approx(4.0)
+        # a state file of another metagraph size is ignored tensor by tensor, an unreadable one entirely
+        w.final_scores = torch.zeros(3)
+        w.load_state()
+        assert w.final_scores.shape == (3,) and float(w.final_scores.sum()) == 0.0
+        with open(v.state_path, "wb") as f:
+            f.write(b"not a checkpoint")
+        w.global_step = 1
+        w.load_state()
+        assert w.global_step == 1
+    run(go())
