@@ -118,3 +118,59 @@ def test_dataset_prep_cli_synthetic_and_ids(tmp_path, capsys):
     assert P.main(["ids", "--dir", str(tmp_path), "--seq-len", "64", "--workers", "3"]) == 0
     assert np.array_equal(np.load(tmp_path / "sample_ids_000001.npy"), ids)
     assert P.shard_names(5, "anneal") == ("anneal_000005.npy", "sample_ids_anneal_000005.npy")
+
+
+def test_http_row_source_against_a_local_rows_service():
+    """HttpRowSource on a datasets-server shaped service started in-process: size listing, row pages, retry on 503."""
+    from aiohttp import web
+
+    from templar_b200.dataset import HttpRowSource
+
+    tok = _Tok()
+    docs = {"cfgA": [f"w{'x' * (i % 5)} yy z" for i in range(300)], "default": ["skip me"]}
+    hits = {"rows": 0}
+
+    async def size(request):
+        assert request.query["dataset"] == "org/name"
+        return web.json_response({"size": {"splits": [{"config": c, "split": "train", "num_rows": len(d)} for c, d in docs.items()]}})
+
+    async def rows(request):
+        hits["rows"] += 1
+        if hits["rows"] == 1:
+            return web.Response(status=503)                     # the first request fails: the source retries
+        q = request.query
+        off, lim = int(q["offset"]), int(q["limit"])
+        return web.json_response({"rows": [{"row": {"text": t}} for t in docs[q["config"]][off: off + lim]]})
+
+    async def go():
+        app = web.Application()
+        app.add_routes([web.get("/size", size), web.get("/rows", rows)])
+        runner = web.AppRunner(app)
+        await runner.setup()
+        site = web.TCPSite(runner, "127.0.0.1", 0)
+        await site.start()
+        port = site._server.sockets[0].getsockname()[1]
+        try:
+            src = HttpRowSource("org/name", f"http://127.0.0.1:{port}/rows", f"http://127.0.0.1:{port}/size",
+                                retry_limit=3, retry_delay=0.0)
+            cfgs = await DatasetLoader.fetch_dataset_configs(source=src)
+            assert cfgs == {"cfgA": {"num_rows": 300, "split": "train"}}
+            ds = await DatasetLoader.create(batch_size=2, sequence_length=8, pages_info=[("cfgA", 10, "train")],
+                                            tokenizer=tok, source=src)
+            assert hits["rows"] == 2 and ds.get_page_names() == ["cfgA_10_train"]
+            first = next(iter(ds))
+            assert first.shape == (2, 8)
+            want = tok.encode(docs["cfgA"][10], max_length=8)
+            assert first[0, : len(want)].tolist() == want and first[0, len(want):].tolist() == [0] * (8 - len(want))
+            hits["rows"] = -10                                    # every request fails from here on
+            app_rows_fail = HttpRowSource("org/name", f"http://127.0.0.1:{port}/nope", f"http://127.0.0.1:{port}/size",
+                                          retry_limit=2, retry_delay=0.0)
+            try:
+                await app_rows_fail.rows(("cfgA", 0, "train"), 5)
+                raise AssertionError("a missing end point must raise after the retries")
+            except RuntimeError as e:
+                assert "Maximum retry attempts exceeded" in str(e)
+        finally:
+            await runner.cleanup()
+
+    asyncio.run(go())
