@@ -242,7 +242,12 @@ class S3Store(ObjectStore):
         try:
             return await coro_fn(await self._client(bucket))
         except Exception as e:  # noqa: BLE001
-            if _is_named(e, "ConnectionClosedError", "EndpointConnectionError", "ClientError"):
+            # a connection-level failure (or a server-side error) drops the cached client so that the next call
+            # reconnects; "no such object" / "not allowed" answers come over a healthy connection and keep it
+            # (the reference purges on those too, src/tplr/comms.py:549-552, and reconnects on every miss)
+            code = getattr(e, "response", {}).get("Error", {}).get("Code") if hasattr(e, "response") else None
+            benign = code in ("404", "403", "401", "NoSuchKey", "NotFound", "NoSuchUpload")
+            if _is_named(e, "ConnectionClosedError", "EndpointConnectionError") or (_is_named(e, "ClientError") and not benign):
                 await self.purge(bucket)
             raise
 

@@ -418,3 +418,63 @@ def test_background_activity_tracker_starts_once_and_stops_on_close(net, tmp_pat
         c.delete_local_directory(str(tmp_path / "x"))        # missing path: no error
         assert not (tmp_path / "x").exists()
     run(go())
+
+
+class ClientError(Exception):
+    """Shaped like botocore's: the store recognises it by class name and reads ``response['Error']['Code']``."""
+
+    def __init__(self, code):
+        super().__init__(code)
+        self.response = {"Error": {"Code": code}}
+
+
+class _FakeObjS3:
+    def __init__(self, objects):
+        self.objects, self.made = dict(objects), 0
+
+    async def head_object(self, Bucket, Key):
+        if Key not in self.objects:
+            raise ClientError("404")
+        return {"ContentLength": len(self.objects[Key]), "LastModified": datetime(2026, 1, 1)}       # naive time stamp
+
+    async def get_object(self, Bucket, Key, Range=None):
+        if Key == "boom":
+            raise ClientError("InternalError")
+        if Key not in self.objects:
+            raise ClientError("NoSuchKey")
+        return {"Body": _RangeBody(self.objects[Key])}
+
+    async def list_objects_v2(self, Bucket, Prefix, ContinuationToken=None):
+        keys = sorted(k for k in self.objects if k.startswith(Prefix))
+        start = int(ContinuationToken or 0)
+        page = keys[start: start + 2]
+        more = start + 2 < len(keys)
+        return {"Contents": [{"Key": k, "Size": len(self.objects[k])} for k in page], "IsTruncated": more,
+                "NextContinuationToken": str(start + 2) if more else None}
+
+    async def put_object(self, Bucket, Key, Body):
+        self.objects[Key] = Body
+
+
+def test_s3_store_head_get_list_pagination_and_client_purge():
+    b = Bucket(name="bkt", account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+    made = []
+
+    def factory(bucket):
+        made.append(_FakeObjS3({f"p/{i}": bytes([i]) * (i + 1) for i in range(5)}))
+        return made[-1]
+
+    st = S3Store(client_factory=factory)
+
+    async def go():
+        assert await st.head(b, "p/9") is None and await st.get_bytes(b, "p/9") is None      # missing: None, no raise
+        info = await st.head(b, "p/3")
+        assert info.size == 4 and info.last_modified.tzinfo is not None                       # naive stamps become UTC
+        assert await st.get_bytes(b, "p/2") == bytes([2]) * 3
+        assert [o.key for o in await st.list(b, "p/")] == [f"p/{i}" for i in range(5)]         # three pages of two
+        assert len(made) == 1                                                                 # one cached client so far
+        with pytest.raises(ClientError):
+            await st.get_bytes(b, "boom")                                                     # a real failure propagates
+        await st.put_bytes(b, "q", b"x")
+        assert len(made) == 2                                          # the client was purged after the ClientError
+    run(go())
