@@ -478,3 +478,38 @@ def test_s3_store_head_get_list_pagination_and_client_purge():
         await st.put_bytes(b, "q", b"x")
         assert len(made) == 2                                          # the client was purged after the ClientError
     run(go())
+
+
+def test_commitment_map_of_a_substrate_chain_is_keyed_by_uid(monkeypatch):
+    """The bittensor path: walk Commitments.CommitmentOf, decode account ids, keep registered hotkeys, skip garbage."""
+    import sys
+    import types
+
+    mod = types.ModuleType("bittensor.core.chain_data")
+    mod.decode_account_id = lambda raw: f"hk-{raw}"
+    for name in ("bittensor", "bittensor.core"):
+        monkeypatch.setitem(sys.modules, name, types.ModuleType(name))
+    monkeypatch.setitem(sys.modules, "bittensor.core.chain_data", mod)
+
+    def entry(account, text):
+        return ([account], SimpleNamespace(value={"info": {"fields": [[{"Raw128": [text.encode()]}]]}}))
+
+    good = "a" * 32 + "b" * 32 + "c" * 64
+    asked = {}
+
+    class _Substrate:
+        def get_block_hash(self, block):
+            return f"hash-{block}"
+
+        def query_map(self, module, storage_function, params, block_hash):
+            asked.update(module=module, fn=storage_function, params=params, block_hash=block_hash)
+            return [entry(0, good), entry(1, "too short"), entry(7, good),            # 7 is not in the metagraph
+                    ([2], SimpleNamespace(value={"info": {}}))]                        # undecodable entry
+
+    cm = chain_mod.ChainManager.__new__(chain_mod.ChainManager)
+    cm.netuid = 9
+    cm.metagraph = SimpleNamespace(hotkeys=["hk-0", "hk-1", "hk-2"], uids=[0, 1, 2])
+    cm.subtensor = SimpleNamespace(substrate=_Substrate())
+    got = run(cm.get_commitments(block=5))
+    assert asked == {"module": "Commitments", "fn": "CommitmentOf", "params": [9], "block_hash": "hash-5"}
+    assert set(got) == {0} and got[0].account_id == "a" * 32 and got[0].secret_access_key == "c" * 64
