@@ -1,8 +1,8 @@
 """Chain back-ends: the block clock, the metagraph and bucket commitments.
 
 The reference talks to a Bittensor subtensor (src/tplr/chain.py:39-85).  That network is one
-option here (:class:`BittensorBackend`, used when ``bittensor`` is importable and the config
-asks for it); :class:`StaticChain` is the offline replacement: a metagraph described by a dict /
+option here (``make_subtensor`` returns a ``bittensor.subtensor`` when the config names a network; a missing
+``bittensor`` package is then an error, never a silent fallback); :class:`StaticChain` is the offline replacement: a metagraph described by a dict /
 JSON file, commitments kept in memory (or in a shared JSON file for multi-process runs), and a
 block counter derived from wall time (``block_time`` seconds per block) or advanced by hand.
 """
@@ -113,14 +113,18 @@ class StaticWallet:
 
 
 def make_subtensor(config):
-    """Static chain unless the config names a network and bittensor is importable."""
+    """The static chain for ``static`` / ``offline`` (or no) network, else a ``bittensor.subtensor`` for that network."""
     network = getattr(getattr(config, "subtensor", None), "network", None) or getattr(config, "network", None)
     if network and network not in ("static", "offline", "local-static"):
         try:
             import bittensor as bt
-
+        except ImportError as e:
+            # never fall back silently: a node asked to join a real network must not run against a private chain
+            raise RuntimeError(f"network '{network}' was requested but the bittensor package is not installed; "
+                               f"use --network static for an offline run") from e
+        try:
             return bt.subtensor(config=config)
-        except ImportError:
-            pass
+        except Exception:  # noqa: BLE001  (a plain namespace instead of a bittensor config object)
+            return bt.subtensor(network=network)
     kw = dict(getattr(config, "static_chain", {}) or {})
     return StaticChain(netuid=getattr(config, "netuid", 3), **kw)

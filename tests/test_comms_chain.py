@@ -513,3 +513,21 @@ def test_commitment_map_of_a_substrate_chain_is_keyed_by_uid(monkeypatch):
     got = run(cm.get_commitments(block=5))
     assert asked == {"module": "Commitments", "fn": "CommitmentOf", "params": [9], "block_hash": "hash-5"}
     assert set(got) == {0} and got[0].account_id == "a" * 32 and got[0].secret_access_key == "c" * 64
+
+
+def test_make_subtensor_never_falls_back_silently(monkeypatch):
+    import builtins
+
+    from templar_b200.backends.chain import make_subtensor
+
+    assert isinstance(make_subtensor(SimpleNamespace(network="static", netuid=5, static_chain={"n": 3})), StaticChain)
+    real_import = builtins.__import__
+
+    def no_bittensor(name, *a, **k):
+        if name == "bittensor":
+            raise ImportError("no bittensor here")
+        return real_import(name, *a, **k)
+
+    monkeypatch.setattr(builtins, "__import__", no_bittensor)
+    with pytest.raises(RuntimeError, match="bittensor package is not installed"):
+        make_subtensor(SimpleNamespace(network="finney", netuid=5))
