@@ -58,8 +58,11 @@ def default_store() -> ObjectStore:
             import aiobotocore  # noqa: F401
 
             return S3Store(region=CF_REGION_NAME)
-        except ImportError:
-            logger.warning("R2 credentials present but aiobotocore is not installed; using the local store")
+        except ImportError as e:
+            # credentials say "object store": falling back to a private directory would cut the node off from
+            # its peers without anybody noticing
+            raise RuntimeError("bucket credentials are set but the aiobotocore package is not installed; "
+                               "set TPLR_STORE=local for a local-directory store") from e
     return LocalFSStore(os.environ.get("TPLR_STORE_ROOT", "/tmp/tplr_store"))
 
 
