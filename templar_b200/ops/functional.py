@@ -491,6 +491,9 @@ class _AttentionPacked(torch.autograd.Function):
         return dqkv, None, None, None
 
 
+_attn_fallback_seen: set = set()
+
+
 def attention_packed(qkv, n_heads: int, n_kv: int, hd: int):
     """Causal attention of ``qkv`` [B, S, (H + 2 KV) * hd] (q heads, k heads, v heads); returns [B, S, H * hd]."""
     B, S, C = qkv.shape
@@ -498,6 +501,13 @@ def attention_packed(qkv, n_heads: int, n_kv: int, hd: int):
             and n_heads % n_kv == 0 and qkv.stride(2) == 1 and qkv.stride(0) == S * qkv.stride(1)
             and qkv.stride(1) % 8 == 0 and qkv.data_ptr() % 16 == 0):
         return _AttentionPacked.apply(qkv, n_heads, n_kv, hd)
+    if _ATTN_BACKEND == "tcgen05" and qkv.is_cuda and (hd, S % 128) not in _attn_fallback_seen:
+        # said once per shape class: a GPU run that silently uses the library kernel would misreport what ran
+        _attn_fallback_seen.add((hd, S % 128))
+        import warnings
+
+        warnings.warn(f"attention_packed: head_dim {hd}, sequence {S}, dtype {qkv.dtype} is outside the own flash-attention "
+                      f"kernels (bf16, head_dim 128, sequence a multiple of 128); using torch SDPA for it", stacklevel=2)
     q, k, v = _split_qkv(qkv, n_heads, n_kv, hd)
     return attention(q, k, v).reshape(B, S, n_heads * hd)
 
