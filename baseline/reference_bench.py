@@ -85,7 +85,7 @@ class _TokenDataset(torch.utils.data.Dataset):
 def main(a) -> None:
     try:
         from baseline import ref_env
-        from bench import ClockSampler
+        from bench import ClockSampler, config_labels
 
         report = ref_env.prepare()
     except Exception as e:  # noqa: BLE001
@@ -278,10 +278,9 @@ def main(a) -> None:
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(A * B * S * 8 + h2d_bytes), "d2h_bytes_per_step": 8 * A},
             "gpu_launches": 0,
-            "config": {"model": f"torchtitan llama ({a.model})", "global_batch": B * A * world, "micro_batch": B,
-                       "accum": A, "seq_len": S, "parallelism": f"fsdp2 dp_shard={world}", "peers": a.peers,
-                       "topk": a.topk, "use_dct": True, "outer_update": "sgd", "compile": compile_blocks,
-                       "payload_values": "uint8 (256 bins) + per-tensor lookup, the reference's stock format",
-                       "reference_version": tplr.__version__, "stubbed_packages": report["stubbed"]}}))
+            "impl_detail": {"model_code": "torchtitan llama", "sharding": f"fsdp2 dp_shard={world}", "compile": compile_blocks,
+                            "payload_values": "uint8 (256 bins) + per-tensor lookup, the reference's stock format",
+                            "reference_version": tplr.__version__, "stubbed_packages": report["stubbed"]},
+            "config": config_labels(a, world)}))
     if dist.is_initialized():
         dist.destroy_process_group()

@@ -51,6 +51,25 @@ def parse():
     return ap.parse_args()
 
 
+MODEL_DIMS = {   # the benchmark shapes, as label text shared by both arms
+    "tiny": "d128 L2 H4 F256 V512", "150M": "d768 L12 H12 F3072 V32000", "1B": "d2048 L16 H16 F8192 V32000",
+    "8B": "d4096 L32 H32 KV8 F14336 V128256", "18B-tp": "d8192 L16 H64 KV8 F28672 V128256",
+    "34B": "d8192 L32 H64 KV8 F28672 V128256",
+}
+
+
+def config_labels(a, world: int) -> dict:
+    """The ``config`` object of the JSON line.  It names the workload only (model shapes, batch, window definition), so
+    the two arms of the benchmark print the same object for the same arguments; what differs between the arms
+    (kernels, sharding mechanics, compilation) is reported under ``impl_detail``."""
+    return {"model": f"llama-{a.model} ({MODEL_DIMS.get(a.model, a.model)})",
+            "global_batch": a.micro_batch * a.accum * world, "micro_batch": a.micro_batch, "accum": a.accum,
+            "seq_len": a.seq_len, "parallelism": f"dp{world}: sharded data parallel over {world} ranks of one node"
+            if world > 1 else "single GPU",
+            "peers": a.peers, "topk": a.topk, "use_dct": True, "outer_update": a.outer_update, "payload_values": "uint8",
+            "l2": "inputs larger than L2 (2.4 GB bf16 weights, 134 MB activations per layer)"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while timing."""
 
@@ -244,6 +263,9 @@ def run_ours(a):
         e2e = {"value": tokens_per_step * a.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(io[0]), "d2h_bytes_per_step": int(io[1])}
     status = eng.check_status()
+    sharding_label = ("single GPU" if world == 1 else
+                      "optimizer state, master weights, snapshot and error feedback sharded; bf16 weights and fp32 "
+                      "gradients whole on every rank")
     if rank == 0:
         mfu = value / world * args.flops_per_token(S) / 1e12
         out = {"metric": "1B tokens/s (device-timed, max over ranks); window = inner step + compress + gather + outer step",
@@ -252,11 +274,11 @@ def run_ours(a):
                "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights, seeded synthetic peer payloads",
                "impl": "ours", "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
                "model_tflops_per_gpu": mfu, "kernel_status": status, "gemm_backend": OF.gemm_backend(),
-               "config": {"model": f"llama-{a.model} (d{args.dim} L{args.n_layers} H{args.n_heads} F{args.ffn_hidden} V{args.vocab_size})",
-                          "global_batch": B * A * world, "micro_batch": B, "accum": A, "seq_len": S,
-                          "parallelism": f"zero-shard{world}" if world > 1 else "single",
-                          "peers": a.peers, "topk": a.topk, "use_dct": True, "outer_update": a.outer_update,
-                          "payload_values": a.values, "l2": "inputs larger than L2 (2.4 GB bf16 weights, 134 MB activations per layer)"}}
+               "library_gemm_fallbacks": OF.library_gemm_fallbacks,
+               "impl_detail": {"payload_values": a.values, "sharding": sharding_label},
+               "config": config_labels(a, world)}
+        if a.values != "uint8":
+            out["config"]["payload_values"] = a.values
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -295,7 +295,10 @@ class Trainer:
         entry_loss = None
         try:
             for batch in labelled(loader, "Data Loading"):
-                if self.stop_event.is_set():
+                # A rank never leaves the loop on its own view of the world: the stop request and the window
+                # clock are rank-local, and the optimizer step below contains collectives.  Both are agreed on
+                # at accumulation boundaries, which every rank reaches at the same batch count.
+                if self.stop_event.is_set() and not (self.world_size > 1 and dist_helper.is_distributed()):
                     break
                 with phase("Prepare Inputs"):
                     ids = (batch if isinstance(batch, torch.Tensor) else torch.tensor(batch)).to(
@@ -319,11 +322,16 @@ class Trainer:
                     loss = loss_t.detach() * (accum if not hasattr(self.model, "loss") else 1.0)
                 step_losses.append(loss.float())
                 batch_count += 1
-                window_changed = self.current_window != step_window
-                step_now = batch_count % accum == 0 or window_changed
+                # The step boundary is a function of the batch count alone (the same on every rank).  The reference
+                # instead agrees on `step_now` with a MAX all-reduce after every micro-batch
+                # (neurons/trainer.py:903-918); here the window change and the stop request wait for the boundary
+                # and are agreed on there with ONE reduce per inner step.
+                step_now = batch_count % accum == 0
                 if step_now:
-                    if self.world_size > 1:      # one agreement per inner step, not per micro-batch
-                        window_changed = bool(dist_helper.ddp_reduce(int(window_changed), op=dist.ReduceOp.MAX, device=dev))
+                    leave = self.current_window != step_window or self.stop_event.is_set()
+                    if self.world_size > 1 and dist_helper.is_distributed():
+                        leave = bool(dist_helper.ddp_reduce(int(leave), op=dist.ReduceOp.MAX, device=dev))
+                    window_changed = leave
                     if not null_round:
                         scale = self._warmup_scale()
                         if engine is not None:

@@ -316,14 +316,32 @@ class Comms(ChainManager):
             if name.endswith("quant_params"):
                 if tensor is None:
                     continue
+                if not isinstance(tensor, (tuple, list)) or len(tensor) != 5:
+                    logger.warning(f"Malformed quant-params in {name} from UID {uid}")
+                    return False
                 shift, scale, _offset, lookup, _dtype = tensor
-                bad_shift = not bool(torch.isfinite(torch.as_tensor(shift)).all())
+                try:
+                    bad_shift = not bool(torch.isfinite(torch.as_tensor(shift, dtype=torch.float32)).all())
+                except (TypeError, ValueError, RuntimeError):
+                    bad_shift = True
                 bad_scale = isinstance(scale, float) and (not math.isfinite(scale) or abs(scale) < 1e-12 or abs(scale) > 1e4)
                 if bad_shift or bad_scale:
                     logger.warning(f"Bad quant-params in {name} from UID {uid}; shift={shift}, scale={scale}")
                     return False
-                if torch.is_tensor(lookup) and not torch.isfinite(lookup).all():
+                # The codes index this table on the device: its shape is checked here, on the host, so that a
+                # short or oddly shaped table from a peer can never become an out-of-range gather on the GPU.
+                n_bins = int(getattr(self.hparams, "quantization_bins", 0) or 0)
+                if (not torch.is_tensor(lookup) or lookup.dim() != 1 or not lookup.is_floating_point()
+                        or lookup.numel() < 1 or lookup.numel() > 256 or (n_bins and lookup.numel() != min(n_bins, 256))):
+                    logger.warning(f"Lookup table of {name} from UID {uid} is not a 1-D float table of the expected size")
+                    return False
+                if not torch.isfinite(lookup).all():
                     logger.warning(f"Lookup table contains non-finite values in {name} from UID {uid}")
+                    return False
+                codes = state_dict.get(name[: -len("quant_params")] + "vals")
+                if (torch.is_tensor(codes) and codes.dtype == torch.uint8 and codes.numel()
+                        and int(codes.max()) >= lookup.numel()):
+                    logger.warning(f"Value codes of {name} from UID {uid} exceed the lookup table")
                     return False
             elif name.endswith("idxs"):
                 base = name[:-4]

@@ -22,10 +22,15 @@ LIBNAME = "libtplr_b200.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "--expt-relaxed-constexpr",
 ]
+# Approximate intrinsics and flush-to-zero only where the arithmetic is a softmax in base 2 (the flash
+# attention kernels).  The loss, the norms, the optimizer, the quantiser and the compression kernels are
+# compiled with IEEE division / square root and keep denormals; where they want a fast exponential they
+# call __expf explicitly.
+FAST_MATH_SOURCES = {"attention.cu"}
 
 
 def _nvcc() -> str:
@@ -60,7 +65,8 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         obj = LIBDIR / (src.stem + ".o")
         objs.append(obj)
         if force or _stale(obj, src, headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            extra = ["--use_fast_math"] if src.name in FAST_MATH_SOURCES else []
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

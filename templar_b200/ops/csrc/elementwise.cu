@@ -10,6 +10,7 @@
 // (neurons/trainer.py:280-298, :940).
 #include "common.cuh"
 #include "no_alloc.h"
+#include <atomic>
 
 typedef __nv_bfloat16 bf16;
 
@@ -442,15 +443,26 @@ TPLR_API int tplr_swiglu_bwd(const void* h, const void* dy, void* dh, long long 
 // ------------------------------------------------------------------------------------- //
 // Cross entropy: per-row loss and (optionally) the logit gradient written in place.
 //   loss_row = logsumexp(z) - z[label];  dz = (softmax(z) - onehot) * grad_scale / n_valid
-// Rows whose label == ignore_index give loss 0 and gradient 0.
+// Rows whose label == ignore_index give loss 0 and gradient 0.  So do rows whose label lies outside
+// [0, V) (a shard tokenised with a larger vocabulary, a corrupt label): they are never used as an index,
+// they do not count as valid rows, and TPLR_ST_BAD_INDEX is OR-ed into `status` when one is given.
 // ------------------------------------------------------------------------------------- //
 __global__ void count_valid_kernel(const long long* __restrict__ labels, long long T, long long ignore_index,
-                                   int* __restrict__ out) {
+                                   long long V, int* __restrict__ out, unsigned int* __restrict__ status) {
   __shared__ float red[32];
-  float c = 0.f;
-  for (long long i = threadIdx.x; i < T; i += blockDim.x) c += (labels[i] != ignore_index) ? 1.f : 0.f;
+  float c = 0.f, bad = 0.f;
+  for (long long i = threadIdx.x; i < T; i += blockDim.x) {
+    const long long l = labels[i];
+    if (l == ignore_index) continue;
+    if (l < 0 || l >= V) bad += 1.f;
+    else c += 1.f;
+  }
   c = block_sum(c, red);
-  if (threadIdx.x == 0) out[0] = (int)(c + 0.5f);
+  bad = block_sum(bad, red);
+  if (threadIdx.x == 0) {
+    out[0] = (int)(c + 0.5f);
+    if (bad > 0.f && status) atomicOr(status, TPLR_ST_BAD_INDEX);
+  }
 }
 
 __global__ void __launch_bounds__(512) ce_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels,
@@ -462,7 +474,7 @@ __global__ void __launch_bounds__(512) ce_kernel(bf16* __restrict__ logits, cons
   bf16* z = logits + row * ld;
   const long long label = labels[row];
   const int nv = V / 8;
-  if (label == ignore_index) {
+  if (label == ignore_index || label < 0 || label >= V) {
     if (threadIdx.x == 0) losses[row] = 0.f;
     if (write_grad) {
       bf16x8 zero;
@@ -524,12 +536,14 @@ __global__ void __launch_bounds__(1024) sum_rows_kernel(const float* __restrict_
 
 TPLR_API int tplr_cross_entropy(void* logits, const long long* labels, float* losses, int* n_valid,
                                 float* loss_out, float grad_scale, long long T, int V, long long ld,
-                                long long ignore_index, int write_grad, void* stream) {
+                                long long ignore_index, int write_grad, unsigned int* status, void* stream) {
   TPLR_ENTER();
   if (T <= 0) return 0;
-  if (ld % 8) return (int)cudaErrorInvalidValue;
+  // ce_kernel reads and writes rows as 16-byte vectors: the stride and the base must allow it, and a
+  // row must not overlap the next one
+  if ((ld % 8) || ld < V || V <= 0 || ((uintptr_t)logits & 15)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  count_valid_kernel<<<1, 1024, 0, st>>>(labels, T, ignore_index, n_valid);
+  count_valid_kernel<<<1, 1024, 0, st>>>(labels, T, ignore_index, V, n_valid, status);
   ce_kernel<<<(unsigned)T, 512, 0, st>>>((bf16*)logits, labels, losses, n_valid, grad_scale, V, ld, ignore_index, write_grad);
   sum_rows_kernel<<<1, 1024, 0, st>>>(losses, T, n_valid, 1.f, loss_out);
   return (int)cudaGetLastError();
@@ -713,20 +727,22 @@ TPLR_API int tplr_cast_bf16(const float* src, void* dst, long long n, void* stre
 static __device__ __align__(256) float g_ce_scratch[CE_SCRATCH_HEADER + TPLR_CE_NOALLOC_MAX_ROWS];
 
 #define TPLR_MAX_DEVICES 64
-static float* g_ce_scratch_addr[TPLR_MAX_DEVICES];   // null = not looked up yet on that device
+// null = not looked up yet on that device.  Host threads may race to fill a slot: every one of them
+// would store the same address, and the atomic makes the store and the later loads well defined.
+static std::atomic<float*> g_ce_scratch_addr[TPLR_MAX_DEVICES];
 
 static int ce_scratch_for_current_device(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= TPLR_MAX_DEVICES) return TPLR_ERR_NOALLOC_BAD_ARG;
-  if (!g_ce_scratch_addr[dev]) {
-    float* p = nullptr;
+  float* p = g_ce_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     e = cudaGetSymbolAddress((void**)&p, g_ce_scratch);
     if (e != cudaSuccess) return (int)e;
-    g_ce_scratch_addr[dev] = p;
+    g_ce_scratch_addr[dev].store(p, std::memory_order_release);
   }
-  *out = g_ce_scratch_addr[dev];
+  *out = p;
   return 0;
 }
 
@@ -737,7 +753,8 @@ TPLR_API int tplr_cross_entropy_noalloc(void* logits, const long long* labels, f
                                         int write_grad, void* stream) {
   TPLR_ENTER();
   if (rows > TPLR_CE_NOALLOC_MAX_ROWS) return TPLR_ERR_NOALLOC_TOO_LARGE;
-  if (rows < 0 || vocab <= 0 || (ld % 8) || !logits || !labels || !loss_out) return TPLR_ERR_NOALLOC_BAD_ARG;
+  if (rows < 0 || vocab <= 0 || (ld % 8) || ld < vocab || !logits || !labels || !loss_out) return TPLR_ERR_NOALLOC_BAD_ARG;
+  if ((uintptr_t)logits & 15) return TPLR_ERR_NOALLOC_BAD_ARG;   // rows are read and written as 16-byte vectors
   if (rows == 0) return 0;
   float* sc = nullptr;
   const int rc = ce_scratch_for_current_device(&sc);
@@ -747,7 +764,7 @@ TPLR_API int tplr_cross_entropy_noalloc(void* logits, const long long* labels, f
   cudaStream_t st = (cudaStream_t)stream;
   // count_valid_kernel overwrites n_valid and ce_kernel writes losses[0..rows) before
   // sum_rows_kernel reads them, so whatever an earlier call left in the array is never used.
-  count_valid_kernel<<<1, 1024, 0, st>>>(labels, rows, ignore_index, n_valid);
+  count_valid_kernel<<<1, 1024, 0, st>>>(labels, rows, ignore_index, vocab, n_valid, nullptr);
   ce_kernel<<<(unsigned)rows, 512, 0, st>>>((bf16*)logits, labels, losses, n_valid, grad_scale, vocab, ld,
                                             ignore_index, write_grad);
   sum_rows_kernel<<<1, 1024, 0, st>>>(losses, rows, n_valid, 1.f, loss_out);

@@ -21,7 +21,14 @@
 //    kernels overwrite every slot they later read, so a call never sees stale values.  Two calls
 //    that may run on the GPU at the same time (different streams, no ordering between them) race
 //    on the array: order them yourself.
-//  * No cudaMalloc, cudaFree or allocating library routine is called on any path.
+//  * A label that is neither ignore_index nor inside [0, vocab) is treated like ignore_index (loss 0,
+//    zero gradient, not counted); it is never used as an index.
+//  * `logits` must be 16-byte aligned, `ld` a multiple of 8 and at least `vocab`; anything else is
+//    refused with TPLR_ERR_NOALLOC_BAD_ARG before a kernel is launched.
+//  * This entry point itself calls no cudaMalloc, cudaFree or allocating library routine on any path.
+//    (The CUDA driver loads a library's kernels the first time one of them is launched in a process;
+//    that is the driver's own bookkeeping, happens once, and is another reason to make the first call
+//    during set-up rather than inside a latency-critical section.)
 #pragma once
 
 #ifdef __cplusplus

@@ -92,6 +92,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                  status_word(a.device).data_ptr(), 0, native.stream_ptr())
         native.check(err, "tplr_gemm_bf16")
         return out
+    if a.is_cuda and a.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas":
+        _library_gemm_fallback(a, b)
     A = a.t() if a_mn else a
     Bt = b if b_mn else b.t()
     c = A @ Bt
@@ -102,6 +104,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     else:
         out.copy_(c)
     return out
+
+
+library_gemm_fallbacks = 0        # bf16 CUDA products that left the own kernels (reported by bench.py)
+_gemm_fallback_seen: set = set()
+
+
+def _library_gemm_fallback(a: torch.Tensor, b: torch.Tensor) -> None:
+    """A bf16 CUDA product whose operands the own kernels cannot take (a row stride that is not a multiple of
+    8 elements, a base that is not 16-byte aligned, columns not contiguous) goes to the library.  It is counted,
+    said once per operand layout, and an error under ``TPLR_STRICT_NATIVE=1``: library time must not enter a
+    measurement unnoticed."""
+    global library_gemm_fallbacks
+    import os
+    import warnings
+
+    library_gemm_fallbacks += 1
+    why = (f"strides {tuple(a.stride())} / {tuple(b.stride())}, alignment {a.data_ptr() % 16} / {b.data_ptr() % 16}, "
+           f"dtypes {a.dtype} / {b.dtype}")
+    if os.environ.get("TPLR_STRICT_NATIVE") == "1":
+        raise RuntimeError("gemm: operands outside the own tcgen05 kernels (" + why + ")")
+    key = (tuple(a.stride()), tuple(b.stride()), a.data_ptr() % 16, b.data_ptr() % 16, b.dtype)
+    if key not in _gemm_fallback_seen:
+        _gemm_fallback_seen.add(key)
+        warnings.warn("gemm: operands outside the own tcgen05 kernels (" + why + "); using torch.matmul for them",
+                      stacklevel=3)
 
 
 class _Linear(torch.autograd.Function):
@@ -526,7 +553,8 @@ class _CrossEntropy(torch.autograd.Function):
         T = labels.numel()
         V = logits.shape[-1]
         lg = logits.reshape(T, V)
-        if _native_ok(lg) and lg.stride(-1) == 1 and lg.stride(0) % 8 == 0:
+        if (_native_ok(lg) and lg.stride(-1) == 1 and lg.stride(0) % 8 == 0 and lg.stride(0) >= V
+                and lg.data_ptr() % 16 == 0):
             lab = labels.reshape(-1).contiguous().to(torch.int64)
             losses = torch.empty(T, dtype=torch.float32, device=lg.device)
             nvalid = torch.empty(1, dtype=torch.int32, device=lg.device)
@@ -534,7 +562,9 @@ class _CrossEntropy(torch.autograd.Function):
             want_grad = ctx.needs_input_grad[0]
             native.check(native.lib().tplr_cross_entropy(lg.data_ptr(), lab.data_ptr(), losses.data_ptr(), nvalid.data_ptr(),
                                                          loss.data_ptr(), float(grad_scale), T, V, lg.stride(0),
-                                                         int(ignore_index), int(want_grad), native.stream_ptr()), "cross_entropy")
+                                                         int(ignore_index), int(want_grad),
+                                                         status_word(lg.device).data_ptr(), native.stream_ptr()),
+                         "cross_entropy")
             # the logits buffer now holds d(loss)/d(logits); it is handed to autograd in backward
             ctx.inplace = True
             ctx.shape = logits.shape

@@ -71,7 +71,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_rope": [vp, vp, vp, ll, i, i, i, ll, i, vp],
         "tplr_swiglu_fwd": [vp, vp, ll, i, vp],
         "tplr_swiglu_bwd": [vp, vp, vp, ll, i, vp],
-        "tplr_cross_entropy": [vp, vp, vp, vp, vp, f, ll, i, ll, ll, i, vp],
+        "tplr_cross_entropy": [vp, vp, vp, vp, vp, f, ll, i, ll, ll, i, vp, vp],
+        "tplr_cross_entropy_noalloc": [vp, vp, vp, f, ll, i, ll, ll, i, vp],
         "tplr_embedding_fwd": [vp, vp, vp, ll, i, i, vp],
         "tplr_embedding_bwd": [vp, vp, vp, ll, i, i, vp],
         "tplr_sumsq_blocks": [],

@@ -634,9 +634,16 @@ class WindowEngine:
         if qp is None:
             raise ValueError(f"{name}vals holds 8-bit codes but the payload has no {name}quant_params")
         shift, _, _, lookup, _ = qp
+        lookup = torch.as_tensor(lookup)
+        # the codes are uint8, so a table of 256 entries can never be indexed out of range; a shorter one is
+        # padded with its last entry (gather's acceptance test has already rejected codes beyond the table)
+        if lookup.dim() != 1 or lookup.numel() < 1:
+            raise ValueError(f"{name}quant_params: the lookup table must be a non-empty 1-D tensor")
         if device is not None:
             vals = vals.to(device, non_blocking=True)
-        lookup = torch.as_tensor(lookup).to(vals.device, torch.float32)
+        lookup = lookup.to(vals.device, torch.float32)
+        if lookup.numel() < 256:
+            lookup = torch.cat((lookup, lookup[-1:].expand(256 - lookup.numel())))
         shift = torch.as_tensor(shift).to(vals.device, torch.float32)
         return lookup[vals.long()] + shift
 

@@ -367,13 +367,15 @@ def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
     totalks, xshapes = {"w.": 4096}, {"w.": (2, 2, 64, 64)}
     comp = C.TopKCompressor(use_quantization=True, quantization_bins=16)
 
-    def qpayload(seed, *, shift=None, scale=None, lookup_nan=False, drop_params=False):
+    def qpayload(seed, *, shift=None, scale=None, lookup_nan=False, drop_params=False, lookup_edit=None):
         g = torch.Generator().manual_seed(seed)
         idx, q, xshape, totalk, qp = comp.compress(torch.randn(2, 2, 64, 64, generator=g), 4)
         sh, sc, off, lut, dt = qp
         lut = lut.clone()
         if lookup_nan:
             lut[3] = float("nan")
+        if lookup_edit is not None:
+            lut = lookup_edit(lut, q)
         qp = (sh if shift is None else torch.tensor(shift), sc if scale is None else scale, off, lut, dt)
         return {"w.idxs": idx, "w.vals": q, "w.quant_params": None if drop_params else qp}
 
@@ -389,6 +391,19 @@ def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
         assert sd["w.vals"][0].dtype == torch.uint8 and len(sd["w.quant_params"]) == 1      # codes kept, tables beside them
         deq = comp.maybe_dequantize_values(sd["w.vals"], sd["w.quant_params"], "cpu")
         assert deq[0].dtype == torch.float32 and torch.isfinite(deq[0]).all()
+        # a table that the codes would index out of range, or that is not a 1-D float table, is refused on the host
+        bad_tables = [lambda lut, q: lut[: int(q.max())],                  # shorter than the largest code
+                      lambda lut, q: lut.view(4, 4),                        # not 1-D
+                      lambda lut, q: lut.to(torch.int64),                   # not floating point
+                      lambda lut, q: torch.cat((lut, lut) * 16)]            # more entries than a byte can address
+        for n, edit in enumerate(bad_tables):
+            await comms[1].put(qpayload(10 + n, lookup_edit=edit), window=7 + n, key="gradient", uid="1", local=False)
+            assert await comms[0].gather(my_uid=0, uids=[1], window=7 + n, key="gradient", timeout=1, device="cpu",
+                                         totalks=totalks, local=False, xshapes=xshapes, compressor=comp) is None, n
+        comms[0].hparams.quantization_bins = 256          # a table of another size than the configured bins
+        assert await comms[0].gather(my_uid=0, uids=[0], window=5, key="gradient", timeout=1, device="cpu",
+                                     totalks=totalks, local=False, xshapes=xshapes, compressor=comp) is None
+        del comms[0].hparams.quantization_bins
         # codes without their table are refused
         await comms[1].put(qpayload(4, drop_params=True), window=6, key="gradient", uid="1", local=False)
         assert await comms[0].gather(my_uid=0, uids=[1], window=6, key="gradient", timeout=1, device="cpu", totalks=totalks,

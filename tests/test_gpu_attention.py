@@ -59,6 +59,31 @@ def _run_case(B, S, H, KV):
         assert err < 2e-2 * max(scale, 1.0), (name, err, scale)
 
 
+def test_attention_at_the_benchmark_shape():
+    """B 8, S 2048, 16 query heads on 8 key/value heads (head_dim 128): the shape of the 1B benchmark's micro-batch,
+    with grouped queries.  The fp32 oracle runs one batch element at a time to bound its memory."""
+    B, S, H, KV, hd = 8, 2048, 16, 8, 128
+    torch.manual_seed(7)
+    qkv = torch.randn(B, S, (H + 2 * KV) * hd, device=DEV).to(torch.bfloat16).requires_grad_()
+    OF.status_word(DEV).zero_()
+    out = OF.attention_packed(qkv, H, KV, hd)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    assert int(OF.status_word(DEV).item()) == 0
+    nq, nk = H * hd, KV * hd
+    for b in range(B):
+        ref_in = qkv.detach()[b:b + 1].clone().requires_grad_()
+        ref = _reference(ref_in, H, KV, hd)
+        ref.backward(dout[b:b + 1].float())
+        assert (out[b:b + 1].float() - ref).abs().max().item() < 2e-2, b
+        g, gr = qkv.grad[b:b + 1].float(), ref_in.grad.float()
+        for name, sl in (("dq", slice(0, nq)), ("dk", slice(nq, nq + nk)), ("dv", slice(nq + nk, None))):
+            err = (g[..., sl] - gr[..., sl]).abs().max().item()
+            scale = gr[..., sl].abs().max().item()
+            assert err < 2e-2 * max(scale, 1.0), (b, name, err, scale)
+
+
 def test_attention_matches_sdpa_backend_in_model_block():
     """The packed path and the library path give the same block output (RoPE applied before both)."""
     B, S, H, KV, hd = 2, 256, 4, 2, 128

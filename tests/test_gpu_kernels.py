@@ -205,6 +205,29 @@ def test_cross_entropy_loss_and_grad():
     assert torch.allclose(lg.grad.float(), 0.25 * lf.grad, atol=2e-5, rtol=2e-2)
 
 
+def test_cross_entropy_out_of_range_labels_are_ignored_and_reported():
+    """A label outside [0, V) is never used as an index: the row behaves like ignore_index and the status word
+    carries the bad-index bit.  The oracle is PyTorch on labels masked on the host."""
+    T, V = 64, 1000
+    logits = (torch.randn(T, V, device=DEV) * 2).to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[3], labels[10], labels[11] = V, -5, 2 ** 40
+    labels[::9] = -100
+    masked = torch.where((labels >= 0) & (labels < V), labels, torch.full_like(labels, -100))
+    lf = logits.float().requires_grad_()
+    ref = F.cross_entropy(lf, masked, ignore_index=-100)
+    ref.backward()
+    st = OF.status_word(DEV)
+    st.zero_()
+    lg = logits.clone().requires_grad_()
+    loss = OF.cross_entropy(lg * 1.0, labels, 1.0)
+    loss.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3
+    assert torch.allclose(lg.grad.float(), lf.grad, atol=2e-5, rtol=2e-2)
+    assert int(st.item()) & 1, "TPLR_ST_BAD_INDEX was not reported"
+    st.zero_()
+
+
 def test_embedding_fwd_bwd():
     V, D = 1000, 256
     table = torch.randn(V, D, device=DEV, dtype=torch.bfloat16)

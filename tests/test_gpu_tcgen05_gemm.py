@@ -55,6 +55,60 @@ def test_gemm_shapes(M, N, K):
     _check(M, N, K, False, False, "bf16")
 
 
+# (tokens, out features, in features) of the projections of the 1B benchmark model (16384 tokens per micro-batch)
+# and of the 18B tensor-parallel configuration (2048 tokens, features divided over 8 ranks where the plan shards them)
+MODEL_SHAPES = [(16384, 6144, 2048), (16384, 2048, 2048), (16384, 16384, 2048), (16384, 2048, 8192), (16384, 32000, 2048),
+                (2048, 1280, 8192), (2048, 8192, 1024), (2048, 7168, 8192), (2048, 8192, 3584), (2048, 16032, 8192)]
+
+
+@pytest.mark.parametrize("T,N,K", MODEL_SHAPES)
+def test_gemm_model_shapes_forward_dgrad_wgrad(T, N, K, backend):
+    """Forward (x W^T), input gradient (dy W) and weight gradient (dy^T x, fp32 accumulate) of one projection."""
+    if backend != "tcgen05_2sm" and T * N > 2 ** 27:
+        pytest.skip("the one-CTA kernel is the secondary backend: large cases run on the CTA-pair kernel only")
+    torch.manual_seed(T + N + K)
+    x = (torch.randn(T, K, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    OF.status_word(DEV).zero_()
+    y = OF.gemm(x, w)
+    ref = x.float() @ w.float().t()
+    assert (y.float() - ref).abs().max().item() < 2e-2 * max(ref.abs().max().item(), 1.0)
+    dy = (torch.randn(T, N, device=DEV) * 0.1).to(torch.bfloat16)
+    dx = OF.gemm(dy, w, b_mn=True)
+    ref = dy.float() @ w.float()
+    assert (dx.float() - ref).abs().max().item() < 2e-2 * max(ref.abs().max().item(), 1.0)
+    del ref
+    acc = torch.ones(N, K, device=DEV)
+    OF.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    ref = dy.float().t() @ x.float() + 1.0
+    assert (acc - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+    torch.cuda.synchronize()
+    assert int(OF.status_word(DEV).item()) == 0
+
+
+def test_library_fallback_is_counted_and_said(backend):
+    """Operands that the own kernels cannot take (a row stride that is not a multiple of 8 elements) go to the
+    library with a warning and a counter; under TPLR_STRICT_NATIVE=1 they are an error."""
+    import os
+    import warnings
+
+    a = torch.randn(64, 36, device=DEV).to(torch.bfloat16)[:, :32]        # row stride 36
+    b = torch.randn(48, 32, device=DEV).to(torch.bfloat16)
+    before = OF.library_gemm_fallbacks
+    OF._gemm_fallback_seen.clear()
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        c = OF.gemm(a, b)
+    assert OF.library_gemm_fallbacks == before + 1 and any("own tcgen05 kernels" in str(w.message) for w in seen)
+    assert (c.float() - a.float() @ b.float().t()).abs().max().item() < 0.5
+    os.environ["TPLR_STRICT_NATIVE"] = "1"
+    try:
+        with pytest.raises(RuntimeError):
+            OF.gemm(a, b)
+    finally:
+        del os.environ["TPLR_STRICT_NATIVE"]
+
+
 def test_linear_backward_matches_autograd():
     x = torch.randn(3, 100, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     w = (torch.randn(512, 256, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()

@@ -38,7 +38,7 @@ def _reference_call(L, logits, labels, grad_scale, write_grad):
     loss = torch.empty((), dtype=torch.float32, device=logits.device)
     native.check(L.tplr_cross_entropy(logits.data_ptr(), labels.data_ptr(), losses.data_ptr(), n_valid.data_ptr(),
                                       loss.data_ptr(), grad_scale, T, V, logits.stride(0), -100, int(write_grad),
-                                      native.stream_ptr()), "cross_entropy")
+                                      None, native.stream_ptr()), "cross_entropy")
     return loss
 
 
@@ -52,6 +52,8 @@ def test_noalloc_matches_regular_entry_point_twice(rows, vocab):
         logits = (torch.randn(rows - call * 7, vocab, device=dev) * 2).to(torch.bfloat16)
         labels = torch.randint(0, vocab, (logits.shape[0],), device=dev)
         labels[::5] = -100
+        if call == 1:                           # labels outside [0, vocab) behave like ignore_index, never as an index
+            labels[1], labels[2] = vocab + 5, -7
         want_grad = logits.clone()
         want_loss = _reference_call(L, want_grad, labels, 0.5, True)
         got_grad = logits.clone()
@@ -62,6 +64,10 @@ def test_noalloc_matches_regular_entry_point_twice(rows, vocab):
         torch.cuda.synchronize()
         assert abs(float(got_loss) - float(want_loss)) < 2e-3
         assert torch.allclose(got_grad.float(), want_grad.float(), atol=2e-5, rtol=2e-2)
+        # and against the plain fp32 PyTorch loss, with the out-of-range labels masked on the host
+        masked = torch.where((labels >= 0) & (labels < vocab), labels, torch.full_like(labels, -100))
+        torch_loss = torch.nn.functional.cross_entropy(logits.float(), masked, ignore_index=-100)
+        assert abs(float(got_loss) - float(torch_loss)) < 2e-3
         # loss-only mode leaves the logits alone
         keep = logits.clone()
         rc = fn(keep.data_ptr(), labels.data_ptr(), got_loss.data_ptr(), 1.0, logits.shape[0], vocab, keep.stride(0),
@@ -82,4 +88,8 @@ def test_noalloc_rejects_shapes_beyond_capacity():
     assert rc == -201                       # TPLR_ERR_NOALLOC_TOO_LARGE, nothing launched
     rc = fn(tiny.data_ptr(), labels.data_ptr(), out.data_ptr(), 1.0, 8, 8, 7, -100, 0, native.stream_ptr())
     assert rc == -202                       # row stride must be a multiple of 8 elements
+    rc = fn(tiny.data_ptr(), labels.data_ptr(), out.data_ptr(), 1.0, 8, 16, 8, -100, 0, native.stream_ptr())
+    assert rc == -202                       # a row stride below the vocabulary would make rows overlap
+    rc = fn(tiny.data_ptr() + 2, labels.data_ptr(), out.data_ptr(), 1.0, 4, 8, 8, -100, 0, native.stream_ptr())
+    assert rc == -202                       # rows are accessed as 16-byte vectors: the base must be aligned
     torch.cuda.synchronize()
