@@ -42,6 +42,13 @@ def parse():
     ap.add_argument("--values", default="uint8", choices=["fp32", "uint8"],
                     help="wire format of this node's payload values: fp32, or the reference miner's 8-bit codes "
                          "(256 bins, 6 sigma) with the quantisation error kept in the error feedback")
+    ap.add_argument("--shard-params", action="store_true",
+                    help="hold bf16 weights and fp32 gradients as shards too (the FSDP role): weights gathered per block "
+                         "over NVLink ahead of their use, weight gradients reduce-added into the owners' shards by the "
+                         "GEMM epilogue; the model is initialised tensor by tensor and never exists whole on a GPU")
+    ap.add_argument("--gather-buffers", type=int, default=2,
+                    help="with --shard-params: block buffers in rotation (>= the number of blocks keeps all gathered)")
+    ap.add_argument("--checkpoint-blocks", action="store_true", help="recompute every block in the backward pass")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--breakdown", action="store_true",
@@ -137,10 +144,20 @@ def run_ours(a):
     if a.gemm:
         OF.set_gemm_backend(a.gemm)
     args = PRESETS[a.model]
-    model = build_model(args, device=dev, dtype=torch.bfloat16, seed=0)
     cfg = EngineConfig(topk=a.topk, use_dct=True, outer_update=a.outer_update, max_peers=a.peers,
-                       quantize=a.values == "uint8", quant_bins=256, quant_range=6.0)
-    eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
+                       quantize=a.values == "uint8", quant_bins=256, quant_range=6.0, shard_params=a.shard_params,
+                       gather_buffers=a.gather_buffers)
+    if a.shard_params:
+        from templar_b200.models.llama import LlamaModel
+        with torch.device("meta"):
+            model = LlamaModel(args)
+        model.freqs_cis = model._freqs_cis().to(dev)
+        eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap,
+                           materialize=lambda name: model.materialize_param(name, dev, torch.bfloat16, seed=0))
+    else:
+        model = build_model(args, device=dev, dtype=torch.bfloat16, seed=0)
+        eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
+    model.activation_checkpointing = a.checkpoint_blocks
     L = eng.layout
     B, S, A = a.micro_batch, a.seq_len, a.accum
     g = torch.Generator().manual_seed(1234 + rank)
@@ -263,9 +280,16 @@ def run_ours(a):
         e2e = {"value": tokens_per_step * a.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(io[0]), "d2h_bytes_per_step": int(io[1])}
     status = eng.check_status()
-    sharding_label = ("single GPU" if world == 1 else
+    sharding_label = ("bf16 weights, fp32 gradients and all optimizer state sharded; weights gathered per block, "
+                      f"{a.gather_buffers} block buffers" if a.shard_params else
+                      "single GPU" if world == 1 else
                       "optimizer state, master weights, snapshot and error feedback sharded; bf16 weights and fp32 "
                       "gradients whole on every rank")
+    free_b, total_b = torch.cuda.mem_get_info(dev)       # includes the symmetric heap, which torch's allocator does not see
+    peak = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2 ** 30, (total_b - free_b) / 2 ** 30],
+                        dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX)
     if rank == 0:
         mfu = value / world * args.flops_per_token(S) / 1e12
         out = {"metric": "1B tokens/s (device-timed, max over ranks); window = inner step + compress + gather + outer step",
@@ -275,7 +299,10 @@ def run_ours(a):
                "impl": "ours", "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
                "model_tflops_per_gpu": mfu, "kernel_status": status, "gemm_backend": OF.gemm_backend(),
                "library_gemm_fallbacks": OF.library_gemm_fallbacks,
-               "impl_detail": {"payload_values": a.values, "sharding": sharding_label},
+               "impl_detail": {"payload_values": a.values, "sharding": sharding_label,
+                               "peak_torch_allocated_gib_max_over_ranks": round(float(peak[0]), 2),
+                               "device_memory_in_use_gib_max_over_ranks": round(float(peak[1]), 2),
+                               "weight_gathers": eng.store.gather.gathers if a.shard_params else 0},
                "config": config_labels(a, world)}
         if a.values != "uint8":
             out["config"]["payload_values"] = a.values

@@ -330,10 +330,11 @@ class Comms(ChainManager):
                     return False
                 # The codes index this table on the device: its shape is checked here, on the host, so that a
                 # short or oddly shaped table from a peer can never become an out-of-range gather on the GPU.
-                n_bins = int(getattr(self.hparams, "quantization_bins", 0) or 0)
+                # Peers may quantise with fewer bins than this node: any table that a byte can address is accepted,
+                # as long as no code of the payload points past its end (checked below).
                 if (not torch.is_tensor(lookup) or lookup.dim() != 1 or not lookup.is_floating_point()
-                        or lookup.numel() < 1 or lookup.numel() > 256 or (n_bins and lookup.numel() != min(n_bins, 256))):
-                    logger.warning(f"Lookup table of {name} from UID {uid} is not a 1-D float table of the expected size")
+                        or lookup.numel() < 1 or lookup.numel() > 256):
+                    logger.warning(f"Lookup table of {name} from UID {uid} is not a 1-D float table of 1..256 entries")
                     return False
                 if not torch.isfinite(lookup).all():
                     logger.warning(f"Lookup table contains non-finite values in {name} from UID {uid}")

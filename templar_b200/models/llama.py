@@ -80,6 +80,8 @@ PRESETS: dict[str, ModelArgs] = {
                     rope_theta=500000.0),
     "18B-tp": ModelArgs(dim=8192, n_layers=16, n_heads=64, n_kv_heads=8, vocab_size=128256,
                         intermediate_size=28672, rope_theta=500000.0),
+    "34B": ModelArgs(dim=8192, n_layers=32, n_heads=64, n_kv_heads=8, vocab_size=128256, intermediate_size=28672,
+                     rope_theta=500000.0),
     "70B": ModelArgs(dim=8192, n_layers=80, n_heads=64, n_kv_heads=8, vocab_size=128256, intermediate_size=28672,
                      rope_theta=500000.0),
 }
@@ -223,20 +225,64 @@ class LlamaModel(nn.Module):
             nn.init.trunc_normal_(self.output.weight, mean=0.0, std=std, a=-3 * std, b=3 * std, generator=gen)
         self.freqs_cis = self._freqs_cis().to(buffer_device or self.freqs_cis.device)
 
+    def materialize_param(self, name: str, device, dtype=None, seed: int = 0) -> torch.Tensor:
+        """One parameter's initial value, created on ``device`` on its own (the distributions of
+        :meth:`init_weights`, seeded per tensor).  Lets a model that was built on the meta device be initialised
+        tensor by tensor straight into sharded storage, so that a model too large for one GPU never exists whole."""
+        shape = dict(self.named_parameters())[name].shape
+        gen = torch.Generator(device=device)
+        index = [n for n, _ in self.named_parameters()].index(name)
+        gen.manual_seed(int(seed) * 1_000_003 + index)
+        t = torch.empty(shape, dtype=torch.float32, device=device)
+        if name.endswith("norm.weight"):
+            t.fill_(1.0)
+        elif name == "tok_embeddings.weight":
+            t.normal_(generator=gen)
+        elif name == "output.weight":
+            std = self.args.dim ** -0.5
+            nn.init.trunc_normal_(t, mean=0.0, std=std, a=-3 * std, b=3 * std, generator=gen)
+        else:
+            layer = self.layers[name.split(".")[1]]
+            scaled = any(k in name for k in ("attention.wo.", "feed_forward.w2.", "feed_forward.w3."))
+            nn.init.trunc_normal_(t, mean=0.0, std=layer.weight_init_std if scaled else 0.02, generator=gen)
+        return t if dtype is None else t.to(dtype)
+
     # -- forward ---------------------------------------------------------------------------
     def hidden_states(self, tokens: torch.Tensor) -> torch.Tensor:
         cos, sin = self._rope(tokens.device)
+        # With sharded parameters (parallel/fsdp.py) the weights of a block are only present while the block runs:
+        # `pg` brings them in ahead of the block in both directions of the pass.
+        pg = getattr(self, "_param_gather", None)
+        if pg is not None:
+            pg.begin_forward()
         h = OF.embedding(tokens, self.tok_embeddings.weight)
         delta = None
-        for layer in self.layers.values():
+        for key, layer in self.layers.items():
+            fn = layer.forward_fused
+            if pg is not None:
+                fn = self._gated_block(pg, f"layers.{key}", layer)
             if self.activation_checkpointing and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
-                h, delta = checkpoint(layer.forward_fused, h, delta, cos, sin, use_reentrant=False)
+                h, delta = checkpoint(fn, h, delta, cos, sin, use_reentrant=False)
             else:
-                h, delta = layer.forward_fused(h, delta, cos, sin)
+                h, delta = fn(h, delta, cos, sin)
+            if pg is not None:
+                h, delta = pg.leave(f"layers.{key}", h, delta)
+        if pg is not None:
+            pg.acquire("post")
         if delta is None:
             return self.norm(h)
         return OF.add_rmsnorm(h, delta, self.norm.weight, self.norm.eps)[1]
+
+    @staticmethod
+    def _gated_block(pg, group: str, layer):
+        def run(h, delta, cos, sin):
+            if delta is None:
+                h = pg.enter(group, h)
+            else:
+                h, delta = pg.enter(group, h, delta)
+            return layer.forward_fused(h, delta, cos, sin)
+        return run
 
     def forward(self, tokens: torch.Tensor, labels: torch.Tensor | None = None) -> torch.Tensor:
         return self.output(self.hidden_states(tokens))

@@ -64,7 +64,7 @@ struct Gemm2Params {
   unsigned int* ag_flags;            // one per CHUNK_ROWS rows of the full buffer (local memory)
   // scatter
   int rs_on;
-  int rs_rows_per_rank;
+  int rs_bound[MAX_RANKS + 1];       // owner o holds rows [rs_bound[o], rs_bound[o + 1]) of C; multiples of 32
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -204,10 +204,11 @@ __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem
   const uint32_t sw = (uint32_t)(lane & 7);
   const CUtensorMap* map = &p.tmC;
   int y = row0;
-  if (p.rs_on && row0 < p.M) {                       // the 32 rows of a warp have one owner (128 | rows per rank)
-    const int owner = row0 / p.rs_rows_per_rank;
+  if (p.rs_on && row0 < p.M) {                       // the 32 rows of a warp have one owner (32 | every bound)
+    int owner = 0;
+    while (owner + 1 < p.world && row0 >= p.rs_bound[owner + 1]) ++owner;
     map = &p.tmCr[owner];
-    y = row0 - owner * p.rs_rows_per_rank;
+    y = row0 - p.rs_bound[owner];
   }
 #pragma unroll 1
   for (int c = 0; c < TILE_N / COLS; ++c) {
@@ -638,7 +639,8 @@ TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, int M, int N, int 
   p.M = M;                                 // fill_common built tmC over the owned rows only
   if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
   p.world = world; p.rank = rank;
-  p.rs_on = 1; p.rs_rows_per_rank = rows_per_rank;
+  p.rs_on = 1;
+  for (int r = 0; r <= world; ++r) p.rs_bound[r] = r * rows_per_rank;
   for (int r = 0; r < world; ++r) {
     if ((uintptr_t)peer_out[r] & 15) return -108;
     if (!make_map(&p.tmCr[r], peer_out[r], N, rows_per_rank, ld_out, out_fp32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -648,4 +650,48 @@ TPLR_API int tplr_gemm2_scatter(const void* A, const void* B, int M, int N, int 
   const int tiles_m = (M + TILE_M - 1) / TILE_M;
   if (world > 1 && tiles_m % world == 0) p.m_inter = world;
   return dispatch2(p, a_mn, b_mn, epi, 0, 0, (cudaStream_t)stream);
+}
+
+// GEMM fused with a reduce-scatter over the rows of C whose owners hold UNEQUAL row ranges: owner o holds rows
+// [bounds[o], bounds[o + 1]) (multiples of 32, bounds[0] = 0, bounds[world] = M; an owner may hold none) in
+// `peer_out[o]`, a dense fp32 [rows_o, N] array as mapped in this process (its own, for o == rank).  This is the
+// weight-gradient GEMM of sharded data parallelism: every rank multiplies its own tokens (the whole K range) and
+// the epilogue reduce-adds each tile into the shard of the rank that owns those rows, over NVLink for a peer
+// and in the local L2 for itself, so the fp32 gradient exists only as shards and the reduce-scatter ends with
+// the backward pass.  Nothing is zeroed here: the shards accumulate over micro-batches; the caller zeroes them
+// between inner steps and separates that from the next backward pass with a barrier.
+// Replaces FSDP2's per-block fp32 reduce-scatter (src/tplr/model_factory.py:153,183).
+TPLR_API int tplr_gemm2_scatter_v(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                  int a_mn, int b_mn, int world, int rank, const int* bounds,
+                                  void* const* peer_out, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -107;
+  if (bounds[0] != 0 || bounds[world] != M || (N * 4) % 16) return -108;
+  for (int r = 0; r < world; ++r)
+    if (bounds[r + 1] < bounds[r] || (bounds[r + 1] % 32)) return -108;
+  int first = 0;
+  while (first < world && bounds[first + 1] == bounds[first]) ++first;      // first owner that holds rows
+  Gemm2Params p = {};
+  if (int r = fill_common(p, A, B, peer_out[first], bounds[first + 1] - bounds[first], N, K, lda, ldb, N, a_mn, b_mn, 1,
+                          status)) return r;
+  if (!p.c_tma) return -108;
+  p.M = M;
+  if (!(a_mn ? make_map(&p.tmA, A, M, K, lda, 64, BK) : make_map(&p.tmA, A, K, M, lda, BK, CTA_M))) return -102;
+  p.world = world; p.rank = rank;
+  p.rs_on = 1;
+  for (int r = 0; r <= world; ++r) p.rs_bound[r] = bounds[r];
+  for (int r = 0; r < world; ++r) {
+    const int rows = bounds[r + 1] - bounds[r];
+    if (rows == 0) continue;
+    if ((uintptr_t)peer_out[r] & 15) return -108;
+    if (!make_map(&p.tmCr[r], peer_out[r], N, rows, N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B, true)) return -109;
+  }
+  // ranks start on different owners and consecutive tile rows go to different owners where the tile rows
+  // divide evenly, so that every owner's link receives traffic throughout the GEMM
+  const int tiles_m = (M + TILE_M - 1) / TILE_M;
+  if (world > 1 && tiles_m % world == 0) p.m_inter = world;
+  if (world > 1) p.m_rot = (int)(((long long)rank * tiles_m) / world);
+  p.k_splits = pick_k_splits(M, N, K, 0);
+  return dispatch2(p, a_mn, b_mn, 1, 0, 0, (cudaStream_t)stream);
 }

@@ -152,3 +152,83 @@ TPLR_API int tplr_push_copy(const void* src, void* const* dsts, int n_dst, long 
   push_copy_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------- //
+// Block-table copy: the all-gather of sharded parameters.  `table` (device memory) holds `n_blocks` records
+// {src, dst, bytes}: src points into a peer's shard (mapped through the symmetric heap) or into this
+// GPU's own, dst into the local full-size buffer of the group being gathered; both 16-byte aligned, bytes a
+// multiple of 16.  The CTAs keep no shared memory and few registers, so they run beside the CTAs of a GEMM
+// that occupies every SM instead of waiting for one to retire; `max_ctas` bounds how many SMs they touch.
+// Replaces the per-block all-gather of FSDP2 (torchtitan models/llama3/infra/parallelize.py:383-422).
+// ------------------------------------------------------------------------------------- //
+struct CopyBlock { const uint4* src; uint4* dst; long long bytes; };
+
+__global__ void __launch_bounds__(256) copy_blocks_kernel(const CopyBlock* __restrict__ table, int n_blocks) {
+  for (int b = blockIdx.x; b < n_blocks; b += gridDim.x) {
+    const CopyBlock cb = table[b];
+    const long long n16 = cb.bytes >> 4;
+    long long i = threadIdx.x;
+    for (; i + 3 * 256 < n16; i += 4 * 256) {        // four 16-byte loads in flight per thread
+      const uint4 v0 = cb.src[i], v1 = cb.src[i + 256], v2 = cb.src[i + 512], v3 = cb.src[i + 768];
+      cb.dst[i] = v0; cb.dst[i + 256] = v1; cb.dst[i + 512] = v2; cb.dst[i + 768] = v3;
+    }
+    for (; i < n16; i += 256) cb.dst[i] = cb.src[i];
+  }
+}
+
+TPLR_API int tplr_copy_blocks(const void* table, int n_blocks, int max_ctas, void* stream) {
+  TPLR_ENTER();
+  if (n_blocks <= 0) return 0;
+  int grid = n_blocks;
+  if (max_ctas <= 0) max_ctas = tplr_sm_count();
+  if (grid > max_ctas) grid = max_ctas;
+  copy_blocks_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const CopyBlock*)table, n_blocks);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
+// Block-table reduce: dst[dst_off + i] += sum over ranks r of bufs[r][src_off + i] (fp32).  Used for the
+// gradients that are accumulated locally in full size (embedding rows, norm weights) and reduced into the
+// owner's gradient shard once per inner step; the matrices' gradients never take this path (their GEMM
+// epilogue adds them into the owner's shard directly).  Records: {src_off, dst_off, n} in elements, all
+// multiples of 4.  The caller orders it after a barrier.
+// ------------------------------------------------------------------------------------- //
+struct ReduceBlock { long long src_off, dst_off, n; };
+struct ReduceBlocksArgs {
+  const float* bufs[TPLR_MAX_PEERS];
+  int n_ranks;
+  const ReduceBlock* table;
+  int n_blocks;
+  float* dst;
+};
+
+__global__ void __launch_bounds__(256) reduce_blocks_kernel(const ReduceBlocksArgs a) {
+  for (int b = blockIdx.x; b < a.n_blocks; b += gridDim.x) {
+    const ReduceBlock rb = a.table[b];
+    float4* out = reinterpret_cast<float4*>(a.dst + rb.dst_off);
+    const long long n4 = rb.n >> 2;
+    for (long long i = threadIdx.x; i < n4; i += 256) {
+      float4 s = out[i];
+      for (int r = 0; r < a.n_ranks; ++r) {
+        const float4 v = reinterpret_cast<const float4*>(a.bufs[r] + rb.src_off)[i];
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+      out[i] = s;
+    }
+  }
+}
+
+TPLR_API int tplr_reduce_blocks(void* const* bufs, int n_ranks, const void* table, int n_blocks, void* dst,
+                                void* stream) {
+  TPLR_ENTER();
+  if (n_ranks > TPLR_MAX_PEERS || n_ranks <= 0) return (int)cudaErrorInvalidValue;
+  if (n_blocks <= 0) return 0;
+  ReduceBlocksArgs a;
+  for (int i = 0; i < n_ranks; ++i) a.bufs[i] = (const float*)bufs[i];
+  a.n_ranks = n_ranks; a.table = (const ReduceBlock*)table; a.n_blocks = n_blocks; a.dst = (float*)dst;
+  int grid = n_blocks;
+  const int cap = tplr_sm_count() * 4;
+  if (grid > cap) grid = cap;
+  reduce_blocks_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}

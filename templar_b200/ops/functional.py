@@ -155,7 +155,9 @@ class _Linear(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view_as(x)
-        if ctx.main_grad is not None:
+        if ctx.main_grad is not None and not torch.is_tensor(ctx.main_grad):
+            ctx.main_grad.accumulate(dy2, x2)        # sharded parameters: reduce-add into the owners' gradient shards
+        elif ctx.main_grad is not None:
             gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.main_grad, accumulate=True)
         elif ctx.needs_input_grad[1]:
             dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)

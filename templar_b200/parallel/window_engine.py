@@ -56,6 +56,8 @@ class EngineConfig:
     quantize: bool = False             # 8-bit value codes on the wire (the reference miner's format)
     quant_bins: int = 256
     quant_range: float = 6.0
+    shard_params: bool = False         # weights and gradients held as shards too (the FSDP role), gathered per block
+    gather_buffers: int = 2            # block buffers in rotation; >= the number of blocks keeps every block gathered
 
 
 def peer_slice(state_dict: dict, j: int) -> dict:
@@ -65,13 +67,18 @@ def peer_slice(state_dict: dict, j: int) -> dict:
 
 class WindowEngine:
     def __init__(self, model: torch.nn.Module, cfg: EngineConfig, *, device=None, rank: int = 0,
-                 world_size: int = 1, group=None, heap=None, compute_dtype: torch.dtype | None = None):
+                 world_size: int = 1, group=None, heap=None, compute_dtype: torch.dtype | None = None,
+                 materialize=None):
         self.cfg = cfg
         self.model = model
         self.rank, self.world_size, self.group = rank, world_size, group
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        if self.device.type == "meta":
+            raise ValueError("the model is on the meta device: pass the device its shards are to live on")
         self.cuda = self.device.type == "cuda"
         self.heap = heap
+        if materialize is not None and not cfg.shard_params:
+            raise ValueError("a model on the meta device is materialised tensor by tensor only with shard_params")
         if compute_dtype is None:
             compute_dtype = torch.bfloat16 if self.cuda else torch.float32
         alloc = None
@@ -80,11 +87,20 @@ class WindowEngine:
                 if symmetric:
                     return heap.alloc(n, dtype)
                 return torch.zeros(n, dtype=dtype, device=self.device)
+        self.status = OF.status_word(self.device) if self.cuda else torch.zeros(1, dtype=torch.int32)
+        self.fsdp = bool(cfg.shard_params)
+        if self.fsdp and cfg.inner_optimizer == "muon":
+            raise NotImplementedError("shard_params with the Muon inner optimizer: the engine's Muon step needs whole "
+                                      "gradient matrices on a rank; run Muon without shard_params")
+        if self.fsdp and self.cuda and world_size > 1 and heap is None:
+            raise ValueError("shard_params on CUDA with several ranks needs the symmetric heap (peer-memory gathers)")
         self.store = FlatParamStore(model, compute_dtype=compute_dtype, device=self.device,
                                     target_chunk=cfg.target_chunk, topk=cfg.topk, rank=rank,
-                                    world_size=world_size, alloc=alloc)
+                                    world_size=world_size, alloc=alloc, shard_params=self.fsdp,
+                                    n_buffers=cfg.gather_buffers, group=group, heap=heap, status=self.status,
+                                    materialize=materialize)
         L = self.layout = self.store.layout
-        n_shard = self.store.hi - self.store.lo
+        n_shard = self.store.n_shard
         z = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=self.device)
         self.exp_avg, self.exp_avg_sq = z(n_shard), z(n_shard)
         self.theta0 = z(n_shard)
@@ -119,9 +135,12 @@ class WindowEngine:
         self.skip = z(L.n_params, torch.int32)
         self.gnorm_sq = z(1)
         self._sumsq_scratch = z(native.lib().tplr_sumsq_blocks() if self.cuda else 1)
-        self.status = OF.status_word(self.device) if self.cuda else torch.zeros(1, dtype=torch.int32)
         self.window_open = False
         model._window_engine = self
+        model._param_gather = self.store.gather          # None unless shard_params: the model gates its blocks on it
+        if self.fsdp and self.cuda:
+            rec = self.store.stage_blocks()
+            self._stage_table = (torch.tensor(rec, dtype=torch.int64, device=self.device).reshape(-1, 3), len(rec))
 
     def _slots(self) -> int:
         """Peer-payload slots held by this rank: with a symmetric heap the peers are spread
@@ -146,7 +165,9 @@ class WindowEngine:
         self.window_open = True
 
     def zero_grad(self) -> None:
-        self.store.grad.zero_()
+        self.store.zero_grad()
+        if self.fsdp and self.world_size > 1:
+            self._barrier()                         # peers add into this shard: none may start before it is zero
 
     def micro_step(self, tokens: torch.Tensor, labels: torch.Tensor, grad_scale: float = 1.0) -> torch.Tensor:
         """Forward + backward of one micro-batch; returns the (device) mean loss."""
@@ -160,6 +181,8 @@ class WindowEngine:
         cfg, st = self.cfg, self.store
         lr = cfg.inner_lr if lr is None else lr
         self.adam_step += 1
+        if self.fsdp:
+            return self._optimizer_step_sharded(lr)
         if self.world_size > 1:
             self._reduce_grads()
         if cfg.inner_optimizer == "muon":
@@ -198,6 +221,72 @@ class WindowEngine:
         st.grad.zero_()
         self._publish_compute()
 
+    @torch.no_grad()
+    def _optimizer_step_sharded(self, lr: float) -> None:
+        """Inner step under ``shard_params``.  The matrices' gradients are already summed in the owners' shards
+        (the weight-gradient GEMMs added them there); what was accumulated locally in full size (embedding rows,
+        norm weights; on CPU everything) is reduced into the shards now.  Then global-norm clip and AdamW on the
+        shard, writing the new bf16 weights into this rank's own weight shard, from which the peers gather.
+
+        Ordering across ranks: (1) a barrier so that every rank's backward pass, and with it every remote add
+        into this shard, is complete; (2) the norm all-reduce also orders every rank's pull of the staged
+        gradients before anybody zeroes its staging buffer; (3) a barrier after the zeroing, because the next
+        backward pass of a peer adds into this rank's shard."""
+        cfg, st = self.cfg, self.store
+        n = st.n_shard
+        gshard = st.grad_shard[:n]
+        self._barrier()
+        if self.cuda:
+            L = native.lib()
+            table, n_rec = self._stage_table
+            if n_rec:
+                stages = ([self.heap.peer_ptr(st.stage, r) for r in range(self.world_size)]
+                          if (self.heap is not None and self.world_size > 1) else [st.stage.data_ptr()])
+                native.check(L.tplr_reduce_blocks(native.ptr_array(stages), len(stages), table.data_ptr(), n_rec,
+                                                  st.grad_shard.data_ptr(), native.stream_ptr()), "reduce_blocks")
+            native.check(L.tplr_sumsq(gshard.data_ptr(), n, self._sumsq_scratch.data_ptr(), self.gnorm_sq.data_ptr(),
+                                      native.stream_ptr()), "sumsq")
+            if self.world_size > 1:
+                dist.all_reduce(self.gnorm_sq, group=self.group)
+            shadows = [st.compute_shard.data_ptr()]
+            native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                                      gshard.data_ptr(), native.ptr_array(shadows), 1, n, lr, cfg.betas[0],
+                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
+                                      cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
+        else:
+            self._reduce_staged_cpu()
+            g = gshard / self.world_size
+            self.gnorm_sq.copy_((g * g).sum().reshape(1))
+            if self.world_size > 1:
+                dist.all_reduce(self.gnorm_sq, group=self.group)
+            coef = torch.clamp(cfg.max_grad_norm / (self.gnorm_sq.sqrt() + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else 1.0
+            g = g * coef
+            b1, b2 = cfg.betas
+            self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+            self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+            bc1, bc2 = 1 - b1 ** self.adam_step, 1 - b2 ** self.adam_step
+            p = st.master_shard
+            p.mul_(1 - lr * cfg.weight_decay)
+            p.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + cfg.eps, value=-lr)
+            st.compute_shard[:n].copy_(p.to(st.compute_dtype))
+        st.zero_grad()
+        st.gather.invalidate()
+        self._barrier()
+
+    def _reduce_staged_cpu(self) -> None:
+        """CPU / gloo: every tensor's gradient was accumulated locally in full size (``stage``); the parts that a
+        rank owns are summed onto it, piece by piece in an order that is the same on every rank."""
+        st, L = self.store, self.layout
+        for r in range(self.world_size):
+            dst = dist.get_global_rank(self.group, r) if self.group is not None else r
+            for sp, a, b, la in L.segments(r):
+                so = st.stage_off[sp.name] + (a - sp.offset)
+                part = st.stage[so: so + (b - a)].clone()
+                if self.world_size > 1:
+                    dist.reduce(part, dst=dst, group=self.group)
+                if r == self.rank:
+                    st.grad_shard[la: la + (b - a)].add_(part)
+
     # -- Muon as the inner optimizer ------------------------------------------------------------- #
     @staticmethod
     def muon_class(name: str, ndim: int) -> str:
@@ -211,13 +300,7 @@ class WindowEngine:
 
     def _segments(self):
         """[(spec, class, a, b)]: the part [a, b) (flat element range) of every tensor inside this rank's shard."""
-        st = self.store
-        out = []
-        for s in self.layout.specs:
-            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
-            if a < b:
-                out.append((s, self.muon_class(s.name, len(s.shape)), a, b))
-        return out
+        return [(s, self.muon_class(s.name, len(s.shape)), a, b) for s, a, b, _ in self.layout.segments(self.rank)]
 
     @torch.no_grad()
     def _muon_step(self, lr: float) -> None:
@@ -303,6 +386,8 @@ class WindowEngine:
 
     def _compute_shadow_ptrs(self) -> list[int]:
         st = self.store
+        if self.fsdp:
+            return [st.compute_shard.data_ptr()]
         if st.compute is st.master_shard:
             return []
         esz = st.compute.element_size()
@@ -313,6 +398,9 @@ class WindowEngine:
     def _publish_compute(self) -> None:
         """CPU / generic path: compute[lo:hi] <- master shard, then make every rank's copy whole."""
         st = self.store
+        if self.fsdp:
+            st.refresh_compute_from_master()
+            return
         if st.compute is not st.master_shard:
             st.compute[st.lo:st.hi].copy_(st.master_shard.to(st.compute.dtype))
         if self.world_size > 1:
@@ -364,8 +452,7 @@ class WindowEngine:
         if self.world_size > 1 and own_slot_ptrs is None:
             self.own_idx.zero_()                    # only this rank's chunks are written: the rest must read as
             self.own_val.zero_()                    # zero for merge_own_payload()
-        # flat pointers are biased so that descriptor offsets (full-model) address the shard arrays
-        bias = st.lo * 4
+        bias = 0                                    # descriptor offsets address the shard arrays directly
         L = native.lib()
         for square in (True, False):
             desc, n_desc, n_chunks = self._desc[square]
@@ -423,7 +510,7 @@ class WindowEngine:
         if self.world_size > 1:
             self._barrier()                        # codes and tables are complete
         at0 = (lambda t: self.heap.peer_ptr(t, 0)) if self.world_size > 1 else (lambda t: t.data_ptr())
-        bias = st.lo * 4
+        bias = 0
         for square in (True, False):
             desc, n_desc, n_chunks = self._desc[square]
             if n_chunks == 0:
@@ -462,10 +549,9 @@ class WindowEngine:
         if sharded:
             self.own_idx.zero_()
             self.own_val.zero_()
-        entries = L.shard_entries(self.rank) if sharded else [(s, 0, s.chunk_rows) for s in L.specs]
+        entries = L.shard_entries(self.rank) if (sharded or self.fsdp) else [(s, 0, s.chunk_rows, s.offset) for s in L.specs]
         parts = []
-        for s, r0, nrows in entries:
-            a = s.offset + r0 * s.h * s.cols - st.lo
+        for s, r0, nrows, a in entries:
             b = a + nrows * s.h * s.cols
             shape = (nrows * s.h, s.cols) if len(s.shape) >= 2 else (s.cols,)
             tr.register_shape(shape)
@@ -730,11 +816,13 @@ class WindowEngine:
         vdt = {torch.float32: 0, torch.bfloat16: 1}[cfg.val_dtype]
         stream = native.stream_ptr()
         np_ = self.layout.n_params
-        bias = st.lo * 4
+        bias = 0
         base_buf = self.theta0 if base == "theta0" else st.master_shard
-        shadow = None
-        if st.compute is not st.master_shard:
-            shadow = st.compute.data_ptr()   # full-size local compute buffer, descriptor offsets are absolute
+        shadow = None                        # the compute-dtype copy of the shard, addressed like the shard arrays
+        if self.fsdp:
+            shadow = st.compute_shard.data_ptr()
+        elif st.compute is not st.master_shard:
+            shadow = st.compute.data_ptr() + st.lo * st.compute.element_size()
         mode = {"sgd": 0, "sign": 1}[cfg.outer_update]
         for square in (True, False):
             desc, n_desc, n_chunks = self._desc[square]
@@ -757,7 +845,10 @@ class WindowEngine:
                                                 base_buf.data_ptr() - bias, st.master_shard.data_ptr() - bias, shadow, None,
                                                 lr, cfg.outer_weight_decay, int(cfg.use_dct), mode, int(not square),
                                                 self.status.data_ptr(), stream), "aggregate_apply")
-        if self.world_size > 1:
+        if self.fsdp:
+            st.gather.invalidate()
+            self._barrier()
+        elif self.world_size > 1:
             self._barrier()
             self._allgather_compute_native()
 
@@ -785,25 +876,29 @@ class WindowEngine:
                 bufs.append((self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]]))
         base_buf = self.theta0 if base == "theta0" else st.master_shard
         clip = self.clip[: len(ids) * L.n_params].view(len(ids), L.n_params)
+        mine: dict[str, list] = {}
+        for s, a, b, la in L.segments(self.rank):
+            mine.setdefault(s.name, []).append((a, b, la))
         for s in L.specs:
+            if s.name not in mine:
+                continue
             tr.register_shape(s.shape)
             idxs, vals = zip(*(L.payload_views(ib, vb, s.name) for ib, vb in bufs))
             vals = [v.float() * (clip[a, s.index] if use_clip else 1.0) for a, v in enumerate(vals)]
             ref = torch.empty(s.shape, dtype=torch.float32, device=self.device)
             if use_clip and bool(self.skip[s.index]):
                 vals = [v * float("nan") for v in vals]
-            g = tr.decode(comp.batch_decompress(ref, list(idxs), list(vals), L.xshape(s.name), s.totalk,
-                                                clip_norm=False), use_dct=cfg.use_dct).reshape(-1)
-            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
-            if a >= b:
-                continue
-            g = g[a - s.offset: b - s.offset]
-            if not torch.isfinite(g).all():
-                st.master_shard[a - st.lo: b - st.lo].copy_(base_buf[a - st.lo: b - st.lo])
-                continue
-            step = torch.sign(g) if cfg.outer_update == "sign" else g
-            st.master_shard[a - st.lo: b - st.lo].copy_(
-                base_buf[a - st.lo: b - st.lo] * (1 - lr * cfg.outer_weight_decay) - lr * step)
+            full = tr.decode(comp.batch_decompress(ref, list(idxs), list(vals), L.xshape(s.name), s.totalk,
+                                                   clip_norm=False), use_dct=cfg.use_dct).reshape(-1)
+            finite = bool(torch.isfinite(full).all())       # a tensor is applied whole or not at all
+            for a, b, la in mine[s.name]:
+                g = full[a - s.offset: b - s.offset]
+                if not finite:
+                    st.master_shard[la: la + (b - a)].copy_(base_buf[la: la + (b - a)])
+                    continue
+                step = torch.sign(g) if cfg.outer_update == "sign" else g
+                st.master_shard[la: la + (b - a)].copy_(
+                    base_buf[la: la + (b - a)] * (1 - lr * cfg.outer_weight_decay) - lr * step)
         self._publish_compute()
 
     # ------------------------------------------------------------------------------------ #
@@ -846,6 +941,15 @@ class WindowEngine:
         """master <- theta0 and compute copy refreshed (undo of an evaluation-time apply)."""
         st = self.store
         st.master_shard.copy_(self.theta0)
+        if self.fsdp:
+            if self.cuda:
+                native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(), st.compute_shard.data_ptr(),
+                                                         st.n_shard, native.stream_ptr()), "cast_bf16")
+                st.gather.invalidate()
+            else:
+                st.refresh_compute_from_master()
+            self._barrier()
+            return
         if self.cuda and st.compute is not st.master_shard:
             native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(),
                                                      st.compute.data_ptr() + st.lo * st.compute.element_size(),
@@ -903,14 +1007,15 @@ class WindowEngine:
     def full_master(self) -> torch.Tensor:
         """The whole fp32 master vector on every rank (shards exchanged by broadcast)."""
         st = self.store
-        if self.world_size == 1:
+        if self.world_size == 1 and not self.fsdp:
             return st.master_shard
         full = torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
-        full[st.lo:st.hi].copy_(st.master_shard)
-        for r in range(self.world_size):
-            a, b = self.layout.shard_range(r)
-            dist.broadcast(full[a:b], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
-                           group=self.group)
+        for p in self.layout.pieces(self.rank):
+            full[p.g_lo:p.g_hi].copy_(st.master_shard[p.local: p.local + (p.g_hi - p.g_lo)])
+        for r in range(self.world_size if self.world_size > 1 else 0):
+            for p in self.layout.pieces(r):
+                dist.broadcast(full[p.g_lo:p.g_hi], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                               group=self.group)
         return full
 
     @torch.no_grad()
@@ -926,14 +1031,21 @@ class WindowEngine:
     @torch.no_grad()
     def load_full_state_dict(self, state: dict) -> None:
         st = self.store
-        for s in self.layout.specs:
+        for s, a, b, la in self.layout.segments(self.rank):
             if s.name not in state:
                 continue
-            src = state[s.name].reshape(-1).to(device=self.device, dtype=torch.float32)
-            a, b = max(s.offset, st.lo), min(s.offset + s.numel, st.hi)
-            if a < b:
-                st.master_shard[a - st.lo: b - st.lo].copy_(src[a - s.offset: b - s.offset])
+            src = state[s.name].reshape(-1)[a - s.offset: b - s.offset].to(device=self.device, dtype=torch.float32)
+            st.master_shard[la: la + (b - a)].copy_(src)
+            if self.fsdp:
+                st.compute_shard[la: la + (b - a)].copy_(src.to(st.compute_dtype))
+        if self.fsdp:
+            st.gather.invalidate()
+            self._barrier()
+        for s in self.layout.specs:
+            if s.name not in state or self.fsdp:
+                continue
             if st.compute is not st.master_shard:
+                src = state[s.name].reshape(-1).to(device=self.device, dtype=torch.float32)
                 st.compute[s.offset: s.offset + s.numel].copy_(src.to(st.compute.dtype))
         for k, v in state.items():
             if k not in self.layout.by_name:

@@ -132,6 +132,39 @@ def main():
     out["m_mean_diff"], out["m_max_diff"] = md.mean().item(), md.max().item()
     out["m_moved_mean"] = (mref.store.master_shard[lo:hi] - start).abs().mean().item()
     out["m_vs_adamw"] = (mref.store.master_shard - ref.store.master_shard).abs().mean().item()
+    # 6. sharded parameters (the FSDP role): weights gathered per block over NVLink on a side stream, weight
+    #    gradients reduce-added into the owners' shards by the GEMM epilogue; two windows, so that the second one
+    #    starts from gathered weights that the first one's outer step has replaced
+    def shard_view(engine, full):
+        return torch.cat([full[p.g_lo:p.g_hi] for p in engine.layout.pieces(engine.rank)])
+
+    def local_view(engine, vec):
+        return torch.cat([vec[p.local: p.local + (p.g_hi - p.g_lo)] for p in engine.layout.pieces(engine.rank)])
+
+    for tag, extra in (("f", {}), ("fq", {"quantize": True, "quant_bins": 256}), ("fk", {"gather_buffers": 8})):
+        fcfg = dataclasses.replace(cfg, shard_params=True, **extra)
+        fmodel = build_model(args, device=dev, dtype=torch.bfloat16, seed=5)
+        fmodel.activation_checkpointing = tag == "fk"
+        feng = WindowEngine(fmodel, fcfg, device=dev, rank=rank, world_size=world, heap=heap)
+        fref = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5),
+                            dataclasses.replace(cfg, **{k: v for k, v in extra.items() if k != "gather_buffers"}), device=dev)
+        for _ in range(2):
+            run(feng, [rank], heap)
+            run(fref, list(range(world)), None)
+        heap.check()
+        out[tag + "_status"] = feng.check_status()
+        out[tag + "_master_max_diff"] = (local_view(feng, feng.store.master_shard)
+                                         - shard_view(feng, fref.store.master_shard)).abs().max().item()
+        out[tag + "_ef_max_diff"] = (local_view(feng, feng.ef) - shard_view(feng, fref.ef)).abs().max().item()
+        out[tag + "_ef_scale"] = fref.ef.abs().max().item()
+        out[tag + "_scale"] = fref.store.master_shard.abs().max().item()
+        out[tag + "_moved"] = (fref.store.master_shard - fref.theta0).abs().max().item()
+        out[tag + "_gathers"] = feng.store.gather.gathers
+        out[tag + "_no_full_buffers"] = feng.store.compute is None and feng.store.grad is None
+        t = toks[0, 0].to(dev)
+        with torch.no_grad():
+            out[tag + "_loss_diff"] = abs(float(fmodel.loss(t[:, :-1], t[:, 1:])) - float(fref.model.loss(t[:, :-1], t[:, 1:])))
+
     heap.barrier()
     torch.cuda.synchronize()
     heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank

@@ -1,0 +1,112 @@
+"""Sharded parameters (the FSDP role) on CPU: layout arithmetic, and a 2-rank gloo run against the engine that
+keeps weights and gradients whole on every rank."""
+
+import torch
+
+from templar_b200.models.llama import LlamaModel, ModelArgs, PRESETS, build_model
+from templar_b200.parallel.flat import FlatLayout
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+from templar_b200.utils.synthetic import synthetic_payload
+from test_distributed_cpu import launch
+
+
+def _named(args):
+    with torch.device("meta"):
+        m = LlamaModel(args)
+    return [(n, tuple(p.shape)) for n, p in m.named_parameters()]
+
+
+def test_unit_sharding_covers_every_element_once_and_balances():
+    for preset, world in (("1B", 8), ("150M", 8), ("tiny", 2), ("8B", 8)):
+        L = FlatLayout(_named(PRESETS[preset]), 64, 32, world, shard_params=True)
+        cover = []
+        for r in range(world):
+            local = 0
+            for p in L.pieces(r):
+                assert p.local >= local and p.local % 64 == 0          # pieces do not overlap in the shard arrays
+                local = p.local + (p.g_hi - p.g_lo)
+                cover.append((p.g_lo, p.g_hi))
+            assert local <= L.shard_size(r)
+        cover.sort()
+        spans = sorted((s.offset, s.offset + s.numel) for s in L.specs)
+        # the union of all ranks' pieces is exactly the union of the tensors
+        merged = []
+        for a, b in cover:
+            if merged and merged[-1][1] == a:
+                merged[-1][1] = b
+            else:
+                assert not merged or merged[-1][1] <= a              # no element is owned twice
+                merged.append([a, b])
+        assert sum(b - a for a, b in merged) == sum(b - a for a, b in spans)
+        sizes = [L.shard_size(r) for r in range(world)]
+        # even when the chunk rows of every unit divide by the world size; 12 chunk rows over 8 ranks (150M) cannot be
+        slack = 1.25 if preset == "150M" else 1.01
+        assert max(sizes) < slack * (sum(sizes) / world) + 64 * 8192, (preset, sizes)
+        # every matrix unit is cut at multiples of its chunk edge: a warp of the gradient GEMM's epilogue (32 rows)
+        # never straddles two owners
+        for ui, u in enumerate(L.units):
+            if len(u.specs[0].shape) == 2:
+                for p in L.unit_pieces[ui]:
+                    if p is not None:
+                        assert (p.g_lo - u.g_lo) % (u.specs[0].h * u.cols) == 0
+        # packed projections are one unit, in the order the model multiplies them
+        names = [[s.name.split(".", 2)[-1] for s in u.specs] for u in L.units if u.group == "layers.0"]
+        assert ["attention.wq.weight", "attention.wk.weight", "attention.wv.weight"] in names
+        assert ["feed_forward.w1.weight", "feed_forward.w3.weight"] in names
+
+
+def test_descriptors_address_the_shard_arrays():
+    """elem_off + (chunk_row0 + y) * h * cols must land on the local offset of that chunk row."""
+    L = FlatLayout(_named(PRESETS["tiny"]), 64, 32, 2, shard_params=True)
+    for r in range(2):
+        seg = {(s.name, a): la for s, a, b, la in L.segments(r)}
+        d = L.descriptors(r, square=None)
+        ent = L.shard_entries(r)
+        assert len(d) == len(ent)
+        for row, (s, r0, nrows, local) in zip(d, ent):
+            assert row["elem_off"] + r0 * s.h * s.cols == local
+            assert 0 <= local and local + nrows * s.h * s.cols <= L.shard_size(r)
+        assert seg
+
+
+def test_single_process_sharded_engine_equals_the_plain_engine():
+    args = ModelArgs(dim=128, n_layers=3, n_heads=2, vocab_size=256, intermediate_size=256, max_seq_len=32)
+
+    def run(shard, ckpt=False):
+        m = build_model(args, seed=3)
+        m.activation_checkpointing = ckpt
+        eng = WindowEngine(m, EngineConfig(shard_params=shard, max_peers=2))
+        g = torch.Generator().manual_seed(1)
+        eng.snapshot()
+        losses = []
+        for _ in range(2):
+            for _ in range(2):
+                tok = torch.randint(0, 256, (2, 33), generator=g)
+                losses.append(float(eng.micro_step(tok[:, :-1], tok[:, 1:], 0.5)))
+            eng.optimizer_step()
+        eng.compress()
+        eng.load_peer_payload(1, synthetic_payload(eng.layout, 1))
+        eng.outer_step(2)
+        eng.apply_single_peer(1, 0.1)
+        after = {k: v.clone() for k, v in eng.full_state_dict().items() if v.is_floating_point()}
+        eng.restore()
+        return losses, after, eng.full_state_dict(), eng
+
+    l0, a0, s0, _ = run(False)
+    for ckpt in (False, True):
+        l1, a1, s1, e1 = run(True, ckpt)
+        assert l0 == l1
+        for k in a0:
+            assert torch.equal(a0[k], a1[k]) and torch.equal(s0[k].float(), s1[k].float()), k
+        assert e1.store.compute is None and e1.store.grad is None and e1.store.gather.gathers > 0
+
+
+def test_two_rank_sharded_parameters_match_whole_weights_engine():
+    res = launch(2, [], worker="_gloo_fsdp_worker.py", port=29649, timeout=900)
+    assert len(res) == 2
+    for r in res:
+        for tag in ("fsdp", "fsdp_ckpt"):
+            assert r[tag]["loss"] < 1e-6 and r[tag]["weights"] < 1e-6, r
+            assert r[tag]["moved"] > 1e-5 and r[tag]["full_buffers"], r
+            assert r[tag]["shard_elems"] < 0.51 * r[tag]["total"] + 4096, r
+        assert r["fsdp_quant"]["loss"] < 1e-6 and r["fsdp_quant"]["weights"] < 1e-6, r

@@ -45,6 +45,15 @@ def test_two_rank_runtime_and_window():
         # Muon inner optimizer: sharded == single rank up to the bf16 roundings inside Newton-Schulz
         assert r["m_status"] == 0 and r["m_vs_adamw"] > 0, r
         assert r["m_mean_diff"] < 0.1 * r["m_moved_mean"] and r["m_max_diff"] < 0.1, r
+        # sharded parameters: same weights and error feedback as one rank with the whole batch, up to the order of
+        # the fp32 reduce-adds and the bf16 roundings of two pipelines; no full-size weight or gradient buffer
+        for tag in ("f", "fq", "fk"):
+            assert r[tag + "_status"] == 0 and r[tag + "_no_full_buffers"], (tag, r)
+            assert r[tag + "_moved"] > 1e-4, (tag, r)
+            assert r[tag + "_master_max_diff"] < 2e-3 * max(r[tag + "_scale"], 1.0), (tag, r)
+            assert r[tag + "_ef_max_diff"] < 0.05 * r[tag + "_ef_scale"], (tag, r)
+            assert r[tag + "_loss_diff"] < 2e-2, (tag, r)
+        assert r["fk_gathers"] < r["f_gathers"], r        # enough buffers for every block: gathered once per step
         if "q_val_max_diff" in r:
             assert r["q_val_max_diff"] < 0.05 * r["q_val_scale"], r
             assert r["q_codes_equal"] > 0.9, r
