@@ -234,38 +234,41 @@ def run_ours(a):
         return float(t.item()), native.launch_count - l0, clocks
 
     def breakdown():
-        marks = []
-
-        def mark(name):
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            marks.append((name, e))
-
-        mark("start")
-        eng.snapshot(); mark("snapshot")
+        """One extra window with a CUDA event at every phase boundary (and inside the optimizer, compress and outer
+        steps); per phase the MAX over ranks, since a rank's barrier wait is another rank's work."""
+        eng.start_trace()
+        eng.snapshot()
         for m in range(A):
             tok = dev_tokens[m % n_pool]
             eng.micro_step(tok[:, :-1], tok[:, 1:], 1.0 / A)
-        mark("micro_steps")
-        eng.optimizer_step(); mark("optimizer_step")
+        eng.optimizer_step()
         own_ptrs = None
         if heap is not None:
             own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
-        eng.compress(own_slot_ptrs=own_ptrs); mark("compress")
+        eng.compress(own_slot_ptrs=own_ptrs)
         for j in hosted:
             eng.load_peer_payload(j // world, host_payload[j])
-        mark("peer_payload_h2d")
+        eng._mark("peer_payload_h2d")
         if world > 1:
             eng._barrier()
-        eng.outer_step(a.peers); mark("outer_step")
-        torch.cuda.synchronize()
-        return {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 3) for i in range(1, len(marks))}
+            eng._mark("outer.barrier_payloads_staged")
+        eng.outer_step(a.peers)
+        ms = eng.trace_ms()
+        names = sorted(ms)
+        if world > 1:
+            all_names = [None] * world
+            dist.all_gather_object(all_names, names)
+            names = sorted(set().union(*all_names))
+        t = torch.tensor([ms.get(n, 0.0) for n in names], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return {n: round(float(v), 3) for n, v in zip(names, t.tolist())}
 
     ms_total, launches, clocks = timed(False, a.steps, a.warmup)
-    if a.breakdown and rank == 0:
-        print("breakdown_ms " + json.dumps(breakdown()), file=sys.stderr)
-    elif a.breakdown:
-        breakdown()
+    if a.breakdown:
+        bd = breakdown()
+        if rank == 0:
+            print("breakdown_ms " + json.dumps(bd), file=sys.stderr)
     tokens_per_step = B * S * A * world
     value = tokens_per_step * a.steps / (ms_total / 1e3)
     e2e = None

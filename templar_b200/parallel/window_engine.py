@@ -140,7 +140,31 @@ class WindowEngine:
         model._param_gather = self.store.gather          # None unless shard_params: the model gates its blocks on it
         if self.fsdp and self.cuda:
             rec = self.store.stage_blocks()
-            self._stage_table = (torch.tensor(rec, dtype=torch.int64, device=self.device).reshape(-1, 3), len(rec))
+            self._grad_stage_table = (torch.tensor(rec, dtype=torch.int64, device=self.device).reshape(-1, 3), len(rec))
+
+    # -- phase marks ------------------------------------------------------------------------------
+    def start_trace(self) -> None:
+        """Record a CUDA event at every named point of the window from now on (read with :meth:`trace_ms`)."""
+        self._trace = []
+        self._mark("start")
+
+    def _mark(self, name: str) -> None:
+        tr = getattr(self, "_trace", None)
+        if tr is None or not self.cuda:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        tr.append((name, ev))
+
+    def trace_ms(self) -> dict:
+        """Device time between consecutive marks since :meth:`start_trace`, summed per name; ends the trace.
+        A mark's time includes any wait for another rank that its kernels contain (the barriers)."""
+        tr, self._trace = self._trace, None
+        torch.cuda.synchronize(self.device)
+        out: dict[str, float] = {}
+        for (_, a), (name, b) in zip(tr, tr[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
 
     def _slots(self) -> int:
         """Peer-payload slots held by this rank: with a symmetric heap the peers are spread
@@ -162,6 +186,7 @@ class WindowEngine:
     def snapshot(self) -> None:
         """theta0 <- master: opens a window (the next compress / outer step refer to this snapshot)."""
         self.theta0.copy_(self.store.master_shard)
+        self._mark("snapshot")
         self.window_open = True
 
     def zero_grad(self) -> None:
@@ -173,6 +198,7 @@ class WindowEngine:
         """Forward + backward of one micro-batch; returns the (device) mean loss."""
         loss = self.model.loss(tokens, labels, grad_scale)
         loss.backward()
+        self._mark("micro_steps")
         return loss.detach()
 
     @torch.no_grad()
@@ -195,14 +221,18 @@ class WindowEngine:
                                       native.stream_ptr()), "sumsq")
             if self.world_size > 1:
                 dist.all_reduce(self.gnorm_sq, group=self.group)
+            self._mark("opt.grad_norm_allreduce")
             shadows = self._compute_shadow_ptrs()
             native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                                       gshard.data_ptr(), native.ptr_array(shadows), len(shadows), n, lr, cfg.betas[0],
                                       cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
                                       cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
+            self._mark("opt.adamw_and_weight_push")
             if self.world_size > 1:
                 self._barrier()
+                self._mark("opt.barrier_after_push")
                 st.grad.zero_()
+                self._mark("opt.zero_grad")
             return
         # CPU path (same arithmetic); gradients were summed over ranks, the mean is what is applied
         g = gshard / self.world_size
@@ -236,23 +266,27 @@ class WindowEngine:
         n = st.n_shard
         gshard = st.grad_shard[:n]
         self._barrier()
+        self._mark("opt.barrier_before_reduce")
         if self.cuda:
             L = native.lib()
-            table, n_rec = self._stage_table
+            table, n_rec = self._grad_stage_table
             if n_rec:
                 stages = ([self.heap.peer_ptr(st.stage, r) for r in range(self.world_size)]
                           if (self.heap is not None and self.world_size > 1) else [st.stage.data_ptr()])
                 native.check(L.tplr_reduce_blocks(native.ptr_array(stages), len(stages), table.data_ptr(), n_rec,
                                                   st.grad_shard.data_ptr(), native.stream_ptr()), "reduce_blocks")
+            self._mark("opt.reduce_staged")
             native.check(L.tplr_sumsq(gshard.data_ptr(), n, self._sumsq_scratch.data_ptr(), self.gnorm_sq.data_ptr(),
                                       native.stream_ptr()), "sumsq")
             if self.world_size > 1:
                 dist.all_reduce(self.gnorm_sq, group=self.group)
+            self._mark("opt.grad_norm_allreduce")
             shadows = [st.compute_shard.data_ptr()]
             native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                                       gshard.data_ptr(), native.ptr_array(shadows), 1, n, lr, cfg.betas[0],
                                       cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
                                       cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
+            self._mark("opt.adamw")
         else:
             self._reduce_staged_cpu()
             g = gshard / self.world_size
@@ -270,8 +304,10 @@ class WindowEngine:
             p.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + cfg.eps, value=-lr)
             st.compute_shard[:n].copy_(p.to(st.compute_dtype))
         st.zero_grad()
+        self._mark("opt.zero_grad")
         st.gather.invalidate()
         self._barrier()
+        self._mark("opt.barrier_after_zero")
 
     def _reduce_staged_cpu(self) -> None:
         """CPU / gloo: every tensor's gradient was accumulated locally in full size (``stage``); the parts that a
@@ -417,9 +453,11 @@ class WindowEngine:
         st = self.store
         if self.cuda and self.heap is not None:
             self._barrier()
+            self._mark("opt.barrier_before_reduce")
             ptrs = [self.heap.peer_ptr(st.grad, r) for r in range(self.world_size)]
             native.check(native.lib().tplr_reduce_shards(native.ptr_array(ptrs), self.world_size, self.rank, st.lo,
                                                          st.hi - st.lo, native.stream_ptr()), "reduce_shards")
+            self._mark("opt.reduce_shards")
             return
         for r in range(self.world_size):
             a, b = self.layout.shard_range(r)
@@ -470,6 +508,7 @@ class WindowEngine:
                                                 st.master_shard.data_ptr() - bias, idx_ptr, val_ptr,
                                                 self.status.data_ptr(), cfg.momentum_decay, int(cfg.use_dct), 1,
                                                 int(null_round), 1, int(not square), native.stream_ptr()), "compress")
+        self._mark("compress.kernels")
         if cfg.quantize:
             self._quantize_own(on_rank0=own_slot_ptrs is not None)
 
@@ -501,14 +540,17 @@ class WindowEngine:
         L = native.lib()
         if self.world_size > 1:
             self._barrier()                        # every rank's chunks have landed on rank 0
+            self._mark("compress.barrier_payload_assembled")
         if self.rank == 0:
             desc_full, n_full = self._desc_full
             native.check(L.tplr_quantize_values(desc_full.data_ptr(), n_full, self.own_val.data_ptr(), codes.data_ptr(),
                                                 table.data_ptr(), scratch.data_ptr(), self.layout.n_params,
                                                 cfg.quant_bins, float(cfg.quant_range), native.stream_ptr()),
                          "quantize_values")
+        self._mark("compress.quantize_on_rank0")
         if self.world_size > 1:
             self._barrier()                        # codes and tables are complete
+            self._mark("compress.barrier_codes_ready")
         at0 = (lambda t: self.heap.peer_ptr(t, 0)) if self.world_size > 1 else (lambda t: t.data_ptr())
         bias = 0
         for square in (True, False):
@@ -519,6 +561,7 @@ class WindowEngine:
                                                  self.ef.data_ptr() - bias, at0(self.own_idx), at0(self.own_val),
                                                  at0(codes), at0(table), cfg.quant_bins, int(cfg.use_dct),
                                                  int(not square), native.stream_ptr()), "requant_residual")
+        self._mark("compress.requant_residual")
 
     def merge_own_payload(self) -> None:
         """Sharded engine without a symmetric heap: every rank has written only its own chunks of the node's
@@ -808,6 +851,7 @@ class WindowEngine:
             self.skip.zero_()
         elif clip_norm:
             self.compute_peer_norms(peers=ids)
+        self._mark("outer.peer_norms")
         use_clip = clip_norm or clip_override is not None
         if not self.cuda:
             return self._outer_step_torch(ids, lr, use_clip, base)
@@ -845,12 +889,16 @@ class WindowEngine:
                                                 base_buf.data_ptr() - bias, st.master_shard.data_ptr() - bias, shadow, None,
                                                 lr, cfg.outer_weight_decay, int(cfg.use_dct), mode, int(not square),
                                                 self.status.data_ptr(), stream), "aggregate_apply")
+        self._mark("outer.aggregate_apply")
         if self.fsdp:
             st.gather.invalidate()
             self._barrier()
+            self._mark("outer.barrier")
         elif self.world_size > 1:
             self._barrier()
+            self._mark("outer.barrier")
             self._allgather_compute_native()
+            self._mark("outer.weight_allgather")
 
     def _allgather_compute_native(self) -> None:
         """Push the owned range of the compute buffer to every other rank (plain stores over NVLink)."""
