@@ -241,6 +241,12 @@ class Miner(BaseNode, Trainer):
         gradient, _, _ = tplr.prepare_gradient_dict(self, step_window, null_round)
         compress_time = tplr.T() - t0
         put_time = 0.0
+        # The gradient of a window is uploaded once the window is over: validators and peers accept an upload only
+        # between the first block of the next window and `time_window_delta_seconds` after it, so a miner that
+        # finishes early waits for the chain (reference neurons/miner.py:685-701).  Local runs have no clock.
+        if not self.config.local and self.current_window == step_window:
+            tplr.logger.info("Training complete; waiting for window to be exhausted...")
+            await self.wait_until_window(step_window + 1)
         if self.is_master:
             gidx = self.sampler._global_indices()
             ids = self.sampler.ids_for_indices(gidx.tolist())
@@ -250,9 +256,12 @@ class Miner(BaseNode, Trainer):
             put_time = await self.comms.put(state_dict={k: (v.clone() if torch.is_tensor(v) else v) for k, v in gradient.items()},
                                             uid=str(self.uid), window=step_window, key="gradient",
                                             global_step=self.global_step, local=False, stale_retention=100)
-        # upload-time acceptance window of the peers' gradients
-        sync_block = (step_window + 1) * hp.blocks_per_window
+        # upload-time acceptance window of the peers' gradients: it opens with the first block of the window the
+        # chain is in now, a block that exists (reference neurons/miner.py:718-730)
+        sync_block = (self.current_window if not self.config.local else step_window + 1) * hp.blocks_per_window
         ts = await self.loop.run_in_executor(None, self.query_block_timestamp, sync_block)
+        if ts is None:
+            tplr.logger.warning(f"Could not get timestamp for sync block {sync_block}. Using current time as fall back.")
         tmin = datetime.fromtimestamp(ts if ts is not None else time.time(), tz=timezone.utc)
         tmax = tmin + timedelta(seconds=getattr(hp, "time_window_delta_seconds", 70))
         if self.config.test:

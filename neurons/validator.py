@@ -89,7 +89,9 @@ class Validator(BaseNode, Trainer):
             from templar_b200.parallel.symmetric import SymmetricHeap
 
             heap = SymmetricHeap.create(self.device, self.rank, self.world_size)
-        self.attach_engine(heap=heap)
+        # one payload slot more than the largest gather: the uid under evaluation is staged beside the gathered peers
+        self.attach_engine(heap=heap, max_peers=int(getattr(self.hparams, "gather_peer_count", 8))
+                           + int(getattr(self.hparams, "reserve_peer_count", 0)) + 1)
         self.transformer = tplr.compress.ChunkingTransformer(self.model, target_chunk=self.hparams.target_chunk)
         self.compressor = tplr.compress.TopKCompressor(use_quantization=False)
         self.init_optimizers_schedulers(validator=True)
@@ -609,6 +611,7 @@ class Validator(BaseNode, Trainer):
         await self.save_state()
         await self.maybe_switch_shard(self.sync_window, validator=True)
         gather_result = None
+        self._accept_window = (None, None)
         if self.is_master:
             await self.comms.refresh_active_peers()
             self.comms.update_peers_with_buckets()
@@ -626,6 +629,7 @@ class Validator(BaseNode, Trainer):
             tmax = tmin + timedelta(seconds=hp.time_window_delta_seconds) if tmin is not None else None
             if self.config.local:
                 tmin = tmax = None
+            self._accept_window = (tmin, tmax)
             if self.comms.peers:
                 t_gather = tplr.T()
                 gather_result = await self.comms.gather_with_reserve(
@@ -654,7 +658,7 @@ class Validator(BaseNode, Trainer):
                 self.note_delivered(list(gather_result.uids))
                 self.offload_gather_results(gather_result, log=False)
             t_eval = tplr.T()
-            scored = await self.score_peers(gather_result, n_peers)
+            scored = await self.score_peers(gather_result, n_peers, *self._accept_window)
             self.log_timing("evaluation", tplr.T() - t_eval)
             if self.is_master:
                 self.apply_negative_evaluation_penalties()
@@ -730,7 +734,7 @@ class Validator(BaseNode, Trainer):
         eng = self.engine
         sd = vars(gather_result.state_dict) if (self.is_master and gather_result is not None) else None
         n = len(gather_result.uids) if sd is not None else 0
-        n = min(n, eng.cfg.max_peers)
+        n = min(n, eng.cfg.max_peers - 1)          # the last slot is kept for the uid under evaluation
         t = torch.tensor([n], dtype=torch.int32, device=self.device)
         dist_helper.broadcast(t, src=0)
         n = int(t.item())
@@ -742,26 +746,62 @@ class Validator(BaseNode, Trainer):
         self.staged_peers = n                       # slot j holds uids[j]: the overlap check reads the slots
         return n
 
-    async def score_peers(self, gather_result, n_peers: int) -> list[dict]:
-        """For a sample of the gathered peers: loss on the peer's own data and on random data, before
-        and after applying that peer's gradient alone; update gradient / binary / sync scores."""
+    async def fetch_eval_gradient(self, uid: int, time_min, time_max) -> dict | None:
+        """Master only: the upload of the uid that is about to be scored, fetched from the uid's own bucket with
+        the window's acceptance times, checked like a gathered payload and against the data the uid was assigned.
+        A missing, too early or too late upload is slashed as missing; a malformed one as invalid (reference
+        neurons/validator.py:1912-1957).  A transport error is neither: the uid is only skipped.  Returns the
+        payload, or ``None`` when the uid cannot be scored this window."""
+        try:
+            res = await self.comms.get(uid=str(uid), window=self.sync_window, key="gradient", local=False, stale_retention=10,
+                                       time_min=time_min, time_max=time_max)
+        except Exception as e:  # noqa: BLE001
+            tplr.logger.warning(f"[validator] fetch gradient failed for {uid}: {e} - marking invalid")
+            return None
+        if res.status == "ERROR":
+            tplr.logger.warning(f"[validator] fetch gradient failed for {uid} (transport) - marking invalid")
+            return None
+        if not res.success or not isinstance(res.data, dict):
+            tplr.logger.info(f"UID {uid}: no acceptable gradient for window {self.sync_window} ({res.status}); slashing")
+            self.slash_for_missing_gradient(uid)
+            return None
+        state = res.data
+        if (state.get("metadata") or {}).get("dummy"):               # the liveness marker of a miner that has not trained yet
+            self.slash_for_missing_gradient(uid)
+            return None
+        try:
+            self.validate_gradient_data(uid, state)
+            missing = self.expected_compressed_params - set(state)
+            if missing:
+                raise ValueError(f"UID {uid}: payload lacks {len(missing)} expected entries, e.g. {sorted(missing)[0]}")
+            self.log_digest_match(uid, state.get("metadata", {}) or {})
+        except Exception as e:  # noqa: BLE001
+            tplr.logger.warning(f"UID {uid}: invalid gradient ({e}); slashing")
+            self.slash_for_invalid_gradient(uid, e)
+            return None
+        return state
+
+    async def score_peers(self, gather_result, n_peers: int, time_min=None, time_max=None) -> list[dict]:
+        """For a sample of the *evaluation* peers (whether or not they are on the gather list): fetch the uid's own
+        upload, check it, and measure the loss on the uid's assigned data and on random data before and after
+        applying that gradient alone; update gradient / binary / sync scores.  The loop ends early when the chain
+        moves to the next window (reference neurons/validator.py:1879-2318)."""
         hp, eng = self.hparams, self.engine
         if self.is_master:
             bins = self.bin_evaluation_peers(getattr(hp, "num_evaluation_bins", 5))
             uids = self.select_evaluation_uids_from_bin(bins, self.select_next_bin_for_evaluation(max(len(bins), 1)))
-            gathered = list(gather_result.uids)
-            uids = [u for u in uids if u in gathered] or gathered[: hp.uids_per_window]
+            if not uids:                                   # no eligible evaluation peer known yet: score who delivered
+                uids = list(gather_result.uids)[: hp.uids_per_window]
             pad = uids[: N_UIDS] + [-1] * (N_UIDS - len(uids))
         else:
             pad = [-1] * N_UIDS
-            gathered = []
         t = torch.tensor(pad, dtype=torch.int32, device=self.device)
         dist_helper.broadcast(t, src=0)
         uids = [int(u) for u in t.tolist() if u >= 0]
-        g = torch.tensor((gathered + [-1] * N_UIDS)[:N_UIDS], dtype=torch.int32, device=self.device)
-        dist_helper.broadcast(g, src=0)
-        gathered = [int(u) for u in g.tolist() if u >= 0]
         median = self.compute_peer_val_norms(n_peers)
+        eval_slot = eng.cfg.max_peers - 1                  # spare slot: the gathered peers keep theirs for the outer step
+        if n_peers > eval_slot:
+            raise RuntimeError("the engine has no spare payload slot for the uid under evaluation")
         eng.snapshot()
         random_seed = random.randint(1000, 10_000_000) if self.is_master else 0
         rs = torch.tensor([random_seed], dtype=torch.long, device=self.device)
@@ -772,13 +812,29 @@ class Validator(BaseNode, Trainer):
         loss_before_random = lb_rand_sum / max(lb_rand_n, 1)
         out = []
         lr_eval = self.lr * getattr(hp, "eval_lr_factor", 1.0)
+        eval_window = self.current_window
         for uid in uids:
             t0 = time.time()
-            slot = gathered.index(uid)
+            state, stop = None, False
+            if self.is_master:
+                stop = (not self.config.local) and self.current_window != eval_window
+                if stop:
+                    tplr.logger.info(f"Window changed during evaluation (was {eval_window}, now {self.current_window}); "
+                                     f"leaving the evaluation loop after {len(out)}/{len(uids)} uids")
+                else:
+                    self.peers_last_eval_window[uid] = self.sync_window
+                    state = await self.fetch_eval_gradient(uid, time_min, time_max)
+            flags = torch.tensor([int(state is not None), int(stop)], dtype=torch.int32, device=self.device)
+            dist_helper.broadcast(flags, src=0)                       # every rank takes the master's view
+            if bool(flags[1].item()):
+                break
+            if not bool(flags[0].item()):
+                continue
+            eng.stage_single_peer(state, eval_slot)
             self.sampler.set_window_uid(uid, self.sync_window)
             s, n = await self.evaluate_model(self.model, self.loader)
             loss_before_own = s / max(n, 1)
-            eng.apply_single_peer(slot, lr_eval, median)
+            eng.apply_single_peer(eval_slot, lr_eval, median)
             s, n = await self.evaluate_model(self.model, self.loader)
             loss_after_own = s / max(n, 1)
             self.sampler.set_window_uid(random_seed, self.sync_window)

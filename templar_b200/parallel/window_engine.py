@@ -1052,6 +1052,31 @@ class WindowEngine:
         self._barrier()
 
     @torch.no_grad()
+    def stage_single_peer(self, payload: dict | None, peer: int) -> None:
+        """One peer's reference-format payload (held by rank 0; ``None`` elsewhere) into the slot of peer index
+        ``peer``: the validator stages the upload of the uid it is about to score this way.  With a symmetric heap
+        rank 0 stores into the owner's slot over NVLink, otherwise the flat buffers are broadcast."""
+        owner, slot = self.slot_of(peer)
+        if self.world_size == 1:
+            self.load_peer_payload(slot, payload)
+            return
+        if self.heap is not None:
+            if self.rank == 0:
+                idx, val = self.pack_payload(payload, device=self.device)
+                for src, dst in ((idx, self.peer_idx[slot]), (val, self.peer_val[slot])):
+                    native.check(native.lib().tplr_push_copy(
+                        src.data_ptr(), native.ptr_array([self.heap.peer_ptr(dst, owner)]), 1,
+                        -(-src.numel() * src.element_size() // 16) * 16, native.stream_ptr()), "push_copy")
+        else:
+            if self.rank == 0:
+                idx, val = self.pack_payload(payload, device=self.device)
+                self.peer_idx[slot].copy_(idx)
+                self.peer_val[slot].copy_(val)
+            dist.broadcast(self.peer_idx[slot], src=0, group=self.group)
+            dist.broadcast(self.peer_val[slot], src=0, group=self.group)
+        self._barrier()
+
+    @torch.no_grad()
     def full_master(self) -> torch.Tensor:
         """The whole fp32 master vector on every rank (shards exchanged by broadcast)."""
         st = self.store

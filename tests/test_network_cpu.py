@@ -515,17 +515,158 @@ def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
         m.set_dataloader()
         m.config.local, m.start_window = False, 10
         before = {n: p.detach().clone() for n, p in m.model.named_parameters()}
+        def tick(to_window):           # outside local mode a miner waits for the chain before it uploads
+            asyncio.get_running_loop().call_later(0.3, lambda: setattr(m, "current_window", to_window))
+
         m.current_window = m.comms.current_window = 11                 # offset 1 < warm-up of 3 windows
+        tick(12)
         await m.run_window(11)
         assert float(m.engine.ef.abs().max()) == 0.0 and float(m.engine.own_val.abs().max()) == 0.0
         for n, p in m.model.named_parameters():
             assert torch.equal(p.detach(), before[n]), n
         m.comms.peers = []                                             # warm-up over, but nobody to gather from
         m.current_window = m.comms.current_window = 14
+        tick(15)
         await m.run_window(14)
         assert float(m.engine.ef.abs().max()) == 0.0
         for n, p in m.model.named_parameters():
             assert torch.equal(p.detach(), before[n]), n
+    run(go())
+
+
+def test_upload_times_and_own_uploads_decide_who_is_gathered_scored_and_slashed(cwd_tmp):
+    """The protocol on a chain with a clock (no ``--local``).  Miners finish training early, wait for the window to
+    end and upload after the first block of the next window; everyone accepts an upload only from that block's
+    time until ``time_window_delta_seconds`` later.  The validator scores every evaluation peer from that peer's
+    OWN upload: a miner that is not on the gather list is scored all the same, an upload stamped before the window
+    opened or after it closed is slashed as missing, and a malformed one is zeroed."""
+    from datetime import datetime, timedelta, timezone
+    import io
+    import time as _time
+
+    async def go():
+        bpw, w = 4, 6
+        store = MemoryStore()
+        chain = StaticChain(n=7, manual=True, block_time=1.0)
+        chain._manual_block = w * bpw
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        miners = {u: _node(Miner, Miner.miner_config, ["--uid", str(u), "--peers", "2", "3", "5"], store, chain) for u in (2, 3, 4)}
+        ghosts = {u: tplr.Comms(wallet=tplr.backends.chain.StaticWallet(f"hotkey-{u}"), config=miners[2].config,
+                                hparams=miners[2].hparams, uid=u, store=store, subtensor=chain) for u in (1, 5, 6)}
+        for c in ghosts.values():
+            c.try_commit(c.wallet, c.bucket)
+        waiting = {u: asyncio.Event() for u in miners}
+        for u, m in miners.items():
+            m.config.local = False                       # a clock, acceptance times, the wait before the upload
+            m.hparams.blocks_per_window = bpw
+            m.loop = asyncio.get_running_loop()
+            m.comms.commitments = await m.comms.get_commitments()
+            m.comms.peers = [2, 3, 5]
+            m.gather_timeout = 3
+            m.start_window = 0
+            await m.dataset_manager.initialize_datasets(0)
+            m.set_dataloader()
+            m.current_window = m.comms.current_window = w
+            orig = m.wait_until_window
+
+            async def waits(target, _orig=orig, _u=u):
+                waiting[_u].set()
+                await _orig(target)
+            m.wait_until_window = waits
+
+        async def clock():
+            """Once every miner has trained and waits: the ghosts' uploads appear (copies of miner 4's payload, one
+            of them malformed), the next window's first block is stamped `now`, and the chain moves on."""
+            await asyncio.gather(*(e.wait() for e in waiting.values()))
+            pay = {k: (t.clone() if torch.is_tensor(t) else t) for k, t in miners[4].engine.own_payload().items()}
+            pay["metadata"] = {"window": w}
+            bad = dict(pay)
+            name = next(k for k in pay if k.endswith("vals") and pay[k].numel() > 8)
+            bad[name] = torch.full_like(pay[name].float(), float("nan"))
+            bad[name[:-4] + "quant_params"] = None
+            for u, c in ghosts.items():
+                await c.put(state_dict=bad if u == 6 else pay, uid=str(u), window=w, key="gradient", local=False)
+            chain.genesis = _time.time() - (w + 1) * bpw * chain.block_time
+            t_open = datetime.fromtimestamp(chain.block_timestamp((w + 1) * bpw), tz=timezone.utc)
+            delta = timedelta(seconds=miners[2].hparams.time_window_delta_seconds)
+            store.faults[f"gradient-{w}-5-"] = ("mtime", t_open - timedelta(seconds=5))           # before the window opened
+            store.faults[f"gradient-{w}-1-"] = ("mtime", t_open + delta + timedelta(seconds=5))   # after it closed
+            store.faults[f"gradient-{w}-6-"] = ("mtime", t_open + timedelta(seconds=1))
+            chain._manual_block = (w + 1) * bpw
+            for m in miners.values():
+                m._on_block(chain.block)
+
+        res, _ = await asyncio.gather(asyncio.gather(*(m.run_window(w) for m in miners.values())), clock())
+        for r in res:                                      # peer 5's upload carries a stamp from before the window opened
+            assert r["skipped_uids"] == [5] and r["global_step"] == 1, r
+        for u in (2, 3, 4):                               # the real uploads were made after the window had opened
+            key = next(k for (b, k) in store.objects if k.startswith(f"gradient-{w}-{u}-"))
+            stamp = next(v_[1] for (b, k), v_ in store.objects.items() if k == key)
+            assert stamp.timestamp() >= chain.block_timestamp((w + 1) * bpw) - 1e-3
+        # the validator: gather list [2, 3]; evaluation peers are everybody who uploads
+        v.config.local = False
+        v.hparams.blocks_per_window, v.hparams.uids_per_window = bpw, 6
+        v.loop = asyncio.get_running_loop()
+        v.comms.commitments = await v.comms.get_commitments()
+        v.gather_timeout = 3
+        await v.dataset_manager.initialize_datasets(0)
+        v.set_dataloader(validator=True)
+        v.current_window, v.comms.current_window, v.sync_window = w + 1, w + 1, w
+        slashed = {"missing": [], "invalid": []}
+        for kind, name in (("missing", "slash_for_missing_gradient"), ("invalid", "slash_for_invalid_gradient")):
+            def spy(uid, *a, _orig=getattr(v, name), _kind=kind):
+                slashed[_kind].append((uid, float(v.final_scores[uid])))
+                _orig(uid, *a)
+                slashed[_kind][-1] += (float(v.final_scores[uid]),)
+            setattr(v, name, spy)
+        for u in (1, 5, 6):
+            v.final_scores[u] = 1.0
+        out = await v.run_window()
+        assert sorted(out["gathered"]) == [2, 3]
+        scored = sorted(r["uid"] for r in out["scored"])
+        assert scored == [2, 3, 4], out["scored"]          # 4 is on nobody's gather list and is scored from its own upload
+        # too early / too late: the score is scaled by the missing-gradient rate; malformed: zeroed
+        assert sorted(slashed["missing"]) == [(1, 1.0, pytest.approx(0.75)), (5, 1.0, pytest.approx(0.75))]
+        assert slashed["invalid"] == [(6, 1.0, 0.0)]
+        assert {1, 5, 6} <= v.evaluated_uids
+        for n in [*miners.values(), v]:
+            n.metrics_logger.close()
+        import json as _json
+        slashes = [_json.loads(l) for l in (cwd_tmp / "metrics.jsonl").read_text().splitlines() if "validator_slash" in l]
+        assert any(r["tags"].get("reason_code") == "invalid_gradient" and r["tags"].get("eval_uid") == "6" for r in slashes)
+    run(go())
+
+
+def test_validator_leaves_the_evaluation_loop_when_the_window_changes(cwd_tmp):
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        miners = [_node(Miner, Miner.miner_config, ["--uid", str(u), "--peers", "2", "3"], store, chain) for u in (2, 3)]
+        for n in miners + [v]:
+            n.loop = asyncio.get_running_loop()
+            n.comms.commitments = await n.comms.get_commitments()
+            n.comms.peers = [2, 3]
+            n.gather_timeout = 5
+            await n.dataset_manager.initialize_datasets(0)
+        for m in miners:
+            m.set_dataloader()
+            m.current_window = m.comms.current_window = 1
+        v.set_dataloader(validator=True)
+        await asyncio.gather(*(m.run_window(1) for m in miners))
+        v.current_window, v.comms.current_window, v.sync_window = 2, 1, 1
+        v.config.local = False                         # the loop watches the clock only outside local mode
+        v.hparams.uids_per_window = 2
+        fetched = []
+        orig = v.fetch_eval_gradient
+
+        async def fetch(uid, tmin, tmax):
+            fetched.append(uid)
+            v.current_window = 3                       # the chain moves on while the first uid is being scored
+            return await orig(uid, None, None)
+        v.fetch_eval_gradient = fetch
+        v.query_block_timestamp = lambda block: None   # no acceptance window: this test is about the loop exit
+        out = await v.run_window()
+        assert len(fetched) == 1 and len(out["scored"]) == 1 and out["global_step"] == 1
     run(go())
 
 
