@@ -20,3 +20,6 @@ from .schemas import Bucket, CommsGetResult  # noqa: E402,F401
 from .dataset import DatasetLoader, SubsetLoader  # noqa: E402,F401
 from .sharded_dataset import SharedShardedDataset, ShardedDatasetManager, SyntheticDataset, compute_shard_state  # noqa: E402,F401
 from .sharded_sampler import EvalSampler, MinerSampler  # noqa: E402,F401
+from .wandb_ops import initialize_wandb  # noqa: E402,F401
+from .metrics import MetricsLogger  # noqa: E402,F401
+from . import backends, metrics, model_factory, muon, profilers, wandb_ops  # noqa: E402,F401

@@ -1,0 +1,61 @@
+"""The flat public namespace (the reference's ``tplr.*``, src/tplr/__init__.py:22-40) and the ``tplr`` alias package."""
+
+import inspect
+
+import templar_b200
+
+# name -> parameters the reference's callers pass by keyword (a subset of each signature)
+SURFACE = {
+    "Comms": ["wallet", "save_location", "key_prefix", "config", "hparams", "uid"],
+    "ChainManager": [],
+    "DCPCheckpointer": ["comms", "uid", "version", "repo_root"],
+    "MinerSampler": ["dataset", "uid", "window", "steps_per_window", "micro_bs", "batch_size", "target_batch_size", "rank", "world_size"],
+    "EvalSampler": ["dataset", "uid", "window", "steps_per_window", "micro_bs", "batch_size", "validation_bs", "rank", "world_size"],
+    "SharedShardedDataset": ["shard_index", "sequence_length", "rank", "world_size"],
+    "ChunkingTransformer": ["model", "target_chunk"],
+    "TopKCompressor": ["use_quantization", "quantization_bins", "quantization_range"],
+    "MetricsLogger": ["prefix", "uid", "config", "role", "group", "job_type"],
+    "prepare_gradient_dict": ["miner", "step_window", "null_round"],
+    "outer_step": ["model", "optimizer", "gather_result", "transformer", "compressor", "xshapes", "totalks", "device",
+                   "is_master", "world_size", "use_dct", "wandb_run", "global_step"],
+    "update_peers": ["instance", "window", "peer_start"],
+    "load_checkpoint_with_fallback": ["instance"],
+    "handle_checkpoint_catchup": ["instance"],
+    "catchup_with_aggregation_server": ["instance", "checkpoint_current_window"],
+    "compare_model_with_debug_dict": ["model", "debug_dict", "learning_rate", "param_avg_change", "min_step_size", "index_range"],
+    "check_uid_index_overlap": ["neuron", "gather_result", "window", "overlap_threshold"],
+    "determine_slash_egregiousness": [], "instantiate_slashing_multiplier": [],
+    "pack_12bit_indices": ["indices"], "unpack_12bit_indices": ["packed", "values_shape"],
+    "load_hparams": ["hparams_dir", "use_local_run_hparams"],
+    "initialize_wandb": [], "Bucket": [], "CommsGetResult": [],
+    "logger": None, "T": None, "P": None, "log_with_context": None, "setup_loki_logger": None,
+    "muon": None, "distributed": None, "compress": None,
+}
+
+
+def test_flat_namespace_has_the_reference_surface():
+    for name, params in SURFACE.items():
+        assert hasattr(templar_b200, name), name
+        if params:
+            obj = getattr(templar_b200, name)
+            sig = inspect.signature(obj.__init__ if inspect.isclass(obj) else obj)
+            missing = [p for p in params if p not in sig.parameters]
+            assert not missing, (name, missing)
+    assert templar_b200.muon.Muon and templar_b200.muon.SingleDeviceMuonWithAuxAdam
+    assert templar_b200.distributed.dist_helper is not None
+
+
+def test_tplr_is_the_same_package_under_the_reference_name():
+    import tplr
+    import tplr.compress
+    import tplr.neurons
+    from tplr.compress import TopKCompressor
+    from tplr.muon import Muon
+    import tplr.distributed as d
+
+    assert tplr.__version__ == templar_b200.__version__
+    assert tplr.compress is templar_b200.compress and tplr.neurons is templar_b200.neurons
+    assert tplr.Comms is templar_b200.Comms and TopKCompressor is templar_b200.compress.TopKCompressor
+    assert Muon is templar_b200.muon.Muon and d.dist_helper is templar_b200.distributed.dist_helper
+    assert tplr.initialize_wandb is templar_b200.wandb_ops.initialize_wandb
+    assert tplr.MetricsLogger is templar_b200.metrics.MetricsLogger
