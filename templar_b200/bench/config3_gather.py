@@ -11,10 +11,10 @@ Every rank is one peer and holds fp32 momentum-like tensors with the parameter s
              ONE kernel per rank pulls every peer's packed payload over NVLink for the chunks this rank
              owns, unpacks, clips, means, inverse-DCTs and updates, and the bf16 result is pushed to all
              ranks.  No intermediate all-gather buffer exists.
-  reference  the algorithm of the reference's gather path on the same box with torch + NCCL: per-tensor
-             encode + top-k + pack (templar_b200.compress, the line-for-line oracle of src/tplr/compress.py),
-             ``all_gather`` of the packed tensors, batch_decompress + inverse DCT per tensor, sign update.
-             Run with ``--reference`` (slow: seconds per k).
+  reference  the UNMODIFIED reference on the same box (``--reference``; baseline/reference_config3.py): its own
+             ``ChunkingTransformer.encode`` + ``TopKCompressor.compress`` per tensor, NCCL ``all_gather`` of the packed
+             tensors, and its own ``outer_step`` (rank 0 clips, batch-decompresses and inverse-transforms, broadcasts
+             the dense gradient, every rank applies SGD).  Slow: about a second per round.
 
 Reports ms, payload GB/s over NVLink, and the fraction of the roofline max(HBM bytes / measured copy
 bandwidth, NVLink bytes / 770 GB/s).
@@ -103,44 +103,35 @@ def main():
         rec = {"case": "config3_gather", "model": a.model, "world": world, "topk": k, "ours_ms": ms,
                "payload_bytes_per_peer": payload, "nvlink_gbs": link / ms / 1e6, "roofline_ms": roof,
                "frac_of_roofline": roof / ms, "kernel_status": eng.check_status(), "peaks": pk["source"]}
-        if a.reference:
-            rec["reference_ms"] = timed(lambda: _reference_step(eng, k, world, dev))
-            rec["speedup"] = rec["reference_ms"] / ms
-        if rank == 0:
-            print(json.dumps(rec))
         del eng, model
         torch.cuda.empty_cache()
+        if a.reference:
+            ref_step = _reference_step(a.model, k, world, rank, dev)
+            rec["reference_ms"] = timed(ref_step)
+            rec["reference"] = "unmodified reference install (tplr.compress + tplr.neurons.outer_step + NCCL all_gather)"
+            rec["speedup"] = rec["reference_ms"] / ms
+            del ref_step
+            torch.cuda.empty_cache()
+        if rank == 0:
+            print(json.dumps(rec))
     if heap is not None:
         heap.close()
     dist.destroy_process_group()
 
 
-def _reference_step(eng, k, world, dev):
-    """The reference's per-tensor algorithm with torch ops + NCCL all_gather on this rank's full tensors."""
-    from ..compress import ChunkingTransformer, TopKCompressor
+def _reference_step(model_name, k, world, rank, dev):
+    """One round of the UNMODIFIED reference (its ``ChunkingTransformer`` / ``TopKCompressor`` / ``outer_step`` with
+    NCCL ``all_gather`` of the payloads), built by ``baseline/reference_config3.py`` from the install under
+    ``baseline/_ref``; nothing of this package is on that path."""
+    import importlib
+    import sys
+    from pathlib import Path
 
-    if not hasattr(eng, "_ref_state"):
-        specs = eng.layout.specs
-        model = eng.model
-        tr = ChunkingTransformer(model, 64)
-        comp = TopKCompressor(use_quantization=False)
-        gen = torch.Generator(device=dev).manual_seed(7)
-        mom = {s.name: torch.randn(s.shape, device=dev, generator=gen) * 1e-3 for s in specs}
-        eng._ref_state = (tr, comp, mom)
-    tr, comp, mom = eng._ref_state
-    for name, m in mom.items():
-        enc = tr.encode(m, use_dct=True)
-        idx, val, xshape, totalk = comp.compress(enc, k)
-        if world > 1:
-            gi = [torch.empty_like(idx) for _ in range(world)]
-            gv = [torch.empty_like(val) for _ in range(world)]
-            dist.all_gather(gi, idx)
-            dist.all_gather(gv, val)
-        else:
-            gi, gv = [idx], [val]
-        dec = comp.batch_decompress(m, gi, gv, xshape, totalk)
-        g = tr.decode(dec, use_dct=True)
-        m.sub_(torch.sign(g) * 1e-3)
+    root = str(Path(__file__).resolve().parents[2])
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    step, _ = importlib.import_module("baseline.reference_config3").make_step(model_name, k, world, rank, dev)
+    return step
 
 
 if __name__ == "__main__":
