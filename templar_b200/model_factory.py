@@ -173,7 +173,13 @@ def create_meta_model(hparams: SimpleNamespace, role: Literal["miner", "validato
     with torch.device("meta"):
         model = LlamaModel(args)
     model.parallel_dims, model.job_config = pdims, job
-    model.activation_checkpointing = job.activation_checkpoint_mode in ("full", "selective") and args.n_layers > 32
+    # torchtitan.activation_checkpoint of the hparams: {"mode": "none" | "full" | "selective", "option": "op" | "<N>"}
+    # (reference src/tplr/model_factory.py:195-204)
+    mode = str(job.activation_checkpoint_mode or "none").lower()
+    if mode not in ("none", "full", "selective"):
+        raise ValueError(f"activation_checkpoint.mode must be none, full or selective, got {mode!r}")
+    model.activation_checkpointing = mode
+    model.ac_option = str(job.selective_ac_option)
     return model
 
 

@@ -161,7 +161,22 @@ class TransformerBlock(nn.Module):
 
     def forward_fused(self, res, delta, cos, sin):
         """Same block on a split residual stream: the hidden state is ``res + delta`` and the sum is
-        formed inside the norm kernels (``delta`` None: ``res`` alone).  Returns the next ``(res, delta)``."""
+        formed inside the norm kernels (``delta`` None: ``res`` alone).  Returns the next ``(res, delta)``.
+
+        With ``recompute_ops`` (per-op selective activation checkpointing) the normalised activations and the
+        SwiGLU output are not stored: each is recomputed in the backward pass for the weight gradient of the
+        GEMM that consumed it, while every GEMM and attention output is kept."""
+        att, ff = self.attention, self.feed_forward
+        if getattr(self, "recompute_ops", False) and att.packed is not None and ff.packed is not None:
+            nw, eps = self.attention_norm, self.attention_norm.eps
+            if delta is None:
+                qkv = OF.norm_linear(res, None, nw.weight, eps, att.packed[0], att.packed[1])
+            else:
+                res, qkv = OF.norm_linear(res, delta, nw.weight, eps, att.packed[0], att.packed[1])
+            qkv = OF.rope(qkv, cos, sin, att.n_heads + att.n_kv, att.hd)
+            a = att.wo(OF.attention_packed(qkv, att.n_heads, att.n_kv, att.hd))
+            res, h13 = OF.norm_linear(res, a, self.ffn_norm.weight, self.ffn_norm.eps, ff.packed[0], ff.packed[1])
+            return res, OF.swiglu_linear(h13, ff.w2.weight)
         if delta is None:
             y = self.attention_norm(res)
         else:
@@ -194,7 +209,11 @@ class LlamaModel(nn.Module):
             self.output.weight = self.tok_embeddings.weight
         self.register_buffer("freqs_cis", self._freqs_cis(), persistent=True)
         self._rope_cache: dict = {}
+        # False / True (every block recomputed), or the reference's modes (hparams torchtitan.activation_checkpoint):
+        # "none", "full", "selective" with ``ac_option`` = "op" (per-op policy: GEMM and attention outputs kept,
+        # norms and activations recomputed) or an integer N (every N-th block recomputed whole)
         self.activation_checkpointing = False
+        self.ac_option = "op"
 
     # -- rotary tables --------------------------------------------------------------------
     def _freqs_cis(self) -> torch.Tensor:
@@ -257,11 +276,16 @@ class LlamaModel(nn.Module):
             pg.begin_forward()
         h = OF.embedding(tokens, self.tok_embeddings.weight)
         delta = None
-        for key, layer in self.layers.items():
+        mode = self.activation_checkpointing
+        mode = {True: "full", False: "none", None: "none"}.get(mode, mode)
+        per_op = mode == "selective" and str(self.ac_option) == "op"
+        every = int(self.ac_option) if mode == "selective" and str(self.ac_option).isdigit() else (1 if mode == "full" else 0)
+        for count, (key, layer) in enumerate(self.layers.items(), start=1):
+            layer.recompute_ops = per_op and torch.is_grad_enabled()
             fn = layer.forward_fused
             if pg is not None:
                 fn = self._gated_block(pg, f"layers.{key}", layer)
-            if self.activation_checkpointing and torch.is_grad_enabled():
+            if every and count % every == 0 and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 h, delta = checkpoint(fn, h, delta, cos, sin, use_reentrant=False)
             else:

@@ -407,6 +407,140 @@ def swiglu(h):
 
 
 # --------------------------------------------------------------------------- #
+# Per-op selective activation checkpointing: the outputs of GEMMs and of attention are kept, the
+# cheap element-wise producers of a GEMM's input (SwiGLU, RMSNorm) are recomputed in the backward
+# pass instead of being stored.  The reference gets the same policy from torchtitan's selective
+# "op" mode, which saves matmul / attention results and recomputes the rest
+# (models/llama3/infra/parallelize.py:234-322, hparams torchtitan.activation_checkpoint).
+# --------------------------------------------------------------------------- #
+def _swiglu_raw(h: torch.Tensor) -> torch.Tensor:
+    with torch.no_grad():
+        return _SwiGLU.forward(_NoCtx(), h)
+
+
+def _weight_grad(main_grad, dy2, x2, w, needs_grad: bool):
+    """dW of ``y = x W^T`` routed like :class:`_Linear` does: into ``main_grad`` (fp32 buffer or gradient
+    scatter target) when there is one, else returned."""
+    if main_grad is not None and not torch.is_tensor(main_grad):
+        main_grad.accumulate(dy2, x2)
+        return None
+    if main_grad is not None:
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+        return None
+    return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype) if needs_grad else None
+
+
+class _NoCtx:
+    """Stand-in context for calling a Function's forward as a plain computation."""
+
+    needs_input_grad = (False,) * 8
+
+    def save_for_backward(self, *a):
+        self.saved = a
+
+    def mark_dirty(self, *a):
+        pass
+
+
+class _SwiGLULinear(torch.autograd.Function):
+    """``y = swiglu(h) W^T`` that stores ``h`` only: the activation ``swiglu(h)`` (a third of a block's stored
+    activations) is recomputed for the weight gradient."""
+
+    @staticmethod
+    def forward(ctx, h, w, main_grad):
+        ctx.save_for_backward(h, w)
+        ctx.main_grad = main_grad
+        s = _swiglu_raw(h)
+        y = torch.empty(*s.shape[:-1], w.shape[0], dtype=s.dtype, device=s.device)
+        gemm(s.reshape(-1, s.shape[-1]), w, out=y.view(-1, w.shape[0]))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        s = _swiglu_raw(h)
+        s2 = s.reshape(-1, s.shape[-1])
+        ds = gemm(dy2, w, b_mn=True).view_as(s)
+        dw = _weight_grad(ctx.main_grad, dy2, s2, w, ctx.needs_input_grad[1])
+        del s, s2
+        sw = _NoCtx()
+        sw.saved_tensors = (h,)
+        with torch.no_grad():
+            dh = _SwiGLU.backward(sw, ds)
+        return dh, dw, None
+
+
+def swiglu_linear(h, w, main_grad=None):
+    """``swiglu(h) @ w.T`` with the activation recomputed in the backward pass."""
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    return _SwiGLULinear.apply(h, w, main_grad)
+
+
+class _NormLinear(torch.autograd.Function):
+    """``(hsum, y)`` with ``hsum = res + delta`` (``delta`` may be None) and ``y = rmsnorm(hsum) W^T``; stores
+    ``hsum`` (needed by the residual stream anyway) and the row statistics, not the normalised activations."""
+
+    @staticmethod
+    def forward(ctx, res, delta, wn, eps, main_grad_n, w, main_grad_w):
+        nctx = _NoCtx()
+        with torch.no_grad():
+            if delta is None:
+                xn = _RMSNorm.forward(nctx, res, wn, eps, None)
+                hsum = res
+            else:
+                hsum, xn = _AddRMSNorm.forward(nctx, res, delta, wn, eps, None)
+        ctx.kind = "plain" if delta is None else "add"
+        ctx.native = nctx.native
+        ctx.eps, ctx.main_grad_n, ctx.main_grad_w = eps, main_grad_n, main_grad_w
+        ctx.save_for_backward(*nctx.saved, w)              # (x or h, wn, rstd, w)
+        y = torch.empty(*xn.shape[:-1], w.shape[0], dtype=xn.dtype, device=xn.device)
+        gemm(xn.reshape(-1, xn.shape[-1]), w, out=y.view(-1, w.shape[0]))
+        if delta is None:
+            return y
+        return hsum, y
+
+    @staticmethod
+    def backward(ctx, *grads):
+        x, wn, rstd, w = ctx.saved_tensors
+        dh, dy = (None, grads[0]) if ctx.kind == "plain" else grads
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        # the normalised activations again (one pass over x), for the weight gradient only
+        with torch.no_grad():
+            if ctx.native and x.is_contiguous() and x.shape[-1] <= 8192:
+                xn = torch.empty_like(x)
+                T = x.numel() // x.shape[-1]
+                native.check(native.lib().tplr_rmsnorm_fwd(x.data_ptr(), wn.data_ptr(), xn.data_ptr(), rstd.data_ptr(), T,
+                                                           x.shape[-1], ctx.eps, native.stream_ptr()), "rmsnorm_fwd")
+            else:
+                xn = (x.float() * rstd.reshape(*x.shape[:-1], 1) * wn.float()).to(x.dtype)
+        dw = _weight_grad(ctx.main_grad_w, dy2, xn.reshape(-1, xn.shape[-1]), w, ctx.needs_input_grad[5])
+        del xn
+        dxn = gemm(dy2, w, b_mn=True).view_as(x)
+        nctx = _NoCtx()
+        nctx.saved_tensors, nctx.main_grad, nctx.native, nctx.eps = (x, wn, rstd), ctx.main_grad_n, ctx.native, ctx.eps
+        with torch.no_grad():
+            if ctx.kind == "plain":
+                dx, dwn, _, _ = _RMSNorm.backward(nctx, dxn)
+                return dx, None, dwn, None, None, dw, None
+            dx, _, dwn, _, _ = _AddRMSNorm.backward(nctx, dh, dxn)
+        return dx, dx, dwn, None, None, dw, None
+
+
+def norm_linear(res, delta, wn, eps, w, main_grad_w=None):
+    """``rmsnorm(res + delta) @ w.T`` (and the sum, when ``delta`` is given) with the normalised activations
+    recomputed in the backward pass."""
+    if main_grad_w is None:
+        main_grad_w = getattr(w, "main_grad", None)
+    return _NormLinear.apply(res, delta, wn, eps, getattr(wn, "main_grad", None), w, main_grad_w)
+
+
+# --------------------------------------------------------------------------- #
 # Embedding
 # --------------------------------------------------------------------------- #
 class _Embedding(torch.autograd.Function):

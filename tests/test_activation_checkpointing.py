@@ -1,0 +1,73 @@
+"""Activation checkpointing modes (hparams ``torchtitan.activation_checkpoint``): none, full, selective with the per-op
+policy ("op": GEMM and attention outputs kept, norms and SwiGLU recomputed) or every N-th block."""
+
+import pytest
+import torch
+import torch.autograd.graph as ag
+
+from templar_b200.models.llama import ModelArgs, build_model
+from templar_b200.parallel.window_engine import EngineConfig, WindowEngine
+
+ARGS = ModelArgs(dim=128, n_layers=4, n_heads=2, n_kv_heads=1, vocab_size=256, intermediate_size=256, max_seq_len=32)
+TOK = torch.randint(0, 256, (3, 33), generator=torch.Generator().manual_seed(0))
+
+
+def _run(mode, option="op", shard=False, device="cpu", dtype=None):
+    m = build_model(ARGS, device=device, dtype=dtype, seed=3)
+    m.activation_checkpointing, m.ac_option = mode, option
+    eng = WindowEngine(m, EngineConfig(shard_params=shard), device=device)
+    stored = [0]
+
+    def pack(t):
+        stored[0] += t.numel() * t.element_size()
+        return t
+
+    tok = TOK.to(device)
+    with ag.saved_tensors_hooks(pack, lambda t: t):
+        loss = m.loss(tok[:, :-1], tok[:, 1:])
+    loss.backward()
+    grad = eng.store.stage.clone() if shard else eng.store.grad.clone()
+    return float(loss), grad, stored[0]
+
+
+def test_every_mode_gives_the_gradients_of_the_plain_pass_and_stores_less():
+    l0, g0, b0 = _run("none")
+    seen = {}
+    for mode, opt in (("selective", "op"), ("selective", "2"), ("full", "op"), (True, "op")):
+        l, g, b = _run(mode, opt)
+        assert l == l0 and torch.equal(g, g0), (mode, opt)
+        seen[(mode, opt)] = b
+    assert seen[("full", "op")] < seen[("selective", "2")] < seen[("selective", "op")] < b0
+    assert seen[(True, "op")] == seen[("full", "op")]
+
+
+def test_per_op_policy_with_sharded_parameters():
+    l0, g0, _ = _run("none", shard=True)
+    l, g, _ = _run("selective", "op", shard=True)
+    assert l == l0 and torch.equal(g, g0)
+
+
+def test_model_factory_reads_the_mode_from_the_hparams(tmp_path):
+    from types import SimpleNamespace
+
+    from templar_b200 import model_factory as mf
+
+    hp = SimpleNamespace(model_size="tiny", sequence_length=32,
+                         model_config=SimpleNamespace(vocab_size=256, hidden_size=128, num_hidden_layers=2, num_attention_heads=2,
+                                                      num_key_value_heads=2, intermediate_size=256, rms_norm_eps=1e-5,
+                                                      rope_theta=10000.0),
+                         torchtitan=SimpleNamespace(activation_checkpoint={"mode": "selective", "option": "op"}))
+    model = mf.initialize_torchtitan_model(hp, role="miner", device="cpu", world_size=1)
+    assert model.activation_checkpointing == "selective" and model.ac_option == "op"
+    hp.torchtitan.activation_checkpoint = {"mode": "sometimes", "option": "op"}
+    with pytest.raises(ValueError):
+        mf.initialize_torchtitan_model(hp, role="miner", device="cpu", world_size=1)
+
+
+@pytest.mark.gpu
+def test_per_op_policy_on_the_native_kernels():
+    """bf16 on CUDA: the recomputed norms / SwiGLU come from the same kernels as the stored ones would."""
+    l0, g0, b0 = _run("none", device="cuda", dtype=torch.bfloat16)
+    l, g, b = _run("selective", "op", device="cuda", dtype=torch.bfloat16)
+    assert abs(l - l0) < 1e-6 and b < b0
+    assert (g - g0).abs().max().item() <= 1e-6 * max(g0.abs().max().item(), 1.0)
