@@ -334,11 +334,7 @@ class Miner(BaseNode, Trainer):
     async def _publish_debug(self, window: int) -> None:
         """Two elements ([10:12]) of every parameter of the local view, used by validators to
         measure how far this miner is from the consensus weights."""
-        dbg = {}
-        for name, p in self.model.named_parameters():
-            flat = p.detach().flatten()
-            if flat.numel() >= 12:
-                dbg[name + "_debug"] = flat[10:12].float().cpu().tolist()
+        dbg = {name + "_debug": v.float().cpu().tolist() for name, v in tplr.neurons.param_samples(self.model, 10, 12).items()}
         dbg["successful_peers"] = sorted(set(self.comms.peers))
         await self.comms.put(state_dict=dbg, uid=str(self.uid), window=window, key="debug", local=False)
 

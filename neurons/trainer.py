@@ -129,11 +129,31 @@ class Trainer:
             quantize=bool(getattr(hp, "payload_quantization", False))
             and (self.world_size == 1 or heap is not None or torch.device(self.device).type == "cpu"),
             quant_bins=min(int(getattr(hp, "quantization_bins", 256)), 256),
-            quant_range=float(getattr(hp, "quantization_range", 6)))
+            quant_range=float(getattr(hp, "quantization_range", 6)),
+            # torchtitan.shard_params: bf16 weights and fp32 gradients held as shards too (what the reference's
+            # dp_shard does with FSDP2, src/tplr/model_factory.py:215-332), for models whose whole weights and
+            # gradients do not fit beside the activations; on CUDA with several ranks it needs the symmetric heap
+            shard_params=self._shard_params(heap),
+            gather_buffers=int((lambda tt: (tt.get("gather_buffers", 2) if isinstance(tt, dict)
+                                            else getattr(tt, "gather_buffers", 2)) or 2)(getattr(hp, "torchtitan", None))))
         kw.update(self._muon_engine_args(kind, spec))
         cfg = EngineConfig(**kw)
         self.engine = WindowEngine(self.model, cfg, device=self.device, rank=self.rank, world_size=self.world_size, heap=heap)
         return self.engine
+
+    def _shard_params(self, heap) -> bool:
+        tt = getattr(self.hparams, "torchtitan", None)
+        want = bool(tt.get("shard_params", False) if isinstance(tt, dict) else getattr(tt, "shard_params", False))
+        if not want:
+            return False
+        kind, _, _ = _opt_cfg(self.hparams)
+        if kind == "muon":
+            tplr.logger.warning("torchtitan.shard_params is ignored with the Muon inner optimizer (it needs whole gradient "
+                                "matrices on a rank); optimizer state stays sharded")
+            return False
+        if torch.device(self.device).type == "cuda" and self.world_size > 1 and heap is None:
+            raise ValueError("torchtitan.shard_params on several GPUs needs the symmetric heap")
+        return True
 
     def _muon_engine_args(self, kind: str, spec: dict) -> dict:
         """Engine settings for ``optimizer.type == "muon"``: the same groups, LR scales and decays that

@@ -890,10 +890,8 @@ class Validator(BaseNode, Trainer):
 
     def _track_param_change(self) -> None:
         a = self.param_change_alpha
-        for name, p in self.model.named_parameters():
-            if p.numel() < 12:
-                continue
-            cur = p.detach().flatten()[10:12].float().cpu()
+        for name, cur in tplr.neurons.param_samples(self.model, 10, 12).items():
+            cur = cur.float().cpu()
             if name in self.prev_param_state:
                 d = (cur - self.prev_param_state[name]).abs()
                 self.param_avg_change[name] = d.clone() if name not in self.param_avg_change else \
@@ -901,8 +899,7 @@ class Validator(BaseNode, Trainer):
             self.prev_param_state[name] = cur
 
     async def _publish_debug(self) -> None:
-        dbg = {name + "_debug": p.detach().flatten()[:2].float().cpu().tolist()
-               for name, p in self.model.named_parameters() if p.numel() >= 2}
+        dbg = {name + "_debug": v.float().cpu().tolist() for name, v in tplr.neurons.param_samples(self.model, 0, 2).items()}
         await self.comms.put(state_dict=dbg, uid=str(self.uid), window=self.sync_window, key="debug", local=False)
 
 

@@ -534,10 +534,8 @@ async def catchup_with_aggregation_server(instance, checkpoint_current_window: i
             if instance.is_master:
                 dbg = await instance.comms.get(uid=str(leader), window=start_w, key="debug", local=False, stale_retention=10)
                 if dbg.success and isinstance(dbg.data, dict):
-                    for name, p in instance.model.named_parameters():
-                        if p.numel() < 2:
-                            continue
-                        cur = (p.to_local() if _is_dtensor(p) else p).detach().cpu().flatten()[0:2]
+                    for name, cur in param_samples(instance.model, 0, 2).items():
+                        cur = cur.detach().cpu()
                         if name in prev_state:
                             delta = (cur - prev_state[name]).abs()
                             if name not in avg_change:
@@ -563,6 +561,21 @@ async def catchup_with_aggregation_server(instance, checkpoint_current_window: i
     logger.info("Catch-up finished – model now in sync.")
 
 
+def param_samples(model: nn.Module, lo: int, hi: int) -> dict[str, torch.Tensor]:
+    """``{name: flatten()[lo:hi]}`` of every parameter with at least ``hi`` elements: the slices that nodes publish
+    as debug information and compare for the sync score.  Read from the module tree, or, when the engine holds the
+    parameters as shards only, from the elements the ranks collected at the last window boundary."""
+    engine = getattr(model, "_window_engine", None)
+    if engine is not None and getattr(engine, "fsdp", False):
+        return engine.param_samples(lo, hi)
+    out = {}
+    for name, p in _named_parameters(model):
+        flat = (p.to_local() if _is_dtensor(p) else p).detach().flatten()
+        if flat.numel() >= hi:
+            out[name] = flat[lo:hi]
+    return out
+
+
 # --------------------------------------------------------------------------------------- #
 # sync metric
 # --------------------------------------------------------------------------------------- #
@@ -576,12 +589,19 @@ async def compare_model_with_debug_dict(model: nn.Module, debug_dict: dict, lear
     max_diff = max_steps = 0.0
     ratios = []
     lo, hi = index_range
+    engine = getattr(model, "_window_engine", None)
+    sharded = param_samples(model, lo, hi) if engine is not None and getattr(engine, "fsdp", False) else None
     for name, p in _named_parameters(model):
         ref = debug_dict.get(name + "_debug")
         if not isinstance(ref, list):
             continue
-        cur = (p.to_local() if _is_dtensor(p) else p).data.flatten()[lo:hi]
-        diff = cur - torch.tensor(ref, dtype=p.dtype, device=cur.device)
+        if sharded is not None:
+            if name not in sharded:
+                continue
+            cur = sharded[name]
+        else:
+            cur = (p.to_local() if _is_dtensor(p) else p).data.flatten()[lo:hi]
+        diff = cur - torch.tensor(ref, dtype=cur.dtype, device=cur.device)
         a = diff.abs()
         sq += float((diff.float() ** 2).sum())
         ab += float(a.sum())

@@ -141,6 +141,7 @@ class WindowEngine:
         if self.fsdp and self.cuda:
             rec = self.store.stage_blocks()
             self._grad_stage_table = (torch.tensor(rec, dtype=torch.int64, device=self.device).reshape(-1, 3), len(rec))
+        self._refresh_samples()
 
     # -- phase marks ------------------------------------------------------------------------------
     def start_trace(self) -> None:
@@ -436,6 +437,7 @@ class WindowEngine:
         st = self.store
         if self.fsdp:
             st.refresh_compute_from_master()
+            self._refresh_samples()
             return
         if st.compute is not st.master_shard:
             st.compute[st.lo:st.hi].copy_(st.master_shard.to(st.compute.dtype))
@@ -894,6 +896,7 @@ class WindowEngine:
             st.gather.invalidate()
             self._barrier()
             self._mark("outer.barrier")
+            self._refresh_samples()
         elif self.world_size > 1:
             self._barrier()
             self._mark("outer.barrier")
@@ -997,6 +1000,7 @@ class WindowEngine:
             else:
                 st.refresh_compute_from_master()
             self._barrier()
+            self._refresh_samples()
             return
         if self.cuda and st.compute is not st.master_shard:
             native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(),
@@ -1114,6 +1118,7 @@ class WindowEngine:
         if self.fsdp:
             st.gather.invalidate()
             self._barrier()
+            self._refresh_samples()
         for s in self.layout.specs:
             if s.name not in state or self.fsdp:
                 continue
@@ -1125,6 +1130,51 @@ class WindowEngine:
                 buf = dict(self.model.named_buffers()).get(k)
                 if buf is not None and torch.is_tensor(v):
                     buf.copy_(v.to(buf.device))
+
+    # -- a few elements of every tensor, for the nodes' debug / sync bookkeeping ------------------------ #
+    SAMPLE_RANGES = ((0, 2), (10, 12))
+
+    @torch.no_grad()
+    def _refresh_samples(self) -> None:
+        """With sharded parameters no rank can read a tensor's elements from the module tree (the parameters are
+        views of gather buffers).  The elements that the nodes publish and compare (``flatten()[0:2]`` and
+        ``[10:12]`` of every tensor, reference neurons/miner.py:822-832, neurons/validator.py:2589-2598) are
+        therefore collected from the owners' master shards whenever the weights change at a window boundary:
+        one small all-reduce, called by every rank, so that the master-only readers need no collective."""
+        if not self.fsdp:
+            return
+        L, st = self.layout, self.store
+        width = sum(b - a for a, b in self.SAMPLE_RANGES)
+        if getattr(self, "_sample_index", None) is None:          # (positions in the shard, positions in the table)
+            src, dst, col = [], [], 0
+            for lo, hi in self.SAMPLE_RANGES:
+                for sp, a, b, la in L.segments(self.rank):
+                    x, y = max(sp.offset + lo, a), min(sp.offset + min(hi, sp.numel), b)
+                    for e in range(x, y):
+                        src.append(la + (e - a))
+                        dst.append(sp.index * width + col + (e - sp.offset - lo))
+                col += hi - lo
+            self._sample_index = (torch.tensor(src, dtype=torch.long, device=self.device),
+                                  torch.tensor(dst, dtype=torch.long, device=self.device))
+        src, dst = self._sample_index
+        buf = torch.zeros(L.n_params * width, dtype=torch.float32, device=self.device)
+        buf[dst] = st.master_shard[src]
+        if self.world_size > 1:
+            dist.all_reduce(buf, group=self.group)
+        self._samples = buf.view(L.n_params, width).cpu()
+
+    def param_samples(self, lo: int, hi: int) -> dict[str, torch.Tensor]:
+        """``{name: flatten()[lo:hi]}`` of every tensor with at least ``hi`` elements (fp32, host), for one of
+        :attr:`SAMPLE_RANGES`."""
+        col = 0
+        for a, b in self.SAMPLE_RANGES:
+            if (a, b) == (lo, hi):
+                if getattr(self, "_samples", None) is None:
+                    raise RuntimeError("parameter samples are collected by every rank at window boundaries; none yet")
+                return {sp.name: self._samples[sp.index, col: col + (b - a)].clone() for sp in self.layout.specs
+                        if sp.numel >= hi}
+            col += b - a
+        raise KeyError(f"elements [{lo}:{hi}] are not among the cached sample ranges {self.SAMPLE_RANGES}")
 
     def check_status(self) -> int:
         """Reads (and clears) the kernel status word — a host sync; call between windows."""

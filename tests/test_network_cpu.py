@@ -107,6 +107,54 @@ def test_two_miners_and_a_validator_stay_in_sync(cwd_tmp):
     run(go())
 
 
+def test_nodes_with_sharded_parameters_follow_the_same_protocol(cwd_tmp, monkeypatch):
+    """``torchtitan.shard_params`` in the hparams: miners and the validator hold weights and gradients as shards (one
+    rank each here, so the whole machinery runs in-process); they publish debug slices, score and stay in sync as the
+    nodes with whole weights do."""
+    real = tplr.load_hparams
+
+    def sharded(*a, **k):
+        hp = real(*a, **k)
+        hp.torchtitan.shard_params = True
+        return hp
+    monkeypatch.setattr(tplr, "load_hparams", sharded)
+
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        miners = [_node(Miner, Miner.miner_config, ["--uid", str(u), "--peers", "2", "3"], store, chain) for u in (2, 3)]
+        for n in miners + [v]:
+            assert n.engine.fsdp and n.engine.store.compute is None
+            n.loop = asyncio.get_running_loop()
+            n.comms.commitments = await n.comms.get_commitments()
+            n.comms.peers = [2, 3]
+            n.gather_timeout = 5
+            await n.dataset_manager.initialize_datasets(0)
+        for m in miners:
+            m.set_dataloader()
+        v.set_dataloader(validator=True)
+        for w in range(1, 3):
+            for m in miners:
+                m.current_window = m.comms.current_window = w
+            res = await asyncio.gather(*(m.run_window(w) for m in miners))
+            assert all(r["gather_success_rate"] == 1.0 and r["global_step"] == w for r in res)
+            v.current_window, v.comms.current_window, v.sync_window = w + 1, w, w
+            out = await v.run_window()
+            assert sorted(out["gathered"]) == [2, 3] and len(out["scored"]) == 2 and out["global_step"] == w
+        full = [n.engine.full_state_dict() for n in miners + [v]]
+        for k, t in full[0].items():
+            if t.is_floating_point():
+                assert torch.allclose(t, full[1][k], atol=1e-6) and torch.allclose(t, full[2][k], atol=1e-5), k
+        # the published debug slices are the master weights' elements, not whatever a gather buffer holds
+        dbg = await v.comms.get(uid="2", window=2, key="debug", local=False)
+        name = "layers.0.attention.wq.weight"
+        assert dbg.data[name + "_debug"] == pytest.approx(full[0][name].flatten()[10:12].tolist(), abs=1e-7)
+        v.sync_window = 3                          # the sync check reads the debug slices of sync_window - 1
+        sync = await v.evaluate_miner_sync(2)
+        assert sync["success"] and sync["sync_score"] > 0.9, sync
+    run(go())
+
+
 def test_miner_survives_missing_and_corrupt_peers(cwd_tmp):
     async def go():
         store, chain = MemoryStore(), StaticChain(n=4, manual=True)
