@@ -46,8 +46,9 @@ def parse():
                     help="hold bf16 weights and fp32 gradients as shards too (the FSDP role): weights gathered per block "
                          "over NVLink ahead of their use, weight gradients reduce-added into the owners' shards by the "
                          "GEMM epilogue; the model is initialised tensor by tensor and never exists whole on a GPU")
-    ap.add_argument("--gather-buffers", type=int, default=2,
-                    help="with --shard-params: block buffers in rotation (>= the number of blocks keeps all gathered)")
+    ap.add_argument("--gather-buffers", type=int, default=0,
+                    help="with --shard-params: block buffers in rotation (>= the number of blocks keeps all gathered; "
+                         "0 = all blocks when the bf16 weights are at most 8 GiB, else 2)")
     ap.add_argument("--checkpoint-blocks", action="store_true", help="recompute every block in the backward pass")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
@@ -284,7 +285,7 @@ def run_ours(a):
                "h2d_bytes_per_step": int(io[0]), "d2h_bytes_per_step": int(io[1])}
     status = eng.check_status()
     sharding_label = ("bf16 weights, fp32 gradients and all optimizer state sharded; weights gathered per block, "
-                      f"{a.gather_buffers} block buffers" if a.shard_params else
+                      f"{eng.store.gather.n_buffers} block buffers" if a.shard_params else
                       "single GPU" if world == 1 else
                       "optimizer state, master weights, snapshot and error feedback sharded; bf16 weights and fp32 "
                       "gradients whole on every rank")

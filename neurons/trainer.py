@@ -134,8 +134,8 @@ class Trainer:
             # dp_shard does with FSDP2, src/tplr/model_factory.py:215-332), for models whose whole weights and
             # gradients do not fit beside the activations; on CUDA with several ranks it needs the symmetric heap
             shard_params=self._shard_params(heap),
-            gather_buffers=int((lambda tt: (tt.get("gather_buffers", 2) if isinstance(tt, dict)
-                                            else getattr(tt, "gather_buffers", 2)) or 2)(getattr(hp, "torchtitan", None))))
+            gather_buffers=int((lambda tt: (tt.get("gather_buffers", 0) if isinstance(tt, dict)
+                                            else getattr(tt, "gather_buffers", 0)) or 0)(getattr(hp, "torchtitan", None))))
         kw.update(self._muon_engine_args(kind, spec))
         cfg = EngineConfig(**kw)
         self.engine = WindowEngine(self.model, cfg, device=self.device, rank=self.rank, world_size=self.world_size, heap=heap)

@@ -69,6 +69,12 @@ class ParamGather:
         self.range = {g: (L.units[u[0]].g_lo, L.units[u[-1]].g_hi) for g, u in L.groups.items()}
         size = lambda g: self.range[g][1] - self.range[g][0]
         n_layers = len(self.layer_names)
+        if n_buffers <= 0:
+            # automatic: keep every block gathered between optimizer steps when the whole model's weights are a small
+            # part of the device memory (nothing is re-gathered in the backward pass or in later micro-batches), else
+            # rotate two buffers
+            whole = sum(size(g) for g in self.layer_names) * compute_shard.element_size()
+            n_buffers = n_layers if whole <= 8 * 2 ** 30 else 2
         self.n_buffers = max(min(n_buffers, n_layers), min(2, n_layers))
         layer_elems = max((size(g) for g in self.layer_names), default=0)
         z = lambda n: torch.zeros(max(n, 1), dtype=self.dtype, device=self.device)

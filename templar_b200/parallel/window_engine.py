@@ -57,7 +57,8 @@ class EngineConfig:
     quant_bins: int = 256
     quant_range: float = 6.0
     shard_params: bool = False         # weights and gradients held as shards too (the FSDP role), gathered per block
-    gather_buffers: int = 2            # block buffers in rotation; >= the number of blocks keeps every block gathered
+    gather_buffers: int = 0            # block buffers in rotation; >= the number of blocks keeps every block gathered;
+                                       # 0: all blocks when the weights are at most 8 GiB, else two
 
 
 def peer_slice(state_dict: dict, j: int) -> dict:
