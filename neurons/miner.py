@@ -60,6 +60,9 @@ def common_args(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--uid", type=int, default=None, help="uid on the static chain")
     parser.add_argument("--wallet-hotkey", type=str, default=None)
     parser.add_argument("--max-windows", type=int, default=0, help="stop after this many windows (0 = run forever)")
+    parser.add_argument("--colocated", action="store_true",
+                        help="the ranks of this launch are independent nodes (uid = --uid + rank) that share one box: "
+                             "they read each other's gradients from GPU peer memory instead of the object store")
 
 
 def finish_config(ns: argparse.Namespace) -> SimpleNamespace:
@@ -105,6 +108,12 @@ class Miner(BaseNode, Trainer):
         self.config = config or Miner.miner_config()
         dist_helper.init_process_group(backend="nccl" if str(self.config.device).startswith("cuda") else "gloo",
                                        timeout_minutes=45)
+        # --colocated: every rank of the launch is a whole miner of its own; the group only carries peer memory
+        self.group_rank, self.group_world = 0, 1
+        if getattr(self.config, "colocated", False) and dist_helper.world_size > 1:
+            self.group_rank, self.group_world = dist_helper.solo()
+            if self.config.uid is not None:
+                self.config.uid = int(self.config.uid) + self.group_rank
         self.rank, self.world_size = dist_helper.rank, dist_helper.world_size
         self.local_rank, self.is_master = dist_helper.local_rank, dist_helper.is_master
         self.device = torch.device(self.config.device if not str(self.config.device).startswith("cuda")
@@ -135,7 +144,22 @@ class Miner(BaseNode, Trainer):
             from templar_b200.parallel.symmetric import SymmetricHeap
 
             heap = SymmetricHeap.create(self.device, self.rank, self.world_size)
+        elif self.group_world > 1 and self.device.type == "cuda":
+            from templar_b200.parallel.symmetric import SymmetricHeap
+
+            # co-located nodes wait for each other once per window: the bound is a window, not a kernel
+            heap = SymmetricHeap.create(self.device, self.group_rank, self.group_world, timeout_s=1800.0)
         self.attach_engine(heap=heap)
+        self.peer_group = None
+        if self.group_world > 1:
+            from templar_b200.backends.store import PeerMemoryStore
+            from templar_b200.comms import default_store
+            from templar_b200.parallel.peer_group import LocalPeerGroup
+
+            self.peer_group = LocalPeerGroup(self.uid, rank=self.group_rank, world_size=self.group_world, heap=heap,
+                                             device=self.device)
+            self.peer_group.attach(self.engine)
+            store = PeerMemoryStore(store or default_store(), self.peer_group)
         self.transformer = tplr.compress.ChunkingTransformer(self.model, target_chunk=self.hparams.target_chunk)
         self.compressor = tplr.compress.TopKCompressor(use_quantization=False)
         self.init_optimizers_schedulers()
@@ -240,6 +264,8 @@ class Miner(BaseNode, Trainer):
         t0 = tplr.T()
         gradient, _, _ = tplr.prepare_gradient_dict(self, step_window, null_round)
         compress_time = tplr.T() - t0
+        if self.peer_group is not None:
+            self.peer_group.publish(step_window)      # the payload in this rank's buffers is this window's
         put_time = 0.0
         # The gradient of a window is uploaded once the window is over: validators and peers accept an upload only
         # between the first block of the next window and `time_window_delta_seconds` after it, so a miner that
@@ -267,6 +293,8 @@ class Miner(BaseNode, Trainer):
         if self.config.test:
             self.comms.peers = [u for u in range(len(self.comms.metagraph.S)) if u != self.uid]
         gather_result, gather_time = None, 0.0
+        if self.peer_group is not None:
+            self.peer_group.exchange()                # every co-located node's payload of this window is in place
         if self.is_master and self.comms.peers:
             t0 = tplr.T()
             gather_result = await self.comms.gather_with_reserve(

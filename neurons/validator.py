@@ -733,7 +733,7 @@ class Validator(BaseNode, Trainer):
         """Put the gathered payloads into the engine's device slots (all ranks); returns the peer count."""
         eng = self.engine
         sd = vars(gather_result.state_dict) if (self.is_master and gather_result is not None) else None
-        n = len(gather_result.uids) if sd is not None else 0
+        n = (len(gather_result.uids) - len(getattr(gather_result, "local_ranks", None) or {})) if sd is not None else 0
         n = min(n, eng.cfg.max_peers - 1)          # the last slot is kept for the uid under evaluation
         t = torch.tensor([n], dtype=torch.int32, device=self.device)
         dist_helper.broadcast(t, src=0)

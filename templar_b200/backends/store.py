@@ -1,7 +1,7 @@
 """Object-store backends behind :class:`templar_b200.comms.Comms`.
 
 ``ObjectStore`` is the small async interface Comms needs (put/get/head/list/delete by
-``(bucket, key)``).  Three implementations:
+``(bucket, key)``).  Implementations:
 
 * :class:`LocalFSStore` — a directory per bucket; what offline runs, tests and single-box
   deployments use.  ``last_modified`` is the file mtime, so the upload-time window checks work.
@@ -12,6 +12,8 @@
   upload id, parallel ranged download with resume for very large objects.  Mirrors the transport
   behaviour of the reference (src/tplr/comms.py:140-203, :634-891, :936-1187) behind the same
   interface; the client factory is injectable so the logic is testable with a fake client.
+* :class:`PeerMemoryStore` — wraps one of the above for nodes that share a box: gradients of co-located uids are
+  not fetched at all but read by the aggregation kernel from the owner's GPU memory.
 """
 
 from __future__ import annotations
@@ -172,6 +174,53 @@ class MemoryStore(ObjectStore):
     async def delete(self, bucket, keys):
         for k in keys:
             self.objects.pop((bucket.name, k), None)
+
+
+# --------------------------------------------------------------------------------------- #
+class PeerMemoryStore(ObjectStore):
+    """The transport of nodes that share a box: gradients of co-located uids are read from peer memory, everything
+    else goes through ``inner`` (a directory, S3 / R2, ...).
+
+    Uploads are passed on unchanged, since peers and validators on other machines read them from the bucket.  What
+    changes is the read side: :meth:`local_rank` tells :meth:`templar_b200.comms.Comms.gather` that a uid's payload of
+    the current window sits in the symmetric heap of the rank it runs on, so the gather neither downloads nor
+    deserialises it and the aggregation kernel pulls the packed payload over NVLink from the owner's buffers
+    (see parallel/peer_group.py).  ``head`` answers for such gradients too, so liveness checks of co-located peers
+    do not touch the bucket."""
+
+    def __init__(self, inner: ObjectStore, peer_group):
+        self.inner, self.peer_group = inner, peer_group
+
+    def local_rank(self, uid: int, window: int) -> int | None:
+        """Rank whose buffers hold ``uid``'s payload of ``window``, or None when that uid is not on this box (or has
+        not posted this window)."""
+        return self.peer_group.fresh(window).get(int(uid))
+
+    def _local_gradient(self, key: str) -> bool:
+        parts = key.split("-")
+        if len(parts) < 3 or parts[0] != "gradient":
+            return False
+        try:
+            window, uid = int(parts[1]), int(parts[2])
+        except ValueError:
+            return False
+        return self.local_rank(uid, window) is not None
+
+    async def put_file(self, bucket, key, path): return await self.inner.put_file(bucket, key, path)
+    async def put_bytes(self, bucket, key, data): return await self.inner.put_bytes(bucket, key, data)
+    async def get_bytes(self, bucket, key): return await self.inner.get_bytes(bucket, key)
+    async def get_to_file(self, bucket, key, path): return await self.inner.get_to_file(bucket, key, path)
+    async def list(self, bucket, prefix=""): return await self.inner.list(bucket, prefix)
+    async def delete(self, bucket, keys): return await self.inner.delete(bucket, keys)
+    async def close(self): return await self.inner.close()
+
+    async def head(self, bucket, key):
+        if self._local_gradient(key):
+            return ObjectInfo(key, 0, datetime.now(timezone.utc))
+        return await self.inner.head(bucket, key)
+
+    def __getattr__(self, name):              # transport-specific extras (multipart plans, fault tables, ...)
+        return getattr(self.inner, name)
 
 
 # --------------------------------------------------------------------------------------- #

@@ -394,6 +394,17 @@ class Comms(ChainManager):
         agg: dict[str, list] = {}
         valid, skipped, steps = [], [], []
         nbytes = 0
+        # uids that run on this box and have posted this window's payload in peer memory are not fetched: the engine
+        # reads them where they are (backends/store.py PeerMemoryStore)
+        local_ranks: dict[int, int] = {}
+        locate = getattr(self.store, "local_rank", None)
+        if locate is not None and not local:
+            for u in uids:
+                r = locate(u, window)
+                if r is not None:
+                    local_ranks[int(u)] = int(r)
+            uids = [u for u in uids if int(u) not in local_ranks]
+        n_asked = len(uids) + len(local_ranks)
         async with self.gather_semaphore:
             tasks = [self.get_with_retry(uid=str(u), window=window, key=key, timeout=timeout, local=local,
                                          stale_retention=stale_retention, time_min=time_min, time_max=time_max,
@@ -429,13 +440,17 @@ class Comms(ChainManager):
                             nbytes += tensor.element_size() * tensor.nelement()
                 valid.append(uid)
                 steps.append(resp.global_step)
-        if not valid:
+        if not valid and not local_ranks:
             logger.info("No valid gradients received from any UID")
             return None
         dt = time.time() - t_start
-        logger.info(f"Gather done in {dt:.2f}s. Success rate: {len(valid)}/{len(uids)}, Download: {nbytes} bytes")
-        return SimpleNamespace(time=dt, upload_bytes=0, download_bytes=nbytes, success_rate=len(valid) / len(uids),
-                               state_dict=SimpleNamespace(**agg), uids=valid, global_steps=steps, skipped_uids=skipped)
+        n_ok = len(valid) + len(local_ranks)
+        logger.info(f"Gather done in {dt:.2f}s. Success rate: {n_ok}/{n_asked}, Download: {nbytes} bytes"
+                    + (f", {len(local_ranks)} from peer memory" if local_ranks else ""))
+        # fetched peers come first (their list entries fill the engine's slots in this order), then the co-located ones
+        return SimpleNamespace(time=dt, upload_bytes=0, download_bytes=nbytes, success_rate=n_ok / max(n_asked, 1),
+                               state_dict=SimpleNamespace(**agg), uids=valid + sorted(local_ranks), global_steps=steps,
+                               skipped_uids=skipped, local_ranks=local_ranks)
 
     async def gather_with_reserve(self, *, my_uid: int | None, gather_uids: list[int], reserve_uids: list[int],
                                   expected_compressed_params: set[str] | None = None, **kwargs) -> SimpleNamespace | None:
@@ -460,7 +475,12 @@ class Comms(ChainManager):
                 if fb:
                     for k, v in vars(fb.state_dict).items():
                         setattr(primary.state_dict, k, getattr(primary.state_dict, k, []) + v)
-                    primary.uids.extend(fb.uids)
+                    n_fetched = len(primary.uids) - len(getattr(primary, "local_ranks", {}) or {})
+                    fb_local = getattr(fb, "local_ranks", {}) or {}
+                    fb_fetched = [u for u in fb.uids if u not in fb_local]
+                    primary.uids[n_fetched:n_fetched] = fb_fetched          # fetched peers stay in front, in list order
+                    primary.uids.extend(sorted(fb_local))
+                    primary.local_ranks = {**(getattr(primary, "local_ranks", {}) or {}), **fb_local}
                     primary.global_steps.extend(fb.global_steps)
                     primary.skipped_uids.extend(fb.skipped_uids)
                     primary.upload_bytes += fb.upload_bytes

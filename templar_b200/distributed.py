@@ -56,8 +56,16 @@ class DistributedHelper:
         logger.info(f"[Distributed] rank={self.rank}/{self.world_size} local_rank={self.local_rank} "
                     f"backend={backend} device={self.device}")
 
+    def solo(self) -> tuple[int, int]:
+        """Co-located nodes: the ranks of the process group are independent nodes (one uid each) that only share peer
+        memory.  From here on this helper answers as a single-rank node (no collective of a node's own protocol runs
+        across the group); returns ``(group_rank, group_world_size)`` for the code that does use the group."""
+        self.group_rank, self.group_world_size = self.rank, self.world_size
+        self.rank, self.world_size, self.is_master = 0, 1, True
+        return self.group_rank, self.group_world_size
+
     def destroy_process_group(self) -> None:
-        if self.world_size > 1 and dist.is_initialized():
+        if (self.world_size > 1 or getattr(self, "group_world_size", 1) > 1) and dist.is_initialized():
             dist.destroy_process_group()
 
     def is_distributed(self) -> bool:

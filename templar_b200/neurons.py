@@ -299,11 +299,13 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
         first = next((v for k, v in sd.items() if k.endswith("vals")), None)
         n_peers = len(first) if isinstance(first, (list, tuple)) else (1 if first is not None else 0)
     n_peers = min(n_peers, engine.cfg.max_peers)
+    # co-located peers (gather_result.local_ranks): read from the owners' GPU memory, nothing to stage
+    local = sorted((getattr(gather_result, "local_ranks", None) or {}).values()) if gather_result is not None else []
     if engine.world_size > 1:
         t = torch.tensor([n_peers], device=engine.device, dtype=torch.int32)
         dist.broadcast(t, 0)
         n_peers = int(t.item())
-    if n_peers == 0:
+    if n_peers == 0 and not local:
         return None
     if engine.world_size == 1:
         for j in range(n_peers):
@@ -314,7 +316,11 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
     if not engine.window_open:
         engine.snapshot()           # catch-up / validator flow: apply to the current weights
     with phase("Outer Step"):
-        engine.outer_step(n_peers, lr=lr, include_own=False, base="theta0")
+        if local:
+            engine.outer_step(peers=list(range(n_peers)) + [("rank", r) for r in local], lr=lr, include_own=False,
+                              base="theta0")
+        else:
+            engine.outer_step(n_peers, lr=lr, include_own=False, base="theta0")
     engine.window_open = False
     # fingerprint: the applied update is (theta0 - theta) / lr on every shard
     d = engine.theta0 - engine.store.master_shard

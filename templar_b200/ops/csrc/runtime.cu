@@ -232,3 +232,16 @@ TPLR_API int tplr_reduce_blocks(void* const* bufs, int n_ranks, const void* tabl
   reduce_blocks_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
+
+// One 64-bit store into (possibly peer) memory, stream ordered: the "this window's payload is in place" post of
+// co-located nodes.  System-scope release so that the payload written before it is visible to whoever reads the cell.
+__global__ void store_i64_kernel(long long* dst, long long value) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(value) : "memory");
+}
+TPLR_API int tplr_store_i64(void* dst, long long value, void* stream) {
+  TPLR_ENTER();
+  if (!dst || ((uintptr_t)dst & 7)) return (int)cudaErrorInvalidValue;
+  store_i64_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((long long*)dst, value);
+  return (int)cudaGetLastError();
+}

@@ -88,6 +88,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_gemm2_scatter": [vp, vp, i, i, i, ll, ll, i, i, i, i, i, vp, ll, i, vp, vp],
         "tplr_gemm2_scatter_v": [vp, vp, i, i, i, ll, ll, i, i, i, i, ctypes.POINTER(c_int), vp, vp, vp],
         "tplr_copy_blocks": [vp, i, i, vp],
+        "tplr_store_i64": [vp, ll, vp],
         "tplr_reduce_blocks": [vp, i, vp, i, vp, vp],
         "tplr_heap_alloc": [ctypes.c_ulonglong, ctypes.POINTER(c_void_p)],
         "tplr_heap_free": [vp],

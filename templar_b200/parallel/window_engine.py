@@ -137,6 +137,8 @@ class WindowEngine:
         self.gnorm_sq = z(1)
         self._sumsq_scratch = z(native.lib().tplr_sumsq_blocks() if self.cuda else 1)
         self.window_open = False
+        self.peer_group = None                    # set by LocalPeerGroup.attach(): co-located nodes on the same heap
+        self.rank_payloads: dict = {}             # CPU stand-in for peer memory: rank -> (own_idx, own_val) copies
         model._window_engine = self
         model._param_gather = self.store.gather          # None unless shard_params: the model gates its blocks on it
         if self.fsdp and self.cuda:
@@ -786,11 +788,30 @@ class WindowEngine:
             ids[0] = -1
         return ids
 
+    def _payload_buffers(self, j):
+        """Host-addressable (index, value) buffers of peer ``j`` (CPU paths)."""
+        if isinstance(j, tuple):
+            return self.rank_payloads[int(j[1])]
+        if j < 0:
+            return self.own_idx, self.own_val
+        return self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]]
+
     def _peer_ptrs(self, ids: list[int]):
-        """Pointers of the payloads: -1 = this node's own payload (held by rank 0), the others live
-        round-robin in the ranks' slots (peer j on rank j % world, slot j // world)."""
+        """Pointers of the payloads: -1 = this node's own payload (held by rank 0), ``("rank", r)`` = the own payload
+        of the co-located node that runs as rank r (see parallel/peer_group.py), the others live round-robin in
+        the ranks' slots (peer j on rank j % world, slot j // world)."""
         idx_ptrs, val_ptrs = [], []
         for j in ids:
+            if isinstance(j, tuple):                 # ("rank", r): the own payload of the node that runs as rank r
+                r = int(j[1])
+                if self.heap is None or self.cuda is False:
+                    ib, vb = self.rank_payloads[r]
+                    idx_ptrs.append(ib.data_ptr())
+                    val_ptrs.append(vb.data_ptr())
+                else:
+                    idx_ptrs.append(self.heap.peer_ptr(self.own_idx, r))
+                    val_ptrs.append(self.heap.peer_ptr(self.own_val, r))
+                continue
             if j < 0:
                 owner = 0
                 ib, vb = self.own_idx, self.own_val
@@ -814,7 +835,7 @@ class WindowEngine:
         if not self.cuda:
             norms = torch.zeros(len(ids), np_)
             for a, j in enumerate(ids):
-                ib, vb = (self.own_idx, self.own_val) if j < 0 else (self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]])
+                ib, vb = self._payload_buffers(j)
                 for s in self.layout.specs:
                     norms[a, s.index] = self.layout.payload_views(ib, vb, s.name)[1].float().norm()
             med = norms.median(dim=0).values
@@ -920,12 +941,7 @@ class WindowEngine:
         cfg, st, L = self.cfg, self.store, self.layout
         tr = C.ChunkingTransformer(None, cfg.target_chunk)
         comp = C.TopKCompressor(use_quantization=False)
-        bufs = []
-        for j in ids:
-            if j < 0:
-                bufs.append((self.own_idx, self.own_val))
-            else:
-                bufs.append((self.peer_idx[self.slot_of(j)[1]], self.peer_val[self.slot_of(j)[1]]))
+        bufs = [self._payload_buffers(j) for j in ids]
         base_buf = self.theta0 if base == "theta0" else st.master_shard
         clip = self.clip[: len(ids) * L.n_params].view(len(ids), L.n_params)
         mine: dict[str, list] = {}

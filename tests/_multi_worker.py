@@ -165,6 +165,41 @@ def main():
         with torch.no_grad():
             out[tag + "_loss_diff"] = abs(float(fmodel.loss(t[:, :-1], t[:, 1:])) - float(fref.model.loss(t[:, :-1], t[:, 1:])))
 
+    # 7. co-located nodes: every rank is a whole node of its own (engine world_size 1, buffers on the shared heap);
+    #    after compress + post + barrier each node aggregates all nodes' payloads by reading them from the owners'
+    #    memory over NVLink.  Checked against one engine that has the same payloads staged in its slots.
+    from templar_b200.parallel.peer_group import LocalPeerGroup
+
+    ccfg = dataclasses.replace(cfg, max_peers=world)
+    node = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), ccfg, device=dev, heap=heap)
+    pg = LocalPeerGroup(100 + rank, rank=rank, world_size=world, heap=heap, device=dev)
+    pg.attach(node)
+    node.snapshot()
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    node.store.master_shard.add_(torch.randn(node.store.master_shard.shape, device=dev, generator=gen) * 1e-3)
+    node.compress()
+    pg.publish(42)
+    pg.exchange()
+    out["c_fresh"] = pg.fresh(42) == {100 + r: r for r in range(world)} and pg.fresh(41) == {}
+    own_idx, own_val = node.own_idx.clone(), node.own_val.clone()
+    node.outer_step(peers=[("rank", r) for r in range(world)], include_own=False)
+    torch.cuda.synchronize()
+    out["c_status"] = node.check_status()
+    # the same aggregation from slots: payloads moved with NCCL
+    idxs = [torch.empty_like(own_idx) for _ in range(world)]
+    vals = [torch.empty_like(own_val) for _ in range(world)]
+    dist.all_gather(idxs, own_idx)
+    dist.all_gather(vals, own_val)
+    cref = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), ccfg, device=dev)
+    cref.snapshot()
+    for r in range(world):
+        cref.load_peer_payload(r, (idxs[r], vals[r]))
+    cref.outer_step(world, include_own=False)
+    torch.cuda.synchronize()
+    out["c_master_max_diff"] = (node.store.master_shard - cref.store.master_shard).abs().max().item()
+    out["c_moved"] = (cref.store.master_shard - cref.theta0).abs().max().item()
+    pg.barrier()                 # nobody's buffers are reused while a peer may still read them
+
     heap.barrier()
     torch.cuda.synchronize()
     heap.check_guards()           # no store of any rank ran past the end of a symmetric block of this rank

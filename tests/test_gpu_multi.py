@@ -54,6 +54,9 @@ def test_two_rank_runtime_and_window():
             assert r[tag + "_ef_max_diff"] < 0.05 * r[tag + "_ef_scale"], (tag, r)
             assert r[tag + "_loss_diff"] < 2e-2, (tag, r)
         assert r["fk_gathers"] <= r["f_gathers"], r       # enough buffers for every block: never more gathers
+        # co-located nodes: payloads read from the owners' memory == the same payloads staged in slots
+        assert r["c_fresh"] and r["c_status"] == 0 and r["c_moved"] > 1e-5, r
+        assert r["c_master_max_diff"] == 0.0, r
         if "q_val_max_diff" in r:
             assert r["q_val_max_diff"] < 0.05 * r["q_val_scale"], r
             assert r["q_codes_equal"] > 0.9, r
