@@ -647,6 +647,11 @@ class Validator(BaseNode, Trainer):
         scored = []
         if not bool(skip.item()):
             n_peers = self._stage_gather(gather_result)
+            # every rank of a sharded engine counts the index overlap over its own chunks (a collective); the master
+            # then judges the pairs
+            self.overlap_matrix = None
+            if self.engine.cuda and self.engine.world_size > 1 and n_peers >= 2:
+                self.overlap_matrix = self.engine.index_overlap(n_peers)
             if self.is_master:
                 asyncio.create_task(self.upload_gather_results(gather_result))
                 overlap = await tplr.neurons.check_uid_index_overlap(self, gather_result, self.sync_window,

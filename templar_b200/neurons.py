@@ -658,10 +658,15 @@ async def check_uid_index_overlap(neuron, gather_result, window: int, *, overlap
     device = neuron.config.device
     eng = getattr(neuron, "engine", None)
     staged = getattr(neuron, "staged_peers", None)
-    if eng is not None and eng.cuda and eng.world_size == 1 and staged == n:
+    m = getattr(neuron, "overlap_matrix", None)          # a sharded engine's ranks computed it together beforehand
+    if m is not None and tuple(m.shape) != (n, n):
+        m = None
+    if m is None and eng is not None and eng.cuda and eng.world_size == 1 and staged == n:
         # the gathered payloads already sit in the engine's peer slots (slot j = uids[j]): one kernel over the
         # packed indices gives every pair's overlap
-        m = eng.index_overlap(n).cpu()
+        m = eng.index_overlap(n)
+    if m is not None:
+        m = m.cpu()
         for i in range(n):
             for j in range(i + 1, n):
                 acc[(i, j)] = [float(m[i, j]), 1.0]

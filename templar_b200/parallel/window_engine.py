@@ -975,17 +975,30 @@ class WindowEngine:
     @torch.no_grad()
     def index_overlap(self, n_peers: int) -> torch.Tensor:
         """[n_peers, n_peers] matrix whose (i, j), i < j, entry is the fraction of (chunk, index) selections that
-        the staged peers i and j share over the whole payload (one kernel over the packed indices; CUDA,
-        unsharded engine).  Equals the size-weighted mean over tensors of the per-chunk overlap fraction."""
-        native.require(self.cuda and self.world_size == 1, "index_overlap needs the CUDA engine with all payloads local")
+        the staged peers i and j share over the whole payload (one kernel over the packed indices; CUDA).
+        Equals the size-weighted mean over tensors of the per-chunk overlap fraction.
+
+        A sharded engine counts over the chunks of its own shard, reading the packed indices from the slots of the
+        ranks that hold them, and the counts are summed over the ranks: a collective, so every rank calls it."""
+        native.require(self.cuda, "index_overlap needs the CUDA engine")
         ids = list(range(n_peers))
         idx_ptrs, _ = self._peer_ptrs(ids)
         counts = torch.zeros(n_peers * n_peers, dtype=torch.int64, device=self.device)
-        desc_full, n_full = self._desc_full
-        total_chunks = sum(s.n_chunks for s in self.layout.specs)
-        native.check(native.lib().tplr_index_overlap(desc_full.data_ptr(), n_full, total_chunks, n_peers,
-                                                     native.ptr_array(idx_ptrs), counts.data_ptr(),
-                                                     native.stream_ptr()), "index_overlap")
+        if self.world_size == 1:
+            desc, n_desc = self._desc_full
+            n_chunks = sum(s.n_chunks for s in self.layout.specs)
+        else:
+            if getattr(self, "_desc_rank_all", None) is None:
+                arr = self.layout.descriptors(self.rank, square=None)
+                self._desc_rank_all = (torch.from_numpy(arr.view(np.uint8).reshape(-1).copy()).to(self.device), len(arr),
+                                       int(arr["n_chunks"].sum()) if len(arr) else 0)
+            desc, n_desc, n_chunks = self._desc_rank_all
+        if n_chunks:
+            native.check(native.lib().tplr_index_overlap(desc.data_ptr(), n_desc, n_chunks, n_peers,
+                                                         native.ptr_array(idx_ptrs), counts.data_ptr(),
+                                                         native.stream_ptr()), "index_overlap")
+        if self.world_size > 1:
+            dist.all_reduce(counts, group=self.group)
         total = sum(s.n_chunks * s.topk(self.layout.topk) for s in self.layout.specs)
         return counts.view(n_peers, n_peers).double() / float(total)
 

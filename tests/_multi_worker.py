@@ -96,6 +96,10 @@ def main():
     out["master_max_diff"], out["compute_max_diff"], out["scale"] = diff, cdiff, scale
     moved = (ref.store.master_shard - ref.theta0).abs().max().item()
     out["moved"] = moved
+    # index overlap of the staged peers: the ranks of the sharded engine count over their own chunks and sum
+    ov, ov_ref = eng.index_overlap(4), ref.index_overlap(4)
+    out["overlap_max_diff"] = (ov - ov_ref).abs().max().item()
+    out["overlap_some"] = float(ov_ref.max().item())
 
     # 4. the same with 8-bit payload values: rank 0 encodes the assembled payload, every rank corrects its chunks
     import dataclasses

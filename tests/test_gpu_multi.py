@@ -37,6 +37,7 @@ def test_two_rank_runtime_and_window():
         assert r["moved"] > 1e-4, r
         assert r["master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
         assert r["compute_max_diff"] < 2e-2 * max(r["scale"], 1.0), r
+        assert r["overlap_max_diff"] < 1e-12 and r["overlap_some"] > 0, r
         # quantised payload values: sharded == single rank up to the bf16 summation order of the gradients
         assert r["q_status"] == 0, r
         assert r["q_master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
