@@ -81,5 +81,9 @@ def test_tensor_parallel_model_matches_unsharded():
     res = _run(2, worker="_tp_model_worker.py")
     for r in res:
         assert r["status"] == 0, r
-        assert abs(r["loss"] - r["ref_loss"]) < 3e-2 and r["guards_ok"], r
-        assert r["worst_rel"] < 0.12, r   # two bf16 pipelines with different summation orders
+        assert abs(r["loss"] - r["oracle_loss"]) < 3e-2 and abs(r["ref_loss"] - r["oracle_loss"]) < 3e-2 and r["guards_ok"], r
+        # Both bf16 pipelines are measured against the same model in fp32.  The tensor-parallel gradients may be off
+        # from the fp32 ones by at most twice what the single-GPU bf16 pipeline is off, tensor by tensor: a wrong shard
+        # slice or a missing 1 / world factor is an O(1) error and cannot hide behind that.
+        assert r["worst_ratio"] < 2.0, (r["worst_tensor"], r["worst_ratio"], r["rel"][r["worst_tensor"]])
+        assert r["worst_rel"] < 0.08, r
