@@ -53,6 +53,8 @@ struct Gemm2Params {
   int n_rot;                         // rotation of the tile-column order (in 256-column tiles)
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
   int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
+  int stream_k;                      // 1 (reduce-add epilogues only): the flattened (tile, k block) space is cut into one
+                                     // contiguous range per CTA pair, so every pair does the same number of k blocks
   int world, rank;
   unsigned int epoch;
   // gather
@@ -143,6 +145,41 @@ __device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int
   }
   *abort_flag = 1;
   return false;
+}
+
+// The work units of one CTA pair, walked identically by its producer, MMA and epilogue roles.  Static mode: units
+// pair, pair + P, ... of the (tile, k split) list.  Stream-K mode: the pair's contiguous range of the flattened
+// (tile, k block) space, cut at tile boundaries; a unit that covers part of a tile's K range is added into C by the
+// reduce-add epilogue like any other, so no fix-up pass exists.
+struct Work {
+  long long g, g_end;                // stream-K position / end (k blocks)
+  int t;                             // static unit index
+  int tile, kb0, nkb;                // current unit: tile index, first k block, k blocks
+};
+__device__ __forceinline__ void work_init(const Gemm2Params& p, Work& w, int pair, int tiles, int k_blocks_all) {
+  w.t = pair;
+  const long long total = (long long)tiles * k_blocks_all;
+  w.g = total * pair / p.n_compute_pairs;
+  w.g_end = total * (pair + 1) / p.n_compute_pairs;
+}
+__device__ __forceinline__ bool work_get(const Gemm2Params& p, Work& w, int tiles, int k_blocks_all, int k_per) {
+  if (p.stream_k) {
+    if (w.g >= w.g_end) return false;
+    w.tile = (int)(w.g / k_blocks_all);
+    w.kb0 = (int)(w.g - (long long)w.tile * k_blocks_all);
+    const long long left = w.g_end - w.g;
+    w.nkb = k_blocks_all - w.kb0 < left ? k_blocks_all - w.kb0 : (int)left;
+    return true;
+  }
+  if (w.t >= tiles * p.k_splits) return false;
+  w.tile = w.t / p.k_splits;
+  w.kb0 = (w.t % p.k_splits) * k_per;
+  w.nkb = min(k_per, k_blocks_all - w.kb0);
+  return true;
+}
+__device__ __forceinline__ void work_next(const Gemm2Params& p, Work& w) {
+  if (p.stream_k) w.g += w.nkb;
+  else            w.t += p.n_compute_pairs;
 }
 
 // tile index -> (tile row, tile column) under the launch's order
@@ -274,8 +311,8 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
   const bool is_compute = pair < p.n_compute_pairs;
   const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + TILE_N - 1) / TILE_N;
   const int k_blocks_all = (p.K + BK - 1) / BK;
-  const int k_per = (k_blocks_all + p.k_splits - 1) / p.k_splits;   // k blocks per work unit
-  const int num_tiles = tiles_m * tiles_n * p.k_splits;             // work units: (tile, k split), k split fastest
+  const int k_per = (k_blocks_all + p.k_splits - 1) / p.k_splits;   // k blocks per work unit (static mode)
+  const int num_tiles = tiles_m * tiles_n;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
@@ -320,11 +357,13 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         };
         uint32_t it = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs) {
+        Work w;
+        work_init(p, w, pair, num_tiles, k_blocks_all);
+        for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w)) {
           int tm, tn;
-          tile_coords(p, t / p.k_splits, tiles_m, tiles_n, tm, tn);
-          const int kb0 = (t % p.k_splits) * k_per;
-          const int k_blocks = min(k_per, k_blocks_all - kb0);
+          tile_coords(p, w.tile, tiles_m, tiles_n, tm, tn);
+          const int kb0 = w.kb0;
+          const int k_blocks = w.nkb;
           const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N + (int)cr * CTA_N;
           if (p.ag_operand == 1 && !A_MN) ok = rows_ready(m0, CTA_M);
           if (p.ag_operand == 2 && !B_MN) ok = ok && rows_ready(n0, CTA_N);
@@ -332,7 +371,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
             // k order rotated so that the rows of the local shard come first when k is the gathered dimension
             int kbr = kb0 + kb;
             if ((p.ag_operand == 1 && A_MN) || (p.ag_operand == 2 && B_MN)) {
-              kbr = kb + p.rank * (p.ag_rows_per_rank / BK);       // gathered k: never split
+              kbr = kb + p.rank * (p.ag_rows_per_rank / BK);       // gathered k: never split (host side)
               if (kbr >= k_blocks) kbr -= k_blocks;
               if (!(ok = rows_ready(kbr * BK, BK))) break;
             }
@@ -373,8 +412,10 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
                                ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
         uint32_t it = 0, tile_i = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
-          const int k_blocks = min(k_per, k_blocks_all - (t % p.k_splits) * k_per);
+        Work w;
+        work_init(p, w, pair, num_tiles, k_blocks_all);
+        for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w), ++tile_i) {
+          const int k_blocks = w.nkb;
           const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
           if (!(ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_ph ^ 1, abort_flag))) break;
           tcgen05_fence_after();
@@ -403,9 +444,11 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
       const int quad = warp & 3;
       uint32_t tile_i = 0, n_boxes = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += p.n_compute_pairs, ++tile_i) {
+      Work w;
+      work_init(p, w, pair, num_tiles, k_blocks_all);
+      for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w), ++tile_i) {
         int tm, tn;
-        tile_coords(p, t / p.k_splits, tiles_m, tiles_n, tm, tn);
+        tile_coords(p, w.tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N;
         const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
         ok = mbar_wait(smem_u32(&bar_tfull[acc]), acc_ph, abort_flag);
@@ -519,7 +562,8 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   if (n_comm_pairs >= pairs) return -106;
   const int tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
   int compute = pairs - n_comm_pairs;
-  if (compute > tiles) compute = tiles;
+  const long long units = p.stream_k ? (long long)tiles * ((p.K + BK - 1) / BK) / 8 : (long long)tiles * p.k_splits;
+  if (compute > units) compute = (int)(units > 0 ? units : 1);   // stream-K: at least 8 k blocks per pair
   p.n_compute_pairs = compute;
   cfg.gridDim = dim3(2 * (compute + n_comm_pairs));
   return (int)cudaLaunchKernelEx(&cfg, kern, p);
@@ -539,6 +583,24 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
 // Accumulating GEMMs (C += ...) reduce-add their tiles, so K may be cut in two to fill the last wave.
 // Every split costs another M*N*4 bytes of L2 reductions (measured: 4 and 8 splits lose more than the
 // fuller waves win), so K is halved only when that lifts the wave efficiency by more than 10 points.
+// Stream-K for accumulating GEMMs: when the tile count leaves the last wave of CTA pairs badly filled, cut the
+// flattened (tile, k block) space evenly over the pairs instead.  TPLR_GEMM_STREAMK=0 turns it off, =1 forces it.
+int g_stream_k_mode = -2;             // -2: not read yet; -1 automatic, 0 off, 1 forced (tplr_gemm2_set_stream_k)
+int pick_stream_k(int M, int N, int K, int max_pairs) {
+  if (g_stream_k_mode == -2) { const char* e = getenv("TPLR_GEMM_STREAMK"); g_stream_k_mode = e ? atoi(e) : 0; }
+  const int mode = g_stream_k_mode;
+  if (mode == 0) return 0;
+  int pairs = tplr_sm_count() / 2;
+  if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
+  const long long tiles = (long long)((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
+  const int kb = (K + BK - 1) / BK;
+  if (kb < 32) return 0;                                   // short K: units would be a few k blocks long
+  if (mode == 1) return 1;
+  if (mode != -1) return 0;
+  const double eff = (double)tiles / (double)(((tiles + pairs - 1) / pairs) * pairs);
+  return eff < 0.95 ? 1 : 0;
+}
+
 int pick_k_splits(int M, int N, int K, int max_pairs) {
   static const int forced = [] { const char* e = getenv("TPLR_GEMM_KSPLITS"); return e ? atoi(e) : 0; }();
   if (forced > 0) return (K + BK - 1) / BK / forced >= 1 ? forced : 1;   // tuning override
@@ -559,6 +621,7 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
   static const int group_m = [] { const char* e = getenv("TPLR_GEMM_GROUP_M"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
   p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.n_rot = 0; p.m_inter = 1; p.k_splits = 1;
+  p.stream_k = 0;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
@@ -568,6 +631,13 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
 
 }  // namespace
 
+// Scheduling of accumulating GEMMs (epilogue C += acc): -1 automatic, 0 never stream-K, 1 always (tuning, tests).
+TPLR_API int tplr_gemm2_set_stream_k(int mode) {
+  if (mode < -1 || mode > 1) return -1;
+  g_stream_k_mode = mode;
+  return 0;
+}
+
 // Same contract as tplr_gemm_bf16; max_pairs <= 0 uses every SM pair.
 TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int a_mn, int b_mn, int epi, unsigned int* status,
@@ -576,7 +646,10 @@ TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   Gemm2Params p = {};
   if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
-  if (epi == 1 && p.c_tma) p.k_splits = pick_k_splits(M, N, K, max_pairs);
+  if (epi == 1 && p.c_tma) {
+    p.stream_k = pick_stream_k(M, N, K, max_pairs);
+    if (!p.stream_k) p.k_splits = pick_k_splits(M, N, K, max_pairs);
+  }
   return dispatch2(p, a_mn, b_mn, epi, 0, max_pairs, (cudaStream_t)stream);
 }
 
@@ -692,6 +765,7 @@ TPLR_API int tplr_gemm2_scatter_v(const void* A, const void* B, int M, int N, in
   const int tiles_m = (M + TILE_M - 1) / TILE_M;
   if (world > 1 && tiles_m % world == 0) p.m_inter = world;
   if (world > 1) p.m_rot = (int)(((long long)rank * tiles_m) / world);
-  p.k_splits = pick_k_splits(M, N, K, 0);
+  p.stream_k = pick_stream_k(M, N, K, 0);
+  if (!p.stream_k) p.k_splits = pick_k_splits(M, N, K, 0);
   return dispatch2(p, a_mn, b_mn, 1, 0, 0, (cudaStream_t)stream);
 }
