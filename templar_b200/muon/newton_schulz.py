@@ -7,8 +7,10 @@ src/tplr/muon/newton_schulz_triton.py:336-374):
     B = b A + c A A              "line 2"  -> ``gemm(A, A)`` + axpby  (A is symmetric, so A A = A A^T)
     X = a X + B X                "line 3"  -> ``gemm(B, X, b_mn=True)`` + axpby
 
-bf16 operands, fp32 accumulation in TMEM.  The reference runs lines 1-2 as Triton kernels and line 3
-through cuBLAS; here all three are the same hand-written kernel and no transposed copy is made.
+bf16 operands, fp32 accumulation in TMEM.  The reference runs lines 1-2 as Triton kernels that compute one triangle
+of the symmetric results and mirror it on the store, and line 3 through cuBLAS; here all three are the same
+hand-written tcgen05 kernel, lines 1-2 in its one-triangle mode (``_ns_2d_symmetric``), and no transposed copy is
+made.  ``python -m templar_b200.muon.bench`` times the variants and the reference's kernels.
 Batched inputs (leading dimensions) are processed matrix by matrix.
 """
 
@@ -22,12 +24,45 @@ NS_CONSTS = [(4.0848, -6.8946, 2.9270), (3.9505, -6.3029, 2.6377), (3.7418, -5.5
              (2.8769, -3.1427, 1.2046), (2.8366, -3.0525, 1.2012)]
 
 
+def _one_triangle_ok(X: torch.Tensor) -> bool:
+    return (X.is_cuda and X.dtype == torch.bfloat16 and OF.gemm_backend() == "tcgen05_2sm" and X.shape[0] >= 512
+            and X.shape[0] % 8 == 0 and X.shape[1] % 8 == 0 and SYMMETRIC_PRODUCTS)
+
+
+SYMMETRIC_PRODUCTS = True        # lines 1 and 2 as one-triangle products (module switch, for the comparison benchmark)
+
+
+def _ns_2d_symmetric(X: torch.Tensor) -> torch.Tensor:
+    """Lines 1 and 2 compute only the 256 x 256 tiles on or above the diagonal of their symmetric results
+    (``tplr_gemm2_syrk``: half the tensor-core work) and one small kernel mirrors the triangle while it applies the
+    line's scalars (``tplr_sym_axpby``)."""
+    from ..ops import native
+
+    L = native.lib()
+    M = X.shape[0]
+    st = OF.status_word(X.device).data_ptr()
+    U = torch.empty(M, M, dtype=torch.bfloat16, device=X.device)          # triangle scratch
+    A = torch.empty_like(U)
+    B = torch.empty_like(U)
+    for a, b, c in NS_CONSTS:
+        stream = native.stream_ptr()
+        native.check(L.tplr_gemm2_syrk(X.data_ptr(), U.data_ptr(), M, X.shape[1], X.stride(0), M, st, stream), "syrk")
+        native.check(L.tplr_sym_axpby(U.data_ptr(), M, M, 1.0, None, 0, 0.0, A.data_ptr(), M, stream), "sym_axpby")
+        native.check(L.tplr_gemm2_syrk(A.data_ptr(), U.data_ptr(), M, M, M, M, st, stream), "syrk")    # A A = A A^T
+        native.check(L.tplr_sym_axpby(U.data_ptr(), M, M, c, A.data_ptr(), M, b, B.data_ptr(), M, stream), "sym_axpby")
+        X = (a * X + OF.gemm(B, X, b_mn=True)).contiguous()
+    return X
+
+
 def _ns_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:
     X = G.to(torch.bfloat16)
     transposed = G.size(-2) > G.size(-1)
     if transposed:
         X = X.mT
     X = (X / (X.float().norm() + epsilon).to(X.dtype)).contiguous()
+    if _one_triangle_ok(X):
+        X = _ns_2d_symmetric(X)
+        return X.mT if transposed else X
     for a, b, c in NS_CONSTS:
         A = OF.gemm(X, X)                       # X X^T
         AA = OF.gemm(A, A)                      # A A^T = A A

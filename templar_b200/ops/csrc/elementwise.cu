@@ -717,6 +717,46 @@ TPLR_API int tplr_cast_bf16(const float* src, void* dst, long long n, void* stre
 }
 
 // ------------------------------------------------------------------------------------- //
+// Mirror of a symmetric product computed as one triangle, fused with the Newton-Schulz combination:
+//   out[i][j] = alpha * U[i][j] (+ beta * aux[i][j])   where U[i][j] is read at (i, j) when the 256 x 256 tile of
+//   (i, j) lies on or above the diagonal and at (j, i) otherwise (tplr_gemm2_syrk leaves the lower tiles unwritten).
+// 32 x 32 tiles; a lower tile is the transpose of its mirror tile, staged through shared memory.
+// ------------------------------------------------------------------------------------- //
+__global__ void __launch_bounds__(256) sym_axpby_kernel(const bf16* __restrict__ U, long long ldu, int M, float alpha,
+                                                        const bf16* __restrict__ aux, long long ldaux, float beta,
+                                                        bf16* __restrict__ out, long long ldo) {
+  __shared__ float tile[32][33];
+  const int ti = blockIdx.y, tj = blockIdx.x;
+  const bool upper = (tj * 32) / 256 >= (ti * 32) / 256;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;              // 32 x 8 threads, 4 rows each
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int li = ty * 4 + r;
+    const int si = (upper ? ti : tj) * 32 + li, sj = (upper ? tj : ti) * 32 + tx;
+    tile[li][tx] = (si < M && sj < M) ? __bfloat162float(U[(long long)si * ldu + sj]) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int li = ty * 4 + r;
+    const int i = ti * 32 + li, j = tj * 32 + tx;
+    if (i >= M || j >= M) continue;
+    float v = alpha * (upper ? tile[li][tx] : tile[tx][li]);
+    if (aux) v += beta * __bfloat162float(aux[(long long)i * ldaux + j]);
+    out[(long long)i * ldo + j] = __float2bfloat16(v);
+  }
+}
+TPLR_API int tplr_sym_axpby(const void* U, long long ldu, int M, float alpha, const void* aux, long long ldaux, float beta,
+                            void* out, long long ldo, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0) return 0;
+  const unsigned t = (unsigned)((M + 31) / 32);
+  sym_axpby_kernel<<<dim3(t, t), 256, 0, (cudaStream_t)stream>>>((const bf16*)U, ldu, M, alpha, (const bf16*)aux, ldaux,
+                                                               beta, (bf16*)out, ldo);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------- //
 // Cross entropy without caller-provided scratch (see no_alloc.h). The per-row losses and the
 // valid-row counter live in a file-scope device array. In host code the array's name is only a
 // handle: its device address is looked up once per device with cudaGetSymbolAddress (with that

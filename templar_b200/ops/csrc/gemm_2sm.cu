@@ -53,6 +53,7 @@ struct Gemm2Params {
   int n_rot;                         // rotation of the tile-column order (in 256-column tiles)
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
   int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
+  int tri;                           // 1: C is symmetric (B is A): only tiles on or above the diagonal are computed
   int stream_k;                      // 1 (reduce-add epilogues only): the flattened (tile, k block) space is cut into one
                                      // contiguous range per CTA pair, so every pair does the same number of k blocks
   int world, rank;
@@ -184,6 +185,13 @@ __device__ __forceinline__ void work_next(const Gemm2Params& p, Work& w) {
 
 // tile index -> (tile row, tile column) under the launch's order
 __device__ __forceinline__ void tile_coords(const Gemm2Params& p, int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  if (p.tri) {                       // t-th tile of the upper triangle, row by row: row i holds tiles_n - i tiles
+    int i = 0, left = t;
+    while (left >= tiles_n - i) { left -= tiles_n - i; ++i; }
+    tm = i;
+    tn = i + left;
+    return;
+  }
   const int band = p.group_m * tiles_n;
   const int g = t / band, first = g * p.group_m;
   const int rows = p.group_m < tiles_m - first ? p.group_m : tiles_m - first;
@@ -312,7 +320,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
   const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + TILE_N - 1) / TILE_N;
   const int k_blocks_all = (p.K + BK - 1) / BK;
   const int k_per = (k_blocks_all + p.k_splits - 1) / p.k_splits;   // k blocks per work unit (static mode)
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = p.tri ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
@@ -560,7 +568,8 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   int pairs = mc < tplr_sm_count() / 2 ? mc : tplr_sm_count() / 2;
   if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
   if (n_comm_pairs >= pairs) return -106;
-  const int tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
+  const int tiles_m_h = (p.M + TILE_M - 1) / TILE_M;
+  const int tiles = p.tri ? tiles_m_h * (tiles_m_h + 1) / 2 : tiles_m_h * ((p.N + TILE_N - 1) / TILE_N);
   int compute = pairs - n_comm_pairs;
   const long long units = p.stream_k ? (long long)tiles * ((p.K + BK - 1) / BK) / 8 : (long long)tiles * p.k_splits;
   if (compute > units) compute = (int)(units > 0 ? units : 1);   // stream-K: at least 8 k blocks per pair
@@ -621,7 +630,7 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
   static const int group_m = [] { const char* e = getenv("TPLR_GEMM_GROUP_M"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
   p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.n_rot = 0; p.m_inter = 1; p.k_splits = 1;
-  p.stream_k = 0;
+  p.stream_k = 0; p.tri = 0;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
@@ -636,6 +645,20 @@ TPLR_API int tplr_gemm2_set_stream_k(int mode) {
   if (mode < -1 || mode > 1) return -1;
   g_stream_k_mode = mode;
   return 0;
+}
+
+// Symmetric rank-k product for Newton-Schulz: the 256 x 256 tiles of C = A A^T (A: [M, K] bf16, K-major; C bf16) that
+// lie on or above the diagonal.  Tiles below the diagonal are NOT written: tplr_sym_axpby mirrors them.  Half the
+// tensor-core work of the full product, as the reference's Triton kernels ns_line_1 / ns_line_2 do with one triangle
+// and a mirrored store (src/tplr/muon/newton_schulz_triton.py:62-131, :173-258).
+TPLR_API int tplr_gemm2_syrk(const void* A, void* C, int M, int K, long long lda, long long ldc, unsigned int* status,
+                             void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || K <= 0) return 0;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, A, A, C, M, M, K, lda, lda, ldc, 0, 0, 0, status)) return r;
+  p.tri = 1;
+  return dispatch2(p, 0, 0, 0, 0, 0, (cudaStream_t)stream);
 }
 
 // Same contract as tplr_gemm_bf16; max_pairs <= 0 uses every SM pair.

@@ -150,6 +150,50 @@ def test_newton_schulz_on_own_gemm_matches_fp32_iterations():
     assert int(OF.status_word(torch.device("cuda")).item()) == 0
 
 
+@pytest.mark.gpu
+def test_one_triangle_products_match_full_products_and_fp32():
+    """Lines 1 and 2 of the iteration as one-triangle products (tiles on or above the diagonal + mirror kernel)
+    against the same kernel computing every tile, and against fp32 iterations; sizes with several 256-tiles per
+    side, one that is not a multiple of 256, and both orientations."""
+    from templar_b200.muon import newton_schulz as ns
+    from templar_b200.ops import functional as OF
+    from templar_b200.ops import native
+
+    torch.manual_seed(8)
+    # the triangle product and the mirror by themselves, bit for bit against the full product
+    for M, K in ((1024, 512), (768, 2048), (520, 264)):
+        x = (torch.randn(M, K, device="cuda") * 0.05).to(torch.bfloat16)
+        full = OF.gemm(x, x)
+        u = torch.full((M, M), float("nan"), dtype=torch.bfloat16, device="cuda")
+        out = torch.empty_like(u)
+        L, st = native.lib(), OF.status_word(torch.device("cuda")).data_ptr()
+        native.check(L.tplr_gemm2_syrk(x.data_ptr(), u.data_ptr(), M, K, K, M, st, native.stream_ptr()), "syrk")
+        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 1.0, None, 0, 0.0, out.data_ptr(), M, native.stream_ptr()), "sym")
+        assert torch.equal(out.triu(256), full.triu(256))                 # tiles above the diagonal: the same numbers
+        assert torch.equal(out, out.t()) and torch.isfinite(out.float()).all()
+        assert (out.float() - full.float()).abs().max().item() <= 2 ** -7 * full.float().abs().max().item()
+        aux = torch.randn_like(out)
+        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 0.5, aux.data_ptr(), M, -2.0, out.data_ptr(), M,
+                                      native.stream_ptr()), "sym")
+        want = 0.5 * torch.where(torch.ones(M, M, device="cuda").triu().bool(), full.float(), full.float().t()) - 2.0 * aux.float()
+        assert (out.float() - want).abs().max().item() < 0.05 * max(want.abs().max().item(), 1.0)
+    for shape in [(1024, 1024), (768, 2048), (2048, 512), (520, 1032)]:
+        G = torch.randn(*shape, device="cuda")
+        ns.SYMMETRIC_PRODUCTS = True
+        X = newton_schulz(G).float()
+        ns.SYMMETRIC_PRODUCTS = False
+        try:
+            F = newton_schulz(G).float()
+        finally:
+            ns.SYMMETRIC_PRODUCTS = True
+        ref = _ns_reference(G)
+        assert float((X - F).norm() / F.norm()) < 2e-2
+        assert float((X - ref).norm() / ref.norm()) < 4e-2
+        sv = torch.linalg.svdvals(X)
+        assert float(sv.max()) < 1.3 and 0.9 < float(sv.median()) < 1.1
+    assert int(OF.status_word(torch.device("cuda")).item()) == 0
+
+
 def test_engine_muon_step_equals_single_device_muon_with_aux_adam():
     """The window engine's Muon inner step (flat fp32 state) against the optimizer class on the module tree,
     with the groups, LR scales and decays the trainer builds for ``optimizer.type == "muon"``."""
