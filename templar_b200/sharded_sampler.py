@@ -23,7 +23,7 @@ def _window_seed(uid: int, window: int) -> int:
 class _WindowSampler(Sampler):
     def __init__(self, dataset, uid: int, window: int, *, steps_per_window: int, micro_bs: int, batch_size: int,
                  rank: int = 0, world_size: int = 1):
-        self._dataset_ref = dataset
+        self._source = dataset
         self.dataset_len = len(dataset)
         self.steps_per_window, self.micro_bs, self.batch_size = steps_per_window, micro_bs, batch_size
         self.rank, self.world_size = rank, world_size
@@ -32,16 +32,16 @@ class _WindowSampler(Sampler):
 
     def set_window_uid(self, uid: int, window: int) -> None:
         self.uid, self.window = uid, window
-        self._local = self._global_indices()[self.rank:: self.world_size].tolist()
+        self._mine = self._global_indices()[self.rank:: self.world_size].tolist()
 
     def __iter__(self):
-        return iter(self._local)
+        return iter(self._mine)
 
     def __len__(self):
-        return len(self._local)
+        return len(self._mine)
 
     def ids_for_indices(self, idx_list) -> list[int]:
-        return [self._dataset_ref.sample_id(i) for i in idx_list]
+        return [self._source.sample_id(i) for i in idx_list]
 
     def _global_indices(self) -> np.ndarray:  # pragma: no cover - abstract
         raise NotImplementedError
@@ -57,18 +57,18 @@ class MinerSampler(_WindowSampler):
     def _global_indices(self) -> np.ndarray:
         wanted = self.steps_per_window * self.target_batch_size
         if wanted > self.dataset_len:
-            raise ValueError(f"Window needs {wanted} samples but dataset has only {self.dataset_len}")
+            raise ValueError(f"a window draws {wanted} samples; the dataset holds {self.dataset_len}")
         rng = np.random.default_rng(_window_seed(self.uid, self.window))
         return rng.choice(self.dataset_len, size=wanted, replace=False)
 
 
 class EvalSampler(_WindowSampler):
-    _cached_indices: dict[tuple[int, int], np.ndarray] = {}
+    _subset_cache: dict[tuple[int, int], np.ndarray] = {}
 
     def __init__(self, dataset, uid, window, *, steps_per_window, micro_bs, batch_size, validation_bs,
                  rank: int = 0, world_size: int = 1):
         if validation_bs > batch_size:
-            raise ValueError("validation_bs must be ≤ batch_size")
+            raise ValueError("the validation subset cannot be larger than the batch it is drawn from")
         self.validation_bs = validation_bs
         super().__init__(dataset, uid, window, steps_per_window=steps_per_window, micro_bs=micro_bs,
                          batch_size=batch_size, rank=rank, world_size=world_size)
@@ -78,13 +78,13 @@ class EvalSampler(_WindowSampler):
 
     def _global_indices(self) -> np.ndarray:
         key = (self.uid, self.window)
-        hit = self._cached_indices.get(key)
+        hit = self._subset_cache.get(key)
         if hit is not None:
             return hit
         total = self.steps_per_window * self.batch_size
         if total > self.dataset_len:
-            raise ValueError("Training pool larger than dataset!")
+            raise ValueError("the reconstructed training pool does not fit the dataset")
         pool = np.random.default_rng(_window_seed(self.uid, self.window)).choice(self.dataset_len, size=total, replace=False)
         val = np.random.default_rng(self._eval_seed()).choice(pool, size=self.validation_bs, replace=False)
-        self._cached_indices[key] = val
+        self._subset_cache[key] = val
         return val

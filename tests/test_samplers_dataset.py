@@ -40,7 +40,7 @@ def test_too_small_dataset_raises():
 
 
 def test_eval_sampler_is_subset_of_training_pool_and_cached():
-    tplr.EvalSampler._cached_indices.clear()
+    tplr.EvalSampler._subset_cache.clear()
     ds = _DS(3000)
     ev = tplr.EvalSampler(ds, 5, 77, steps_per_window=2, micro_bs=1, batch_size=16, validation_bs=8)
     pool = set(np.random.default_rng(_window_seed(5, 77)).choice(3000, size=32, replace=False).tolist())
