@@ -1,0 +1,56 @@
+"""Operator tools over the object-store interface (in-memory store)."""
+
+import asyncio
+import io
+
+import torch
+
+from templar_b200 import bucket_tools as bt
+from templar_b200.backends.store import MemoryStore
+from templar_b200.schemas import Bucket
+
+B = Bucket(name="b", account_id="a", access_key_id="k", secret_access_key="s")
+
+
+def _blob(obj):
+    buf = io.BytesIO()
+    torch.save(obj, buf)
+    return buf.getvalue()
+
+
+def test_classify_names():
+    assert bt.classify("gradient-12-3-v2.1.28.pt") == ("gradient", 12, "2.1.28")
+    assert bt.classify("aggregator-7-v2.1.28.pt") == ("aggregator", 7, "2.1.28")
+    assert bt.classify("debug-5-0-v2.1.27.pt") == ("debug", 5, "2.1.27")
+    assert bt.classify("peers_40_v2.1.28.json")[0] == "peers"
+    assert bt.classify("checkpoints/2.1.28/30/__0_0.distcp") == ("checkpoint", 30, "2.1.28")
+    assert bt.classify("notes.txt") == ("other", None, None)
+
+
+def test_validate_summary_cleanup_and_versions():
+    async def go():
+        st = MemoryStore()
+        assert await bt.validate(st, B) == {"put": True, "head": True, "get": True, "delete": True}
+        for w in range(1, 6):
+            await st.put_bytes(B, f"gradient-{w}-3-v2.1.28.pt", _blob({"state_dict": {"a.vals": torch.zeros(4), "a.idxs": torch.zeros(6, dtype=torch.uint8),
+                                                                                      "a.quant_params": None, "metadata": {"window": w}},
+                                                                       "global_step": w}))
+            await st.put_bytes(B, f"debug-{w}-3-v2.1.28.pt", b"x")
+        await st.put_bytes(B, "gradient-1-3-v2.1.20.pt", b"old")
+        await st.put_bytes(B, "checkpoints/2.1.28/4/.metadata", b"m")
+        s = await bt.summary(st, B)
+        assert s["gradient@2.1.28"]["objects"] == 5 and s["gradient@2.1.20"]["objects"] == 1 and s["checkpoint@2.1.28"]["objects"] == 1
+        would = await bt.cleanup(st, B, keep_windows=2, dry_run=True)
+        assert len(would) == 7 and len(await st.list(B, "")) == 12          # nothing deleted on a dry run
+        gone = await bt.cleanup(st, B, keep_windows=2)
+        assert sorted(gone) == sorted(would)
+        left = [o.key for o in await st.list(B, "")]
+        assert "gradient-5-3-v2.1.28.pt" in left and "gradient-4-3-v2.1.28.pt" in left and "gradient-3-3-v2.1.28.pt" not in left
+        assert "checkpoints/2.1.28/4/.metadata" in left                        # checkpoints are not window litter
+        await st.put_bytes(B, "gradient-9-3-v2.1.20.pt", b"old")
+        assert await bt.clean_versions(st, B, keep="2.1.28") == ["gradient-9-3-v2.1.20.pt"]
+        obj = await bt.get_gradient(st, B, 3, 5, "2.1.28")
+        d = bt.describe_gradient(obj)
+        assert d["global_step"] == 5 and d["tensors"] == 1 and d["values"] == 4 and d["index_bytes"] == 6 and not d["quantised"]
+        assert await bt.get_gradient(st, B, 3, 99, "2.1.28") is None
+    asyncio.run(go())
