@@ -25,8 +25,11 @@ def main():
     ap.add_argument("--reference", action="store_true")
     a = ap.parse_args()
 
+    import importlib
+
     from ..ops.microbench import time_ms
-    from . import newton_schulz as ns
+
+    ns = importlib.import_module("templar_b200.muon.newton_schulz")     # the module (the package re-exports the function)
 
     ref_fn = None
     if a.reference:

@@ -54,8 +54,6 @@ struct Gemm2Params {
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
   int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
   int tri;                           // 1: C is symmetric (B is A): only tiles on or above the diagonal are computed
-  int stream_k;                      // 1 (reduce-add epilogues only): the flattened (tile, k block) space is cut into one
-                                     // contiguous range per CTA pair, so every pair does the same number of k blocks
   int world, rank;
   unsigned int epoch;
   // gather
@@ -148,40 +146,23 @@ __device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int
   return false;
 }
 
-// The work units of one CTA pair, walked identically by its producer, MMA and epilogue roles.  Static mode: units
-// pair, pair + P, ... of the (tile, k split) list.  Stream-K mode: the pair's contiguous range of the flattened
-// (tile, k block) space, cut at tile boundaries; a unit that covers part of a tile's K range is added into C by the
-// reduce-add epilogue like any other, so no fix-up pass exists.
+// The work units of one CTA pair, walked identically by its producer, MMA and epilogue roles: units pair, pair + P,
+// ... of the (tile, k split) list, k split fastest.  (A stream-K cut of the flattened (tile, k block) space, every pair
+// an equal contiguous run, was measured on the weight-gradient shapes and lost 20-25 % to this static order: pairs
+// that share operand tiles stop running in step, and the L2 reuse between them goes.)
 struct Work {
-  long long g, g_end;                // stream-K position / end (k blocks)
-  int t;                             // static unit index
+  int t;                             // unit index
   int tile, kb0, nkb;                // current unit: tile index, first k block, k blocks
 };
-__device__ __forceinline__ void work_init(const Gemm2Params& p, Work& w, int pair, int tiles, int k_blocks_all) {
-  w.t = pair;
-  const long long total = (long long)tiles * k_blocks_all;
-  w.g = total * pair / p.n_compute_pairs;
-  w.g_end = total * (pair + 1) / p.n_compute_pairs;
-}
+__device__ __forceinline__ void work_init(const Gemm2Params& p, Work& w, int pair) { w.t = pair; }
 __device__ __forceinline__ bool work_get(const Gemm2Params& p, Work& w, int tiles, int k_blocks_all, int k_per) {
-  if (p.stream_k) {
-    if (w.g >= w.g_end) return false;
-    w.tile = (int)(w.g / k_blocks_all);
-    w.kb0 = (int)(w.g - (long long)w.tile * k_blocks_all);
-    const long long left = w.g_end - w.g;
-    w.nkb = k_blocks_all - w.kb0 < left ? k_blocks_all - w.kb0 : (int)left;
-    return true;
-  }
   if (w.t >= tiles * p.k_splits) return false;
   w.tile = w.t / p.k_splits;
   w.kb0 = (w.t % p.k_splits) * k_per;
   w.nkb = min(k_per, k_blocks_all - w.kb0);
   return true;
 }
-__device__ __forceinline__ void work_next(const Gemm2Params& p, Work& w) {
-  if (p.stream_k) w.g += w.nkb;
-  else            w.t += p.n_compute_pairs;
-}
+__device__ __forceinline__ void work_next(const Gemm2Params& p, Work& w) { w.t += p.n_compute_pairs; }
 
 // tile index -> (tile row, tile column) under the launch's order
 __device__ __forceinline__ void tile_coords(const Gemm2Params& p, int t, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -366,7 +347,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         uint32_t it = 0;
         bool ok = true;
         Work w;
-        work_init(p, w, pair, num_tiles, k_blocks_all);
+        work_init(p, w, pair);
         for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w)) {
           int tm, tn;
           tile_coords(p, w.tile, tiles_m, tiles_n, tm, tn);
@@ -421,7 +402,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         uint32_t it = 0, tile_i = 0;
         bool ok = true;
         Work w;
-        work_init(p, w, pair, num_tiles, k_blocks_all);
+        work_init(p, w, pair);
         for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w), ++tile_i) {
           const int k_blocks = w.nkb;
           const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
@@ -453,7 +434,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
       uint32_t tile_i = 0, n_boxes = 0;
       bool ok = true;
       Work w;
-      work_init(p, w, pair, num_tiles, k_blocks_all);
+      work_init(p, w, pair);
       for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w), ++tile_i) {
         int tm, tn;
         tile_coords(p, w.tile, tiles_m, tiles_n, tm, tn);
@@ -571,8 +552,7 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   const int tiles_m_h = (p.M + TILE_M - 1) / TILE_M;
   const int tiles = p.tri ? tiles_m_h * (tiles_m_h + 1) / 2 : tiles_m_h * ((p.N + TILE_N - 1) / TILE_N);
   int compute = pairs - n_comm_pairs;
-  const long long units = p.stream_k ? (long long)tiles * ((p.K + BK - 1) / BK) / 8 : (long long)tiles * p.k_splits;
-  if (compute > units) compute = (int)(units > 0 ? units : 1);   // stream-K: at least 8 k blocks per pair
+  if (compute > tiles * p.k_splits) compute = tiles * p.k_splits;
   p.n_compute_pairs = compute;
   cfg.gridDim = dim3(2 * (compute + n_comm_pairs));
   return (int)cudaLaunchKernelEx(&cfg, kern, p);
@@ -592,24 +572,6 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
 // Accumulating GEMMs (C += ...) reduce-add their tiles, so K may be cut in two to fill the last wave.
 // Every split costs another M*N*4 bytes of L2 reductions (measured: 4 and 8 splits lose more than the
 // fuller waves win), so K is halved only when that lifts the wave efficiency by more than 10 points.
-// Stream-K for accumulating GEMMs: when the tile count leaves the last wave of CTA pairs badly filled, cut the
-// flattened (tile, k block) space evenly over the pairs instead.  TPLR_GEMM_STREAMK=0 turns it off, =1 forces it.
-int g_stream_k_mode = -2;             // -2: not read yet; -1 automatic, 0 off, 1 forced (tplr_gemm2_set_stream_k)
-int pick_stream_k(int M, int N, int K, int max_pairs) {
-  if (g_stream_k_mode == -2) { const char* e = getenv("TPLR_GEMM_STREAMK"); g_stream_k_mode = e ? atoi(e) : 0; }
-  const int mode = g_stream_k_mode;
-  if (mode == 0) return 0;
-  int pairs = tplr_sm_count() / 2;
-  if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
-  const long long tiles = (long long)((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
-  const int kb = (K + BK - 1) / BK;
-  if (kb < 32) return 0;                                   // short K: units would be a few k blocks long
-  if (mode == 1) return 1;
-  if (mode != -1) return 0;
-  const double eff = (double)tiles / (double)(((tiles + pairs - 1) / pairs) * pairs);
-  return eff < 0.95 ? 1 : 0;
-}
-
 int pick_k_splits(int M, int N, int K, int max_pairs) {
   static const int forced = [] { const char* e = getenv("TPLR_GEMM_KSPLITS"); return e ? atoi(e) : 0; }();
   if (forced > 0) return (K + BK - 1) / BK / forced >= 1 ? forced : 1;   // tuning override
@@ -630,7 +592,7 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.status = status;
   static const int group_m = [] { const char* e = getenv("TPLR_GEMM_GROUP_M"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
   p.world = 1; p.rank = 0; p.epoch = 0; p.group_m = group_m; p.m_rot = 0; p.n_rot = 0; p.m_inter = 1; p.k_splits = 1;
-  p.stream_k = 0; p.tri = 0;
+  p.tri = 0;
   p.ag_operand = 0; p.rs_on = 0;
   const bool f32 = epi != 0;
   p.c_tma = !((uintptr_t)C & 15) && (ldc * (f32 ? 4 : 2)) % 16 == 0;
@@ -639,13 +601,6 @@ int fill_common(Gemm2Params& p, const void* A, const void* B, void* C, int M, in
 }
 
 }  // namespace
-
-// Scheduling of accumulating GEMMs (epilogue C += acc): -1 automatic, 0 never stream-K, 1 always (tuning, tests).
-TPLR_API int tplr_gemm2_set_stream_k(int mode) {
-  if (mode < -1 || mode > 1) return -1;
-  g_stream_k_mode = mode;
-  return 0;
-}
 
 // Symmetric rank-k product for Newton-Schulz: the 256 x 256 tiles of C = A A^T (A: [M, K] bf16, K-major; C bf16) that
 // lie on or above the diagonal.  Tiles below the diagonal are NOT written: tplr_sym_axpby mirrors them.  Half the
@@ -669,10 +624,7 @@ TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   Gemm2Params p = {};
   if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
-  if (epi == 1 && p.c_tma) {
-    p.stream_k = pick_stream_k(M, N, K, max_pairs);
-    if (!p.stream_k) p.k_splits = pick_k_splits(M, N, K, max_pairs);
-  }
+  if (epi == 1 && p.c_tma) p.k_splits = pick_k_splits(M, N, K, max_pairs);
   return dispatch2(p, a_mn, b_mn, epi, 0, max_pairs, (cudaStream_t)stream);
 }
 
@@ -788,7 +740,6 @@ TPLR_API int tplr_gemm2_scatter_v(const void* A, const void* B, int M, int N, in
   const int tiles_m = (M + TILE_M - 1) / TILE_M;
   if (world > 1 && tiles_m % world == 0) p.m_inter = world;
   if (world > 1) p.m_rot = (int)(((long long)rank * tiles_m) / world);
-  p.stream_k = pick_stream_k(M, N, K, 0);
-  if (!p.stream_k) p.k_splits = pick_k_splits(M, N, K, 0);
+  p.k_splits = pick_k_splits(M, N, K, 0);
   return dispatch2(p, a_mn, b_mn, 1, 0, 0, (cudaStream_t)stream);
 }

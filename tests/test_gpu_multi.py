@@ -86,4 +86,6 @@ def test_tensor_parallel_model_matches_unsharded():
         # from the fp32 ones by at most twice what the single-GPU bf16 pipeline is off, tensor by tensor: a wrong shard
         # slice or a missing 1 / world factor is an O(1) error and cannot hide behind that.
         assert r["worst_ratio"] < 2.0, (r["worst_tensor"], r["worst_ratio"], r["rel"][r["worst_tensor"]])
-        assert r["worst_rel"] < 0.08, r
+        # (the absolute error of either bf16 pipeline against fp32 reaches about 0.1 on the tensors with the smallest
+        # gradients of this small random model, which is why the bound is relative to the single-GPU pipeline)
+        assert r["worst_rel"] < 0.25, sorted(r["rel"].items(), key=lambda kv: -kv[1][0])[:3]

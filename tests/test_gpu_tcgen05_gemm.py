@@ -86,38 +86,6 @@ def test_gemm_model_shapes_forward_dgrad_wgrad(T, N, K, backend):
     assert int(OF.status_word(DEV).item()) == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(6144, 2048, 16384), (2048, 2048, 16384), (2048, 8192, 4096), (512, 768, 2560),
-                                   (300, 520, 2112)])
-def test_accumulating_gemm_stream_k_matches_static_schedule(M, N, K):
-    """Weight-gradient layout (both operands MN-major, C += acc): the stream-K schedule (every CTA pair gets an equal
-    run of the flattened (tile, k block) space, partial tiles reduce-added) against fp32 and against the static
-    schedule."""
-    from templar_b200.ops import native
-
-    prev = OF.gemm_backend()
-    OF.set_gemm_backend("tcgen05_2sm")
-    torch.manual_seed(M + K)
-    dy = (torch.randn(K, M, device=DEV) * 0.1).to(torch.bfloat16)
-    x = (torch.randn(K, N, device=DEV) * 0.5).to(torch.bfloat16)
-    ref = dy.float().t() @ x.float() + 1.0
-    L = native.lib()
-    outs = {}
-    try:
-        for mode in (0, 1):
-            assert L.tplr_gemm2_set_stream_k(mode) == 0
-            OF.status_word(DEV).zero_()
-            acc = torch.ones(M, N, device=DEV)
-            OF.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
-            torch.cuda.synchronize()
-            assert int(OF.status_word(DEV).item()) == 0
-            assert (acc - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0), mode
-            outs[mode] = acc
-        assert (outs[0] - outs[1]).abs().max().item() < 1e-3 * max(ref.abs().max().item(), 1.0)
-    finally:
-        L.tplr_gemm2_set_stream_k(-1)
-        OF.set_gemm_backend(prev)
-
-
 def test_library_fallback_is_counted_and_said(backend):
     """Operands that the own kernels cannot take (a row stride that is not a multiple of 8 elements) go to the
     library with a warning and a counter; under TPLR_STRICT_NATIVE=1 they are an error."""
