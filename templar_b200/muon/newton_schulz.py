@@ -32,26 +32,64 @@ def _one_triangle_ok(X: torch.Tensor) -> bool:
 SYMMETRIC_PRODUCTS = True        # lines 1 and 2 as one-triangle products (module switch, for the comparison benchmark)
 
 
-def _ns_2d_symmetric(X: torch.Tensor) -> torch.Tensor:
-    """Lines 1 and 2 compute only the 256 x 256 tiles on or above the diagonal of their symmetric results
-    (``tplr_gemm2_syrk``: half the tensor-core work) and one small kernel mirrors the triangle while it applies the
-    line's scalars (``tplr_sym_axpby``)."""
-    from ..ops import native
+class _SymmetricChain:
+    """The five iterations for one matrix shape on static buffers, captured once in a CUDA graph and replayed:
+    25 launches (per iteration: one-triangle X X^T, mirror, one-triangle A A, mirror with the line's scalars and the
+    identity term, full product) with no host work between them.
 
-    L = native.lib()
-    M = X.shape[0]
-    st = OF.status_word(X.device).data_ptr()
-    U = torch.empty(M, M, dtype=torch.bfloat16, device=X.device)          # triangle scratch
-    A = torch.empty_like(U)
-    B = torch.empty_like(U)
-    for a, b, c in NS_CONSTS:
-        stream = native.stream_ptr()
-        native.check(L.tplr_gemm2_syrk(X.data_ptr(), U.data_ptr(), M, X.shape[1], X.stride(0), M, st, stream), "syrk")
-        native.check(L.tplr_sym_axpby(U.data_ptr(), M, M, 1.0, None, 0, 0.0, A.data_ptr(), M, stream), "sym_axpby")
-        native.check(L.tplr_gemm2_syrk(A.data_ptr(), U.data_ptr(), M, M, M, M, st, stream), "syrk")    # A A = A A^T
-        native.check(L.tplr_sym_axpby(U.data_ptr(), M, M, c, A.data_ptr(), M, b, B.data_ptr(), M, stream), "sym_axpby")
-        X = (a * X + OF.gemm(B, X, b_mn=True)).contiguous()
-    return X
+    Lines 1 and 2 compute only the 256 x 256 tiles on or above the diagonal of their symmetric results
+    (``tplr_gemm2_syrk``: half the tensor-core work) and ``tplr_sym_axpby`` mirrors the triangle while it applies
+    the line's scalars.  Line 3, ``a X + B X``, is one product ``(B + a I) X``: the mirror kernel of line 2 adds
+    ``a`` on the diagonal, so no element-wise pass over X remains."""
+
+    def __init__(self, M: int, K: int, device):
+        from ..ops import native
+
+        self.M, self.K, self.native = M, K, native
+        z = lambda *shape: torch.empty(*shape, dtype=torch.bfloat16, device=device)       # noqa: E731
+        self.x = [z(M, K), z(M, K)]
+        self.U, self.A, self.B = z(M, M), z(M, M), z(M, M)
+        self.status = OF.status_word(device)
+        self.graph = None
+        self._run()                                    # warm-up outside the capture (first-use set-up of the kernels)
+        torch.cuda.synchronize(device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run()
+        self.graph = g
+
+    def _run(self) -> None:
+        native, L, M, K = self.native, self.native.lib(), self.M, self.K
+        st = self.status.data_ptr()
+        src, dst = self.x
+        for a, b, c in NS_CONSTS:
+            s = native.stream_ptr()
+            native.check(L.tplr_gemm2_syrk(src.data_ptr(), self.U.data_ptr(), M, K, K, M, st, s), "syrk")
+            native.check(L.tplr_sym_axpby(self.U.data_ptr(), M, M, 1.0, None, 0, 0.0, 0.0, self.A.data_ptr(), M, s), "sym_axpby")
+            native.check(L.tplr_gemm2_syrk(self.A.data_ptr(), self.U.data_ptr(), M, M, M, M, st, s), "syrk")   # A A = A A^T
+            native.check(L.tplr_sym_axpby(self.U.data_ptr(), M, M, c, self.A.data_ptr(), M, b, a, self.B.data_ptr(), M, s),
+                         "sym_axpby")
+            OF.gemm(self.B, src, b_mn=True, out=dst)                                      # (B + a I) X
+            src, dst = dst, src
+        self.result = src
+
+    def __call__(self, X: torch.Tensor) -> torch.Tensor:
+        self.x[0].copy_(X)
+        self.graph.replay()
+        return self.result.clone()
+
+
+_chains: dict = {}
+
+
+def _ns_2d_symmetric(X: torch.Tensor) -> torch.Tensor:
+    key = (X.shape[0], X.shape[1], X.device.index, torch.cuda.current_stream(X.device).cuda_stream)
+    chain = _chains.get(key)
+    if chain is None:
+        if len(_chains) >= 32:                          # a model has a handful of matrix shapes; bound the cache anyway
+            _chains.clear()
+        chain = _chains[key] = _SymmetricChain(X.shape[0], X.shape[1], X.device)
+    return chain(X)
 
 
 def _ns_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:

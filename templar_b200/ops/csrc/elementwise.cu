@@ -718,13 +718,13 @@ TPLR_API int tplr_cast_bf16(const float* src, void* dst, long long n, void* stre
 
 // ------------------------------------------------------------------------------------- //
 // Mirror of a symmetric product computed as one triangle, fused with the Newton-Schulz combination:
-//   out[i][j] = alpha * U[i][j] (+ beta * aux[i][j])   where U[i][j] is read at (i, j) when the 256 x 256 tile of
+//   out[i][j] = alpha * U[i][j] (+ beta * aux[i][j]) (+ diag when i == j)   where U[i][j] is read at (i, j) when the 256 x 256 tile of
 //   (i, j) lies on or above the diagonal and at (j, i) otherwise (tplr_gemm2_syrk leaves the lower tiles unwritten).
 // 32 x 32 tiles; a lower tile is the transpose of its mirror tile, staged through shared memory.
 // ------------------------------------------------------------------------------------- //
 __global__ void __launch_bounds__(256) sym_axpby_kernel(const bf16* __restrict__ U, long long ldu, int M, float alpha,
                                                         const bf16* __restrict__ aux, long long ldaux, float beta,
-                                                        bf16* __restrict__ out, long long ldo) {
+                                                        float diag, bf16* __restrict__ out, long long ldo) {
   __shared__ float tile[32][33];
   const int ti = blockIdx.y, tj = blockIdx.x;
   const bool upper = (tj * 32) / 256 >= (ti * 32) / 256;
@@ -743,16 +743,17 @@ __global__ void __launch_bounds__(256) sym_axpby_kernel(const bf16* __restrict__
     if (i >= M || j >= M) continue;
     float v = alpha * (upper ? tile[li][tx] : tile[tx][li]);
     if (aux) v += beta * __bfloat162float(aux[(long long)i * ldaux + j]);
+    if (i == j) v += diag;
     out[(long long)i * ldo + j] = __float2bfloat16(v);
   }
 }
 TPLR_API int tplr_sym_axpby(const void* U, long long ldu, int M, float alpha, const void* aux, long long ldaux, float beta,
-                            void* out, long long ldo, void* stream) {
+                            float diag, void* out, long long ldo, void* stream) {
   TPLR_ENTER();
   if (M <= 0) return 0;
   const unsigned t = (unsigned)((M + 31) / 32);
   sym_axpby_kernel<<<dim3(t, t), 256, 0, (cudaStream_t)stream>>>((const bf16*)U, ldu, M, alpha, (const bf16*)aux, ldaux,
-                                                               beta, (bf16*)out, ldo);
+                                                               beta, diag, (bf16*)out, ldo);
   return (int)cudaGetLastError();
 }
 

@@ -87,7 +87,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_gemm2_gather": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, i, i, i, i, vp, vp, ctypes.c_uint, i, vp, vp],
         "tplr_gemm2_scatter": [vp, vp, i, i, i, ll, ll, i, i, i, i, i, vp, ll, i, vp, vp],
         "tplr_gemm2_syrk": [vp, vp, i, i, ll, ll, vp, vp],
-        "tplr_sym_axpby": [vp, ll, i, f, vp, ll, f, vp, ll, vp],
+        "tplr_sym_axpby": [vp, ll, i, f, vp, ll, f, f, vp, ll, vp],
         "tplr_gemm2_scatter_v": [vp, vp, i, i, i, ll, ll, i, i, i, i, ctypes.POINTER(c_int), vp, vp, vp],
         "tplr_copy_blocks": [vp, i, i, vp],
         "tplr_store_i64": [vp, ll, vp],

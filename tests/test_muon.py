@@ -170,14 +170,15 @@ def test_one_triangle_products_match_full_products_and_fp32():
         out = torch.empty_like(u)
         L, st = native.lib(), OF.status_word(torch.device("cuda")).data_ptr()
         native.check(L.tplr_gemm2_syrk(x.data_ptr(), u.data_ptr(), M, K, K, M, st, native.stream_ptr()), "syrk")
-        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 1.0, None, 0, 0.0, out.data_ptr(), M, native.stream_ptr()), "sym")
+        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 1.0, None, 0, 0.0, 0.0, out.data_ptr(), M, native.stream_ptr()), "sym")
         assert torch.equal(out.triu(256), full.triu(256))                 # tiles above the diagonal: the same numbers
         assert torch.equal(out, out.t()) and torch.isfinite(out.float()).all()
         assert (out.float() - full.float()).abs().max().item() <= 2 ** -7 * full.float().abs().max().item()
         aux = torch.randn_like(out)
-        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 0.5, aux.data_ptr(), M, -2.0, out.data_ptr(), M,
+        native.check(L.tplr_sym_axpby(u.data_ptr(), M, M, 0.5, aux.data_ptr(), M, -2.0, 3.0, out.data_ptr(), M,
                                       native.stream_ptr()), "sym")
-        want = 0.5 * torch.where(torch.ones(M, M, device="cuda").triu().bool(), full.float(), full.float().t()) - 2.0 * aux.float()
+        want = (0.5 * torch.where(torch.ones(M, M, device="cuda").triu().bool(), full.float(), full.float().t())
+                - 2.0 * aux.float() + 3.0 * torch.eye(M, device="cuda"))
         assert (out.float() - want).abs().max().item() < 0.05 * max(want.abs().max().item(), 1.0)
     for shape in [(1024, 1024), (768, 2048), (2048, 512), (520, 1032)]:
         G = torch.randn(*shape, device="cuda")
