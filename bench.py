@@ -49,6 +49,8 @@ def parse():
     ap.add_argument("--gather-buffers", type=int, default=0,
                     help="with --shard-params: block buffers in rotation (>= the number of blocks keeps all gathered; "
                          "0 = all blocks when the bf16 weights are at most 8 GiB, else 2)")
+    ap.add_argument("--gather-engine", default=None, choices=[None, "sm", "dma"],
+                    help="with --shard-params: weight gathers by the copy kernel (sm) or by the copy engines (dma)")
     ap.add_argument("--checkpoint-blocks", action="store_true", help="recompute every block in the backward pass")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--no-e2e", action="store_true")
@@ -148,6 +150,8 @@ def run_ours(a):
     cfg = EngineConfig(topk=a.topk, use_dct=True, outer_update=a.outer_update, max_peers=a.peers,
                        quantize=a.values == "uint8", quant_bins=256, quant_range=6.0, shard_params=a.shard_params,
                        gather_buffers=a.gather_buffers)
+    if a.gather_engine:
+        os.environ["TPLR_GATHER_ENGINE"] = a.gather_engine
     if a.shard_params:
         from templar_b200.models.llama import LlamaModel
         with torch.device("meta"):
@@ -285,7 +289,7 @@ def run_ours(a):
                "h2d_bytes_per_step": int(io[0]), "d2h_bytes_per_step": int(io[1])}
     status = eng.check_status()
     sharding_label = ("bf16 weights, fp32 gradients and all optimizer state sharded; weights gathered per block, "
-                      f"{eng.store.gather.n_buffers} block buffers" if a.shard_params else
+                      f"{eng.store.gather.n_buffers} block buffers, gathers by {eng.store.gather.engine}" if a.shard_params else
                       "single GPU" if world == 1 else
                       "optimizer state, master weights, snapshot and error feedback sharded; bf16 weights and fp32 "
                       "gradients whole on every rank")

@@ -57,12 +57,20 @@ class ParamGather:
     with ``shard_params``."""
 
     def __init__(self, layout, compute_shard: torch.Tensor, *, rank: int, world_size: int, group=None, heap=None,
-                 n_buffers: int = 2, copy_ctas: int = 32):
+                 n_buffers: int = 2, copy_ctas: int = 32, engine: str | None = None):
         self.layout, self.shard = layout, compute_shard
         self.rank, self.world_size, self.group, self.heap = rank, world_size, group, heap
         self.device, self.dtype = compute_shard.device, compute_shard.dtype
         self.cuda = self.device.type == "cuda"
         self.copy_ctas = copy_ctas
+        # who moves the bytes of a gather: "sm" = the block-table copy kernel (one launch per gather, plain loads from
+        # the peers' shards), "dma" = the copy engines (one asynchronous peer copy per piece, no SM and no L2 traffic
+        # of its own beside the GEMMs); TPLR_GATHER_ENGINE overrides
+        import os
+
+        self.engine = engine or os.environ.get("TPLR_GATHER_ENGINE", "sm")
+        if self.engine not in ("sm", "dma"):
+            raise ValueError(f"gather engine must be 'sm' or 'dma', got {self.engine!r}")
         L = layout
         self.names = list(L.groups)                                  # gather groups in storage order
         self.layer_names = [g for g in self.names if g.startswith("layers.")]
@@ -95,9 +103,13 @@ class ParamGather:
         self.gathers = 0                                            # gathers issued (for tests and the bench)
         self.in_backward = False                                    # direction of the pass, for the look-ahead
         self._tables: dict[str, tuple[torch.Tensor, int]] = {}
+        self._copies: dict[str, list] = {}
         if self.cuda:
             for g in self.names:
-                self._tables[g] = self._block_table(g)
+                if self.engine == "dma":
+                    self._copies[g] = self._copy_list(g)
+                else:
+                    self._tables[g] = self._block_table(g)
 
     # -- static description ------------------------------------------------------------------
     def param_view(self, spec) -> torch.Tensor:
@@ -138,6 +150,31 @@ class ParamGather:
         arr = np.array(rec, dtype=np.int64).reshape(-1, 3)
         return torch.from_numpy(arr).to(self.device), len(rec)
 
+    def _copy_list(self, g: str):
+        """[(destination view, source view)] of group ``g``: every rank's piece of every unit; the source views
+        address the peers' shards as mapped into this process."""
+        from .symmetric import _DeviceBlock
+
+        esz = self.shard.element_size()
+        lo, _ = self.range[g]
+        if not hasattr(self, "_peer_shards"):
+            self._peer_shards = []
+            for r in range(self.world_size):
+                if r == self.rank or self.heap is None or self.world_size == 1:
+                    self._peer_shards.append(self.shard)
+                else:
+                    blk = _DeviceBlock(self._peer_base(r), self.shard.numel() * esz)
+                    self._peer_blocks = getattr(self, "_peer_blocks", []) + [blk]
+                    self._peer_shards.append(torch.as_tensor(blk, device=self.device).view(self.dtype))
+        out = []
+        for ui in self.layout.groups[g]:
+            for r, p in enumerate(self.layout.unit_pieces[ui]):
+                if p is None:
+                    continue
+                n = p.g_hi - p.g_lo
+                out.append((self.buf[g][p.g_lo - lo: p.g_lo - lo + n], self._peer_shards[r][p.local: p.local + n]))
+        return out
+
     # -- schedule ------------------------------------------------------------------------------
     def invalidate(self) -> None:
         """The shards changed (optimizer or outer step): nothing gathered so far is current."""
@@ -153,10 +190,14 @@ class ParamGather:
         if self.cuda:
             cur = torch.cuda.current_stream(self.device)
             self.comm.wait_stream(cur)
-            table, n = self._tables[g]
             with torch.cuda.stream(self.comm):
-                native.check(native.lib().tplr_copy_blocks(table.data_ptr(), n, self.copy_ctas,
-                                                           self.comm.cuda_stream), "copy_blocks")
+                if self.engine == "dma":
+                    for dst, src in self._copies[g]:
+                        dst.data.copy_(src, non_blocking=True)      # `.data`: no version bump on views autograd holds
+                else:
+                    table, n = self._tables[g]
+                    native.check(native.lib().tplr_copy_blocks(table.data_ptr(), n, self.copy_ctas,
+                                                               self.comm.cuda_stream), "copy_blocks")
                 ev = torch.cuda.Event()
                 ev.record(self.comm)
             self.ready[slot] = ev

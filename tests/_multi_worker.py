@@ -145,7 +145,9 @@ def main():
     def local_view(engine, vec):
         return torch.cat([vec[p.local: p.local + (p.g_hi - p.g_lo)] for p in engine.layout.pieces(engine.rank)])
 
-    for tag, extra in (("f", {}), ("fq", {"quantize": True, "quant_bins": 256}), ("fk", {"gather_buffers": 8})):
+    for tag, extra in (("f", {"gather_buffers": 2}), ("fq", {"quantize": True, "quant_bins": 256}), ("fk", {"gather_buffers": 8}),
+                       ("fd", {"gather_buffers": 2})):
+        os.environ["TPLR_GATHER_ENGINE"] = "dma" if tag == "fd" else "sm"     # fd: gathers by the copy engines
         fcfg = dataclasses.replace(cfg, shard_params=True, **extra)
         fmodel = build_model(args, device=dev, dtype=torch.bfloat16, seed=5)
         fmodel.activation_checkpointing = tag == "fk"

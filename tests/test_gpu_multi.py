@@ -48,7 +48,7 @@ def test_two_rank_runtime_and_window():
         assert r["m_mean_diff"] < 0.1 * r["m_moved_mean"] and r["m_max_diff"] < 0.1, r
         # sharded parameters: same weights and error feedback as one rank with the whole batch, up to the order of
         # the fp32 reduce-adds and the bf16 roundings of two pipelines; no full-size weight or gradient buffer
-        for tag in ("f", "fq", "fk"):
+        for tag in ("f", "fq", "fk", "fd"):
             assert r[tag + "_status"] == 0 and r[tag + "_no_full_buffers"], (tag, r)
             assert r[tag + "_moved"] > 1e-4, (tag, r)
             assert r[tag + "_master_max_diff"] < 2e-3 * max(r[tag + "_scale"], 1.0), (tag, r)
