@@ -751,6 +751,57 @@ class Validator(BaseNode, Trainer):
         self.staged_peers = n                       # slot j holds uids[j]: the overlap check reads the slots
         return n
 
+    # -- the reference's per-peer evaluation API on top of the engine ---------------------------------------- #
+    def _save_model_state(self):
+        """Remember the weights that the per-peer applies start from (reference neurons/validator.py:274-288: a copy
+        of the local shards on the host).  Here the engine's window snapshot is that state and stays on the device."""
+        self.engine.snapshot()
+        return "engine-snapshot"
+
+    def _restore_model_state(self, state=None) -> None:
+        """Back to the saved weights (reference neurons/validator.py:290-302)."""
+        self.engine.restore()
+
+    def update_model_with_gradient(self, model, eval_uid: int, eval_state_dict: dict, clip_norm_dict=None) -> None:
+        """Apply one peer's payload alone, scaled by ``lr * eval_lr_factor``, its values clipped per tensor to the
+        median norm of the gathered peers (reference neurons/validator.py:3563-3738).  ``clip_norm_dict``: the
+        per-tensor medians as a ``[n_params]`` tensor (:meth:`compute_peer_val_norms`) or the reference's
+        ``{name + "vals": norm}`` dict.  Raises ``ValueError`` for a payload that does not decode to finite values."""
+        eng = self.engine
+        median = clip_norm_dict
+        if isinstance(clip_norm_dict, dict):
+            median = torch.full((eng.layout.n_params,), float("inf"), device=eng.device)
+            for sp in eng.layout.specs:
+                if sp.name + "vals" in clip_norm_dict:
+                    median[sp.index] = float(clip_norm_dict[sp.name + "vals"])
+        slot = eng.cfg.max_peers - 1
+        eng.stage_single_peer(eval_state_dict if self.is_master else None, slot)
+        eng.apply_single_peer(slot, self.lr * getattr(self.hparams, "eval_lr_factor", 1.0), median)
+        bad = bool(eng.check_status() & 3)             # bad index / non-finite value met while decoding the payload
+        bad = dist_helper.any_ok(bad, self.device, "eval_payload_bad")    # every rank decodes its own chunks: agree
+        if bad:
+            eng.restore()
+            raise ValueError(f"Invalid gradient from peer {eval_uid}: payload did not decode to finite values")
+
+    def log_sync_score(self, eval_uid: int, sync_result: dict) -> None:
+        """``validator_sync_score`` measurement and the wandb series of one peer (reference neurons/validator.py:
+        851-903)."""
+        keys = ("l2_norm", "avg_l2_norm", "avg_abs_diff", "max_diff", "avg_steps_behind",
+                "interquartile_mean_steps_behind", "max_steps_behind")
+        vals = {k: float(sync_result.get(k, 99.0)) for k in keys}
+        tplr.log_with_context(level="info", message=f"Sync average steps behind: {vals['avg_steps_behind']:.3f}, "
+                              f"interquartile mean: {vals['interquartile_mean_steps_behind']:.3f}",
+                              sync_window=self.sync_window, current_window=self.current_window, eval_uid=eval_uid)
+        if not self.is_master:
+            return
+        if self.wandb is not None:
+            names = {"max_diff": "sync_max_diff"}
+            self.wandb.log({f"validator/sync/{names.get(k, k)}/{eval_uid}": v for k, v in vals.items()}, step=self.global_step)
+        if self.metrics_logger is not None:
+            self.metrics_logger.log("validator_sync_score",
+                                    tags={"uid": str(eval_uid), "window": int(self.sync_window),
+                                          "global_step": int(self.global_step)}, fields=vals)
+
     async def fetch_eval_gradient(self, uid: int, time_min, time_max) -> dict | None:
         """Master only: the upload of the uid that is about to be scored, fetched from the uid's own bucket with
         the window's acceptance times, checked like a gathered payload and against the data the uid was assigned.
@@ -816,7 +867,6 @@ class Validator(BaseNode, Trainer):
         lb_rand_sum, lb_rand_n = await self.evaluate_model(self.model, self.loader)
         loss_before_random = lb_rand_sum / max(lb_rand_n, 1)
         out = []
-        lr_eval = self.lr * getattr(hp, "eval_lr_factor", 1.0)
         eval_window = self.current_window
         for uid in uids:
             t0 = time.time()
@@ -835,11 +885,15 @@ class Validator(BaseNode, Trainer):
                 break
             if not bool(flags[0].item()):
                 continue
-            eng.stage_single_peer(state, eval_slot)
             self.sampler.set_window_uid(uid, self.sync_window)
             s, n = await self.evaluate_model(self.model, self.loader)
             loss_before_own = s / max(n, 1)
-            eng.apply_single_peer(eval_slot, lr_eval, median)
+            try:
+                self.update_model_with_gradient(self.model, uid, state, median)
+            except ValueError as e:                      # decoded to non-finite values: every rank sees the same status
+                if self.is_master:
+                    self.slash_for_invalid_gradient(uid, e)
+                continue
             s, n = await self.evaluate_model(self.model, self.loader)
             loss_after_own = s / max(n, 1)
             self.sampler.set_window_uid(random_seed, self.sync_window)
@@ -859,6 +913,7 @@ class Validator(BaseNode, Trainer):
                 self.binary_moving_averages[uid] = (1 - a) * self.binary_moving_averages[uid] + a * self.binary_indicator_scores[uid]
                 sync = await self.evaluate_miner_sync(uid)
                 self.sync_scores[uid] = float(sync.get("sync_score", 0.0))
+                self.log_sync_score(uid, sync)
             self.evaluated_uids.add(uid)
             self.peers_last_eval_window[uid] = self.sync_window
             out.append({"uid": uid, "gradient_score": float(score), "loss_before_own": loss_before_own,
