@@ -146,11 +146,6 @@ class Trainer:
         want = bool(tt.get("shard_params", False) if isinstance(tt, dict) else getattr(tt, "shard_params", False))
         if not want:
             return False
-        kind, _, _ = _opt_cfg(self.hparams)
-        if kind == "muon":
-            tplr.logger.warning("torchtitan.shard_params is ignored with the Muon inner optimizer (it needs whole gradient "
-                                "matrices on a rank); optimizer state stays sharded")
-            return False
         if torch.device(self.device).type == "cuda" and self.world_size > 1 and heap is None:
             raise ValueError("torchtitan.shard_params on several GPUs needs the symmetric heap")
         return True

@@ -90,9 +90,6 @@ class WindowEngine:
                 return torch.zeros(n, dtype=dtype, device=self.device)
         self.status = OF.status_word(self.device) if self.cuda else torch.zeros(1, dtype=torch.int32)
         self.fsdp = bool(cfg.shard_params)
-        if self.fsdp and cfg.inner_optimizer == "muon":
-            raise NotImplementedError("shard_params with the Muon inner optimizer: the engine's Muon step needs whole "
-                                      "gradient matrices on a rank; run Muon without shard_params")
         if self.fsdp and self.cuda and world_size > 1 and heap is None:
             raise ValueError("shard_params on CUDA with several ranks needs the symmetric heap (peer-memory gathers)")
         self.store = FlatParamStore(model, compute_dtype=compute_dtype, device=self.device,
@@ -212,7 +209,7 @@ class WindowEngine:
         lr = cfg.inner_lr if lr is None else lr
         self.adam_step += 1
         if self.fsdp:
-            return self._optimizer_step_sharded(lr)
+            return self._muon_step_sharded(lr) if cfg.inner_optimizer == "muon" else self._optimizer_step_sharded(lr)
         if self.world_size > 1:
             self._reduce_grads()
         if cfg.inner_optimizer == "muon":
@@ -312,6 +309,135 @@ class WindowEngine:
         st.gather.invalidate()
         self._barrier()
         self._mark("opt.barrier_after_zero")
+
+    # -- Muon on sharded parameters ---------------------------------------------------------------------- #
+    def _reduce_staged(self) -> None:
+        """Staged gradients (embedding rows, norm weights; on CPU everything) into the owners' gradient shards."""
+        st = self.store
+        if not self.cuda:
+            return self._reduce_staged_cpu()
+        table, n_rec = self._grad_stage_table
+        if n_rec:
+            stages = ([self.heap.peer_ptr(st.stage, r) for r in range(self.world_size)]
+                      if (self.heap is not None and self.world_size > 1) else [st.stage.data_ptr()])
+            native.check(native.lib().tplr_reduce_blocks(native.ptr_array(stages), len(stages), table.data_ptr(), n_rec,
+                                                         st.grad_shard.data_ptr(), native.stream_ptr()), "reduce_blocks")
+
+    def _matrix_tables(self):
+        """Per orthogonalised matrix: its owner rank (round-robin, as the reference's sharded Muon assigns them,
+        src/tplr/muon/muon_fsdp2.py:319-343) and every rank's rows of it as (rank, first element in the matrix,
+        elements, offset in that rank's shard arrays)."""
+        if getattr(self, "_muon_tables", None) is None:
+            out, k = [], 0
+            for sp in self.layout.specs:
+                if self.muon_class(sp.name, len(sp.shape)) != "muon":
+                    continue
+                parts = []
+                for r in range(self.world_size):
+                    for s2, a, b, la in self.layout.segments(r):
+                        if s2 is sp:
+                            parts.append((r, a - sp.offset, b - a, la))
+                out.append((sp, k % self.world_size, parts))
+                k += 1
+            self._muon_tables = out
+        return self._muon_tables
+
+    def _move_rows(self, parts, full: torch.Tensor, to_full: bool) -> None:
+        """CUDA: rows of one matrix between the ranks' gradient shards (peer memory) and ``full`` on this rank."""
+        st = self.store
+        rec = []
+        for r, off, n, la in parts:
+            base = (self.heap.peer_ptr(st.grad_shard, r) if (self.heap is not None and self.world_size > 1)
+                    else st.grad_shard.data_ptr()) + la * 4
+            mine = full.data_ptr() + off * 4
+            for o in range(0, n * 4, 1 << 20):
+                m = min(1 << 20, n * 4 - o)
+                rec.append((base + o, mine + o, m) if to_full else (mine + o, base + o, m))
+        table = torch.tensor(rec, dtype=torch.int64, device=self.device)
+        native.check(native.lib().tplr_copy_blocks(table.data_ptr(), len(rec), 0, native.stream_ptr()), "copy_blocks")
+        self._keep_alive.append(table)
+
+    @torch.no_grad()
+    def _muon_step_sharded(self, lr: float) -> None:
+        """Muon on sharded parameters.  Momentum and the Nesterov blend are element-wise and run on the shards; the
+        blended direction of every hidden matrix is then collected on that matrix's owner rank (matrices are dealt
+        round-robin), orthogonalised there (Newton-Schulz on the own GEMM) and its rows are sent back to the ranks
+        that hold them, which apply them to their master shards.  Embeddings, the head and vectors get Adam, as in
+        :meth:`_muon_step`.  The reference does the same with ``dist.gather`` / ``dist.scatter`` per matrix
+        (src/tplr/muon/muon_fsdp2.py:77-158); here the rows move over peer memory between two barriers."""
+        from ..muon.muon import adam_update
+        from ..muon.newton_schulz import newton_schulz
+
+        cfg, st = self.cfg, self.store
+        n = st.n_shard
+        self._barrier()                                     # every rank's backward pass (remote adds) is complete
+        self._reduce_staged()
+        g = st.grad_shard[:n]
+        g.mul_(1.0 / self.world_size)
+        self.gnorm_sq.copy_((g * g).sum().reshape(1))
+        if self.world_size > 1:
+            dist.all_reduce(self.gnorm_sq, group=self.group)
+        if cfg.max_grad_norm > 0:
+            g.mul_(torch.clamp(cfg.max_grad_norm / (self.gnorm_sq.sqrt() + 1e-6), max=1.0))
+        beta = cfg.muon_momentum
+        segs = [(sp, self.muon_class(sp.name, len(sp.shape)), a, b, la) for sp, a, b, la in self.layout.segments(self.rank)]
+        for sp, cls, a, b, la in segs:
+            if cls != "muon":
+                continue
+            gs, ms = g[la: la + (b - a)], self.exp_avg[la: la + (b - a)]
+            ms.lerp_(gs, 1 - beta)
+            if cfg.muon_nesterov:
+                gs.lerp_(ms, beta)
+            else:
+                gs.copy_(ms)
+        self._barrier()                                     # every rank's directions are in its gradient shard
+        self._keep_alive = []
+        for sp, owner, parts in self._matrix_tables():
+            shape = (sp.shape[0], sp.numel // sp.shape[0])
+            if self.cuda:
+                if owner != self.rank:
+                    continue
+                full = torch.empty(shape, dtype=torch.float32, device=self.device)
+                self._move_rows(parts, full, to_full=True)
+                o = (newton_schulz(full).float() * max(1.0, shape[0] / shape[1]) ** 0.5).contiguous()
+                self._move_rows(parts, o, to_full=False)
+            else:
+                # gloo: every rank rebuilds the matrix from broadcasts and orthogonalises it (tiny test models)
+                full = torch.zeros(shape, dtype=torch.float32)
+                flat = full.view(-1)
+                for r, off, cnt, la in parts:
+                    piece = flat[off: off + cnt]
+                    if r == self.rank:
+                        piece.copy_(g[la: la + cnt])
+                    if self.world_size > 1:
+                        dist.broadcast(piece, src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                                       group=self.group)
+                o = (newton_schulz(full).float() * max(1.0, shape[0] / shape[1]) ** 0.5).reshape(-1)
+                for r, off, cnt, la in parts:
+                    if r == self.rank:
+                        g[la: la + cnt].copy_(o[off: off + cnt])
+        self._barrier()                                     # the orthogonalised rows have arrived
+        self._keep_alive = []
+        scale = dict(cfg.muon_aux_lr_scale)
+        for sp, cls, a, b, la in segs:
+            p = st.master_shard[la: la + (b - a)]
+            if cls == "muon":
+                p.mul_(1 - lr * cfg.muon_weight_decay)
+                p.add_(g[la: la + (b - a)], alpha=-lr)
+            else:
+                upd = adam_update(g[la: la + (b - a)], self.exp_avg[la: la + (b - a)], self.exp_avg_sq[la: la + (b - a)],
+                                  self.adam_step, cfg.betas, cfg.eps)
+                lr_c = lr * scale.get(cls, 1.0)
+                p.mul_(1 - lr_c * cfg.weight_decay)
+                p.add_(upd, alpha=-lr_c)
+        if self.cuda:
+            native.check(native.lib().tplr_cast_bf16(st.master_shard.data_ptr(), st.compute_shard.data_ptr(), n,
+                                                     native.stream_ptr()), "cast_bf16")
+        else:
+            st.compute_shard[:n].copy_(st.master_shard.to(st.compute_dtype))
+        st.zero_grad()
+        st.gather.invalidate()
+        self._barrier()
 
     def _reduce_staged_cpu(self) -> None:
         """CPU / gloo: every tensor's gradient was accumulated locally in full size (``stage``); the parts that a

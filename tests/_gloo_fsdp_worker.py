@@ -15,11 +15,12 @@ from templar_b200.parallel.window_engine import EngineConfig, WindowEngine  # no
 from templar_b200.utils.synthetic import synthetic_payload  # noqa: E402
 
 
-def run(rank, world, shard_params, ckpt=False, quantize=False):
+def run(rank, world, shard_params, ckpt=False, quantize=False, muon=False):
     args = ModelArgs(dim=128, n_layers=3, n_heads=2, vocab_size=256, intermediate_size=256, max_seq_len=32)
     model = build_model(args, seed=3)
     model.activation_checkpointing = ckpt
-    eng = WindowEngine(model, EngineConfig(shard_params=shard_params, max_peers=2, quantize=quantize), rank=rank,
+    extra = dict(inner_optimizer="muon", inner_lr=0.02, muon_momentum=0.9) if muon else {}
+    eng = WindowEngine(model, EngineConfig(shard_params=shard_params, max_peers=2, quantize=quantize, **extra), rank=rank,
                        world_size=world)
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, 256, (2, 2, 2, world, 2, 33), generator=g)       # [window, step, micro, rank, batch, seq + 1]
@@ -61,6 +62,11 @@ def main():
     l, s, _ = run(rank, world, True, quantize=True)
     out["fsdp_quant"] = {"loss": max(abs(a - b) for a, b in zip(l, ql)),
                          "weights": max(float((s[k] - qs[k]).abs().max()) for k in qs)}
+    ml, ms, _ = run(rank, world, False, muon=True)
+    l, s, _ = run(rank, world, True, muon=True)
+    out["fsdp_muon"] = {"loss": max(abs(a - b) for a, b in zip(l, ml)),
+                        "weights": max(float((s[k] - ms[k]).abs().max()) for k in ms),
+                        "vs_adamw": max(float((ms[k] - ref_s[k]).abs().max()) for k in ms)}
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

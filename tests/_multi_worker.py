@@ -146,7 +146,7 @@ def main():
         return torch.cat([vec[p.local: p.local + (p.g_hi - p.g_lo)] for p in engine.layout.pieces(engine.rank)])
 
     for tag, extra in (("f", {"gather_buffers": 2}), ("fq", {"quantize": True, "quant_bins": 256}), ("fk", {"gather_buffers": 8}),
-                       ("fd", {"gather_buffers": 2})):
+                       ("fd", {"gather_buffers": 2}), ("fm", {"inner_optimizer": "muon", "inner_lr": 0.02})):
         os.environ["TPLR_GATHER_ENGINE"] = "dma" if tag == "fd" else "sm"     # fd: gathers by the copy engines
         fcfg = dataclasses.replace(cfg, shard_params=True, **extra)
         fmodel = build_model(args, device=dev, dtype=torch.bfloat16, seed=5)
@@ -165,6 +165,9 @@ def main():
         out[tag + "_ef_scale"] = fref.ef.abs().max().item()
         out[tag + "_scale"] = fref.store.master_shard.abs().max().item()
         out[tag + "_moved"] = (fref.store.master_shard - fref.theta0).abs().max().item()
+        out[tag + "_master_mean_diff"] = (local_view(feng, feng.store.master_shard)
+                                          - shard_view(feng, fref.store.master_shard)).abs().mean().item()
+        out[tag + "_moved_mean"] = (fref.store.master_shard - fref.theta0).abs().mean().item()
         out[tag + "_gathers"] = feng.store.gather.gathers
         out[tag + "_no_full_buffers"] = feng.store.compute is None and feng.store.grad is None
         t = toks[0, 0].to(dev)

@@ -110,3 +110,5 @@ def test_two_rank_sharded_parameters_match_whole_weights_engine():
             assert r[tag]["moved"] > 1e-5 and r[tag]["full_buffers"], r
             assert r[tag]["shard_elems"] < 0.51 * r[tag]["total"] + 4096, r
         assert r["fsdp_quant"]["loss"] < 1e-6 and r["fsdp_quant"]["weights"] < 1e-6, r
+        # Muon on sharded parameters: every matrix collected on its owner, orthogonalised, rows sent back
+        assert r["fsdp_muon"]["loss"] < 1e-5 and r["fsdp_muon"]["weights"] < 1e-5 and r["fsdp_muon"]["vs_adamw"] > 1e-4, r
