@@ -140,10 +140,8 @@ class Miner(BaseNode, Trainer):
         self.init_model(meta=False)
         self.model_initialized = True
         heap = None
-        if self.world_size > 1 and self.device.type == "cuda":
-            from templar_b200.parallel.symmetric import SymmetricHeap
-
-            heap = SymmetricHeap.create(self.device, self.rank, self.world_size)
+        if self.world_size > 1:
+            heap = self.make_heap()
         elif self.group_world > 1 and self.device.type == "cuda":
             from templar_b200.parallel.symmetric import SymmetricHeap
 

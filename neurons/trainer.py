@@ -110,9 +110,48 @@ class Trainer:
         self.expected_compressed_params = self.get_expected_params()
         self.tokenizer = self.hparams.tokenizer
 
-    def attach_engine(self, heap=None, max_peers: int | None = None) -> WindowEngine:
+    def engine_topology(self, validator: bool = False) -> dict:
+        """Which ranks share one copy of the sharded state and which ranks are replicas of each other.
+
+        ``torchtitan.dp_replicate = R`` on a miner (the reference's DDP setting, src/tplr/model_factory.py:139-160,
+        and with ``world_size / R > 1`` ranks per copy the hybrid layout torchtitan calls HSDP) cuts the node's
+        ranks into R copies of ``world_size / R`` consecutive ranks: the state is sharded inside a copy (peer
+        memory of that copy's symmetric heap) and the gradient shards are summed over the copies with one
+        all-reduce per inner step.  Everything else, and every validator, is one copy over all ranks: on one
+        NVSwitch box every peer is equally near, so a second copy of the state buys nothing there.
+        Collective: every rank creates every group."""
+        if getattr(self, "_engine_topology", None) is not None:
+            return self._engine_topology
+        tt = getattr(self.hparams, "torchtitan", None)
+        replicas = int((tt.get("dp_replicate", 1) if isinstance(tt, dict) else getattr(tt, "dp_replicate", 1)) or 1)
+        world = self.world_size
+        topo = dict(shard_rank=self.rank, shard_world=world, shard_group=None, replicate_group=None, replicas=1)
+        if not validator and replicas > 1 and world > 1:
+            if world % replicas:
+                raise ValueError(f"World size ({world}) must be divisible by torchtitan.dp_replicate ({replicas})")
+            per = world // replicas
+            shard_groups = [dist.new_group(list(range(r * per, (r + 1) * per))) for r in range(replicas)]
+            replicate_groups = [dist.new_group(list(range(s, world, per))) for s in range(per)]
+            topo = dict(shard_rank=self.rank % per, shard_world=per,
+                        shard_group=shard_groups[self.rank // per] if per > 1 else None,
+                        replicate_group=replicate_groups[self.rank % per], replicas=replicas)
+        self._engine_topology = topo
+        return topo
+
+    def make_heap(self, validator: bool = False, timeout_s: float = 30.0):
+        """The symmetric heap of this rank's copy of the sharded state (None on CPU or for a copy of one rank)."""
+        topo = self.engine_topology(validator)
+        if topo["shard_world"] <= 1 or torch.device(self.device).type != "cuda":
+            return None
+        from templar_b200.parallel.symmetric import SymmetricHeap
+
+        return SymmetricHeap.create(self.device, topo["shard_rank"], topo["shard_world"], group=topo["shard_group"],
+                                    timeout_s=timeout_s)
+
+    def attach_engine(self, heap=None, max_peers: int | None = None, validator: bool = False) -> WindowEngine:
         """Put the (materialised) model on the flat store and the fused per-window kernels."""
         hp = self.hparams
+        topo = self.engine_topology(validator)
         kind, spec, _ = _opt_cfg(hp)
         adam = (getattr(hp, "optimizer", {}) or {}).get("adamw", {}) or {}
         kw = dict(
@@ -127,7 +166,7 @@ class Trainer:
             # whole tensor, so a sharded CUDA engine needs the symmetric heap for it (the CPU path merges the
             # payload with a collective)
             quantize=bool(getattr(hp, "payload_quantization", False))
-            and (self.world_size == 1 or heap is not None or torch.device(self.device).type == "cpu"),
+            and (topo["shard_world"] == 1 or heap is not None or torch.device(self.device).type == "cpu"),
             quant_bins=min(int(getattr(hp, "quantization_bins", 256)), 256),
             quant_range=float(getattr(hp, "quantization_range", 6)),
             # torchtitan.shard_params: bf16 weights and fp32 gradients held as shards too (what the reference's
@@ -138,7 +177,9 @@ class Trainer:
                                             else getattr(tt, "gather_buffers", 0)) or 0)(getattr(hp, "torchtitan", None))))
         kw.update(self._muon_engine_args(kind, spec))
         cfg = EngineConfig(**kw)
-        self.engine = WindowEngine(self.model, cfg, device=self.device, rank=self.rank, world_size=self.world_size, heap=heap)
+        self.engine = WindowEngine(self.model, cfg, device=self.device, rank=topo["shard_rank"],
+                                   world_size=topo["shard_world"], group=topo["shard_group"], heap=heap,
+                                   replicate_group=topo["replicate_group"], replicate_size=topo["replicas"])
         return self.engine
 
     def _shard_params(self, heap) -> bool:
@@ -146,7 +187,7 @@ class Trainer:
         want = bool(tt.get("shard_params", False) if isinstance(tt, dict) else getattr(tt, "shard_params", False))
         if not want:
             return False
-        if torch.device(self.device).type == "cuda" and self.world_size > 1 and heap is None:
+        if torch.device(self.device).type == "cuda" and self.engine_topology()["shard_world"] > 1 and heap is None:
             raise ValueError("torchtitan.shard_params on several GPUs needs the symmetric heap")
         return True
 

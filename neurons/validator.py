@@ -84,13 +84,9 @@ class Validator(BaseNode, Trainer):
         self.uid = self.metagraph.hotkeys.index(hotkey)
         self.init_model(validator=False, meta=False)
         self.model_initialized = True
-        heap = None
-        if self.world_size > 1 and self.device.type == "cuda":
-            from templar_b200.parallel.symmetric import SymmetricHeap
-
-            heap = SymmetricHeap.create(self.device, self.rank, self.world_size)
+        heap = self.make_heap(validator=True)
         # one payload slot more than the largest gather: the uid under evaluation is staged beside the gathered peers
-        self.attach_engine(heap=heap, max_peers=int(getattr(self.hparams, "gather_peer_count", 8))
+        self.attach_engine(heap=heap, validator=True, max_peers=int(getattr(self.hparams, "gather_peer_count", 8))
                            + int(getattr(self.hparams, "reserve_peer_count", 0)) + 1)
         self.transformer = tplr.compress.ChunkingTransformer(self.model, target_chunk=self.hparams.target_chunk)
         self.compressor = tplr.compress.TopKCompressor(use_quantization=False)

@@ -162,7 +162,7 @@ def _prepare_gradient_dict_engine(miner, engine, step_window: int, null_round: b
             engine._barrier()
     gradient, xshapes, totalks = {}, {}, {}
     L = engine.layout
-    want_payload = engine.rank == 0
+    want_payload = engine.rank == 0 and engine.replica == 0        # the replicas hold the same payload
     quant = None
     if want_payload:
         idx_host = _to_host_async(engine.own_idx)
@@ -301,18 +301,24 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
     n_peers = min(n_peers, engine.cfg.max_peers)
     # co-located peers (gather_result.local_ranks): read from the owners' GPU memory, nothing to stage
     local = sorted((getattr(gather_result, "local_ranks", None) or {}).values()) if gather_result is not None else []
-    if engine.world_size > 1:
+    if engine.dp_size > 1:
         t = torch.tensor([n_peers], device=engine.device, dtype=torch.int32)
         dist.broadcast(t, 0)
         n_peers = int(t.item())
     if n_peers == 0 and not local:
         return None
+    leader = engine.rank == 0                        # the rank of a copy of the state that stages the payloads
+    if engine.replicate_size > 1 and leader:
+        # the gathered payloads are on the master rank: hand them to the leader of every other copy
+        box = [sd if engine.replica == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(engine.replicate_group, 0), group=engine.replicate_group)
+        sd = box[0]
     if engine.world_size == 1:
         for j in range(n_peers):
             from .parallel.window_engine import peer_slice
             engine.load_peer_payload(j, peer_slice(sd, j))
     else:
-        engine.distribute_peer_payloads(sd if is_master else None, n_peers)
+        engine.distribute_peer_payloads(sd if leader else None, n_peers)
     if not engine.window_open:
         engine.snapshot()           # catch-up / validator flow: apply to the current weights
     with phase("Outer Step"):

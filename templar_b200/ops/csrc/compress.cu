@@ -24,6 +24,13 @@
 // src/tplr/neurons.py:138-173 (error feedback), :342-450 (outer step).
 #include "tcgen05.cuh"
 
+#include <atomic>
+
+// Switches of the tensor-core compress / aggregate kernels, for comparison runs (tplr_compress_set_variant):
+// bit 0 candidate threshold search instead of the radix select, bit 1 L2 prefetch of the next chunk pair in the
+// compress kernel, bit 2 payload entries fetched one pair ahead in the aggregate kernel.  Default: all on.
+static std::atomic<int> g_tc_variant{7};
+
 #define NT 256
 #define LD 64
 
@@ -92,6 +99,7 @@ struct CompressArgs {
   int n_desc, total_chunks;
   float gamma;
   int use_dct, delta_mode, null_round, write_residual, distinct;
+  int variant;              // tensor-core kernel: bit 0 candidate threshold search, bit 1 L2 prefetch of the next pair
 };
 
 __global__ void __launch_bounds__(NT, 2) compress_kernel(const CompressArgs a) {
@@ -315,7 +323,7 @@ TPLR_API int tplr_compress_chunks(const void* descs, int n_desc, int total_chunk
   a.descs = (const TplrParamDesc*)descs; a.basis = basis; a.ef = ef; a.theta0 = theta0; a.theta = theta;
   a.idx_out = idx_out; a.val_out = val_out; a.status = status; a.n_desc = n_desc;
   a.total_chunks = total_chunks; a.gamma = gamma; a.use_dct = use_dct; a.delta_mode = delta_mode;
-  a.null_round = null_round; a.write_residual = write_residual; a.distinct = distinct;
+  a.null_round = null_round; a.write_residual = write_residual; a.distinct = distinct; a.variant = 0;
   const int smem = (distinct ? 7 : 5) * TPLR_TILE_ELEMS * (int)sizeof(float);
   cudaError_t err = cudaFuncSetAttribute(compress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return (int)err;
@@ -440,6 +448,7 @@ struct AggArgs {
   int n_desc, total_chunks, n_peers, n_params, n_bins;
   float lr, weight_decay;
   int use_dct, update_mode, val_dtype, distinct;
+  int variant;              // tensor-core kernel: bit 2 payload entries of the next pair fetched one pair ahead
   PeerPtrs pp;
 };
 
@@ -574,7 +583,7 @@ TPLR_API int tplr_aggregate_apply(const void* descs, int n_desc, int total_chunk
   a.theta0 = theta0; a.theta = theta; a.theta_bf16 = (__nv_bfloat16*)theta_bf16; a.grad_out = grad_out;
   a.status = status; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_peers = n_peers;
   a.n_params = n_params; a.n_bins = n_bins; a.lr = lr; a.weight_decay = weight_decay; a.use_dct = use_dct;
-  a.update_mode = update_mode; a.val_dtype = val_dtype; a.distinct = distinct;
+  a.update_mode = update_mode; a.val_dtype = val_dtype; a.distinct = distinct; a.variant = 0;
   for (int i = 0; i < n_peers; ++i) { a.pp.idx[i] = (const uint8_t*)idx_ptrs[i]; a.pp.val[i] = val_ptrs[i]; }
   const int smem = (distinct ? 5 : 4) * TPLR_TILE_ELEMS * (int)sizeof(float);
   cudaError_t err = cudaFuncSetAttribute(aggregate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -690,6 +699,8 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ TplrParamDesc s_desc[2];
+  __shared__ long long s_gbase[2];                                 // element offset of each chunk of the pair, -1: none
+  __shared__ int s_cols[2], s_skip[2];
   float* S = reinterpret_cast<float*>(smem);                       // [2][4096] sums, later the A tiles
   int* Cnt = reinterpret_cast<int*>(smem + 2 * 4096 * 4);          // [2][4096] contributor counts
   const uint32_t sA = smem_u32(smem), sB = sA + TC_ACC_BYTES;
@@ -720,6 +731,50 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
   bool ok = true;
   TplrParamDesc d = a.descs[0];
 
+  // One pair ahead: thread t owns scatter task t of a pair (chunk of the pair, peer, index pair) and holds
+  // that task's raw bytes for the NEXT pair in registers, so the dependent chain packed index -> value ->
+  // table entry of a pair is already under way while the previous pair is in the tensor cores.  The loaded
+  // registers are not touched before the scatter that consumes them.  Tasks beyond the first NT of a pair
+  // (more than 8 peers at k = 32) are fetched in line as before.
+  const bool ahead = (a.variant & 4) != 0;
+  const int pf_pairs = max(1, d.k / 2), pf_per = max(1, a.n_peers) * pf_pairs;
+  const int pf_c2 = tid / pf_per, pf_rem = tid - pf_c2 * pf_per;
+  const int pf_peer = pf_rem / pf_pairs, pf_pr = pf_rem - pf_peer * pf_pairs;
+  int pf_begin = d.chunk_begin, pf_n = d.n_chunks, pf_param = d.param_id;     // cached descriptor fields of the task's tensor
+  long long pf_idx_off = d.idx_off, pf_val_off = d.val_off;
+  unsigned pf_b0 = 0, pf_b1 = 0, pf_b2 = 0, pf_r0 = 0, pf_r1 = 0;
+  float pf_sc = 1.f;
+  bool pf_valid = false;
+  auto fetch_ahead = [&](int qq) {
+    pf_valid = false;
+    if (!ahead || tid >= 2 * pf_per || qq >= n_pairs) return;
+    const int cc = 2 * qq + pf_c2;
+    if (cc >= a.total_chunks) return;
+    if (!(cc >= pf_begin && cc < pf_begin + pf_n)) {
+      const TplrParamDesc& dn = a.descs[find_desc(a.descs, a.n_desc, cc)];
+      pf_begin = dn.chunk_begin; pf_n = dn.n_chunks; pf_param = dn.param_id;
+      pf_idx_off = dn.idx_off; pf_val_off = dn.val_off;
+    }
+    if (a.skip && a.skip[pf_param]) return;
+    const int cl2 = cc - pf_begin;
+    const uint8_t* ip = a.pp.idx[pf_peer] + pf_idx_off + ((long long)cl2 * pf_pairs + pf_pr) * 3;
+    const long long vo = pf_val_off + (long long)cl2 * (2 * pf_pairs) + 2 * pf_pr;
+    pf_b0 = ip[0]; pf_b1 = ip[1]; pf_b2 = ip[2];
+    if (a.val_dtype == 0) {
+      pf_r0 = __float_as_uint(reinterpret_cast<const float*>(a.pp.val[pf_peer])[vo]);
+      pf_r1 = __float_as_uint(reinterpret_cast<const float*>(a.pp.val[pf_peer])[vo + 1]);
+    } else if (a.val_dtype == 1) {
+      pf_r0 = reinterpret_cast<const unsigned short*>(a.pp.val[pf_peer])[vo];
+      pf_r1 = reinterpret_cast<const unsigned short*>(a.pp.val[pf_peer])[vo + 1];
+    } else {
+      pf_r0 = reinterpret_cast<const uint8_t*>(a.pp.val[pf_peer])[vo];
+      pf_r1 = reinterpret_cast<const uint8_t*>(a.pp.val[pf_peer])[vo + 1];
+    }
+    pf_sc = a.clip ? a.clip[(long long)pf_peer * a.n_params + pf_param] : 1.f;
+    pf_valid = true;
+  };
+  fetch_ahead(blockIdx.x);
+
   for (int q = blockIdx.x; q < n_pairs && ok; q += gridDim.x) {
     // this thread's chunk of the pair
     const int c = 2 * q + ch;
@@ -734,7 +789,12 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
     const long long base = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64;
     const bool skipped = a.skip && a.skip[d.param_id];
     __syncthreads();                                   // previous pair's tiles and accumulators are free
-    if (rin == 0 && hf == 0) s_desc[ch] = d;           // the scatter below works on both chunks of the pair
+    if (rin == 0 && hf == 0) {                         // the scatter and the update below work on both chunks of the pair
+      s_desc[ch] = d;
+      s_gbase[ch] = active ? base : -1;
+      s_cols[ch] = d.cols;
+      s_skip[ch] = skipped ? 1 : 0;
+    }
     if (d.fh_off != cur_f) {                           // uniform: every 64 x 64 chunk uses the same basis
       load_basis_split(a.basis + d.fh_off, sB);
       cur_f = d.fh_off;
@@ -742,9 +802,29 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
     for (int i = tid; i < TC_ACC_BYTES / 16; i += NT) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     // ---- pull + unpack + scale + scatter-add, both chunks --------------------------------
+    if (ahead) {
+      if (pf_valid) {                                  // this thread's task of the pair, fetched one pair ago
+        const int i0 = (int)(pf_b0 | ((pf_b1 & 0xfu) << 8));
+        const int i1 = (int)(((pf_b1 >> 4) & 0xfu) | (pf_b2 << 4));
+        float v0, v1;
+        if (a.val_dtype == 0) {
+          v0 = __uint_as_float(pf_r0); v1 = __uint_as_float(pf_r1);
+        } else if (a.val_dtype == 1) {
+          v0 = __uint_as_float(pf_r0 << 16); v1 = __uint_as_float(pf_r1 << 16);
+        } else {
+          const float* qt = a.qtable + ((long long)pf_peer * a.n_params + pf_param) * (a.n_bins + 1);
+          const float shift = qt[a.n_bins];
+          v0 = qt[min((int)pf_r0, a.n_bins - 1)] + shift; v1 = qt[min((int)pf_r1, a.n_bins - 1)] + shift;
+        }
+        v0 *= pf_sc; v1 *= pf_sc;
+        atomicAdd(&S[pf_c2 * 4096 + i0], v0); atomicAdd(&Cnt[pf_c2 * 4096 + i0], 1);
+        atomicAdd(&S[pf_c2 * 4096 + i1], v1); atomicAdd(&Cnt[pf_c2 * 4096 + i1], 1);
+      }
+      fetch_ahead(q + gridDim.x);
+    }
     {
       const int pairs = d.k / 2;                       // k is the same for all 64 x 64 chunks of a layout
-      for (int t = tid; t < 2 * a.n_peers * pairs; t += NT) {
+      for (int t = ahead ? tid + NT : tid; t < 2 * a.n_peers * pairs; t += NT) {
         const int c2 = t / (a.n_peers * pairs), rem = t - c2 * (a.n_peers * pairs);
         const int cc = 2 * q + c2;
         if (cc >= a.total_chunks) continue;
@@ -798,6 +878,20 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
     }
     // Z_c rows (index j) into block c of the tiles: read back M-contiguous by the second GEMM
     store_split_row(sA + (uint32_t)ch * 8192u, TC_A_TILE, rin, hf, v);
+    // The update runs in a row-contiguous mapping: half a warp per row of the stacked 128 x 64 result, 16 bytes
+    // per lane, so that every global access of a warp covers two whole 256-byte rows (the accumulator mapping,
+    // one row per lane, touches 32 lines per instruction).  The snapshot values are requested here and used
+    // after the second product.
+    const int urow = tid >> 4, uc4 = tid & 15;
+    float4 t0r[8];
+    if (a.update_mode != 2) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 16 + urow, c2 = row >> 6;
+        const long long gb = s_gbase[c2];
+        if (gb >= 0) t0r[i] = *reinterpret_cast<const float4*>(a.theta0 + gb + (long long)(row & 63) * s_cols[c2] + uc4 * 4);
+      }
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tcgen05_fence_before();
     __syncthreads();
@@ -814,34 +908,48 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
     uint32_t gr[32];
     tmem_ld32(tG + hf * 32 + lane_off, gr);
     tcgen05_fence_before();
-    // ---- outer update of row `rin`, columns 32*hf .. of chunk c -------------------------------
-    if (active) {
-      const float lr = skipped ? 0.f : a.lr;
-      const float decay = skipped ? 1.f : (1.f - a.lr * a.weight_decay);
-      const long long g0 = base + (long long)rin * d.cols + hf * 32;
+    // ---- outer update ---------------------------------------------------------------------------
+    // g leaves the accumulator mapping through shared memory (the tiles of the finished products are free):
+    // row trow, 16-byte slots swizzled by the row so that both mappings are conflict-free.
+    {
+      const uint32_t st_own = sA + (uint32_t)trow * 256u + (uint32_t)hf * 128u;
+      const uint32_t sw = (uint32_t)(trow & 7);
 #pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        float gv[4];
+      for (int q4 = 0; q4 < 8; ++q4)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st_own + (((uint32_t)q4 ^ sw) << 4)), "r"(gr[4 * q4]),
+                     "r"(gr[4 * q4 + 1]), "r"(gr[4 * q4 + 2]), "r"(gr[4 * q4 + 3]) : "memory");
+    }
+    __syncthreads();
 #pragma unroll
-        for (int e = 0; e < 4; ++e) gv[e] = skipped ? 0.f : __uint_as_float(gr[4 * q4 + e]);
-        if (a.grad_out) *reinterpret_cast<float4*>(a.grad_out + g0 + 4 * q4) = make_float4(gv[0], gv[1], gv[2], gv[3]);
-        if (a.update_mode != 2) {
-          const float4 t0 = *reinterpret_cast<const float4*>(a.theta0 + g0 + 4 * q4);
-          const float tv[4] = {t0.x, t0.y, t0.z, t0.w};
-          float o[4];
+    for (int i = 0; i < 8; ++i) {
+      const int row = i * 16 + urow, c2 = row >> 6;
+      const long long gb = s_gbase[c2];
+      if (gb < 0) continue;
+      const bool skp = s_skip[c2] != 0;
+      const float lr = skp ? 0.f : a.lr;
+      const float decay = skp ? 1.f : (1.f - a.lr * a.weight_decay);
+      const long long g0 = gb + (long long)(row & 63) * s_cols[c2] + uc4 * 4;
+      float gv[4];
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(gv[0]), "=f"(gv[1]), "=f"(gv[2]), "=f"(gv[3])
+                   : "r"(sA + (uint32_t)row * 256u + (uint32_t)(uc4 >> 3) * 128u + ((((uint32_t)uc4 & 7u) ^ (uint32_t)(row & 7)) << 4))
+                   : "memory");
+      if (skp) { gv[0] = gv[1] = gv[2] = gv[3] = 0.f; }
+      if (a.grad_out) *reinterpret_cast<float4*>(a.grad_out + g0) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+      if (a.update_mode != 2) {
+        const float tv[4] = {t0r[i].x, t0r[i].y, t0r[i].z, t0r[i].w};
+        float o[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float step = (a.update_mode == 1) ? (gv[e] > 0.f ? 1.f : (gv[e] < 0.f ? -1.f : 0.f)) : gv[e];
-            o[e] = tv[e] * decay - lr * step;
-          }
-          *reinterpret_cast<float4*>(a.theta + g0 + 4 * q4) = make_float4(o[0], o[1], o[2], o[3]);
-          if (a.theta_bf16) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
-            uint2 pk;
-            pk.x = *reinterpret_cast<unsigned int*>(&lo);
-            pk.y = *reinterpret_cast<unsigned int*>(&hi);
-            *reinterpret_cast<uint2*>(a.theta_bf16 + g0 + 4 * q4) = pk;
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float step = (a.update_mode == 1) ? (gv[e] > 0.f ? 1.f : (gv[e] < 0.f ? -1.f : 0.f)) : gv[e];
+          o[e] = tv[e] * decay - lr * step;
+        }
+        *reinterpret_cast<float4*>(a.theta + g0) = make_float4(o[0], o[1], o[2], o[3]);
+        if (a.theta_bf16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+          uint2 pk;
+          pk.x = *reinterpret_cast<unsigned int*>(&lo);
+          pk.y = *reinterpret_cast<unsigned int*>(&hi);
+          *reinterpret_cast<uint2*>(a.theta_bf16 + g0) = pk;
         }
       }
     }
@@ -863,6 +971,7 @@ __global__ void __launch_bounds__(NT, 2) aggregate_tc_kernel(const AggArgs a) {
 // select for it.  Thread (chunk ch, row rin, column half hf) owns X[rin][32*hf..] and, after the
 // second GEMM, the coefficients Y[32*hf .. 32*hf+31][rin] (the GEMM pair leaves Y transposed).
 // ------------------------------------------------------------------------------------- //
+constexpr int TC_NCAND = 256;                // candidates of the threshold search per chunk (the histogram's storage)
 constexpr int TC_X_BYTES = 128 * 64 * 4;     // fp32 copy of the two chunks (each thread re-reads only its own part)
 constexpr int TC_SMEM_CMP = 3 * TC_A_TILE + 3 * TC_B_TILE + TC_X_BYTES + 1024;
 
@@ -875,6 +984,10 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
   __shared__ int s_hist[2][256];
   __shared__ int s_wsum[8];
   __shared__ int s_bin[2], s_krem[2];
+  __shared__ __align__(16) unsigned int s_tmax[2][128];
+  __shared__ unsigned int s_thr[2];
+  __shared__ long long s_gbase[2];                       // element offset of each chunk of the pair, -1: none
+  __shared__ int s_cols[2];
   __shared__ int s_sel_idx[2][TPLR_TILE];
   __shared__ float s_sel_val[2][TPLR_TILE];
   const uint32_t sA = smem_u32(smem), sB = sA + 3 * TC_A_TILE, sX = sB + 3 * TC_B_TILE;
@@ -934,32 +1047,58 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
     const int k = d.k;
     const int cl = c - d.chunk_begin;
     const int cy = d.chunk_row0 + cl / d.chunks_x, cx = cl % d.chunks_x;
-    const long long g0 = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64 + (long long)rin * d.cols + hf * 32;
+    const long long gbase = d.elem_off + (long long)cy * 64 * d.cols + (long long)cx * 64;
     __syncthreads();
+    if (rin == 0 && hf == 0) { s_gbase[ch] = active ? gbase : -1; s_cols[ch] = d.cols; }
     if (d.fh_off != cur_f) {
       load_basis_split(a.basis + d.fh_off, sB);
       cur_f = d.fh_off;
     }
-    // ---- X = gamma*e + delta: this thread's 32 values; fp32 copy kept in shared memory --------
-    float v[32];
+    __syncthreads();
+    // ---- X = gamma*e + delta into the fp32 copy in shared memory ------------------------------------
+    // Row-contiguous mapping: half a warp per row of the stacked 128 x 64 tile, 16 bytes per lane, so that every
+    // global access of a warp covers two whole 256-byte rows (one row per lane would touch 32 lines per
+    // instruction).  Slot (row, 16-byte column c4) of the copy: row * 256 + (c4 / 8) * 128 + ((c4 % 8) ^ (row % 8)) * 16.
+    const int urow = tid >> 4, uc4 = tid & 15;
 #pragma unroll
-    for (int q4 = 0; q4 < 8; ++q4) {
+    for (int i = 0; i < 8; ++i) {
+      const int row = i * 16 + urow, c2 = row >> 6;
+      const long long gb = s_gbase[c2];
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (active && !a.null_round) {
-        const float4 e = *reinterpret_cast<const float4*>(a.ef + g0 + 4 * q4);
-        float4 dl = *reinterpret_cast<const float4*>(a.theta0 + g0 + 4 * q4);
+      if (gb >= 0 && !a.null_round) {
+        const long long g = gb + (long long)(row & 63) * s_cols[c2] + uc4 * 4;
+        const float4 e = *reinterpret_cast<const float4*>(a.ef + g);
+        float4 dl = *reinterpret_cast<const float4*>(a.theta0 + g);
         if (a.delta_mode) {
-          const float4 t = *reinterpret_cast<const float4*>(a.theta + g0 + 4 * q4);
+          const float4 t = *reinterpret_cast<const float4*>(a.theta + g);
           dl.x -= t.x; dl.y -= t.y; dl.z -= t.z; dl.w -= t.w;
         }
         x.x = fmaf(a.gamma, e.x, dl.x); x.y = fmaf(a.gamma, e.y, dl.y);
         x.z = fmaf(a.gamma, e.z, dl.z); x.w = fmaf(a.gamma, e.w, dl.w);
       }
-      v[4 * q4] = x.x; v[4 * q4 + 1] = x.y; v[4 * q4 + 2] = x.z; v[4 * q4 + 3] = x.w;
-      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(xaddr + (((uint32_t)q4 ^ xsw) << 4)), "f"(x.x), "f"(x.y),
-                   "f"(x.z), "f"(x.w) : "memory");
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sX + (uint32_t)row * 256u + (uint32_t)(uc4 >> 3) * 128u +
+                   ((((uint32_t)uc4 & 7u) ^ (uint32_t)(row & 7)) << 4)), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
     }
+    __syncthreads();
+    // this thread's 32 values (row trow, columns 32*hf ..) for the operand tile
+    float v[32];
+#pragma unroll
+    for (int q4 = 0; q4 < 8; ++q4)
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[4 * q4]), "=f"(v[4 * q4 + 1]), "=f"(v[4 * q4 + 2]),
+                   "=f"(v[4 * q4 + 3]) : "r"(xaddr + (((uint32_t)q4 ^ xsw) << 4)) : "memory");
     store_split_row(sA, TC_A_TILE, trow, hf, v);
+    if ((a.variant & 2) && !a.null_round) {
+      // the next pair's 128 bytes of this thread in the three dense tensors, asked into L2 now
+      const int cn = c + 2 * (int)gridDim.x;
+      if (cn < a.total_chunks && cn < d.chunk_begin + d.n_chunks) {
+        const int cln = cn - d.chunk_begin;
+        const long long gn = d.elem_off + (long long)(d.chunk_row0 + cln / d.chunks_x) * 64 * d.cols +
+                             (long long)(cln % d.chunks_x) * 64 + (long long)rin * d.cols + hf * 32;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a.ef + gn));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a.theta0 + gn));
+        if (a.delta_mode) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.theta + gn));
+      }
+    }
     if (!(ok = run_gemm(tZ, /*a_mn=*/false, /*b_mn=*/false))) break;          // Z = X F^T
     {
       uint32_t r[32];
@@ -976,11 +1115,83 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
       for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);             // v[e] = Y[32*hf + e][rin]
     }
     tcgen05_fence_before();
-    // ---- radix select of the k largest |Y| of each chunk (its 128 threads, 32 keys each) ------
+    // ---- threshold of the k largest |Y| of each chunk (its 128 threads, 32 keys each) ---------
+    // Result: prefix = the k-th largest key, krem = how many keys equal to it belong to the selection.
+    // Fast path: the k-th largest of the 128 per-thread maxima is a lower bound of the k-th largest key
+    // (k distinct keys are at least that large), so only the keys at or above it (a few dozen for k = 32)
+    // are candidates; they are compacted into shared memory and the exact threshold is found by counting
+    // among them.  No shared-memory atomics: the histogram of the radix select below serialises on the
+    // few exponent values that the keys share.  More candidates than fit (ties, all-zero chunks) or
+    // k > 128 take the radix select.
     unsigned int prefix = 0u, mask = 0u;
     int krem = k;
+    bool radix = true;
+    if (k <= 128 && (a.variant & 1)) {
+      unsigned int m = 0u;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) m = max(m, __float_as_uint(v[i]) & 0x7fffffffu);
+      s_tmax[ch][lt] = m;
+      __syncthreads();
+      {
+        int rank = 0;
+        const uint4* row = reinterpret_cast<const uint4*>(s_tmax[ch]);
+#pragma unroll 8
+        for (int j4 = 0; j4 < 32; ++j4) {
+          const uint4 o = row[j4];
+          const int j = 4 * j4;
+          rank += (o.x > m) || (o.x == m && j < lt);
+          rank += (o.y > m) || (o.y == m && j + 1 < lt);
+          rank += (o.z > m) || (o.z == m && j + 2 < lt);
+          rank += (o.w > m) || (o.w == m && j + 3 < lt);
+        }
+        if (rank == k - 1) s_thr[ch] = m;
+      }
+      __syncthreads();
+      const unsigned int t0 = s_thr[ch];
+      int cnt = 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cnt += (__float_as_uint(v[i]) & 0x7fffffffu) >= t0;
+      int incl = cnt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (lane == 31) s_wsum[warp] = incl;
+      __syncthreads();
+      // warps of chunk ch hold lt blocks in the order 2ch, 2ch+1, 2ch+4, 2ch+5
+      const int w0 = s_wsum[2 * ch], w1 = s_wsum[2 * ch + 1], w2 = s_wsum[2 * ch + 4], w3 = s_wsum[2 * ch + 5];
+      const int slot = (warp & 1) + 2 * (warp >> 2);
+      int off = incl - cnt + (slot > 0 ? w0 : 0) + (slot > 1 ? w1 : 0) + (slot > 2 ? w2 : 0);
+      const int n_cand = w0 + w1 + w2 + w3;
+      // both chunks of the pair take the same path (the radix select synchronises the whole CTA)
+      const int n_other = s_wsum[2 * (ch ^ 1)] + s_wsum[2 * (ch ^ 1) + 1] + s_wsum[2 * (ch ^ 1) + 4] + s_wsum[2 * (ch ^ 1) + 5];
+      radix = n_cand > TC_NCAND || n_other > TC_NCAND;
+      if (!radix) {
+        unsigned int* cand = reinterpret_cast<unsigned int*>(s_hist[ch]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const unsigned int key = __float_as_uint(v[i]) & 0x7fffffffu;
+          if (key >= t0) cand[off++] = key;
+        }
+        __syncthreads();
+        for (int j = lt; j < n_cand; j += 128) {
+          const unsigned int cj = cand[j];
+          int gt = 0, ge = 0;
+          for (int i = 0; i < n_cand; ++i) {
+            const unsigned int x = cand[i];
+            gt += x > cj; ge += x >= cj;
+          }
+          if (gt < k && k <= ge) { s_bin[ch] = (int)cj; s_krem[ch] = k - gt; }   // ties write the same pair
+        }
+        __syncthreads();
+        prefix = (unsigned int)s_bin[ch];
+        krem = s_krem[ch];
+      }
+      __syncthreads();            // s_hist, s_wsum, s_bin and s_krem are reused below
+    }
 #pragma unroll 1
-    for (int pass = 0; pass < 4; ++pass) {
+    for (int pass = 0; radix && pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
       s_hist[0][tid] = 0; s_hist[1][tid] = 0;
       __syncthreads();
@@ -1105,15 +1316,26 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
 #pragma unroll
       for (int e = 0; e < 32; ++e) t32[e] = 0.f;
     }
-    if (active) {
+    // e <- X - transmit: subtracted in place in the shared copy (own slots), written out in the row-contiguous mapping
 #pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        float4 x;
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                     : "r"(xaddr + (((uint32_t)q4 ^ xsw) << 4)) : "memory");
-        *reinterpret_cast<float4*>(a.ef + g0 + 4 * q4) =
-            make_float4(x.x - t32[4 * q4], x.y - t32[4 * q4 + 1], x.z - t32[4 * q4 + 2], x.w - t32[4 * q4 + 3]);
-      }
+    for (int q4 = 0; q4 < 8; ++q4) {
+      float4 x;
+      const uint32_t ad = xaddr + (((uint32_t)q4 ^ xsw) << 4);
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(ad) : "memory");
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(ad), "f"(x.x - t32[4 * q4]), "f"(x.y - t32[4 * q4 + 1]),
+                   "f"(x.z - t32[4 * q4 + 2]), "f"(x.w - t32[4 * q4 + 3]) : "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = i * 16 + urow, c2 = row >> 6;
+      const long long gb = s_gbase[c2];
+      if (gb < 0) continue;
+      float4 x;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                   : "r"(sX + (uint32_t)row * 256u + (uint32_t)(uc4 >> 3) * 128u + ((((uint32_t)uc4 & 7u) ^ (uint32_t)(row & 7)) << 4))
+                   : "memory");
+      *reinterpret_cast<float4*>(a.ef + gb + (long long)(row & 63) * s_cols[c2] + uc4 * 4) = x;
     }
   }
   tcgen05_fence_before();
@@ -1140,6 +1362,7 @@ TPLR_API int tplr_compress_chunks_tc(const void* descs, int n_desc, int total_ch
   a.idx_out = idx_out; a.val_out = val_out; a.status = status; a.n_desc = n_desc;
   a.total_chunks = total_chunks; a.gamma = gamma; a.use_dct = 1; a.delta_mode = delta_mode;
   a.null_round = null_round; a.write_residual = write_residual; a.distinct = 0;
+  a.variant = g_tc_variant.load(std::memory_order_relaxed);
   cudaError_t err = cudaFuncSetAttribute(compress_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_CMP);
   if (err != cudaSuccess) return (int)err;
   int grid = tplr_sm_count() * 2;
@@ -1166,6 +1389,7 @@ TPLR_API int tplr_aggregate_apply_tc(const void* descs, int n_desc, int total_ch
   a.status = status; a.n_desc = n_desc; a.total_chunks = total_chunks; a.n_peers = n_peers;
   a.n_params = n_params; a.n_bins = n_bins; a.lr = lr; a.weight_decay = weight_decay; a.use_dct = 1;
   a.update_mode = update_mode; a.val_dtype = val_dtype; a.distinct = 0;
+  a.variant = g_tc_variant.load(std::memory_order_relaxed);
   for (int i = 0; i < n_peers; ++i) { a.pp.idx[i] = (const uint8_t*)idx_ptrs[i]; a.pp.val[i] = val_ptrs[i]; }
   cudaError_t err = cudaFuncSetAttribute(aggregate_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_AGG);
   if (err != cudaSuccess) return (int)err;
@@ -1537,3 +1761,8 @@ TPLR_API int tplr_index_overlap(const void* descs, int n_desc, int total_chunks,
 }
 
 TPLR_API int tplr_param_desc_size() { return (int)sizeof(TplrParamDesc); }
+
+// Selects the variants of the tensor-core compress / aggregate kernels (see g_tc_variant); returns the old value.
+TPLR_API int tplr_compress_set_variant(int v) {
+  return g_tc_variant.exchange(v & 7, std::memory_order_relaxed);
+}

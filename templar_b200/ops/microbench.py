@@ -241,7 +241,12 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--variant", type=int, default=None,
+                    help="compress / aggregate: switches of the tensor-core kernels (tplr_compress_set_variant)")
     a = ap.parse_args()
+    if a.variant is not None:
+        from . import native
+        native.lib().tplr_compress_set_variant(a.variant)
     {"gemm": bench_gemm, "compress": bench_compress, "quantize": bench_quantize, "aggregate": bench_aggregate,
      "elementwise": bench_elementwise, "attention": bench_attention}[a.case](a)
 

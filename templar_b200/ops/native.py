@@ -80,6 +80,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_adamw": [vp, vp, vp, vp, vp, i, ll, f, f, f, f, f, i, f, f, vp, i, vp],
         "tplr_cast_bf16": [vp, vp, ll, vp],
         "tplr_attention_set_bwd_variant": [i],
+        "tplr_compress_set_variant": [i],
         "tplr_attention_fwd": [vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_attention_bwd": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_gemm_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, vp, i, vp],

@@ -69,10 +69,21 @@ def peer_slice(state_dict: dict, j: int) -> dict:
 class WindowEngine:
     def __init__(self, model: torch.nn.Module, cfg: EngineConfig, *, device=None, rank: int = 0,
                  world_size: int = 1, group=None, heap=None, compute_dtype: torch.dtype | None = None,
-                 materialize=None):
+                 materialize=None, replicate_group=None, replicate_size: int = 1):
+        """``rank`` / ``world_size`` / ``group`` / ``heap`` describe the ranks that share one copy of the sharded
+        state.  ``replicate_group`` (``replicate_size`` ranks, one from every such copy, all holding the same
+        shard) adds the reference's ``dp_replicate`` dimension: the gradient shards are summed over it with one
+        all-reduce per inner step, after which every copy takes the same step.  ``world_size == 1`` with a
+        replicate group is plain data parallelism (whole state on every rank, bucketed gradient all-reduce);
+        both together are the hybrid layout (src/tplr/model_factory.py:122-176, torchtitan's HSDP / DDP)."""
         self.cfg = cfg
         self.model = model
         self.rank, self.world_size, self.group = rank, world_size, group
+        self.replicate_group, self.replicate_size = replicate_group, max(1, int(replicate_size))
+        if self.replicate_size > 1 and replicate_group is None:
+            raise ValueError("replicate_size > 1 needs the process group of the replicas")
+        self.dp_size = world_size * self.replicate_size       # ranks whose gradients are averaged
+        self.replica = dist.get_rank(replicate_group) if self.replicate_size > 1 else 0     # which copy this rank is in
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         if self.device.type == "meta":
             raise ValueError("the model is on the meta device: pass the device its shards are to live on")
@@ -212,6 +223,7 @@ class WindowEngine:
             return self._muon_step_sharded(lr) if cfg.inner_optimizer == "muon" else self._optimizer_step_sharded(lr)
         if self.world_size > 1:
             self._reduce_grads()
+        self._replicate_reduce(st.grad[st.lo:st.hi])
         if cfg.inner_optimizer == "muon":
             return self._muon_step(lr)
         gshard = st.grad[st.lo:st.hi]
@@ -226,7 +238,7 @@ class WindowEngine:
             shadows = self._compute_shadow_ptrs()
             native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                                       gshard.data_ptr(), native.ptr_array(shadows), len(shadows), n, lr, cfg.betas[0],
-                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
+                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.dp_size,
                                       cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
             self._mark("opt.adamw_and_weight_push")
             if self.world_size > 1:
@@ -236,7 +248,7 @@ class WindowEngine:
                 self._mark("opt.zero_grad")
             return
         # CPU path (same arithmetic); gradients were summed over ranks, the mean is what is applied
-        g = gshard / self.world_size
+        g = gshard / self.dp_size
         self.gnorm_sq.copy_((g * g).sum().reshape(1))
         if self.world_size > 1:
             dist.all_reduce(self.gnorm_sq, group=self.group)
@@ -277,6 +289,7 @@ class WindowEngine:
                 native.check(L.tplr_reduce_blocks(native.ptr_array(stages), len(stages), table.data_ptr(), n_rec,
                                                   st.grad_shard.data_ptr(), native.stream_ptr()), "reduce_blocks")
             self._mark("opt.reduce_staged")
+            self._replicate_reduce(gshard)
             native.check(L.tplr_sumsq(gshard.data_ptr(), n, self._sumsq_scratch.data_ptr(), self.gnorm_sq.data_ptr(),
                                       native.stream_ptr()), "sumsq")
             if self.world_size > 1:
@@ -285,12 +298,13 @@ class WindowEngine:
             shadows = [st.compute_shard.data_ptr()]
             native.check(L.tplr_adamw(st.master_shard.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                                       gshard.data_ptr(), native.ptr_array(shadows), 1, n, lr, cfg.betas[0],
-                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.world_size,
+                                      cfg.betas[1], cfg.eps, cfg.weight_decay, self.adam_step, 1.0 / self.dp_size,
                                       cfg.max_grad_norm, self.gnorm_sq.data_ptr(), 1, native.stream_ptr()), "adamw")
             self._mark("opt.adamw")
         else:
             self._reduce_staged_cpu()
-            g = gshard / self.world_size
+            self._replicate_reduce(gshard)
+            g = gshard / self.dp_size
             self.gnorm_sq.copy_((g * g).sum().reshape(1))
             if self.world_size > 1:
                 dist.all_reduce(self.gnorm_sq, group=self.group)
@@ -373,7 +387,8 @@ class WindowEngine:
         self._barrier()                                     # every rank's backward pass (remote adds) is complete
         self._reduce_staged()
         g = st.grad_shard[:n]
-        g.mul_(1.0 / self.world_size)
+        self._replicate_reduce(g)
+        g.mul_(1.0 / self.dp_size)
         self.gnorm_sq.copy_((g * g).sum().reshape(1))
         if self.world_size > 1:
             dist.all_reduce(self.gnorm_sq, group=self.group)
@@ -483,7 +498,7 @@ class WindowEngine:
 
         cfg, st = self.cfg, self.store
         g = st.grad[st.lo:st.hi]
-        g.mul_(1.0 / self.world_size)
+        g.mul_(1.0 / self.dp_size)
         self.gnorm_sq.copy_((g * g).sum().reshape(1))
         if self.world_size > 1:
             dist.all_reduce(self.gnorm_sq, group=self.group)
@@ -594,6 +609,24 @@ class WindowEngine:
             a, b = self.layout.shard_range(r)
             dist.reduce(st.grad[a:b], dst=dist.get_global_rank(self.group, r) if self.group is not None else r,
                         group=self.group)
+
+    def _global(self, r: int) -> int:
+        """Global rank of rank ``r`` of this engine's group."""
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    REPLICATE_BUCKET = 64 * 1024 * 1024       # elements per all-reduce over the replicas (256 MB of fp32)
+
+    def _replicate_reduce(self, gshard: torch.Tensor) -> None:
+        """Sum this rank's gradient shard over the replicas (the ranks of the other copies that hold the same
+        shard).  Issued in buckets so that no single collective holds more than a quarter of a gigabyte of
+        NCCL work in flight; all of them are enqueued before the first wait."""
+        if self.replicate_size <= 1 or gshard.numel() == 0:
+            return
+        works = [dist.all_reduce(gshard[a:a + self.REPLICATE_BUCKET], group=self.replicate_group, async_op=True)
+                 for a in range(0, gshard.numel(), self.REPLICATE_BUCKET)]
+        for w in works:
+            w.wait()
+        self._mark("opt.replicate_allreduce")
 
     def _barrier(self) -> None:
         if self.world_size > 1:
@@ -1207,8 +1240,8 @@ class WindowEngine:
                     self.peer_idx[slot].copy_(idx)
                     self.peer_val[slot].copy_(val)
                 if self.world_size > 1:
-                    dist.broadcast(self.peer_idx[slot], src=0, group=self.group)
-                    dist.broadcast(self.peer_val[slot], src=0, group=self.group)
+                    dist.broadcast(self.peer_idx[slot], src=self._global(0), group=self.group)
+                    dist.broadcast(self.peer_val[slot], src=self._global(0), group=self.group)
         self._barrier()
 
     @torch.no_grad()
@@ -1232,8 +1265,8 @@ class WindowEngine:
                 idx, val = self.pack_payload(payload, device=self.device)
                 self.peer_idx[slot].copy_(idx)
                 self.peer_val[slot].copy_(val)
-            dist.broadcast(self.peer_idx[slot], src=0, group=self.group)
-            dist.broadcast(self.peer_val[slot], src=0, group=self.group)
+            dist.broadcast(self.peer_idx[slot], src=self._global(0), group=self.group)
+            dist.broadcast(self.peer_val[slot], src=self._global(0), group=self.group)
         self._barrier()
 
     @torch.no_grad()
