@@ -49,6 +49,10 @@ def parse():
     ap.add_argument("--gather-buffers", type=int, default=0,
                     help="with --shard-params: block buffers in rotation (>= the number of blocks keeps all gathered; "
                          "0 = all blocks when the bf16 weights are at most 8 GiB, else 2)")
+    ap.add_argument("--replicas", type=int, default=1,
+                    help="copies of the sharded state (the reference's dp_replicate): the ranks form this many groups of "
+                         "world/replicas consecutive ranks, state sharded inside a group, gradient shards all-reduced "
+                         "across the groups once per inner step; replicas == world is plain data parallelism")
     ap.add_argument("--gather-engine", default=None, choices=[None, "sm", "dma"],
                     help="with --shard-params: weight gathers by the copy kernel (sm) or by the copy engines (dma)")
     ap.add_argument("--checkpoint-blocks", action="store_true", help="recompute every block in the backward pass")
@@ -141,9 +145,20 @@ def run_ours(a):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     heap = None
+    srank, sworld = rank, world                   # this rank's place inside its copy of the sharded state
+    shard_group = replicate_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        heap = symmetric.SymmetricHeap.create(dev, rank, world)
+        if a.replicas > 1:
+            if world % a.replicas:
+                raise SystemExit(f"--replicas {a.replicas} does not divide {world} ranks")
+            per = world // a.replicas
+            sgs = [dist.new_group(list(range(r * per, (r + 1) * per))) for r in range(a.replicas)]
+            rgs = [dist.new_group(list(range(s, world, per))) for s in range(per)]
+            shard_group, replicate_group = (sgs[rank // per] if per > 1 else None), rgs[rank % per]
+            srank, sworld = rank % per, per
+        if sworld > 1:
+            heap = symmetric.SymmetricHeap.create(dev, srank, sworld, group=shard_group)
     if a.gemm:
         OF.set_gemm_backend(a.gemm)
     args = PRESETS[a.model]
@@ -157,11 +172,13 @@ def run_ours(a):
         with torch.device("meta"):
             model = LlamaModel(args)
         model.freqs_cis = model._freqs_cis().to(dev)
-        eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap,
+        eng = WindowEngine(model, cfg, device=dev, rank=srank, world_size=sworld, heap=heap, group=shard_group,
+                           replicate_group=replicate_group, replicate_size=a.replicas if replicate_group is not None else 1,
                            materialize=lambda name: model.materialize_param(name, dev, torch.bfloat16, seed=0))
     else:
         model = build_model(args, device=dev, dtype=torch.bfloat16, seed=0)
-        eng = WindowEngine(model, cfg, device=dev, rank=rank, world_size=world, heap=heap)
+        eng = WindowEngine(model, cfg, device=dev, rank=srank, world_size=sworld, heap=heap, group=shard_group,
+                           replicate_group=replicate_group, replicate_size=a.replicas if replicate_group is not None else 1)
     model.activation_checkpointing = a.checkpoint_blocks
     L = eng.layout
     B, S, A = a.micro_batch, a.seq_len, a.accum
@@ -171,7 +188,7 @@ def run_ours(a):
     host_tokens = [torch.randint(0, args.vocab_size, (B, S + 1), generator=g).pin_memory() for _ in range(n_pool)]
     dev_tokens = [t.to(dev) for t in host_tokens]
     # synthetic peers 1..P-1: seeded payloads in pinned host memory (flat wire format of this layout)
-    hosted = [j for j in range(1, a.peers) if j % world == rank]
+    hosted = [j for j in range(1, a.peers) if j % sworld == srank]      # every copy of the state stages all peers
     host_payload = {}
     from templar_b200.utils.synthetic import synthetic_payload
     for j in hosted:
@@ -198,8 +215,8 @@ def run_ours(a):
             own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
         eng.compress(own_slot_ptrs=own_ptrs)
         for j in hosted:
-            eng.load_peer_payload(j // world, host_payload[j])
-        if world > 1:
+            eng.load_peer_payload(j // sworld, host_payload[j])
+        if sworld > 1:
             eng._barrier()
         eng.outer_step(a.peers)
         loss = torch.stack(losses).mean()
@@ -252,9 +269,9 @@ def run_ours(a):
             own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
         eng.compress(own_slot_ptrs=own_ptrs)
         for j in hosted:
-            eng.load_peer_payload(j // world, host_payload[j])
+            eng.load_peer_payload(j // sworld, host_payload[j])
         eng._mark("peer_payload_h2d")
-        if world > 1:
+        if sworld > 1:
             eng._barrier()
             eng._mark("outer.barrier_payloads_staged")
         eng.outer_step(a.peers)
@@ -291,8 +308,11 @@ def run_ours(a):
     sharding_label = ("bf16 weights, fp32 gradients and all optimizer state sharded; weights gathered per block, "
                       f"{eng.store.gather.n_buffers} block buffers, gathers by {eng.store.gather.engine}" if a.shard_params else
                       "single GPU" if world == 1 else
+                      "whole state on every rank" if sworld == 1 else
                       "optimizer state, master weights, snapshot and error feedback sharded; bf16 weights and fp32 "
                       "gradients whole on every rank")
+    if eng.replicate_size > 1:
+        sharding_label += f"; {eng.replicate_size} copies of {sworld} ranks, gradient shards all-reduced across the copies (NCCL)"
     free_b, total_b = torch.cuda.mem_get_info(dev)       # includes the symmetric heap, which torch's allocator does not see
     peak = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2 ** 30, (total_b - free_b) / 2 ** 30],
                         dtype=torch.float64, device=dev)

@@ -120,10 +120,10 @@ class Attention(nn.Module):
 
     def forward(self, x, cos, sin):
         B, S, _ = x.shape
-        if self.packed is not None:
-            qkv = OF.linear(x, self.packed[0], self.packed[1])
-        else:
-            qkv = OF.linear(x, torch.cat((self.wq.weight, self.wk.weight, self.wv.weight), dim=0))
+        if self.packed is not None:          # projection, rotary embedding and attention as one node on the own kernels
+            return self.wo(OF.rope_attention_projection(x, self.packed[0], cos, sin, self.n_heads, self.n_kv, self.hd,
+                                                        self.packed[1]))
+        qkv = OF.linear(x, torch.cat((self.wq.weight, self.wk.weight, self.wv.weight), dim=0))
         qkv = OF.rope(qkv, cos, sin, self.n_heads + self.n_kv, self.hd)
         return self.wo(OF.attention_packed(qkv, self.n_heads, self.n_kv, self.hd))
 
@@ -138,9 +138,8 @@ class FeedForward(nn.Module):
 
     def forward(self, x):
         if self.packed is not None:
-            h = OF.linear(x, self.packed[0], self.packed[1])
-        else:
-            h = OF.linear(x, torch.cat((self.w1.weight, self.w3.weight), dim=0))
+            return self.w2(OF.linear_swiglu(x, self.packed[0], self.packed[1]))      # activation in the GEMM's epilogue
+        h = OF.linear(x, torch.cat((self.w1.weight, self.w3.weight), dim=0))
         return self.w2(OF.swiglu(h))
 
 

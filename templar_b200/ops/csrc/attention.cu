@@ -364,6 +364,10 @@ struct AttnBwdParams {
   int B, S, H, KV;
   float scale, scale_log2;
   unsigned int* status;
+  // not null: q and k were rotated (rotary embedding, interleaved pairs, tables [S, 64] fp32) by the producer of qkv and
+  // the gradient is wanted with respect to the un-rotated projection: dK is rotated back in the epilogue
+  const float* rope_cos;
+  const float* rope_sin;
 };
 
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
@@ -584,6 +588,22 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t v[32];
           tmem_ld32(tacc + ch * 64 + hf * 32 + lane_off, v);
+          if (acc == 1 && p.rope_cos) {          // dK back through the rotation of this key row: the opposite angle
+            const long long tb = (long long)((orow0 + lane) % p.S) * (DH / 2) + (ch * 64 + hf * 32) / 2;
+            const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + tb);
+            const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + tb);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 cv = cp[q], sv = sp[q];
+              const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a = __uint_as_float(v[8 * q + 2 * e]), b = __uint_as_float(v[8 * q + 2 * e + 1]);
+                v[8 * q + 2 * e] = __float_as_uint(a * cc[e] + b * ss[e]);
+                v[8 * q + 2 * e + 1] = __float_as_uint(b * cc[e] - a * ss[e]);
+              }
+            }
+          }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint32_t pw[4];
@@ -637,13 +657,20 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 }
 
 // dq32 [tokens, H*128] fp32 -> first H*128 columns of the packed bf16 gradient
+// cosb / sinb not null: the two pairs are rotated back by the angles of (token % S, pair index in the head) on the way
 __global__ void __launch_bounds__(256) attn_dq_cast_kernel(const float* __restrict__ dq32, __nv_bfloat16* __restrict__ dqkv,
-                                                           long long tokens, int width, long long ld) {
+                                                           long long tokens, int width, long long ld,
+                                                           const float* __restrict__ cosb, const float* __restrict__ sinb, int S) {
   const long long n4 = tokens * (width / 4);
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n4; v += (long long)gridDim.x * blockDim.x) {
     const long long tok = v / (width / 4);
     const int c4 = (int)(v % (width / 4));
-    const float4 f = reinterpret_cast<const float4*>(dq32)[v];
+    float4 f = reinterpret_cast<const float4*>(dq32)[v];
+    if (cosb) {
+      const long long tb = (tok % S) * (DH / 2) + ((c4 * 4) % DH) / 2;
+      const float2 c = *reinterpret_cast<const float2*>(cosb + tb), sn = *reinterpret_cast<const float2*>(sinb + tb);
+      f = make_float4(f.x * c.x + f.y * sn.x, f.y * c.x - f.x * sn.x, f.z * c.y + f.w * sn.y, f.w * c.y - f.z * sn.y);
+    }
     __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
     uint2 o;
     o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -1004,10 +1031,12 @@ TPLR_API int tplr_attention_set_bwd_variant(int v) {
 // Gradient of tplr_attention_fwd.  qkv / dqkv: packed [B*S, C] bf16 with row stride ld_qkv; out: the forward's
 // output (row stride ld_o); dout: contiguous [B*S, H*128]; lse from the forward; delta: [B,H,S] fp32 scratch;
 // dq32: [B*S, H*128] fp32 scratch that the caller has zeroed.  dqkv receives dq | dk | dv.
-TPLR_API int tplr_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
-                                float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
-                                float scale, unsigned int* status, void* stream) {
-  TPLR_ENTER();
+extern "C" int tplr_rope(void* buf, const float* cosb, const float* sinb, long long tokens, int S, int n_heads, int Dh,
+                         long long row_stride, int inverse, void* stream);
+
+static int attention_bwd_impl(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                              float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
+                              float scale, const float* cosb, const float* sinb, unsigned int* status, void* stream) {
   if (B <= 0 || S <= 0) return 0;
   if (S % BQ || H % KV || (ld_qkv % 8) || (ld_o % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)dqkv & 15) ||
       ((uintptr_t)dout & 15) || ((uintptr_t)out & 7) || ((uintptr_t)dq32 & 15))
@@ -1032,6 +1061,7 @@ TPLR_API int tplr_attention_bwd(const void* qkv, const void* out, const void* do
     attn_bwd2_kernel<<<(unsigned)((S / BKV) * KV * B), B2_THREADS, B2_SMEM, st>>>(p);
     attn_dq_transpose_kernel<<<dim3((unsigned)(S / 32), (unsigned)(B * H * DH / 32)), 256, 0, st>>>(
         dq32, (__nv_bfloat16*)dqkv, S, H, ld_qkv);
+    if (cosb) return tplr_rope(dqkv, cosb, sinb, tokens, S, H + KV, DH, ld_qkv, 1, stream);   // this variant rotates back in a pass of its own
     return (int)cudaGetLastError();
   }
   AttnBwdParams p = {};
@@ -1041,9 +1071,29 @@ TPLR_API int tplr_attention_bwd(const void* qkv, const void* out, const void* do
   if (!make_map(&p.tmDQKV, dqkv, C, tokens, ld_qkv, 64, 32)) return -205;
   p.lse = lse; p.delta = delta; p.B = B; p.S = S; p.H = H; p.KV = KV;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.rope_cos = cosb; p.rope_sin = sinb;
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
   if (e != cudaSuccess) return (int)e;
   attn_bwd_kernel<<<(unsigned)((S / BKV) * KV * B), BWD_THREADS, BWD_SMEM, st>>>(p);
-  attn_dq_cast_kernel<<<tplr_sm_count() * 8, 256, 0, st>>>(dq32, (__nv_bfloat16*)dqkv, tokens, H * DH, ld_qkv);
+  attn_dq_cast_kernel<<<tplr_sm_count() * 8, 256, 0, st>>>(dq32, (__nv_bfloat16*)dqkv, tokens, H * DH, ld_qkv, cosb, sinb, S);
   return (int)cudaGetLastError();
+}
+
+TPLR_API int tplr_attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
+                                float scale, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  return attention_bwd_impl(qkv, out, dout, lse, delta, dq32, dqkv, B, S, H, KV, ld_qkv, ld_o, scale, nullptr, nullptr, status, stream);
+}
+
+// tplr_attention_bwd for a qkv whose q and k heads were rotated by the producer (tplr_gemm2_rope): dq and dk are
+// returned with respect to the un-rotated projection, i.e. rotated back by the opposite angles where they are written
+// (dq in the fp32 -> bf16 pass, dk in the kernel's epilogue), so that no separate pass over the gradient is needed.
+// cosb / sinb: [S, 64] fp32, 16-byte aligned.
+TPLR_API int tplr_attention_bwd_unrope(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                       float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
+                                       float scale, const float* cosb, const float* sinb, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (!cosb || !sinb || ((uintptr_t)cosb & 15) || ((uintptr_t)sinb & 15)) return -201;
+  return attention_bwd_impl(qkv, out, dout, lse, delta, dq32, dqkv, B, S, H, KV, ld_qkv, ld_o, scale, cosb, sinb, status, stream);
 }

@@ -54,6 +54,15 @@ struct Gemm2Params {
   int m_inter;                       // > 1: logical tile row l is row (l % m_inter) * (tiles_m / m_inter) + l / m_inter
   int k_splits;                      // > 1 (reduce-add epilogues only): a tile's K range is cut into this many work units
   int tri;                           // 1: C is symmetric (B is A): only tiles on or above the diagonal are computed
+  int swiglu_f;                      // > 0 (EPI 3): B is the packed [w1; w3] weight of 2 * swiglu_f rows.  Tile column j pairs
+                                     // gate rows [128 j, 128 j + 128) (staged by the even CTA) with up rows swiglu_f + the same
+                                     // (odd CTA), so every accumulator row holds g and u of the same 128 features; the epilogue
+                                     // stores both into C [M, 2 * swiglu_f] and silu(g) * u into tmCr[0]'s tensor [M, swiglu_f]
+  // rotary embedding in the epilogue (EPI 4): the first rope_cols columns of C are heads of rope_dh columns whose
+  // interleaved pairs (2i, 2i + 1) are rotated by the angle of (row % rope_s, i); tables [rope_s, rope_dh / 2] fp32
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_s, rope_cols, rope_dh;
   int world, rank;
   unsigned int epoch;
   // gather
@@ -196,7 +205,7 @@ __device__ __forceinline__ void epilogue_direct(const Gemm2Params& p, uint32_t t
     tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(quad * 32) << 16), r);
     const int col0 = n0 + c * 32;
     if (row < p.M && col0 < p.N) {
-      if (EPI == 0) {
+      if (EPI == 0 || EPI >= 3) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
         for (int e = 0; e < 32 && col0 + e < p.N; ++e) crow[e] = __float2bfloat16(__uint_as_float(r[e]));
       } else {
@@ -225,7 +234,8 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
 template <int EPI>
 __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int n0,
                                              uint32_t stage_base, uint32_t& n_boxes) {
-  constexpr int COLS = EPI == 0 ? 64 : 32;
+  constexpr bool BF16_OUT = EPI == 0 || EPI == 4;
+  constexpr int COLS = BF16_OUT ? 64 : 32;
   const int row0 = m0 + quad * 32;
   const uint32_t sw = (uint32_t)(lane & 7);
   const CUtensorMap* map = &p.tmC;
@@ -246,11 +256,29 @@ __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem
       __syncwarp();
     }
     const uint32_t rowaddr = buf + (uint32_t)lane * 128u;
-    if (EPI == 0) {
+    if (BF16_OUT) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t r[32];
         tmem_ld32(tmem_acc + c * 64 + h * 32 + ((uint32_t)(quad * 32) << 16), r);
+        if (EPI == 4 && col0 + h * 32 < p.rope_cols) {
+          // rotary pairs of this lane's token: 16 angles starting at pair ((col % head) / 2) of position row % S
+          const int row = min(row0 + lane, p.M - 1);
+          const long long tb = (long long)(row % p.rope_s) * (p.rope_dh / 2) + ((col0 + h * 32) % p.rope_dh) / 2;
+          const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + tb);
+          const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + tb);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 cv = cp[q], sv = sp[q];
+            const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float a = __uint_as_float(r[8 * q + 2 * e]), b = __uint_as_float(r[8 * q + 2 * e + 1]);
+              r[8 * q + 2 * e] = __float_as_uint(a * cc[e] - b * ss[e]);
+              r[8 * q + 2 * e + 1] = __float_as_uint(a * ss[e] + b * cc[e]);
+            }
+          }
+        }
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint32_t pw[4];
@@ -283,7 +311,89 @@ __device__ __forceinline__ void epilogue_tma(const Gemm2Params& p, uint32_t tmem
   }
 }
 
-// EPI: 0 store bf16, 1 fp32 accumulate (C += acc), 2 store fp32
+// Staging of one 32 x 64 bf16 box in two halves of 32 columns (same double-buffer protocol as epilogue_tma):
+// box_begin waits until the buffer is free, box_half writes this lane's 32 values of half `hh`, box_store issues the store.
+__device__ __forceinline__ uint32_t box_begin(int lane, uint32_t stage_base, uint32_t n_boxes) {
+  if (n_boxes >= 2) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+  }
+  return stage_base + (n_boxes & 1u) * 4096u;
+}
+__device__ __forceinline__ void box_half(uint32_t buf, int lane, int hh, const float* v) {
+  const uint32_t rowaddr = buf + (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t pw[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+      pw[e] = *reinterpret_cast<uint32_t*>(&b2);
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((uint32_t)(hh * 4 + j) ^ sw) << 4)), "r"(pw[0]),
+                 "r"(pw[1]), "r"(pw[2]), "r"(pw[3]) : "memory");
+  }
+}
+__device__ __forceinline__ void box_store(const CUtensorMap* map, uint32_t buf, int lane, uint32_t& n_boxes, int col0, int row0) {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map, buf, col0, row0);
+    bulk_commit();
+  }
+  ++n_boxes;
+}
+
+// Epilogue of the fused [w1; w3] projection (EPI 3): accumulator columns 0..127 of a row are the gate values g of features
+// [128 tn, 128 tn + 128), columns 128..255 the up values u of the same features.  Per 64 features: g and u go to C (bf16,
+// columns 128 tn + .. and swiglu_f + 128 tn + ..: what the backward pass reads) and h = silu(g) * u, computed from the fp32
+// accumulators, goes to the [M, swiglu_f] tensor behind tmCr[0].  Replaces a separate pass that re-reads g and u
+// (the reference's F.silu(w1(x)) * w3(x), torchtitan models/llama3/model/model.py FeedForward.forward).
+// The accumulators are read twice (once for the g / u boxes, once for h): tensor-memory loads are cheap and 32 values
+// at a time keep the register count of the epilogue warps where it was.
+__device__ __forceinline__ void epilogue_swiglu(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int tn,
+                                                uint32_t stage_base, uint32_t& n_boxes) {
+  const int row0 = m0 + quad * 32;
+  if (row0 >= p.M) return;                           // warp-uniform
+  const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    const int f0 = tn * CTA_N + c * 64;              // first feature of this box
+    if (f0 >= p.swiglu_f) break;
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {           // 0: g box, 1: u box
+      const uint32_t buf = box_begin(lane, stage_base, n_boxes);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t r[32];
+        float v[32];
+        tmem_ld32(tmem_acc + part * CTA_N + c * 64 + hh * 32 + lane_sel, r);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+        box_half(buf, lane, hh, v);
+      }
+      box_store(&p.tmC, buf, lane, n_boxes, part * p.swiglu_f + f0, row0);
+    }
+    const uint32_t buf = box_begin(lane, stage_base, n_boxes);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t rg[32], ru[32];
+      float v[32];
+      tmem_ld32(tmem_acc + c * 64 + hh * 32 + lane_sel, rg);
+      tmem_ld32(tmem_acc + CTA_N + c * 64 + hh * 32 + lane_sel, ru);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float g = __uint_as_float(rg[e]);
+        v[e] = __fdividef(g, 1.f + __expf(-g)) * __uint_as_float(ru[e]);            // silu(g) * u
+      }
+      box_half(buf, lane, hh, v);
+    }
+    box_store(&p.tmCr[0], buf, lane, n_boxes, f0, row0);
+  }
+}
+
+// EPI: 0 store bf16, 1 fp32 accumulate (C += acc), 2 store fp32, 3 fused SwiGLU of a packed [w1; w3] projection,
+// 4 store bf16 with the rotary embedding applied to the leading columns
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ Gemm2Params p) {
@@ -353,7 +463,8 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
           tile_coords(p, w.tile, tiles_m, tiles_n, tm, tn);
           const int kb0 = w.kb0;
           const int k_blocks = w.nkb;
-          const int m0 = tm * TILE_M + (int)cr * CTA_M, n0 = tn * TILE_N + (int)cr * CTA_N;
+          const int m0 = tm * TILE_M + (int)cr * CTA_M;
+          const int n0 = EPI == 3 ? tn * CTA_N + (int)cr * p.swiglu_f : tn * TILE_N + (int)cr * CTA_N;
           if (p.ag_operand == 1 && !A_MN) ok = rows_ready(m0, CTA_M);
           if (p.ag_operand == 2 && !B_MN) ok = ok && rows_ready(n0, CTA_N);
           for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
@@ -445,8 +556,9 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * TILE_N;
-        if (p.c_tma) epilogue_tma<EPI>(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
-        else         epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
+        if (EPI == 3)      epilogue_swiglu(p, tmem_acc, quad, lane, m0, tn, sEpi + (uint32_t)quad * 8192u, n_boxes);
+        else if (p.c_tma)  epilogue_tma<EPI>(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
+        else               epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bar_tempty[acc]), 0));
@@ -536,7 +648,7 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
   // all CTAs must be resident at once: compute CTAs wait for comm CTAs of the same launch
-  static int max_clusters[2][2][3] = {};
+  static int max_clusters[2][2][5] = {};
   int& mc = max_clusters[A_MN][B_MN][EPI];
   if (mc == 0) {
     cfg.gridDim = dim3(2 * (tplr_sm_count() / 2));
@@ -565,6 +677,7 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
   TPLR_GEMM2_CASE(0, 1, 0) TPLR_GEMM2_CASE(0, 1, 1) TPLR_GEMM2_CASE(0, 1, 2)
   TPLR_GEMM2_CASE(1, 1, 0) TPLR_GEMM2_CASE(1, 1, 1) TPLR_GEMM2_CASE(1, 1, 2)
   TPLR_GEMM2_CASE(1, 0, 0) TPLR_GEMM2_CASE(1, 0, 1) TPLR_GEMM2_CASE(1, 0, 2)
+  TPLR_GEMM2_CASE(0, 0, 3) TPLR_GEMM2_CASE(0, 0, 4)
 #undef TPLR_GEMM2_CASE
   return -104;
 }
@@ -626,6 +739,40 @@ TPLR_API int tplr_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
   if (int r = fill_common(p, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, status)) return r;
   if (epi == 1 && p.c_tma) p.k_splits = pick_k_splits(M, N, K, max_pairs);
   return dispatch2(p, a_mn, b_mn, epi, 0, max_pairs, (cudaStream_t)stream);
+}
+
+// GU[M, 2F] = X W^T for the packed weight W = [w1; w3] ([2F, K] bf16, K-major) and H[M, F] = silu(GU[:, :F]) * GU[:, F:]
+// in one launch (see Gemm2Params::swiglu_f).  F a multiple of 128; X, W, GU, H 16-byte aligned with leading dimensions
+// that are multiples of 8 elements.  -111: shapes or alignment that this entry does not take (the caller runs the
+// projection and the activation as two launches instead).
+TPLR_API int tplr_gemm2_swiglu(const void* X, const void* W, void* GU, void* H, int M, int F, int K, long long ldx,
+                               long long ldw, long long ldgu, long long ldh, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if (F % CTA_N || ((uintptr_t)GU & 15) || ((uintptr_t)H & 15) || (ldgu % 8) || (ldh % 8)) return -111;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, X, W, GU, M, 2 * F, K, ldx, ldw, ldgu, 0, 0, 0, status)) return r;
+  if (!p.c_tma) return -111;
+  if (!make_map(&p.tmCr[0], H, F, M, ldh, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, false)) return -110;
+  p.swiglu_f = F;
+  return dispatch2(p, 0, 0, 3, 0, 0, (cudaStream_t)stream);
+}
+
+// QKV[M, N] = X W^T (bf16, W K-major) with the rotary embedding applied to the first rope_cols columns in the epilogue:
+// heads of `head_dim` columns, interleaved pairs, angle tables cos / sin [S, head_dim / 2] fp32, position = row % S
+// (the reference's apply_rotary_emb on xq and xk, torchtitan models/llama3/model/model.py, after the wq / wk projections).
+// rope_cols and head_dim multiples of 32 and 16-byte aligned tables; -111 when this entry does not take the arguments.
+TPLR_API int tplr_gemm2_rope(const void* X, const void* W, void* QKV, int M, int N, int K, long long ldx, long long ldw,
+                             long long ldc, const float* cosb, const float* sinb, int S, int rope_cols, int head_dim,
+                             unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (S <= 0 || head_dim % 32 || rope_cols % 32 || rope_cols > N || ((uintptr_t)cosb & 15) || ((uintptr_t)sinb & 15)) return -111;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, X, W, QKV, M, N, K, ldx, ldw, ldc, 0, 0, 0, status)) return r;
+  if (!p.c_tma) return -111;
+  p.rope_cos = cosb; p.rope_sin = sinb; p.rope_s = S; p.rope_cols = rope_cols; p.rope_dh = head_dim;
+  return dispatch2(p, 0, 0, 4, 0, 0, (cudaStream_t)stream);
 }
 
 // All-gather fused into the GEMM.  Operand `ag_operand` (1 = A, 2 = B) is the local FULL buffer

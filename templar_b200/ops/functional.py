@@ -25,6 +25,9 @@ from . import native
 # "tcgen05": own GEMM kernel, one CTA per tile; "tcgen05_2sm": own GEMM kernel on CTA pairs
 # (cta_group::2); "cublas": torch.matmul (library).  Switched by templar_b200.ops.set_gemm_backend().
 _GEMM_BACKEND = "tcgen05_2sm"
+# Element-wise work folded into the projections' GEMM epilogues (SwiGLU of [w1; w3], rotary embedding of q and k).
+# TPLR_FUSED_PROJECTIONS=0 runs the projection and the element-wise kernel as separate launches (comparison runs).
+FUSED_PROJECTIONS = __import__("os").environ.get("TPLR_FUSED_PROJECTIONS", "1") == "1"
 _status_words: dict[int, torch.Tensor] = {}
 
 
@@ -406,6 +409,56 @@ def swiglu(h):
     return _SwiGLU.apply(h)
 
 
+class _LinearSwiGLU(torch.autograd.Function):
+    """``swiglu(x W^T)`` for the packed weight ``W = [w1; w3]``.  On the own GEMM the activation is computed in
+    the projection's epilogue from the fp32 accumulators (``tplr_gemm2_swiglu``): the packed projection ``gu`` is
+    still written, because the backward pass needs it, but it is not read back by a separate activation pass.
+    The backward pass is the one of :class:`_SwiGLU` followed by the one of :class:`_Linear`."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        ctx.main_grad = main_grad
+        F2, Fd = w.shape[0], w.shape[0] // 2
+        x2 = x.reshape(-1, x.shape[-1])
+        gu = torch.empty(*x.shape[:-1], F2, dtype=x.dtype, device=x.device)
+        h = None
+        if (FUSED_PROJECTIONS and _native_ok(x2, w) and _GEMM_BACKEND == "tcgen05_2sm" and x.dtype == torch.bfloat16 and Fd % 128 == 0
+                and x2.is_contiguous() and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x2.shape[1] % 8 == 0):
+            h = torch.empty(*x.shape[:-1], Fd, dtype=x.dtype, device=x.device)
+            rc = native.lib().tplr_gemm2_swiglu(x2.data_ptr(), w.data_ptr(), gu.data_ptr(), h.data_ptr(), x2.shape[0], Fd,
+                                                x2.shape[1], x2.stride(0), w.stride(0), F2, Fd, status_word(x.device).data_ptr(),
+                                                native.stream_ptr())
+            if rc == -111:                      # shapes or alignment the fused entry does not take
+                h = None
+            else:
+                native.check(rc, "gemm2_swiglu")
+        if h is None:
+            gemm(x2, w, out=gu.view(-1, F2))
+            h = _swiglu_raw(gu)
+        ctx.save_for_backward(x, w, gu)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, w, gu = ctx.saved_tensors
+        sw = _NoCtx()
+        sw.saved_tensors = (gu,)
+        with torch.no_grad():
+            dgu = _SwiGLU.backward(sw, dh)
+        dgu2 = dgu.reshape(-1, dgu.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = gemm(dgu2, w, b_mn=True).view_as(x) if ctx.needs_input_grad[0] else None
+        dw = _weight_grad(ctx.main_grad, dgu2, x2, w, ctx.needs_input_grad[1])
+        return dx, dw, None
+
+
+def linear_swiglu(x, w, main_grad=None):
+    """``silu(x w1^T) * (x w3^T)`` for the packed ``w = [w1; w3]`` ([2F, K]); one GEMM launch on CUDA."""
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    return _LinearSwiGLU.apply(x, w, main_grad)
+
+
 # --------------------------------------------------------------------------- #
 # Per-op selective activation checkpointing: the outputs of GEMMs and of attention are kept, the
 # cheap element-wise producers of a GEMM's input (SwiGLU, RMSNorm) are recomputed in the backward
@@ -652,6 +705,70 @@ class _AttentionPacked(torch.autograd.Function):
                                                      status_word(qkv.device).data_ptr(), native.stream_ptr()),
                      "attention_bwd")
         return dqkv, None, None, None
+
+
+class _QKVRopeAttention(torch.autograd.Function):
+    """``attention(rope(x W^T))`` for the packed ``W = [wq; wk; wv]`` as one autograd node on the own kernels:
+    the rotary embedding is applied to the q and k columns in the projection's epilogue (``tplr_gemm2_rope``) and
+    undone for dq and dk where the attention backward writes them (``tplr_attention_bwd_unrope``), so neither
+    pass runs a separate rotation over the projection or its gradient.  One node, because the gradient that
+    leaves the attention backward is already the one of the un-rotated projection."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad, cos, sin, n_heads, n_kv, hd):
+        B, S, _ = x.shape
+        C = w.shape[0]
+        x2 = x.reshape(-1, x.shape[-1])
+        qkv = torch.empty(B, S, C, dtype=x.dtype, device=x.device)
+        st = status_word(x.device).data_ptr()
+        L = native.lib()
+        native.check(L.tplr_gemm2_rope(x2.data_ptr(), w.data_ptr(), qkv.data_ptr(), x2.shape[0], C, x2.shape[1], x2.stride(0),
+                                       w.stride(0), C, cos.data_ptr(), sin.data_ptr(), S, (n_heads + n_kv) * hd, hd, st,
+                                       native.stream_ptr()), "gemm2_rope")
+        out = torch.empty(B, S, n_heads * hd, dtype=x.dtype, device=x.device)
+        lse = torch.empty(B, n_heads, S, dtype=torch.float32, device=x.device)
+        native.check(L.tplr_attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, n_heads, n_kv, qkv.stride(1),
+                                          out.stride(1), hd ** -0.5, st, native.stream_ptr()), "attention_fwd")
+        ctx.save_for_backward(x, w, qkv, out, lse, cos, sin)
+        ctx.main_grad, ctx.dims = main_grad, (n_heads, n_kv, hd)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w, qkv, out, lse, cos, sin = ctx.saved_tensors
+        n_heads, n_kv, hd = ctx.dims
+        B, S, C = qkv.shape
+        do = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq32 = torch.zeros(B, S, n_heads * hd, dtype=torch.float32, device=qkv.device)
+        delta = torch.empty(B, n_heads, S, dtype=torch.float32, device=qkv.device)
+        native.check(native.lib().tplr_attention_bwd_unrope(
+            qkv.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq32.data_ptr(), dqkv.data_ptr(),
+            B, S, n_heads, n_kv, qkv.stride(1), out.stride(1), hd ** -0.5, cos.data_ptr(), sin.data_ptr(),
+            status_word(qkv.device).data_ptr(), native.stream_ptr()), "attention_bwd_unrope")
+        del dq32, delta
+        d2 = dqkv.view(-1, C)
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = gemm(d2, w, b_mn=True).view_as(x) if ctx.needs_input_grad[0] else None
+        dw = _weight_grad(ctx.main_grad, d2, x2, w, ctx.needs_input_grad[1])
+        return dx, dw, None, None, None, None, None, None
+
+
+def rope_attention_projection(x, w, cos, sin, n_heads: int, n_kv: int, hd: int, main_grad=None):
+    """Causal attention of the rotary-embedded packed projection ``x @ w.T`` (``w = [wq; wk; wv]``); returns
+    [B, S, H * hd].  On the own kernels this is one autograd node with the rotation inside the GEMM and attention
+    kernels; elsewhere the projection, the rotation and the attention are three."""
+    if main_grad is None:
+        main_grad = getattr(w, "main_grad", None)
+    B, S, K = x.shape
+    if (FUSED_PROJECTIONS and _ATTN_BACKEND == "tcgen05" and _GEMM_BACKEND == "tcgen05_2sm" and _native_ok(x, w) and x.dtype == torch.bfloat16
+            and hd == 128 and S % 128 == 0 and n_heads % n_kv == 0 and x.is_contiguous() and w.stride(1) == 1
+            and w.stride(0) % 8 == 0 and K % 8 == 0 and w.shape[0] % 8 == 0 and cos.is_cuda and cos.dtype == torch.float32
+            and cos.is_contiguous() and sin.is_contiguous() and cos.shape[0] >= S and cos.shape[1] == hd // 2
+            and cos.data_ptr() % 16 == 0 and sin.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return _QKVRopeAttention.apply(x, w, main_grad, cos, sin, n_heads, n_kv, hd)
+    qkv = rope(_Linear.apply(x, w, main_grad), cos, sin, n_heads + n_kv, hd)
+    return attention_packed(qkv, n_heads, n_kv, hd)
 
 
 _attn_fallback_seen: set = set()

@@ -81,6 +81,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_cast_bf16": [vp, vp, ll, vp],
         "tplr_attention_set_bwd_variant": [i],
         "tplr_compress_set_variant": [i],
+        "tplr_gemm2_swiglu": [vp, vp, vp, vp, i, i, i, ll, ll, ll, ll, vp, vp],
+        "tplr_gemm2_rope": [vp, vp, vp, i, i, i, ll, ll, ll, vp, vp, i, i, i, vp, vp],
+        "tplr_attention_bwd_unrope": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp, vp, vp],
         "tplr_attention_fwd": [vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_attention_bwd": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_gemm_bf16": [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, vp, i, vp],

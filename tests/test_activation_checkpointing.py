@@ -66,8 +66,22 @@ def test_model_factory_reads_the_mode_from_the_hparams(tmp_path):
 
 @pytest.mark.gpu
 def test_per_op_policy_on_the_native_kernels():
-    """bf16 on CUDA: the recomputed norms / SwiGLU come from the same kernels as the stored ones would."""
-    l0, g0, b0 = _run("none", device="cuda", dtype=torch.bfloat16)
-    l, g, b = _run("selective", "op", device="cuda", dtype=torch.bfloat16)
-    assert abs(l - l0) < 1e-6 and b < b0
-    assert (g - g0).abs().max().item() <= 1e-6 * max(g0.abs().max().item(), 1.0)
+    """bf16 on CUDA.  With the projections' element-wise work in separate launches both modes run the same kernels on
+    the same values and agree to the last bit; with it in the GEMM epilogues (the default) the plain pass forms
+    silu(g) * u from the fp32 accumulators while the per-op mode recomputes it from the stored bf16 g and u, so the
+    two differ by that rounding."""
+    from templar_b200.ops import functional as OF
+
+    prev = OF.FUSED_PROJECTIONS
+    try:
+        OF.FUSED_PROJECTIONS = False
+        l0, g0, b0 = _run("none", device="cuda", dtype=torch.bfloat16)
+        l, g, b = _run("selective", "op", device="cuda", dtype=torch.bfloat16)
+        assert abs(l - l0) < 1e-6 and b < b0
+        assert (g - g0).abs().max().item() <= 1e-6 * max(g0.abs().max().item(), 1.0)
+        OF.FUSED_PROJECTIONS = True
+        lf, gf, bf = _run("none", device="cuda", dtype=torch.bfloat16)
+        assert abs(lf - l0) < 5e-3 and bf <= b0
+        assert ((gf - g0).norm() / g0.norm()).item() < 3e-2
+    finally:
+        OF.FUSED_PROJECTIONS = prev

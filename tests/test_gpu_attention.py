@@ -95,3 +95,52 @@ def test_attention_matches_sdpa_backend_in_model_block():
     finally:
         OF.set_attention_backend("tcgen05")
     assert (a.float() - b.float()).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("B,S,H,KV,K", [(2, 256, 4, 2, 512), (1, 384, 3, 1, 192), (8, 2048, 16, 8, 2048)])
+def test_projection_rope_attention_as_one_node_matches_the_three_node_path(B, S, H, KV, K):
+    """Rotary embedding in the projection's epilogue and its inverse in the attention backward's outputs, against the
+    projection, the in-place rotation kernel and the attention as separate autograd nodes (which other tests pin to
+    fp32 PyTorch), and against an fp32 PyTorch evaluation of the whole expression."""
+    from templar_b200.ops import functional as OF
+
+    hd = 128
+    torch.manual_seed(B * S + H)
+    x = (torch.randn(B, S, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    cos, sin = OF.rope_tables(S + 64, hd, 10000.0, "cuda")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    dout = torch.randn(B, S, H * hd, device="cuda").to(torch.bfloat16)
+    OF.status_word("cuda").zero_()
+
+    def run(fused):
+        xx, ww = x.clone().requires_grad_(), w.clone().requires_grad_()
+        if fused:
+            from templar_b200.ops import native
+            n0 = native.launch_count
+            out = OF.rope_attention_projection(xx, ww, cos, sin, H, KV, hd)
+            assert native.launch_count - n0 == 2    # projection with the rotation, attention: no rotation pass
+        else:
+            out = OF.attention_packed(OF.rope(OF.linear(xx, ww), cos, sin, H + KV, hd), H, KV, hd)
+        out.backward(dout)
+        return out.float(), xx.grad.float(), ww.grad.float()
+
+    o1, gx1, gw1 = run(True)
+    o0, gx0, gw0 = run(False)
+    torch.cuda.synchronize()
+    assert int(OF.status_word("cuda").item()) == 0
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()      # noqa: E731
+    # same arithmetic up to where the bf16 rounding of q and k happens (before the rotation there, after it here)
+    assert rel(o1, o0) < 1.5e-2 and rel(gx1, gx0) < 2e-2 and rel(gw1, gw0) < 2e-2, (rel(o1, o0), rel(gx1, gx0), rel(gw1, gw0))
+    if B * S <= 1024:
+        xf, wf = x.float().requires_grad_(), w.float().requires_grad_()
+        qkv = OF._rope_torch(xf @ wf.t(), cos, sin, (H + KV) * hd, hd, False)
+        q, k, v = OF._split_qkv(qkv, H, KV, hd)
+        k, v = (t.repeat_interleave(H // KV, dim=2) for t in (k, v))
+        ref = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                               is_causal=True).transpose(1, 2).reshape(B, S, H * hd)
+        ref.backward(dout.float())
+        e_fused = (rel(o1, ref), rel(gx1, xf.grad), rel(gw1, wf.grad))
+        e_three = (rel(o0, ref), rel(gx0, xf.grad), rel(gw0, wf.grad))
+        assert max(e_fused) < 3e-2, (e_fused, e_three)
+        assert all(a < 1.5 * b + 2e-3 for a, b in zip(e_fused, e_three)), (e_fused, e_three)
