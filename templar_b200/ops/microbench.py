@@ -83,6 +83,40 @@ def bench_gemm(a):
     print(json.dumps(rec))
 
 
+def bench_fused(a):
+    """The projections whose element-wise consumers run in the GEMM epilogue, against the same work as separate launches:
+    [w1; w3] projection + SwiGLU (forward), and packed q/k/v projection + rotary embedding + attention (forward, and
+    forward + backward, where the inverse rotation is folded into the attention backward's outputs)."""
+    T, D, Fd = a.m, a.k, a.n // 2
+    B, S, H, KV, hd = a.batch, a.seq, a.heads, a.kv_heads, 128
+    x = (torch.randn(T, D, device="cuda") * 0.5).to(torch.bfloat16)
+    w13 = (torch.randn(2 * Fd, D, device="cuda") / D ** 0.5).to(torch.bfloat16)
+    rec = {"case": "fused_projections", "T": T, "D": D, "F": Fd, "B": B, "S": S, "H": H, "KV": KV}
+    with torch.no_grad():
+        for name, flag in (("fused", True), ("separate", False)):
+            OF.FUSED_PROJECTIONS = flag
+            rec[f"swiglu_projection_{name}_ms"], _ = time_ms(lambda: OF.linear_swiglu(x, w13), a.iters)
+    xq = (torch.randn(B, S, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    wq = (torch.randn((H + 2 * KV) * hd, D, device="cuda") / D ** 0.5).to(torch.bfloat16).requires_grad_()
+    wq.main_grad = torch.zeros(wq.shape, device="cuda")
+    cos, sin = OF.rope_tables(S, hd, 10000.0, "cuda")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    dout = torch.randn(B, S, H * hd, device="cuda").to(torch.bfloat16)
+    for name, flag in (("fused", True), ("separate", False)):
+        OF.FUSED_PROJECTIONS = flag
+        with torch.no_grad():
+            rec[f"qkv_rope_attention_fwd_{name}_ms"], _ = time_ms(
+                lambda: OF.rope_attention_projection(xq, wq, cos, sin, H, KV, hd), a.iters)
+
+        def fb():
+            xq.grad = None
+            OF.rope_attention_projection(xq, wq, cos, sin, H, KV, hd).backward(dout)
+        rec[f"qkv_rope_attention_fwdbwd_{name}_ms"], _ = time_ms(fb, a.iters)
+    OF.FUSED_PROJECTIONS = True
+    rec["status"] = int(OF.status_word("cuda").item())
+    print(json.dumps(rec))
+
+
 def bench_attention(a):
     """Own flash attention (forward, forward+backward) vs torch SDPA on the packed layout of one layer."""
     B, S, H, KV, hd = a.batch, a.seq, a.heads, a.kv_heads, 128
@@ -225,7 +259,7 @@ def bench_elementwise(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "compress", "quantize", "aggregate", "elementwise", "attention"])
+    ap.add_argument("case", choices=["gemm", "compress", "quantize", "aggregate", "elementwise", "attention", "fused"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=2048)
@@ -248,7 +282,7 @@ def main():
         from . import native
         native.lib().tplr_compress_set_variant(a.variant)
     {"gemm": bench_gemm, "compress": bench_compress, "quantize": bench_quantize, "aggregate": bench_aggregate,
-     "elementwise": bench_elementwise, "attention": bench_attention}[a.case](a)
+     "elementwise": bench_elementwise, "attention": bench_attention, "fused": bench_fused}[a.case](a)
 
 
 if __name__ == "__main__":
