@@ -314,3 +314,49 @@ def convert_titan_to_hf(titan_model: nn.Module, hparams: SimpleNamespace, save_p
                 json.dump(cfg, f, indent=2)
             torch.save(hf_sd, os.path.join(save_path, "pytorch_model.bin"))
     return hf_model if hf_model is not None else hf_sd
+
+
+# --------------------------------------------------------------------------------------- #
+# Deterministic-initialisation check
+# --------------------------------------------------------------------------------------- #
+def model_fingerprint(model: nn.Module) -> str:
+    """MD5 over the bytes of every parameter in ``named_parameters`` order (fp32 view), preceded by its name."""
+    import hashlib
+
+    h = hashlib.md5()
+    for name, p in model.named_parameters():
+        h.update(name.encode())
+        h.update(p.detach().float().cpu().contiguous().numpy().tobytes())
+    return h.hexdigest()
+
+
+def check_init(hparams: SimpleNamespace, role: str = "miner", device: str = "cpu", builds: int = 2) -> dict:
+    """Build the model ``builds`` times and compare the parameters: every node of the network must start from the
+    same weights, so two builds with the same hparams have to agree to the last bit (the check of the reference's
+    scripts/test_init.py).  Returns the fingerprints and the names of tensors that differ from the first build."""
+    first, prints, differing = None, [], []
+    for _ in range(builds):
+        m = initialize_torchtitan_model(hparams, role=role, device=device, world_size=1)
+        prints.append(model_fingerprint(m))
+        sd = {n: p.detach().float().cpu() for n, p in m.named_parameters()}
+        if first is None:
+            first = sd
+        else:
+            differing += [n for n in first if n not in sd or not torch.equal(first[n], sd[n])]
+        del m
+    return {"fingerprints": prints, "identical": len(set(prints)) == 1 and not differing, "differing": sorted(set(differing))}
+
+
+if __name__ == "__main__":          # python -m templar_b200.model_factory [--hparams-dir hparams] [--device cpu]
+    import argparse
+
+    from .hparams import load_hparams
+
+    _ap = argparse.ArgumentParser(description="check that the model initialisation is deterministic")
+    _ap.add_argument("--hparams-dir", default="hparams")
+    _ap.add_argument("--role", default="miner", choices=["miner", "validator", "evaluator"])
+    _ap.add_argument("--device", default="cpu")
+    _a = _ap.parse_args()
+    _rep = check_init(load_hparams(_a.hparams_dir), _a.role, _a.device)
+    print(json.dumps(_rep))
+    raise SystemExit(0 if _rep["identical"] else 1)
