@@ -286,9 +286,10 @@ class _AddRMSNorm(torch.autograd.Function):
             dhc = dh.contiguous() if dh is not None else None
             dx = torch.empty_like(h)
             dw_buf = mg if mg is not None else torch.zeros(D, dtype=torch.float32, device=h.device)
-            native.check(native.lib().tplr_add_rmsnorm_bwd(dyc.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
-                                                           dhc.data_ptr() if dhc is not None else None, dx.data_ptr(),
-                                                           dw_buf.data_ptr(), T, D, native.stream_ptr()), "add_rmsnorm_bwd")
+            native.check(native.lib().tplr_add_rmsnorm_bwd_v2(dyc.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                                              dhc.data_ptr() if dhc is not None else None, dx.data_ptr(),
+                                                              dw_buf.data_ptr(), T, D, status_word(h.device).data_ptr(),
+                                                              native.stream_ptr()), "add_rmsnorm_bwd")
             return dx, dx, (None if mg is not None else dw_buf.to(w.dtype)), None, None
         hf, g = h.float(), dy.float()
         xh = hf * rstd

@@ -68,6 +68,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, ll, i, vp],
         "tplr_add_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, ll, i, f, vp],
         "tplr_add_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, vp, ll, i, vp],
+        "tplr_add_rmsnorm_bwd_v2": [vp, vp, vp, vp, vp, vp, vp, ll, i, vp, vp],
         "tplr_rope": [vp, vp, vp, ll, i, i, i, ll, i, vp],
         "tplr_swiglu_fwd": [vp, vp, ll, i, vp],
         "tplr_swiglu_bwd": [vp, vp, vp, ll, i, vp],

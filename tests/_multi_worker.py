@@ -68,7 +68,7 @@ def main():
         for m in range(2):
             for r in my_ranks:
                 t = toks[r, m].to(dev)
-                engine.micro_step(t[:, :-1], t[:, 1:], 0.5 / (1 if engine.world_size > 1 else world))
+                engine.micro_step(t[:, :-1], t[:, 1:], 0.5 / (1 if engine.dp_size > 1 else world))
         engine.optimizer_step()
         own = None
         if engine.heap is not None:
@@ -208,6 +208,16 @@ def main():
     out["c_master_max_diff"] = (node.store.master_shard - cref.store.master_shard).abs().max().item()
     out["c_moved"] = (cref.store.master_shard - cref.theta0).abs().max().item()
     pg.barrier()                 # nobody's buffers are reused while a peer may still read them
+
+    # 8. replicas of the whole state (plain data parallelism): every rank is a copy of its own, the gradient is summed
+    #    over the copies with NCCL in buckets; same window as the sharded engine of section 1
+    reng = WindowEngine(build_model(args, device=dev, dtype=torch.bfloat16, seed=5), cfg, device=dev,
+                        replicate_group=dist.group.WORLD, replicate_size=world)
+    reng.REPLICATE_BUCKET = 1 << 20                       # several buckets even on this small model
+    run(reng, [rank], None)
+    out["r_status"] = reng.check_status()
+    out["r_master_max_diff"] = (reng.store.master_shard - ref.store.master_shard).abs().max().item()
+    out["r_moved"] = (ref.store.master_shard - ref.theta0).abs().max().item()
 
     heap.barrier()
     torch.cuda.synchronize()

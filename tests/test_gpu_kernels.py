@@ -140,7 +140,8 @@ def test_rmsnorm_fwd_bwd():
 def test_add_rmsnorm_fwd_bwd():
     """Residual add fused with RMSNorm (warp-per-row kernels) against fp32 autograd of the same math."""
     torch.manual_seed(1)
-    for D, T in ((256, 37), (1024, 300), (2048, 2051), (776, 19)):
+    # rows above 1024 elements take the bulk-copy-fed streaming backward: ragged last tile, many tiles per CTA
+    for D, T in ((256, 37), (1024, 300), (2048, 2051), (776, 19), (1536, 999), (2048, 16385)):
         res = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
         delta = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
         w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
@@ -156,6 +157,41 @@ def test_add_rmsnorm_fwd_bwd():
         assert torch.allclose(res.grad.float(), rf.grad, atol=4e-2, rtol=2e-2)
         assert torch.equal(res.grad, delta.grad)
         assert torch.allclose(w.grad.float(), wf.grad, atol=0.05 * T ** 0.5, rtol=3e-2)
+
+
+def test_streaming_norm_backward_equals_the_warp_per_row_kernel():
+    """Same arithmetic in the same order per row: dx bit-equal, dw equal up to the order of the atomic adds; with and
+    without a residual gradient and without a weight-gradient target."""
+    from templar_b200.ops import native
+
+    L = native.lib()
+    torch.manual_seed(3)
+    for D, T, with_res in ((2048, 4099, True), (2048, 4096, False), (1280, 777, True)):
+        dy, x = (torch.randn(T, D, device=DEV).to(torch.bfloat16) for _ in range(2))
+        dres = torch.randn(T, D, device=DEV).to(torch.bfloat16) if with_res else None
+        w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5).contiguous()
+        outs = []
+        for v2 in (False, True):
+            dx = torch.full((T, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+            dw = torch.zeros(D, device=DEV)
+            args = [dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr() if with_res else None,
+                    dx.data_ptr(), dw.data_ptr(), T, D]
+            if v2:
+                native.check(L.tplr_add_rmsnorm_bwd_v2(*args, OF.status_word(DEV).data_ptr(), native.stream_ptr()), "bwd_v2")
+            else:
+                native.check(L.tplr_add_rmsnorm_bwd(*args, native.stream_ptr()), "bwd")
+            outs.append((dx, dw))
+        torch.cuda.synchronize()
+        assert int(OF.status_word(DEV).item()) == 0
+        assert torch.equal(outs[0][0], outs[1][0]), (D, T)
+        assert torch.allclose(outs[0][1], outs[1][1], rtol=1e-4, atol=1e-3 * T ** 0.5), (D, T)
+    # no weight-gradient target
+    dx = torch.empty(T, D, device=DEV, dtype=torch.bfloat16)
+    native.check(L.tplr_add_rmsnorm_bwd_v2(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), None,
+                                           T, D, OF.status_word(DEV).data_ptr(), native.stream_ptr()), "bwd_v2")
+    torch.cuda.synchronize()
+    assert torch.isfinite(dx.float()).all() and int(OF.status_word(DEV).item()) == 0
 
 
 def test_rope_matches_complex_multiply():

@@ -62,6 +62,9 @@ def test_two_rank_runtime_and_window():
         # co-located nodes: payloads read from the owners' memory == the same payloads staged in slots
         assert r["c_fresh"] and r["c_status"] == 0 and r["c_moved"] > 1e-5, r
         assert r["c_master_max_diff"] == 0.0, r
+        # replicas of the whole state with the gradient all-reduced over NCCL: the single-rank window on all data
+        assert r["r_status"] == 0 and r["r_moved"] > 1e-4, r
+        assert r["r_master_max_diff"] < 2e-3 * max(r["scale"], 1.0), r
         if "q_val_max_diff" in r:
             assert r["q_val_max_diff"] < 0.05 * r["q_val_scale"], r
             assert r["q_codes_equal"] > 0.9, r
