@@ -113,6 +113,18 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with descriptors given as (low word, high word): the low word carries the start address (bytes >> 4), so the
+// issuing thread advances an operand by one 32-bit add instead of rebuilding a 64-bit descriptor per instruction.
+__device__ __forceinline__ void umma_bf16_pair_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                    uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -514,6 +526,13 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         bool ok = true;
         Work w;
         work_init(p, w, pair);
+        // descriptors of stage 0, built once: a stage or a k step only moves the start address (bytes >> 4 in the low
+        // word; the whole ring lies below 256 KB, so the additions never carry out of the 14-bit address field).
+        // The issuing thread is one lane: every instruction it does not execute per MMA is tensor-pipe time.
+        const DescBase dA0 = A_MN ? desc_base(sA, BK * 128, 1024) : desc_base(sA, 16, 1024);
+        const DescBase dB0 = B_MN ? desc_base(sB, BK * 128, 1024) : desc_base(sB, 16, 1024);
+        constexpr uint32_t A_KSTEP = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4, B_KSTEP = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+        uint32_t s = 0, ph = 0;                          // ring position of `it` (no division in the loop)
         for (; ok && work_get(p, w, num_tiles, k_blocks_all, k_per); work_next(p, w), ++tile_i) {
           const int k_blocks = w.nkb;
           const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
@@ -521,20 +540,15 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * TILE_N;
           for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
             if (!(ok = mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag))) break;
             tcgen05_fence_after();
-            const uint32_t a_base = sA + s * A_STAGE, b_base = sB + s * B_STAGE;
+            const uint32_t a_lo = dA0.lo + s * (A_STAGE >> 4), b_lo = dB0.lo + s * (B_STAGE >> 4);
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              const uint64_t da = A_MN ? make_desc(a_base + kk * (UMMA_K * 128), BK * 128, 1024)
-                                       : make_desc(a_base + kk * (UMMA_K * 2), 16, 1024);
-              const uint64_t db = B_MN ? make_desc(b_base + kk * (UMMA_K * 128), BK * 128, 1024)
-                                       : make_desc(b_base + kk * (UMMA_K * 2), 16, 1024);
-              umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-            }
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_bf16_pair_lohi(d_tmem, a_lo + kk * A_KSTEP, dA0.hi, b_lo + kk * B_KSTEP, dB0.hi, idesc,
+                                  (kb > 0 || kk > 0) ? 1u : 0u);
             umma_commit_pair(smem_u32(&bar_empty[s]));
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
           }
           if (ok) umma_commit_pair(smem_u32(&bar_tfull[acc]));
         }
