@@ -25,6 +25,7 @@ def run(grank, world, replicas, groups, shard_params=False, muon=False):
     extra = dict(inner_optimizer="muon", inner_lr=0.02, muon_momentum=0.9) if muon else {}
     eng = WindowEngine(model, EngineConfig(shard_params=shard_params, max_peers=2, **extra), rank=grank % shards,
                        world_size=shards, group=shard_group, replicate_group=rep_group, replicate_size=replicas)
+    eng.REPLICATE_BUCKET = 10_000                  # several all-reduce buckets per step even on this small model
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, 256, (2, 2, world, 2, 33), generator=g)           # [window, step, rank, batch, seq + 1]
     losses = []
