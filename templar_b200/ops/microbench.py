@@ -251,6 +251,18 @@ def bench_elementwise(a):
                                              1.0, 1.0, gsq.data_ptr(), 1, native.stream_ptr()), "adamw")
 
     cases["adamw"] = (adamw, n * (4 * 4 + 4 * 3 + 4 + 2))      # the gradient is zeroed in the same pass
+    # the backward kernel of add+RMSNorm alone (three distinct bf16 inputs, one output, fp32 weight gradient)
+    b_dy, b_x, b_dres = (torch.randn(T, D, device="cuda").to(torch.bfloat16) for _ in range(3))
+    b_dx = torch.empty(T, D, device="cuda", dtype=torch.bfloat16)
+    b_dw = torch.zeros(D, device="cuda")
+    b_rstd = torch.rsqrt(b_x.float().pow(2).mean(-1) + 1e-5).contiguous()
+
+    def norm_bwd():
+        native.check(native.lib().tplr_add_rmsnorm_bwd_v2(b_dy.data_ptr(), b_x.data_ptr(), w.data_ptr(), b_rstd.data_ptr(),
+                                                          b_dres.data_ptr(), b_dx.data_ptr(), b_dw.data_ptr(), T, D,
+                                                          OF.status_word("cuda").data_ptr(), native.stream_ptr()), "norm_bwd")
+
+    cases["add_rmsnorm_bwd_kernel"] = (norm_bwd, T * D * 2 * 4)
     for name, (fn, byts) in cases.items():
         med, best = time_ms(fn, a.iters)
         print(json.dumps({"case": name, "ms_median": med, "gbs": byts / med / 1e6,
