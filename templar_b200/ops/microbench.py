@@ -203,6 +203,21 @@ def bench_aggregate(a):
                       "peaks": pk["source"], "status": eng.check_status()}))
 
 
+def bench_overlap(a):
+    """Pairwise index overlap of the staged peers' packed payloads (the validator's copy check), one kernel."""
+    from ..utils.synthetic import synthetic_payload
+
+    eng = _engine(a.model, a.topk, a.peers)
+    for j in range(a.peers):
+        eng.load_peer_payload(j, synthetic_payload(eng.layout, 7 + j, device="cuda"))
+    med, best = time_ms(lambda: eng.index_overlap(a.peers), a.iters)
+    byts = a.peers * eng.layout.idx_bytes
+    pk = peaks()
+    print(json.dumps({"case": "index_overlap", "model": a.model, "peers": a.peers, "topk": a.topk, "ms_median": med,
+                      "ms_best": best, "index_bytes": byts, "gbs": byts / med / 1e6, "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"],
+                      "peaks": pk["source"], "status": eng.check_status()}))
+
+
 def bench_elementwise(a):
     pk = peaks()
     T, D, F, V = (2048, 2048, 8192, 32000) if a.small else (16384, 2048, 8192, 32000)
@@ -263,15 +278,54 @@ def bench_elementwise(a):
                                                           OF.status_word("cuda").data_ptr(), native.stream_ptr()), "norm_bwd")
 
     cases["add_rmsnorm_bwd_kernel"] = (norm_bwd, T * D * 2 * 4)
+    # --compare: the same operations as the reference's stack runs them (PyTorch eager ops on the same tensors:
+    # torchtitan's RMSNorm / SwiGLU / cross entropy modules and torch.optim.AdamW(fused=True) + clip_grad_norm_)
+    library = {}
+    if a.compare:
+        import torch.nn.functional as TF
+
+        xr, dr = res.detach().clone().requires_grad_(), delta.detach().clone().requires_grad_()
+        wr = wn.detach().clone().requires_grad_()
+        hr = h.clone().requires_grad_()
+        lr_ = logits.clone().requires_grad_()
+        pm = torch.nn.Parameter(master.clone())
+        opt = torch.optim.AdamW([pm], lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
+
+        def lib_norm():
+            xr.grad = dr.grad = wr.grad = None
+            hh = xr + dr
+            y = TF.rms_norm(hh, (D,), wr, 1e-5)
+            torch.autograd.backward([hh, y], [x, x])
+
+        def lib_swiglu():
+            hr.grad = None
+            (TF.silu(hr[:, :F]) * hr[:, F:]).backward(dyh)
+
+        def lib_ce():
+            lr_.grad = None
+            TF.cross_entropy(lr_.float(), labels).backward()
+
+        def lib_adamw():
+            pm.grad = grad
+            torch.nn.utils.clip_grad_norm_([pm], 1.0)
+            opt.step()
+
+        library = {"rmsnorm_fwd": lambda: TF.rms_norm(x, (D,), w, 1e-5), "add_rmsnorm_fwd_bwd": lib_norm,
+                   "swiglu_fwd": lambda: TF.silu(h[:, :F]) * h[:, F:], "swiglu_fwd_bwd": lib_swiglu,
+                   "cross_entropy_fwd_bwd": lib_ce, "adamw": lib_adamw}
     for name, (fn, byts) in cases.items():
         med, best = time_ms(fn, a.iters)
-        print(json.dumps({"case": name, "ms_median": med, "gbs": byts / med / 1e6,
-                          "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"], "peaks": pk["source"]}))
+        rec = {"case": name, "ms_median": med, "gbs": byts / med / 1e6, "frac_of_hbm": byts / med / 1e6 / pk["hbm_gbs"],
+               "peaks": pk["source"]}
+        if name in library:
+            rec["torch_ms"], _ = time_ms(library[name], a.iters)
+            rec["vs_torch"] = rec["torch_ms"] / med
+        print(json.dumps(rec))
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "compress", "quantize", "aggregate", "elementwise", "attention", "fused"])
+    ap.add_argument("case", choices=["gemm", "compress", "quantize", "aggregate", "overlap", "elementwise", "attention", "fused"])
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=2048)
@@ -294,7 +348,7 @@ def main():
         from . import native
         native.lib().tplr_compress_set_variant(a.variant)
     {"gemm": bench_gemm, "compress": bench_compress, "quantize": bench_quantize, "aggregate": bench_aggregate,
-     "elementwise": bench_elementwise, "attention": bench_attention, "fused": bench_fused}[a.case](a)
+     "elementwise": bench_elementwise, "attention": bench_attention, "fused": bench_fused, "overlap": bench_overlap}[a.case](a)
 
 
 if __name__ == "__main__":
