@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--breakdown", action="store_true",
                     help="also print per-phase device times of one extra window (stderr; not part of the timed region)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="also run one extra window under torch.profiler and print the summed duration of every kernel at "
+                         "in-window clocks plus the total of the gaps between kernels (stderr; diagnostic, not a timing)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -286,7 +289,36 @@ def run_ours(a):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return {n: round(float(v), 3) for n, v in zip(names, t.tolist())}
 
+    def kernel_times():
+        """One window under torch.profiler (CUPTI): where the device time of a window goes at the clocks the window
+        really runs at, and how much of it is idle between kernels.  Diagnostic only: nothing here is a reported timing."""
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            window(False, a.warmup + a.steps + 1)
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+        if not evs:
+            return {}
+        by = {}
+        for e in evs:
+            name = e.name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+            name = name.split("(")[0].replace("void ", "")[:60]
+            d = by.setdefault(name, [0, 0.0])
+            d[0] += 1
+            d[1] += (e.time_range.end - e.time_range.start) / 1e3
+        gaps = sum(max(0, b_.time_range.start - a_.time_range.end) for a_, b_ in zip(evs, evs[1:])) / 1e3
+        top = sorted(by.items(), key=lambda kv: -kv[1][1])[:24]
+        return {"kernels": len(evs), "kernel_ms_sum": round(sum(v[1] for v in by.values()), 2),
+                "span_ms": round((evs[-1].time_range.end - evs[0].time_range.start) / 1e3, 2), "gap_ms_sum": round(gaps, 2),
+                "by_kernel_ms": {k: [v[0], round(v[1], 2)] for k, v in top}}
+
     ms_total, launches, clocks = timed(False, a.steps, a.warmup)
+    if a.kernel_times:
+        kt = kernel_times()
+        if rank == 0:
+            print("kernel_times " + json.dumps(kt), file=sys.stderr)
     if a.breakdown:
         bd = breakdown()
         if rank == 0:

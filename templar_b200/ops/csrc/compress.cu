@@ -1121,7 +1121,7 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
     // (k distinct keys are at least that large), so only the keys at or above it (a few dozen for k = 32)
     // are candidates; they are compacted into shared memory and the exact threshold is found by counting
     // among them.  No shared-memory atomics: the histogram of the radix select below serialises on the
-    // few exponent values that the keys share.  More candidates than fit (ties, all-zero chunks) or
+    // few exponent values that the keys share.  More candidates than fit (many equal keys) or
     // k > 128 take the radix select.
     unsigned int prefix = 0u, mask = 0u;
     int krem = k;
@@ -1147,7 +1147,10 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
         if (rank == k - 1) s_thr[ch] = m;
       }
       __syncthreads();
-      const unsigned int t0 = s_thr[ch];
+      // zero keys never are candidates: a chunk with fewer than k non-zero coefficients (rows of the embedding that
+      // no token touched, a null round) has t0 == 0 and is resolved without any search: all non-zero keys and the
+      // first k - n_cand zeros in order
+      const unsigned int t0 = s_thr[ch] ? s_thr[ch] : 1u;
       int cnt = 0;
 #pragma unroll
       for (int i = 0; i < 32; ++i) cnt += (__float_as_uint(v[i]) & 0x7fffffffu) >= t0;
@@ -1185,8 +1188,8 @@ __global__ void __launch_bounds__(NT, 2) compress_tc_kernel(const CompressArgs a
           if (gt < k && k <= ge) { s_bin[ch] = (int)cj; s_krem[ch] = k - gt; }   // ties write the same pair
         }
         __syncthreads();
-        prefix = (unsigned int)s_bin[ch];
-        krem = s_krem[ch];
+        if (n_cand < k) { prefix = 0u; krem = k - n_cand; }      // sparse chunk (only possible with t0 == 1)
+        else { prefix = (unsigned int)s_bin[ch]; krem = s_krem[ch]; }
       }
       __syncthreads();            // s_hist, s_wsum, s_bin and s_krem are reused below
     }

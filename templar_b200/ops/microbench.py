@@ -80,7 +80,63 @@ def bench_gemm(a):
         med_c, _ = time_ms(lambda: torch.matmul(Am, Bm), a.iters)
         rec["cublas_ms"] = med_c
         rec["vs_cublas"] = med_c / med
+    if a.sustain > 0:
+        # back-to-back launches for a.sustain seconds (what a training step sees: the board sits at its power cap);
+        # SM clock and board power are READ through NVML while the loop runs
+        lib_out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        Am, Bm = (A.t() if a_mn else A), (B if b_mn else B.t())
+        rec["sustained_own"] = sustained(lambda: OF.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=(a.layout == "tn")),
+                                         fl, a.sustain)
+        rec["sustained_library_bf16_out"] = sustained(lambda: torch.matmul(Am, Bm, out=lib_out), fl, a.sustain)
     print(json.dumps(rec))
+
+
+def sustained(fn, flops: float, seconds: float) -> dict:
+    """ms per launch and TFLOP/s over ``seconds`` of back-to-back launches, with the median SM clock and the mean board
+    power of the second half of the loop (NVML reads from a sampling thread; absent NVML: timing only)."""
+    import threading
+    import time
+
+    samples, stop = [], threading.Event()
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+
+        def sample():
+            while not stop.is_set():
+                samples.append((pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM),
+                                pynvml.nvmlDeviceGetPowerUsage(handle) / 1e3))
+                time.sleep(0.1)
+    except Exception:  # noqa: BLE001
+        sample = None
+    for _ in range(20):
+        fn()
+    torch.cuda.synchronize()
+    th = threading.Thread(target=sample) if sample else None
+    if th:
+        th.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.time()
+    e0.record()
+    while time.time() - t0 < seconds:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    stop.set()
+    if th:
+        th.join()
+    ms = e0.elapsed_time(e1) / n
+    out = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "launches": n}
+    tail = samples[len(samples) // 2:]
+    if tail:
+        out["sm_mhz_median"] = sorted(c for c, _ in tail)[len(tail) // 2]
+        out["watts_mean"] = round(sum(p for _, p in tail) / len(tail), 1)
+    return out
 
 
 def bench_fused(a):
@@ -331,6 +387,9 @@ def main():
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
     ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="gemm: also run back-to-back launches for this many seconds (own kernel, then the library) and "
+                         "report the rate with the SM clock and board power read through NVML")
     ap.add_argument("--backend", default="tcgen05_2sm", choices=["tcgen05", "tcgen05_2sm"])
     ap.add_argument("--model", default="1B")
     ap.add_argument("--topk", type=int, default=32)
