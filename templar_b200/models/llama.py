@@ -137,8 +137,8 @@ class FeedForward(nn.Module):
         self.packed = None  # [w1; w3]
 
     def forward(self, x):
-        if self.packed is not None:
-            return self.w2(OF.linear_swiglu(x, self.packed[0], self.packed[1]))      # activation in the GEMM's epilogue
+        if self.packed is not None:      # the activation and its backward run in the epilogues of the two projections
+            return OF.feed_forward(x, self.packed[0], self.w2.weight, self.packed[1], getattr(self.w2.weight, "main_grad", None))
         h = OF.linear(x, torch.cat((self.w1.weight, self.w3.weight), dim=0))
         return self.w2(OF.swiglu(h))
 

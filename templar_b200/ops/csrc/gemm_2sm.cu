@@ -58,6 +58,11 @@ struct Gemm2Params {
                                      // gate rows [128 j, 128 j + 128) (staged by the even CTA) with up rows swiglu_f + the same
                                      // (odd CTA), so every accumulator row holds g and u of the same 128 features; the epilogue
                                      // stores both into C [M, 2 * swiglu_f] and silu(g) * u into tmCr[0]'s tensor [M, swiglu_f]
+  // backward of the SwiGLU in the epilogue of the down projection's data gradient (EPI 5): the accumulator tile is
+  // dh[M, swiglu_f] = dY W2; gu is the forward's packed [M, 2 * swiglu_f] projection (gate | up), leading dimension ld_gu;
+  // the epilogue stores dg | du (bf16) through tmC, a map over the [M, 2 * swiglu_f] gradient of that projection
+  const __nv_bfloat16* gu;
+  long long ld_gu;
   // rotary embedding in the epilogue (EPI 4): the first rope_cols columns of C are heads of rope_dh columns whose
   // interleaved pairs (2i, 2i + 1) are rotated by the angle of (row % rope_s, i); tables [rope_s, rope_dh / 2] fp32
   const float* rope_cos;
@@ -217,7 +222,7 @@ __device__ __forceinline__ void epilogue_direct(const Gemm2Params& p, uint32_t t
     tmem_ld32(tmem_acc + c * 32 + ((uint32_t)(quad * 32) << 16), r);
     const int col0 = n0 + c * 32;
     if (row < p.M && col0 < p.N) {
-      if (EPI == 0 || EPI >= 3) {
+      if (EPI == 0 || EPI >= 3) {      // (the epilogue modes 3-5 never take this path: their entries require TMA stores)
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
         for (int e = 0; e < 32 && col0 + e < p.N; ++e) crow[e] = __float2bfloat16(__uint_as_float(r[e]));
       } else {
@@ -404,8 +409,75 @@ __device__ __forceinline__ void epilogue_swiglu(const Gemm2Params& p, uint32_t t
   }
 }
 
+// Epilogue of the down projection's data gradient fused with the backward of the SwiGLU (EPI 5).  The accumulator row
+// holds dh for 256 features; with g and u of the same row and features read from the forward's packed projection,
+//   s = sigmoid(g),  du = dh * g * s,  dg = dh * u * s * (1 + g * (1 - s)),
+// and dg / du are stored (bf16) at columns f and swiglu_f + f of the packed gradient.  This replaces a pass that writes
+// dh, reads it back with g and u and writes dg | du (the backward of the reference's F.silu(w1(x)) * w3(x)).
+// Both staging buffers of the warp are in use at once (one box of dg, one of du), so a step waits until the two stores
+// of the previous step have read them.
+__device__ __forceinline__ void epilogue_swiglu_bwd(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int n0,
+                                                    uint32_t stage_base, uint32_t& n_boxes) {
+  const int row0 = m0 + quad * 32;
+  if (row0 >= p.M) return;                           // warp-uniform
+  const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+  const int row = min(row0 + lane, p.M - 1);
+  const __nv_bfloat16* grow = p.gu + (long long)row * p.ld_gu;
+  const uint32_t buf_g = stage_base, buf_u = stage_base + 4096u;
+#pragma unroll 1
+  for (int c = 0; c < TILE_N / 64; ++c) {
+    const int f0 = n0 + c * 64;
+    if (f0 >= p.swiglu_f) break;
+    if (n_boxes > 0) {                               // both buffers free: the previous step's stores have read them
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      // g and u of this lane's row, 32 features: 64 bytes each (the row base and the feature offset are multiples of 8)
+      uint4 gq[4], uq[4];
+      const uint4* gp = reinterpret_cast<const uint4*>(grow + f0 + hh * 32);
+      const uint4* up = reinterpret_cast<const uint4*>(grow + p.swiglu_f + f0 + hh * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { gq[q] = gp[q]; uq[q] = up[q]; }
+      uint32_t r[32];
+      tmem_ld32(tmem_acc + c * 64 + hh * 32 + lane_sel, r);
+      float dg[32], du[32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t gw[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w}, uw[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e]));
+          const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[e]));
+          const float gg[2] = {g2.x, g2.y}, uu[2] = {u2.x, u2.y};
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const float dh = __uint_as_float(r[8 * q + 2 * e + k]);
+            const float sg = __fdividef(1.f, 1.f + __expf(-gg[k]));
+            const float silu = gg[k] * sg;
+            du[8 * q + 2 * e + k] = dh * silu;
+            dg[8 * q + 2 * e + k] = dh * uu[k] * (sg + silu * (1.f - sg));
+          }
+        }
+      }
+      box_half(buf_g, lane, hh, dg);
+      box_half(buf_u, lane, hh, du);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&p.tmC, buf_g, f0, row0);
+      tma_store_2d(&p.tmC, buf_u, p.swiglu_f + f0, row0);
+      bulk_commit();
+    }
+    n_boxes += 2;
+  }
+}
+
 // EPI: 0 store bf16, 1 fp32 accumulate (C += acc), 2 store fp32, 3 fused SwiGLU of a packed [w1; w3] projection,
-// 4 store bf16 with the rotary embedding applied to the leading columns
+// 4 store bf16 with the rotary embedding applied to the leading columns, 5 backward of the SwiGLU on the data gradient
+// of the down projection
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ Gemm2Params p) {
@@ -571,6 +643,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * TILE_N;
         if (EPI == 3)      epilogue_swiglu(p, tmem_acc, quad, lane, m0, tn, sEpi + (uint32_t)quad * 8192u, n_boxes);
+        else if (EPI == 5) epilogue_swiglu_bwd(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
         else if (p.c_tma)  epilogue_tma<EPI>(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
         else               epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
         tcgen05_fence_before();
@@ -662,7 +735,7 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
   // all CTAs must be resident at once: compute CTAs wait for comm CTAs of the same launch
-  static int max_clusters[2][2][5] = {};
+  static int max_clusters[2][2][6] = {};
   int& mc = max_clusters[A_MN][B_MN][EPI];
   if (mc == 0) {
     cfg.gridDim = dim3(2 * (tplr_sm_count() / 2));
@@ -691,7 +764,7 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
   TPLR_GEMM2_CASE(0, 1, 0) TPLR_GEMM2_CASE(0, 1, 1) TPLR_GEMM2_CASE(0, 1, 2)
   TPLR_GEMM2_CASE(1, 1, 0) TPLR_GEMM2_CASE(1, 1, 1) TPLR_GEMM2_CASE(1, 1, 2)
   TPLR_GEMM2_CASE(1, 0, 0) TPLR_GEMM2_CASE(1, 0, 1) TPLR_GEMM2_CASE(1, 0, 2)
-  TPLR_GEMM2_CASE(0, 0, 3) TPLR_GEMM2_CASE(0, 0, 4)
+  TPLR_GEMM2_CASE(0, 0, 3) TPLR_GEMM2_CASE(0, 0, 4) TPLR_GEMM2_CASE(0, 1, 5)
 #undef TPLR_GEMM2_CASE
   return -104;
 }
@@ -770,6 +843,26 @@ TPLR_API int tplr_gemm2_swiglu(const void* X, const void* W, void* GU, void* H, 
   if (!make_map(&p.tmCr[0], H, F, M, ldh, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, false)) return -110;
   p.swiglu_f = F;
   return dispatch2(p, 0, 0, 3, 0, 0, (cudaStream_t)stream);
+}
+
+// dGU[M, 2F] = backward of the SwiGLU applied to dH = dY W2 (dY [M, K] bf16 K-major, W2 [K, F] bf16 with F contiguous:
+// the down projection's weight as stored), with GU [M, 2F] the forward's packed gate | up projection: one launch instead
+// of the data-gradient GEMM followed by an element-wise pass (see epilogue_swiglu_bwd).  F a multiple of 64, all tensors
+// 16-byte aligned with leading dimensions that are multiples of 8; -111 when this entry does not take the arguments.
+TPLR_API int tplr_gemm2_swiglu_bwd(const void* dY, const void* W2, const void* GU, void* dGU, int M, int F, int K,
+                                   long long lddy, long long ldw2, long long ldgu, long long lddgu, unsigned int* status,
+                                   void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if (F % 64 || ((uintptr_t)GU & 15) || ((uintptr_t)dGU & 15) || (ldgu % 8) || (lddgu % 8)) return -111;
+  Gemm2Params p = {};
+  // operands and tile grid of the [M, F] product; the output map then covers the [M, 2F] packed gradient
+  if (int r = fill_common(p, dY, W2, dGU, M, F, K, lddy, ldw2, lddgu, 0, 1, 0, status)) return r;
+  if (!p.c_tma) return -111;
+  if (!make_map(&p.tmC, dGU, 2LL * F, M, lddgu, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B, false)) return -110;
+  p.swiglu_f = F;
+  p.gu = (const __nv_bfloat16*)GU; p.ld_gu = ldgu;
+  return dispatch2(p, 0, 1, 5, 0, 0, (cudaStream_t)stream);
 }
 
 // QKV[M, N] = X W^T (bf16, W K-major) with the rotary embedding applied to the first rope_cols columns in the epilogue:

@@ -466,6 +466,66 @@ class _LinearSwiGLU(torch.autograd.Function):
         return dx, dw, None
 
 
+class _FeedForward(torch.autograd.Function):
+    """``swiglu(x W13^T) W2^T`` (``W13 = [w1; w3]``) as one autograd node on the own GEMM: the activation is formed in
+    the epilogue of the first projection (``tplr_gemm2_swiglu``) and its backward in the epilogue of the second
+    projection's data gradient (``tplr_gemm2_swiglu_bwd``), so neither direction runs an element-wise pass over the
+    [T, 2F] projection.  Saved for the backward pass: x, the packed projection and the activation (as the separate
+    nodes save them)."""
+
+    @staticmethod
+    def forward(ctx, x, w13, w2, mg13, mg2):
+        F2, Fd = w13.shape[0], w13.shape[0] // 2
+        x2 = x.reshape(-1, x.shape[-1])
+        T = x2.shape[0]
+        st = status_word(x.device).data_ptr()
+        gu = torch.empty(T, F2, dtype=x.dtype, device=x.device)
+        h = torch.empty(T, Fd, dtype=x.dtype, device=x.device)
+        native.check(native.lib().tplr_gemm2_swiglu(x2.data_ptr(), w13.data_ptr(), gu.data_ptr(), h.data_ptr(), T, Fd,
+                                                    x2.shape[1], x2.stride(0), w13.stride(0), F2, Fd, st, native.stream_ptr()),
+                     "gemm2_swiglu")
+        y = torch.empty(*x.shape[:-1], w2.shape[0], dtype=x.dtype, device=x.device)
+        gemm(h, w2, out=y.view(-1, w2.shape[0]))
+        ctx.save_for_backward(x, w13, w2, gu, h)
+        ctx.mg = (mg13, mg2)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w13, w2, gu, h = ctx.saved_tensors
+        mg13, mg2 = ctx.mg
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        T, Fd = gu.shape[0], gu.shape[1] // 2
+        dgu = torch.empty_like(gu)
+        native.check(native.lib().tplr_gemm2_swiglu_bwd(dy2.data_ptr(), w2.data_ptr(), gu.data_ptr(), dgu.data_ptr(), T, Fd,
+                                                        dy2.shape[1], dy2.stride(0), w2.stride(0), gu.stride(0), dgu.stride(0),
+                                                        status_word(x.device).data_ptr(), native.stream_ptr()),
+                     "gemm2_swiglu_bwd")
+        dw2 = _weight_grad(mg2, dy2, h, w2, ctx.needs_input_grad[2])
+        dx = gemm(dgu, w13, b_mn=True).view_as(x) if ctx.needs_input_grad[0] else None
+        dw13 = _weight_grad(mg13, dgu, x2, w13, ctx.needs_input_grad[1])
+        return dx, dw13, dw2, None, None
+
+
+def feed_forward(x, w13, w2, main_grad13=None, main_grad2=None):
+    """``(silu(x w1^T) * (x w3^T)) w2^T`` for the packed ``w13 = [w1; w3]`` ([2F, D]) and ``w2`` [D, F]."""
+    if main_grad13 is None:
+        main_grad13 = getattr(w13, "main_grad", None)
+    if main_grad2 is None:
+        main_grad2 = getattr(w2, "main_grad", None)
+    Fd = w13.shape[0] // 2
+    x2 = x.reshape(-1, x.shape[-1])
+    if (FUSED_PROJECTIONS and _GEMM_BACKEND == "tcgen05_2sm" and _native_ok(x2, w13, w2) and x.dtype == torch.bfloat16
+            and Fd % 128 == 0 and x2.is_contiguous() and w13.stride(1) == 1 and w2.stride(1) == 1 and w13.stride(0) % 8 == 0
+            and w2.stride(0) % 8 == 0 and x2.shape[1] % 8 == 0 and w2.shape[0] % 8 == 0
+            and all(t.data_ptr() % 16 == 0 for t in (x2, w13, w2))):
+        return _FeedForward.apply(x, w13, w2, main_grad13, main_grad2)
+    return _Linear.apply(linear_swiglu(x, w13, main_grad13), w2, main_grad2)
+
+
 def linear_swiglu(x, w, main_grad=None):
     """``silu(x w1^T) * (x w3^T)`` for the packed ``w = [w1; w3]`` ([2F, K]); one GEMM launch on CUDA."""
     if main_grad is None:

@@ -174,3 +174,48 @@ def test_fused_swiglu_projection_matches_fp32_reference(M, F, K, backend):
     for got, want in ((x.grad, xf.grad), (w.grad, wf.grad)):
         rel = (got.float() - want).norm() / want.norm()
         assert rel.item() < 2e-2, rel.item()
+
+
+@pytest.mark.parametrize("T,D,F", [(512, 256, 256), (300, 192, 384), (16384, 2048, 8192), (1000, 64, 128)])
+def test_feed_forward_with_both_swiglu_epilogues_matches_fp32_reference(T, D, F, backend):
+    """swiglu(x W13^T) W2^T as one node: activation in the first projection's epilogue, its backward in the epilogue of
+    the second projection's data gradient.  Output and all three gradients against autograd through the fp32 formula,
+    and against the node-per-op path (which other tests pin to fp32 PyTorch)."""
+    if backend != "tcgen05_2sm":
+        pytest.skip("the fused epilogues are modes of the CTA-pair kernel")
+    from templar_b200.ops import native
+
+    torch.manual_seed(T + F)
+    x = (torch.randn(T, D, device=DEV) * 0.5).to(torch.bfloat16)
+    w13 = (torch.randn(2 * F, D, device=DEV) / D ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn(D, F, device=DEV) / F ** 0.5).to(torch.bfloat16)
+    dy = torch.randn(T, D, device=DEV).to(torch.bfloat16)
+    OF.status_word(DEV).zero_()
+
+    def run(fused):
+        prev = OF.FUSED_PROJECTIONS
+        OF.FUSED_PROJECTIONS = fused
+        try:
+            xs, a, b = (t.clone().requires_grad_() for t in (x, w13, w2))
+            n0 = native.launch_count
+            y = OF.feed_forward(xs, a, b)
+            fwd = native.launch_count - n0
+            y.backward(dy)
+            return y.float(), xs.grad.float(), a.grad.float(), b.grad.float(), fwd, native.launch_count - n0
+        finally:
+            OF.FUSED_PROJECTIONS = prev
+
+    yf, *gf, fwd_f, all_f = run(True)
+    ys, *gs, fwd_s, all_s = run(False)
+    torch.cuda.synchronize()
+    assert int(OF.status_word(DEV).item()) == 0
+    assert fwd_f == 2 and all_f == 6 and fwd_s == 3 and all_s == 8      # one launch less in each direction
+    xf, af, bf = (t.float().requires_grad_() for t in (x, w13, w2))
+    gu = xf @ af.t()
+    ref = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ bf.t()
+    ref.backward(dy.float())
+    rel = lambda a_, b_: ((a_ - b_).norm() / b_.norm()).item()      # noqa: E731
+    errs_f = [rel(yf, ref)] + [rel(g, r.grad) for g, r in zip(gf, (xf, af, bf))]
+    errs_s = [rel(ys, ref)] + [rel(g, r.grad) for g, r in zip(gs, (xf, af, bf))]
+    assert max(errs_f) < 2e-2, (errs_f, errs_s)
+    assert all(a_ < 1.3 * b_ + 1e-3 for a_, b_ in zip(errs_f, errs_s)), (errs_f, errs_s)
