@@ -217,8 +217,8 @@ def run_ours(a):
         if heap is not None:
             own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
         eng.compress(own_slot_ptrs=own_ptrs)
-        for j in hosted:
-            eng.load_peer_payload(j // sworld, host_payload[j])
+        # peers' payloads: pinned host memory -> device slots on a side stream, beside this node's own compress
+        eng.load_peer_payloads_async([(j // sworld, host_payload[j]) for j in hosted])
         if sworld > 1:
             eng._barrier()
         eng.outer_step(a.peers)
@@ -271,8 +271,8 @@ def run_ours(a):
         if heap is not None:
             own_ptrs = (heap.peer_ptr(eng.own_idx, 0), heap.peer_ptr(eng.own_val, 0))
         eng.compress(own_slot_ptrs=own_ptrs)
-        for j in hosted:
-            eng.load_peer_payload(j // sworld, host_payload[j])
+        # peers' payloads: pinned host memory -> device slots on a side stream, beside this node's own compress
+        eng.load_peer_payloads_async([(j // sworld, host_payload[j]) for j in hosted])
         eng._mark("peer_payload_h2d")
         if sworld > 1:
             eng._barrier()

@@ -146,6 +146,8 @@ class WindowEngine:
         self._sumsq_scratch = z(native.lib().tplr_sumsq_blocks() if self.cuda else 1)
         self.window_open = False
         self.peer_group = None                    # set by LocalPeerGroup.attach(): co-located nodes on the same heap
+        self._h2d_stream = None                   # side stream of load_peer_payloads_async
+        self._h2d_pending = None                  # event: payloads staged on the side stream and not yet joined
         self.rank_payloads: dict = {}             # CPU stand-in for peer memory: rank -> (own_idx, own_val) copies
         model._window_engine = self
         model._param_gather = self.store.gather          # None unless shard_params: the model gates its blocks on it
@@ -629,6 +631,7 @@ class WindowEngine:
         self._mark("opt.replicate_allreduce")
 
     def _barrier(self) -> None:
+        self.join_payloads()                      # a barrier publishes this rank's slots to the ranks that pull from them
         if self.world_size > 1:
             if self.heap is not None and self.cuda:
                 self.heap.barrier()
@@ -873,6 +876,36 @@ class WindowEngine:
         self.peer_idx[slot][: idx_flat.numel()].copy_(idx_flat, non_blocking=non_blocking)
         self.peer_val[slot][: val_flat.numel()].copy_(val_flat, non_blocking=non_blocking)
 
+    def load_peer_payloads_async(self, items) -> None:
+        """Stage several peers' payloads (``[(slot, payload), ...]``, payloads as for :meth:`load_peer_payload`, host
+        tensors pinned) on a side stream: the copy engines and the small decode kernel run beside whatever the compute
+        stream is doing (this node's own compress, or the end of its backward pass).  The slots were last read by the
+        previous outer step, which the side stream waits for; everything that reads the slots
+        (:meth:`compute_peer_norms`, :meth:`outer_step`, :meth:`index_overlap`, :meth:`apply_single_peer`, the barrier
+        that publishes them to the other ranks) first joins the side stream (:meth:`join_payloads`)."""
+        if not self.cuda:
+            for slot, payload in items:
+                self.load_peer_payload(slot, payload)
+            return
+        if self._h2d_stream is None:
+            self._h2d_stream = torch.cuda.Stream(self.device)
+        side = self._h2d_stream
+        done = getattr(self, "_slots_read", None)
+        if done is not None:
+            side.wait_event(done)
+        with torch.cuda.stream(side):
+            for slot, payload in items:
+                self.load_peer_payload(slot, payload)
+            ev = torch.cuda.Event()
+            ev.record(side)
+        self._h2d_pending = ev
+
+    def join_payloads(self) -> None:
+        """The compute stream waits for the payloads staged by :meth:`load_peer_payloads_async` (no host wait)."""
+        if self._h2d_pending is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._h2d_pending)
+            self._h2d_pending = None
+
     def _decode_flat(self, codes: torch.Tensor, table: torch.Tensor, out: torch.Tensor, non_blocking: bool) -> None:
         """out <- lookup[code] + shift per tensor.  ``codes`` [val_elems] uint8 and ``table`` [n_params, bins + 2]
         (lookup | shift | scale) may live on the host: they cross the link as they are (one byte per value) and
@@ -989,6 +1022,7 @@ class WindowEngine:
     def compute_peer_norms(self, n_peers: int | None = None, *, include_own: bool = False, peers=None) -> torch.Tensor:
         """Per-(peer, tensor) value norms, their per-tensor lower median, clip factors and skip flags
         (all left on the device in ``peer_norms`` / ``median`` / ``clip`` / ``skip``).  Returns the medians."""
+        self.join_payloads()
         ids = self._peer_list(n_peers, include_own, peers)
         np_ = self.layout.n_params
         if not self.cuda:
@@ -1027,6 +1061,7 @@ class WindowEngine:
         """
         cfg, st = self.cfg, self.store
         lr = cfg.outer_lr if lr is None else lr
+        self.join_payloads()
         ids = self._peer_list(n_peers, include_own, peers)
         n_peers = len(ids)
         if clip_override is not None:
@@ -1083,6 +1118,9 @@ class WindowEngine:
             self._mark("outer.barrier")
             self._allgather_compute_native()
             self._mark("outer.weight_allgather")
+        # the peer slots may be refilled from here on (every rank's aggregate kernel is past the barrier above)
+        self._slots_read = torch.cuda.Event()
+        self._slots_read.record()
 
     def _allgather_compute_native(self) -> None:
         """Push the owned range of the compute buffer to every other rank (plain stores over NVLink)."""
@@ -1140,6 +1178,7 @@ class WindowEngine:
         A sharded engine counts over the chunks of its own shard, reading the packed indices from the slots of the
         ranks that hold them, and the counts are summed over the ranks: a collective, so every rank calls it."""
         native.require(self.cuda, "index_overlap needs the CUDA engine")
+        self.join_payloads()
         ids = list(range(n_peers))
         idx_ptrs, _ = self._peer_ptrs(ids)
         counts = torch.zeros(n_peers * n_peers, dtype=torch.int64, device=self.device)

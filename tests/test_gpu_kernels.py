@@ -491,6 +491,47 @@ def test_encode_values_and_flat_quantised_staging():
         assert abs(float(qp[1]) / float(row[65]) - 1) < 1e-4
 
 
+def test_payloads_staged_on_the_side_stream_give_the_same_outer_step():
+    """Peers' payloads copied from pinned host memory on a side stream (beside a busy compute stream) and joined by the
+    outer step: the same weights as with copies on the compute stream, for two windows in a row (the second reuses the
+    slots, which the side stream may only refill after the first outer step has read them)."""
+    def run(asynchronous):
+        torch.manual_seed(0)
+        model = _Bag([(256, 192), (256,), (128, 64)]).to(DEV)
+        eng = WindowEngine(model, EngineConfig(topk=16, max_peers=4, quant_bins=64), device=DEV, compute_dtype=torch.float32)
+        busy = torch.randn(4096, 4096, device=DEV)
+        out = []
+        for w in range(2):
+            eng.snapshot()
+            eng.store.master_shard.add_(1e-3)
+            eng.compress()
+            items = []
+            for j in range(1, 4):
+                idx, val = synthetic_payload(eng.layout, 40 + 10 * w + j, device=DEV, scale=1e-2)
+                if j == 2:                                     # one peer in the 8-bit wire format
+                    codes, table = eng.encode_values(val)
+                    items.append((j, (idx.cpu().pin_memory(), codes.cpu().pin_memory(), table.cpu().pin_memory())))
+                else:
+                    items.append((j, (idx.cpu().pin_memory(), val.cpu().pin_memory())))
+            torch.cuda.synchronize()
+            for _ in range(8):
+                busy = busy @ busy * 1e-4                      # work in flight on the compute stream while the copies run
+            if asynchronous:
+                eng.load_peer_payloads_async(items)
+            else:
+                for slot, pl in items:
+                    eng.load_peer_payload(slot, pl)
+            eng.outer_step(4)
+            out.append(eng.store.master_shard.clone())
+        torch.cuda.synchronize()
+        assert eng.check_status() == 0
+        return out
+
+    a, b = run(True), run(False)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    assert not torch.equal(a[0], a[1])
+
+
 @pytest.mark.parametrize("quantize", [False, True])
 def test_compress_and_aggregate_are_bitwise_repeatable(quantize):
     """The same inputs give the same bytes: payload, codes and tables, error feedback and updated weights.  The
