@@ -424,54 +424,65 @@ __device__ __forceinline__ void epilogue_swiglu_bwd(const Gemm2Params& p, uint32
   const int row = min(row0 + lane, p.M - 1);
   const __nv_bfloat16* grow = p.gu + (long long)row * p.ld_gu;
   const uint32_t buf_g = stage_base, buf_u = stage_base + 4096u;
-#pragma unroll 1
-  for (int c = 0; c < TILE_N / 64; ++c) {
+  // g and u of this lane's row for one step of 32 features: 64 bytes each (row base and feature offset are multiples
+  // of 8 elements).  The loads of step i + 1 are issued before step i is computed: a step's loads come from L2 or
+  // DRAM, and eight such latencies in a row would make the epilogue as long as the tile's main loop.
+  uint4 gq[4], uq[4], gn[4], un[4];
+  auto fetch = [&](int step, uint4* g4, uint4* u4) {
+    const int f = n0 + step * 32;
+    if (f < p.swiglu_f) {
+      const uint4* gp = reinterpret_cast<const uint4*>(grow + f);
+      const uint4* up = reinterpret_cast<const uint4*>(grow + p.swiglu_f + f);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { g4[q] = gp[q]; u4[q] = up[q]; }
+    }
+  };
+  fetch(0, gq, uq);
+#pragma unroll
+  for (int step = 0; step < TILE_N / 32; ++step) {
+    const int c = step >> 1, hh = step & 1;
     const int f0 = n0 + c * 64;
-    if (f0 >= p.swiglu_f) break;
-    if (n_boxes > 0) {                               // both buffers free: the previous step's stores have read them
+    if (f0 >= p.swiglu_f) break;                     // warp-uniform (swiglu_f is a multiple of 64)
+    if (step + 1 < TILE_N / 32) fetch(step + 1, gn, un);
+    if (hh == 0 && n_boxes > 0) {                    // both buffers free: the previous step's stores have read them
       if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       __syncwarp();
     }
+    uint32_t r[32];
+    tmem_ld32(tmem_acc + c * 64 + hh * 32 + lane_sel, r);
+    float dg[32], du[32];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      // g and u of this lane's row, 32 features: 64 bytes each (the row base and the feature offset are multiples of 8)
-      uint4 gq[4], uq[4];
-      const uint4* gp = reinterpret_cast<const uint4*>(grow + f0 + hh * 32);
-      const uint4* up = reinterpret_cast<const uint4*>(grow + p.swiglu_f + f0 + hh * 32);
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t gw[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w}, uw[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) { gq[q] = gp[q]; uq[q] = up[q]; }
-      uint32_t r[32];
-      tmem_ld32(tmem_acc + c * 64 + hh * 32 + lane_sel, r);
-      float dg[32], du[32];
+      for (int e = 0; e < 4; ++e) {
+        const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e]));
+        const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[e]));
+        const float gg[2] = {g2.x, g2.y}, uu[2] = {u2.x, u2.y};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t gw[4] = {gq[q].x, gq[q].y, gq[q].z, gq[q].w}, uw[4] = {uq[q].x, uq[q].y, uq[q].z, uq[q].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e]));
-          const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[e]));
-          const float gg[2] = {g2.x, g2.y}, uu[2] = {u2.x, u2.y};
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const float dh = __uint_as_float(r[8 * q + 2 * e + k]);
-            const float sg = __fdividef(1.f, 1.f + __expf(-gg[k]));
-            const float silu = gg[k] * sg;
-            du[8 * q + 2 * e + k] = dh * silu;
-            dg[8 * q + 2 * e + k] = dh * uu[k] * (sg + silu * (1.f - sg));
-          }
+        for (int k = 0; k < 2; ++k) {
+          const float dh = __uint_as_float(r[8 * q + 2 * e + k]);
+          const float sg = __fdividef(1.f, 1.f + __expf(-gg[k]));
+          const float silu = gg[k] * sg;
+          du[8 * q + 2 * e + k] = dh * silu;
+          dg[8 * q + 2 * e + k] = dh * uu[k] * (sg + silu * (1.f - sg));
         }
       }
-      box_half(buf_g, lane, hh, dg);
-      box_half(buf_u, lane, hh, du);
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(&p.tmC, buf_g, f0, row0);
-      tma_store_2d(&p.tmC, buf_u, p.swiglu_f + f0, row0);
-      bulk_commit();
+    box_half(buf_g, lane, hh, dg);
+    box_half(buf_u, lane, hh, du);
+    if (hh == 1) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&p.tmC, buf_g, f0, row0);
+        tma_store_2d(&p.tmC, buf_u, p.swiglu_f + f0, row0);
+        bulk_commit();
+      }
+      n_boxes += 2;
     }
-    n_boxes += 2;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { gq[q] = gn[q]; uq[q] = un[q]; }
   }
 }
 

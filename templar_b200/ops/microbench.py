@@ -152,6 +152,19 @@ def bench_fused(a):
         for name, flag in (("fused", True), ("separate", False)):
             OF.FUSED_PROJECTIONS = flag
             rec[f"swiglu_projection_{name}_ms"], _ = time_ms(lambda: OF.linear_swiglu(x, w13), a.iters)
+    # the whole feed-forward, forward + backward (the backward of the SwiGLU runs in the down projection's dgrad epilogue)
+    w2 = (torch.randn(D, Fd, device="cuda") / Fd ** 0.5).to(torch.bfloat16).requires_grad_()
+    w13g = w13.clone().requires_grad_()
+    w2.main_grad, w13g.main_grad = torch.zeros(w2.shape, device="cuda"), torch.zeros(w13.shape, device="cuda")
+    xg = x.clone().requires_grad_()
+    dyf = torch.randn(T, D, device="cuda").to(torch.bfloat16)
+    for name, flag in (("fused", True), ("separate", False)):
+        OF.FUSED_PROJECTIONS = flag
+
+        def ffn():
+            xg.grad = None
+            OF.feed_forward(xg, w13g, w2).backward(dyf)
+        rec[f"feed_forward_fwdbwd_{name}_ms"], _ = time_ms(ffn, a.iters)
     xq = (torch.randn(B, S, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
     wq = (torch.randn((H + 2 * KV) * hd, D, device="cuda") / D ** 0.5).to(torch.bfloat16).requires_grad_()
     wq.main_grad = torch.zeros(wq.shape, device="cuda")
