@@ -120,9 +120,9 @@ class Attention(nn.Module):
 
     def forward(self, x, cos, sin):
         B, S, _ = x.shape
-        if self.packed is not None:          # projection, rotary embedding and attention as one node on the own kernels
-            return self.wo(OF.rope_attention_projection(x, self.packed[0], cos, sin, self.n_heads, self.n_kv, self.hd,
-                                                        self.packed[1]))
+        if self.packed is not None:          # projections, rotary embedding and attention as one node on the own kernels
+            return OF.attention_block(x, self.packed[0], self.wo.weight, cos, sin, self.n_heads, self.n_kv, self.hd,
+                                      self.packed[1], getattr(self.wo.weight, "main_grad", None))
         qkv = OF.linear(x, torch.cat((self.wq.weight, self.wk.weight, self.wv.weight), dim=0))
         qkv = OF.rope(qkv, cos, sin, self.n_heads + self.n_kv, self.hd)
         return self.wo(OF.attention_packed(qkv, self.n_heads, self.n_kv, self.hd))

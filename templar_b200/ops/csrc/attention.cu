@@ -1036,7 +1036,8 @@ extern "C" int tplr_rope(void* buf, const float* cosb, const float* sinb, long l
 
 static int attention_bwd_impl(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                               float* dq32, void* dqkv, int B, int S, int H, int KV, long long ld_qkv, long long ld_o,
-                              float scale, const float* cosb, const float* sinb, unsigned int* status, void* stream) {
+                              float scale, const float* cosb, const float* sinb, unsigned int* status, void* stream,
+                              bool delta_ready = false) {
   if (B <= 0 || S <= 0) return 0;
   if (S % BQ || H % KV || (ld_qkv % 8) || (ld_o % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)dqkv & 15) ||
       ((uintptr_t)dout & 15) || ((uintptr_t)out & 7) || ((uintptr_t)dq32 & 15))
@@ -1044,8 +1045,9 @@ static int attention_bwd_impl(const void* qkv, const void* out, const void* dout
   cudaStream_t st = (cudaStream_t)stream;
   const long long tokens = (long long)B * S;
   const int C = (H + 2 * KV) * DH;
-  attn_delta_kernel<<<(unsigned)((tokens * H + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
-                                                                       delta, tokens, S, H, ld_o);
+  if (!delta_ready)
+    attn_delta_kernel<<<(unsigned)((tokens * H + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout,
+                                                                         delta, tokens, S, H, ld_o);
   if (g_bwd_variant == 2) {
     // pipelined kernel: dq32 is used as the transposed scratch [B*H*128, S]
     AttnBwd2Params p = {};
@@ -1097,3 +1099,17 @@ TPLR_API int tplr_attention_bwd_unrope(const void* qkv, const void* out, const v
   if (!cosb || !sinb || ((uintptr_t)cosb & 15) || ((uintptr_t)sinb & 15)) return -201;
   return attention_bwd_impl(qkv, out, dout, lse, delta, dq32, dqkv, B, S, H, KV, ld_qkv, ld_o, scale, cosb, sinb, status, stream);
 }
+
+// tplr_attention_bwd_unrope for a caller that has already filled `delta` ([B, H, S] fp32, delta[b, h, s] = sum over the
+// head's 128 columns of dout * out): the producer of `dout` (tplr_gemm2_attn_dout, the output projection's data
+// gradient) forms it in its epilogue, where a row of dout is in registers anyway.
+TPLR_API int tplr_attention_bwd_unrope_delta(const void* qkv, const void* out, const void* dout, const float* lse,
+                                             float* delta, float* dq32, void* dqkv, int B, int S, int H, int KV,
+                                             long long ld_qkv, long long ld_o, float scale, const float* cosb,
+                                             const float* sinb, unsigned int* status, void* stream) {
+  TPLR_ENTER();
+  if (!cosb || !sinb || ((uintptr_t)cosb & 15) || ((uintptr_t)sinb & 15)) return -201;
+  return attention_bwd_impl(qkv, out, dout, lse, delta, dq32, dqkv, B, S, H, KV, ld_qkv, ld_o, scale, cosb, sinb, status, stream,
+                            true);
+}
+

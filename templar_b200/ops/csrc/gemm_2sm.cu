@@ -63,6 +63,11 @@ struct Gemm2Params {
   // the epilogue stores dg | du (bf16) through tmC, a map over the [M, 2 * swiglu_f] gradient of that projection
   const __nv_bfloat16* gu;
   long long ld_gu;
+  // data gradient of the attention output projection (EPI 6): C = dO [M, heads * 128] stored as bf16, and for every row
+  // and head delta = sum over the head's 128 columns of dO * O, with O = gu (leading dimension ld_gu), written to
+  // attn_delta[(row / attn_s * heads + head) * attn_s + row % attn_s]
+  float* attn_delta;
+  int attn_s, attn_heads;
   // rotary embedding in the epilogue (EPI 4): the first rope_cols columns of C are heads of rope_dh columns whose
   // interleaved pairs (2i, 2i + 1) are rotated by the angle of (row % rope_s, i); tables [rope_s, rope_dh / 2] fp32
   const float* rope_cos;
@@ -486,9 +491,70 @@ __device__ __forceinline__ void epilogue_swiglu_bwd(const Gemm2Params& p, uint32
   }
 }
 
+// Epilogue of the attention output projection's data gradient (EPI 6): the accumulator row is dO for two heads (256
+// columns).  dO is stored as bf16 like a plain epilogue; on the way every lane multiplies its (bf16-rounded) values
+// with the forward's attention output O of the same row and sums per head, which is the `delta` term of the attention
+// backward (the row sum of dO * O): no separate pass over dO and O.  O is fetched one step of 32 columns ahead.
+__device__ __forceinline__ void epilogue_attn_dout(const Gemm2Params& p, uint32_t tmem_acc, int quad, int lane, int m0, int n0,
+                                                   uint32_t stage_base, uint32_t& n_boxes) {
+  const int row0 = m0 + quad * 32;
+  if (row0 >= p.M) return;                           // warp-uniform
+  const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+  const int row = min(row0 + lane, p.M - 1);
+  const bool live = row0 + lane < p.M;
+  const __nv_bfloat16* orow = p.gu + (long long)row * p.ld_gu;
+  const long long drow = (long long)(row / p.attn_s) * p.attn_heads * p.attn_s + row % p.attn_s;
+  uint4 oq[4], on[4];
+  auto fetch = [&](int step, uint4* o4) {
+    const int f = n0 + step * 32;
+    if (f < p.N) {
+      const uint4* op = reinterpret_cast<const uint4*>(orow + f);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o4[q] = op[q];
+    }
+  };
+  fetch(0, oq);
+  float acc = 0.f;
+#pragma unroll
+  for (int step = 0; step < TILE_N / 32; ++step) {
+    const int c = step >> 1, hh = step & 1;
+    const int f0 = n0 + c * 64;
+    if (f0 >= p.N) break;                            // warp-uniform (N is a multiple of 128)
+    if (step + 1 < TILE_N / 32) fetch(step + 1, on);
+    uint32_t buf = 0;
+    if (hh == 0) buf = box_begin(lane, stage_base, n_boxes); else buf = stage_base + (n_boxes & 1u) * 4096u;
+    uint32_t r[32];
+    tmem_ld32(tmem_acc + c * 64 + hh * 32 + lane_sel, r);
+    float v[32];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t ow[4] = {oq[q].x, oq[q].y, oq[q].z, oq[q].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 o2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[e]));
+        // the attention kernels read dO as bf16: the sum is taken over the values they will see
+        const __nv_bfloat162 d2 = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * e]), __uint_as_float(r[8 * q + 2 * e + 1]));
+        const float2 df = __bfloat1622float2(d2);
+        v[8 * q + 2 * e] = df.x; v[8 * q + 2 * e + 1] = df.y;
+        acc = fmaf(df.x, o2.x, acc);
+        acc = fmaf(df.y, o2.y, acc);
+      }
+    }
+    box_half(buf, lane, hh, v);
+    if (hh == 1) box_store(&p.tmC, buf, lane, n_boxes, f0, row0);
+    if ((step & 3) == 3) {                           // a head (128 columns) is complete
+      const int head = (n0 + step * 32) / 128;
+      if (live) p.attn_delta[drow + (long long)head * p.attn_s] = acc;
+      acc = 0.f;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) oq[q] = on[q];
+  }
+}
+
 // EPI: 0 store bf16, 1 fp32 accumulate (C += acc), 2 store fp32, 3 fused SwiGLU of a packed [w1; w3] projection,
 // 4 store bf16 with the rotary embedding applied to the leading columns, 5 backward of the SwiGLU on the data gradient
-// of the down projection
+// of the down projection, 6 data gradient of the attention output projection with the attention backward's delta term
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ Gemm2Params p) {
@@ -655,6 +721,7 @@ gemm2_kernel(const __grid_constant__ Gemm2Params p) {
         const uint32_t tmem_acc = tmem_base + acc * TILE_N;
         if (EPI == 3)      epilogue_swiglu(p, tmem_acc, quad, lane, m0, tn, sEpi + (uint32_t)quad * 8192u, n_boxes);
         else if (EPI == 5) epilogue_swiglu_bwd(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
+        else if (EPI == 6) epilogue_attn_dout(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
         else if (p.c_tma)  epilogue_tma<EPI>(p, tmem_acc, quad, lane, m0, n0, sEpi + (uint32_t)quad * 8192u, n_boxes);
         else               epilogue_direct<EPI>(p, tmem_acc, quad, lane, m0, n0);
         tcgen05_fence_before();
@@ -746,7 +813,7 @@ int launch2(Gemm2Params& p, int n_comm_pairs, int max_pairs, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
   // all CTAs must be resident at once: compute CTAs wait for comm CTAs of the same launch
-  static int max_clusters[2][2][6] = {};
+  static int max_clusters[2][2][7] = {};
   int& mc = max_clusters[A_MN][B_MN][EPI];
   if (mc == 0) {
     cfg.gridDim = dim3(2 * (tplr_sm_count() / 2));
@@ -775,7 +842,7 @@ int dispatch2(Gemm2Params& p, int a_mn, int b_mn, int epi, int n_comm_pairs, int
   TPLR_GEMM2_CASE(0, 1, 0) TPLR_GEMM2_CASE(0, 1, 1) TPLR_GEMM2_CASE(0, 1, 2)
   TPLR_GEMM2_CASE(1, 1, 0) TPLR_GEMM2_CASE(1, 1, 1) TPLR_GEMM2_CASE(1, 1, 2)
   TPLR_GEMM2_CASE(1, 0, 0) TPLR_GEMM2_CASE(1, 0, 1) TPLR_GEMM2_CASE(1, 0, 2)
-  TPLR_GEMM2_CASE(0, 0, 3) TPLR_GEMM2_CASE(0, 0, 4) TPLR_GEMM2_CASE(0, 1, 5)
+  TPLR_GEMM2_CASE(0, 0, 3) TPLR_GEMM2_CASE(0, 0, 4) TPLR_GEMM2_CASE(0, 1, 5) TPLR_GEMM2_CASE(0, 1, 6)
 #undef TPLR_GEMM2_CASE
   return -104;
 }
@@ -874,6 +941,23 @@ TPLR_API int tplr_gemm2_swiglu_bwd(const void* dY, const void* W2, const void* G
   p.swiglu_f = F;
   p.gu = (const __nv_bfloat16*)GU; p.ld_gu = ldgu;
   return dispatch2(p, 0, 1, 5, 0, 0, (cudaStream_t)stream);
+}
+
+// dO[M, N] = dY Wo (dY [M, K] bf16 K-major, Wo [K, N] bf16 with N contiguous: the attention output projection's weight
+// as stored; N = heads * 128), and delta[b, h, s] = sum over head h's 128 columns of dO * O for row b * S + s, with O
+// [M, N] the forward's attention output (see epilogue_attn_dout).  -111 when this entry does not take the arguments.
+TPLR_API int tplr_gemm2_attn_dout(const void* dY, const void* Wo, const void* O, void* dO, float* delta, int M, int N, int K,
+                                  int S, long long lddy, long long ldwo, long long ldo, long long lddo, unsigned int* status,
+                                  void* stream) {
+  TPLR_ENTER();
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 128 || S <= 0 || M % S || ((uintptr_t)O & 15) || ((uintptr_t)dO & 15) || (ldo % 8) || (lddo % 8) || !delta) return -111;
+  Gemm2Params p = {};
+  if (int r = fill_common(p, dY, Wo, dO, M, N, K, lddy, ldwo, lddo, 0, 1, 0, status)) return r;
+  if (!p.c_tma) return -111;
+  p.gu = (const __nv_bfloat16*)O; p.ld_gu = ldo;
+  p.attn_delta = delta; p.attn_s = S; p.attn_heads = N / 128;
+  return dispatch2(p, 0, 1, 6, 0, 0, (cudaStream_t)stream);
 }
 
 // QKV[M, N] = X W^T (bf16, W K-major) with the rotary embedding applied to the first rope_cols columns in the epilogue:

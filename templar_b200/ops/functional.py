@@ -828,6 +828,84 @@ class _QKVRopeAttention(torch.autograd.Function):
         return dx, dw, None, None, None, None, None, None
 
 
+class _AttentionBlock(torch.autograd.Function):
+    """``attention(rope(x Wqkv^T)) Wo^T`` as one autograd node on the own kernels.  Beyond :class:`_QKVRopeAttention`
+    (rotation in the projection's epilogue, inverse rotation in the attention backward's outputs) the output projection
+    belongs to the node, so that its data gradient ``dO = dY Wo`` can form the attention backward's ``delta`` term (the
+    row sum of dO * O per head) in its epilogue (``tplr_gemm2_attn_dout``) instead of a separate pass over dO and O."""
+
+    @staticmethod
+    def forward(ctx, x, wqkv, wo, mg_qkv, mg_wo, cos, sin, n_heads, n_kv, hd):
+        B, S, _ = x.shape
+        C = wqkv.shape[0]
+        x2 = x.reshape(-1, x.shape[-1])
+        st = status_word(x.device).data_ptr()
+        L = native.lib()
+        qkv = torch.empty(B, S, C, dtype=x.dtype, device=x.device)
+        native.check(L.tplr_gemm2_rope(x2.data_ptr(), wqkv.data_ptr(), qkv.data_ptr(), x2.shape[0], C, x2.shape[1], x2.stride(0),
+                                       wqkv.stride(0), C, cos.data_ptr(), sin.data_ptr(), S, (n_heads + n_kv) * hd, hd, st,
+                                       native.stream_ptr()), "gemm2_rope")
+        out = torch.empty(B, S, n_heads * hd, dtype=x.dtype, device=x.device)
+        lse = torch.empty(B, n_heads, S, dtype=torch.float32, device=x.device)
+        native.check(L.tplr_attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, n_heads, n_kv, qkv.stride(1),
+                                          out.stride(1), hd ** -0.5, st, native.stream_ptr()), "attention_fwd")
+        y = torch.empty(B, S, wo.shape[0], dtype=x.dtype, device=x.device)
+        gemm(out.view(-1, n_heads * hd), wo, out=y.view(-1, wo.shape[0]))
+        ctx.save_for_backward(x, wqkv, wo, qkv, out, lse, cos, sin)
+        ctx.mg, ctx.dims = (mg_qkv, mg_wo), (n_heads, n_kv, hd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wqkv, wo, qkv, out, lse, cos, sin = ctx.saved_tensors
+        mg_qkv, mg_wo = ctx.mg
+        n_heads, n_kv, hd = ctx.dims
+        B, S, C = qkv.shape
+        T, N = B * S, n_heads * hd
+        L = native.lib()
+        st = status_word(qkv.device).data_ptr()
+        dy2 = dy.reshape(T, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        out2 = out.view(T, N)
+        do = torch.empty(T, N, dtype=qkv.dtype, device=qkv.device)
+        delta = torch.empty(B, n_heads, S, dtype=torch.float32, device=qkv.device)
+        native.check(L.tplr_gemm2_attn_dout(dy2.data_ptr(), wo.data_ptr(), out2.data_ptr(), do.data_ptr(), delta.data_ptr(), T, N,
+                                            dy2.shape[1], S, dy2.stride(0), wo.stride(0), out2.stride(0), do.stride(0), st,
+                                            native.stream_ptr()), "gemm2_attn_dout")
+        dwo = _weight_grad(mg_wo, dy2, out2, wo, ctx.needs_input_grad[2])
+        dqkv = torch.empty_like(qkv)
+        dq32 = torch.zeros(B, S, N, dtype=torch.float32, device=qkv.device)
+        native.check(L.tplr_attention_bwd_unrope_delta(
+            qkv.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq32.data_ptr(), dqkv.data_ptr(),
+            B, S, n_heads, n_kv, qkv.stride(1), out.stride(1), hd ** -0.5, cos.data_ptr(), sin.data_ptr(), st,
+            native.stream_ptr()), "attention_bwd_unrope_delta")
+        del dq32, delta, do
+        d2 = dqkv.view(T, C)
+        x2 = x.reshape(T, x.shape[-1])
+        dx = gemm(d2, wqkv, b_mn=True).view_as(x) if ctx.needs_input_grad[0] else None
+        dwqkv = _weight_grad(mg_qkv, d2, x2, wqkv, ctx.needs_input_grad[1])
+        return dx, dwqkv, dwo, None, None, None, None, None, None, None
+
+
+def attention_block(x, wqkv, wo, cos, sin, n_heads: int, n_kv: int, hd: int, main_grad_qkv=None, main_grad_wo=None):
+    """Causal attention block without its norm and residual: ``attention(rope(x @ wqkv.T)) @ wo.T`` for the packed
+    ``wqkv = [wq; wk; wv]``.  One autograd node on the own kernels, three elsewhere."""
+    if main_grad_qkv is None:
+        main_grad_qkv = getattr(wqkv, "main_grad", None)
+    if main_grad_wo is None:
+        main_grad_wo = getattr(wo, "main_grad", None)
+    B, S, K = x.shape
+    if (FUSED_PROJECTIONS and _ATTN_BACKEND == "tcgen05" and _GEMM_BACKEND == "tcgen05_2sm" and _native_ok(x, wqkv, wo)
+            and x.dtype == torch.bfloat16 and hd == 128 and S % 128 == 0 and n_heads % n_kv == 0 and x.is_contiguous()
+            and wqkv.stride(1) == 1 and wo.stride(1) == 1 and wqkv.stride(0) % 8 == 0 and wo.stride(0) % 8 == 0 and K % 8 == 0
+            and wo.shape[0] % 8 == 0 and wo.shape[1] == n_heads * hd and cos.is_cuda and cos.dtype == torch.float32
+            and cos.is_contiguous() and sin.is_contiguous() and cos.shape[0] >= S and cos.shape[1] == hd // 2
+            and all(t.data_ptr() % 16 == 0 for t in (x, wqkv, wo, cos, sin))):
+        return _AttentionBlock.apply(x, wqkv, wo, main_grad_qkv, main_grad_wo, cos, sin, n_heads, n_kv, hd)
+    return _Linear.apply(rope_attention_projection(x, wqkv, cos, sin, n_heads, n_kv, hd, main_grad_qkv), wo, main_grad_wo)
+
+
 def rope_attention_projection(x, w, cos, sin, n_heads: int, n_kv: int, hd: int, main_grad=None):
     """Causal attention of the rotary-embedded packed projection ``x @ w.T`` (``w = [wq; wk; wv]``); returns
     [B, S, H * hd].  On the own kernels this is one autograd node with the rotation inside the GEMM and attention

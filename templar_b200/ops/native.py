@@ -85,6 +85,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "tplr_gemm2_swiglu": [vp, vp, vp, vp, i, i, i, ll, ll, ll, ll, vp, vp],
         "tplr_gemm2_rope": [vp, vp, vp, i, i, i, ll, ll, ll, vp, vp, i, i, i, vp, vp],
         "tplr_gemm2_swiglu_bwd": [vp, vp, vp, vp, i, i, i, ll, ll, ll, ll, vp, vp],
+        "tplr_gemm2_attn_dout": [vp, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, ll, vp, vp],
+        "tplr_attention_bwd_unrope_delta": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp, vp, vp],
         "tplr_attention_bwd_unrope": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp, vp, vp],
         "tplr_attention_fwd": [vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],
         "tplr_attention_bwd": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ll, ll, f, vp, vp],

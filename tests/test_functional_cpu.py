@@ -70,3 +70,17 @@ def test_linear_swiglu_equals_projection_then_activation():
     h2 = OF.swiglu(OF.linear(x, w))
     g2 = _grads(h2, x, w)
     assert torch.equal(h, h2) and all(torch.equal(a, b) for a, b in zip(g, g2))
+
+
+def test_attention_block_equals_projection_rotation_attention_projection():
+    torch.manual_seed(4)
+    B, S, H, KV, hd, K = 1, 8, 2, 1, 16, 32
+    x = torch.randn(B, S, K, requires_grad=True)
+    w = torch.randn((H + 2 * KV) * hd, K, requires_grad=True)
+    wo = torch.randn(K, H * hd, requires_grad=True)
+    cos, sin = OF.rope_tables(S, hd)
+    o = OF.attention_block(x, w, wo, cos, sin, H, KV, hd)
+    g = _grads(o, x, w, wo)
+    o2 = OF.linear(OF.attention_packed(OF.rope(OF.linear(x, w), cos, sin, H + KV, hd), H, KV, hd), wo)
+    g2 = _grads(o2, x, w, wo)
+    assert torch.equal(o, o2) and all(torch.equal(a, b) for a, b in zip(g, g2))

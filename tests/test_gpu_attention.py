@@ -144,3 +144,55 @@ def test_projection_rope_attention_as_one_node_matches_the_three_node_path(B, S,
         e_three = (rel(o0, ref), rel(gx0, xf.grad), rel(gw0, wf.grad))
         assert max(e_fused) < 3e-2, (e_fused, e_three)
         assert all(a < 1.5 * b + 2e-3 for a, b in zip(e_fused, e_three)), (e_fused, e_three)
+
+
+@pytest.mark.parametrize("B,S,H,KV,K", [(2, 256, 4, 2, 512), (1, 384, 3, 1, 192), (8, 2048, 16, 8, 2048)])
+def test_attention_block_with_delta_from_the_output_projection_epilogue(B, S, H, KV, K):
+    """The whole block as one node: the output projection's data-gradient GEMM forms the attention backward's delta term
+    (row sum of dO * O per head) in its epilogue.  Against the node-per-op path (separate delta kernel) and, for the small
+    shapes, an fp32 PyTorch evaluation."""
+    from templar_b200.ops import functional as OF, native
+
+    hd = 128
+    torch.manual_seed(B * S + H + 1)
+    x = (torch.randn(B, S, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    wo = (torch.randn(K, H * hd, device="cuda") / (H * hd) ** 0.5).to(torch.bfloat16)
+    cos, sin = OF.rope_tables(S, hd, 10000.0, "cuda")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    dy = torch.randn(B, S, K, device="cuda").to(torch.bfloat16)
+    OF.status_word("cuda").zero_()
+
+    def run(fused):
+        prev = OF.FUSED_PROJECTIONS
+        OF.FUSED_PROJECTIONS = fused
+        try:
+            xx, ww, oo = (t.clone().requires_grad_() for t in (x, w, wo))
+            n0 = native.launch_count
+            y = OF.attention_block(xx, ww, oo, cos, sin, H, KV, hd)
+            y.backward(dy)
+            return y.float(), xx.grad.float(), ww.grad.float(), oo.grad.float(), native.launch_count - n0
+        finally:
+            OF.FUSED_PROJECTIONS = prev
+
+    yf, *gf, n_f = run(True)
+    ys, *gs, n_s = run(False)
+    torch.cuda.synchronize()
+    assert int(OF.status_word("cuda").item()) == 0
+    assert n_f == 8 and n_s == 10          # no rotation pass in either direction (the delta pass is inside the attention launch count)
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()      # noqa: E731
+    errs = [rel(yf, ys)] + [rel(a, b) for a, b in zip(gf, gs)]
+    assert max(errs) < 2e-2, errs
+    if B * S <= 1024:
+        xf, wf, of = (t.float().requires_grad_() for t in (x, w, wo))
+        qkv = OF._rope_torch(xf @ wf.t(), cos, sin, (H + KV) * hd, hd, False)
+        q, k, v = OF._split_qkv(qkv, H, KV, hd)
+        k, v = (t.repeat_interleave(H // KV, dim=2) for t in (k, v))
+        att = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                               is_causal=True).transpose(1, 2).reshape(B, S, H * hd)
+        ref = att @ of.t()
+        ref.backward(dy.float())
+        e_f = [rel(yf, ref)] + [rel(a, b.grad) for a, b in zip(gf, (xf, wf, of))]
+        e_s = [rel(ys, ref)] + [rel(a, b.grad) for a, b in zip(gs, (xf, wf, of))]
+        assert max(e_f) < 3e-2, (e_f, e_s)
+        assert all(a < 1.5 * b + 2e-3 for a, b in zip(e_f, e_s)), (e_f, e_s)
