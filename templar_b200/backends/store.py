@@ -48,6 +48,14 @@ class ObjectStore:
     async def delete(self, bucket: Bucket, keys: list[str]) -> None: raise NotImplementedError
     async def close(self) -> None: return None
 
+    async def get_range(self, bucket: Bucket, key: str, start: int, end: int) -> bytes | None:
+        """Bytes ``start..end`` (inclusive, as in an HTTP Range header) of an object; None when the object is
+        missing or shorter than ``end + 1``.  Transports without a ranged read slice the whole object."""
+        data = await self.get_bytes(bucket, key)
+        if data is None or start < 0 or end < start or len(data) <= end:
+            return None
+        return data[start:end + 1]
+
 
 # --------------------------------------------------------------------------------------- #
 class LocalFSStore(ObjectStore):
@@ -395,6 +403,22 @@ class S3Store(ObjectStore):
             if code in ("404", "NoSuchKey", "NotFound"):
                 return None
             raise
+
+    async def get_range(self, bucket, key, start, end):
+        async def _get(c):
+            r = await c.get_object(Bucket=bucket.name, Key=key, Range=f"bytes={start}-{end}")
+            async with r["Body"] as stream:
+                return await stream.read()
+        if start < 0 or end < start:
+            return None
+        try:
+            data = await self._guard(bucket, _get)
+        except Exception as e:  # noqa: BLE001
+            code = getattr(e, "response", {}).get("Error", {}).get("Code") if hasattr(e, "response") else None
+            if code in ("404", "416", "NoSuchKey", "NotFound", "InvalidRange"):
+                return None
+            raise
+        return data if len(data) == end - start + 1 else None
 
     async def get_to_file(self, bucket, key, path):
         info = await self.head(bucket, key)

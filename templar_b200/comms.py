@@ -180,6 +180,17 @@ class Comms(ChainManager):
         info = await self.store.head(bucket, key)
         return None if info is None else info.size
 
+    async def s3_get_object_range(self, bucket: Bucket, key: str, start: int, end: int, timeout: int = 30) -> bytes | None:
+        """Bytes ``start..end`` (inclusive) of an object, or None on a miss, a short read or a timeout
+        (reference: src/tplr/comms.py:2648-2703)."""
+        try:
+            return await asyncio.wait_for(self.store.get_range(bucket, key, start, end), timeout=timeout)
+        except asyncio.TimeoutError:
+            logger.error(f"timeout reading bytes {start}-{end} of {key}")
+        except Exception as e:  # noqa: BLE001
+            logger.error(f"reading bytes {start}-{end} of {key} failed: {e}")
+        return None
+
     # ------------------------------------------------------------------------------------ #
     # cleanup
     # ------------------------------------------------------------------------------------ #

@@ -362,6 +362,26 @@ def test_ranged_download_retries_short_chunks_and_resumes(tmp_path, monkeypatch)
     assert fake.requests == [(6000, 8999)] and out.read_bytes() == data
 
 
+def test_ranged_read_on_every_transport(net, tmp_path):
+    """Inclusive byte ranges through the S3 client, the local store and the in-memory store, and through
+    Comms.s3_get_object_range; a range past the end, a short answer and a missing object read as None."""
+    data = os.urandom(5000)
+    b = Bucket(name="bkt", account_id="a" * 32, access_key_id="k" * 32, secret_access_key="s" * 64)
+    fake = _FakeRangedS3(data)
+    s3 = S3Store(client_factory=lambda bk: fake)
+    assert run(s3.get_range(b, "x", 10, 19)) == data[10:20] and fake.requests == [(10, 19)]
+    assert run(s3.get_range(b, "x", 4990, 5200)) is None               # the fake answers with fewer bytes
+    assert run(s3.get_range(b, "x", 5, 4)) is None
+    fs = LocalFSStore(tmp_path)
+    run(fs.put_bytes(b, "x", data))
+    assert run(fs.get_range(b, "x", 0, 0)) == data[:1] and run(fs.get_range(b, "x", 4000, 4999)) == data[4000:]
+    assert run(fs.get_range(b, "x", 4000, 5000)) is None and run(fs.get_range(b, "nope", 0, 1)) is None
+    comms = net[2][0]
+    run(comms.store.put_bytes(comms.bucket, "blob", data))
+    assert run(comms.s3_get_object_range(comms.bucket, "blob", 100, 163)) == data[100:164]
+    assert run(comms.s3_get_object_range(comms.bucket, "missing", 0, 3)) is None
+
+
 def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
     store, chain, comms = net
     totalks, xshapes = {"w.": 4096}, {"w.": (2, 2, 64, 64)}
