@@ -4,11 +4,13 @@
     torchrun --standalone --nproc-per-node 2 neurons/evaluator.py --device cuda [--local]
 
 Flow (reference: neurons/evaluator.py:1113-1222): read the start window → find the newest complete
-checkpoint (``_LATEST.json`` pointer or listing, completeness gate) → load it (DCP reshards to this
-topology) → convert to HF layout and cache it → custom evaluation (cross entropy → perplexity and
-bits per byte) → ``lm_eval`` in a subprocess when available (rank 0 runs it, the other ranks wait
-on a sentinel file) → metrics → sleep ``eval_interval``.  ``--backfill-start/-end`` walks a window
-range instead of following the head.
+checkpoint (``_LATEST.json`` pointer or listing, completeness gate; rank 0 decides, the others follow) →
+load it (DCP reshards to this topology) → custom evaluation (cross entropy → perplexity and bits per
+byte) → convert to HF layout into a per-window cache → ``lm_eval`` in a subprocess when available (the
+model leaves the GPU first; rank 0 runs the child, the other ranks wait on a sentinel file) → metrics →
+old exports and local checkpoints pruned → sleep ``eval_interval``.  With nothing published and no
+bootstrap version the untrained weights are evaluated once as the baseline.  ``--from-window/--to-window``
+walk a window range first.
 """
 
 from __future__ import annotations
@@ -37,6 +39,7 @@ from templar_b200 import model_factory  # noqa: E402
 from templar_b200.backends.chain import StaticWallet, make_subtensor  # noqa: E402
 from templar_b200.distributed import dist_helper  # noqa: E402
 from templar_b200.metrics import MetricsLogger  # noqa: E402
+from templar_b200.wandb_ops import NullRun, initialize_wandb  # noqa: E402
 
 DEFAULT_TASKS = "arc_challenge,arc_easy,openbookqa,winogrande,piqa,hellaswag,mmlu"
 
@@ -47,25 +50,61 @@ def compute_bpb(total_nll_nats: float, total_bytes: int) -> float:
 
 
 class ModelCache:
-    """Remembers which window's HF export sits in ``path`` so it is not rebuilt."""
+    """HF exports of evaluated windows, one directory per window under ``base_dir/<version>`` (the same window
+    number can exist under several versions; reference: neurons/evaluator.py:144-210)."""
 
-    def __init__(self, path: str | Path):
-        self.path = Path(path)
-        self.meta = self.path / "cache_meta.json"
+    WEIGHT_FILES = ("model.safetensors", "pytorch_model.bin")
 
-    def is_valid(self, window: int, version: str) -> bool:
-        try:
-            m = json.loads(self.meta.read_text())
-            return m.get("window") == window and m.get("version") == version and (self.path / "config.json").exists()
-        except Exception:  # noqa: BLE001
-            return False
+    def __init__(self, base_dir: str | Path, namespace: str | None = None):
+        self.base_dir = Path(base_dir) / namespace if namespace else Path(base_dir)
 
-    def mark(self, window: int, version: str) -> None:
-        self.path.mkdir(parents=True, exist_ok=True)
-        self.meta.write_text(json.dumps({"window": window, "version": version, "time": time.time()}))
+    def get_path(self, window: int) -> Path:
+        return self.base_dir / f"window_{window}"
 
-    def clear(self) -> None:
-        shutil.rmtree(self.path, ignore_errors=True)
+    def exists(self, window: int) -> bool:
+        """A finished export: the config, a weight file (whole or sharded) and the completion mark."""
+        p = self.get_path(window)
+        has_weights = any((p / f).exists() for f in self.WEIGHT_FILES) or any(p.glob("model-*.safetensors"))
+        return (p / "config.json").exists() and has_weights and (p / "cache_meta.json").exists()
+
+    def mark(self, window: int) -> None:
+        p = self.get_path(window)
+        p.mkdir(parents=True, exist_ok=True)
+        (p / "cache_meta.json").write_text(json.dumps({"window": window, "time": time.time()}))
+
+    def clear(self, window: int) -> None:
+        shutil.rmtree(self.get_path(window), ignore_errors=True)
+
+    def windows(self) -> list[int]:
+        out = []
+        if self.base_dir.is_dir():
+            for d in self.base_dir.iterdir():
+                tail = d.name[len("window_"):] if d.is_dir() and d.name.startswith("window_") else ""
+                if tail.isdigit():
+                    out.append(int(tail))
+        return sorted(out)
+
+    def cleanup(self, keep_latest: int = 2) -> list[int]:
+        """Remove all but the ``keep_latest`` highest windows; returns the removed ones."""
+        ws = self.windows()
+        drop = ws[:-keep_latest] if keep_latest > 0 else ws
+        for w in drop:
+            self.clear(w)
+        return drop
+
+
+def release_device_memory(label: str = "") -> None:
+    """Collect garbage and give cached device memory back to the driver, so that a child process (the task
+    harness with its own inference engine) finds the GPU empty."""
+    import gc
+
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        torch.cuda.ipc_collect()
+        free, total = torch.cuda.mem_get_info()
+        tplr.logger.debug(f"[eval] {label}: {free / 2**30:.1f} of {total / 2**30:.1f} GiB free")
 
 
 class Evaluator(BaseNode, Trainer):
@@ -115,11 +154,16 @@ class Evaluator(BaseNode, Trainer):
         self.comms = tplr.Comms(wallet=self.wallet, config=self.config, hparams=self.hparams, uid=self.uid, store=store,
                                 subtensor=self.subtensor)
         self.ckpt = tplr.DCPCheckpointer(self.comms, uid=self.uid, version=self.version, repo_root=".")
-        self.cache = ModelCache(self.config.cache_dir)
+        self.cache = ModelCache(self.config.cache_dir, namespace=self.version)
         self.metrics_logger = MetricsLogger(prefix="E", uid=self.uid, config=self.config, role="evaluator",
                                             group="evaluator", job_type="eval") if self.is_master else None
+        self.wandb = initialize_wandb("E", self.uid, self.config, "evaluator", "eval") if self.is_master else NullRun()
+        self.tasks = [t.strip() for t in str(self.config.tasks or "").split(",") if t.strip()]
         self.last_eval_window = -1
         self.eval_counter = 0
+        self.evaluated_windows: set[int] = set()
+        self.baseline_evaluated = False
+        self.start_window: int | None = None
 
     # -- checkpoints --------------------------------------------------------------------------
     async def check_latest_checkpoint(self) -> int | None:
@@ -133,17 +177,22 @@ class Evaluator(BaseNode, Trainer):
         return await self.ckpt.download_and_load(model=self.model, window=window, shared_fs=True)
 
     def save_model_for_eval(self, window: int) -> Path | None:
-        """HF export of the loaded weights (rank 0 writes; cached per window)."""
-        if self.cache.is_valid(window, self.version):
-            return self.cache.path
-        if self.is_master:
-            self.cache.clear()
-        model_factory.convert_titan_to_hf(self.model, self.hparams, save_path=str(self.cache.path) if self.is_master else None,
-                                          is_master=self.is_master)
-        if self.is_master:
-            self.cache.mark(window, self.version)
+        """HF export of the loaded weights into this window's cache directory (rank 0 writes; an export that is
+        already complete is reused).  None when the export failed."""
+        path = self.cache.get_path(window)
+        if not self.cache.exists(window):
+            if self.is_master:
+                self.cache.clear(window)
+            try:
+                model_factory.convert_titan_to_hf(self.model, self.hparams, save_path=str(path) if self.is_master else None,
+                                                  is_master=self.is_master)
+                if self.is_master:
+                    self.cache.mark(window)
+            except Exception as e:  # noqa: BLE001
+                tplr.logger.error(f"[eval] export of window {window} failed: {e}")
+                path = None
         dist_helper.safe_barrier("hf_export", self.local_rank)
-        return self.cache.path
+        return path
 
     # -- custom eval ---------------------------------------------------------------------------
     def _custom_eval_rows(self, n_batches: int):
@@ -227,11 +276,25 @@ class Evaluator(BaseNode, Trainer):
 
     def run_lm_eval(self, model_path: Path, tasks: list[str], window: int, global_step: int) -> dict[str, float]:
         """Rank 0 runs the harness in a clean (non-torchrun) environment; other ranks wait on a sentinel."""
-        sentinel = Path(f"/tmp/tplr_lm_eval_done_{window}")
-        if not self.is_master:
-            while not sentinel.exists() and not self.stop_event.is_set():
-                time.sleep(1.0)
-            return {}
+        sentinel = Path(f"/tmp/tplr_lm_eval_done_{self.uid}_{window}")
+        if dist_helper.is_distributed():
+            # all ranks arrive before rank 0 starts the child, and leave together after it: the sentinel of one
+            # evaluation cannot be seen by the next (reference: neurons/evaluator.py:76-106)
+            dist_helper.safe_barrier(f"lm_eval_enter_{window}", self.local_rank)
+        try:
+            if not self.is_master:
+                while not sentinel.exists() and not self.stop_event.is_set():
+                    time.sleep(0.25)
+                return {}
+            return self._run_lm_eval_master(model_path, tasks, window, global_step, sentinel)
+        finally:
+            if dist_helper.is_distributed():
+                dist_helper.safe_barrier(f"lm_eval_exit_{window}", self.local_rank)
+            if self.is_master:
+                sentinel.unlink(missing_ok=True)
+
+    def _run_lm_eval_master(self, model_path: Path, tasks: list[str], window: int, global_step: int,
+                            sentinel: Path) -> dict[str, float]:
         out_dir = Path(f"/tmp/eval_{int(time.time())}")
         out_dir.mkdir(parents=True, exist_ok=True)
         cmd = self.lm_eval_command(model_path, tasks, out_dir)
@@ -245,101 +308,209 @@ class Evaluator(BaseNode, Trainer):
                        ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_NAME",
                         "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS")}
                 env["VLLM_WORKER_MULTIPROC_METHOD"] = "spawn"
+                if torch.cuda.is_available():
+                    env["CUDA_VISIBLE_DEVICES"] = ",".join(str(i) for i in range(torch.cuda.device_count()))
+                t0 = time.perf_counter()
                 rc = subprocess.Popen(cmd, env=env).wait()
+                # the inference engine of the harness may abort on exit (134) after it has written its results
                 if rc in (0, 134):
-                    results = self.parse_lm_eval_results(out_dir)
+                    scored = self.parse_lm_eval_results(out_dir, with_metric=True)
+                    results = {t: v for t, (m, v) in scored.items()}
+                    self._log_task_scores(scored, window, global_step)
+                tplr.logger.info(f"[eval] lm_eval exit code {rc} after {time.perf_counter() - t0:.1f} s, "
+                                 f"{len(results)} task results")
         finally:
             sentinel.write_text("done")
-            shutil.rmtree(out_dir, ignore_errors=True)
+            if results or cmd is None:
+                shutil.rmtree(out_dir, ignore_errors=True)
+            else:
+                tplr.logger.warning(f"[eval] no task results; {out_dir} kept for inspection")
         return results
 
+    def _log_task_scores(self, scored: dict[str, tuple[str, float]], window: int, global_step: int) -> None:
+        """``benchmark_task`` per task and one ``benchmark_summary`` (reference: neurons/evaluator.py:640-690)."""
+        if self.metrics_logger is not None:
+            for task, (metric, value) in scored.items():
+                self.metrics_logger.log("benchmark_task", tags={"task": task, "metric": metric, "global_step": global_step,
+                                                                "window": window}, fields={"score": float(value)})
+            self.metrics_logger.log("benchmark_summary", tags={"global_step": global_step, "window": window},
+                                    fields={"num_tasks": len(scored), "global_step": global_step,
+                                            "mean_score": sum(v for _, v in scored.values()) / max(len(scored), 1)})
+        self.wandb.log({**{f"evaluator/benchmark/{t}/{m}": v for t, (m, v) in scored.items()},
+                        "evaluator/benchmark/num_tasks": len(scored)}, step=global_step)
+
     @staticmethod
-    def parse_lm_eval_results(output_dir: Path) -> dict[str, float]:
-        """``{task: score}`` from the newest ``results*.json`` (acc_norm preferred over acc)."""
-        files = sorted(Path(output_dir).rglob("results*.json"), key=lambda p: p.stat().st_mtime)
+    def parse_lm_eval_results(output_dir: Path, with_metric: bool = False) -> dict:
+        """``{task: score}`` (``{task: (metric, score)}`` with ``with_metric``) from the newest JSON file under
+        ``output_dir`` - the harness writes into a sub-directory named after the model - with the normalised
+        accuracy preferred over the plain one (reference: neurons/evaluator.py:573-695)."""
+        files = [f for f in Path(output_dir).rglob("*.json") if f.is_file()]
         if not files:
             return {}
-        data = json.loads(files[-1].read_text())
+        try:
+            data = json.loads(max(files, key=lambda f: f.stat().st_mtime).read_text())
+        except (OSError, ValueError) as e:
+            tplr.logger.error(f"[eval] unreadable result file under {output_dir}: {e}")
+            return {}
         out = {}
         for task, res in (data.get("results") or {}).items():
             for key in ("acc_norm,none", "acc,none", "acc_norm", "acc"):
-                if key in res:
-                    out[task] = float(res[key])
+                if isinstance(res, dict) and res.get(key) is not None:
+                    out[task] = (key, float(res[key])) if with_metric else float(res[key])
                     break
+            else:
+                tplr.logger.warning(f"[eval] {task}: no accuracy metric in the results")
         return out
 
     # -- main -------------------------------------------------------------------------------------
-    async def evaluate_window(self, window: int) -> dict | None:
-        res = await self.load_window(window)
-        if res is None:
-            return None
-        sync_window, global_step = res
+    async def evaluate_window(self, window: int, is_baseline: bool = False) -> dict | None:
+        """Evaluate the checkpoint of ``window`` (or, as the baseline, the freshly initialised weights).  The global
+        step comes from the checkpoint's sidecar; an older checkpoint without one gets ``window - start_window``
+        (reference: neurons/evaluator.py:871-985).  None when the checkpoint could not be loaded."""
+        if window in self.evaluated_windows and not self.config.force_reval:
+            tplr.logger.info(f"[eval] window {window} already evaluated")
+            return {"window": window, "skipped": True}
+        global_step = 0
+        if not is_baseline and window > 0:
+            try:
+                res = await self.load_window(window)
+            except Exception as e:  # noqa: BLE001
+                tplr.logger.error(f"[eval] loading the checkpoint of window {window} failed: {e}")
+                return None
+            if res is None:
+                return None
+            loaded_window, global_step = res
+            if loaded_window != window:
+                tplr.logger.error(f"[eval] asked for window {window}, the checkpoint is of window {loaded_window}")
+                return None
+            if global_step is None or global_step < 0:
+                global_step = window - (self.start_window if self.start_window is not None else window)
+        global_step = max(int(global_step), 0)           # backfill before the start window: no negative steps
         custom = await self.run_custom_eval()
-        tasks = {}
-        if not self.config.skip_lm_eval:
+        tasks: dict[str, float] = {}
+        if self.tasks and not self.config.skip_lm_eval:
             path = self.save_model_for_eval(window)
-            tasks = self.run_lm_eval(path, self.config.tasks.split(","), window, global_step)
-        self.last_eval_window = window
+            if path is None:
+                return None
+            # the harness loads the export into an inference engine of its own: hand it an empty GPU
+            on_gpu = self.device.type == "cuda" and shutil.which("lm_eval") is not None
+            if on_gpu:
+                self.model.to("cpu")
+                release_device_memory("before lm_eval")
+            try:
+                tasks = self.run_lm_eval(path, self.tasks, window, global_step)
+            finally:
+                if on_gpu:
+                    self.model.to(self.device)
+        self.last_eval_window = max(self.last_eval_window, window)
+        self.evaluated_windows.add(window)
         self.eval_counter += 1
         if self.metrics_logger is not None:
-            self.metrics_logger.log("custom_evaluation", tags={"window": window, "global_step": global_step}, fields=custom)
-            for task, score in tasks.items():
-                self.metrics_logger.log("benchmark_task", tags={"window": window, "task": task}, fields={"score": score})
-            if tasks:
-                self.metrics_logger.log("benchmark_summary", tags={"window": window},
-                                        fields={"num_tasks": len(tasks), "mean_score": sum(tasks.values()) / len(tasks)})
-        tplr.logger.info(f"[eval] window {window} step {global_step}: loss={custom['loss']:.4f} ppl={custom['perplexity']:.2f} "
-                         f"bpb={custom['bits_per_byte']:.4f} tasks={tasks}")
-        return {"window": window, "global_step": global_step, **custom, "tasks": tasks}
+            self.metrics_logger.log("custom_evaluation", tags={"window": window, "global_step": global_step,
+                                                               "baseline": int(is_baseline)}, fields=custom)
+        self.wandb.log({f"evaluator/custom/{k}": custom[k] for k in ("loss", "perplexity", "bits_per_byte")}, step=global_step)
+        tplr.logger.info(f"[eval] window {window} step {global_step}{' (baseline)' if is_baseline else ''}: "
+                         f"loss={custom['loss']:.4f} ppl={custom['perplexity']:.2f} bpb={custom['bits_per_byte']:.4f} tasks={tasks}")
+        if self.is_master:                                # one export and one local checkpoint stay on disk
+            self.cache.cleanup(keep_latest=1)
+            self.ckpt.cleanup_local_checkpoints(keep_latest=1)
+        return {"window": window, "global_step": global_step, "baseline": is_baseline, **custom, "tasks": tasks}
+
+    def _from_master(self, *values: int | None) -> list[int | None]:
+        """Rank 0's values on every rank (None travels as -1): what the object store shows can differ between
+        two ranks that look a moment apart, and the ranks have to take the same branch."""
+        t = torch.tensor([-1 if v is None else int(v) for v in values], dtype=torch.long, device=self.device)
+        dist_helper.broadcast(t, src=0)
+        return [None if v < 0 else v for v in t.tolist()]
 
     async def _backfill_range(self) -> tuple[int, int] | None:
         """Window range of a backfill run; an open end is resolved from the network (start window / newest
-        complete checkpoint)."""
+        complete checkpoint) by rank 0.  A reversed range is put in order."""
         lo, hi = self.config.backfill_start, self.config.backfill_end
         if lo is None and hi is None:
             return None
-        if lo is None:
-            lo = await self.comms.get_start_window()
-        if hi is None:
-            hi = await self.ckpt._discover_latest(prefer_highest_staked=True)
+        if self.is_master:
+            if lo is None:
+                lo = self.start_window if self.start_window is not None else await self.comms.get_start_window()
+            if hi is None:
+                hi = await self.ckpt._discover_latest(prefer_highest_staked=True)
+                if hi is not None and not await self.ckpt.check_checkpoint_exists(window=hi):
+                    hi = None
+        lo, hi = self._from_master(lo, hi)
         if lo is None or hi is None:
             tplr.logger.warning("[eval] backfill range could not be resolved")
             return None
-        return int(lo), int(hi)
+        return (int(lo), int(hi)) if lo <= hi else (int(hi), int(lo))
+
+    async def backfill_range(self) -> list[int]:
+        """Evaluate every complete checkpoint of the range; returns the evaluated windows."""
+        rng = await self._backfill_range()
+        out: list[int] = []
+        if rng is None:
+            return out
+        tplr.logger.info(f"[eval] backfilling windows {rng[0]}..{rng[1]} of version {self.version}")
+        for w in range(rng[0], rng[1] + 1):
+            if self.stop_event.is_set():
+                break
+            ready = (await self.ckpt.check_checkpoint_exists(window=w)) if self.is_master else None
+            if not self._from_master(int(bool(ready)))[0]:
+                continue
+            rep = await self.evaluate_window(w)
+            if rep is not None and not rep.get("skipped"):
+                out.append(w)
+            dist_helper.safe_barrier(f"backfill_win_{w}", self.local_rank)
+        return out
 
     async def run(self):
+        """Start window -> newest checkpoint (or, when the network has published none and no bootstrap version is
+        configured, the freshly initialised weights as the baseline) -> backfill range if one was asked for ->
+        follow new checkpoints every ``eval_interval`` seconds (reference: neurons/evaluator.py:1113-1222)."""
         self.loop = asyncio.get_running_loop()
         self.comms.commitments = await self.comms.get_commitments()
-        done: set[int] = set()
-        rng = await self._backfill_range()
-        if rng is not None:
-            for w in range(rng[0], rng[1] + 1):
-                if self.stop_event.is_set():
-                    break
-                if (w in done and not self.config.force_reval) or not await self.ckpt.check_checkpoint_exists(window=w):
-                    continue
-                if await self.evaluate_window(w) is not None:
-                    done.add(w)
-            if self.config.no_follow or (self.config.backfill_start is not None and self.config.backfill_end is not None):
-                return
+        sw = (await self.comms.get_start_window(version=self.version)) if self.is_master else None
+        self.start_window = self._from_master(sw)[0]
+        backfill = self.config.backfill_start is not None or self.config.backfill_end is not None
+        first = True
         while not self.stop_event.is_set():
-            w = await self.check_latest_checkpoint() if self.is_master else None
-            t = torch.tensor([w if w is not None else -1], dtype=torch.long, device=self.device)
-            dist_helper.broadcast(t, src=0)
-            w = int(t.item())
-            if w >= 0 and (w not in done or self.config.force_reval):
-                if await self.evaluate_window(w) is not None:
-                    done.add(w)
+            if not first:
+                self.comms.commitments = await self.comms.get_commitments()
+            w = self._from_master((await self.check_latest_checkpoint()) if self.is_master else None)[0]
+            if w is not None:
+                await self.evaluate_window(w)
+                dist_helper.safe_barrier("eval_complete", self.local_rank)
+            elif (first and not backfill and not self.baseline_evaluated and self.start_window is not None
+                  and not getattr(self.hparams, "checkpoint_init_version", None)):
+                # nothing published yet and no bootstrap version: the untrained weights give the curve its origin
+                if await self.evaluate_window(self.start_window, is_baseline=True) is not None:
+                    self.baseline_evaluated = True
+            if first and backfill:
+                await self.backfill_range()
+            first = False
             if self.config.no_follow or (self.config.max_windows and self.eval_counter >= self.config.max_windows):
                 break
+            if backfill and self.config.backfill_start is not None and self.config.backfill_end is not None:
+                break                                     # a closed range is a one-shot job
             try:
                 await asyncio.wait_for(self.stop_event.wait(), timeout=self.config.eval_interval)
             except asyncio.TimeoutError:
                 pass
 
+    def cleanup(self) -> None:
+        """Release the model's device memory and the loggers at shutdown."""
+        if getattr(self, "model", None) is not None and self.device.type == "cuda":
+            self.model.to("cpu")
+            release_device_memory("shutdown")
+        if self.metrics_logger is not None:
+            self.metrics_logger.close()
+        self.wandb.finish()
+
 
 def main():
-    asyncio.run(Evaluator().main())
+    node = Evaluator()
+    try:
+        asyncio.run(node.main())
+    finally:
+        node.cleanup()
 
 
 if __name__ == "__main__":

@@ -5,6 +5,7 @@ the trainer's LR warm-up / flatten rules, the model factory and small modules.""
 import asyncio
 import math
 import os
+import time
 from types import SimpleNamespace
 
 import pytest
@@ -397,16 +398,28 @@ def test_hf_export_matches_model_logits(tmp_path):
 
 def test_small_modules(tmp_path, monkeypatch):
     assert compute_bpb(math.log(2.0) * 80, 10) == pytest.approx(8.0) and math.isinf(compute_bpb(1.0, 0))
-    c = ModelCache(tmp_path / "cache")
-    assert not c.is_valid(1, "v")
-    (tmp_path / "cache").mkdir()
-    (tmp_path / "cache" / "config.json").write_text("{}")
-    c.mark(1, "v")
-    assert c.is_valid(1, "v") and not c.is_valid(2, "v")
+    c = ModelCache(tmp_path / "cache", namespace="v")
+    assert not c.exists(1) and c.get_path(1) == tmp_path / "cache" / "v" / "window_1"
+    for w in (1, 5, 12):
+        c.get_path(w).mkdir(parents=True)
+        (c.get_path(w) / "config.json").write_text("{}")
+    (c.get_path(1) / "model.safetensors").write_bytes(b"x")
+    (c.get_path(5) / "model-00001-of-00002.safetensors").write_bytes(b"x")
+    assert not c.exists(1)                                  # not marked complete yet
+    c.mark(1); c.mark(5); c.mark(12)
+    assert c.exists(1) and c.exists(5) and not c.exists(12) and not c.exists(2)      # 12 has no weight file
+    (c.base_dir / "window_old").mkdir()                                         # not a window directory: left alone
+    assert c.windows() == [1, 5, 12] and c.cleanup(keep_latest=1) == [1, 5]
+    assert c.windows() == [12] and (c.base_dir / "window_old").exists()
     out = tmp_path / "lm"
-    out.mkdir()
-    (out / "results_1.json").write_text('{"results": {"arc_easy": {"acc,none": 0.5, "acc_norm,none": 0.6}, "piqa": {"acc,none": 0.7}}}')
+    (out / "model_name").mkdir(parents=True)
+    (out / "model_name" / "results_1.json").write_text(
+        '{"results": {"arc_easy": {"acc,none": 0.5, "acc_norm,none": 0.6}, "piqa": {"acc,none": 0.7}, "odd": {"f1": 1}}}')
     assert Evaluator.parse_lm_eval_results(out) == {"arc_easy": 0.6, "piqa": 0.7}
+    assert Evaluator.parse_lm_eval_results(out, with_metric=True) == {"arc_easy": ("acc_norm,none", 0.6), "piqa": ("acc,none", 0.7)}
+    (out / "broken.json").write_text("{")
+    os.utime(out / "broken.json", (time.time() + 5, time.time() + 5))
+    assert Evaluator.parse_lm_eval_results(out) == {} and Evaluator.parse_lm_eval_results(tmp_path / "nothing") == {}
     chain = StaticChain(n=3, manual=True)
     chain.advance(400)
     assert burn_run(burn_config(["--max-iterations", "3", "--poll-seconds", "0"]), subtensor=chain, sleep=lambda s: chain.advance(200)) == 2
@@ -547,6 +560,70 @@ def test_evaluator_cli_spellings_and_dataset_path_evaluation(cwd_tmp):
         assert rep["loss"] == pytest.approx(synth["loss"]) and rep["perplexity"] > 1
         assert rep["bits_per_byte"] == pytest.approx(compute_bpb(rep["loss"] * rep["tokens"], 6 * seq * 2))
     run(go())
+
+
+FAKE_HARNESS = """#!/usr/bin/env python3
+import json, os, sys
+a = sys.argv[1:]
+out, tasks = a[a.index("--output_path") + 1], a[a.index("--tasks") + 1].split(",")
+model = dict(kv.split("=", 1) for kv in a[a.index("--model_args") + 1].split(","))["pretrained"]
+assert os.path.exists(os.path.join(model, "config.json")), model
+leaked = [k for k in ("RANK", "WORLD_SIZE", "MASTER_ADDR", "NCCL_DEBUG", "TORCHELASTIC_RUN_ID") if k in os.environ]
+os.makedirs(os.path.join(out, "model"), exist_ok=True)
+if os.environ.get("FAKE_HARNESS_FAIL"):
+    sys.exit(3)
+json.dump({"results": {t: {"acc,none": 0.25, "acc_norm,none": 0.5 - 0.1 * len(leaked)} for t in tasks}},
+          open(os.path.join(out, "model", "results_x.json"), "w"))
+"""
+
+
+def test_evaluator_baseline_then_checkpoints_with_a_task_harness(cwd_tmp, monkeypatch):
+    """Nothing published: the untrained weights are evaluated once at step 0.  Then a checkpoint appears and is
+    evaluated with the downstream-task child process, which gets the exported model and an environment without the
+    launcher's variables; the per-window export cache keeps one window; a failing child leaves no scores."""
+    import json as _json
+    import stat
+
+    bindir = cwd_tmp / "bin"
+    bindir.mkdir()
+    (bindir / "lm_eval").write_text(FAKE_HARNESS)
+    (bindir / "lm_eval").chmod((bindir / "lm_eval").stat().st_mode | stat.S_IXUSR)
+    monkeypatch.setenv("PATH", f"{bindir}{os.pathsep}{os.environ['PATH']}")
+
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        v = _node(Validator, Validator.validator_config, ["--uid", "0", "--peers", "2", "3"], store, chain)
+        v.comms.commitments = await v.comms.get_commitments()
+        await v.comms.post_start_window(3)
+        e = _node(Evaluator, Evaluator.evaluator_config,
+                  ["--uid", "1", "--tasks", "arc_easy,piqa", "--custom-eval-batches", "1", "--no-follow"], store, chain)
+        monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("NCCL_DEBUG", "INFO")      # must not reach the child
+        await e.run()
+        assert e.start_window == 3 and e.baseline_evaluated and e.evaluated_windows == {3} and e.eval_counter == 1
+        assert e.cache.windows() == [3] and e.cache.exists(3)
+        # a checkpoint of window 5 (global step 2) is published; the follow loop picks it up and keeps one export
+        v.global_step = 2
+        await v.ckpt.save_local(model=v.model, window=5, sync_window=5, global_step=2)
+        await v.ckpt.upload(window=5, background=False)
+        await e.run()
+        assert e.evaluated_windows == {3, 5} and e.last_eval_window == 5 and e.cache.windows() == [5]
+        again = await e.evaluate_window(5)
+        assert again["skipped"] and e.eval_counter == 2
+        # failing child: custom metrics still there, no task scores, export still pruned to one window
+        monkeypatch.setenv("FAKE_HARNESS_FAIL", "1")
+        e.config.force_reval = True
+        rep = await e.evaluate_window(5)
+        assert rep["tasks"] == {} and rep["perplexity"] > 1 and rep["global_step"] == 2
+        e.metrics_logger.close()
+    run(go())
+    recs = [_json.loads(l) for l in (cwd_tmp / "metrics.jsonl").read_text().splitlines()]
+    tasks = [r for r in recs if r["measurement"].endswith("benchmark_task")]
+    assert len(tasks) == 4 and {r["tags"]["task"] for r in tasks} == {"arc_easy", "piqa"}
+    assert all(r["fields"]["score"] == pytest.approx(0.5) and r["tags"]["metric"] == "acc_norm,none" for r in tasks)
+    custom = [r for r in recs if r["measurement"].endswith("custom_evaluation")]
+    assert [int(r["tags"]["baseline"]) for r in custom] == [1, 0, 0] and [int(r["tags"]["global_step"]) for r in custom] == [0, 2, 2]
+    summ = [r for r in recs if r["measurement"].endswith("benchmark_summary")]
+    assert len(summ) == 2 and all(r["fields"]["num_tasks"] == 2 for r in summ)
 
 
 def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
