@@ -6,11 +6,17 @@
     python -m templar_b200.bucket_tools get-gradient --uid U --window W [--out file.pt]
     python -m templar_b200.bucket_tools cleanup --keep-windows N [--dry-run]        drop all but the newest N windows
     python -m templar_b200.bucket_tools clean-versions [--keep 2.1.28] [--dry-run]  drop objects of other versions
+    python -m templar_b200.bucket_tools delete-version --version 2.1.20 [--dry-run]   drop every object of one version
+    python -m templar_b200.bucket_tools delete-gather --version 2.1.28 [--dry-run]    drop the stored gather results
+    python -m templar_b200.bucket_tools delete [--prefix P] [--suffix S] [--older-than-hours H] [--all] [--dry-run]
+                                               [--bucket gradients|aggregator|dataset]
+                                               objects that match every given selector (``--all``: the whole bucket)
 
 They work on whatever store the environment selects (a local directory offline, S3 / R2 with credentials; see
 :func:`templar_b200.comms.default_store`), on the bucket that the ``R2_GRADIENTS_*`` variables name (offline: the
 per-uid bucket of ``--uid``).  Counterparts in the reference: scripts/validate_r2_access.py, scripts/s3_manager.py,
-scripts/cleanup_bucket.py, scripts/clean_versions.py, scripts/get_gradients.py.
+scripts/cleanup_bucket.py, scripts/clean_versions.py, scripts/delete_version.py, scripts/delete_gather.py,
+scripts/get_gradients.py.
 """
 
 from __future__ import annotations
@@ -84,6 +90,40 @@ async def clean_versions(store: ObjectStore, bucket, keep: str = __version__, dr
     return doomed
 
 
+async def delete_selected(store: ObjectStore, bucket, *, prefix: str = "", suffix: str = "", older_than_hours: float | None = None,
+                          everything: bool = False, dry_run: bool = False, now: datetime | None = None) -> list[str]:
+    """Delete the objects that match every selector given (name prefix, name suffix, age).  Without a selector
+    nothing is deleted unless ``everything`` says that the whole bucket is meant."""
+    if not (prefix or suffix or older_than_hours is not None or everything):
+        raise ValueError("no selector given: pass a prefix, a suffix, an age, or everything=True for the whole bucket")
+    now = now or datetime.now(timezone.utc)
+    doomed = []
+    for o in await store.list(bucket, prefix):
+        if suffix and not o.key.endswith(suffix):
+            continue
+        if older_than_hours is not None and (now - o.last_modified).total_seconds() < older_than_hours * 3600.0:
+            continue
+        doomed.append(o.key)
+    if doomed and not dry_run:
+        await store.delete(bucket, doomed)
+    return doomed
+
+
+async def delete_version(store: ObjectStore, bucket, version: str, dry_run: bool = False) -> list[str]:
+    """Delete every object that carries ``version`` in its name or path (gradients, debug dictionaries, peer lists,
+    start window, aggregated gradients, checkpoints, gather results)."""
+    doomed = [o.key for o in await store.list(bucket, "")
+              if classify(o.key)[2] == version or o.key.startswith(f"gathers/{version}/")]
+    if doomed and not dry_run:
+        await store.delete(bucket, doomed)
+    return doomed
+
+
+async def delete_gather(store: ObjectStore, bucket, version: str = __version__, dry_run: bool = False) -> list[str]:
+    """Delete the gather results stored under ``gathers/<version>/``."""
+    return await delete_selected(store, bucket, prefix=f"gathers/{version}/", dry_run=dry_run)
+
+
 async def get_gradient(store: ObjectStore, bucket, uid: int, window: int, version: str = __version__) -> dict | None:
     data = await store.get_bytes(bucket, f"gradient-{window}-{uid}-v{version}.pt")
     if data is None:
@@ -103,7 +143,13 @@ def describe_gradient(obj: dict) -> dict:
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("command", choices=["validate", "list", "summary", "get-gradient", "cleanup", "clean-versions"])
+    ap.add_argument("command", choices=["validate", "list", "summary", "get-gradient", "cleanup", "clean-versions",
+                                        "delete-version", "delete-gather", "delete"])
+    ap.add_argument("--bucket", choices=["gradients", "aggregator", "dataset"], default="gradients")
+    ap.add_argument("--version", default=__version__)
+    ap.add_argument("--suffix", default="")
+    ap.add_argument("--older-than-hours", type=float, default=None)
+    ap.add_argument("--all", action="store_true", help="delete: the whole bucket")
     ap.add_argument("--uid", type=int, default=0)
     ap.add_argument("--window", type=int, default=None)
     ap.add_argument("--prefix", default="")
@@ -116,7 +162,8 @@ def main(argv=None):
     from .comms import Comms
 
     comms = Comms(wallet=StaticWallet(f"hotkey-{a.uid}"), uid=a.uid)
-    store, bucket = comms.store, comms.bucket
+    store = comms.store
+    bucket = comms.bucket if a.bucket == "gradients" else comms.get_own_bucket(a.bucket, "write")
     now = datetime.now(timezone.utc)
 
     async def run():
@@ -139,7 +186,15 @@ def main(argv=None):
             gone = await cleanup(store, bucket, a.keep_windows, a.dry_run)
             print(f"{'would delete' if a.dry_run else 'deleted'} {len(gone)} objects")
         else:
-            gone = await clean_versions(store, bucket, a.keep, a.dry_run)
+            if a.command == "clean-versions":
+                gone = await clean_versions(store, bucket, a.keep, a.dry_run)
+            elif a.command == "delete-version":
+                gone = await delete_version(store, bucket, a.version, a.dry_run)
+            elif a.command == "delete-gather":
+                gone = await delete_gather(store, bucket, a.version, a.dry_run)
+            else:
+                gone = await delete_selected(store, bucket, prefix=a.prefix, suffix=a.suffix, older_than_hours=a.older_than_hours,
+                                             everything=a.all, dry_run=a.dry_run)
             print(f"{'would delete' if a.dry_run else 'deleted'} {len(gone)} objects")
     asyncio.run(run())
 

@@ -54,3 +54,44 @@ def test_validate_summary_cleanup_and_versions():
         assert d["global_step"] == 5 and d["tensors"] == 1 and d["values"] == 4 and d["index_bytes"] == 6 and not d["quantised"]
         assert await bt.get_gradient(st, B, 3, 99, "2.1.28") is None
     asyncio.run(go())
+
+
+def test_delete_by_selector_version_and_gather_results(tmp_path, monkeypatch):
+    import os
+    import time
+
+    import pytest
+
+    from templar_b200.backends.store import LocalFSStore
+
+    async def go():
+        st = LocalFSStore(tmp_path)
+        names = ["gradient-1-3-v2.1.20.pt", "gradient-2-3-v2.1.28.pt", "debug-2-3-v2.1.28.pt", "peers_4_v2.1.20.json",
+                 "checkpoints/2.1.20/4/.metadata", "gathers/2.1.20/3.pt", "gathers/2.1.28/9.pt", "notes.txt"]
+        for n in names:
+            await st.put_bytes(B, n, b"x")
+        with pytest.raises(ValueError):
+            await bt.delete_selected(st, B)                                   # no selector: refuses
+        assert await bt.delete_gather(st, B, "2.1.28", dry_run=True) == ["gathers/2.1.28/9.pt"]
+        assert sorted(await bt.delete_version(st, B, "2.1.20")) == sorted(n for n in names if "2.1.20" in n)
+        left = sorted(o.key for o in await st.list(B, ""))
+        assert left == sorted(["gradient-2-3-v2.1.28.pt", "debug-2-3-v2.1.28.pt", "gathers/2.1.28/9.pt", "notes.txt"])
+        assert sorted(await bt.delete_selected(st, B, prefix="g", suffix=".pt", dry_run=True)) == ["gathers/2.1.28/9.pt", "gradient-2-3-v2.1.28.pt"]
+        # age: only the object that was last written two hours ago
+        old = st._path(B, "notes.txt")
+        os.utime(old, (time.time() - 7200, time.time() - 7200))
+        assert await bt.delete_selected(st, B, older_than_hours=1.0) == ["notes.txt"]
+        assert len(await bt.delete_selected(st, B, everything=True)) == 3 and await st.list(B, "") == []
+    asyncio.run(go())
+
+    # the command line on the offline store of the environment
+    monkeypatch.setenv("TPLR_STORE", "local")
+    monkeypatch.setenv("TPLR_STORE_ROOT", str(tmp_path / "cli"))
+    from templar_b200.backends.chain import StaticWallet
+    from templar_b200.comms import Comms
+    c = Comms(wallet=StaticWallet("hotkey-0"), uid=0)
+    asyncio.run(c.store.put_bytes(c.bucket, "gathers/9.9.9/1.pt", b"x"))
+    bt.main(["delete-gather", "--version", "9.9.9", "--dry-run"])
+    assert asyncio.run(c.store.head(c.bucket, "gathers/9.9.9/1.pt")) is not None
+    bt.main(["delete-gather", "--version", "9.9.9"])
+    assert asyncio.run(c.store.head(c.bucket, "gathers/9.9.9/1.pt")) is None
