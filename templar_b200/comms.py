@@ -153,8 +153,19 @@ class Comms(ChainManager):
                 if tmax is not None and lm > tmax:
                     return {"__status": "TOO_LATE"}
                 if not load_data:
-                    # materialise next to where the caller expects the file (dataset shards)
-                    return await self.store.get_to_file(bucket, key, key if os.path.isabs(key) else tmp)
+                    # the object becomes a local file at the path that the key spells (dataset shards are kept under
+                    # the same relative or absolute path in the bucket and on disk; reference: src/tplr/comms.py:
+                    # 608-617); written beside it first, so that a reader never sees half a file
+                    part = f"{key}.part{os.getpid()}"
+                    os.makedirs(os.path.dirname(key) or ".", exist_ok=True)
+                    try:
+                        if not await self.store.get_to_file(bucket, key, part):
+                            return None
+                        os.replace(part, key)
+                    finally:
+                        if os.path.exists(part):
+                            os.remove(part)
+                    return key
                 ok = await asyncio.wait_for(self.store.get_to_file(bucket, key, tmp), timeout=max(timeout, 1) * 10)
                 if not ok:
                     return None

@@ -12,7 +12,11 @@ Three steps, each a function and a sub-command of ``python -m templar_b200.datas
 * ``synthetic``    a small shard of seeded random tokens with its ids, for smoke tests and air-gapped
   boxes (the role of scripts/dataset_prep/single_testing_shard.py).
 
-Object-store upload is not part of this module: ``templar_b200.comms`` moves files.
+* ``upload`` / ``download``  shards and their ids between a directory and the dataset bucket, under the key that
+  the nodes ask for (``$DATASET_BINS_PATH/<file name>``; scripts/download_dataset.py, and the upload half of
+  scripts/dataset_prep/02_consolidate_shards.py);
+* ``scan``         per shard: tokens, sequences, dtype, whether the ids file matches (scripts/shard_scanner.py
+  counts rows of the raw dataset the same way, from metadata only: the token file is memory-mapped).
 """
 
 from __future__ import annotations
@@ -148,6 +152,79 @@ def synthetic_shard(directory: str, index: int, n_tokens: int, seq_len: int, voc
     return os.path.join(directory, tok_name), write_sample_ids(directory, index, seq_len, prefix)
 
 
+def shard_key(index: int, prefix: str, which: int, key_root: str | None = None) -> str:
+    """Object key of a shard's token file (``which`` 0) or ids file (1): the path that the nodes build from
+    ``DATASET_BINS_PATH``, which is also where they keep the file on disk."""
+    root = key_root if key_root is not None else os.getenv("DATASET_BINS_PATH", "")
+    return os.path.join(root, shard_names(index, prefix)[which])
+
+
+async def upload_shards(comms, directory: str, indices: Iterable[int], prefix: str = "train", key_root: str | None = None,
+                        seq_len: int | None = None) -> list[str]:
+    """Put the token and ids files of ``indices`` into the dataset bucket (ids are computed first when ``seq_len``
+    is given and the file is missing).  Returns the keys written."""
+    bucket = comms.get_own_bucket("dataset", "write")
+    out = []
+    for i in indices:
+        names = shard_names(i, prefix)
+        if seq_len and not os.path.exists(os.path.join(directory, names[1])):
+            write_sample_ids(directory, i, seq_len, prefix)
+        for which in (0, 1):
+            key = shard_key(i, prefix, which, key_root)
+            await comms.s3_put_object(key, os.path.join(directory, names[which]), bucket)
+            out.append(key)
+    return out
+
+
+async def download_shards(comms, directory: str, indices: Iterable[int], prefix: str = "train", key_root: str | None = None,
+                          overwrite: bool = False) -> dict[int, bool]:
+    """Fetch the token and ids files of ``indices`` from the dataset bucket into ``directory`` (files that are there
+    already are kept).  Returns ``{index: complete}``."""
+    bucket = comms.get_own_bucket("dataset", "read")
+    os.makedirs(directory, exist_ok=True)
+    done = {}
+    for i in indices:
+        ok = True
+        for which, name in enumerate(shard_names(i, prefix)):
+            dest = os.path.join(directory, name)
+            if os.path.exists(dest) and not overwrite:
+                continue
+            part = dest + ".part"
+            got = await comms.store.get_to_file(bucket, shard_key(i, prefix, which, key_root), part)
+            if got:
+                os.replace(part, dest)
+            elif os.path.exists(part) and not os.path.exists(part + ".progress"):
+                os.remove(part)                           # nothing worth resuming
+            ok = ok and bool(got)
+        done[i] = ok
+    return done
+
+
+def scan_shards(directory: str, prefix: str = "train", seq_len: int = 2048) -> list[dict]:
+    """One record per ``<prefix>_*.npy`` shard in ``directory``: size, dtype, sequences, and whether the ids file
+    exists with one id per complete sequence.  Reads headers only (memory map)."""
+    out = []
+    for f in sorted(glob.glob(os.path.join(directory, f"{prefix}_*.npy"))):
+        stem = os.path.basename(f)[len(prefix) + 1: -4]
+        if not stem.isdigit():
+            continue
+        tok = np.load(f, mmap_mode="r", allow_pickle=False)
+        ids_path = os.path.join(directory, shard_names(int(stem), prefix)[1])
+        n_ids = int(np.load(ids_path, mmap_mode="r", allow_pickle=False).shape[0]) if os.path.exists(ids_path) else None
+        out.append({"shard": int(stem), "file": f, "tokens": int(tok.shape[0]), "dtype": str(tok.dtype),
+                    "bytes": os.path.getsize(f), "sequences": int(tok.shape[0]) // seq_len,
+                    "leftover_tokens": int(tok.shape[0]) % seq_len, "ids": n_ids,
+                    "ids_ok": n_ids is not None and n_ids == int(tok.shape[0]) // seq_len})
+    return out
+
+
+def _dataset_comms(uid: int = 0):
+    from .backends.chain import StaticWallet
+    from .comms import Comms
+
+    return Comms(wallet=StaticWallet(f"hotkey-{uid}"), uid=uid)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -176,8 +253,36 @@ def main(argv=None) -> int:
     p.add_argument("--vocab-size", type=int, default=128256)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--prefix", default="train")
+    for name in ("upload", "download"):
+        p = sub.add_parser(name)
+        p.add_argument("shards", type=int, nargs="*", default=[0, 1], help="shard indices (default: 0 and 1)")
+        p.add_argument("--path", "-p", default=os.getenv("DATASET_BINS_PATH", "."), help="local directory")
+        p.add_argument("--prefix", default="train")
+        p.add_argument("--key-root", default=None, help="directory part of the object keys (default: $DATASET_BINS_PATH)")
+        if name == "upload":
+            p.add_argument("--seq-len", type=int, default=None, help="compute missing ids files with this sequence length")
+        else:
+            p.add_argument("--overwrite", action="store_true")
+    p = sub.add_parser("scan")
+    p.add_argument("--dir", default=os.getenv("DATASET_BINS_PATH", "."))
+    p.add_argument("--prefix", default="train")
+    p.add_argument("--seq-len", type=int, default=2048)
     a = ap.parse_args(argv)
-    if a.cmd == "pretokenize":
+    if a.cmd in ("upload", "download"):
+        import asyncio
+
+        comms = _dataset_comms()
+        if a.cmd == "upload":
+            keys = asyncio.run(upload_shards(comms, a.path, a.shards, a.prefix, a.key_root, a.seq_len))
+            print(f"uploaded {len(keys)} objects")
+        else:
+            done = asyncio.run(download_shards(comms, a.path, a.shards, a.prefix, a.key_root, a.overwrite))
+            print(json.dumps({str(k): v for k, v in done.items()}))
+            return 0 if all(done.values()) else 1
+    elif a.cmd == "scan":
+        for rec in scan_shards(a.dir, a.prefix, a.seq_len):
+            print(json.dumps(rec))
+    elif a.cmd == "pretokenize":
         from transformers import AutoTokenizer
 
         files = sorted(f for pat in a.input for f in (glob.glob(pat) or [pat]))

@@ -1,8 +1,10 @@
 """Page-addressed streaming dataset on an in-memory row source (no network)."""
 
 import asyncio
+import os
 
 import numpy as np
+import torch
 
 from templar_b200.dataset import DatasetLoader, MemoryRowSource, SubsetLoader
 
@@ -174,3 +176,54 @@ def test_http_row_source_against_a_local_rows_service():
             await runner.cleanup()
 
     asyncio.run(go())
+
+
+def test_shards_travel_through_the_dataset_bucket_and_the_manager_rotates_them(tmp_path, monkeypatch):
+    """Shards uploaded with the prep tool are what a node's dataset manager downloads under a RELATIVE dataset path
+    (the key is the path): the active shard on demand, the next one ahead of time, and after a swap the old files go."""
+    import asyncio
+    import json
+
+    from templar_b200 import dataset_prep as P
+    from templar_b200.backends.chain import StaticWallet
+    from templar_b200.backends.store import MemoryStore
+    from templar_b200.comms import Comms
+    from templar_b200.sharded_dataset import ShardedDatasetManager
+
+    seq, src = 8, tmp_path / "src"
+    for i in range(3):
+        P.synthetic_shard(str(src), i, seq * 5, seq, 100, seed=7)
+    os.remove(src / "sample_ids_000002.npy")
+    recs = P.scan_shards(str(src), "train", seq)
+    assert [r["shard"] for r in recs] == [0, 1, 2] and recs[0]["sequences"] == 5 and recs[0]["leftover_tokens"] == 0
+    assert recs[0]["ids_ok"] and recs[2]["ids"] is None and not recs[2]["ids_ok"]
+    P.synthetic_shard(str(tmp_path / "ragged"), 4, seq * 5 + 3, seq, 100, seed=7)
+    rag = P.scan_shards(str(tmp_path / "ragged"), "train", seq)[0]
+    assert (rag["shard"], rag["sequences"], rag["leftover_tokens"], rag["ids_ok"], rag["dtype"]) == (4, 5, 3, True, "uint32")
+
+    work = tmp_path / "node"
+    work.mkdir()
+    monkeypatch.chdir(work)
+    monkeypatch.setenv("DATASET_BINS_PATH", "remote/tokenized")
+    comms = Comms(wallet=StaticWallet("hotkey-1"), uid=1, store=MemoryStore())
+
+    async def go():
+        keys = await P.upload_shards(comms, str(src), [0, 1, 2], seq_len=seq)       # computes the missing ids of shard 2
+        assert "remote/tokenized/train_000001.npy" in keys and len(keys) == 6 and (src / "sample_ids_000002.npy").exists()
+        mgr = ShardedDatasetManager(seq, 0, 1, comms)
+        mgr.max_dataset_idx = 3
+        await mgr.initialize_datasets(0)
+        assert len(mgr.active_dataset) == 5 and os.path.exists("remote/tokenized/train_000000.npy")
+        await mgr.upcoming_dataset
+        assert os.path.exists("remote/tokenized/train_000001.npy") and os.path.exists("remote/tokenized/sample_ids_000001.npy")
+        assert not [f for f in os.listdir("remote/tokenized") if ".part" in f]
+        first = mgr.active_dataset[1].clone()
+        assert await mgr.swap_datasets() == 1
+        assert not os.path.exists("remote/tokenized/train_000000.npy") and mgr.active_dataset.tokens_file.endswith("train_000001.npy")
+        assert not torch.equal(first, mgr.active_dataset[1])
+        await mgr.upcoming_dataset
+        # the stand-alone downloader: keeps what is there, reports a shard that the bucket does not have
+        done = await P.download_shards(comms, str(tmp_path / "dl"), [2, 9])
+        assert done == {2: True, 9: False} and sorted(os.listdir(tmp_path / "dl")) == ["sample_ids_000002.npy", "train_000002.npy"]
+    asyncio.run(go())
+    assert P.main(["scan", "--dir", str(tmp_path / "dl"), "--seq-len", str(seq)]) == 0
