@@ -25,5 +25,8 @@ def get_shard_profiler(name: str | None = None):
     return _shard
 
 
-__all__ = ["TimerProfiler", "ShardProfiler", "DummyTimerProfiler", "DummyShardProfiler", "CudaEventTimer",
+get_profiler = get_shard_profiler          # the reference's name for the shard profiler's accessor
+
+
+__all__ = ["get_profiler", "TimerProfiler", "ShardProfiler", "DummyTimerProfiler", "DummyShardProfiler", "CudaEventTimer",
            "get_timer_profiler", "get_shard_profiler"]

@@ -22,7 +22,14 @@ class TimerProfiler:
     def __init__(self, name: str = "TimerProfiler"):
         self.name = name
         self.timings: dict[str, list[float]] = defaultdict(list)
+        self.errors: dict[str, int] = defaultdict(int)
         self.active: dict[str, float] = {}
+
+    def _record_timing(self, name: str, elapsed: float, error: bool = False) -> None:
+        """One finished call of ``name``; a call that raised is timed too and counted as an error."""
+        self.timings[name].append(elapsed)
+        if error:
+            self.errors[name] += 1
 
     def start_timer(self, name: str) -> None:
         self.active[name] = time.perf_counter()
@@ -41,40 +48,53 @@ class TimerProfiler:
             if asyncio.iscoroutinefunction(fn):
                 @functools.wraps(fn)
                 async def awrap(*a, **kw):
-                    t0 = time.perf_counter()
+                    t0, failed = time.perf_counter(), True
                     try:
-                        return await fn(*a, **kw)
+                        out = await fn(*a, **kw)
+                        failed = False
+                        return out
                     finally:
-                        self.timings[label].append(time.perf_counter() - t0)
+                        self._record_timing(label, time.perf_counter() - t0, error=failed)
                 return awrap
 
             @functools.wraps(fn)
             def wrap(*a, **kw):
-                t0 = time.perf_counter()
+                t0, failed = time.perf_counter(), True
                 try:
-                    return fn(*a, **kw)
+                    out = fn(*a, **kw)
+                    failed = False
+                    return out
                 finally:
-                    self.timings[label].append(time.perf_counter() - t0)
+                    self._record_timing(label, time.perf_counter() - t0, error=failed)
             return wrap
         return deco
 
     def get_stats(self, func_name: str | None = None) -> dict:
-        def one(v):
-            return {"count": len(v), "total": sum(v), "min": min(v), "max": max(v), "mean": sum(v) / len(v)} if v else {}
+        """Per function: count, errors, total / min / max / mean seconds (``avg`` is the same number under the
+        reference's key) and the last ten durations."""
+        def one(k, v):
+            if not v:
+                return {}
+            mean = sum(v) / len(v)
+            return {"function": k, "count": len(v), "errors": self.errors.get(k, 0), "total": sum(v), "min": min(v),
+                    "max": max(v), "mean": mean, "avg": mean, "timings": v[-10:]}
         if func_name is not None:
-            return one(self.timings.get(func_name, []))
-        return {k: one(v) for k, v in self.timings.items()}
+            return one(func_name, self.timings.get(func_name, []))
+        return {k: one(k, v) for k, v in self.timings.items()}
 
     def log_summary(self) -> None:
         for k, s in sorted(self.get_stats().items(), key=lambda kv: -kv[1].get("total", 0)):
-            logger.info(f"[{self.name}] {k}: n={s['count']} total={s['total']:.3f}s mean={s['mean'] * 1e3:.2f}ms "
+            logger.info(f"[{self.name}] {k}: n={s['count']} errors={s['errors']} total={s['total']:.3f}s mean={s['mean'] * 1e3:.2f}ms "
                         f"min={s['min'] * 1e3:.2f}ms max={s['max'] * 1e3:.2f}ms")
 
     def reset(self, func_name: str | None = None) -> None:
         if func_name is None:
             self.timings.clear()
+            self.errors.clear()
+            self.active.clear()
         else:
             self.timings.pop(func_name, None)
+            self.errors.pop(func_name, None)
 
 
 class DummyTimerProfiler:
@@ -85,6 +105,7 @@ class DummyTimerProfiler:
 
     def start_timer(self, name): return None
     def end_timer(self, name): return 0.0
+    def _record_timing(self, *a, **k): return None
     def get_stats(self, func_name=None): return {}
     def log_summary(self): return None
     def reset(self, func_name=None): return None

@@ -22,6 +22,7 @@ import torch.distributed as dist
 from torch.utils.data import Dataset
 
 from .logging import logger
+from .profilers import get_shard_profiler
 
 
 def compute_shard_state(global_step: int, outer_steps_per_shard: int, reset_outer_step: int | None = None) -> tuple[int, int]:
@@ -46,7 +47,11 @@ class SharedShardedDataset(Dataset):
                 dist.barrier()
         self.tokens_file, self.ids_file = self.locate_shards(shard_index, custom_path, file_prefix)
         self.check_paths([self.tokens_file, self.ids_file])
+        prof = get_shard_profiler()                       # a no-op stand-in unless the profilers are switched on
+        tid = prof.start_read(self.tokens_file, {"shard": shard_index, "rank": rank, "what": "open"})
         self.mmap_tokens_and_ids(token_dtype)
+        prof.log_shard_metadata(self.tokens_file, os.path.getsize(self.tokens_file), 1, self.total_samples)
+        prof.end_read(tid, self.tokens_file)
         logger.info(f"[Dataset] rank {rank}: shard {shard_index} ready in {time.perf_counter() - t0:.1f}s "
                     f"({self.total_samples} samples)")
 
@@ -147,6 +152,14 @@ class ShardedDatasetManager:
         return asyncio.create_task(self.download_files(bucket, tokens_file, ids_file))
 
     async def download_files(self, bucket, tokens_file, ids_file):
+        prof = get_shard_profiler()
+        tid = prof.start_read(tokens_file, {"what": "download"})
+        try:
+            return await self._download_files(bucket, tokens_file, ids_file)
+        finally:
+            prof.end_read(tid, tokens_file)
+
+    async def _download_files(self, bucket, tokens_file, ids_file):
         return await asyncio.gather(self.comms.s3_get_object(tokens_file, bucket, load_data=False),
                                     self.comms.s3_get_object(ids_file, bucket, load_data=False))
 

@@ -447,6 +447,28 @@ def test_small_modules(tmp_path, monkeypatch):
     async def g():
         return 4
     assert f() == 3 and run(g()) == 4 and tp.get_stats("f")["count"] == 1 and tp.get_stats()["g"]["count"] == 1
+
+    @tp.profile("boom")
+    def boom():
+        raise KeyError("x")
+
+    @tp.profile("aboom")
+    async def aboom():
+        raise KeyError("y")
+    for _ in range(12):
+        with pytest.raises(KeyError):
+            boom()
+    with pytest.raises(KeyError):
+        run(aboom())
+    sb = tp.get_stats("boom")
+    assert (sb["count"], sb["errors"], len(sb["timings"]), sb["function"]) == (12, 12, 10, "boom") and sb["avg"] == sb["mean"]
+    assert tp.get_stats("aboom")["errors"] == 1 and tp.get_stats("f")["errors"] == 0 and tp.get_stats("nope") == {}
+    tp.start_timer("region"); assert tp.end_timer("region") >= 0 and tp.end_timer("region") == 0.0
+    tp.log_summary()
+    tp.reset("boom")
+    assert "boom" not in tp.get_stats() and "f" in tp.get_stats()
+    tp.reset()
+    assert tp.get_stats() == {}
     assert DummyTimerProfiler().profile("x")(f)() == 3
     sp = ShardProfiler("s", slow_read_s=10)
     sp.end_read(sp.start_read("a.npy", {"idx": 1}))
