@@ -467,7 +467,16 @@ class Evaluator(BaseNode, Trainer):
         follow new checkpoints every ``eval_interval`` seconds (reference: neurons/evaluator.py:1113-1222)."""
         self.loop = asyncio.get_running_loop()
         self.comms.commitments = await self.comms.get_commitments()
-        sw = (await self.comms.get_start_window(version=self.version)) if self.is_master else None
+        sw = None
+        if self.is_master:
+            # on a network the start window always appears (the validators publish it) and the evaluator waits for it;
+            # an offline run may have no validator at all and then counts its steps from the window it starts in
+            offline = bool(getattr(self.config, "local", False))
+            sw = await self.comms.get_start_window(version=self.version, retries=3 if offline else -1,
+                                                   retry_delay=0.5 if offline else 10.0)
+            if sw is None:
+                sw = int(self.current_window)
+                tplr.logger.warning(f"[eval] no start window published; counting steps from window {sw}")
         self.start_window = self._from_master(sw)[0]
         backfill = self.config.backfill_start is not None or self.config.backfill_end is not None
         first = True

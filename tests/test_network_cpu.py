@@ -648,6 +648,19 @@ def test_evaluator_baseline_then_checkpoints_with_a_task_harness(cwd_tmp, monkey
     assert len(summ) == 2 and all(r["fields"]["num_tasks"] == 2 for r in summ)
 
 
+def test_offline_evaluator_without_any_validator_evaluates_the_untrained_weights(cwd_tmp):
+    """No validator, hence no start window and no checkpoint: an offline evaluator does not wait for ever; it counts its
+    steps from the window it starts in and reports the baseline."""
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        e = _node(Evaluator, Evaluator.evaluator_config, ["--uid", "1", "--skip-lm-eval", "--custom-eval-batches", "1", "--no-follow"],
+                  store, chain)
+        e.current_window = 7
+        await asyncio.wait_for(e.run(), timeout=60)
+        assert e.start_window == 7 and e.baseline_evaluated and e.evaluated_windows == {7}
+    run(go())
+
+
 def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
     """Outside local mode the first validator_offset + peer_list_window_margin windows after the start window, and
     windows without gather peers, are null rounds: no inner update is kept and nothing is fed into the error feedback."""
