@@ -166,16 +166,27 @@ class Validator(BaseNode, Trainer):
                 "consecutive_negative_count": dict(self.consecutive_negative_count)}
 
     async def save_state(self):
+        """Scores, ratings and the step counter to ``state_path``: rank 0 only (the other ranks hold no scores of their
+        own, reference neurons/validator.py:3795-3811), written beside the file and renamed, so that a restart
+        never reads half a file."""
+        if not getattr(self, "is_master", True):
+            return
+        tmp = f"{self.state_path}.tmp{os.getpid()}"
         try:
-            await asyncio.to_thread(torch.save, self._state_dict(), self.state_path)
+            await asyncio.to_thread(torch.save, self._state_dict(), tmp)
+            os.replace(tmp, self.state_path)
         except Exception as e:  # noqa: BLE001
             tplr.logger.warning(f"Failed to save validator state: {e}")
+            if os.path.exists(tmp):
+                os.remove(tmp)
 
     def load_state(self):
         if not os.path.exists(self.state_path):
             return
         try:
-            st = torch.load(self.state_path, map_location="cpu", weights_only=False)
+            st = torch.load(self.state_path, map_location="cpu", weights_only=True)    # tensors, numbers and dicts only
+            if not isinstance(st, dict):
+                raise TypeError(f"state file holds a {type(st).__name__}, not a dict")
         except Exception as e:  # noqa: BLE001
             tplr.logger.warning(f"Failed to load validator state: {e}")
             return

@@ -894,4 +894,15 @@ def test_validator_state_round_trip(cwd_tmp):
         w.global_step = 1
         w.load_state()
         assert w.global_step == 1
+        torch.save([1, 2, 3], v.state_path)                      # readable, but not a state dictionary
+        w.load_state()
+        assert w.global_step == 1
+        # only rank 0 writes the file; nothing half-written is left beside it
+        os.remove(v.state_path)
+        v.is_master = False
+        await v.save_state()
+        assert not os.path.exists(v.state_path)
+        v.is_master = True
+        await v.save_state()
+        assert os.path.exists(v.state_path) and not [f for f in os.listdir(".") if ".tmp" in f]
     run(go())
