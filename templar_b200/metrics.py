@@ -2,9 +2,10 @@
 
 Interface parity with the reference's ``MetricsLogger`` (src/tplr/metrics.py:63-368): ``log(measurement,
 tags, fields, timestamp=None, with_system_metrics=False, with_gpu_metrics=False, sample_rate=1.0)``
-queues a point (queue bound 600 000) that a private writer thread flushes in batches; list-valued
-fields are expanded to mean/min/max/median statistics; system (psutil) and GPU memory fields are
-added on request; tags carry role / uid / version / host config.
+queues a point (queue bound 600 000) that a private writer thread flushes in batches; lists of numbers
+are expanded to mean/min/max/median statistics and lists of integers (uids) are written as text; system
+(psutil) and GPU memory fields are added on request; tags carry uid / prefix / version / runtime id /
+role / group / job type and one ``config_<name>`` per scalar option of the node.
 
 Sinks: InfluxDB when ``influxdb_client`` is importable and a token is configured, otherwise (and in
 addition when ``TPLR_METRICS_JSONL`` is set) a JSON-lines file — the offline sink.
@@ -43,16 +44,22 @@ def get_system_metrics() -> dict[str, float]:
         return {}
 
 
-def get_gpu_metrics() -> dict[str, float]:
+def get_gpu_metrics() -> dict[str, Any]:
+    """Allocator figures of the current device; ``gpu_id`` / ``gpu_name`` become tags of the point."""
     if not torch.cuda.is_available():
         return {}
     try:
-        return {"gpu_mem_segments": float(torch.cuda.memory_stats().get("segment.all.current", 0)),
-                "gpu_mem_allocated_mb": torch.cuda.memory_allocated() / 1024 ** 2,
-                "gpu_mem_cached_mb": torch.cuda.memory_reserved() / 1024 ** 2,
-                "gpu_mem_total_mb": torch.cuda.max_memory_allocated() / 1024 ** 2}
+        dev = torch.cuda.current_device()
+        return {"gpu_mem_segments": float(torch.cuda.memory_stats(dev).get("segment.all.current", 0)),
+                "gpu_mem_allocated_mb": torch.cuda.memory_allocated(dev) / 1024 ** 2,
+                "gpu_mem_cached_mb": torch.cuda.memory_reserved(dev) / 1024 ** 2,
+                "gpu_mem_total_mb": torch.cuda.max_memory_allocated(dev) / 1024 ** 2,
+                "gpu_name": f"CUDA:{dev}", "gpu_id": dev}
     except Exception:  # noqa: BLE001
         return {}
+
+
+RUNTIME_ID = os.environ.get("TPLR_RUNTIME_ID") or f"{int(time.time()):x}-{os.getpid():x}"      # one per process start
 
 
 class _JsonlSink:
@@ -92,9 +99,10 @@ class MetricsLogger:
     def __init__(self, prefix: str = "", uid: str | None = None, role: str = "", config: Any = None, group: str = "",
                  job_type: str = "", host: str = DEFAULT_HOST, port: int = DEFAULT_PORT, token: str | None = None,
                  org: str = DEFAULT_ORG, database: str = DEFAULT_BUCKET, max_queue_size: int = 600_000,
-                 batch_size: int = 500, flush_interval: float = 5.0, jsonl_path: str | None = None):
+                 batch_size: int = 500, flush_interval: float = 5.0, jsonl_path: str | None = None,
+                 version: str = __version__, runtime_id: str = RUNTIME_ID):
         self.prefix, self.uid, self.role, self.config = prefix, uid, role, config
-        self.group, self.job_type = group, job_type
+        self.group, self.job_type, self.version, self.runtime_id = group, job_type, version, runtime_id
         self.batch_size, self.flush_interval = batch_size, flush_interval
         self._q: queue.Queue = queue.Queue(maxsize=max_queue_size)
         self._sinks = []
@@ -118,10 +126,12 @@ class MetricsLogger:
             return
         try:
             f = self.process_fields(fields)
+            tags = dict(tags or {})
             if with_system_metrics:
                 f.update(get_system_metrics())
             if with_gpu_metrics:
-                f.update(get_gpu_metrics())
+                for k, v in get_gpu_metrics().items():
+                    (tags if k in ("gpu_id", "gpu_name") else f)[k] = v
             point = {"measurement": f"{self.prefix}{measurement}", "tags": self._tags(tags), "fields": f,
                      "time": timestamp if timestamp is not None else time.time()}
             self._q.put_nowait(point)
@@ -130,39 +140,54 @@ class MetricsLogger:
         except Exception as e:  # noqa: BLE001
             logger.debug(f"metrics log failed: {e}")
 
+    def process_value(self, v):
+        """One field value in the form the time-series store takes (reference src/tplr/metrics.py:155-181): numbers
+        stay numbers (booleans as 0 / 1); a non-empty list of integers is a list of uids and is written as its text; any
+        other list of numbers becomes mean / min / max / median (and count); an empty list and None are 0.0; tensors
+        are read back (one element: the number, more: the list); everything else is its text."""
+        if isinstance(v, torch.Tensor):
+            v = v.detach().float().cpu().tolist() if v.numel() > 1 else float(v)
+        if isinstance(v, bool):
+            return int(v)
+        if isinstance(v, (int, float)):
+            return v
+        if isinstance(v, (list, tuple)):
+            if not v:
+                return 0.0
+            if all(isinstance(x, int) and not isinstance(x, bool) for x in v):
+                return str(list(v))
+            nums = [float(x) for x in v if isinstance(x, (int, float))]
+            if not nums:
+                return str(list(v))
+            return {"mean": statistics.fmean(nums), "min": min(nums), "max": max(nums), "median": statistics.median(nums),
+                    "count": len(nums)}
+        if v is None:
+            return 0.0
+        return str(v)
+
     def process_fields(self, fields: dict) -> dict:
         out = {}
         for k, v in fields.items():
-            if v is None:
-                continue
-            if isinstance(v, torch.Tensor):
-                v = v.detach().float().cpu().tolist() if v.numel() > 1 else float(v)
-            if isinstance(v, (list, tuple)):
-                nums = [float(x) for x in v if isinstance(x, (int, float))]
-                if nums:
-                    out[f"{k}_mean"], out[f"{k}_min"], out[f"{k}_max"] = statistics.fmean(nums), min(nums), max(nums)
-                    out[f"{k}_median"] = statistics.median(nums)
-                    out[f"{k}_count"] = len(nums)
-                else:
-                    out[k] = str(list(v))
-            elif isinstance(v, bool):
-                out[k] = int(v)
-            elif isinstance(v, (int, float)):
-                out[k] = v
+            pv = self.process_value(v)
+            if isinstance(pv, dict):
+                out.update({f"{k}_{stat}": x for stat, x in pv.items()})
             else:
-                out[k] = str(v)
+                out[k] = pv
         return out
 
     def _tags(self, tags: dict) -> dict:
-        base = {"version": __version__, "role": self.role or "unknown", "uid": str(self.uid)}
-        if self.group:
-            base["group"] = self.group
-        if self.job_type:
-            base["job_type"] = self.job_type
+        """Standard tags (uid, prefix, version, runtime id, role, group, job type: those that are set), one
+        ``config_<name>`` tag per scalar attribute of the node's config, then the caller's tags."""
+        base = {k: str(v) for k, v in (("uid", self.uid), ("prefix", self.prefix), ("version", self.version),
+                                       ("runtime_id", self.runtime_id), ("role", self.role or "unknown"),
+                                       ("group", self.group), ("job_type", self.job_type)) if v not in (None, "")}
         cfg = self.config
-        for attr in ("netuid", "device"):
-            if cfg is not None and getattr(cfg, attr, None) is not None:
-                base[f"config_{attr}"] = str(getattr(cfg, attr))
+        try:
+            for key, value in (vars(cfg) if cfg is not None and hasattr(cfg, "__dict__") else {}).items():
+                if not key.startswith("_") and value is not None and isinstance(value, (str, int, float, bool)):
+                    base[f"config_{key}"] = str(value)
+        except Exception as e:  # noqa: BLE001
+            logger.debug(f"config tags skipped: {e}")
         base.update({k: str(v) for k, v in (tags or {}).items()})
         return base
 

@@ -426,13 +426,24 @@ def test_small_modules(tmp_path, monkeypatch):
     from templar_b200.metrics import MetricsLogger
     from templar_b200.profilers import TimerProfiler, ShardProfiler, DummyTimerProfiler
     from templar_b200.wandb_ops import NullRun, versioned
-    ml = MetricsLogger(prefix="T", uid=1, role="miner", jsonl_path=str(tmp_path / "m.jsonl"), flush_interval=0.05)
-    ml.log("m", {"w": 1}, {"loss": 1.5, "xs": [1, 2, 3], "t": torch.tensor([2.0, 4.0]), "flag": True, "name": "x", "none": None},
+    ml = MetricsLogger(prefix="T", uid=1, role="miner", jsonl_path=str(tmp_path / "m.jsonl"), flush_interval=0.05,
+                       config=SimpleNamespace(netuid=3, device="cpu", project="p", _private=1, nested={"a": 1}, nothing=None))
+    ml.log("m", {"w": 1}, {"loss": 1.5, "xs": [1.0, 2, 3.0], "uids": [4, 5, 6], "t": torch.tensor([2.0, 4.0]), "flag": True,
+                           "name": "x", "none": None, "empty": [], "one": torch.tensor(7.0), "count": 3},
            with_system_metrics=True)
+    ml.log("skipped", {}, {"a": 1}, sample_rate=0.0)
     ml.close()
     import json
-    rec = json.loads((tmp_path / "m.jsonl").read_text().splitlines()[0])
-    assert rec["measurement"] == "Tm" and rec["fields"]["xs_mean"] == 2 and rec["fields"]["t_max"] == 4 and rec["tags"]["role"] == "miner"
+    lines = (tmp_path / "m.jsonl").read_text().splitlines()
+    rec = json.loads(lines[0])
+    f, t = rec["fields"], rec["tags"]
+    assert len(lines) == 1 and rec["measurement"] == "Tm"
+    assert (f["xs_mean"], f["xs_min"], f["xs_max"], f["xs_median"]) == (2, 1, 3, 2) and f["t_max"] == 4 and f["one"] == 7
+    assert f["uids"] == "[4, 5, 6]" and f["none"] == 0.0 and f["empty"] == 0.0 and f["flag"] == 1 and f["name"] == "x"
+    assert f["count"] == 3 and isinstance(f["count"], int) and "sys_cpu_usage" in f and "sys_mem_total" in f
+    assert (t["role"], t["uid"], t["prefix"], t["w"], t["config_netuid"], t["config_project"]) == ("miner", "1", "T", "1", "3", "p")
+    assert t["runtime_id"] and t["version"] == tplr.__version__ and "config__private" not in t and "config_nested" not in t
+    assert "config_nothing" not in t
     assert versioned({"a": 1}, "9") == {"v9/a": 1, "latest/a": 1}
     r = NullRun()
     r.log({"a": 1}, step=2)
