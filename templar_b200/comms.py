@@ -46,6 +46,10 @@ from .schemas import Bucket, CommsGetResult
 CF_REGION_NAME = "enam"
 LOCAL_TMP_DIR = os.environ.get("TPLR_LOCAL_STORE", "/tmp/local_store")
 PEERS_FILE_PREFIX = "peers_"
+CPU_COUNT = os.cpu_count() or 4
+CPU_MAX_CONNECTIONS = min(100, max(30, CPU_COUNT * 4))       # connection-pool bound of the object-store clients
+SAFE_BUCKET_RE = re.compile(r"^[a-zA-Z0-9._-]+$")           # bucket names and object keys a node will talk about
+SAFE_KEY_RE = re.compile(r"^[a-zA-Z0-9._/-]+$")
 _WINDOW_RE = re.compile(r"^(?:gradient|debug|aggregator|checkpoint)-(\d+)-")
 
 

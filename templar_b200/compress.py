@@ -30,7 +30,16 @@ __all__ = [
     "TopKCompressor",
     "dct_basis",
     "chunk_size_for",
+    "ShapeT", "Shape4D", "TotK", "IdxT", "QuantParamsT", "ValT",
 ]
+
+# names for the pieces of a payload, as annotations in callers' code use them (src/tplr/compress.py:35-48)
+ShapeT = tuple[int, ...]                        # shape of the dense tensor
+Shape4D = tuple[int, int, int, int]             # (rows of chunks, columns of chunks, chunk height, chunk width)
+TotK = int                                      # elements per chunk
+IdxT = torch.Tensor                             # packed 12-bit indices, uint8
+ValT = torch.Tensor                             # kept values (or their 8-bit codes)
+QuantParamsT = tuple[torch.Tensor, float, int, torch.Tensor, torch.dtype]      # shift, scale, offset, lookup, dtype
 
 
 # --------------------------------------------------------------------------- #

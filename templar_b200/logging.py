@@ -66,12 +66,31 @@ if not logger.handlers:
     logger.propagate = False
 
 
-def trace(msg, *a, **kw):
+def _trace_message(msg, *a, **kw):
     if logger.isEnabledFor(TRACE):
         logger._log(TRACE, msg, a, **kw)
 
 
-logger.trace = trace  # type: ignore[attr-defined]
+logger.trace = _trace_message  # type: ignore[attr-defined]
+
+
+def trace(msg=None, *a, **kw) -> None:
+    """``trace()`` switches the logger to the TRACE level, as ``debug()`` switches it to DEBUG (the call the
+    reference's neurons make for ``--trace``, src/tplr/logging.py:113-146); ``trace("text")`` logs at that level."""
+    if msg is None:
+        logger.setLevel(TRACE)
+    else:
+        _trace_message(msg, *a, **kw)
+
+
+class NoSubtensorWarning(_logging.Filter):
+    """Drops the chain client's repeated "not connected / reconnecting" warnings from a handler."""
+
+    NEEDLES = ("Verify your local subtensor", "subtensor is running", "reconnecting to subtensor")
+
+    def filter(self, record: _logging.LogRecord) -> bool:
+        text = record.getMessage()
+        return not any(n in text for n in self.NEEDLES)
 
 
 def debug() -> None:
@@ -125,4 +144,5 @@ def shutdown_logging() -> None:
         _listener = None
 
 
-__all__ = ["logger", "T", "P", "debug", "trace_on", "log_with_context", "setup_loki_logger", "JsonFormatter"]
+__all__ = ["logger", "T", "P", "debug", "trace", "trace_on", "log_with_context", "setup_loki_logger", "JsonFormatter",
+           "NoSubtensorWarning"]

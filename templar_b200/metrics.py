@@ -31,6 +31,7 @@ DEFAULT_HOST = os.environ.get("INFLUXDB_HOST", "localhost")
 DEFAULT_PORT = int(os.environ.get("INFLUXDB_PORT", 8086))
 DEFAULT_ORG = os.environ.get("INFLUXDB_ORG", "templar")
 DEFAULT_BUCKET = os.environ.get("INFLUXDB_BUCKET", "tplr")
+DEFAULT_DATABASE = DEFAULT_BUCKET          # the same setting under the name the reference gives it
 
 
 def get_system_metrics() -> dict[str, float]:

@@ -18,6 +18,7 @@ from __future__ import annotations
 import asyncio
 import gc
 import math
+import typing
 from collections import defaultdict
 from datetime import datetime, timedelta, timezone
 from types import SimpleNamespace
@@ -33,7 +34,9 @@ from .utils.ranges import phase
 
 __all__ = ["prepare_gradient_dict", "outer_step", "update_peers", "load_checkpoint_with_fallback",
            "handle_checkpoint_catchup", "catchup_with_aggregation_server", "compare_model_with_debug_dict",
-           "check_uid_index_overlap", "determine_slash_egregiousness", "instantiate_slashing_multiplier"]
+           "check_uid_index_overlap", "determine_slash_egregiousness", "instantiate_slashing_multiplier", "NeuronT"]
+
+NeuronT = typing.TypeVar("NeuronT")            # a miner or a validator: what these functions take as ``instance``
 
 
 def _is_dtensor(x) -> bool:

@@ -59,3 +59,27 @@ def test_tplr_is_the_same_package_under_the_reference_name():
     assert Muon is templar_b200.muon.Muon and d.dist_helper is templar_b200.distributed.dist_helper
     assert tplr.initialize_wandb is templar_b200.wandb_ops.initialize_wandb
     assert tplr.MetricsLogger is templar_b200.metrics.MetricsLogger
+
+
+def test_every_public_name_of_the_reference_package_root_resolves():
+    """The reference's root star-imports chain, comms, compress, dataset, neurons, hparams, logging, schemas and
+    metrics (src/tplr/__init__.py:26-35).  Their public top-level names, listed here from those files: a caller's
+    ``tplr.<name>`` keeps resolving.  Omitted on purpose: the InfluxDB fallback token and write-options class of the
+    reference's metrics module (this package takes the token from the environment only)."""
+    names = """
+      ChainManager Comms CF_REGION_NAME LOCAL_TMP_DIR PEERS_FILE_PREFIX CPU_COUNT CPU_MAX_CONNECTIONS SAFE_BUCKET_RE SAFE_KEY_RE
+      ShapeT Shape4D TotK IdxT QuantParamsT ValT pack_12bit_indices unpack_12bit_indices ChunkingTransformer TopKCompressor
+      DatasetLoader SubsetLoader NeuronT prepare_gradient_dict outer_step update_peers load_checkpoint_with_fallback
+      handle_checkpoint_catchup catchup_with_aggregation_server compare_model_with_debug_dict check_uid_index_overlap
+      determine_slash_egregiousness instantiate_slashing_multiplier DEFAULT_HPARAMS create_namespace load_hparams
+      logger T P debug trace log_with_context setup_loki_logger Bucket CommsGetResult MetricsLogger RUNTIME_ID DEFAULT_HOST
+      DEFAULT_PORT DEFAULT_DATABASE DEFAULT_ORG get_gpu_metrics get_system_metrics initialize_wandb SharedShardedDataset
+      EvalSampler MinerSampler DCPCheckpointer muon distributed
+    """.split()
+    import tplr
+
+    missing = [n for n in names if not hasattr(templar_b200, n) or not hasattr(tplr, n)]
+    assert not missing, missing
+    assert templar_b200.SAFE_KEY_RE.match("checkpoints/2.1.28/5/__0_0.distcp") and not templar_b200.SAFE_BUCKET_RE.match("a/b")
+    ns = templar_b200.create_namespace({"topk_compression": 7})
+    assert ns.topk_compression == 7 and hasattr(ns, "blocks_per_window")
