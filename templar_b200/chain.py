@@ -140,6 +140,16 @@ class ChainManager:
                 logger.error(f"Invalid commitment for UID {uid}: {e}")
         return out
 
+    @staticmethod
+    def decode_metadata(encoded_ss58: tuple, metadata: dict, decode_account_id=None) -> tuple[str, str]:
+        """(hotkey address, commitment text) of one entry of the chain's commitment map: the key's first element is the
+        account id, the text sits as a byte tuple under the only key of ``info.fields[0][0]``
+        (reference: src/tplr/chain.py:256-262)."""
+        if decode_account_id is None:
+            from bittensor.core.chain_data import decode_account_id  # optional dependency
+        commitment = metadata["info"]["fields"][0][0]
+        return decode_account_id(encoded_ss58[0]), bytes(commitment[next(iter(commitment.keys()))][0]).decode()
+
     def _query_commitment_map(self, block):
         """Bittensor path: walk the Commitments.CommitmentOf map and key it by uid."""
         from bittensor.core.chain_data import decode_account_id  # optional dependency
@@ -151,9 +161,7 @@ class ChainManager:
         raw = {}
         for key, value in result:
             try:
-                ss58 = decode_account_id(key[0])
-                commitment = value.value["info"]["fields"][0][0]
-                data = bytes(commitment[next(iter(commitment.keys()))][0]).decode()
+                ss58, data = self.decode_metadata(key, value.value, decode_account_id)
             except Exception as e:  # noqa: BLE001
                 logger.error(f"Failed to decode commitment metadata: {e}")
                 continue

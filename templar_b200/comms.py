@@ -195,6 +195,23 @@ class Comms(ChainManager):
         info = await self.store.head(bucket, key)
         return None if info is None else info.size
 
+    async def upload_large_file(self, file_path: str, key: str, bucket: Bucket | None = None) -> None:
+        """Multipart upload of a file, whatever its size (parallel parts, per-part retries, restart when the store
+        forgets the upload; reference src/tplr/comms.py:634-891).  Stores without multipart take it as one object."""
+        bucket = bucket or self.bucket
+        up = getattr(self.store, "upload_large_file", None)
+        if up is None:
+            return await self.store.put_file(bucket, key, file_path)
+        await up(bucket, key, file_path)
+
+    async def download_large_file(self, bucket: Bucket, key: str, file_size: int, temp_file_path: str) -> bool:
+        """Ranged, parallel, resumable download of ``key`` into ``temp_file_path`` (reference src/tplr/comms.py:
+        936-1187); stores without ranged reads fetch the object whole."""
+        down = getattr(self.store, "download_large_file", None)
+        if down is None:
+            return bool(await self.store.get_to_file(bucket, key, temp_file_path))
+        return bool(await down(bucket, key, file_size, temp_file_path))
+
     async def s3_get_object_range(self, bucket: Bucket, key: str, start: int, end: int, timeout: int = 30) -> bytes | None:
         """Bytes ``start..end`` (inclusive) of an object, or None on a miss, a short read or a timeout
         (reference: src/tplr/comms.py:2648-2703)."""

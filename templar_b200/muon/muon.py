@@ -18,21 +18,32 @@ from collections import deque
 import torch
 import torch.distributed as dist
 
-from .newton_schulz import newton_schulz
+from .newton_schulz import newton_schulz, zeropower_via_newtonschulz5
+
+zeropower_via_newtonschulz5_optimized = newton_schulz       # the kernel-backed chain, under the reference's name for it
 
 
-def muon_update(grad, momentum, beta: float = 0.95, nesterov: bool = True, rms_scale: bool = False):
+def apply_momentum(grad, momentum, beta: float, nesterov: bool):
+    """Momentum step in place (``momentum <- lerp(momentum, grad, 1 - beta)``) and the direction to orthogonalise:
+    the Nesterov look-ahead (written into ``grad``) or the momentum itself; 4-D filters flattened to matrices
+    (reference: src/tplr/muon/muon_fsdp2.py:31-36)."""
     momentum.lerp_(grad, 1 - beta)
     update = grad.lerp_(momentum, beta) if nesterov else momentum
     if update.ndim == 4:
         update = update.view(len(update), -1)
-    shape = update.shape
-    update = newton_schulz(update).to(grad.dtype)
-    if rms_scale:
-        update = update * (0.2 * max(shape[-2], shape[-1]) ** 0.5)
-    else:
-        update = update * max(1, shape[-2] / shape[-1]) ** 0.5
     return update
+
+
+def apply_scaling(update, rms_scale: bool = False):
+    """Step-size scaling of an orthogonalised [rows, cols] direction: ``0.2 * sqrt(max(rows, cols))`` (matches the
+    RMS of an Adam step) or ``sqrt(max(1, rows / cols))`` (reference: src/tplr/muon/muon_fsdp2.py:39-47)."""
+    rows, cols = update.shape[-2], update.shape[-1]
+    return update * (0.2 * max(rows, cols) ** 0.5 if rms_scale else max(1, rows / cols) ** 0.5)
+
+
+def muon_update(grad, momentum, beta: float = 0.95, nesterov: bool = True, rms_scale: bool = False):
+    update = apply_momentum(grad, momentum, beta, nesterov)
+    return apply_scaling(newton_schulz(update).to(grad.dtype), rms_scale)
 
 
 def adam_update(grad, buf1, buf2, step, betas, eps):
@@ -127,8 +138,7 @@ class _ShardedWork:
         g = self.group
         grad = self.p.grad.to_local()
         mom = self.state["momentum_buffer"].to_local()
-        mom.lerp_(grad, 1 - g["momentum"])
-        self.local = (grad.lerp_(mom, g["momentum"]) if g["nesterov"] else mom).contiguous()
+        self.local = apply_momentum(grad, mom, g["momentum"], g["nesterov"]).contiguous()
         self.gathered = ([torch.empty_like(self.local) for _ in range(self.world)] if self.rank == self.owner else None)
         self.handle = dist.gather(self.local, self.gathered, dst=dist.get_global_rank(self.pg, self.owner), group=self.pg,
                                   async_op=True)
@@ -140,9 +150,7 @@ class _ShardedWork:
         parts = None
         if self.rank == self.owner:
             full = torch.cat(self.gathered, dim=0)
-            shape = full.shape
-            upd = newton_schulz(full).to(self.local.dtype)
-            upd = upd * (0.2 * max(shape) ** 0.5 if g["rms_scale"] else max(1, shape[-2] / shape[-1]) ** 0.5)
+            upd = apply_scaling(newton_schulz(full).to(self.local.dtype), g["rms_scale"])
             parts = [c.contiguous() for c in upd.chunk(self.world, dim=0)]
         dist.scatter(out, parts, src=dist.get_global_rank(self.pg, self.owner), group=self.pg)
         local_p = self.p.to_local()

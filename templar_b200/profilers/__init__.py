@@ -13,8 +13,12 @@ def _on(name: str) -> bool:
     return os.environ.get("TPLR_ENABLE_PROFILERS", "0").lower() in truthy or os.environ.get(name, "0").lower() in truthy
 
 
-_timer = TimerProfiler("global") if _on("TPLR_ENABLE_TIMER_PROFILER") else DummyTimerProfiler()
-_shard = ShardProfiler("global") if _on("TPLR_ENABLE_SHARD_PROFILER") else DummyShardProfiler()
+ENABLE_PROFILERS = os.environ.get("TPLR_ENABLE_PROFILERS", "0").lower() in ("1", "true", "yes", "on")
+ENABLE_TIMER_PROFILER = _on("TPLR_ENABLE_TIMER_PROFILER")
+ENABLE_SHARD_PROFILER = _on("TPLR_ENABLE_SHARD_PROFILER")
+
+_timer = TimerProfiler("global") if ENABLE_TIMER_PROFILER else DummyTimerProfiler()
+_shard = ShardProfiler("global") if ENABLE_SHARD_PROFILER else DummyShardProfiler()
 
 
 def get_timer_profiler(name: str | None = None):
@@ -28,5 +32,5 @@ def get_shard_profiler(name: str | None = None):
 get_profiler = get_shard_profiler          # the reference's name for the shard profiler's accessor
 
 
-__all__ = ["get_profiler", "TimerProfiler", "ShardProfiler", "DummyTimerProfiler", "DummyShardProfiler", "CudaEventTimer",
+__all__ = ["ENABLE_PROFILERS", "ENABLE_TIMER_PROFILER", "ENABLE_SHARD_PROFILER", "get_profiler", "TimerProfiler", "ShardProfiler", "DummyTimerProfiler", "DummyShardProfiler", "CudaEventTimer",
            "get_timer_profiler", "get_shard_profiler"]

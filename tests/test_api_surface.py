@@ -83,3 +83,28 @@ def test_every_public_name_of_the_reference_package_root_resolves():
     assert templar_b200.SAFE_KEY_RE.match("checkpoints/2.1.28/5/__0_0.distcp") and not templar_b200.SAFE_BUCKET_RE.match("a/b")
     ns = templar_b200.create_namespace({"topk_compression": 7})
     assert ns.topk_compression == 7 and hasattr(ns, "blocks_per_window")
+
+
+def test_methods_and_module_names_callers_of_the_reference_use():
+    from templar_b200 import profilers
+    from templar_b200.muon import muon as muon_mod
+
+    for name in ("upload_large_file", "download_large_file", "s3_get_object_range", "s3_get_object_size", "s3_put_object",
+                 "s3_get_object", "gather", "gather_with_reserve", "get_with_retry", "put", "get", "post_peer_list",
+                 "post_start_window", "get_peer_list", "get_start_window", "check_compressed_indices", "is_miner_active",
+                 "track_active_peers", "get_debug_dict", "weighted_random_sample_no_replacement", "cleanup_local_data",
+                 "cleanup_s3_data", "gradient_timestamp", "get_own_bucket", "get_base_url", "delete_local_directory",
+                 "start_background_tasks"):
+        assert callable(getattr(templar_b200.Comms, name, None)), name
+    assert callable(templar_b200.ChainManager.decode_metadata)
+    for name in ("apply_momentum", "apply_scaling", "adam_update", "zeropower_via_newtonschulz5",
+                 "zeropower_via_newtonschulz5_optimized", "Muon", "SingleDeviceMuonWithAuxAdam"):
+        assert hasattr(muon_mod, name), name
+    for name in ("ENABLE_PROFILERS", "ENABLE_TIMER_PROFILER", "ENABLE_SHARD_PROFILER", "get_timer_profiler", "get_profiler"):
+        assert hasattr(profilers, name), name
+    import torch
+    g, m = torch.ones(4, 2), torch.zeros(4, 2)
+    u = templar_b200.muon.apply_momentum(g, m, 0.5, nesterov=True)
+    assert torch.allclose(m, torch.full((4, 2), 0.5)) and torch.allclose(u, torch.full((4, 2), 0.75))
+    assert torch.allclose(templar_b200.muon.apply_scaling(torch.ones(4, 2)), torch.full((4, 2), 2 ** 0.5))
+    assert torch.allclose(templar_b200.muon.apply_scaling(torch.ones(4, 2), rms_scale=True), torch.full((4, 2), 0.4))

@@ -382,6 +382,38 @@ def test_ranged_read_on_every_transport(net, tmp_path):
     assert run(comms.s3_get_object_range(comms.bucket, "missing", 0, 3)) is None
 
 
+def test_large_file_calls_on_comms_and_chain_metadata_decoding(net, tmp_path, monkeypatch):
+    """Comms.upload_large_file / download_large_file reach the transport's multipart upload and ranged download where it
+    has them and fall back to whole objects where it has not; ChainManager.decode_metadata reads one commitment entry."""
+    store, chain, comms = net
+    c = comms[1]
+    src = tmp_path / "blob.bin"
+    src.write_bytes(os.urandom(9000))
+    run(c.upload_large_file(str(src), "big/blob.bin"))                     # in-memory store: one object
+    assert run(store.get_bytes(c.bucket, "big/blob.bin")) == src.read_bytes()
+    assert run(c.download_large_file(c.bucket, "big/blob.bin", 9000, str(tmp_path / "back.bin")))
+    assert (tmp_path / "back.bin").read_bytes() == src.read_bytes()
+    assert not run(c.download_large_file(c.bucket, "big/none.bin", 1, str(tmp_path / "none.bin")))
+
+    fake = _FakeS3()
+    fake.fail_parts, fake.forget_once = 0, False
+    s3 = S3Store(client_factory=lambda bk: fake, part_size=4000, max_retries=2)
+    c3 = tplr.Comms(wallet=StaticWallet("hotkey-9"), config=SimpleNamespace(netuid=3, device="cpu"),
+                    hparams=SimpleNamespace(topk_compression=4, blocks_per_window=4), uid=9, store=s3, subtensor=chain)
+    run(c3.upload_large_file(str(src), "big/blob.bin"))
+    assert fake.objects["big/blob.bin"] == src.read_bytes() and len(fake.uploads["u0"]) == 3      # three parts
+    ranged = _FakeRangedS3(src.read_bytes())
+    c3.store = S3Store(client_factory=lambda bk: ranged)
+    monkeypatch.setattr(c3.store, "download_plan", lambda size, workers=None: (4000, 2))
+    assert run(c3.download_large_file(c3.bucket, "big/blob.bin", 9000, str(tmp_path / "r.bin")))
+    assert (tmp_path / "r.bin").read_bytes() == src.read_bytes() and sorted(ranged.requests) == [(0, 3999), (4000, 7999), (8000, 8999)]
+
+    text = "x" * 128
+    entry = {"info": {"fields": [[{"Raw128": [tuple(text.encode())]}]]}}
+    got = tplr.ChainManager.decode_metadata((b"\x01" * 32,), entry, decode_account_id=lambda raw: "5F" + raw.hex()[:6])
+    assert got == ("5F010101", text)
+
+
 def test_gather_accepts_quantised_payloads_and_rejects_bad_tables(net):
     store, chain, comms = net
     totalks, xshapes = {"w.": 4096}, {"w.": (2, 2, 64, 64)}
