@@ -38,15 +38,28 @@ from neurons.trainer import Trainer  # noqa: E402
 from templar_b200 import model_factory  # noqa: E402
 from templar_b200.backends.chain import StaticWallet, make_subtensor  # noqa: E402
 from templar_b200.distributed import dist_helper  # noqa: E402
-from templar_b200.metrics import MetricsLogger  # noqa: E402
+from templar_b200.metrics import MetricsLogger, NullMetricsLogger  # noqa: E402,F401
 from templar_b200.wandb_ops import NullRun, initialize_wandb  # noqa: E402
 
 DEFAULT_TASKS = "arc_challenge,arc_easy,openbookqa,winogrande,piqa,hellaswag,mmlu"
 
 
-def compute_bpb(total_nll_nats: float, total_bytes: int) -> float:
+def compute_bpb(total_nll_nats: float, total_bytes: float) -> float:
     """Bits per byte from a summed negative log-likelihood in nats."""
     return total_nll_nats / (math.log(2.0) * total_bytes) if total_bytes > 0 else float("inf")
+
+
+def loss_to_bpb(total_loss_nats: float, total_tokens: int, *, total_bytes: int | None = None,
+                bytes_per_token: float | None = None) -> float:
+    """Bits per byte from a summed cross entropy in nats: exact with the byte count of the evaluated text, estimated
+    with an average number of bytes per token (reference neurons/evaluator.py:120-141)."""
+    if total_tokens <= 0:
+        return float("inf")
+    if total_bytes is not None and total_bytes > 0:
+        return compute_bpb(total_loss_nats, total_bytes)
+    if bytes_per_token is not None and bytes_per_token > 0:
+        return compute_bpb(total_loss_nats, total_tokens * bytes_per_token)
+    raise ValueError("Provide total_bytes or bytes_per_token to compute bpb.")
 
 
 class ModelCache:
@@ -293,6 +306,8 @@ class Evaluator(BaseNode, Trainer):
             if self.is_master:
                 sentinel.unlink(missing_ok=True)
 
+    run_lm_eval_multi_gpu = run_lm_eval              # the reference's name (one child drives all GPUs of the node)
+
     def _run_lm_eval_master(self, model_path: Path, tasks: list[str], window: int, global_step: int,
                             sentinel: Path) -> dict[str, float]:
         out_dir = Path(f"/tmp/eval_{int(time.time())}")
@@ -512,6 +527,9 @@ class Evaluator(BaseNode, Trainer):
         if self.metrics_logger is not None:
             self.metrics_logger.close()
         self.wandb.finish()
+
+
+get_config = Evaluator.evaluator_config
 
 
 def main():

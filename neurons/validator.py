@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import contextlib
 import hashlib
 import os
 import random
@@ -36,7 +37,7 @@ from neurons.miner import _noop_async, common_args, finish_config, load_node_hpa
 from neurons.trainer import Trainer  # noqa: E402
 from templar_b200.backends.chain import StaticWallet, make_subtensor  # noqa: E402
 from templar_b200.distributed import dist_helper  # noqa: E402
-from templar_b200.metrics import MetricsLogger  # noqa: E402
+from templar_b200.metrics import MetricsLogger, NullMetricsLogger  # noqa: E402,F401
 from templar_b200.parallel.window_engine import peer_slice  # noqa: E402
 from templar_b200.utils.ranges import phase  # noqa: E402
 from templar_b200.utils.rating import PlackettLuce  # noqa: E402
@@ -53,6 +54,22 @@ def min_power_normalization(logits: torch.Tensor, power: float = 2.0, epsilon: f
     p = logits ** power
     s = p.sum()
     return p / s if s > epsilon else torch.zeros_like(p)
+
+
+@contextlib.contextmanager
+def timer(name: str, wandb_obj=None, step=None, metrics_logger=None):
+    """Time a phase: debug line, ``validator/<name>`` on the wandb run and a ``timing`` measurement, the last two only
+    with a step to file them under (reference neurons/validator.py:76-87)."""
+    t0 = time.perf_counter()
+    try:
+        yield
+    finally:
+        dt = time.perf_counter() - t0
+        tplr.logger.debug(f"{name} took {dt:.2f}s")
+        if wandb_obj is not None and step is not None:
+            wandb_obj.log({f"validator/{name}": dt}, step=step)
+        if metrics_logger is not None and step is not None:
+            metrics_logger.log(measurement="timing", tags={"window": step}, fields={name: dt})
 
 
 class Validator(BaseNode, Trainer):

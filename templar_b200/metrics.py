@@ -216,3 +216,14 @@ class MetricsLogger:
     def close(self, timeout: float = 5.0) -> None:
         self._stop.set()
         self._thread.join(timeout=timeout)
+
+
+class NullMetricsLogger:
+    """Stand-in with the logger's surface that drops everything: what the ranks other than rank 0 hold."""
+
+    def log(self, *_a, **_k) -> None:
+        return None
+
+    def close(self, *_a, **_k) -> None:
+        return None
+

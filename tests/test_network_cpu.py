@@ -398,6 +398,21 @@ def test_hf_export_matches_model_logits(tmp_path):
 
 def test_small_modules(tmp_path, monkeypatch):
     assert compute_bpb(math.log(2.0) * 80, 10) == pytest.approx(8.0) and math.isinf(compute_bpb(1.0, 0))
+    from neurons.evaluator import loss_to_bpb
+    from neurons.validator import timer
+    from templar_b200.metrics import NullMetricsLogger
+    from templar_b200.wandb_ops import NullRun as _Run
+    assert loss_to_bpb(math.log(2.0) * 80, 40, total_bytes=10) == pytest.approx(8.0)
+    assert loss_to_bpb(math.log(2.0) * 80, 40, bytes_per_token=0.25) == pytest.approx(8.0) and math.isinf(loss_to_bpb(1.0, 0))
+    with pytest.raises(ValueError):
+        loss_to_bpb(1.0, 4)
+    wb, seen = _Run(), []
+    with timer("phase", wb, step=3, metrics_logger=SimpleNamespace(log=lambda **kw: seen.append(kw))):
+        pass
+    with timer("quiet", wb, step=None, metrics_logger=NullMetricsLogger()):
+        pass
+    assert list(wb.history[0][0]) == ["validator/phase"] and wb.history[0][1] == 3 and len(wb.history) == 1
+    assert seen[0]["measurement"] == "timing" and seen[0]["tags"] == {"window": 3} and "phase" in seen[0]["fields"]
     c = ModelCache(tmp_path / "cache", namespace="v")
     assert not c.exists(1) and c.get_path(1) == tmp_path / "cache" / "v" / "window_1"
     for w in (1, 5, 12):
