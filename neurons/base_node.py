@@ -78,6 +78,16 @@ class BaseNode(abc.ABC):
     async def run(self):
         raise NotImplementedError
 
+    def gather_wait_seconds(self) -> float:
+        """How long a gather waits for peers' uploads.  On a network the upload-time window ends the wait; an offline
+        run has no such window, and a peer that skipped a window would otherwise hold everyone for the whole
+        time-out: there the wait is one window long (blocks per window x block time), at least two seconds."""
+        limit = float(getattr(self, "gather_timeout", 90))
+        if getattr(self.config, "local", False):
+            window_s = float(getattr(self.hparams, "blocks_per_window", 7)) * float(getattr(self.config, "block_time", 12.0))
+            limit = min(limit, max(2.0, window_s))
+        return limit
+
     # -- windows ----------------------------------------------------------------------------
     async def wait_until_window(self, target_window: int) -> None:
         evt = self.window_changed

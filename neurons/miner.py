@@ -207,8 +207,7 @@ class Miner(BaseNode, Trainer):
         if self.config.peers is not None:
             self.comms.peers = [u for u in self.config.peers]
         elif self.is_master:
-            await tplr.neurons.update_peers(instance=self, window=self.current_window, peer_start=tplr.T()) \
-                if self.peers_update_window >= 0 else None
+            await tplr.neurons.update_peers(instance=self, window=self.current_window, peer_start=tplr.T())
         # start window (validator-published); offline default: now
         sw = await self.comms.get_start_window(retries=2, retry_delay=0.5) if self.is_master else None
         t = torch.tensor([sw if sw is not None else self.current_window], dtype=torch.long, device=self.device)
@@ -237,7 +236,9 @@ class Miner(BaseNode, Trainer):
         """One full window; returns its timing / loss summary."""
         hp = self.hparams
         t_win = tplr.T()
-        if self.is_master and self.config.peers is None and self.peers_update_window >= 0:
+        if self.is_master and self.config.peers is None:
+            # every window, as the reference does (neurons/miner.py:484-489): the first list a validator publishes has
+            # to be found by a miner that has none yet
             await tplr.neurons.update_peers(instance=self, window=step_window, peer_start=tplr.T())
         await self.maybe_switch_shard(step_window)
         self.sampler.set_window_uid(self.uid, step_window)
@@ -297,7 +298,7 @@ class Miner(BaseNode, Trainer):
             t0 = tplr.T()
             gather_result = await self.comms.gather_with_reserve(
                 my_uid=self.uid, gather_uids=list(self.comms.peers), reserve_uids=list(self.comms.reserve_peers),
-                window=step_window, key="gradient", timeout=self.gather_timeout, device="cpu", local=False,
+                window=step_window, key="gradient", timeout=self.gather_wait_seconds(), device="cpu", local=False,
                 stale_retention=100, totalks=self.totalks, xshapes=self.xshapes, compressor=self.compressor,
                 time_min=None if self.config.local else tmin, time_max=None if self.config.local else tmax,
                 expected_compressed_params=self.expected_compressed_params)

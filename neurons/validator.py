@@ -641,12 +641,15 @@ class Validator(BaseNode, Trainer):
             self.comms.update_peers_with_buckets()
             self.eval_peers = self.comms.eval_peers
             await self.create_and_post_peers()
-            if self.config.peers is None and self.peers_update_window >= 0:
-                await tplr.neurons.update_peers(instance=self, window=self.sync_window, peer_start=tplr.T())
-            elif self.config.peers is not None:
+            if self.config.peers is not None:
                 self.comms.peers = list(self.config.peers)
-            elif not self.comms.peers:
-                self.comms.peers = sorted(int(u) for u in self.comms.active_peers if int(u) != self.uid)[:hp.gather_peer_count]
+            else:
+                # the validator gathers from the list it (or a higher-staked validator) published, like the miners
+                # (reference neurons/validator.py:1366-1373); until a first list is in effect: whoever is active
+                await tplr.neurons.update_peers(instance=self, window=self.sync_window, peer_start=tplr.T())
+                if not self.comms.peers:
+                    self.comms.peers = sorted(int(u) for u in self.comms.active_peers
+                                              if int(u) != self.uid)[:hp.gather_peer_count]
             self.penalize_inactive_peers()
             ts = await self.loop.run_in_executor(None, self.query_block_timestamp, (self.sync_window + 1) * hp.blocks_per_window)
             tmin = datetime.fromtimestamp(ts, tz=timezone.utc) if ts is not None else None
@@ -658,7 +661,7 @@ class Validator(BaseNode, Trainer):
                 t_gather = tplr.T()
                 gather_result = await self.comms.gather_with_reserve(
                     my_uid=self.uid, gather_uids=list(self.comms.peers), reserve_uids=list(self.comms.reserve_peers),
-                    window=self.sync_window, key="gradient", timeout=getattr(self, "gather_timeout", 90), device="cpu",
+                    window=self.sync_window, key="gradient", timeout=self.gather_wait_seconds(), device="cpu",
                     local=False, totalks=self.totalks, xshapes=self.xshapes, compressor=self.compressor, time_min=tmin,
                     time_max=tmax, expected_compressed_params=self.expected_compressed_params)
                 self.log_timing("gather", tplr.T() - t_gather)

@@ -92,6 +92,8 @@ class Comms(ChainManager):
         self.current_window = 0
         self.recent_windows = getattr(self.hparams, "recent_windows", 3)
         self.active_check_interval = getattr(self.hparams, "active_check_interval", 60)
+        # how often the chain's bucket commitments are read again; an offline run with windows of seconds sets it low
+        self.fetch_interval = getattr(self.hparams, "commitment_fetch_interval", self.fetch_interval)
         self.client_semaphore = asyncio.Semaphore(30)
         self.gather_semaphore = asyncio.Semaphore(20)
         self.gather_timeout = 600

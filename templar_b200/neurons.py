@@ -352,8 +352,11 @@ def _outer_step_engine(model, engine, optimizer, gather_result, is_master: bool)
 # --------------------------------------------------------------------------------------- #
 async def update_peers(instance, window: int, peer_start: float) -> None:
     comms, hp = instance.comms, instance.hparams
+    # on a network the list always appears (the validators publish it) and the node waits for it; an offline run may
+    # have no validator at all and must not wait for ever
+    kw = {"retries": 2, "retry_delay": 0.5} if getattr(getattr(instance, "config", None), "local", False) else {}
     if len(comms.peers) == 0:
-        prev = await comms.get_peer_list(fetch_previous=True)
+        prev = await comms.get_peer_list(fetch_previous=True, **kw)
         if prev is not None:
             comms.peers, comms.reserve_peers = prev[0], prev[1]
             logger.info(f"Got previous peer list with {len(prev[0])} peers and update window {prev[2]}")
@@ -362,7 +365,7 @@ async def update_peers(instance, window: int, peer_start: float) -> None:
     due = (instance.next_peers is None and
            instance.peers_update_window + hp.peer_replacement_frequency - window <= hp.peer_list_window_margin)
     if due:
-        res = await comms.get_peer_list()
+        res = await comms.get_peer_list(**kw)
         if res is None:
             logger.info("Unable to get peer list from bucket")
         else:
