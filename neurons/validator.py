@@ -136,6 +136,8 @@ class Validator(BaseNode, Trainer):
         self.idx_similarity_slashing_rate = tplr.neurons.instantiate_slashing_multiplier()
         self.naughty_peers: dict[int, int] = {}
         self.naughty_peer_timeout = 20           # windows a mega-slashed peer stays excluded (reference neurons/validator.py:510-511)
+        _uids = self.metagraph.uids.tolist() if hasattr(self.metagraph.uids, "tolist") else list(self.metagraph.uids)
+        self.current_hotkeys = {int(u): hk for u, hk in zip(_uids, self.metagraph.hotkeys)}      # who owns which slot
         self.peer_eval_history: dict[int, deque] = {}
         self.eval_history_limit = 20
         self.consecutive_negative_count: dict[int, int] = {}
@@ -237,7 +239,7 @@ class Validator(BaseNode, Trainer):
     def should_skip_negative_penalty(self) -> bool:
         """True when the 5th best score of the current window (or the worst, if fewer) is negative:
         the whole window went badly, so nobody is punished for it."""
-        if not self.current_window_scores:
+        if not getattr(self, "current_window_scores", None):
             return False
         ranked = sorted(self.current_window_scores.values(), reverse=True)
         return ranked[min(4, len(ranked) - 1)] < 0
@@ -418,8 +420,22 @@ class Validator(BaseNode, Trainer):
                 self.missing_gradient_history[uid].append(False)
 
     def check_deregistered_uids(self, peers: dict) -> dict:
-        valid = set(int(u) for u in self.comms.metagraph.uids.tolist())
-        return {u: lvl for u, lvl in peers.items() if u in valid}
+        """Drop from ``peers`` (uid -> overlap level, the repeat offenders included) every uid whose hotkey changed
+        since the last look: the slot has a new owner, who must not inherit the old one's punishment - unless the new
+        owner is itself caught copying outright ("mega").  Such a uid also leaves the list of repeat offenders
+        (reference neurons/validator.py:4140-4170)."""
+        mg = self.comms.metagraph
+        uids = mg.uids.tolist() if hasattr(mg.uids, "tolist") else list(mg.uids)
+        latest = {int(u): hk for u, hk in zip(uids, mg.hotkeys)}
+        known = getattr(self, "current_hotkeys", None)
+        if known is None:
+            known = latest                              # first look: nothing to compare with
+        for uid in list(peers.keys()):
+            if latest.get(uid) != known.get(uid) and peers.get(uid) != "mega":
+                self.naughty_peers.pop(uid, None)
+                peers.pop(uid, None)
+        self.current_hotkeys = latest
+        return peers
 
     def slash_from_overlap(self, idx_overlap: dict) -> None:
         peers = {uid: "max" for uid in self.naughty_peers}

@@ -20,6 +20,7 @@ Behavioural parity with the reference (paths are relative to its project root):
 from __future__ import annotations
 
 import math
+import typing
 
 import torch
 
@@ -30,7 +31,7 @@ __all__ = [
     "TopKCompressor",
     "dct_basis",
     "chunk_size_for",
-    "ShapeT", "Shape4D", "TotK", "IdxT", "QuantParamsT", "ValT",
+    "ShapeT", "Shape4D", "TotK", "IdxT", "QuantParamsT", "ValT", "Q",
 ]
 
 # names for the pieces of a payload, as annotations in callers' code use them (src/tplr/compress.py:35-48)
@@ -40,6 +41,7 @@ TotK = int                                      # elements per chunk
 IdxT = torch.Tensor                             # packed 12-bit indices, uint8
 ValT = torch.Tensor                             # kept values (or their 8-bit codes)
 QuantParamsT = tuple[torch.Tensor, float, int, torch.Tensor, torch.dtype]      # shift, scale, offset, lookup, dtype
+Q = typing.TypeVar("Q", typing.Literal[True], typing.Literal[False])           # "quantises" flag of a compressor type
 
 
 # --------------------------------------------------------------------------- #
@@ -228,7 +230,7 @@ def _to_local(x):
     return to_local() if callable(to_local) else x
 
 
-class TopKCompressor:
+class TopKCompressor(typing.Generic[Q]):      # TopKCompressor[Literal[True]] in annotations: a quantising compressor
     """Per-chunk magnitude top-k with 12-bit packed indices and optional 8-bit values.
 
     ``compress`` returns ``(idx_u8, val, xshape, totalk)`` or, when quantisation is on,

@@ -39,8 +39,20 @@ __all__ = ["prepare_gradient_dict", "outer_step", "update_peers", "load_checkpoi
 NeuronT = typing.TypeVar("NeuronT")            # a miner or a validator: what these functions take as ``instance``
 
 
+def _engine_of(model):
+    """The window engine attached to ``model`` (``model._window_engine``), or None.  Looked up in the instance
+    dictionary: an object that answers every attribute (a mock standing in for a model) has no engine."""
+    return getattr(model, "__dict__", {}).get("_window_engine")
+
+
+try:
+    from torch.distributed.tensor import DTensor as _DTensor
+except Exception:  # noqa: BLE001  (a torch build without the distributed tensor package)
+    _DTensor = None
+
+
 def _is_dtensor(x) -> bool:
-    return x is not None and hasattr(x, "full_tensor") and hasattr(x, "to_local")
+    return _DTensor is not None and isinstance(x, _DTensor)
 
 
 def _dist_on() -> bool:
@@ -82,7 +94,7 @@ def prepare_gradient_dict(miner, step_window: int, null_round: bool = False):
     Error feedback: ``e <- momentum_decay * e + grad`` (``e <- 0`` on a null round), the payload is
     ``compress(encode(e))`` and ``e <- e - decode(decompress(payload))``.
     """
-    engine = getattr(miner.model, "_window_engine", None)
+    engine = _engine_of(miner.model)
     if engine is not None and getattr(miner, "use_engine", True):
         return _prepare_gradient_dict_engine(miner, engine, step_window, null_round)
 
@@ -196,7 +208,7 @@ def outer_step(model: nn.Module, optimizer, *, gather_result, transformer, compr
     """Aggregate the gathered payloads (median-norm clip, mean over contributors, inverse
     transform) and apply them parameter by parameter with ``optimizer`` (plain SGD in the
     reference).  Returns the gradient fingerprint on the source rank."""
-    engine = getattr(model, "_window_engine", None)
+    engine = _engine_of(model)
     if engine is not None and getattr(model, "_use_engine_outer_step", True):
         return _outer_step_engine(model, engine, optimizer, gather_result, is_master)
 
@@ -354,7 +366,7 @@ async def update_peers(instance, window: int, peer_start: float) -> None:
     comms, hp = instance.comms, instance.hparams
     # on a network the list always appears (the validators publish it) and the node waits for it; an offline run may
     # have no validator at all and must not wait for ever
-    kw = {"retries": 2, "retry_delay": 0.5} if getattr(getattr(instance, "config", None), "local", False) else {}
+    kw = {"retries": 2, "retry_delay": 0.5} if getattr(getattr(instance, "config", None), "local", False) is True else {}
     if len(comms.peers) == 0:
         prev = await comms.get_peer_list(fetch_previous=True, **kw)
         if prev is not None:
@@ -583,7 +595,7 @@ def param_samples(model: nn.Module, lo: int, hi: int) -> dict[str, torch.Tensor]
     """``{name: flatten()[lo:hi]}`` of every parameter with at least ``hi`` elements: the slices that nodes publish
     as debug information and compare for the sync score.  Read from the module tree, or, when the engine holds the
     parameters as shards only, from the elements the ranks collected at the last window boundary."""
-    engine = getattr(model, "_window_engine", None)
+    engine = _engine_of(model)
     if engine is not None and getattr(engine, "fsdp", False):
         return engine.param_samples(lo, hi)
     out = {}
@@ -607,7 +619,7 @@ async def compare_model_with_debug_dict(model: nn.Module, debug_dict: dict, lear
     max_diff = max_steps = 0.0
     ratios = []
     lo, hi = index_range
-    engine = getattr(model, "_window_engine", None)
+    engine = _engine_of(model)
     sharded = param_samples(model, lo, hi) if engine is not None and getattr(engine, "fsdp", False) else None
     for name, p in _named_parameters(model):
         ref = debug_dict.get(name + "_debug")
@@ -696,6 +708,12 @@ async def check_uid_index_overlap(neuron, gather_result, window: int, *, overlap
             unpacked.append(unpack_12bit_indices(ii.to(device), vv.shape))
         idx = torch.stack(unpacked, 0)
         k = idx.shape[-1]
+        if idx.numel() == 0:
+            # nothing was kept for this tensor: the pairs count as compared, with nothing in common
+            for i in range(n):
+                for j in range(i + 1, n):
+                    acc[(i, j)][1] += 0.0
+            continue
         idx = idx.reshape(n, -1, k)
         C = idx.shape[1]
         width = int(idx.max().item()) + 1

@@ -64,6 +64,7 @@ class MinerSampler(_WindowSampler):
 
 class EvalSampler(_WindowSampler):
     _subset_cache: dict[tuple[int, int], np.ndarray] = {}
+    _cached_indices = _subset_cache        # the same dict under the name callers of the reference clear between windows
 
     def __init__(self, dataset, uid, window, *, steps_per_window, micro_bs, batch_size, validation_bs,
                  rank: int = 0, world_size: int = 1):
