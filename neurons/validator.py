@@ -600,9 +600,24 @@ class Validator(BaseNode, Trainer):
             tplr.logger.warning(f"UID {uid}: sample digest mismatch (the miner did not train on its assigned data)")
         return ok
 
-    def compute_peer_val_norms(self, n_peers: int) -> torch.Tensor:
-        """Per-tensor median of the gathered peers' value norms (the clip reference for single-peer applies)."""
-        return self.engine.compute_peer_norms(n_peers).clone()
+    def compute_peer_val_norms(self, gather_result):
+        """Per-tensor median of the gathered peers' value norms: the clip reference for single-peer applies.
+        With the number of peers staged in the engine: the engine's vector, one entry per tensor, computed on the
+        device.  With a gather result: ``{"<name>vals": median norm}`` from its (dequantised) values, tensor by
+        tensor (reference neurons/validator.py:3740-3770)."""
+        if isinstance(gather_result, int):
+            return self.engine.compute_peer_norms(gather_result).clone()
+        state_dict = getattr(gather_result, "state_dict", None)
+        if not state_dict:
+            raise ValueError("Must have gather_result.state_dict to compute norms")
+        out = {}
+        for n, p in self.model.named_parameters():
+            vals = getattr(state_dict, n + "vals", None)
+            if vals is None:
+                continue
+            vals = self.compressor.maybe_dequantize_values(vals, getattr(state_dict, n + "quant_params", None), p.device)
+            out[n + "vals"] = torch.median(torch.stack([torch.norm(v.float(), p=2) for v in vals]).to(p.device))
+        return out
 
     async def upload_gather_results(self, gather_result) -> None:
         if not self.is_master or gather_result is None:

@@ -488,7 +488,7 @@ def test_small_modules(tmp_path, monkeypatch):
         run(aboom())
     sb = tp.get_stats("boom")
     assert (sb["count"], sb["errors"], len(sb["timings"]), sb["function"]) == (12, 12, 10, "boom") and sb["avg"] == sb["mean"]
-    assert tp.get_stats("aboom")["errors"] == 1 and tp.get_stats("f")["errors"] == 0 and tp.get_stats("nope") == {}
+    assert tp.get_stats("aboom")["errors"] == 1 and tp.get_stats("f")["errors"] == 0 and "error" in tp.get_stats("nope")
     tp.start_timer("region"); assert tp.end_timer("region") >= 0 and tp.end_timer("region") == 0.0
     tp.log_summary()
     tp.reset("boom")
@@ -497,9 +497,11 @@ def test_small_modules(tmp_path, monkeypatch):
     assert tp.get_stats() == {}
     assert DummyTimerProfiler().profile("x")(f)() == 3
     sp = ShardProfiler("s", slow_read_s=10)
-    sp.end_read(sp.start_read("a.npy", {"idx": 1}))
+    sp.end_read(sp.start_read("a.npy", {"idx": 1, "num_rows": 9}), "a.npy", num_row_groups=3, rows_per_group=3)
     sp.export_data(str(tmp_path / "rep.json"))
-    assert sp.get_stats("a.npy")["reads"] == 1 and (tmp_path / "rep.json").exists()
+    rec = sp.get_stats("a.npy")
+    assert (rec["reads"], rec["num_rows"], rec["row_groups"], rec["timings"][0]["idx"]) == (1, 9, 3, 1)
+    assert (tmp_path / "rep.json").exists() and sp.get_stats("never") == {}
     m = PlackettLuce()
     a, b = m.rate([[m.rating()], [m.rating()]], scores=[1.0, 0.0])
     assert a[0].mu > 25 > b[0].mu and a[0].sigma < 25 / 3
