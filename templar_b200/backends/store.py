@@ -232,6 +232,27 @@ class PeerMemoryStore(ObjectStore):
 
 
 # --------------------------------------------------------------------------------------- #
+def download_params(file_size: int, custom_workers: str | None = None) -> dict:
+    """Chunk size and worker count of a ranged download by object size (reference src/tplr/comms.py:1251-1285):
+    above 100 GB 512 MB chunks and 8-32 workers, above 10 GB 256 MB and 8-16, below that 64 MB and 6-8; a valid
+    ``custom_workers`` replaces the worker count; never more workers than chunks."""
+    cpus = os.cpu_count() or 4
+    gb = file_size / 1024 ** 3
+    if gb > 100:
+        chunk, workers = 512 * 1024 ** 2, min(32, max(8, cpus))
+    elif gb > 10:
+        chunk, workers = 256 * 1024 ** 2, min(16, max(8, cpus))
+    else:
+        chunk, workers = 64 * 1024 ** 2, min(8, max(6, 2 * cpus))
+    if custom_workers:
+        try:
+            workers = max(1, int(custom_workers))
+        except ValueError:
+            pass
+    chunks = max(1, -(-file_size // chunk))
+    return {"chunk_size": chunk, "max_workers": min(workers, chunks), "total_chunks": chunks, "file_size_gb": gb}
+
+
 def _is_named(e: BaseException, *names: str) -> bool:
     return any(c.__name__ in names for c in type(e).__mro__)
 
@@ -434,12 +455,10 @@ class S3Store(ObjectStore):
         return True
 
     def download_plan(self, size: int, workers: int | None = None) -> tuple[int, int]:
-        """(chunk_size, n_workers) for a ranged download: 64 MB..1 GB chunks, workers bounded by
-        ``DOWNLOAD_MAX_WORKERS`` (default: twice the CPU count, at most 32)."""
-        max_workers = workers or int(os.getenv("DOWNLOAD_MAX_WORKERS", min(32, 2 * (os.cpu_count() or 8))))
-        chunk = min(max(64 * 1024 * 1024, size // max(max_workers * 4, 1)), 1024 * 1024 * 1024)
-        n_chunks = max(1, -(-size // chunk))
-        return chunk, max(1, min(max_workers, n_chunks))
+        """(chunk_size, n_workers) for a ranged download (see :func:`download_params`); the worker count can be
+        fixed with ``workers`` or the ``DOWNLOAD_MAX_WORKERS`` variable."""
+        p = download_params(size, str(workers) if workers else os.getenv("DOWNLOAD_MAX_WORKERS"))
+        return p["chunk_size"], p["max_workers"]
 
     async def download_large_file(self, bucket, key, size: int, path: str) -> bool:
         """Parallel ranged GETs written at their offsets; chunks finished by an earlier, interrupted

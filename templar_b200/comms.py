@@ -36,7 +36,7 @@ from typing import Any, Literal
 import torch
 
 from . import __version__
-from .backends.store import LocalFSStore, MemoryStore, ObjectStore, S3Store
+from .backends.store import LocalFSStore, MemoryStore, ObjectStore, S3Store, download_params
 from .chain import ChainManager
 from .compress import TopKCompressor, unpack_12bit_indices
 from .config import BUCKET_SECRETS
@@ -205,6 +205,8 @@ class Comms(ChainManager):
         if up is None:
             return await self.store.put_file(bucket, key, file_path)
         await up(bucket, key, file_path)
+
+    _calc_download_params = staticmethod(download_params)      # the plan of a ranged download, under the reference's name
 
     async def download_large_file(self, bucket: Bucket, key: str, file_size: int, temp_file_path: str) -> bool:
         """Ranged, parallel, resumable download of ``key`` into ``temp_file_path`` (reference src/tplr/comms.py:
