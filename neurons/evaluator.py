@@ -161,7 +161,7 @@ class Evaluator(BaseNode, Trainer):
         self.wallet = StaticWallet(self.config.wallet_hotkey or self.metagraph.hotkeys[-1])
         self.uid = self.metagraph.hotkeys.index(self.wallet.hotkey.ss58_address)
         self.version = self.config.version or tplr.__version__
-        self.model = model_factory.initialize_torchtitan_model(self.hparams, role="evaluator", device=str(self.device),
+        self.model = model_factory.initialize_torchtitan_model(hparams=self.hparams, role="evaluator", device=str(self.device),
                                                                world_size=self.world_size)
         self.tokenizer = self.hparams.tokenizer
         self.comms = tplr.Comms(wallet=self.wallet, config=self.config, hparams=self.hparams, uid=self.uid, store=store,

@@ -103,9 +103,9 @@ class Trainer:
     def init_model(self, validator: bool = False, meta: bool = False):
         role = "validator" if validator else "miner"
         if meta:
-            self.model = model_factory.create_meta_model(self.hparams, role=role, world_size=self.world_size)
+            self.model = model_factory.create_meta_model(hparams=self.hparams, role=role, world_size=self.world_size)
         else:
-            self.model = model_factory.initialize_torchtitan_model(self.hparams, role=role, device=str(self.device),
+            self.model = model_factory.initialize_torchtitan_model(hparams=self.hparams, role=role, device=str(self.device),
                                                                    world_size=self.world_size)
         self.expected_compressed_params = self.get_expected_params()
         self.tokenizer = self.hparams.tokenizer

@@ -181,8 +181,8 @@ class Validator(BaseNode, Trainer):
                 "weights": self.weights.cpu(),
                 "openskill_ratings": {int(u): {"mu": float(r.mu), "sigma": float(r.sigma), "ordinal": float(r.ordinal())}
                                       for u, r in self.openskill_ratings.items()},
-                "naughty_peers": dict(self.naughty_peers),
-                "consecutive_negative_count": dict(self.consecutive_negative_count)}
+                "naughty_peers": dict(getattr(self, "naughty_peers", {}) or {}),
+                "consecutive_negative_count": dict(getattr(self, "consecutive_negative_count", {}) or {})}
 
     async def save_state(self):
         """Scores, ratings and the step counter to ``state_path``: rank 0 only (the other ranks hold no scores of their
@@ -200,7 +200,8 @@ class Validator(BaseNode, Trainer):
                 os.remove(tmp)
 
     def load_state(self):
-        if not os.path.exists(self.state_path):
+        """Rank 0 only, like ``save_state``: the scores live there (reference neurons/validator.py:3813-3887)."""
+        if not getattr(self, "is_master", True) or not os.path.exists(self.state_path):
             return
         try:
             st = torch.load(self.state_path, map_location="cpu", weights_only=True)    # tensors, numbers and dicts only
