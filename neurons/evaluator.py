@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import contextlib
 import json
 import math
 import os
@@ -106,6 +107,28 @@ class ModelCache:
         return drop
 
 
+@contextlib.contextmanager
+def pause_ddp_for_lm_eval(tag: str, stop=None):
+    """The hand-over of a node's GPUs to a child process that only rank 0 starts.  All ranks arrive at a barrier;
+    inside the block rank 0 runs the child and touches the sentinel file the block yields when it is done; on the
+    way out the other ranks wait for that file (or for ``stop``, the node's shutdown event), all ranks meet at a
+    second barrier and rank 0 removes the file: the sentinel of one evaluation is never seen by the next
+    (reference: neurons/evaluator.py:76-106)."""
+    if dist_helper.is_distributed():
+        dist_helper.safe_barrier(f"pause_ddp_enter_{tag}", dist_helper.local_rank)
+    sentinel = Path(f"/tmp/tplr_eval_done_{tag}")
+    try:
+        yield sentinel
+    finally:
+        if not dist_helper.is_master:
+            while not sentinel.exists() and not (stop is not None and stop.is_set()):
+                time.sleep(0.25)
+        if dist_helper.is_distributed():
+            dist_helper.safe_barrier(f"pause_ddp_exit_{tag}", dist_helper.local_rank)
+        if dist_helper.is_master:
+            sentinel.unlink(missing_ok=True)
+
+
 def release_device_memory(label: str = "") -> None:
     """Collect garbage and give cached device memory back to the driver, so that a child process (the task
     harness with its own inference engine) finds the GPU empty."""
@@ -161,28 +184,47 @@ class Evaluator(BaseNode, Trainer):
         self.wallet = StaticWallet(self.config.wallet_hotkey or self.metagraph.hotkeys[-1])
         self.uid = self.metagraph.hotkeys.index(self.wallet.hotkey.ss58_address)
         self.version = self.config.version or tplr.__version__
-        self.model = model_factory.initialize_torchtitan_model(hparams=self.hparams, role="evaluator", device=str(self.device),
-                                                               world_size=self.world_size)
+        self._initialize_or_load_model()
         self.tokenizer = self.hparams.tokenizer
         self.comms = tplr.Comms(wallet=self.wallet, config=self.config, hparams=self.hparams, uid=self.uid, store=store,
                                 subtensor=self.subtensor)
         self.ckpt = tplr.DCPCheckpointer(self.comms, uid=self.uid, version=self.version, repo_root=".")
-        self.cache = ModelCache(self.config.cache_dir, namespace=self.version)
+        self.model_cache = ModelCache(self.config.cache_dir, namespace=self.version)
         self.metrics_logger = MetricsLogger(prefix="E", uid=self.uid, config=self.config, role="evaluator",
                                             group="evaluator", job_type="eval") if self.is_master else None
         self.wandb = initialize_wandb("E", self.uid, self.config, "evaluator", "eval") if self.is_master else NullRun()
         self.tasks = [t.strip() for t in str(self.config.tasks or "").split(",") if t.strip()]
-        self.last_eval_window = -1
+        # the options that steer the loop, as attributes (a driver or a test may change them on a live node)
+        self.from_window, self.to_window = self.config.backfill_start, self.config.backfill_end
+        self.no_follow, self.force_reval = bool(self.config.no_follow), bool(self.config.force_reval)
+        self.eval_interval = self.config.eval_interval
         self.eval_counter = 0
         self.evaluated_windows: set[int] = set()
+        self.last_discovered_window: int | None = None
         self.baseline_evaluated = False
         self.start_window: int | None = None
+
+    def _initialize_or_load_model(self) -> None:
+        """The model with fresh weights on this node's device (a checkpoint is loaded into it per evaluated window)."""
+        self.model = model_factory.initialize_torchtitan_model(hparams=self.hparams, role="evaluator", device=str(self.device),
+                                                               world_size=self.world_size)
+
+    @property
+    def cache(self) -> ModelCache:
+        return self.model_cache
+
+    @property
+    def last_eval_window(self) -> int:
+        return max(self.evaluated_windows, default=-1)
 
     # -- checkpoints --------------------------------------------------------------------------
     async def check_latest_checkpoint(self) -> int | None:
         """Newest window whose checkpoint is complete and not evaluated yet."""
         w = await self.ckpt._discover_latest(prefer_highest_staked=True)
-        if w is None or w <= self.last_eval_window:
+        if w is None:
+            return None
+        self.last_discovered_window = w
+        if w in self.evaluated_windows and not self.force_reval:
             return None
         return w if await self.ckpt.check_checkpoint_exists(window=w) else None
 
@@ -289,22 +331,10 @@ class Evaluator(BaseNode, Trainer):
 
     def run_lm_eval(self, model_path: Path, tasks: list[str], window: int, global_step: int) -> dict[str, float]:
         """Rank 0 runs the harness in a clean (non-torchrun) environment; other ranks wait on a sentinel."""
-        sentinel = Path(f"/tmp/tplr_lm_eval_done_{self.uid}_{window}")
-        if dist_helper.is_distributed():
-            # all ranks arrive before rank 0 starts the child, and leave together after it: the sentinel of one
-            # evaluation cannot be seen by the next (reference: neurons/evaluator.py:76-106)
-            dist_helper.safe_barrier(f"lm_eval_enter_{window}", self.local_rank)
-        try:
+        with pause_ddp_for_lm_eval(f"{getattr(self, 'uid', 0)}_{window}", stop=getattr(self, "stop_event", None)) as sentinel:
             if not self.is_master:
-                while not sentinel.exists() and not self.stop_event.is_set():
-                    time.sleep(0.25)
                 return {}
             return self._run_lm_eval_master(model_path, tasks, window, global_step, sentinel)
-        finally:
-            if dist_helper.is_distributed():
-                dist_helper.safe_barrier(f"lm_eval_exit_{window}", self.local_rank)
-            if self.is_master:
-                sentinel.unlink(missing_ok=True)
 
     run_lm_eval_multi_gpu = run_lm_eval              # the reference's name (one child drives all GPUs of the node)
 
@@ -382,7 +412,7 @@ class Evaluator(BaseNode, Trainer):
         """Evaluate the checkpoint of ``window`` (or, as the baseline, the freshly initialised weights).  The global
         step comes from the checkpoint's sidecar; an older checkpoint without one gets ``window - start_window``
         (reference: neurons/evaluator.py:871-985).  None when the checkpoint could not be loaded."""
-        if window in self.evaluated_windows and not self.config.force_reval:
+        if window in self.evaluated_windows and not self.force_reval:
             tplr.logger.info(f"[eval] window {window} already evaluated")
             return {"window": window, "skipped": True}
         global_step = 0
@@ -417,7 +447,6 @@ class Evaluator(BaseNode, Trainer):
             finally:
                 if on_gpu:
                     self.model.to(self.device)
-        self.last_eval_window = max(self.last_eval_window, window)
         self.evaluated_windows.add(window)
         self.eval_counter += 1
         if self.metrics_logger is not None:
@@ -438,19 +467,33 @@ class Evaluator(BaseNode, Trainer):
         dist_helper.broadcast(t, src=0)
         return [None if v < 0 else v for v in t.tolist()]
 
+    def _stopping(self) -> bool:
+        ev = getattr(self, "stop_event", None)
+        return ev is not None and ev.is_set()
+
+    async def _resolve_to_window(self) -> int | None:
+        """Upper end of a backfill that was given none: the newest complete checkpoint, as rank 0 sees it."""
+        latest = None
+        if self.is_master:
+            try:
+                w = await self.ckpt._discover_latest(prefer_highest_staked=True)
+                if w is not None and await self.ckpt.check_checkpoint_exists(window=w):
+                    latest = w
+            except Exception as e:  # noqa: BLE001
+                tplr.logger.error(f"[eval] resolving the newest checkpoint failed: {e}")
+        return self._from_master(latest)[0]
+
     async def _backfill_range(self) -> tuple[int, int] | None:
         """Window range of a backfill run; an open end is resolved from the network (start window / newest
         complete checkpoint) by rank 0.  A reversed range is put in order."""
-        lo, hi = self.config.backfill_start, self.config.backfill_end
+        lo, hi = self.from_window, self.to_window
         if lo is None and hi is None:
             return None
         if self.is_master:
             if lo is None:
                 lo = self.start_window if self.start_window is not None else await self.comms.get_start_window()
-            if hi is None:
-                hi = await self.ckpt._discover_latest(prefer_highest_staked=True)
-                if hi is not None and not await self.ckpt.check_checkpoint_exists(window=hi):
-                    hi = None
+        if hi is None:
+            hi = await self._resolve_to_window()           # every rank takes part in its broadcast
         lo, hi = self._from_master(lo, hi)
         if lo is None or hi is None:
             tplr.logger.warning("[eval] backfill range could not be resolved")
@@ -465,7 +508,7 @@ class Evaluator(BaseNode, Trainer):
             return out
         tplr.logger.info(f"[eval] backfilling windows {rng[0]}..{rng[1]} of version {self.version}")
         for w in range(rng[0], rng[1] + 1):
-            if self.stop_event.is_set():
+            if self._stopping():
                 break
             ready = (await self.ckpt.check_checkpoint_exists(window=w)) if self.is_master else None
             if not self._from_master(int(bool(ready)))[0]:
@@ -493,9 +536,9 @@ class Evaluator(BaseNode, Trainer):
                 sw = int(self.current_window)
                 tplr.logger.warning(f"[eval] no start window published; counting steps from window {sw}")
         self.start_window = self._from_master(sw)[0]
-        backfill = self.config.backfill_start is not None or self.config.backfill_end is not None
+        backfill = self.from_window is not None or self.to_window is not None
         first = True
-        while not self.stop_event.is_set():
+        while not self._stopping():
             if not first:
                 self.comms.commitments = await self.comms.get_commitments()
             w = self._from_master((await self.check_latest_checkpoint()) if self.is_master else None)[0]
@@ -510,12 +553,12 @@ class Evaluator(BaseNode, Trainer):
             if first and backfill:
                 await self.backfill_range()
             first = False
-            if self.config.no_follow or (self.config.max_windows and self.eval_counter >= self.config.max_windows):
+            if self.no_follow or (getattr(self.config, "max_windows", 0) and self.eval_counter >= self.config.max_windows):
                 break
-            if backfill and self.config.backfill_start is not None and self.config.backfill_end is not None:
+            if backfill and self.from_window is not None and self.to_window is not None:
                 break                                     # a closed range is a one-shot job
             try:
-                await asyncio.wait_for(self.stop_event.wait(), timeout=self.config.eval_interval)
+                await asyncio.wait_for(self.stop_event.wait(), timeout=self.eval_interval)
             except asyncio.TimeoutError:
                 pass
 

@@ -42,7 +42,7 @@ def main():
         await e.run()
         first = {"evaluated": sorted(e.evaluated_windows), "counter": e.eval_counter, "start_window": e.start_window,
                  "baseline": e.baseline_evaluated}
-        e.config.backfill_start, e.config.backfill_end, e.config.force_reval = 6, 4, True       # reversed on purpose
+        e.from_window, e.to_window, e.force_reval = 6, 4, True       # reversed on purpose
         done = await e.backfill_range()
         return first, done
     first, done = asyncio.run(go())

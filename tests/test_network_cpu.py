@@ -661,7 +661,7 @@ def test_evaluator_baseline_then_checkpoints_with_a_task_harness(cwd_tmp, monkey
         assert again["skipped"] and e.eval_counter == 2
         # failing child: custom metrics still there, no task scores, export still pruned to one window
         monkeypatch.setenv("FAKE_HARNESS_FAIL", "1")
-        e.config.force_reval = True
+        e.force_reval = True
         rep = await e.evaluate_window(5)
         assert rep["tasks"] == {} and rep["perplexity"] > 1 and rep["global_step"] == 2
         e.metrics_logger.close()
