@@ -63,6 +63,9 @@ def loss_to_bpb(total_loss_nats: float, total_tokens: int, *, total_bytes: int |
     raise ValueError("Provide total_bytes or bytes_per_token to compute bpb.")
 
 
+_loss_to_bpb = loss_to_bpb
+
+
 class ModelCache:
     """HF exports of evaluated windows, one directory per window under ``base_dir/<version>`` (the same window
     number can exist under several versions; reference: neurons/evaluator.py:144-210)."""
@@ -76,10 +79,10 @@ class ModelCache:
         return self.base_dir / f"window_{window}"
 
     def exists(self, window: int) -> bool:
-        """A finished export: the config, a weight file (whole or sharded) and the completion mark."""
+        """A usable export: the config and a weight file (whole or sharded), as the reference's cache checks."""
         p = self.get_path(window)
         has_weights = any((p / f).exists() for f in self.WEIGHT_FILES) or any(p.glob("model-*.safetensors"))
-        return (p / "config.json").exists() and has_weights and (p / "cache_meta.json").exists()
+        return (p / "config.json").exists() and has_weights
 
     def mark(self, window: int) -> None:
         p = self.get_path(window)
@@ -448,7 +451,7 @@ class Evaluator(BaseNode, Trainer):
                 if on_gpu:
                     self.model.to(self.device)
         self.evaluated_windows.add(window)
-        self.eval_counter += 1
+        self.eval_counter = getattr(self, "eval_counter", 0) + 1
         if self.metrics_logger is not None:
             self.metrics_logger.log("custom_evaluation", tags={"window": window, "global_step": global_step,
                                                                "baseline": int(is_baseline)}, fields=custom)

@@ -420,7 +420,6 @@ def test_small_modules(tmp_path, monkeypatch):
         (c.get_path(w) / "config.json").write_text("{}")
     (c.get_path(1) / "model.safetensors").write_bytes(b"x")
     (c.get_path(5) / "model-00001-of-00002.safetensors").write_bytes(b"x")
-    assert not c.exists(1)                                  # not marked complete yet
     c.mark(1); c.mark(5); c.mark(12)
     assert c.exists(1) and c.exists(5) and not c.exists(12) and not c.exists(2)      # 12 has no weight file
     (c.base_dir / "window_old").mkdir()                                         # not a window directory: left alone
