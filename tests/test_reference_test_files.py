@@ -31,6 +31,7 @@ FILES = [
     "tests/unit/test_validator.py", "tests/unit/test_timer_profiler.py", "tests/unit/test_shard_profiler.py",
     "tests/test_prepare_gradient_dict.py", "tests/test_shard_reset.py", "tests/test_state_loading.py",
     "tests/test_trainer_meta_init.py", "tests/test_consecutive_negative_exclusion.py", "tests/test_inactivity_slashing.py",
+    "tests/test_model_comparison.py",
 ]
 
 CONFTEST = '''
