@@ -427,12 +427,16 @@ class Validator(BaseNode, Trainer):
         (reference neurons/validator.py:4140-4170)."""
         mg = self.comms.metagraph
         uids = mg.uids.tolist() if hasattr(mg.uids, "tolist") else list(mg.uids)
-        latest = {int(u): hk for u, hk in zip(uids, mg.hotkeys)}
+        hotkeys = getattr(mg, "hotkeys", None) or [None] * len(uids)
+        latest = {int(u): hk for u, hk in zip(uids, hotkeys)}
         known = getattr(self, "current_hotkeys", None)
         if known is None:
             known = latest                              # first look: nothing to compare with
         for uid in list(peers.keys()):
-            if latest.get(uid) != known.get(uid) and peers.get(uid) != "mega":
+            if int(uid) not in latest:                  # not a slot of this subnet (any more): nothing to punish
+                self.naughty_peers.pop(uid, None)
+                peers.pop(uid, None)
+            elif latest.get(uid) != known.get(uid) and peers.get(uid) != "mega":
                 self.naughty_peers.pop(uid, None)
                 peers.pop(uid, None)
         self.current_hotkeys = latest
