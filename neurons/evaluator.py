@@ -72,8 +72,9 @@ class ModelCache:
 
     WEIGHT_FILES = ("model.safetensors", "pytorch_model.bin")
 
-    def __init__(self, base_dir: str | Path, namespace: str | None = None):
+    def __init__(self, base_dir: str | Path = Path("models/cache"), namespace: str | None = None):
         self.base_dir = Path(base_dir) / namespace if namespace else Path(base_dir)
+        self.base_dir.mkdir(parents=True, exist_ok=True)
 
     def get_path(self, window: int) -> Path:
         return self.base_dir / f"window_{window}"
