@@ -688,6 +688,40 @@ def test_offline_evaluator_without_any_validator_evaluates_the_untrained_weights
     run(go())
 
 
+def test_miner_without_fixed_peers_finds_the_published_list_and_does_not_wait_for_ever(cwd_tmp):
+    """A miner started without --peers asks for the validators' peer list every window: with no validator in sight it
+    gives up after a bounded number of tries (offline) and runs a null round; once a list is published it adopts it
+    when the list comes into effect.  Offline, a gather waits one window at most, not the network time-out."""
+    async def go():
+        store, chain = MemoryStore(), StaticChain(n=4, manual=True)
+        m = _node(Miner, Miner.miner_config, ["--uid", "2", "--block-time", "0.5"], store, chain)
+        m.loop = asyncio.get_running_loop()
+        m.comms.commitments = await m.comms.get_commitments()
+        await m.dataset_manager.initialize_datasets(0)
+        m.set_dataloader()
+        assert m.gather_wait_seconds() == 2.0                    # 4 blocks x 0.5 s, not the 90 s of a network run
+        m.config.local = False
+        assert m.gather_wait_seconds() == 90.0
+        m.config.local = True
+        m.current_window = m.comms.current_window = 5
+        t0 = time.time()
+        res = await asyncio.wait_for(m.run_window(5), timeout=60)                    # nobody publishes a list
+        assert m.comms.peers == [] and res["gather_success_rate"] == 0.0 and time.time() - t0 < 30
+        # uid 0 (highest stake) commits its bucket and publishes a list that takes effect at window 7
+        v = tplr.Comms(wallet=tplr.backends.chain.StaticWallet("hotkey-0"), config=m.config, hparams=m.hparams, uid=0,
+                       store=store, subtensor=chain)
+        v.try_commit(v.wallet, v.bucket)
+        await v.post_peer_list(peers=[2], reserve_peers=[], first_effective_window=7, sync_window=6, initial_selection=True)
+        m.comms.commitments = await m.comms.get_commitments()
+        m.current_window = m.comms.current_window = 6
+        await m.run_window(6)
+        assert m.next_peers == [2] and m.comms.peers == [] and m.peers_update_window == 7
+        m.current_window = m.comms.current_window = 7
+        res = await m.run_window(7)
+        assert m.comms.peers == [2] and m.next_peers is None and res["gather_success_rate"] == 1.0
+    run(go())
+
+
 def test_miner_runs_null_rounds_until_the_validators_can_know_it(cwd_tmp):
     """Outside local mode the first validator_offset + peer_list_window_margin windows after the start window, and
     windows without gather peers, are null rounds: no inner update is kept and nothing is fed into the error feedback."""
