@@ -4,4 +4,4 @@ from .muon import Muon, SingleDeviceMuonWithAuxAdam, adam_update, apply_momentum
 from .newton_schulz import newton_schulz, newton_schulz_triton, zeropower_via_newtonschulz5
 
 __all__ = ["Muon", "SingleDeviceMuonWithAuxAdam", "newton_schulz", "newton_schulz_triton",
-           "zeropower_via_newtonschulz5", "muon_update", "adam_update"]
+           "zeropower_via_newtonschulz5", "muon_update", "adam_update", "apply_momentum", "apply_scaling"]
