@@ -518,7 +518,7 @@ class Evaluator(BaseNode, Trainer):
             if not self._from_master(int(bool(ready)))[0]:
                 continue
             rep = await self.evaluate_window(w)
-            if rep is not None and not rep.get("skipped"):
+            if rep and not (isinstance(rep, dict) and rep.get("skipped")):
                 out.append(w)
             dist_helper.safe_barrier(f"backfill_win_{w}", self.local_rank)
         return out
@@ -557,23 +557,31 @@ class Evaluator(BaseNode, Trainer):
             if first and backfill:
                 await self.backfill_range()
             first = False
-            if self.no_follow or (getattr(self.config, "max_windows", 0) and self.eval_counter >= self.config.max_windows):
+            limit = getattr(self.config, "max_windows", 0)
+            if self.no_follow or (isinstance(limit, int) and limit > 0 and getattr(self, "eval_counter", 0) >= limit):
                 break
             if backfill and self.from_window is not None and self.to_window is not None:
                 break                                     # a closed range is a one-shot job
+            ev = getattr(self, "stop_event", None)
+            if ev is None:
+                await asyncio.sleep(self.eval_interval)
+                continue
             try:
-                await asyncio.wait_for(self.stop_event.wait(), timeout=self.eval_interval)
+                await asyncio.wait_for(ev.wait(), timeout=self.eval_interval)
             except asyncio.TimeoutError:
                 pass
 
     def cleanup(self) -> None:
         """Release the model's device memory and the loggers at shutdown."""
-        if getattr(self, "model", None) is not None and self.device.type == "cuda":
+        if getattr(self, "model", None) is not None:
             self.model.to("cpu")
             release_device_memory("shutdown")
-        if self.metrics_logger is not None:
-            self.metrics_logger.close()
-        self.wandb.finish()
+        ml = getattr(self, "metrics_logger", None)
+        if ml is not None and hasattr(ml, "close"):
+            ml.close()
+        wb = getattr(self, "wandb", None)
+        if wb is not None:
+            wb.finish()
 
 
 get_config = Evaluator.evaluator_config
