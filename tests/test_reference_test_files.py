@@ -10,8 +10,9 @@ Listed here are the files that pass in full.  Not listed, with the reason: test_
 test_checkpoint_fallback / test_config (import botocore, bittensor or the reference's ``src`` package),
 test_model_factory / test_model (import torchtitan), test_dcp_checkpoint / test_comms / test_download_large_file
 (drive the reference's S3 client objects, which this package replaces by the ObjectStore transports; the
-size-to-plan cases of test_download_large_file pass), test_evaluator (asserts on the reference's return types:
-``evaluate_window`` answers with a report here, with a bool there).
+size-to-plan cases of test_download_large_file pass), test_evaluator (23 of its 31 cases pass; the others assert
+on the reference's return types: ``evaluate_window`` answers with a report here and with a bool there, and
+``run_custom_eval`` is a coroutine here).
 """
 
 import os
