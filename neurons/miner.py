@@ -46,7 +46,9 @@ def common_args(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--trace", action="store_true")
     parser.add_argument("--store-gathers", action="store_true")
     parser.add_argument("--test", action="store_true", help="use every uid of the metagraph as a peer")
-    parser.add_argument("--local", action="store_true", help="toy model / local storage run")
+    # "--offline" is the same switch under a name that torch.distributed.run's own parser does not claim: behind
+    # torchrun, "--local" is rejected as an ambiguous prefix of its --local-addr / --local-ranks-filter options
+    parser.add_argument("--local", "--offline", dest="local", action="store_true", help="toy model / local storage run")
     parser.add_argument("--profile-iters", type=int, default=0)
     parser.add_argument("--profile-dir", type=str, default="./log/profiler")
     parser.add_argument("--hparams-dir", type=str, default=os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "hparams"))

@@ -592,6 +592,8 @@ def test_evaluator_cli_spellings_and_dataset_path_evaluation(cwd_tmp):
     for k in ("eval_interval", "backfill_start", "backfill_end", "no_follow", "force_reval", "custom_eval_path", "cache_dir", "batch_size"):
         assert getattr(a, k) == getattr(b, k), k
     assert (a.backfill_start, a.backfill_end, a.no_follow, a.force_reval, a.batch_size) == (3, 4, True, True, 2)
+    # "--offline" is "--local" under a name that a torchrun command line accepts in front of the script's own options
+    assert Miner.miner_config(["--offline", "--device", "cpu"]).local and not Miner.miner_config(["--device", "cpu"]).local
 
     async def go():
         store, chain = MemoryStore(), StaticChain(n=4, manual=True)
