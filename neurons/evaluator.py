@@ -1,7 +1,7 @@
 """Evaluator: follows the published checkpoints and reports perplexity / bits-per-byte and
 (where a harness is installed) downstream-task scores.
 
-    torchrun --standalone --nproc-per-node 2 neurons/evaluator.py --device cuda [--local]
+    torchrun --standalone --nproc-per-node 2 neurons/evaluator.py --device cuda [--offline]
 
 Flow (reference: neurons/evaluator.py:1113-1222): read the start window → find the newest complete
 checkpoint (``_LATEST.json`` pointer or listing, completeness gate; rank 0 decides, the others follow) →

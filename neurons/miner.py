@@ -1,7 +1,7 @@
 """Miner: trains for a window, publishes a compressed pseudo-gradient, gathers its peers'
 gradients and applies the outer step.
 
-    torchrun --standalone --nproc-per-node 8 neurons/miner.py --device cuda [--local] [--static-chain]
+    torchrun --standalone --nproc-per-node 8 neurons/miner.py --device cuda [--offline]
 
 Window flow (reference: neurons/miner.py:366-984):
 update peers → snapshot parameters → inner steps → pseudo-gradient + error feedback + compression

@@ -2,7 +2,7 @@
 change their individual gradients cause, maintains ratings / weights, publishes peer lists, the
 start window, aggregated gradients, debug slices and DCP checkpoints.
 
-    torchrun --standalone --nproc-per-node 4 neurons/validator.py --device cuda [--local]
+    torchrun --standalone --nproc-per-node 4 neurons/validator.py --device cuda [--offline]
 
 Behavioural parity with the reference's neurons/validator.py (state tensors of length 256, OpenSkill
 Plackett–Luce ratings, binary moving average, sync score, slashing ladders for missing / invalid
